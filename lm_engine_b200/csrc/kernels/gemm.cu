@@ -1,0 +1,447 @@
+// bf16 GEMM on the 5th-generation tensor cores:  C[M,N] = sum_k A(m,k) * B(n,k)   (fp32 accumulate)
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0        TMA producer   (cp.async.bulk.tensor, per-CTA loads, 128-byte swizzle, STAGES-deep ring)
+//   warp 1        MMA issuer     (one elected thread issues tcgen05.mma 128 x BN x 16; accumulators live in TMEM,
+//                                 two accumulator buffers so the epilogue of tile i overlaps the main loop of i+1)
+//   warps 2..5    epilogue       (tcgen05.ld -> registers -> fused epilogue -> global)
+//
+// Either operand may be K-major (row-major [rows, K]) or MN-major (stored [K, rows], i.e. the "transposed"
+// operand of dgrad / wgrad) - the tensor core reads both straight from shared memory, so no transposes are ever
+// materialised:   forward  y = x W^T : A = x (K-major), B = W (K-major)
+//                 dgrad    dx = dy W : A = dy (K-major), B = W (MN-major)
+//                 wgrad    dW = dy^T x: A = dy (MN-major), B = x (MN-major)
+//
+// Fused epilogues (runtime flags): + bias[n], + residual[m,n], C += acc (gradient accumulation, bf16 or fp32 C),
+// and SwiGLU on interleaved columns: out[m, j] = acc[m, 2j+1] * silu(acc[m, 2j]) with optional store of the
+// pre-activation (the layout the MLP's fused gate/up projection uses).
+#include "common.cuh"
+#include "../lme_api.h"
+
+#include <mutex>
+#include <stdio.h>
+
+namespace lme {
+
+static constexpr int BM = 128;
+static constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+static constexpr int UMMA_K = 16;
+
+struct GemmArgs {
+    int M, N, K;
+    void* C;
+    long long ldc;
+    const __nv_bfloat16* bias;
+    const __nv_bfloat16* residual;
+    long long ldr;
+    __nv_bfloat16* preact;
+    long long ldp;
+    int flags;
+    int tiles_m, tiles_n, group_m;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
+    // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base address
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const GemmArgs& p, int& mb, int& nb) {
+    int per_group = p.group_m * p.tiles_n;
+    int g = tile / per_group;
+    int first_m = g * p.group_m;
+    int gsz = min(p.tiles_m - first_m, p.group_m);
+    int in = tile - g * per_group;
+    mb = first_m + in % gsz;
+    nb = in / gsz;
+}
+
+// Fused epilogue for 32 consecutive accumulator columns of one output row (held by one thread).
+__device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row, int col0, const GemmArgs& p,
+                                               bool out_f32, bool accumulate, bool swiglu) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        const int ncols = min(32, p.N - col0);  // N % 8 == 0 is enforced on the host
+        if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                if (i < ncols) {
+                    uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + i);
+                    float2 f;
+                    f = unpack_bf16x2(b.x); v[i] += f.x; v[i + 1] += f.y;
+                    f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+                    f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+                    f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+                }
+            }
+        }
+        if (swiglu) {
+            if (p.preact != nullptr) {
+                __nv_bfloat16* pp = p.preact + static_cast<long long>(row) * p.ldp + col0;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    if (i < ncols) {
+                        uint4 o;
+                        o.x = pack_bf16x2(v[i], v[i + 1]); o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                        o.z = pack_bf16x2(v[i + 4], v[i + 5]); o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                        *reinterpret_cast<uint4*>(pp + i) = o;
+                    }
+                }
+            }
+            // interleaved (gate, up) pairs -> 16 outputs per 32 accumulator columns
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) +
+                                 static_cast<long long>(row) * p.ldc + (col0 >> 1);
+#pragma unroll
+            for (int i = 0; i < 32; i += 16) {
+                if (i < ncols) {
+                    float o8[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        // the pre-activation is rounded to bf16 first so that the result equals
+                        // the unfused path (GEMM output in bf16, then the activation in fp32)
+                        float g = __bfloat162float(__float2bfloat16_rn(v[i + 2 * j]));
+                        float u = __bfloat162float(__float2bfloat16_rn(v[i + 2 * j + 1]));
+                        o8[j] = u * silu_f(g);
+                    }
+                    uint4 o;
+                    o.x = pack_bf16x2(o8[0], o8[1]); o.y = pack_bf16x2(o8[2], o8[3]);
+                    o.z = pack_bf16x2(o8[4], o8[5]); o.w = pack_bf16x2(o8[6], o8[7]);
+                    *reinterpret_cast<uint4*>(out + (i >> 1)) = o;
+                }
+            }
+            return;
+        }
+        if (p.residual != nullptr) {
+            const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                if (i < ncols) {
+                    uint4 b = *reinterpret_cast<const uint4*>(rp + i);
+                    float2 f;
+                    f = unpack_bf16x2(b.x); v[i] += f.x; v[i + 1] += f.y;
+                    f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+                    f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+                    f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+                }
+            }
+        }
+        if (out_f32) {
+            float* out = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                if (i < ncols) {
+                    float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    if (accumulate) {
+                        float4 old = *reinterpret_cast<const float4*>(out + i);
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    *reinterpret_cast<float4*>(out + i) = o;
+                }
+            }
+        } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) +
+                                 static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                if (i < ncols) {
+                    if (accumulate) {
+                        uint4 b = *reinterpret_cast<const uint4*>(out + i);
+                        float2 f;
+                        f = unpack_bf16x2(b.x); v[i] += f.x; v[i + 1] += f.y;
+                        f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+                        f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+                        f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+                    }
+                    uint4 o;
+                    o.x = pack_bf16x2(v[i], v[i + 1]); o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                    o.z = pack_bf16x2(v[i + 4], v[i + 5]); o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                    *reinterpret_cast<uint4*>(out + i) = o;
+                }
+            }
+        }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs p) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::TILES_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.K + BK - 1) / BK;
+    constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
+                                   : (2 * BN <= 256) ? 256 : 512;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tfull_bar[a], 1);
+            mbar_init(&tempty_bar[a], 4);  // one arrival per epilogue warp
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int mb, nb;
+                tile_coords(tile, p, mb, nb);
+                const int m0 = mb * BM, n0 = nb * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1, 100 + s)) { ok = false; break; }
+                    uint8_t* sa = smem + s * L::STAGE_BYTES;
+                    uint8_t* sb = sa + L::A_BYTES;
+                    mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)
+                            tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[s], m0 + c * 64, k0);
+                    } else {
+                        tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, k0);
+                    } else {
+                        tma_load_2d(sb, &tmB, &full_bar[s], k0, n0);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, BM, BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+                const int acc = tcount & 1;
+                const uint32_t aph = (tcount >> 1) & 1;
+                if (!mbar_wait(&tempty_bar[acc], aph ^ 1, 200 + acc)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full_bar[s], ph, 300 + s)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // K-major: step 16 elements (32 bytes) inside the swizzled 128-byte row.
+                        // MN-major: step 16 rows of 128 bytes.
+                        const uint64_t da = A_MN ? make_smem_desc_sw128(sa + kk * (UMMA_K * 128), BK * 128, 1024)
+                                                 : make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * (UMMA_K * 128), BK * 128, 1024)
+                                                 : make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+                        umma_bf16(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);  // frees the smem slot once these MMAs have read it
+                }
+                if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        uint32_t tcount = 0;
+        bool ok = true;
+        const bool out_f32 = p.flags & LME_GEMM_OUT_F32;
+        const bool accumulate = p.flags & LME_GEMM_ACCUMULATE;
+        const bool swiglu = p.flags & LME_GEMM_SWIGLU;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            int mb, nb;
+            tile_coords(tile, p, mb, nb);
+            const int acc = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            if (!mbar_wait(&tfull_bar[acc], aph, 400 + acc)) { ok = false; break; }
+            tc_fence_after();
+            const int row = mb * BM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = nb * BN + c * 32;
+                if (row_ok && col0 < p.N) epilogue_store(r, row, col0, p, out_f32, accumulate, swiglu);
+                __syncwarp();
+            }
+            // accumulator buffer may be overwritten by the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+    }
+
+    // ---------------------------------------------------------------- tear-down
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ----------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(f);
+    });
+    return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements,
+// box = [box_inner x box_outer], 128-byte swizzle (box_inner must be 64).
+int make_tmap_bf16_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return LME_ERR_DRIVER;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        fprintf(stderr, "lme: cuTensorMapEncodeTiled failed (CUresult %d): ptr=%p inner=%llu outer=%llu ld=%llu box=%ux%u\n",
+                static_cast<int>(r), ptr, static_cast<unsigned long long>(inner),
+                static_cast<unsigned long long>(outer), static_cast<unsigned long long>(ld), box_inner, box_outer);
+        return LME_ERR_TMAP;
+    }
+    return LME_OK;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return g_num_sms;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p, int max_ctas,
+                       cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+            return LME_ERR_LAUNCH;
+        configured = true;
+    }
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.N + BN - 1) / BN;
+    p.group_m = 8;
+    int tiles = p.tiles_m * p.tiles_n;
+    int grid = tiles < max_ctas ? tiles : max_ctas;
+    kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, p);
+    return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+}
+
+}  // namespace lme
+
+using namespace lme;
+
+extern "C" int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const void* B, int b_mn_major,
+                             long long ldb, void* C, long long ldc, int M, int N, int K, int flags,
+                             const void* bias, const void* residual, long long ldr, void* preact, long long ldp,
+                             int max_ctas, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return LME_OK;
+    if ((N % 8) || (lda % 8) || (ldb % 8) || (ldc % 4)) return LME_ERR_SHAPE;
+    if ((flags & LME_GEMM_SWIGLU) && (N % 16)) return LME_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc;
+    // K-major operand [rows, K]: inner = K, box 64 x rows_per_tile.  MN-major operand [K, rows]: inner = rows,
+    // box 64 x BK (one 64-wide chunk per copy).
+    rc = a_mn_major ? make_tmap_bf16_2d(&ta, A, M, K, lda, 64, BK) : make_tmap_bf16_2d(&ta, A, K, M, lda, 64, BM);
+    if (rc) return rc;
+    rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK) : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
+    if (rc) return rc;
+    GemmArgs p;
+    p.M = M; p.N = N; p.K = K;
+    p.C = C; p.ldc = ldc;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+    p.preact = static_cast<__nv_bfloat16*>(preact); p.ldp = ldp;
+    p.flags = flags;
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define LME_DISPATCH(BN_, ST_)                                                          \
+    do {                                                                                \
+        if (a_mn_major && b_mn_major) return launch_gemm<BN_, ST_, true, true>(ta, tb, p, max_ctas, st);   \
+        if (a_mn_major) return launch_gemm<BN_, ST_, true, false>(ta, tb, p, max_ctas, st);                \
+        if (b_mn_major) return launch_gemm<BN_, ST_, false, true>(ta, tb, p, max_ctas, st);                \
+        return launch_gemm<BN_, ST_, false, false>(ta, tb, p, max_ctas, st);                               \
+    } while (0)
+    if (BN == 128) LME_DISPATCH(128, 6);
+    LME_DISPATCH(256, 4);
+#undef LME_DISPATCH
+}
+
+extern "C" int lme_read_status(unsigned int* out8, int clear) {
+    unsigned int h[8];
+    if (cudaMemcpyFromSymbol(h, lme_status, sizeof(h)) != cudaSuccess) return LME_ERR_LAUNCH;
+    for (int i = 0; i < 8; ++i) out8[i] = h[i];
+    if (clear) {
+        unsigned int z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (cudaMemcpyToSymbol(lme_status, z, sizeof(z)) != cudaSuccess) return LME_ERR_LAUNCH;
+    }
+    return LME_OK;
+}

@@ -1,0 +1,60 @@
+// C ABI of liblme_cuda.so.  Every entry point takes raw device pointers and a cudaStream_t (as void*), returns
+// LME_OK or a negative error code, never allocates device memory unless stated, and never synchronises.
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LME_OK 0
+#define LME_ERR_SHAPE (-1)
+#define LME_ERR_ALIGN (-2)
+#define LME_ERR_TMAP (-3)
+#define LME_ERR_LAUNCH (-4)
+#define LME_ERR_DRIVER (-5)
+#define LME_ERR_TOO_LARGE (-6)
+
+// lme_gemm_bf16 flags
+#define LME_GEMM_OUT_F32 1
+#define LME_GEMM_ACCUMULATE 2
+#define LME_GEMM_SWIGLU 4
+
+// C[M,N] (+)= A x B^T (+ bias) (+ residual); operands K-major ([rows, K]) or MN-major ([K, rows]).
+// ld* are row pitches in elements.  With LME_GEMM_SWIGLU, C is [M, N/2] and `preact` (optional) gets [M, N].
+int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const void* B, int b_mn_major, long long ldb,
+                  void* C, long long ldc, int M, int N, int K, int flags, const void* bias, const void* residual,
+                  long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
+
+// Copies the 8-word device status block to the host (synchronising copy); optionally clears it.
+int lme_read_status(unsigned int* out8, int clear);
+
+// ---- bandwidth-bound block kernels (bf16 activations, fp32 math) ----
+// y = rmsnorm(x (+ residual)) * w; h_out (optional) receives x + residual; rstd (optional) the per-row 1/rms.
+int lme_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out, float* rstd, int T,
+                    int H, float eps, void* stream);
+int lme_rmsnorm_bwd_partial_rows(int T);
+// dx = d rmsnorm / d h  (+ dres); dw (fp32, optional accumulate) via the fp32 scratch dw_partial
+// [lme_rmsnorm_bwd_partial_rows(T), H].
+int lme_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres, void* dx,
+                    float* dw_partial, float* dw, int dw_accumulate, int T, int H, void* stream);
+// x [T, 2I] with (gate, up) interleaved -> y [T, I] = up * silu(gate)
+int lme_swiglu_fwd(const void* x, void* y, long long T, long long I, void* stream);
+int lme_swiglu_bwd(const void* x, const void* dy, void* dx, long long T, long long I, void* stream);
+// fused QKV split + NeoX rotary embedding (inverse = 1: backward, packs dq/dk/dv into dqkv)
+int lme_qkv_rope(void* qkv, void* q, void* k, void* v, const float* cos_t, const float* sin_t, const int* pos,
+                 int T, int S, int Hkv, int G, int D, int rope_dim, int inverse, void* stream);
+// cross entropy over a vocabulary slice [v0, v0+V): row statistics, then in-place gradient
+int lme_ce_stats(const void* logits, long long ld, const long long* labels, float* row_max, float* row_sum,
+                 float* tgt_logit, int T, int V, int v0, void* stream);
+// gradient scale = scale * (*scale_dev if scale_dev != NULL)
+int lme_ce_grad(void* logits, long long ld, const long long* labels, const float* lse, int T, int V, int v0,
+                float scale, const float* scale_dev, long long ignore_index, void* stream);
+// torch.optim.AdamW step on a flat fp32 shard (+ refresh of the bf16 compute copy); step counts from 1
+int lme_adamw(float* p, float* m, float* v, const void* g, int g_is_bf16, void* p_lp, long long n, float lr,
+              float b1, float b2, float eps, float wd, int step, const float* gscale, void* stream);
+#define LME_SUMSQ_MAX_PARTIALS 1184
+int lme_sumsq(const void* x, int is_bf16, long long n, float* partials, float* out, int accumulate, void* stream);
+int lme_clip_coef(const float* sumsq, float max_norm, float* norm_out, float* coef_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

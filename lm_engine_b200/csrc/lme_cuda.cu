@@ -1,0 +1,4 @@
+// The single translation unit of liblme_cuda.so: every kernel file is included here so that the device status
+// word and the helpers are shared without relocatable device code.
+#include "kernels/gemm.cu"
+#include "kernels/elementwise.cu"

@@ -1,0 +1,160 @@
+"""bf16 GEMM on tcgen05 tensor cores with fused epilogues, and the ``linear`` autograd op built on it.
+
+``gemm(a, b)`` computes ``C[M, N] = sum_k A(m, k) * B(n, k)``.  Each operand is either *K-major* (a row-major
+``[rows, K]`` tensor) or *MN-major* (a row-major ``[K, rows]`` tensor, flag ``a_mn`` / ``b_mn``) - the tensor core
+consumes both layouts directly from shared memory, so the backward GEMMs of a linear layer never materialise a
+transpose:
+
+==========  =======================  ======================
+ forward     ``y  = x  @ W.T``        ``gemm(x, W)``
+ dgrad       ``dx = dy @ W``          ``gemm(dy, W, b_mn=True)``
+ wgrad       ``dW = dy.T @ x``        ``gemm(dy, x, a_mn=True, b_mn=True)``
+==========  =======================  ======================
+
+Plays the role of ``F.linear`` / QuACK ``gemm``/``gemm_act``/``gemm_gated`` in the reference
+(lm_engine/modeling_utils/linear/base.py:17-49, lm_engine/modeling_utils/quack.py:19-132).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise ValueError("gemm operands must be 2-D")
+    if t.stride(1) != 1 or t.stride(0) < t.size(1) or t.stride(0) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=False, bias=None,
+                   residual=None, swiglu=False, preact=None):
+    """PyTorch statement of :func:`gemm` (CPU path and numerical oracle)."""
+    A = a.t() if a_mn else a
+    B = b.t() if b_mn else b
+    out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    acc = A.float() @ B.float().t()
+    if bias is not None:
+        acc = acc + bias.float()
+    if swiglu:
+        pre = acc.to(a.dtype)
+        if preact is not None:
+            preact.copy_(pre)
+        pre = pre.float()
+        res = (pre[:, 1::2] * torch.nn.functional.silu(pre[:, 0::2])).to(out_dtype)
+    else:
+        if residual is not None:
+            acc = acc + residual.float()
+        if accumulate:
+            acc = acc + out.float()
+        res = acc.to(out_dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    accumulate: bool = False,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    swiglu: bool = False,
+    preact: torch.Tensor | None = None,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    if not (a.is_cuda and a.dtype == torch.bfloat16):
+        return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
+                              bias=bias, residual=residual, swiglu=swiglu, preact=preact)
+    a = _rowmajor(a)
+    b = _rowmajor(b)
+    if b.dtype != torch.bfloat16:
+        raise TypeError("gemm: both operands must be bf16")
+    K, M = (a.size(0), a.size(1)) if a_mn else (a.size(1), a.size(0))
+    Kb, N = (b.size(0), b.size(1)) if b_mn else (b.size(1), b.size(0))
+    if K != Kb:
+        raise ValueError(f"gemm: contraction mismatch {K} vs {Kb}")
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype or torch.bfloat16, device=a.device)
+    elif out.stride(1) != 1 or out.shape != (M, n_out):
+        raise ValueError("gemm: out must be a row-major [M, N] tensor")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("gemm: out must be bf16 or fp32")
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= _lib.GEMM_OUT_F32
+    if accumulate:
+        flags |= _lib.GEMM_ACCUMULATE
+    if swiglu:
+        flags |= _lib.GEMM_SWIGLU
+        if preact is not None and (preact.shape != (M, N) or preact.stride(1) != 1):
+            raise ValueError("gemm: preact must be row-major [M, N]")
+    if residual is not None:
+        if residual.shape != (M, N) or residual.stride(1) != 1 or residual.dtype != torch.bfloat16:
+            raise ValueError("gemm: residual must be a row-major bf16 [M, N] tensor")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
+        raise ValueError("gemm: bias must be a contiguous bf16 [N] tensor")
+    rc = _lib.cuda_lib().lme_gemm_bf16(
+        a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0),
+        M, N, K, flags, _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+        _lib.ptr(preact), preact.stride(0) if preact is not None else 0, max_ctas, _lib.stream_ptr(),
+    )
+    _lib.check(rc, f"lme_gemm_bf16 M={M} N={N} K={K}")
+    _lib.count_launch()
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T (+ b) (+ residual).  The weight gradient is accumulated straight into ``weight.main_grad`` by the
+    GEMM epilogue when that buffer exists (gradient accumulation fused into wgrad), else returned to autograd."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        r2 = residual.reshape(-1, weight.size(0)) if residual is not None else None
+        y = gemm(x2, weight, bias=bias, residual=r2)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.has_residual = residual is not None
+        ctx.in_shape = shape
+        return y.view(*shape[:-1], weight.size(0))
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.size(-1))
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                weight.grad_added_to_main_grad = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0, dtype=torch.float32).to(dy.dtype)
+        if ctx.has_residual and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, dw, db, dres
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``F.linear`` with an optional fused residual add; tcgen05 GEMMs on CUDA bf16, PyTorch elsewhere."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        return _Linear.apply(x, weight, bias, residual)
+    y = torch.nn.functional.linear(x, weight, bias)
+    return y if residual is None else y + residual

@@ -1,0 +1,102 @@
+"""Micro-benchmarks of the hand-written kernels against their roofline.
+
+    python -m lm_engine_b200.ops.microbench [--json out.json] [--quick]
+
+Timing: CUDA events on the launching stream, >= 3 warm-up launches, operands rotated through a pool larger than
+the 126 MB L2 so every timed launch reads cold data.  GEMM throughput is reported next to ``torch.matmul`` (cuBLAS)
+on the same operands and as a fraction of the measured bf16 peak when ``MEASURED_PEAKS.json`` is present.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import _lib, gemm
+
+
+def _peaks() -> dict:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def _time(fn, n_pool: int, iters: int = 10, warmup: int = 3) -> float:
+    for i in range(warmup):
+        fn(i % n_pool)
+    torch.cuda.synchronize()
+    start = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    end = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        start[i].record()
+        fn(i % n_pool)
+        end[i].record()
+    torch.cuda.synchronize()
+    times = sorted(s.elapsed_time(e) for s, e in zip(start, end))
+    return times[len(times) // 2] * 1e-3
+
+
+def bench_gemm(M, N, K, a_mn=False, b_mn=False, **kw):
+    dev = "cuda"
+    bytes_per = 2 * (M * K + N * K + M * N)
+    n_pool = max(2, min(8, int(300e6 // bytes_per) + 1))
+    As = [torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16) for _ in range(n_pool)]
+    Bs = [torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16) for _ in range(n_pool)]
+    out = torch.empty((M, N // 2 if kw.get("swiglu") else N), device=dev, dtype=torch.bfloat16)
+    t_ours = _time(lambda i: gemm(As[i], Bs[i], a_mn=a_mn, b_mn=b_mn, out=out, **kw), n_pool)
+
+    def ref(i):
+        A = As[i].t() if a_mn else As[i]
+        B = Bs[i] if b_mn else Bs[i].t()
+        torch.matmul(A, B)
+
+    t_ref = _time(ref, n_pool)
+    fl = 2.0 * M * N * K
+    return {"M": M, "N": N, "K": K, "a_mn": a_mn, "b_mn": b_mn, "epilogue": ",".join(sorted(kw)) or "none",
+            "ms": t_ours * 1e3, "tflops": fl / t_ours / 1e12, "cublas_ms": t_ref * 1e3,
+            "cublas_tflops": fl / t_ref / 1e12}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    peaks = _peaks()
+    T = 8192
+    shapes = [
+        ("qkv fwd", T, 6144, 4096, False, False, {}),
+        ("attn-out fwd", T, 4096, 4096, False, False, {}),
+        ("fc1+swiglu fwd", T, 28672, 4096, False, False, {"swiglu": True}),
+        ("fc2 fwd", T, 4096, 14336, False, False, {}),
+        ("fc1 dgrad", T, 4096, 28672, False, True, {}),
+        ("fc1 wgrad", 28672, 4096, T, True, True, {}),
+        ("fc2 wgrad", 4096, 14336, T, True, True, {}),
+        ("lm-head fwd", T, 128256, 4096, False, False, {}),
+    ]
+    if args.quick:
+        shapes = shapes[:3]
+    rows = []
+    for name, M, N, K, a_mn, b_mn, kw in shapes:
+        r = bench_gemm(M, N, K, a_mn, b_mn, **kw)
+        r["name"] = name
+        r["frac_of_peak"] = r["tflops"] / peaks["bf16_tflops"]
+        rows.append(r)
+        print(f"{name:16s} M={M:6d} N={N:6d} K={K:6d}  ours {r['ms']:8.3f} ms {r['tflops']:7.1f} TF "
+              f"({100 * r['frac_of_peak']:5.1f}% of {peaks['source']} peak)   cuBLAS {r['cublas_ms']:8.3f} ms "
+              f"{r['cublas_tflops']:7.1f} TF", flush=True)
+    st = _lib.read_status()
+    print("device status:", st)
+    if args.json:
+        json.dump({"peaks": peaks, "gemm": rows, "status": st}, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()
