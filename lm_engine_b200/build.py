@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 # --use_fast_math would change exp/div accuracy of the fp32 math; the kernels call the fast intrinsics explicitly
 NVCC_FLAGS.remove("--use_fast_math")
 
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-shared", "-fopenmp"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-shared"]
 
 
 def _nvcc() -> str:

@@ -158,3 +158,46 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         return _Linear.apply(x, weight, bias, residual)
     y = torch.nn.functional.linear(x, weight, bias)
     return y if residual is None else y + residual
+
+
+class _LinearSwiGLU(torch.autograd.Function):
+    """``swiglu_packed(x W^T)`` with the activation fused into the GEMM epilogue.  The bf16 pre-activation is kept
+    for backward (the reference's QuACK path does the same with ``store_preact``)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        N = weight.size(0)
+        pre = torch.empty((x2.size(0), N), dtype=x.dtype, device=x.device)
+        y = gemm(x2, weight, swiglu=True, preact=pre)
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.in_shape = shape
+        return y.view(*shape[:-1], N // 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .activation import swiglu_backward
+
+        x2, weight, pre = ctx.saved_tensors
+        dpre = swiglu_backward(pre, dy.reshape(pre.size(0), -1))
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dpre, weight, b_mn=True).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                gemm(dpre, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                weight.grad_added_to_main_grad = True
+            else:
+                dw = gemm(dpre, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        return dx, dw
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``up * silu(gate)`` of the packed projection ``x W^T`` (gate/up interleaved along the output features)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.size(0) % 16 == 0:
+        return _LinearSwiGLU.apply(x, weight)
+    from .activation import swiglu_packed
+
+    return swiglu_packed(torch.nn.functional.linear(x, weight))

@@ -1,0 +1,121 @@
+"""Optimizers over the flat shards of :class:`~lm_engine_b200.parallel.fsdp.FSDPEngine`.
+
+``TorchAdamW`` (the default) runs the fused CUDA AdamW with device-side global-norm clipping.  The other names of
+the reference's table (lm_engine/optimization/optimizer.py:25-39) run the corresponding ``torch.optim`` class on
+1-D fp32 parameters that alias the master shards - every one of them is element-wise, so the flat layout is exact.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..containers import BackwardHookOptimizerContainer, ModelContainer, OptimizerContainer
+from ..enums import ParamsGroupMethod
+from ..parallel.fsdp import FSDPEngine
+
+_TORCH_OPTIMIZERS = {
+    "TorchAdadelta": "Adadelta", "TorchAdagrad": "Adagrad", "TorchAdam": "Adam", "TorchAdamax": "Adamax",
+    "TorchAdamW": "AdamW", "TorchASGD": "ASGD", "TorchLBFGS": "LBFGS", "TorchNAdam": "NAdam", "TorchRAdam": "RAdam",
+    "TorchRMSprop": "RMSprop", "TorchRprop": "Rprop", "TorchSGD": "SGD",
+}
+
+
+class ShardedOptimizer:
+    """Optimizer facade with ``param_groups`` (for LR schedulers), ``step``, ``zero_grad`` and state dicts."""
+
+    def __init__(self, engine: FSDPEngine, class_name: str, class_args: dict, m_width: float | None,
+                 use_mup: bool, max_grad_norm: float | None) -> None:
+        if class_name not in _TORCH_OPTIMIZERS:
+            raise ValueError(f"invalid class_name ({class_name}) for optimizer")
+        self.engine, self.class_name, self.class_args = engine, class_name, dict(class_args)
+        self.max_grad_norm = max_grad_norm
+        lr = class_args["lr"]
+        self.param_groups = [{"name": "normal", "lr": lr}, {"name": "no_weight_decay", "lr": lr, "weight_decay": 0}]
+        if use_mup:
+            self.param_groups.append({"name": "mup", "lr": lr / m_width})
+        self.fused = class_name == "TorchAdamW" and set(class_args) <= {"lr", "weight_decay", "betas", "eps"}
+        self._torch_opt = None
+        if not self.fused:
+            self._build_torch_optimizer()
+
+    def _build_torch_optimizer(self) -> None:
+        groups: dict[str, list[nn.Parameter]] = {g["name"]: [] for g in self.param_groups}
+        self._aliases: list[tuple[nn.Parameter, torch.Tensor, torch.Tensor]] = []
+        for u in self.engine.units:
+            for g in u.local_group_ranges():
+                sl = slice(g.start, g.end)
+                p = nn.Parameter(u.master[sl])
+                groups[g.name if g.name in groups else "normal"].append(p)
+                self._aliases.append((p, u, sl))
+        cls = getattr(torch.optim, _TORCH_OPTIMIZERS[self.class_name])
+        pgs = []
+        for g in self.param_groups:
+            if groups[g["name"]]:
+                pgs.append({"params": groups[g["name"]], **{k: v for k, v in g.items() if k != "name"}})
+        self._torch_opt = cls(pgs, **self.class_args)
+        self._torch_group_names = [g["name"] for g in self.param_groups if groups[g["name"]]]
+
+    def zero_grad(self) -> None:
+        self.engine.zero_grad()
+
+    @torch.no_grad()
+    def step(self) -> torch.Tensor:
+        e = self.engine
+        lrs = {g["name"]: g["lr"] for g in self.param_groups}
+        a = self.class_args
+        if self.fused:
+            return e.clip_and_step(lr=lrs["normal"], lr_by_group=lrs, betas=tuple(a.get("betas", (0.9, 0.999))),
+                                   eps=a.get("eps", 1e-8), weight_decay=a.get("weight_decay", 1e-2),
+                                   max_grad_norm=self.max_grad_norm)
+        from .. import ops
+
+        e.finish_backward()
+        e.step_count += 1
+        for i, u in enumerate(e.units):
+            ops.sumsq_(u.grad_shard, e.sumsq, accumulate=i > 0)
+        e._reduce_norm()
+        ops.clip_coef_(e.sumsq, self.max_grad_norm, e.grad_norm, e.clip_coef)
+        for p, u, sl in self._aliases:
+            p.grad = u.grad_shard[sl].float() * e.clip_coef
+        for g, name in zip(self._torch_opt.param_groups, self._torch_group_names):
+            g["lr"] = lrs[name]
+        self._torch_opt.step()
+        for p, u, sl in self._aliases:
+            u.lp_shard[sl].copy_(u.master[sl])
+            p.grad = None
+        if e.stage in (1, 2) and e.world > 1:
+            import torch.distributed as dist
+
+            for u in e.units:
+                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=e.shard_group)
+        return e.grad_norm
+
+    def state_dict(self) -> dict:
+        sd = {"step": self.engine.step_count, "param_groups": [dict(g) for g in self.param_groups]}
+        if self._torch_opt is not None:
+            sd["torch"] = self._torch_opt.state_dict()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.engine.step_count = sd["step"]
+        for g, s in zip(self.param_groups, sd["param_groups"]):
+            g.update(s)
+        if self._torch_opt is not None and "torch" in sd:
+            self._torch_opt.load_state_dict(sd["torch"])
+
+
+def get_optimizer_container(optimizer_class_name: str, optimizer_class_args: dict, model_container: ModelContainer,
+                            params_group_method: ParamsGroupMethod | None,
+                            use_optimizer_with_backward_hook: bool = False,
+                            max_grad_norm: float | None = 1.0) -> OptimizerContainer:
+    if use_optimizer_with_backward_hook:
+        raise NotImplementedError("optimizer-in-backward is not supported by the sharded flat-buffer runtime")
+    opts = []
+    for wrapper in model_container:
+        engine = wrapper.engine
+        assert engine is not None, "wrap_model_container_for_distributed_training must run before the optimizer"
+        opts.append(ShardedOptimizer(engine, optimizer_class_name, optimizer_class_args,
+                                     getattr(wrapper.config, "m_width", None),
+                                     params_group_method == ParamsGroupMethod.mup, max_grad_norm))
+    return OptimizerContainer(opts)

@@ -1,0 +1,609 @@
+"""ZeRO / FSDP runtime on flat buffers, with block activation checkpointing and a sharded fused AdamW.
+
+One *unit* per decoder block plus one for the embedding and one for the final norm + LM head (the reference wraps
+the same modules with ``fully_shard``, lm_engine/distributed.py:303-385).  Per unit:
+
+* ``flat_param``  compute-dtype (bf16) buffer holding every parameter of the unit back to back, ordered by optimizer
+  group; module parameters are views into it.  ZeRO-3 keeps only this rank's slice between uses and all-gathers the
+  rest into one of two rotating buffers just before the unit runs (next unit prefetched on a side stream).
+* ``main_grad``   gradient buffer of the same layout.  The wgrad GEMM epilogue accumulates straight into it (see
+  :mod:`lm_engine_b200.ops.gemm`); other parameters' ``.grad`` are folded in by a hook.  After the unit's backward it
+  is reduce-scattered (all-reduced for ZeRO-0) on a side stream, overlapped with the backward of the next unit.
+* ``master / exp_avg / exp_avg_sq``  fp32 shards, updated by one fused AdamW launch per optimizer group that also
+  refreshes the bf16 slice; the squared gradient norm is reduced on the device and the clip coefficient is read by
+  the AdamW kernel from device memory, so a step never synchronises with the host.
+
+Stages: 0 = replicate everything (DDP); 1/2 = shard optimizer state and gradients, keep bf16 parameters whole;
+3 = shard parameters too.  ``ddp x fsdp`` (HSDP) all-reduces the sharded gradients over the replication group.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..parameter import is_parameter_with_mup_learning_rate, is_parameter_with_no_weight_decay
+from .manager import ProcessGroupManager
+
+_ALIGN = 128  # elements; keeps every shard / group boundary 256-byte aligned in bf16
+
+
+def _pad(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+@dataclass
+class _Slot:
+    name: str
+    param: nn.Parameter
+    offset: int
+    numel: int
+    shape: torch.Size
+    group: str
+
+
+@dataclass
+class GroupRange:
+    name: str          # "normal" | "no_weight_decay" | "mup"
+    start: int         # offsets in the (padded) flat buffer
+    end: int
+
+
+class ShardedUnit:
+    """Flat storage of the parameters of a list of modules."""
+
+    def __init__(self, name: str, modules: list[nn.Module], prefixes: list[str], device: torch.device,
+                 compute_dtype: torch.dtype, grad_dtype: torch.dtype, shard_world: int, shard_rank: int,
+                 shard_params: bool, shard_state: bool, use_mup_group: bool) -> None:
+        self.name = name
+        self.modules = modules
+        self.device, self.compute_dtype, self.grad_dtype = device, compute_dtype, grad_dtype
+        self.world, self.rank = shard_world, shard_rank
+        self.shard_params = shard_params and shard_world > 1
+        self.shard_state = shard_state and shard_world > 1
+        # ---- layout: parameters ordered by optimizer group so each group is one contiguous range
+        named: list[tuple[str, nn.Parameter]] = []
+        seen = set()
+        for prefix, m in zip(prefixes, modules):
+            for n, p in m.named_parameters():
+                if id(p) in seen:
+                    continue
+                seen.add(id(p))
+                named.append((f"{prefix}.{n}" if prefix else n, p))
+
+        def group_of(p: nn.Parameter) -> str:
+            if is_parameter_with_no_weight_decay(p):
+                return "no_weight_decay"
+            if use_mup_group and is_parameter_with_mup_learning_rate(p):
+                return "mup"
+            return "normal"
+
+        order = {"normal": 0, "mup": 1, "no_weight_decay": 2}
+        named.sort(key=lambda np_: (order[group_of(np_[1])], np_[0]))
+        self.slots: list[_Slot] = []
+        self.group_ranges: list[GroupRange] = []
+        off = 0
+        for gname in ("normal", "mup", "no_weight_decay"):
+            start = off
+            for n, p in named:
+                if group_of(p) != gname:
+                    continue
+                self.slots.append(_Slot(n, p, off, p.numel(), p.shape, gname))
+                off = _pad(off + p.numel(), 8)
+            off = _pad(off, _ALIGN)
+            if off > start:
+                self.group_ranges.append(GroupRange(gname, start, off))
+        self.numel = _pad(max(off, _ALIGN), _ALIGN * self.world)
+        if self.group_ranges:
+            self.group_ranges[-1].end = self.numel
+        self.shard_size = self.numel // self.world
+        self.state_lo = self.rank * self.shard_size if self.shard_state else 0
+        self.state_hi = self.state_lo + (self.shard_size if self.shard_state else self.numel)
+        # ---- storage
+        n_state = self.state_hi - self.state_lo
+        self.master = torch.zeros(n_state, dtype=torch.float32, device=device)
+        self.exp_avg = torch.zeros(n_state, dtype=torch.float32, device=device)
+        self.exp_avg_sq = torch.zeros(n_state, dtype=torch.float32, device=device)
+        self.grad_shard: torch.Tensor | None = None   # reduced gradient of [state_lo, state_hi)
+        if self.shard_params:
+            self.lp_shard = torch.zeros(self.shard_size, dtype=compute_dtype, device=device)
+            self.flat_param: torch.Tensor | None = None
+        else:
+            self.flat_param = torch.zeros(self.numel, dtype=compute_dtype, device=device)
+            self.lp_shard = self.flat_param[self.state_lo:self.state_hi]
+        self.main_grad: torch.Tensor | None = None
+        self.unsharded = not self.shard_params
+        self.ag_event: torch.cuda.Event | None = None
+        self.rs_event: torch.cuda.Event | None = None
+        self.grad_ready = False
+        self.pending_backward = 0      # forward uses of the current step whose backward has not run yet
+        self.keep_unsharded = False    # stay gathered between forward and backward (tied embedding)
+
+    # ------------------------------------------------------------------ parameter views
+    def bind_params(self, flat: torch.Tensor) -> None:
+        for s in self.slots:
+            s.param.data = flat[s.offset:s.offset + s.numel].view(s.shape)
+
+    def bind_grads(self, flat_grad: torch.Tensor) -> None:
+        self.main_grad = flat_grad
+        for s in self.slots:
+            s.param.main_grad = flat_grad[s.offset:s.offset + s.numel].view(s.shape)
+
+    def release_params(self) -> None:
+        empty = torch.empty(0, dtype=self.compute_dtype, device=self.device)
+        for s in self.slots:
+            s.param.data = empty
+
+    def local_group_ranges(self) -> list[GroupRange]:
+        """Group ranges intersected with this rank's optimizer-state slice, relative to that slice."""
+        out = []
+        for g in self.group_ranges:
+            lo, hi = max(g.start, self.state_lo), min(g.end, self.state_hi)
+            if hi > lo:
+                out.append(GroupRange(g.name, lo - self.state_lo, hi - self.state_lo))
+        return out
+
+
+class _RNGState:
+    def __init__(self, device: torch.device) -> None:
+        self.cpu = torch.get_rng_state()
+        self.cuda = torch.cuda.get_rng_state(device) if device.type == "cuda" else None
+
+    def restore(self, device: torch.device) -> None:
+        torch.set_rng_state(self.cpu)
+        if self.cuda is not None:
+            torch.cuda.set_rng_state(self.cuda, device)
+
+
+class _UnitFunction(torch.autograd.Function):
+    """Runs one unit.  Handles (a) parameter gathering before forward / backward, (b) block activation checkpointing
+    (forward without graph, recompute in backward), (c) gradient reduction after the unit's backward."""
+
+    @staticmethod
+    def forward(ctx, engine: "FSDPEngine", unit: ShardedUnit, fn: Callable, checkpoint: bool, preserve_rng: bool,
+                anchor: torch.Tensor, *inputs: torch.Tensor):
+        # ``anchor`` is a 1-element leaf that requires grad: it makes autograd call ``backward`` even when no real
+        # input does (the embedding unit only sees integer token ids).
+        ctx.engine, ctx.unit, ctx.fn, ctx.checkpoint = engine, unit, fn, checkpoint
+        engine.pre_forward(unit, training=True)
+        if checkpoint:
+            ctx.rng = _RNGState(engine.device) if preserve_rng else None
+            ctx.save_for_backward(*inputs)
+            with torch.no_grad():
+                out = fn(*inputs)
+        else:
+            with torch.enable_grad():
+                detached = [t.detach().requires_grad_(t.requires_grad) for t in inputs]
+                out = fn(*detached)
+            ctx.detached, ctx.out = detached, out
+        engine.post_forward(unit, training=True)
+        if isinstance(out, torch.Tensor):
+            return out.detach() if not checkpoint else out
+        return tuple(o.detach() if isinstance(o, torch.Tensor) else o for o in out)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        engine, unit = ctx.engine, ctx.unit
+        engine.pre_backward(unit)
+        if ctx.checkpoint:
+            inputs = ctx.saved_tensors
+            detached = [t.detach().requires_grad_(t.is_floating_point()) for t in inputs]
+            if ctx.rng is not None:
+                now = _RNGState(engine.device)
+                ctx.rng.restore(engine.device)
+            with torch.enable_grad():
+                out = ctx.fn(*detached)
+            if ctx.rng is not None:
+                now.restore(engine.device)
+        else:
+            detached, out = ctx.detached, ctx.out
+        outs = (out,) if isinstance(out, torch.Tensor) else tuple(out)
+        pairs = [(o, g) for o, g in zip(outs, grads) if isinstance(o, torch.Tensor) and o.requires_grad
+                 and g is not None]
+        if pairs:
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        engine.post_backward(unit)
+        return (None, None, None, None, None, None, *[t.grad if t.requires_grad else None for t in detached])
+
+
+class FSDPEngine:
+    """Owns the units of one model (one pipeline stage) and the sharded optimizer state."""
+
+    def __init__(self, model: nn.Module, units: list[tuple[str, list[nn.Module], list[str]]], *, stage: int = 3,
+                 compute_dtype: torch.dtype = torch.bfloat16, grad_dtype: torch.dtype | None = None,
+                 device: torch.device | None = None, use_mup_group: bool = False,
+                 checkpoint_units: set[str] | None = None, preserve_rng: bool = False,
+                 init_fn: Callable[[nn.Module], None] | None = None, seed: int = 0) -> None:
+        assert stage in (0, 1, 2, 3)
+        self.model, self.stage = model, stage
+        self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                                 else torch.device("cpu"))
+        self.compute_dtype = compute_dtype
+        self.grad_dtype = grad_dtype or compute_dtype
+        self.shard_group = ProcessGroupManager.get_sharding_group() if stage > 0 else None
+        self.replica_group = (ProcessGroupManager.get_replication_group() if stage > 0
+                              else ProcessGroupManager.get_data_parallel_group())
+        self.world = dist.get_world_size(self.shard_group) if self.shard_group is not None else 1
+        self.rank = dist.get_rank(self.shard_group) if self.shard_group is not None else 0
+        self.checkpoint_units = checkpoint_units or set()
+        self.preserve_rng = preserve_rng
+        self.is_cuda = self.device.type == "cuda"
+        self.units: list[ShardedUnit] = []
+        for name, modules, prefixes in units:
+            self.units.append(ShardedUnit(name, modules, prefixes, self.device, compute_dtype, self.grad_dtype,
+                                          self.world, self.rank, shard_params=stage == 3, shard_state=stage >= 1,
+                                          use_mup_group=use_mup_group))
+        self.by_name = {u.name: u for u in self.units}
+        covered = {id(s.param) for u in self.units for s in u.slots}
+        missing = [n for n, p in model.named_parameters() if id(p) not in covered]
+        assert not missing, f"parameters not covered by any unit: {missing[:5]}"
+        self._materialize(init_fn, seed)
+        # rotating buffers for gathered parameters / unreduced gradients of the sharded units
+        self._param_pool: dict[int, list[torch.Tensor]] = {}
+        self._grad_pool: dict[int, list[torch.Tensor]] = {}
+        self._pool_cursor: dict[tuple[str, int], int] = {}
+        if self.is_cuda:
+            self.ag_stream = torch.cuda.Stream(self.device)
+            self.rs_stream = torch.cuda.Stream(self.device)
+        self._anchor = torch.zeros(1, device=self.device, requires_grad=True)
+        self._inflight: dict[str, torch.Tensor] = {}
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
+        self.step_count = 0
+        self.micro_step = 0
+        self._setup_grad_buffers()
+        self._install_grad_hooks()
+
+    # ------------------------------------------------------------------ initialisation
+    @torch.no_grad()
+    def _materialize(self, init_fn, seed: int) -> None:
+        """Gives every unit real storage: parameters are (re)initialised in fp32 into a temporary full buffer, the
+        fp32 master slice and the bf16 copy are cut from it."""
+        tp_rank = ProcessGroupManager.get_tensor_parallel_rank()
+        for ui, u in enumerate(self.units):
+            full = torch.zeros(u.numel, dtype=torch.float32, device=self.device)
+            meta = any(s.param.is_meta for s in u.slots)
+            old = {id(s.param): s.param.data for s in u.slots} if not meta else {}
+            if meta:
+                self._replace_meta_parameters(u)
+            for s in u.slots:
+                view = full[s.offset:s.offset + s.numel].view(s.shape)
+                if not meta:
+                    view.copy_(old[id(s.param)])
+                s.param.data = view
+            if meta:
+                gen_seed = seed + 7919 * ui + 104729 * tp_rank
+                devs = [self.device] if self.is_cuda else []
+                with torch.random.fork_rng(devices=devs):
+                    torch.manual_seed(gen_seed)
+                    for m in u.modules:
+                        for sub in m.modules():
+                            if hasattr(sub, "reset_parameters"):
+                                sub.reset_parameters()
+                    if init_fn is not None:
+                        init_fn(u)
+                self._sync_replicated(u)
+            u.master.copy_(full[u.state_lo:u.state_hi])
+            if u.shard_params:
+                u.lp_shard.copy_(full[u.rank * u.shard_size:(u.rank + 1) * u.shard_size])
+                u.release_params()
+            else:
+                u.flat_param.copy_(full)
+                u.bind_params(u.flat_param)
+            del full
+        # buffers (RoPE tables etc.) that are still on meta
+        for mod in self.model.modules():
+            for bname, buf in list(mod.named_buffers(recurse=False)):
+                if buf.is_meta and hasattr(mod, "reset_parameters"):
+                    mod.reset_parameters()
+        for mod in self.model.modules():
+            for bname, buf in list(mod.named_buffers(recurse=False)):
+                if buf.device != self.device and not buf.is_meta:
+                    mod._buffers[bname] = buf.to(self.device)
+
+    def _replace_meta_parameters(self, u: ShardedUnit) -> None:
+        """Meta parameters cannot adopt real storage: swap each for a fresh ``nn.Parameter`` carrying the same
+        markers (attributes) in its owning module."""
+        owners: dict[int, list[tuple[nn.Module, str]]] = {}
+        for m in u.modules:
+            for sub in m.modules():
+                for pname, p in sub._parameters.items():
+                    if p is not None:
+                        owners.setdefault(id(p), []).append((sub, pname))
+        for s in u.slots:
+            old = s.param
+            new = nn.Parameter(torch.empty(0, dtype=self.compute_dtype, device=self.device),
+                               requires_grad=old.requires_grad)
+            new.__dict__.update(old.__dict__)
+            for sub, pname in owners.get(id(old), []):
+                sub._parameters[pname] = new
+            s.param = new
+
+    def _sync_replicated(self, u: ShardedUnit) -> None:
+        """Parameters replicated over the TP group must be identical on all of its ranks after a per-rank init."""
+        tp_group = ProcessGroupManager.get_tensor_parallel_group()
+        if tp_group is None:
+            return
+        src = ProcessGroupManager.get_tensor_parallel_first_rank()
+        for s in u.slots:
+            if getattr(s.param, "tp_shard_dim", None) is None:
+                dist.broadcast(s.param.data, src=src, group=tp_group)
+
+    def _setup_grad_buffers(self) -> None:
+        for u in self.units:
+            if self.world == 1 or self.stage == 0:
+                # the unreduced buffer is the final gradient
+                g = torch.zeros(u.numel, dtype=self.grad_dtype, device=self.device)
+                u.bind_grads(g)
+                u.grad_shard = g[u.state_lo:u.state_hi]
+            else:
+                u.grad_shard = torch.zeros(u.shard_size, dtype=self.grad_dtype, device=self.device)
+                u.main_grad = None
+
+    def _install_grad_hooks(self) -> None:
+        def make_hook():
+            def hook(p: nn.Parameter) -> None:
+                if p.grad is None:
+                    return
+                mg = getattr(p, "main_grad", None)
+                if mg is not None:
+                    mg.add_(p.grad.view_as(mg))
+                p.grad = None
+
+            return hook
+
+        for u in self.units:
+            for s in u.slots:
+                s.param.register_post_accumulate_grad_hook(make_hook())
+
+    # ------------------------------------------------------------------ buffer pools
+    def _take(self, pool: dict[int, list[torch.Tensor]], kind: str, u: ShardedUnit, dtype) -> torch.Tensor:
+        bufs = pool.setdefault(u.numel, [])
+        if len(bufs) < 2:
+            bufs.append(torch.empty(u.numel, dtype=dtype, device=self.device))
+            return bufs[-1]
+        key = (kind, u.numel)
+        i = self._pool_cursor.get(key, 0)
+        self._pool_cursor[key] = i + 1
+        return bufs[i % 2]
+
+    # ------------------------------------------------------------------ gather / reduce
+    def _all_gather(self, u: ShardedUnit) -> None:
+        """Starts the all-gather of ``u`` (side stream on CUDA) unless it is already gathered or in flight."""
+        if u.unsharded or u.name in self._inflight:
+            return
+        buf = self._take(self._param_pool, "p", u, self.compute_dtype)
+        if self.is_cuda:
+            self.ag_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.ag_stream):
+                dist.all_gather_into_tensor(buf, u.lp_shard, group=self.shard_group)
+                u.ag_event = torch.cuda.Event()
+                u.ag_event.record(self.ag_stream)
+        else:
+            dist.all_gather_into_tensor(buf, u.lp_shard, group=self.shard_group)
+        self._inflight[u.name] = buf
+
+    def _wait_gather(self, u: ShardedUnit) -> None:
+        if u.unsharded:
+            return
+        self._all_gather(u)
+        buf = self._inflight.pop(u.name)
+        if self.is_cuda and u.ag_event is not None:
+            torch.cuda.current_stream().wait_event(u.ag_event)
+        u.flat_param = buf
+        u.bind_params(buf)
+        u.unsharded = True
+
+    def _reshard(self, u: ShardedUnit) -> None:
+        if not u.shard_params or not u.unsharded:
+            return
+        u.release_params()
+        u.flat_param = None
+        u.unsharded = False
+
+    def _neighbour(self, u: ShardedUnit, step: int) -> ShardedUnit | None:
+        i = self.units.index(u) + step
+        return self.units[i] if 0 <= i < len(self.units) else None
+
+    # ------------------------------------------------------------------ hooks called by _UnitFunction
+    def pre_forward(self, u: ShardedUnit, training: bool) -> None:
+        if training:
+            u.pending_backward += 1
+        self._wait_gather(u)
+        nxt = self._neighbour(u, +1)
+        if nxt is not None and nxt.shard_params:
+            self._all_gather(nxt)
+
+    def post_forward(self, u: ShardedUnit, training: bool) -> None:
+        # the last unit's backward starts right after its forward: keep it gathered
+        if u.keep_unsharded or (training and u is self.units[-1]):
+            return
+        self._reshard(u)
+
+    def pre_backward(self, u: ShardedUnit) -> None:
+        self._wait_gather(u)
+        prv = self._neighbour(u, -1)
+        if prv is not None and prv.shard_params:
+            self._all_gather(prv)
+        if u.main_grad is None:
+            buf = self._take(self._grad_pool, "g", u, self.grad_dtype)
+            # a buffer of the pool may still be read by an earlier reduce-scatter
+            if self.is_cuda:
+                torch.cuda.current_stream().wait_stream(self.rs_stream)
+            buf.zero_()
+            u.bind_grads(buf)
+
+    def post_backward(self, u: ShardedUnit) -> None:
+        u.pending_backward -= 1
+        if u.pending_backward > 0:
+            return  # the unit ran more than once in forward (tied embedding / LM head): reduce after the last use
+        self._reduce_grads(u)
+        if not u.keep_unsharded:
+            self._reshard(u)
+
+    def _reduce_grads(self, u: ShardedUnit) -> None:
+        tp_group = ProcessGroupManager.get_tensor_parallel_group()
+        if tp_group is not None:
+            for s in u.slots:
+                if getattr(s.param, "sequence_parallel_grad", False):
+                    dist.all_reduce(s.param.main_grad, group=tp_group)
+        if self.world == 1 and self.replica_group is None:
+            u.grad_ready = True
+            return
+        full = u.main_grad
+        dp_total = ProcessGroupManager.get_data_parallel_world_size()
+
+        def run() -> None:
+            if self.stage == 0 or self.world == 1:
+                if self.replica_group is not None:
+                    full.div_(dp_total)
+                    dist.all_reduce(full, group=self.replica_group)
+                return
+            full.div_(dp_total)
+            out = torch.empty(u.shard_size, dtype=full.dtype, device=self.device)
+            if self.is_cuda:
+                dist.reduce_scatter_tensor(out, full, group=self.shard_group)
+            else:
+                tmp = full.clone()
+                dist.all_reduce(tmp, group=self.shard_group)
+                out.copy_(tmp[u.rank * u.shard_size:(u.rank + 1) * u.shard_size])
+            if self.replica_group is not None:
+                dist.all_reduce(out, group=self.replica_group)
+            u.grad_shard.add_(out)
+
+        if self.is_cuda:
+            self.rs_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.rs_stream):
+                run()
+                u.rs_event = torch.cuda.Event()
+                u.rs_event.record(self.rs_stream)
+        else:
+            run()
+        if self.stage != 0 and self.world > 1:
+            u.main_grad = None
+            for s in u.slots:
+                s.param.main_grad = None
+        u.grad_ready = True
+
+    # ------------------------------------------------------------------ public API
+    def run_unit(self, name: str, fn: Callable, *inputs: torch.Tensor):
+        """Executes ``fn(*inputs)`` (the forward of the modules of unit ``name``) under the engine."""
+        u = self.by_name[name]
+        if not torch.is_grad_enabled():
+            self.pre_forward(u, training=False)
+            out = fn(*inputs)
+            self.post_forward(u, training=False)
+            return out
+        return _UnitFunction.apply(self, u, fn, name in self.checkpoint_units, self.preserve_rng, self._anchor,
+                                   *inputs)
+
+    def zero_grad(self) -> None:
+        for u in self.units:
+            if u.grad_shard is not None:
+                u.grad_shard.zero_()
+            u.grad_ready = False
+            u.pending_backward = 0
+        self.micro_step = 0
+
+    def finish_backward(self) -> None:
+        """Joins the reduction stream; call once after the last ``backward`` of a step."""
+        if self.is_cuda:
+            torch.cuda.current_stream().wait_stream(self.rs_stream)
+
+    @torch.no_grad()
+    def clip_and_step(self, *, lr: float, lr_by_group: dict[str, float] | None = None, betas=(0.9, 0.95),
+                      eps: float = 1e-10, weight_decay: float = 0.1, max_grad_norm: float | None = 1.0,
+                      extra_sumsq: torch.Tensor | None = None) -> torch.Tensor:
+        """Global-norm clipping + AdamW on every shard.  Returns the (device) pre-clip gradient norm."""
+        self.finish_backward()
+        self.step_count += 1
+        first = True
+        for u in self.units:
+            ops.sumsq_(u.grad_shard, self.sumsq, accumulate=not first)
+            first = False
+        if extra_sumsq is not None:
+            self.sumsq.add_(extra_sumsq)
+        self._reduce_norm()
+        ops.clip_coef_(self.sumsq, max_grad_norm, self.grad_norm, self.clip_coef)
+        lr_by_group = lr_by_group or {}
+        for u in self.units:
+            for g in u.local_group_ranges():
+                sl = slice(g.start, g.end)
+                ops.adamw_step(u.master[sl], u.exp_avg[sl], u.exp_avg_sq[sl], u.grad_shard[sl], u.lp_shard[sl],
+                               lr=lr_by_group.get(g.name, lr), betas=betas, eps=eps,
+                               weight_decay=0.0 if g.name == "no_weight_decay" else weight_decay,
+                               step=self.step_count, gscale=self.clip_coef)
+            if self.stage in (1, 2) and self.world > 1:
+                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=self.shard_group)
+        return self.grad_norm
+
+    def _reduce_norm(self) -> None:
+        """Sum of squares over every group that holds a distinct piece of the model."""
+        if self.stage >= 1 and self.shard_group is not None:
+            dist.all_reduce(self.sumsq, group=self.shard_group)
+        tp = ProcessGroupManager.get_tensor_parallel_group()
+        if tp is not None:
+            # replicated parameters were counted tp times; their share is small and the reference counts DTensor
+            # replicas once, so subtract the surplus
+            rep = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for u in self.units:
+                for s in u.slots:
+                    if getattr(s.param, "tp_shard_dim", None) is None:
+                        lo = max(s.offset, u.state_lo) - u.state_lo
+                        hi = min(s.offset + s.numel, u.state_hi) - u.state_lo
+                        if hi > lo:
+                            rep += u.grad_shard[lo:hi].float().pow(2).sum()
+            if self.stage >= 1 and self.shard_group is not None:
+                dist.all_reduce(rep, group=self.shard_group)
+            tpw = dist.get_world_size(tp)
+            dist.all_reduce(self.sumsq, group=tp)
+            self.sumsq.sub_(rep * (tpw - 1))
+        pp = ProcessGroupManager.get_pipeline_parallel_group()
+        if pp is not None:
+            dist.all_reduce(self.sumsq, group=pp)
+
+    # ------------------------------------------------------------------ state access (checkpointing, tests)
+    @torch.no_grad()
+    def gather_full(self, u: ShardedUnit, which: str = "master") -> torch.Tensor:
+        """Full fp32 flat tensor of ``master`` / ``exp_avg`` / ``exp_avg_sq`` / ``grad`` on every rank."""
+        t = {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq,
+             "grad": u.grad_shard}[which]
+        if not u.shard_state:
+            return t.float().clone()
+        out = torch.empty(u.numel, dtype=t.dtype, device=self.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.shard_group)
+        return out.float()
+
+    @torch.no_grad()
+    def full_state_dict(self, which: str = "master") -> dict[str, torch.Tensor]:
+        out = {}
+        for u in self.units:
+            full = self.gather_full(u, which)
+            for s in u.slots:
+                out[s.name] = full[s.offset:s.offset + s.numel].view(s.shape).clone()
+        return out
+
+    @torch.no_grad()
+    def load_full_state_dict(self, sd: dict[str, torch.Tensor], which: str = "master") -> None:
+        for u in self.units:
+            full = self.gather_full(u, which)
+            for s in u.slots:
+                if s.name in sd:
+                    full[s.offset:s.offset + s.numel].copy_(sd[s.name].reshape(-1).to(full.device))
+            piece = full[u.state_lo:u.state_hi]
+            {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq}[which].copy_(piece)
+            if which == "master":
+                if u.shard_params:
+                    u.lp_shard.copy_(full[u.rank * u.shard_size:(u.rank + 1) * u.shard_size])
+                else:
+                    u.flat_param.copy_(full)
+
+    def num_parameters(self) -> int:
+        return sum(s.numel for u in self.units for s in u.slots)
