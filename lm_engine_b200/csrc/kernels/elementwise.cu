@@ -212,7 +212,7 @@ __global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                                 __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                 const int* __restrict__ pos, int T, int S, int Hkv, int G, int D, int rd,
-                                int inverse) {
+                                int max_pos, int inverse) {
     const int heads_per_group = G + 2;
     const int vec_per_head = D / 8;
     const int half = rd / 2;
@@ -245,6 +245,11 @@ __global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
             float b[8];
             load8(src + pc, b);
             int p = pos != nullptr ? pos[t] : static_cast<int>(t % S);
+            if (p < 0 || p >= max_pos) {  // position outside the angle table: record it and leave the head unrotated
+                report_error(STATUS_BOUNDS, static_cast<unsigned int>(p));
+                store8(dst + c, a);
+                continue;
+            }
             const float* cs = cos_t + static_cast<long long>(p) * rd + rc;
             const float* sn = sin_t + static_cast<long long>(p) * rd + rc;
             float sgn = (first ? -1.f : 1.f) * (inverse ? -1.f : 1.f);
@@ -494,14 +499,14 @@ extern "C" int lme_swiglu_bwd(const void* x, const void* dy, void* dx, long long
 }
 
 extern "C" int lme_qkv_rope(void* qkv, void* q, void* k, void* v, const float* cos_t, const float* sin_t,
-                            const int* pos, int T, int S, int Hkv, int G, int D, int rope_dim, int inverse,
-                            void* stream) {
+                            const int* pos, int T, int S, int Hkv, int G, int D, int rope_dim, int max_pos,
+                            int inverse, void* stream) {
     if (D % 8 || rope_dim % 16 || rope_dim > D) return LME_ERR_SHAPE;
     long long total = static_cast<long long>(T) * Hkv * (G + 2) * (D / 8);
     if (total == 0) return LME_OK;
     qkv_rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<__nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k),
-        static_cast<__nv_bfloat16*>(v), cos_t, sin_t, pos, T, S, Hkv, G, D, rope_dim, inverse);
+        static_cast<__nv_bfloat16*>(v), cos_t, sin_t, pos, T, S, Hkv, G, D, rope_dim, max_pos, inverse);
     return LME_LAUNCH_OK();
 }
 

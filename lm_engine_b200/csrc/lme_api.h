@@ -39,9 +39,11 @@ int lme_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* r
 // x [T, 2I] with (gate, up) interleaved -> y [T, I] = up * silu(gate)
 int lme_swiglu_fwd(const void* x, void* y, long long T, long long I, void* stream);
 int lme_swiglu_bwd(const void* x, const void* dy, void* dx, long long T, long long I, void* stream);
-// fused QKV split + NeoX rotary embedding (inverse = 1: backward, packs dq/dk/dv into dqkv)
+// fused QKV split + NeoX rotary embedding (inverse = 1: backward, packs dq/dk/dv into dqkv).  cos_t / sin_t are
+// [max_pos, rope_dim]; pos (optional) has T entries, else position = t % S.  A position outside the table sets the
+// status word (STATUS_BOUNDS) instead of reading out of bounds.
 int lme_qkv_rope(void* qkv, void* q, void* k, void* v, const float* cos_t, const float* sin_t, const int* pos,
-                 int T, int S, int Hkv, int G, int D, int rope_dim, int inverse, void* stream);
+                 int T, int S, int Hkv, int G, int D, int rope_dim, int max_pos, int inverse, void* stream);
 // cross entropy over a vocabulary slice [v0, v0+V): row statistics, then in-place gradient
 int lme_ce_stats(const void* logits, long long ld, const long long* labels, float* row_max, float* row_sum,
                  float* tgt_logit, int T, int V, int v0, void* stream);

@@ -62,7 +62,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
             "lme_swiglu_fwd": [P, P, L, L, P],
             "lme_swiglu_bwd": [P, P, P, L, L, P],
-            "lme_qkv_rope": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+            "lme_qkv_rope": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
             "lme_ce_stats": [P, L, P, P, P, P, I, I, I, P],
             "lme_ce_grad": [P, L, P, P, I, I, I, F, P, L, P],
             "lme_adamw": [P, P, P, P, I, P, L, F, F, F, F, F, I, P, P],

@@ -50,27 +50,31 @@ class _QKVRope(torch.autograd.Function):
         lead = qkv.shape[:-1]
         x = qkv.reshape(-1, qkv.size(-1)).contiguous()
         T = x.size(0)
+        max_pos = cos_table.size(0) if cos_table is not None else 0
+        if positions is not None and positions.numel() != T:
+            raise ValueError(f"qkv_split_rope: {positions.numel()} positions for {T} tokens")
         q = torch.empty((T, Hkv * G, D), dtype=x.dtype, device=x.device)
         k = torch.empty((T, Hkv, D), dtype=x.dtype, device=x.device)
         v = torch.empty((T, Hkv, D), dtype=x.dtype, device=x.device)
         _lib.check(_lib.cuda_lib().lme_qkv_rope(x.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                                 _lib.ptr(cos_table), _lib.ptr(sin_table), _lib.ptr(positions), T, S,
-                                                Hkv, G, D, rope_dim, 0, _lib.stream_ptr()), "lme_qkv_rope")
+                                                Hkv, G, D, rope_dim, max_pos, 0, _lib.stream_ptr()), "lme_qkv_rope")
         _lib.count_launch()
         ctx.tables = (cos_table, sin_table, positions)
-        ctx.dims = (T, S, Hkv, G, D, rope_dim)
+        ctx.dims = (T, S, Hkv, G, D, rope_dim, max_pos)
         ctx.in_shape = qkv.shape
         return q.view(*lead, Hkv * G, D), k.view(*lead, Hkv, D), v.view(*lead, Hkv, D)
 
     @staticmethod
     def backward(ctx, dq, dk, dv):
-        T, S, Hkv, G, D, rope_dim = ctx.dims
+        T, S, Hkv, G, D, rope_dim, max_pos = ctx.dims
         cos_table, sin_table, positions = ctx.tables
         dq, dk, dv = dq.contiguous(), dk.contiguous(), dv.contiguous()
         dqkv = torch.empty((T, Hkv * (G + 2) * D), dtype=dq.dtype, device=dq.device)
         _lib.check(_lib.cuda_lib().lme_qkv_rope(dqkv.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                                 _lib.ptr(cos_table), _lib.ptr(sin_table), _lib.ptr(positions), T, S,
-                                                Hkv, G, D, rope_dim, 1, _lib.stream_ptr()), "lme_qkv_rope(inverse)")
+                                                Hkv, G, D, rope_dim, max_pos, 1, _lib.stream_ptr()),
+                   "lme_qkv_rope(inverse)")
         _lib.count_launch()
         return dqkv.view(ctx.in_shape), None, None, None, None, None, None, None, None
 
@@ -83,6 +87,9 @@ def qkv_split_rope(qkv: torch.Tensor, Hkv: int, G: int, D: int, cos_table: torch
     if qkv.is_cuda and qkv.dtype == torch.bfloat16 and D % 8 == 0 and rope_dim % 16 == 0:
         pos = None
         if position_ids is not None:
+            lead = qkv.shape[:-1]
+            if position_ids.dim() == len(lead) and tuple(position_ids.shape) != tuple(lead):
+                position_ids = position_ids.expand(lead)   # [1, S] positions shared by the whole batch
             pos = position_ids.reshape(-1).to(torch.int32).contiguous()
         return _QKVRope.apply(qkv, cos_table, sin_table, pos, seq_len, Hkv, G, D, rope_dim)
     cos = sin = None

@@ -30,37 +30,65 @@ def test_smoke_entry():
     g.smoke()
 
 
-def test_bf16_step_tracks_fp32_reference():
+def test_bf16_gradients_match_fp32_reference():
+    """Per-parameter gradients of one bf16 step (through checkpointing, fused epilogues and main_grad accumulation)
+    against autograd on an fp32 copy of the model."""
     from lm_engine_b200.models import build_model
     from lm_engine_b200.ops import _lib
 
     cfg, w, eng, opt = _setup(torch.bfloat16)
     ref = build_model(cfg).cuda().float()
-    ref.load_state_dict({k: v for k, v in eng.full_state_dict().items()})
-    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-10, weight_decay=0.1)
+    ref.load_state_dict(eng.full_state_dict())
+    g = torch.Generator(device="cuda").manual_seed(0)
+    fixed = torch.randint(0, 2048, (2, 257), device="cuda", generator=g)
+    opt.zero_grad()
+    out = w(fixed, lm_loss_multiplier=1 / 512)
+    out["loss"].backward()
+    eng.finish_backward()
+    grads = eng.full_state_dict("grad")
+    logits = ref(fixed[:, :-1]).logits
+    rl = torch.nn.functional.cross_entropy(logits.float().view(-1, 2048), fixed[:, 1:].reshape(-1))
+    rl.backward()
+    assert abs(float(out["loss"]) - float(rl)) < 2e-2
+    bad = []
+    for n, p in ref.named_parameters():
+        err = ((grads[n].float() - p.grad).norm() / (p.grad.norm() + 1e-12)).item()
+        if err > 5e-2:
+            bad.append((n, err))
+    assert not bad, bad
+    assert _lib.read_status()[0] == 0
+
+
+def test_bf16_training_tracks_fp32_reference():
+    from lm_engine_b200.models import build_model
+    from lm_engine_b200.ops import _lib
+
+    cfg, w, eng, opt = _setup(torch.bfloat16)
+    ref = build_model(cfg).cuda().float()
+    ref.load_state_dict(eng.full_state_dict())
     nodecay = [p for n, p in ref.named_parameters() if "ln_" in n]
     decay = [p for n, p in ref.named_parameters() if "ln_" not in n]
     ropt = torch.optim.AdamW([{"params": decay}, {"params": nodecay, "weight_decay": 0.0}], lr=1e-3,
                              betas=(0.9, 0.95), eps=1e-10, weight_decay=0.1)
     g = torch.Generator(device="cuda").manual_seed(0)
     fixed = torch.randint(0, 2048, (2, 257), device="cuda", generator=g)
-    losses, ref_losses = [], []
+    losses, ref_losses, norms, ref_norms = [], [], [], []
     for _ in range(8):
         opt.zero_grad()
         out = w(fixed, lm_loss_multiplier=1 / 512)
         out["loss"].backward()
-        gn = opt.step()
+        norms.append(float(opt.step()))
         losses.append(float(out["loss"]))
         ropt.zero_grad()
         logits = ref(fixed[:, :-1]).logits
         rl = torch.nn.functional.cross_entropy(logits.float().view(-1, 2048), fixed[:, 1:].reshape(-1))
         rl.backward()
-        rn = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ref_norms.append(float(torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)))
         ropt.step()
         ref_losses.append(float(rl))
-        assert abs(float(gn) - float(rn)) / float(rn) < 0.05
     assert _lib.read_status()[0] == 0
+    assert abs(norms[0] - ref_norms[0]) / ref_norms[0] < 0.02, (norms, ref_norms)
     # same batch every step: the loss must fall, and the bf16 engine must follow the fp32 trajectory
-    assert losses[-1] < losses[0] - 0.5
+    assert losses[-1] < losses[0] - 0.5, losses
     for a, b in zip(losses, ref_losses):
         assert abs(a - b) < 0.05 * max(1.0, b), (losses, ref_losses)
