@@ -2,3 +2,4 @@
 // word and the helpers are shared without relocatable device code.
 #include "kernels/gemm.cu"
 #include "kernels/elementwise.cu"
+#include "kernels/noalloc.cu"
