@@ -34,8 +34,13 @@ MODELS = {
 }
 
 
+LAYERS_OVERRIDE: int | None = None   # --layers: same per-layer shapes with fewer layers (profiling captures only)
+
+
 def model_config(name: str, seq: int) -> dict:
     v, L, h, nh, nkv, hd, inter, theta = MODELS[name]
+    if LAYERS_OVERRIDE is not None:
+        L = LAYERS_OVERRIDE
     return {
         "model_type": "gpt_base", "vocab_size": v, "max_position_embeddings": seq, "hidden_size": h,
         "num_layers": L, "normalization_function": "rmsnorm", "layer_norm_epsilon": 1e-5,
@@ -218,8 +223,8 @@ def run_ours(a) -> dict:
         "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic uniform-random token ids, seeded random-init weights",
-        "config": {"model": a.model, "global_batch": world * a.mbs, "seq_len": a.seq,
-                   "parallelism": f"zero3-dp{world}", "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
+        "config": {"model": a.model if a.layers is None else f"{a.model}-{a.layers}layers",
+                   "global_batch": world * a.mbs, "seq_len": a.seq, "parallelism": f"zero3-dp{world}", "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
                    "optimizer": "AdamW fp32 master+state", "l2": "working set per step >> 126 MB L2, no flush"},
         "tokens_per_sec_per_gpu": value / world,
         "model_tflops_per_gpu": tfl / (dev_ms * 1e-3 / a.steps) / world,
@@ -246,7 +251,11 @@ def main() -> None:
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--mbs", type=int, default=2)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="override the layer count (profiling captures on a small case; not a benchmark result)")
     a = ap.parse_args()
+    global LAYERS_OVERRIDE
+    LAYERS_OVERRIDE = a.layers
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if a.gpus != world:
         if world == 1 and a.gpus > 1:

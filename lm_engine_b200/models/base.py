@@ -165,7 +165,11 @@ class TransformerModel(nn.Module):
                 key_length = x.size(1) * self._sequence_multiplier()
             if self.position_embedding_type in ("rope", "learned_absolute"):
                 self._setup_positions(position_info, None, 0, key_length, key_length, x.device)
-        if not self.use_padding_free_transformer and is_generation_cache_enabled() and cache_params is None:
+        # a K/V cache is only ever useful for inference; under training it would also break activation
+        # recomputation (the recomputed block would append its keys to the ones cached by the first forward)
+        training_pass = self.training and torch.is_grad_enabled()
+        if (not self.use_padding_free_transformer and is_generation_cache_enabled() and cache_params is None
+                and not training_pass):
             cache_params = GenerationCache()
         x = self.run_blocks(x, cache_params, attention_mask_info, position_info)
         if self.is_last_stage:
