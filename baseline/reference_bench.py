@@ -32,11 +32,12 @@ def _make_tokenizer_dir() -> str:
     path = os.path.join(tempfile.gettempdir(), f"lme_ref_tok_{os.getuid()}")
     if os.path.exists(os.path.join(path, "tokenizer.json")):
         return path
-    vocab = {"<unk>": 0, "<eos>": 1, "<pad>": 2, "a": 3, "b": 4}
+    # special-token ids must equal the model config's bos / eos / pad ids (0 / 1 / 2): the reference asserts it
+    vocab = {"<bos>": 0, "<eos>": 1, "<pad>": 2, "<unk>": 3, "a": 4, "b": 5}
     tok = Tokenizer(models.WordLevel(vocab=vocab, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Whitespace()
     fast = PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="<eos>", pad_token="<pad>",
-                                   bos_token="<eos>")
+                                   bos_token="<bos>")
     os.makedirs(path, exist_ok=True)
     fast.save_pretrained(path)
     return path
@@ -79,6 +80,7 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
         from lm_engine.parallel.manager import ProcessGroupManager
         from lm_engine.train import train_step_without_pipeline_parallel
         from lm_engine.accelerator import Accelerator
+        from lm_engine.utils import disable_generation_cache
     except Exception as e:  # noqa: BLE001
         return _unavailable(f"reference import failed: {type(e).__name__}: {e}")
 
@@ -87,6 +89,12 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
         kernels = [k for k in os.environ.get("LME_REF_KERNELS", "flash_attention_2").split(",") if k]
         cfg = training_config(a.model, a.seq, a.mbs, a.steps, kernels, tok_dir)
         cfg["distributed_args"].pop("expert_parallel_world_size", None)
+        # With this torch version the reference's default (non-reentrant) block checkpointing raises CheckpointError:
+        # FSDP-2 casts the rotary cos/sin inputs of a block to bf16 in forward but skips that cast when the block is
+        # recomputed, and the non-reentrant checkpoint compares tensor metadata.  The reference's own
+        # `use_reentrant` knob selects the checkpoint implementation without that comparison.
+        cfg["distributed_args"]["gradient_checkpointing_args"] = {
+            "use_reentrant": os.environ.get("LME_REF_REENTRANT", "1") == "1"}
         args = TrainingArgs(**cfg)
         d = args.distributed_args
         ProcessGroupManager(zero_stage=d.stage)
@@ -124,7 +132,8 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
             dist.barrier()
             torch.cuda.synchronize()
 
-        with enable_kernels(args.kernel_args.kernels):
+        # the reference's own train() runs its loop inside these two context managers
+        with disable_generation_cache(), enable_kernels(args.kernel_args.kernels):
             for _ in range(a.warmup):
                 m = step(host_iter)
             first_loss = float(m["loss"]) if a.warmup else None

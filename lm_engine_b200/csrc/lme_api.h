@@ -24,6 +24,11 @@ int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const void* B, i
                   void* C, long long ldc, int M, int N, int K, int flags, const void* bias, const void* residual,
                   long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
 
+// Same contract, computed by pairs of CTAs (thread-block clusters of 2, tcgen05.mma.cta_group::2, 256 x 256 tiles).
+int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, const void* B, int b_mn_major, long long ldb,
+                       void* C, long long ldc, int M, int N, int K, int flags, const void* bias,
+                       const void* residual, long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
+
 // Copies the 8-word device status block to the host (synchronising copy); optionally clears it.
 int lme_read_status(unsigned int* out8, int clear);
 

@@ -1,5 +1,6 @@
 // The single translation unit of liblme_cuda.so: every kernel file is included here so that the device status
 // word and the helpers are shared without relocatable device code.
 #include "kernels/gemm.cu"
+#include "kernels/gemm2cta.cu"
 #include "kernels/elementwise.cu"
 #include "kernels/noalloc.cu"

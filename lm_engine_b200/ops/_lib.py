@@ -56,6 +56,7 @@ def cuda_lib() -> ctypes.CDLL:
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         sigs = {
             "lme_gemm_bf16": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
+            "lme_gemm_bf16_2cta": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
             "lme_read_status": [P, I],
             "lme_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
             "lme_rmsnorm_bwd_partial_rows": [I],

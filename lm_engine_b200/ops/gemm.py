@@ -17,9 +17,14 @@ Plays the role of ``F.linear`` / QuACK ``gemm``/``gemm_act``/``gemm_gated`` in t
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
+
+# "1cta": one CTA per 128 x 256 tile; "2cta": CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2)
+DEFAULT_IMPL = os.environ.get("LME_GEMM", "2cta")
 
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
@@ -71,6 +76,7 @@ def gemm(
     swiglu: bool = False,
     preact: torch.Tensor | None = None,
     max_ctas: int = 0,
+    impl: str | None = None,
 ) -> torch.Tensor:
     if not (a.is_cuda and a.dtype == torch.bfloat16):
         return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
@@ -104,7 +110,9 @@ def gemm(
             raise ValueError("gemm: residual must be a row-major bf16 [M, N] tensor")
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
         raise ValueError("gemm: bias must be a contiguous bf16 [N] tensor")
-    rc = _lib.cuda_lib().lme_gemm_bf16(
+    lib = _lib.cuda_lib()
+    fn = lib.lme_gemm_bf16_2cta if (impl or DEFAULT_IMPL) == "2cta" else lib.lme_gemm_bf16
+    rc = fn(
         a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0),
         M, N, K, flags, _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
         _lib.ptr(preact), preact.stride(0) if preact is not None else 0, max_ctas, _lib.stream_ptr(),
