@@ -321,56 +321,63 @@ __global__ void ce_grad_kernel(__nv_bfloat16* __restrict__ logits, long long ld,
 // torch.optim.AdamW semantics on a flat shard.  g may be bf16 or fp32; the bf16 compute copy is refreshed in the
 // same pass.  *gscale (optional, device) multiplies the gradient (clip coefficient x unscale).
 template <typename GT>
-__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
-                             const GT* __restrict__ g, __nv_bfloat16* __restrict__ p_lp, long long n, float lr,
-                             float b1, float b2, float eps, float wd, float bc1, float bc2_sqrt,
-                             const float* __restrict__ gscale) {
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float* __restrict__ m,
+                                                    float* __restrict__ v, const GT* __restrict__ g,
+                                                    __nv_bfloat16* __restrict__ p_lp, long long n, float lr,
+                                                    float b1, float b2, float eps, float wd, float bc1,
+                                                    float bc2_sqrt, const float* __restrict__ gscale) {
     const float gs = gscale != nullptr ? *gscale : 1.f;
     const float step = lr / bc1;
     const float decay = 1.f - lr * wd;
-    for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
-         i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
-        if (i + 4 <= n) {
-            float4 pv = *reinterpret_cast<const float4*>(p + i);
-            float4 mv = *reinterpret_cast<const float4*>(m + i);
-            float4 vv = *reinterpret_cast<const float4*>(v + i);
-            float gg[4];
-            if constexpr (sizeof(GT) == 2) {
-                uint2 raw = *reinterpret_cast<const uint2*>(g + i);
-                float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
-                gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
-            } else {
-                float4 raw = *reinterpret_cast<const float4*>(g + i);
-                gg[0] = raw.x; gg[1] = raw.y; gg[2] = raw.z; gg[3] = raw.w;
-            }
-            float pp[4] = {pv.x, pv.y, pv.z, pv.w}, mm[4] = {mv.x, mv.y, mv.z, mv.w}, v2[4] = {vv.x, vv.y, vv.z, vv.w};
+    const float rbc2 = 1.f / bc2_sqrt;
+    // 8 elements per thread and iteration: 2 x 16-byte accesses on every fp32 stream, one on the bf16 streams
+    for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+        if (i + 8 <= n) {
+            float pp[8], mm[8], v2[8], gg[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int h = 0; h < 2; ++h) {
+                float4 a = *reinterpret_cast<const float4*>(p + i + 4 * h);
+                float4 b = *reinterpret_cast<const float4*>(m + i + 4 * h);
+                float4 c = *reinterpret_cast<const float4*>(v + i + 4 * h);
+                pp[4 * h] = a.x; pp[4 * h + 1] = a.y; pp[4 * h + 2] = a.z; pp[4 * h + 3] = a.w;
+                mm[4 * h] = b.x; mm[4 * h + 1] = b.y; mm[4 * h + 2] = b.z; mm[4 * h + 3] = b.w;
+                v2[4 * h] = c.x; v2[4 * h + 1] = c.y; v2[4 * h + 2] = c.z; v2[4 * h + 3] = c.w;
+            }
+            if constexpr (sizeof(GT) == 2) {
+                load8(reinterpret_cast<const __nv_bfloat16*>(g) + i, gg);
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float4 a = *reinterpret_cast<const float4*>(g + i + 4 * h);
+                    gg[4 * h] = a.x; gg[4 * h + 1] = a.y; gg[4 * h + 2] = a.z; gg[4 * h + 3] = a.w;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
                 float gr = gg[j] * gs;
                 pp[j] *= decay;
                 mm[j] = b1 * mm[j] + (1.f - b1) * gr;
                 v2[j] = b2 * v2[j] + (1.f - b2) * gr * gr;
-                float denom = sqrtf(v2[j]) / bc2_sqrt + eps;
+                float denom = sqrtf(v2[j]) * rbc2 + eps;
                 pp[j] -= step * mm[j] / denom;
             }
-            *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
-            *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-            *reinterpret_cast<float4*>(v + i) = make_float4(v2[0], v2[1], v2[2], v2[3]);
-            if (p_lp != nullptr) {
-                uint2 o;
-                o.x = pack_bf16x2(pp[0], pp[1]);
-                o.y = pack_bf16x2(pp[2], pp[3]);
-                *reinterpret_cast<uint2*>(p_lp + i) = o;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                *reinterpret_cast<float4*>(p + i + 4 * h) = make_float4(pp[4 * h], pp[4 * h + 1], pp[4 * h + 2], pp[4 * h + 3]);
+                *reinterpret_cast<float4*>(m + i + 4 * h) = make_float4(mm[4 * h], mm[4 * h + 1], mm[4 * h + 2], mm[4 * h + 3]);
+                *reinterpret_cast<float4*>(v + i + 4 * h) = make_float4(v2[4 * h], v2[4 * h + 1], v2[4 * h + 2], v2[4 * h + 3]);
             }
+            if (p_lp != nullptr) store8(p_lp + i, pp);
         } else {
             for (long long k = i; k < n; ++k) {
                 float gr = static_cast<float>(g[k]) * gs;
-                float pp = p[k] * decay;
-                float mm = b1 * m[k] + (1.f - b1) * gr;
-                float v2 = b2 * v[k] + (1.f - b2) * gr * gr;
-                pp -= step * mm / (sqrtf(v2) / bc2_sqrt + eps);
-                p[k] = pp; m[k] = mm; v[k] = v2;
-                if (p_lp != nullptr) p_lp[k] = __float2bfloat16_rn(pp);
+                float pq = p[k] * decay;
+                float mq = b1 * m[k] + (1.f - b1) * gr;
+                float vq = b2 * v[k] + (1.f - b2) * gr * gr;
+                pq -= step * mq / (sqrtf(vq) * rbc2 + eps);
+                p[k] = pq; m[k] = mq; v[k] = vq;
+                if (p_lp != nullptr) p_lp[k] = __float2bfloat16_rn(pq);
             }
         }
     }
@@ -534,11 +541,11 @@ extern "C" int lme_adamw(float* p, float* m, float* v, const void* g, int g_is_b
     if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(g)) & 15)
         return LME_ERR_ALIGN;
-    if (p_lp != nullptr && (reinterpret_cast<uintptr_t>(p_lp) & 7)) return LME_ERR_ALIGN;
+    if (p_lp != nullptr && (reinterpret_cast<uintptr_t>(p_lp) & 15)) return LME_ERR_ALIGN;
     float bc1 = 1.f - powf(b1, static_cast<float>(step));
     float bc2 = 1.f - powf(b2, static_cast<float>(step));
     float bc2_sqrt = sqrtf(bc2);
-    int grid = grid_for((n + 3) / 4, 256, 148 * 8);
+    int grid = grid_for((n + 7) / 8, 256, 148 * 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g_is_bf16)
         adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, m, v, static_cast<const __nv_bfloat16*>(g),

@@ -24,7 +24,7 @@ import torch
 from . import _lib
 
 # "1cta": one CTA per 128 x 256 tile; "2cta": CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2)
-DEFAULT_IMPL = os.environ.get("LME_GEMM", "2cta")
+DEFAULT_IMPL = os.environ.get("LME_GEMM", "1cta")
 
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
@@ -122,6 +122,15 @@ def gemm(
     return out
 
 
+def _wgrad_into(main_grad: torch.Tensor, weight: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor) -> None:
+    """dW = dy^T x written into the parameter's gradient buffer by the GEMM epilogue.  The first write of a step
+    overwrites (the buffer was not cleared, flag ``main_grad_stale``), later ones accumulate."""
+    stale = getattr(weight, "main_grad_stale", False)
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=not stale)
+    if stale:
+        weight.main_grad_stale = False
+
+
 class _Linear(torch.autograd.Function):
     """y = x W^T (+ b) (+ residual).  The weight gradient is accumulated straight into ``weight.main_grad`` by the
     GEMM epilogue when that buffer exists (gradient accumulation fused into wgrad), else returned to autograd."""
@@ -148,8 +157,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main_grad = getattr(weight, "main_grad", None)
             if main_grad is not None:
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
-                weight.grad_added_to_main_grad = True
+                _wgrad_into(main_grad, weight, dy2, x2)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
@@ -195,8 +203,7 @@ class _LinearSwiGLU(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main_grad = getattr(weight, "main_grad", None)
             if main_grad is not None:
-                gemm(dpre, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
-                weight.grad_added_to_main_grad = True
+                _wgrad_into(main_grad, weight, dpre, x2)
             else:
                 dw = gemm(dpre, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
         return dx, dw

@@ -354,7 +354,11 @@ class FSDPEngine:
                     return
                 mg = getattr(p, "main_grad", None)
                 if mg is not None:
-                    mg.add_(p.grad.view_as(mg))
+                    if getattr(p, "main_grad_stale", False):
+                        mg.copy_(p.grad.view_as(mg))
+                        p.main_grad_stale = False
+                    else:
+                        mg.add_(p.grad.view_as(mg))
                 p.grad = None
 
             return hook
@@ -505,8 +509,15 @@ class FSDPEngine:
                                    *inputs)
 
     def zero_grad(self) -> None:
+        """Starts a new accumulation window.  Persistent gradient buffers (single shard / ZeRO-0) are not cleared:
+        every parameter is flagged so that its first gradient write of the step overwrites instead of accumulating;
+        parameters that received no gradient are cleared in :meth:`finish_backward`."""
+        lazy = self.world == 1 or self.stage == 0
         for u in self.units:
-            if u.grad_shard is not None:
+            if lazy and u.main_grad is not None:
+                for s in u.slots:
+                    s.param.main_grad_stale = True
+            elif u.grad_shard is not None:
                 u.grad_shard.zero_()
             u.grad_ready = False
             u.pending_backward = 0
@@ -514,6 +525,13 @@ class FSDPEngine:
 
     def finish_backward(self) -> None:
         """Joins the reduction stream; call once after the last ``backward`` of a step."""
+        for u in self.units:
+            for s in u.slots:
+                if getattr(s.param, "main_grad_stale", False):
+                    mg = getattr(s.param, "main_grad", None)
+                    if mg is not None:
+                        mg.zero_()
+                    s.param.main_grad_stale = False
         if self.is_cuda:
             torch.cuda.current_stream().wait_stream(self.rs_stream)
 

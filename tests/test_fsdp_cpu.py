@@ -1,0 +1,76 @@
+"""ZeRO stages 0-3 (and HSDP) of the flat-buffer engine on gloo ranks against a single-process run on the
+concatenated batch."""
+
+import numpy as np
+import pytest
+import torch
+
+from .dist_utils import run_distributed
+
+VOCAB, SEQ = 512, 32
+
+
+def _cfg():
+    from lm_engine_b200.models import dense_config
+
+    return dense_config(vocab_size=VOCAB, hidden_size=64, num_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                        intermediate_size=128, max_position_embeddings=SEQ)
+
+
+def _train(rank, world, stage, ddp, fsdp, steps, mbs):
+    from lm_engine_b200.distributed import shard_model
+    from lm_engine_b200.enums import GradientCheckpointingMethod
+    from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+    from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    ProcessGroupManager(zero_stage=stage, data_parallel_replication_world_size=ddp,
+                        data_parallel_sharding_world_size=fsdp)
+    w = ModelWrapperForPretraining(pretrained_config=_cfg().to_dict(), micro_batch_size=mbs, sequence_length=SEQ,
+                                   efficient_initialization=True)
+    eng = shard_model(w, stage=stage, dtype=torch.float32, communication_dtype=None,
+                      gradient_checkpointing_method=GradientCheckpointingMethod.block, seed=11)
+    opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "eps": 1e-10},
+                           None, False, 1.0)
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, VOCAB, (steps, world * mbs, SEQ + 1), generator=g)
+    losses, norms = [], []
+    for s in range(steps):
+        opt.zero_grad()
+        out = w(data[s, rank * mbs:(rank + 1) * mbs], lm_loss_multiplier=1 / (mbs * SEQ))
+        out["loss"].backward()
+        norms.append(float(opt.step()))
+        losses.append(float(out["loss"].detach()))
+    params = eng.full_state_dict()
+    return losses, norms, {k: v.detach().cpu().numpy().copy() for k, v in params.items()}
+
+
+def _single(steps, total_mbs):
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    ProcessGroupManager.destroy_process_groups()
+    return _train(0, 1, 3, None, None, steps, total_mbs)
+
+
+@pytest.mark.parametrize("stage,ddp,fsdp", [(3, None, None), (2, None, None), (0, None, None), (3, 2, 1), (3, 1, 2)])
+def test_two_ranks_match_single_process(stage, ddp, fsdp):
+    steps, mbs, world = 3, 2, 2
+    ref_losses, ref_norms, ref_params = _single(steps, mbs * world)
+    outs = run_distributed(_train, world, stage, ddp, fsdp, steps, mbs)
+    mean_loss = [sum(o[0][s] for o in outs) / world for s in range(steps)]
+    for a, b in zip(mean_loss, ref_losses):
+        assert abs(a - b) < 2e-4, (mean_loss, ref_losses)
+    for a, b in zip(outs[0][1], ref_norms):
+        assert abs(a - b) / b < 2e-3, (outs[0][1], ref_norms)
+    for k, v in ref_params.items():
+        for o in outs:
+            assert np.allclose(o[2][k], v, atol=2e-5, rtol=1e-4), k
+
+
+def test_four_ranks_hsdp():
+    steps, mbs, world = 2, 1, 4
+    ref_losses, ref_norms, ref_params = _single(steps, mbs * world)
+    outs = run_distributed(_train, world, 3, 2, 2, steps, mbs)
+    for k, v in ref_params.items():
+        assert np.allclose(outs[3][2][k], v, atol=2e-5, rtol=1e-4), k
+    assert abs(outs[0][1][0] - ref_norms[0]) / ref_norms[0] < 2e-3

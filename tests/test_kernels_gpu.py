@@ -37,9 +37,9 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn, impl):
 
 @pytest.mark.parametrize("impl", ["1cta", "2cta"])
 def test_gemm_epilogues(impl, monkeypatch):
-    from lm_engine_b200.ops import gemm as gemm_mod
+    import sys
 
-    monkeypatch.setattr(gemm_mod, "DEFAULT_IMPL", impl)
+    monkeypatch.setattr(sys.modules["lm_engine_b200.ops.gemm"], "DEFAULT_IMPL", impl)
     torch.manual_seed(1)
     M, N, K = 512, 1024, 384
     a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
