@@ -58,7 +58,7 @@ class ModelArgs(BaseArgs):
 
 
 class TuningArgs(BaseArgs):
-    tuning_method: TuningMethod = None
+    tuning_method: TuningMethod | None = None
 
     def model_post_init(self, _ctx: Any) -> None:
         _require(tuning_method=self.tuning_method)
@@ -98,8 +98,8 @@ class TrainingParameters(BaseArgs):
 
 
 class SaveArgs(BaseArgs):
-    save_path: str = None
-    save_interval: int = None
+    save_path: str | None = None
+    save_interval: int | None = None
     save_optimizer: bool = True
     async_checkpointing: bool = False
 
@@ -108,7 +108,7 @@ class SaveArgs(BaseArgs):
 
 
 class LoadArgs(BaseArgs):
-    load_path: str = None
+    load_path: str | None = None
     iteration: int | None = None
     load_optimizer: bool = True
     load_lr_scheduler: bool = True
@@ -127,12 +127,12 @@ class LoadArgs(BaseArgs):
 
 
 class DatasetArgs(BaseArgs):
-    class_name: str = None
+    class_name: str | None = None
     class_args: dict = {}
-    data_name: str = None
+    data_name: str | None = None
     input_format: str = INPUT_FORMAT
     output_format: str = OUTPUT_FORMAT
-    data_sampling_ratio: int = None
+    data_sampling_ratio: int | None = None
     max_input_tokens: int | None = None
     max_output_tokens: int | None = None
 
@@ -219,15 +219,15 @@ class DistributedArgs(BaseArgs):
 
 
 class AimArgs(BaseArgs):
-    repo: str = None
-    experiment: str = None
+    repo: str | None = None
+    experiment: str | None = None
 
     def model_post_init(self, _ctx: Any) -> None:
         _require(repo=self.repo, experiment=self.experiment)
 
 
 class WandBArgs(BaseArgs):
-    project: str = None
+    project: str | None = None
     name: str | None = None
     entity: str | None = None
     tags: list[str] | None = None
@@ -267,7 +267,7 @@ class TeacherArgs(BaseArgs):
     # extension: build the teacher from an inline config (offline runs / tests)
     pretrained_config: dict | None = None
     dtype: str = "fp32"
-    kl_divergence_method: KLDivergenceMethod = None
+    kl_divergence_method: KLDivergenceMethod | None = None
     kl_divergence_weight: float = 1
 
     def model_post_init(self, _ctx: Any) -> None:
@@ -278,12 +278,12 @@ class TeacherArgs(BaseArgs):
 class TrainingArgs(BaseArgs):
     random_args: RandomArgs = RandomArgs()
     tokenizer_args: TokenizerArgs = TokenizerArgs()
-    model_args: ModelArgs = None
-    tuning_args: TuningArgs = None
+    model_args: ModelArgs | None = None
+    tuning_args: TuningArgs | None = None
     optimizer_args: OptimizerArgs = OptimizerArgs()
     lr_scheduler_args: LRSchedulerArgs = LRSchedulerArgs()
     datasets: list[DatasetArgs] = []
-    save_args: SaveArgs = None
+    save_args: SaveArgs | None = None
     load_args: LoadArgs | None = None
     training_parameters: TrainingParameters | None = None
     logging_args: LoggingArgs = LoggingArgs()
@@ -305,8 +305,8 @@ class TrainingArgs(BaseArgs):
 
 
 class UnshardingArgs(BaseArgs):
-    load_args: LoadArgs = None
-    unsharded_path: str = None
+    load_args: LoadArgs | None = None
+    unsharded_path: str | None = None
     mixed_precision_args: MixedPrecisionArgs = MixedPrecisionArgs()
     logging_args: LoggingArgs = LoggingArgs()
     kernel_args: KernelArgs = KernelArgs()
@@ -316,7 +316,7 @@ class UnshardingArgs(BaseArgs):
 
 
 class DistillationArgs(TrainingArgs):
-    teacher_args: TeacherArgs = None
+    teacher_args: TeacherArgs | None = None
     kernel_args: KernelArgs = KernelArgs()
 
     def model_post_init(self, _ctx: Any) -> None:

@@ -1,0 +1,386 @@
+"""Checkpoint save / resume / unshard with the reference's on-disk layout
+(lm_engine/checkpointing/__init__.py:49-446, model.py, optimizer.py, model_optimizer.py, lr_scheduler.py)::
+
+    <save_path>/latest_checkpointed_iteration.json
+    <save_path>/global_step{N}/model/            torch DCP directory, root key "state", keys "model.<parameter fqn>"
+                               optimizer/        torch DCP directory, flattened optimizer state
+                               model_optimizer/  async mode: {"state": {"model": ..., "optimizer": ...}}
+                               lr_scheduler/lr_scheduler-{global_rank}.pt
+                               rng_state/rng_state-{global_rank}.pt
+                               dataloader/dataloader-{data_loading_rank}.pt
+                               experiments_tracker.json, metadata.json, training_config.yml
+
+The runtime keeps parameters as flat per-unit shards; at save time every parameter is re-cut into the standard
+DTensor layout (``Shard(0)`` over the sharding group, ``Shard(tp_dim)`` over the tensor-parallel group), so the
+files are ordinary DCP checkpoints that reshard on load to any topology and that plain ``dcp.load`` / the
+reference's unshard path can read.  Works on CPU (gloo) as well as CUDA.  A checkpoint directory is written under a
+temporary name and renamed when complete; ``latest_checkpointed_iteration.json`` is replaced atomically afterwards.
+A file named ``KILLSWITCH`` in ``save_path`` makes the job exit cleanly after the next checkpoint.
+"""
+
+from __future__ import annotations
+
+import json
+import logging
+import os
+import random
+import shutil
+import subprocess
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+import yaml
+from torch.distributed.tensor import DTensor, Replicate, Shard
+
+from .accelerator import Accelerator
+from .arguments import DistillationArgs, TrainingArgs, UnshardingArgs
+from .containers import LRSchedulerContainer, ModelContainer, OptimizerContainer
+from .logging_utils import log_rank_0
+from .parallel.manager import ProcessGroupManager, run_rank_n
+from .utils import load_yaml, string_to_torch_dtype
+
+_KILLSWITCH = "KILLSWITCH"
+_FUTURE = None
+_PENDING_PUBLISH = None
+
+
+def _tag(iteration: int) -> str:
+    return f"global_step{iteration}"
+
+
+def _base(path: str, iteration: int) -> str:
+    return os.path.join(path, _tag(iteration))
+
+
+def _latest_file(path: str) -> str:
+    return os.path.join(path, "latest_checkpointed_iteration.json")
+
+
+def _rank_file(base: str, kind: str, rank: int) -> str:
+    return os.path.join(base, kind, f"{kind}-{rank}.pt")
+
+
+def _commit_id() -> str | None:
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        r = subprocess.run(["git", "-C", root, "rev-parse", "HEAD"], capture_output=True, text=True, timeout=5)
+        return r.stdout.strip() or None
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def ensure_last_checkpoint_is_saved() -> None:
+    global _FUTURE, _PENDING_PUBLISH
+    if _FUTURE is not None:
+        _FUTURE.result()
+        _FUTURE = None
+    if _PENDING_PUBLISH is not None:
+        _PENDING_PUBLISH()
+        _PENDING_PUBLISH = None
+
+
+# ---------------------------------------------------------------------------------------------- state dicts
+def _to_dtensor(engine, local_full: torch.Tensor, param: torch.nn.Parameter) -> torch.Tensor:
+    """Full (per-TP-rank) tensor -> DTensor in the standard layout, or the tensor itself on a single rank."""
+    tp_dim = getattr(param, "tp_shard_dim", None)
+    tp_group = ProcessGroupManager.get_tensor_parallel_group()
+    if engine.shard_group is not None and tp_group is None and engine.stage >= 1 and local_full.dim() >= 1:
+        mesh = ProcessGroupManager.get_device_mesh("fsdp")
+        n, world, rank = local_full.size(0), engine.world, engine.rank
+        per = -(-n // world)
+        lo, hi = min(rank * per, n), min((rank + 1) * per, n)
+        chunk = local_full[lo:hi].clone()
+        return DTensor.from_local(chunk, mesh, [Shard(0)], run_check=False, shape=local_full.shape,
+                                  stride=local_full.stride())
+    if tp_group is not None:
+        mesh = ProcessGroupManager.get_device_mesh("tp")
+        placement = [Shard(tp_dim)] if tp_dim is not None else [Replicate()]
+        return DTensor.from_local(local_full.clone(), mesh, placement, run_check=False)
+    return local_full.clone()
+
+
+def _from_saved(value: torch.Tensor, engine) -> torch.Tensor:
+    """Inverse of :func:`_to_dtensor`: the full per-TP-rank tensor."""
+    if isinstance(value, DTensor):
+        tp = ProcessGroupManager.get_tensor_parallel_group()
+        if tp is not None and value.device_mesh.mesh_dim_names == ("tp",):
+            return value.to_local()
+        return value.full_tensor()
+    return value
+
+
+def model_state_dict(model_container: ModelContainer, which: str = "master") -> dict[str, torch.Tensor]:
+    """Checkpoint-layout state of all local pipeline stages (keys ``model.<fqn>``, teacher weights excluded)."""
+    out: dict[str, torch.Tensor] = {}
+    for wrapper in model_container:
+        eng = wrapper.engine
+        if eng is None:
+            for k, v in wrapper.model.state_dict().items():
+                out[f"model.{k}"] = v
+            continue
+        for u in eng.units:
+            full = eng.gather_full(u, which)
+            for s in u.slots:
+                out[f"model.{s.name}"] = _to_dtensor(eng, full[s.offset:s.offset + s.numel].view(s.shape), s.param)
+    return out
+
+
+def load_model_state_dict(model_container: ModelContainer, state: dict[str, torch.Tensor],
+                          which: str = "master") -> None:
+    for wrapper in model_container:
+        eng = wrapper.engine
+        if eng is None:
+            wrapper.model.load_state_dict({k[len("model."):]: _from_saved(v, None) for k, v in state.items()},
+                                          strict=False)
+            continue
+        plain = {}
+        for u in eng.units:
+            for s in u.slots:
+                key = f"model.{s.name}"
+                if key in state:
+                    plain[s.name] = _from_saved(state[key], eng)
+        eng.load_full_state_dict(plain, which)
+
+
+_GROUP_KEYS = ("lr", "betas", "eps", "weight_decay", "initial_lr")
+
+
+def optimizer_state_dict(model_container: ModelContainer, optimizer_container: OptimizerContainer) -> dict:
+    """Flattened optimizer state in torch's ``flatten_optimizer_state_dict`` key scheme:
+    ``state.<fqn>.{exp_avg,exp_avg_sq,step}`` and ``param_groups.<fqn>.<hyper-parameter>``."""
+    out: dict = {}
+    for wrapper, opt in zip(model_container, optimizer_container):
+        eng = wrapper.engine
+        groups = {g["name"]: g for g in opt.param_groups}
+        a = opt.class_args
+        for u in eng.units:
+            m, v = eng.gather_full(u, "exp_avg"), eng.gather_full(u, "exp_avg_sq")
+            for s in u.slots:
+                fqn = f"model.{s.name}"
+                sl = slice(s.offset, s.offset + s.numel)
+                out[f"state.{fqn}.exp_avg"] = _to_dtensor(eng, m[sl].view(s.shape), s.param)
+                out[f"state.{fqn}.exp_avg_sq"] = _to_dtensor(eng, v[sl].view(s.shape), s.param)
+                out[f"state.{fqn}.step"] = torch.tensor(float(eng.step_count))
+                g = groups.get(s.group, groups["normal"])
+                hyper = {"lr": g["lr"], "betas": tuple(a.get("betas", (0.9, 0.999))), "eps": a.get("eps", 1e-8),
+                         "weight_decay": 0.0 if s.group == "no_weight_decay" else a.get("weight_decay", 1e-2),
+                         "initial_lr": g.get("initial_lr", g["lr"])}
+                for k in _GROUP_KEYS:
+                    out[f"param_groups.{fqn}.{k}"] = hyper[k]
+    return out
+
+
+def load_optimizer_state_dict(model_container, optimizer_container, state: dict) -> None:
+    for wrapper, opt in zip(model_container, optimizer_container):
+        eng = wrapper.engine
+        for which in ("exp_avg", "exp_avg_sq"):
+            plain = {}
+            for u in eng.units:
+                for s in u.slots:
+                    key = f"state.model.{s.name}.{which}"
+                    if key in state:
+                        plain[s.name] = _from_saved(state[key], eng)
+            eng.load_full_state_dict(plain, which)
+        steps = [float(v) for k, v in state.items() if k.endswith(".step")]
+        if steps:
+            eng.step_count = int(max(steps))
+        for g in opt.param_groups:
+            for u in eng.units:
+                for s in u.slots:
+                    if s.group == g["name"] and f"param_groups.model.{s.name}.lr" in state:
+                        g["lr"] = state[f"param_groups.model.{s.name}.lr"]
+                        g["initial_lr"] = state.get(f"param_groups.model.{s.name}.initial_lr", g["lr"])
+                        break
+                else:
+                    continue
+                break
+
+
+# ---------------------------------------------------------------------------------------------- save
+def save_checkpoint(args: TrainingArgs, model_container: ModelContainer,
+                    optimizer_container: OptimizerContainer | None, lr_scheduler_container: LRSchedulerContainer | None,
+                    train_dataloader, experiments_tracker, iteration: int, metadata: dict | None = None) -> None:
+    global _FUTURE, _PENDING_PUBLISH
+    ensure_last_checkpoint_is_saved()
+    root = args.save_args.save_path
+    final = _base(root, iteration)
+    tmp = final + ".tmp"
+    rank = ProcessGroupManager.get_global_rank()
+    if rank == 0:
+        shutil.rmtree(tmp, ignore_errors=True)
+        os.makedirs(tmp, exist_ok=True)
+    ProcessGroupManager.barrier()
+    if lr_scheduler_container is not None:
+        os.makedirs(os.path.join(tmp, "lr_scheduler"), exist_ok=True)
+        torch.save([s.state_dict() for s in lr_scheduler_container], _rank_file(tmp, "lr_scheduler", rank))
+    os.makedirs(os.path.join(tmp, "rng_state"), exist_ok=True)
+    torch.save({"random_rng_state": random.getstate(), "np_rng_state": np.random.get_state(),
+                "torch_rng_state": torch.get_rng_state(),
+                "accelerator_rng_state": torch.cuda.get_rng_state() if torch.cuda.is_available() else None},
+               _rank_file(tmp, "rng_state", rank))
+    if train_dataloader is not None and hasattr(train_dataloader, "state_dict"):
+        os.makedirs(os.path.join(tmp, "dataloader"), exist_ok=True)
+        torch.save(train_dataloader.state_dict(),
+                   _rank_file(tmp, "dataloader", ProcessGroupManager.get_data_loading_rank()))
+    if rank == 0:
+        if experiments_tracker is not None:
+            json.dump(experiments_tracker.state_dict(), open(os.path.join(tmp, "experiments_tracker.json"), "w"),
+                      indent=4)
+        meta = dict(metadata or {})
+        meta.setdefault("commit_id", _commit_id())
+        meta["accelerator"] = Accelerator.get_accelerator().value
+        json.dump(meta, open(os.path.join(tmp, "metadata.json"), "w"), indent=4)
+        yaml.dump(args.to_dict(), open(os.path.join(tmp, "training_config.yml"), "w"), indent=2)
+    save_opt = args.save_args.save_optimizer and optimizer_container is not None
+
+    def publish() -> None:
+        ProcessGroupManager.barrier()
+        if rank == 0:
+            shutil.rmtree(final, ignore_errors=True)
+            os.replace(tmp, final)
+            latest_tmp = _latest_file(root) + ".tmp"
+            with open(latest_tmp, "w") as f:
+                json.dump({"latest_checkpointed_iteration": iteration}, f, indent=4)
+                f.flush()
+                os.fsync(f.fileno())
+            os.replace(latest_tmp, _latest_file(root))
+        ProcessGroupManager.barrier()
+        log_rank_0(logging.INFO, f"checkpoint saved at {iteration}")
+        if os.path.exists(os.path.join(root, _KILLSWITCH)):
+            log_rank_0(logging.WARNING, "KILLSWITCH found: exiting after checkpoint")
+            ProcessGroupManager.destroy_process_groups()
+            raise SystemExit(0)
+
+    if args.save_args.async_checkpointing:
+        state = {"model": model_state_dict(model_container)}
+        if save_opt:
+            state["optimizer"] = optimizer_state_dict(model_container, optimizer_container)
+        _FUTURE = dcp.async_save({"state": state}, checkpoint_id=os.path.join(tmp, "model_optimizer"))
+        _PENDING_PUBLISH = publish
+        return
+    dcp.save({"state": model_state_dict(model_container)}, checkpoint_id=os.path.join(tmp, "model"))
+    if save_opt:
+        dcp.save({"state": optimizer_state_dict(model_container, optimizer_container)},
+                 checkpoint_id=os.path.join(tmp, "optimizer"))
+    publish()
+
+
+# ---------------------------------------------------------------------------------------------- load
+def _resolve_iteration(load_path: str, iteration: int | None) -> int:
+    if iteration is not None:
+        return iteration
+    return json.load(open(_latest_file(load_path)))["latest_checkpointed_iteration"]
+
+
+def load_checkpoint_for_training(args: TrainingArgs, args_class: type[TrainingArgs | DistillationArgs],
+                                 model_container: ModelContainer, optimizer_container: OptimizerContainer,
+                                 lr_scheduler_container: LRSchedulerContainer, train_dataloader):
+    """Restores model (+ optimizer, LR schedule, RNG, dataloader) state; returns ``(iteration, metadata,
+    experiments-tracker state)``."""
+    la = args.load_args
+    if la is None or la.load_path is None:
+        return 0, None, None
+    iteration = _resolve_iteration(la.load_path, la.iteration)
+    base = _base(la.load_path, iteration)
+    saved_args = args_class(**load_yaml(os.path.join(base, "training_config.yml")))
+    log_rank_0(logging.INFO, f"loading checkpoint saved at {base}")
+    rank = ProcessGroupManager.get_global_rank()
+    if saved_args.save_args.async_checkpointing:
+        state = {"model": model_state_dict(model_container)}
+        if la.load_optimizer:
+            state["optimizer"] = optimizer_state_dict(model_container, optimizer_container)
+        wrapped = {"state": state}
+        dcp.load(wrapped, checkpoint_id=os.path.join(base, "model_optimizer"))
+        load_model_state_dict(model_container, wrapped["state"]["model"])
+        if la.load_optimizer:
+            load_optimizer_state_dict(model_container, optimizer_container, wrapped["state"]["optimizer"])
+    else:
+        wrapped = {"state": model_state_dict(model_container)}
+        dcp.load(wrapped, checkpoint_id=os.path.join(base, "model"))
+        load_model_state_dict(model_container, wrapped["state"])
+        if la.load_optimizer:
+            wrapped = {"state": optimizer_state_dict(model_container, optimizer_container)}
+            dcp.load(wrapped, checkpoint_id=os.path.join(base, "optimizer"))
+            load_optimizer_state_dict(model_container, optimizer_container, wrapped["state"])
+    if la.load_lr_scheduler:
+        assert la.load_optimizer, "load_lr_scheduler requires loading of optimizer"
+        f = _rank_file(base, "lr_scheduler", rank)
+        if not os.path.exists(f):
+            f = _rank_file(base, "lr_scheduler", 0)
+        for sched, sd in zip(lr_scheduler_container, torch.load(f, weights_only=False)):
+            sched.load_state_dict(sd)
+    elif la.resume_learning_rate:
+        # rebuild the schedule position from the iteration, starting from the configured base learning rate
+        for sched in lr_scheduler_container:
+            sched.last_epoch = (iteration if la.load_starting_iteration else 0) - 1
+            sched.step()
+    if la.load_rng_state:
+        f = _rank_file(base, "rng_state", rank)
+        if os.path.exists(f):
+            st = torch.load(f, weights_only=False)
+            random.setstate(st["random_rng_state"])
+            np.random.set_state(st["np_rng_state"])
+            torch.set_rng_state(st["torch_rng_state"])
+            if torch.cuda.is_available() and st.get("accelerator_rng_state") is not None:
+                torch.cuda.set_rng_state(st["accelerator_rng_state"])
+    metadata = json.load(open(os.path.join(base, "metadata.json")))
+    if la.load_dataloader_state and train_dataloader is not None and hasattr(train_dataloader, "load_state_dict"):
+        f = _rank_file(base, "dataloader", ProcessGroupManager.get_data_loading_rank())
+        if os.path.exists(f):
+            train_dataloader.load_state_dict(torch.load(f, weights_only=False))
+    tracker = None
+    tf = os.path.join(base, "experiments_tracker.json")
+    if la.load_experiments_tracker_state and os.path.exists(tf):
+        tracker = json.load(open(tf))
+    return (iteration if la.load_starting_iteration else 0), metadata, tracker
+
+
+def read_full_model_state(load_path: str, iteration: int | None = None) -> tuple[dict[str, torch.Tensor], dict, int]:
+    """Reads a (possibly sharded) checkpoint into full CPU tensors without any process group.  Returns
+    ``(state with keys "model.<fqn>", saved training config dict, iteration)``."""
+    from torch.distributed.checkpoint import FileSystemReader
+    from torch.distributed.checkpoint.default_planner import _EmptyStateDictLoadPlanner
+    from torch.distributed.checkpoint.state_dict_loader import _load_state_dict
+
+    iteration = _resolve_iteration(load_path, iteration)
+    base = _base(load_path, iteration)
+    cfg = load_yaml(os.path.join(base, "training_config.yml"))
+    state: dict = {}
+    if cfg["save_args"].get("async_checkpointing"):
+        _load_state_dict(state, storage_reader=FileSystemReader(os.path.join(base, "model_optimizer")),
+                         planner=_EmptyStateDictLoadPlanner(), no_dist=True)
+        state = state["state"]["model"]
+    else:
+        _load_state_dict(state, storage_reader=FileSystemReader(os.path.join(base, "model")),
+                         planner=_EmptyStateDictLoadPlanner(), no_dist=True)
+        state = state["state"]
+    return state, cfg, iteration
+
+
+def load_checkpoint_and_unshard(args: UnshardingArgs):
+    """Rebuilds the unsharded single-process model from a training checkpoint.  Returns
+    ``(model wrapper, training args of the checkpoint, full state dict)``."""
+    from .model_wrapper import get_model_container
+
+    state, cfg, iteration = read_full_model_state(args.load_args.load_path, args.load_args.iteration)
+    log_rank_0(logging.INFO, f"loading checkpoint saved at {_base(args.load_args.load_path, iteration)}")
+    if "teacher_args" in cfg:
+        cfg["tuning_args"]["tuning_method"] = "pretraining"
+        cfg.pop("teacher_args")
+    saved = TrainingArgs(**cfg)
+    if args.mixed_precision_args is not None:
+        saved.mixed_precision_args = args.mixed_precision_args
+    P = ProcessGroupManager
+    with P.set_dummy_tensor_parallel_rank(0), P.set_dummy_tensor_parallel_world_size(1), \
+            P.set_dummy_pipeline_parallel_rank(0), P.set_dummy_pipeline_parallel_world_size(1), \
+            saved.distributed_args.temporary_argument_value("num_pipeline_stages", 1), \
+            saved.model_args.temporary_argument_value("efficient_initialization", False):
+        wrapper = get_model_container(saved, efficient_initialization=False, keep_in_fp32=False)[0]
+    dtype_name = saved.mixed_precision_args.dtype
+    dtype = torch.bfloat16 if dtype_name == "fp8" else string_to_torch_dtype(dtype_name)
+    plain = {k[len("model."):]: v.to(dtype) for k, v in state.items() if k.startswith("model.")}
+    wrapper.model.to(dtype)
+    wrapper.model.load_state_dict(plain)
+    return wrapper, saved, plain

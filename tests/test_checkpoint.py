@@ -1,0 +1,148 @@
+"""Checkpoint layout, bit-exact resume, unshard, and resharding of a 2-rank checkpoint into one process (CPU)."""
+
+import json
+import os
+
+import numpy as np
+import torch
+
+from .dist_utils import run_distributed
+
+VOCAB, SEQ, MBS = 512, 32, 2
+
+
+def _args(save_path, load_path=None, stage=3):
+    from lm_engine_b200.arguments import TrainingArgs
+    from lm_engine_b200.models import dense_config
+
+    cfg = dense_config(vocab_size=VOCAB, hidden_size=64, num_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                       intermediate_size=128, max_position_embeddings=SEQ).to_dict()
+    d = dict(
+        model_args={"pretrained_config": cfg, "efficient_initialization": True},
+        tuning_args={"tuning_method": "pretraining"},
+        optimizer_args={"class_args": {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "eps": 1e-10}},
+        lr_scheduler_args={"num_warmup_steps": 2, "lr_decay_style": "cosine"},
+        datasets=[{"class_name": "SyntheticDataset", "data_name": "syn", "class_args": {"sequence_length": SEQ}}],
+        save_args={"save_path": save_path, "save_interval": 100},
+        training_parameters={"num_training_steps": 20, "micro_batch_size": MBS, "gradient_accumulation_steps": 1,
+                             "eval_during_training": False},
+        distributed_args={"stage": stage, "gradient_checkpointing_method": "block"})
+    if load_path is not None:
+        d["load_args"] = {"load_path": load_path}
+    return TrainingArgs(**d)
+
+
+def _build(args):
+    from lm_engine_b200.distributed import wrap_model_container_for_distributed_training
+    from lm_engine_b200.model_wrapper import get_model_container
+    from lm_engine_b200.optimization import get_optimizer_container, get_scheduler_container
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    ProcessGroupManager(zero_stage=args.distributed_args.stage)
+    args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
+    models = get_model_container(args)
+    models, _ = wrap_model_container_for_distributed_training(args, models)
+    opts = get_optimizer_container("TorchAdamW", args.optimizer_args.class_args, models, None, max_grad_norm=1.0)
+    ls = args.lr_scheduler_args
+    scheds = get_scheduler_container(models, opts, ls.num_warmup_steps, 0, None, 20, ls.lr_decay_style,
+                                     ls.lr_decay_factor, {})
+    return models, opts, scheds
+
+
+def _steps(models, opts, scheds, batches):
+    from lm_engine_b200.train import train_step_without_pipeline_parallel
+
+    out = []
+    it = iter([{"text": b} for b in batches])
+    for _ in batches:
+        m = train_step_without_pipeline_parallel(models, opts, scheds, it, 1, 1.0)
+        out.append((float(m["loss"]), float(m["grad_norm"])))
+    return out
+
+
+def _data(n, rank=0, world=1):
+    g = torch.Generator().manual_seed(3)
+    d = torch.randint(0, VOCAB, (n, world * MBS, SEQ + 1), generator=g)
+    return [d[i, rank * MBS:(rank + 1) * MBS] for i in range(n)]
+
+
+def test_layout_and_bit_exact_resume(tmp_path):
+    from lm_engine_b200.arguments import TrainingArgs
+    from lm_engine_b200.checkpointing import load_checkpoint_for_training, save_checkpoint
+
+    path = str(tmp_path / "ckpt")
+    args = _args(path)
+    models, opts, scheds = _build(args)
+    data = _data(6)
+    _steps(models, opts, scheds, data[:3])
+    save_checkpoint(args, models, opts, scheds, None, None, 3, {"consumed_samples": 3 * MBS})
+    base = os.path.join(path, "global_step3")
+    for sub in ("model/.metadata", "optimizer/.metadata", "lr_scheduler/lr_scheduler-0.pt",
+                "rng_state/rng_state-0.pt", "metadata.json", "training_config.yml"):
+        assert os.path.exists(os.path.join(base, sub)), sub
+    assert json.load(open(os.path.join(path, "latest_checkpointed_iteration.json"))) == {
+        "latest_checkpointed_iteration": 3}
+    assert json.load(open(os.path.join(base, "metadata.json")))["consumed_samples"] == 3 * MBS
+    cont = _steps(models, opts, scheds, data[3:])
+    # fresh objects, different seed, then resume
+    args2 = _args(path, load_path=path)
+    args2.random_args.seed = 999
+    models2, opts2, scheds2 = _build(args2)
+    it, meta, _ = load_checkpoint_for_training(args2, TrainingArgs, models2, opts2, scheds2, None)
+    assert it == 3 and meta["consumed_samples"] == 3 * MBS
+    resumed = _steps(models2, opts2, scheds2, data[3:])
+    assert resumed == cont, (resumed, cont)
+
+
+def test_unshard_roundtrip(tmp_path):
+    from lm_engine_b200.arguments import UnshardingArgs
+    from lm_engine_b200.checkpointing import load_checkpoint_and_unshard, read_full_model_state, save_checkpoint
+    from lm_engine_b200.utils import SafeTensorsWeightsManager
+
+    path = str(tmp_path / "ckpt")
+    args = _args(path)
+    models, opts, scheds = _build(args)
+    _steps(models, opts, scheds, _data(2))
+    save_checkpoint(args, models, opts, scheds, None, None, 2, {})
+    state, cfg, it = read_full_model_state(path)
+    want = models[0].engine.full_state_dict()
+    assert it == 2 and set(state) == {f"model.{k}" for k in want}
+    for k, v in want.items():
+        assert torch.equal(state[f"model.{k}"], v)
+    wrapper, saved, plain = load_checkpoint_and_unshard(
+        UnshardingArgs(load_args={"load_path": path}, unsharded_path=str(tmp_path / "hf")))
+    wrapper.save_pretrained(str(tmp_path / "hf"), state_dict=plain)
+    mgr = SafeTensorsWeightsManager(str(tmp_path / "hf"))
+    for k, v in want.items():
+        assert torch.equal(mgr.get_tensor(k), v)
+    assert os.path.exists(tmp_path / "hf" / "config.json")
+
+
+def _save_two_ranks(rank, world, path):
+    from lm_engine_b200.checkpointing import save_checkpoint
+
+    args = _args(path)
+    models, opts, scheds = _build(args)
+    _steps(models, opts, scheds, _data(2, rank, world))
+    save_checkpoint(args, models, opts, scheds, None, None, 2, {})
+    return {k: v.numpy().copy() for k, v in models[0].engine.full_state_dict().items()}
+
+
+def test_two_rank_checkpoint_reshards_to_one(tmp_path):
+    from lm_engine_b200.arguments import TrainingArgs
+    from lm_engine_b200.checkpointing import load_checkpoint_for_training, read_full_model_state
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    path = str(tmp_path / "ckpt")
+    outs = run_distributed(_save_two_ranks, 2, path)
+    state, _, _ = read_full_model_state(path)
+    for k, v in outs[0].items():
+        assert np.array_equal(state[f"model.{k}"].numpy(), v), k
+    ProcessGroupManager.destroy_process_groups()
+    args = _args(path, load_path=path)
+    models, opts, scheds = _build(args)
+    load_checkpoint_for_training(args, TrainingArgs, models, opts, scheds, None)
+    got = models[0].engine.full_state_dict()
+    for k, v in outs[0].items():
+        assert np.array_equal(got[k].numpy(), v), k
+    assert models[0].engine.step_count == 2
