@@ -132,6 +132,12 @@ def shard_model(wrapper, *, stage: int, dtype: torch.dtype, communication_dtype:
             return engine.run_unit("embed", lambda h: inner(h), hidden)
 
         model.compute_logits = compute_logits
+        inner_loss = model.compute_lm_loss
+
+        def compute_lm_loss(hidden, labels, **kw):
+            return engine.run_unit("embed", lambda h, l: inner_loss(h, l, **kw), hidden, labels)
+
+        model.compute_lm_loss = compute_lm_loss
     wrapper.engine = engine
     return engine
 

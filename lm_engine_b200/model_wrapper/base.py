@@ -96,13 +96,14 @@ class ModelWrapper(nn.Module):
                  cu_seqlens: torch.Tensor | None = None, lm_loss_multiplier: float = 1) -> dict[str, torch.Tensor]:
         tp = ProcessGroupManager.is_tensor_parallel_enabled()
         fused = model_outputs.logits is None
-        lm_loss = get_autoregressive_language_modeling_loss(
-            lm_logits=None if fused else model_outputs.logits, labels=labels,
-            hidden_states=model_outputs.last_hidden_state if fused else None,
-            vocab_weight=self.model.get_output_embeddings().weight if fused else None, cu_seqlens=cu_seqlens,
-            use_padding_free_transformer=self.use_padding_free_transformer, reduction="sum",
-            shift_logits_and_labels=shift_logits_and_labels, tensor_parallel_enabled=tp,
-            vocab_size=self.config.vocab_size)
+        kw = dict(cu_seqlens=cu_seqlens, use_padding_free_transformer=self.use_padding_free_transformer,
+                  reduction="sum", shift_logits_and_labels=shift_logits_and_labels)
+        if fused:
+            lm_loss = self.model.compute_lm_loss(model_outputs.last_hidden_state, labels, **kw)
+        else:
+            lm_loss = get_autoregressive_language_modeling_loss(
+                lm_logits=model_outputs.logits, labels=labels, tensor_parallel_enabled=tp,
+                vocab_size=self.config.vocab_size, **kw)
         lm_loss = lm_loss * lm_loss_multiplier
         aux = getattr(model_outputs, "aux_loss", 0)
         if is_aux_loss_zero(aux):

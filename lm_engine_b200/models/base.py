@@ -241,6 +241,13 @@ class CausalLM(nn.Module):
             logits = logits * (1 / self.m_width)
         return logits
 
+    def compute_lm_loss(self, hidden_states: torch.Tensor, labels: torch.Tensor, **loss_kwargs) -> torch.Tensor:
+        """Summed cross entropy straight from the final hidden states (LM head evaluated in token chunks)."""
+        if self._tied_word_embeddings:
+            wte = self.transformer.wte
+            return LMHead.loss_with_weight(wte, hidden_states, wte.weight, labels, **loss_kwargs)
+        return self.lm_head(hidden_states, labels=labels, loss_kwargs=loss_kwargs)
+
     def forward(self, input_ids: torch.Tensor | None = None, cache_params: GenerationCache | None = None,
                 attention_mask_info: AttentionMaskInfo | None = None, position_info: PositionInfo | None = None,
                 output_parallel_lm_logits: bool = False, pipeline_parallel_input: PipelineParallelInput | None = None,

@@ -63,6 +63,24 @@ class ParameterizedEmbedding(nn.Module):
             return tp_comm.scatter_to_sequence_parallel(x, tp_comm.seq_dim(x, self.use_padding_free_transformer))
         return tp_comm.reduce_from_tensor_parallel(x)
 
+    # ---- use of the matrix as an output projection (LM head, or tied embeddings)
+    def _tp_input(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_world_size > 1:
+            if self.sequence_parallel:
+                return tp_comm.gather_from_sequence_parallel(x, tp_comm.seq_dim(x, self.use_padding_free_transformer))
+            return tp_comm.copy_to_tensor_parallel(x)
+        return x
+
+    def compute_with_weight(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        return ops.linear(self._tp_input(x), weight)
+
+    def loss_with_weight(self, x: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, **kw) -> torch.Tensor:
+        from ...loss import get_autoregressive_language_modeling_loss
+
+        return get_autoregressive_language_modeling_loss(
+            lm_logits=None, labels=labels, hidden_states=self._tp_input(x), vocab_weight=weight,
+            tensor_parallel_enabled=self.tp_world_size > 1, vocab_size=self.num_embeddings, **kw)
+
     def extra_repr(self) -> str:
         return f"{self.num_embeddings}, {self.embedding_dim}"
 
@@ -70,13 +88,11 @@ class ParameterizedEmbedding(nn.Module):
 class LMHead(ParameterizedEmbedding):
     """Projects hidden states onto the (local slice of the) vocabulary; logits stay vocab-sharded under TP."""
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.compute_with_weight(x, self.weight)
+    def forward(self, x: torch.Tensor, labels: torch.Tensor | None = None,
+                loss_kwargs: dict | None = None) -> torch.Tensor:
+        """Logits, or - when ``labels`` are given - the summed cross entropy computed chunk by chunk so that the
+        full logits never exist (the weight is only guaranteed to be materialised inside this call)."""
+        if labels is None:
+            return self.compute_with_weight(x, self.weight)
+        return self.loss_with_weight(x, self.weight, labels, **(loss_kwargs or {}))
 
-    def compute_with_weight(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-        if self.tp_world_size > 1:
-            if self.sequence_parallel:
-                x = tp_comm.gather_from_sequence_parallel(x, tp_comm.seq_dim(x, self.use_padding_free_transformer))
-            else:
-                x = tp_comm.copy_to_tensor_parallel(x)
-        return ops.linear(x, weight)

@@ -74,3 +74,43 @@ def test_four_ranks_hsdp():
     for k, v in ref_params.items():
         assert np.allclose(outs[3][2][k], v, atol=2e-5, rtol=1e-4), k
     assert abs(outs[0][1][0] - ref_norms[0]) / ref_norms[0] < 2e-3
+
+
+def _train_fused_ce(rank, world, tied):
+    from lm_engine_b200.distributed import shard_model
+    from lm_engine_b200.kernels import enable_kernels
+    from lm_engine_b200.enums import Kernel
+    from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+    from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    ProcessGroupManager(zero_stage=3)
+    cfg = _cfg().to_dict()
+    cfg["tie_word_embeddings"] = tied
+    w = ModelWrapperForPretraining(pretrained_config=cfg, micro_batch_size=2, sequence_length=SEQ,
+                                   efficient_initialization=True)
+    eng = shard_model(w, stage=3, dtype=torch.float32, communication_dtype=None, seed=11)
+    opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "eps": 1e-10},
+                           None, False, 1.0)
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, VOCAB, (world * 2, SEQ + 1), generator=g)[rank * 2:(rank + 1) * 2]
+    res = []
+    for fused in (False, True):
+        opt.zero_grad()
+        kernels = [Kernel.fused_linear_cross_entropy] if fused else []
+        with enable_kernels(kernels):
+            out = w(data, lm_loss_multiplier=1 / (2 * SEQ))
+            out["loss"].backward()
+        eng.finish_backward()
+        grads = eng.full_state_dict("grad")
+        res.append((float(out["loss"].detach()), {k: v.numpy().copy() for k, v in grads.items()}))
+    return res
+
+
+@pytest.mark.parametrize("tied", [False, True])
+def test_fused_linear_cross_entropy_under_zero3(tied):
+    outs = run_distributed(_train_fused_ce, 2, tied)
+    for (l0, g0), (l1, g1) in outs:
+        assert abs(l0 - l1) < 1e-5
+        for k in g0:
+            assert np.allclose(g0[k], g1[k], atol=1e-6, rtol=1e-4), k
