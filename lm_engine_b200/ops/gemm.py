@@ -25,6 +25,20 @@ from . import _lib
 
 # "1cta": one CTA per 128 x 256 tile; "2cta": CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2)
 DEFAULT_IMPL = os.environ.get("LME_GEMM", "1cta")
+# SMs left free for communication kernels that run concurrently with the persistent GEMMs (set by the sharding
+# runtime when collectives overlap compute).  A persistent kernel that cannot place all of its CTAs at once would
+# otherwise wait for the collective to release its SMs.
+RESERVED_SMS = 0
+_NUM_SMS: dict[int, int] = {}
+
+
+def _max_ctas(device: torch.device) -> int:
+    if RESERVED_SMS <= 0:
+        return 0
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _NUM_SMS:
+        _NUM_SMS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return max(_NUM_SMS[idx] - RESERVED_SMS, 8)
 
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
@@ -115,7 +129,8 @@ def gemm(
     rc = fn(
         a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0),
         M, N, K, flags, _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
-        _lib.ptr(preact), preact.stride(0) if preact is not None else 0, max_ctas, _lib.stream_ptr(),
+        _lib.ptr(preact), preact.stride(0) if preact is not None else 0, max_ctas or _max_ctas(a.device),
+        _lib.stream_ptr(),
     )
     _lib.check(rc, f"lme_gemm_bf16 M={M} N={N} K={K}")
     _lib.count_launch()

@@ -103,6 +103,15 @@ class ShardedUnit:
         if self.group_ranges:
             self.group_ranges[-1].end = self.numel
         self.shard_size = self.numel // self.world
+        # element ranges of the flat buffer not covered by any parameter (alignment padding)
+        self.gaps: list[tuple[int, int]] = []
+        cursor = 0
+        for sl in sorted(self.slots, key=lambda t: t.offset):
+            if sl.offset > cursor:
+                self.gaps.append((cursor, sl.offset))
+            cursor = sl.offset + sl.numel
+        if cursor < self.numel:
+            self.gaps.append((cursor, self.numel))
         self.state_lo = self.rank * self.shard_size if self.shard_state else 0
         self.state_hi = self.state_lo + (self.shard_size if self.shard_state else self.numel)
         # ---- storage
@@ -122,6 +131,7 @@ class ShardedUnit:
         self.ag_event: torch.cuda.Event | None = None
         self.rs_event: torch.cuda.Event | None = None
         self.grad_ready = False
+        self.grad_shard_fresh = True   # next reduced gradient overwrites grad_shard instead of accumulating
         self.pending_backward = 0      # forward uses of the current step whose backward has not run yet
         self.keep_unsharded = False    # stay gathered between forward and backward (tied embedding)
 
@@ -251,7 +261,13 @@ class FSDPEngine:
         if self.is_cuda:
             self.ag_stream = torch.cuda.Stream(self.device)
             self.rs_stream = torch.cuda.Stream(self.device)
+            if self.world > 1 or self.replica_group is not None:
+                import os
+                import sys
+
+                sys.modules["lm_engine_b200.ops.gemm"].RESERVED_SMS = int(os.environ.get("LME_COMM_SMS", "16"))
         self._anchor = torch.zeros(1, device=self.device, requires_grad=True)
+        self._buffer_events: dict[int, torch.cuda.Event] = {}
         self._inflight: dict[str, torch.Tensor] = {}
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -438,11 +454,16 @@ class FSDPEngine:
             self._all_gather(prv)
         if u.main_grad is None:
             buf = self._take(self._grad_pool, "g", u, self.grad_dtype)
-            # a buffer of the pool may still be read by an earlier reduce-scatter
-            if self.is_cuda:
-                torch.cuda.current_stream().wait_stream(self.rs_stream)
-            buf.zero_()
+            # the buffer may still be read by the reduce-scatter of the unit that used it last (two units ago)
+            ev = self._buffer_events.get(buf.data_ptr())
+            if self.is_cuda and ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+            # parameters overwrite on their first gradient write; only the padding between them is cleared
+            for lo, hi in u.gaps:
+                buf[lo:hi].zero_()
             u.bind_grads(buf)
+            for s in u.slots:
+                s.param.main_grad_stale = True
 
     def post_backward(self, u: ShardedUnit) -> None:
         u.pending_backward -= 1
@@ -462,25 +483,37 @@ class FSDPEngine:
             u.grad_ready = True
             return
         full = u.main_grad
+        for sl in u.slots:   # parameters that received no gradient in this pass
+            if getattr(sl.param, "main_grad_stale", False) and self.world > 1 and self.stage != 0:
+                sl.param.main_grad.zero_()
+                sl.param.main_grad_stale = False
+        avg = dist.ReduceOp.AVG if self.is_cuda else dist.ReduceOp.SUM
         dp_total = ProcessGroupManager.get_data_parallel_world_size()
 
         def run() -> None:
             if self.stage == 0 or self.world == 1:
                 if self.replica_group is not None:
-                    full.div_(dp_total)
-                    dist.all_reduce(full, group=self.replica_group)
+                    if not self.is_cuda:
+                        full.div_(dp_total)
+                    dist.all_reduce(full, op=avg, group=self.replica_group)
                 return
-            full.div_(dp_total)
             out = torch.empty(u.shard_size, dtype=full.dtype, device=self.device)
             if self.is_cuda:
-                dist.reduce_scatter_tensor(out, full, group=self.shard_group)
+                dist.reduce_scatter_tensor(out, full, op=avg, group=self.shard_group)
             else:
-                tmp = full.clone()
+                tmp = full / dp_total
                 dist.all_reduce(tmp, group=self.shard_group)
                 out.copy_(tmp[u.rank * u.shard_size:(u.rank + 1) * u.shard_size])
             if self.replica_group is not None:
-                dist.all_reduce(out, group=self.replica_group)
-            u.grad_shard.add_(out)
+                if self.is_cuda:
+                    dist.all_reduce(out, op=avg, group=self.replica_group)
+                else:
+                    dist.all_reduce(out, group=self.replica_group)
+            if u.grad_shard_fresh:
+                u.grad_shard.copy_(out)
+                u.grad_shard_fresh = False
+            else:
+                u.grad_shard.add_(out)
 
         if self.is_cuda:
             self.rs_stream.wait_stream(torch.cuda.current_stream())
@@ -488,6 +521,7 @@ class FSDPEngine:
                 run()
                 u.rs_event = torch.cuda.Event()
                 u.rs_event.record(self.rs_stream)
+                self._buffer_events[full.data_ptr()] = u.rs_event
         else:
             run()
         if self.stage != 0 and self.world > 1:
@@ -518,7 +552,7 @@ class FSDPEngine:
                 for s in u.slots:
                     s.param.main_grad_stale = True
             elif u.grad_shard is not None:
-                u.grad_shard.zero_()
+                u.grad_shard_fresh = True
             u.grad_ready = False
             u.pending_backward = 0
         self.micro_step = 0
@@ -534,6 +568,11 @@ class FSDPEngine:
                     s.param.main_grad_stale = False
         if self.is_cuda:
             torch.cuda.current_stream().wait_stream(self.rs_stream)
+            torch.cuda.current_stream().wait_stream(self.ag_stream)
+        for u in self.units:
+            if u.grad_shard_fresh and u.main_grad is None and u.grad_shard is not None:
+                u.grad_shard.zero_()
+            u.grad_shard_fresh = False if u.main_grad is None else u.grad_shard_fresh
 
     @torch.no_grad()
     def clip_and_step(self, *, lr: float, lr_by_group: dict[str, float] | None = None, betas=(0.9, 0.95),
