@@ -1,0 +1,127 @@
+"""Mamba-2 state-space-duality (SSD) scan.
+
+``y_t = C_t . h_t + D x_t``,  ``h_t = exp(dt_t A) h_{t-1} + dt_t B_t (x) x_t``  per head, evaluated chunk by chunk:
+intra-chunk as a masked ``(C B^T) . decay`` product (tensor-core shaped), chunk summaries ``S_c``, a short sequential
+pass over chunk boundaries, and the contribution of the carried state.  Same results as the token-by-token
+recurrence (and as ``mamba_chunk_scan_combined`` / the reference's ``mamba2_torch``,
+lm_engine/modeling_utils/sequence_mixer_blocks/mamba2/op.py:225-457) without materialising a
+``[chunks, L, L, heads, state]`` tensor.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def ssd_recurrent_step(x, dt, A, B, C, D, h):
+    """One token.  x ``[b, N, P]``, dt ``[b, N]``, B/C ``[b, G, Sd]``, h ``[b, N, P, Sd]`` (fp32)."""
+    N, G = x.size(1), B.size(1)
+    Bh = B.float().repeat_interleave(N // G, dim=1)
+    Ch = C.float().repeat_interleave(N // G, dim=1)
+    dA = torch.exp(dt.float() * A.float())[..., None, None]
+    h = h.float() * dA + (dt.float()[..., None] * x.float())[..., None] * Bh[:, :, None, :]
+    y = (h * Ch[:, :, None, :]).sum(-1) + D.float()[None, :, None] * x.float()
+    return y.to(x.dtype), h
+
+
+def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
+    """x ``[b, S, N, P]``, dt ``[b, S, N]`` (already softplus'ed), A ``[N]`` (negative), B/C ``[b, S, G, Sd]``,
+    D ``[N]``.  Returns ``(y [b, S, N, P], final_state [b, N, P, Sd] fp32)``."""
+    b, S, N, P = x.shape
+    G, Sd = B.shape[-2:]
+    dtype = x.dtype
+    L = chunk_size
+    pad = (L - S % L) % L
+    xf, dtf, Bf, Cf = x.float(), dt.float(), B.float(), C.float()
+    if pad:
+        xf = torch.nn.functional.pad(xf, (0, 0, 0, 0, 0, pad))
+        dtf = torch.nn.functional.pad(dtf, (0, 0, 0, pad))
+        Bf = torch.nn.functional.pad(Bf, (0, 0, 0, 0, 0, pad))
+        Cf = torch.nn.functional.pad(Cf, (0, 0, 0, 0, 0, pad))
+    nc = (S + pad) // L
+    xc = xf.view(b, nc, L, N, P)
+    dtc = dtf.view(b, nc, L, N)
+    Bc = Bf.view(b, nc, L, G, Sd)
+    Cc = Cf.view(b, nc, L, G, Sd)
+    rep = N // G
+    dA = dtc * A.float()                                      # [b, nc, L, N]
+    cum = torch.cumsum(dA, dim=2)
+    # ---- intra-chunk: y[t] = sum_{s<=t} exp(cum[t]-cum[s]) (C_t.B_s) dt_s x_s
+    CB = torch.einsum("bclgn,bcsgn->bcgls", Cc, Bc)           # [b, nc, G, L, L]
+    CB = CB.repeat_interleave(rep, dim=2)                     # [b, nc, N, L, L]
+    ct = cum.permute(0, 1, 3, 2)                              # [b, nc, N, L]
+    seg = ct[..., :, None] - ct[..., None, :]                 # cum[t] - cum[s]
+    causal = torch.ones(L, L, dtype=torch.bool, device=x.device).tril()
+    decay = torch.exp(seg.masked_fill(~causal, float("-inf")))
+    xdt = xc * dtc[..., None]                                 # [b, nc, L, N, P]
+    y = torch.einsum("bcnls,bcsnp->bclnp", CB * decay, xdt)
+    # ---- chunk summaries: S_c = sum_s exp(cum[L-1]-cum[s]) B_s (x) (dt_s x_s)
+    tail = torch.exp(cum[:, :, -1:, :] - cum)                 # [b, nc, L, N]
+    Bh = Bc.repeat_interleave(rep, dim=3)                     # [b, nc, L, N, Sd]
+    states = torch.einsum("bcln,bclnp,bclns->bcnps", tail, xdt, Bh)
+    # ---- boundary states: h_c = exp(sum dA of chunk c-1) h_{c-1} + S_{c-1}
+    h = (torch.zeros(b, N, P, Sd, dtype=torch.float32, device=x.device) if initial_state is None
+         else initial_state.float())
+    chunk_decay = torch.exp(cum[:, :, -1, :])                 # [b, nc, N]
+    starts = []
+    for c in range(nc):
+        starts.append(h)
+        h = h * chunk_decay[:, c, :, None, None] + states[:, c]
+    h0 = torch.stack(starts, dim=1)                           # [b, nc, N, P, Sd] state at chunk start
+    # ---- carried state contribution: exp(cum[t]) C_t . h_c
+    Ch = Cc.repeat_interleave(rep, dim=3)
+    y = y + torch.einsum("bclns,bcnps,bcln->bclnp", Ch, h0, torch.exp(cum))
+    y = y + D.float()[None, None, None, :, None] * xc
+    y = y.reshape(b, nc * L, N, P)[:, :S]
+    if pad:
+        # padded steps have dt = 0: decay 1, no input, so ``h`` already is the state after the last real token
+        pass
+    return y.to(dtype), h
+
+
+def ssd_context_parallel_initial_state(final_zero_init: torch.Tensor, total_decay: torch.Tensor, group) -> torch.Tensor:
+    """State entering this rank's sequence shard.  ``final_zero_init [b, N, P, Sd]``: the shard's final state when
+    started from zero; ``total_decay [b, N]``: ``exp(A sum dt)`` over the shard.  The entering state of rank r is
+    ``sum_{j<r} (prod_{j<i<r} decay_i) final_j`` (lm_engine/modeling_utils/sequence_mixer_blocks/mamba2/op.py:73-145)."""
+    return _CPPrefix.apply(final_zero_init, total_decay, group)
+
+
+class _CPPrefix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, f, d, group):
+        world, r = dist.get_world_size(group), dist.get_rank(group)
+        fs = [torch.empty_like(f) for _ in range(world)]
+        ds = [torch.empty_like(d) for _ in range(world)]
+        dist.all_gather(fs, f.contiguous(), group=group)
+        dist.all_gather(ds, d.contiguous(), group=group)
+        h = torch.zeros_like(f)
+        for j in range(r):
+            h = h * ds[j][..., None, None] + fs[j]
+        ctx.group = group
+        ctx.save_for_backward(torch.stack(fs), torch.stack(ds))
+        return h
+
+    @staticmethod
+    def backward(ctx, g):
+        fs, ds = ctx.saved_tensors
+        group = ctx.group
+        world, r = dist.get_world_size(group), dist.get_rank(group)
+        # every rank needs d(loss_i)/d(f_r), d(loss_i)/d(d_r) for the later ranks i > r: exchange the incoming grads
+        gs = [torch.empty_like(g) for _ in range(world)]
+        dist.all_gather(gs, g.contiguous(), group=group)
+        gf = torch.zeros_like(g)
+        gd = torch.zeros_like(ds[0])
+        for i in range(r + 1, world):
+            # h_i = sum_{j<i} (prod_{j<k<i} d_k) f_j
+            coef = torch.ones_like(ds[0])
+            for k in range(r + 1, i):
+                coef = coef * ds[k]
+            gf = gf + gs[i] * coef[..., None, None]
+            # dependence on d_r (r >= 1 contributes to h_i through the terms with j < r)
+            if r >= 1:
+                prefix = torch.zeros_like(g)
+                for j in range(r):
+                    prefix = prefix * ds[j][..., None, None] + fs[j]   # = h_r
+                gd = gd + (gs[i] * prefix).sum((-1, -2)) * coef
+        return gf, gd, None

@@ -265,7 +265,7 @@ class FSDPEngine:
                 import os
                 import sys
 
-                sys.modules["lm_engine_b200.ops.gemm"].RESERVED_SMS = int(os.environ.get("LME_COMM_SMS", "16"))
+                sys.modules["lm_engine_b200.ops.gemm"].RESERVED_SMS = int(os.environ.get("LME_COMM_SMS", "0"))
         self._anchor = torch.zeros(1, device=self.device, requires_grad=True)
         self._buffer_events: dict[int, torch.cuda.Event] = {}
         self._inflight: dict[str, torch.Tensor] = {}

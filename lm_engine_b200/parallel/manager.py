@@ -66,8 +66,10 @@ class ProcessGroupManager:
         _S.cp_lb = context_parallel_load_balancing_method
         _S.async_tp = use_async_tensor_parallel
         Accelerator.set_device(local_rank)
-        # collectives overlap persistent GEMM kernels: bound the SMs NCCL may take (the GEMMs leave as many free)
-        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("LME_COMM_SMS", "16"))
+        # optional cap on the SMs NCCL may take while its collectives overlap the persistent GEMM kernels (the GEMMs
+        # then leave as many free): LME_COMM_SMS=<n>
+        if int(os.environ.get("LME_COMM_SMS", "0")) > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", os.environ["LME_COMM_SMS"])
         if "MASTER_ADDR" in os.environ and not dist.is_initialized():
             backend = "cpu:gloo,cuda:nccl" if torch.cuda.is_available() else "gloo"
             kwargs = {}

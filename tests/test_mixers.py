@@ -1,0 +1,129 @@
+"""Sequence mixers on CPU: chunked SSD == token recurrence; hybrid / recurrent models against the reference."""
+
+import pytest
+import torch
+
+from lm_engine_b200.models import build_model, config_from_dict
+from lm_engine_b200.ops.ssd import ssd_chunk_scan, ssd_recurrent_step
+
+from .refutil import build_reference_model
+
+
+@pytest.mark.parametrize("S,L,G", [(37, 8, 1), (64, 16, 2), (5, 8, 1)])
+def test_ssd_chunked_equals_recurrence(S, L, G):
+    torch.manual_seed(0)
+    b, N, P, Sd = 2, 4, 8, 6
+    x = torch.randn(b, S, N, P)
+    dt = torch.rand(b, S, N) * 0.5 + 0.01
+    A = -torch.rand(N) * 2 - 0.1
+    B, C = torch.randn(b, S, G, Sd), torch.randn(b, S, G, Sd)
+    D = torch.randn(N)
+    h0 = torch.randn(b, N, P, Sd)
+    y, hf = ssd_chunk_scan(x, dt, A, B, C, D, L, initial_state=h0)
+    h = h0.clone()
+    ys = []
+    for t in range(S):
+        yt, h = ssd_recurrent_step(x[:, t], dt[:, t], A, B[:, t], C[:, t], D, h)
+        ys.append(yt)
+    assert torch.allclose(y, torch.stack(ys, 1), atol=1e-4, rtol=1e-4)
+    assert torch.allclose(hf, h, atol=1e-4, rtol=1e-4)
+
+
+def _base(L, mixers, **extra):
+    d = dict(model_type="gpt_base", vocab_size=256, max_position_embeddings=64, hidden_size=32, num_layers=L,
+             normalization_function="rmsnorm", layer_norm_epsilon=1e-5, initializer_range=0.02, bos_token_id=0,
+             eos_token_id=1, pad_token_id=2, position_embedding_type="nope", rope_theta=10000, rope_scaling=None,
+             m_emb=None, m_width=None, m_residual=None, init_method="normal", embedding_init_method="normal",
+             use_depth_scaled_init=False, tie_word_embeddings=False, sequence_mixer_blocks=mixers,
+             mlp_blocks=[dict(mlp_type="MLP", intermediate_size=64, activation_function="swiglu") for _ in range(L)])
+    d.update(extra)
+    return d
+
+
+def _parity(cfg, atol=3e-5):
+    ref = build_reference_model(cfg)
+    ours = build_model(config_from_dict(cfg))
+    ours.load_state_dict(ref.state_dict(), strict=True)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randint(0, 256, (2, 24), generator=g)
+    o, r = ours(x).logits, ref(input_ids=x).logits
+    assert torch.allclose(o, r, atol=atol, rtol=1e-4), (o - r).abs().max()
+    o.float().pow(2).mean().backward()
+    r.float().pow(2).mean().backward()
+    for (n, po), (_, pr) in zip(ours.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(po.grad, pr.grad, atol=atol, rtol=1e-3), n
+
+
+MAMBA = dict(sequence_mixer_type="mamba2", state_size=8, intermediate_size=64, num_heads=4, conv_kernel_size=4,
+             activation_function="silu", num_groups=1, chunk_size=8, normalization_function="rmsnorm")
+ATTN = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2)
+
+
+def test_hybrid_mamba2_attention_matches_reference():
+    _parity(_base(3, [MAMBA, dict(ATTN), MAMBA], position_embedding_type="rope", rope_dim=8))
+
+
+RNN_ = dict(sequence_mixer_type="rnn", state_head_dim=8, num_input_heads=2, num_weight_heads=4, add_bias=False,
+            normalization_function="rmsnorm", gradient_clipping=None, kernel_size=None, activation_function="tanh")
+GRU_ = dict(sequence_mixer_type="gru", state_head_dim=8, num_input_heads=4, num_forget_input_heads=2,
+            num_reset_input_heads=1, num_weight_heads=2, num_forget_weight_heads=4, num_reset_weight_heads=1,
+            add_bias=True, normalization_function="rmsnorm", gradient_clipping=None, kernel_size=4,
+            activation_function="silu")
+M2RNN_ = dict(sequence_mixer_type="m2rnn", k_head_dim=4, v_head_dim=8, num_q_heads=2, num_k_heads=2, num_v_heads=4,
+              num_f_heads=4, num_g_heads=4, num_weight_heads=4, use_residual=True, kernel_size=4,
+              activation_function="silu", add_bias=False, gradient_clipping=None, normalization_function="rmsnorm")
+
+
+def test_rnn_gru_match_reference():
+    _parity(_base(2, [RNN_, GRU_]))
+
+
+def test_m2rnn_matches_reference():
+    _parity(_base(2, [M2RNN_, dict(ATTN)]))
+
+
+def test_gated_delta_rule_properties():
+    """No CPU reference exists in lm-engine for the delta rule; check the recurrence against its definition on a
+    case with a closed form (beta = 1, no decay, orthonormal keys: the state stores v_t under k_t)."""
+    from lm_engine_b200.ops.recurrence import gated_delta_rule_scan
+
+    B, S, N, K, V = 1, 4, 1, 4, 3
+    k = torch.eye(K)[None, :, None, :].expand(B, S, N, K).contiguous()
+    v = torch.randn(B, S, N, V)
+    g = torch.zeros(B, S, N)
+    beta = torch.ones(B, S, N)
+    y, h = gated_delta_rule_scan(k, k, v, g, beta, scale=1.0)
+    assert torch.allclose(y, v, atol=1e-5)
+    assert torch.allclose(h[0, 0], v[0, :, 0], atol=1e-5)
+    cfg = _base(2, [dict(sequence_mixer_type="gated_deltanet", k_head_dim=4, v_head_dim=8, num_k_heads=2,
+                         num_v_heads=4, use_gate=True, attention_multiplier=None, allow_neg_eigval=True,
+                         kernel_size=4), dict(ATTN)])
+    m = build_model(config_from_dict(cfg))
+    out = m(torch.randint(0, 256, (2, 16))).logits
+    out.float().pow(2).mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in m.parameters())
+
+
+def test_other_model_families_run_and_share_kv():
+    x = torch.randint(0, 256, (2, 12))
+    for mt in ("palm", "ladder_residual"):
+        cfg = _base(2, [dict(ATTN), dict(ATTN)], model_type=mt, position_embedding_type="rope", rope_dim=8)
+        ours = build_model(config_from_dict(cfg))
+        ours(x).logits.float().pow(2).mean().backward()
+        assert all(p.grad is not None for p in ours.parameters())
+        try:
+            # in this snapshot of the reference these two families fail inside their own constructors / forward
+            # (TypeError); compare only when they run
+            ref = build_reference_model(cfg)
+            want = ref(input_ids=x).logits
+        except TypeError:
+            continue
+        ours.load_state_dict(ref.state_dict(), strict=True)
+        assert torch.allclose(ours(x).logits, want, atol=3e-5), mt
+    cfg = _base(4, [dict(ATTN) for _ in range(4)], model_type="gpt_crosslayer", sharing_pattern=[0, 0, 2, 2],
+                position_embedding_type="rope", rope_dim=8)
+    m = build_model(config_from_dict(cfg))
+    names = [n for n, _ in m.named_parameters()]
+    assert any("h.0.kv_proj" in n for n in names) and not any("h.1.kv_proj" in n for n in names)
+    m(x).logits.float().pow(2).mean().backward()
+    assert all(p.grad is not None for p in m.parameters())
