@@ -268,6 +268,7 @@ class FSDPEngine:
                 sys.modules["lm_engine_b200.ops.gemm"].RESERVED_SMS = int(os.environ.get("LME_COMM_SMS", "0"))
         self._anchor = torch.zeros(1, device=self.device, requires_grad=True)
         self._buffer_events: dict[int, torch.cuda.Event] = {}
+        self._fence_word = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._inflight: dict[str, torch.Tensor] = {}
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -276,6 +277,12 @@ class FSDPEngine:
         self.micro_step = 0
         self._setup_grad_buffers()
         self._install_grad_hooks()
+        self.copy_engine_gather = False
+        if self.is_cuda and self.world > 1 and self.stage == 3:
+            import os
+
+            if os.environ.get("LME_ALLGATHER", "ce") == "ce":
+                self._setup_symmetric_shards()
 
     # ------------------------------------------------------------------ initialisation
     @torch.no_grad()
@@ -383,6 +390,44 @@ class FSDPEngine:
             for s in u.slots:
                 s.param.register_post_accumulate_grad_hook(make_hook())
 
+    # ------------------------------------------------------------------ symmetric-memory parameter shards
+    def _setup_symmetric_shards(self) -> None:
+        """Moves the bf16 parameter shards of all units into one symmetric-memory allocation so that every rank can
+        read its peers' shards directly.  The parameter all-gather then is ``world`` peer-to-peer copies executed by
+        the copy engines over NVLink: no SM is taken from the GEMMs it overlaps with (an NCCL all-gather kernel
+        competes with the persistent GEMM CTAs for SMs)."""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            units = [u for u in self.units if u.shard_params]
+            total = sum(u.shard_size for u in units)
+            arena = symm_mem.empty(total, dtype=self.compute_dtype, device=self.device)
+            handle = symm_mem.rendezvous(arena, self.shard_group)
+            off = 0
+            for u in units:
+                mine = arena[off:off + u.shard_size]
+                mine.copy_(u.lp_shard)
+                u.lp_shard = mine
+                u.peer_shards = [handle.get_buffer(r, (u.shard_size,), self.compute_dtype, off)
+                                 for r in range(self.world)]
+                off += u.shard_size
+            self._symm_arena, self._symm_handle = arena, handle
+            self.copy_engine_gather = True
+            self._cross_rank_fence()
+        except Exception as e:  # noqa: BLE001 - symmetric memory unavailable: keep the NCCL all-gather
+            import logging
+
+            from ..logging_utils import log_rank_0
+
+            log_rank_0(logging.WARNING, f"symmetric-memory parameter shards unavailable ({e}); using NCCL all-gather")
+            self.copy_engine_gather = False
+
+    def _cross_rank_fence(self) -> None:
+        """Orders this rank's writes to its parameter shard (optimizer step, checkpoint load) before the peers'
+        next reads: a tiny all-reduce on the compute stream; the gather stream waits on the compute stream."""
+        if self.copy_engine_gather and self.shard_group is not None:
+            dist.all_reduce(self._fence_word, group=self.shard_group)
+
     # ------------------------------------------------------------------ buffer pools
     def _take(self, pool: dict[int, list[torch.Tensor]], kind: str, u: ShardedUnit, dtype) -> torch.Tensor:
         bufs = pool.setdefault(u.numel, [])
@@ -403,7 +448,13 @@ class FSDPEngine:
         if self.is_cuda:
             self.ag_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.ag_stream):
-                dist.all_gather_into_tensor(buf, u.lp_shard, group=self.shard_group)
+                if self.copy_engine_gather:
+                    S = u.shard_size
+                    for i in range(self.world):   # own shard first, then the peers in a rank-rotated order
+                        p = (self.rank + i) % self.world
+                        buf[p * S:(p + 1) * S].copy_(u.peer_shards[p], non_blocking=True)
+                else:
+                    dist.all_gather_into_tensor(buf, u.lp_shard, group=self.shard_group)
                 u.ag_event = torch.cuda.Event()
                 u.ag_event.record(self.ag_stream)
         else:
@@ -599,6 +650,7 @@ class FSDPEngine:
                                step=self.step_count, gscale=self.clip_coef)
             if self.stage in (1, 2) and self.world > 1:
                 dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=self.shard_group)
+        self._cross_rank_fence()
         return self.grad_norm
 
     def _reduce_norm(self) -> None:
@@ -661,6 +713,8 @@ class FSDPEngine:
                     u.lp_shard.copy_(full[u.rank * u.shard_size:(u.rank + 1) * u.shard_size])
                 else:
                     u.flat_param.copy_(full)
+        if which == "master":
+            self._cross_rank_fence()
 
     def num_parameters(self) -> int:
         return sum(s.numel for u in self.units for s in u.slots)
