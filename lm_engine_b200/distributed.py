@@ -139,6 +139,8 @@ def shard_model(wrapper, *, stage: int, dtype: torch.dtype, communication_dtype:
 
         model.compute_lm_loss = compute_lm_loss
     wrapper.engine = engine
+    if wrapper.has_teacher_model():
+        wrapper.place_teacher(engine.device)
     return engine
 
 
