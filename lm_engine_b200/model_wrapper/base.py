@@ -111,7 +111,7 @@ class ModelWrapper(nn.Module):
         return {"loss": lm_loss + self.router_aux_loss_coef * aux, "lm_loss": lm_loss, "aux_loss": aux}
 
     def skip_logits(self) -> bool:
-        return is_fused_linear_cross_entropy_enabled() and not self.is_pipeline_parallel_enabled
+        return is_fused_linear_cross_entropy_enabled()
 
     # ------------------------------------------------------------------ misc
     def save_pretrained(self, save_path: str, state_dict: dict | None = None) -> None:

@@ -41,21 +41,38 @@ class ModelWrapperForPretraining(ModelWrapper):
         return self.get_loss(out, labels, shift_logits_and_labels=False, lm_loss_multiplier=lm_loss_multiplier)
 
     # ------------------------------------------------------------------ pipeline stages exchange raw tensors
-    def _forward_pipeline_stage(self, tokens: torch.Tensor, aux_in):
+    def forward_pipeline_stage(self, tokens: torch.Tensor | None, hidden_in: torch.Tensor | None, aux_in=0):
+        """One micro-batch through this stage.  The first stage embeds ``tokens[:, :-1]``; later stages continue from
+        ``hidden_in`` (and the auxiliary loss accumulated so far).  Returns ``(hidden, aux_loss)``, or the loss dict on
+        the last stage, whose labels are ``tokens[:, 1:]``."""
         device = next(self.model.parameters()).device if self.engine is None else self.engine.device
-        tokens = tokens.to(device)
+        tp = ProcessGroupManager.is_tensor_parallel_enabled()
         if self.is_first_stage:
-            ids = tokens[:, :-1]
-            (ids,) = shard_sequence((ids,), seq_dim=1)
-            out = self.model(input_ids=ids, output_parallel_lm_logits=ProcessGroupManager.is_tensor_parallel_enabled())
+            (ids,) = shard_sequence((tokens[:, :-1].to(device),), seq_dim=1)
+            kw = dict(input_ids=ids)
+        else:
+            kw = dict(pipeline_parallel_input=PipelineParallelInput(hidden_states=hidden_in, aux_loss=aux_in))
+        if not self.is_last_stage:
+            out = self.model(**kw)
+            return out.hidden_states, out.aux_loss
+        out = self.model(**kw, output_parallel_lm_logits=tp, skip_logits=self.skip_logits())
+        (labels,) = shard_sequence((tokens[:, 1:].to(device),), seq_dim=1)
+        cp = ProcessGroupManager.get_context_parallel_world_size()
+        return self.get_loss(out, labels, shift_logits_and_labels=False,
+                             lm_loss_multiplier=1 / (self.micro_batch_size * self.sequence_length / cp))
+
+    def _forward_pipeline_stage(self, tokens: torch.Tensor, aux_in):
+        """Reference-shaped entry: a stage called with the raw tensor of its predecessor returns raw tensors."""
+        if self.is_first_stage:
+            hidden, aux = self.forward_pipeline_stage(tokens, None)
         else:
             out = self.model(pipeline_parallel_input=PipelineParallelInput(hidden_states=tokens, aux_loss=aux_in),
                              output_parallel_lm_logits=ProcessGroupManager.is_tensor_parallel_enabled())
-        aux = out.aux_loss
-        tensor = out.logits if isinstance(out, CausalLMOutputWithPast) else out.hidden_states
+            aux = out.aux_loss
+            hidden = out.logits if isinstance(out, CausalLMOutputWithPast) else out.hidden_states
         if is_aux_loss_zero(aux):
-            return tensor
-        return tensor, (aux.unsqueeze(0) if aux.dim() == 0 else aux)
+            return hidden
+        return hidden, (aux.unsqueeze(0) if aux.dim() == 0 else aux)
 
     # ------------------------------------------------------------------ inputs
     def _prepare_model_inputs(self, batch: dict) -> tuple[dict, torch.Tensor]:

@@ -60,21 +60,21 @@ class ShardedOptimizer:
         self.engine.zero_grad()
 
     @torch.no_grad()
-    def step(self) -> torch.Tensor:
+    def step(self, total_sumsq: torch.Tensor | None = None) -> torch.Tensor:
         e = self.engine
         lrs = {g["name"]: g["lr"] for g in self.param_groups}
         a = self.class_args
         if self.fused:
             return e.clip_and_step(lr=lrs["normal"], lr_by_group=lrs, betas=tuple(a.get("betas", (0.9, 0.999))),
                                    eps=a.get("eps", 1e-8), weight_decay=a.get("weight_decay", 1e-2),
-                                   max_grad_norm=self.max_grad_norm)
+                                   max_grad_norm=self.max_grad_norm, total_sumsq=total_sumsq)
         from .. import ops
 
-        e.finish_backward()
         e.step_count += 1
-        for i, u in enumerate(e.units):
-            ops.sumsq_(u.grad_shard, e.sumsq, accumulate=i > 0)
-        e._reduce_norm()
+        if total_sumsq is not None:
+            e.sumsq.copy_(total_sumsq)
+        else:
+            e.local_sumsq(include_pipeline_group=True)
         ops.clip_coef_(e.sumsq, self.max_grad_norm, e.grad_norm, e.clip_coef)
         for p, u, sl in self._aliases:
             p.grad = u.grad_shard[sl].float() * e.clip_coef

@@ -20,6 +20,7 @@ Stages: 0 = replicate everything (DDP); 1/2 = shard optimizer state and gradient
 from __future__ import annotations
 
 import math
+import zlib
 from dataclasses import dataclass, field
 from typing import Callable
 
@@ -275,6 +276,7 @@ class FSDPEngine:
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
         self.step_count = 0
         self.micro_step = 0
+        self.pipeline_mode = False   # several micro-batches in flight: reshard / reduce after every pass
         self._setup_grad_buffers()
         self._install_grad_hooks()
         self.copy_engine_gather = False
@@ -302,7 +304,8 @@ class FSDPEngine:
                     view.copy_(old[id(s.param)])
                 s.param.data = view
             if meta:
-                gen_seed = seed + 7919 * ui + 104729 * tp_rank
+                # keyed by the unit's global name, so that a pipeline split initialises the same weights
+                gen_seed = (seed + zlib.crc32(u.name.encode()) + 104729 * tp_rank) % (2 ** 63)
                 devs = [self.device] if self.is_cuda else []
                 with torch.random.fork_rng(devices=devs):
                     torch.manual_seed(gen_seed)
@@ -494,7 +497,7 @@ class FSDPEngine:
 
     def post_forward(self, u: ShardedUnit, training: bool) -> None:
         # the last unit's backward starts right after its forward: keep it gathered
-        if u.keep_unsharded or (training and u is self.units[-1]):
+        if u.keep_unsharded or (training and u is self.units[-1] and not self.pipeline_mode):
             return
         self._reshard(u)
 
@@ -518,7 +521,7 @@ class FSDPEngine:
 
     def post_backward(self, u: ShardedUnit) -> None:
         u.pending_backward -= 1
-        if u.pending_backward > 0:
+        if u.pending_backward > 0 and not self.pipeline_mode:
             return  # the unit ran more than once in forward (tied embedding / LM head): reduce after the last use
         self._reduce_grads(u)
         if not u.keep_unsharded:
@@ -628,17 +631,18 @@ class FSDPEngine:
     @torch.no_grad()
     def clip_and_step(self, *, lr: float, lr_by_group: dict[str, float] | None = None, betas=(0.9, 0.95),
                       eps: float = 1e-10, weight_decay: float = 0.1, max_grad_norm: float | None = 1.0,
-                      extra_sumsq: torch.Tensor | None = None) -> torch.Tensor:
-        """Global-norm clipping + AdamW on every shard.  Returns the (device) pre-clip gradient norm."""
-        self.finish_backward()
+                      extra_sumsq: torch.Tensor | None = None,
+                      total_sumsq: torch.Tensor | None = None) -> torch.Tensor:
+        """Global-norm clipping + AdamW on every shard.  Returns the (device) pre-clip gradient norm.
+        ``total_sumsq`` (from :meth:`local_sumsq` of every pipeline chunk, summed over the pipeline group) replaces
+        the norm computation when several engines share one clip coefficient."""
         self.step_count += 1
-        first = True
-        for u in self.units:
-            ops.sumsq_(u.grad_shard, self.sumsq, accumulate=not first)
-            first = False
-        if extra_sumsq is not None:
-            self.sumsq.add_(extra_sumsq)
-        self._reduce_norm()
+        if total_sumsq is not None:
+            self.sumsq.copy_(total_sumsq)
+        else:
+            self.local_sumsq(include_pipeline_group=True)
+            if extra_sumsq is not None:
+                self.sumsq.add_(extra_sumsq)
         ops.clip_coef_(self.sumsq, max_grad_norm, self.grad_norm, self.clip_coef)
         lr_by_group = lr_by_group or {}
         for u in self.units:
@@ -653,7 +657,19 @@ class FSDPEngine:
         self._cross_rank_fence()
         return self.grad_norm
 
-    def _reduce_norm(self) -> None:
+    @torch.no_grad()
+    def local_sumsq(self, include_pipeline_group: bool = False) -> torch.Tensor:
+        """Joins the backward pass and returns the squared gradient norm of this engine's parameters (summed over
+        the sharding and tensor-parallel groups; over the pipeline group too when asked)."""
+        self.finish_backward()
+        first = True
+        for u in self.units:
+            ops.sumsq_(u.grad_shard, self.sumsq, accumulate=not first)
+            first = False
+        self._reduce_norm(include_pipeline_group)
+        return self.sumsq
+
+    def _reduce_norm(self, include_pipeline_group: bool = True) -> None:
         """Sum of squares over every group that holds a distinct piece of the model."""
         if self.stage >= 1 and self.shard_group is not None:
             dist.all_reduce(self.sumsq, group=self.shard_group)
@@ -675,7 +691,7 @@ class FSDPEngine:
             dist.all_reduce(self.sumsq, group=tp)
             self.sumsq.sub_(rep * (tpw - 1))
         pp = ProcessGroupManager.get_pipeline_parallel_group()
-        if pp is not None:
+        if pp is not None and include_pipeline_group:
             dist.all_reduce(self.sumsq, group=pp)
 
     # ------------------------------------------------------------------ state access (checkpointing, tests)
