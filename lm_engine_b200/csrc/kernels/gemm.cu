@@ -38,6 +38,11 @@ struct GemmArgs {
     long long ldp;
     int flags;
     int tiles_m, tiles_n, group_m;
+    // 8-bit operands (kind::f8f6f4): element formats (0 = e4m3, 1 = e5m2) and the de-quantisation scales, read on the
+    // device so that no host synchronisation sits between the quantiser and the GEMM
+    int a_fmt, b_fmt;
+    const float* scale_a;
+    const float* scale_b;
 };
 
 template <int BN, int STAGES>
@@ -167,10 +172,14 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row,
         }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// F8: operands are 1-byte e4m3 / e5m2, K-major; a 128-byte swizzle row then holds 128 elements of K and one MMA
+// consumes 32 of them, so the byte geometry of the pipeline is identical to the bf16 one.
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs p) {
+    static_assert(!F8 || (!A_MN && !B_MN), "8-bit operands are K-major");
+    constexpr int BKE = F8 ? 2 * BK : BK;  // K elements per pipeline stage
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -183,7 +192,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_kb = (p.K + BKE - 1) / BKE;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                    : (2 * BN <= 256) ? 256 : 512;
 
@@ -225,7 +234,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                    const int k0 = kb * BK;
+                    const int k0 = kb * BKE;
                     if (A_MN) {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c)
@@ -247,7 +256,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, BM, BN);
+            const uint32_t idesc = F8 ? make_idesc(p.a_fmt, p.b_fmt, false, false, BM, BN)
+                                      : make_idesc(1, 1, A_MN, B_MN, BM, BN);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -271,7 +281,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                                  : make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
                         const uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * (UMMA_K * 128), BK * 128, 1024)
                                                  : make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
-                        umma_bf16(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        if (F8) umma_f8(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        else umma_bf16(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[s]);  // frees the smem slot once these MMAs have read it
                 }
@@ -287,6 +298,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool out_f32 = p.flags & LME_GEMM_OUT_F32;
         const bool accumulate = p.flags & LME_GEMM_ACCUMULATE;
         const bool swiglu = p.flags & LME_GEMM_SWIGLU;
+        float dequant = 1.0f;
+        if (F8) dequant = __ldg(p.scale_a) * __ldg(p.scale_b);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
             int mb, nb;
             tile_coords(tile, p, mb, nb);
@@ -302,6 +315,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32, r);
                 tmem_ld_wait();
+                if (F8) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * dequant);
+                }
                 const int col0 = nb * BN + c * 32;
                 if (row_ok && col0 < p.N) epilogue_store(r, row, col0, p, out_f32, accumulate, swiglu);
                 __syncwarp();
@@ -342,15 +359,25 @@ static EncodeTiledFn get_encode_fn() {
 
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements,
 // box = [box_inner x box_outer], 128-byte swizzle (box_inner must be 64).
+int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                 uint32_t box_outer, int elem_bytes);
+
 int make_tmap_bf16_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer) {
+    return make_tmap_2d(m, ptr, inner, outer, ld, box_inner, box_outer, 2);
+}
+
+// elem_bytes 2 = bf16, 1 = 8-bit; the box's inner extent must span 128 bytes (the swizzle row)
+int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                 uint32_t box_outer, int elem_bytes) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return LME_ERR_DRIVER;
     cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {ld * 2};
+    cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                     const_cast<void*>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -372,11 +399,11 @@ static int num_sms() {
     return g_num_sms;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p, int max_ctas,
                        cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
-    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
@@ -421,6 +448,8 @@ extern "C" int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const
     p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
     p.preact = static_cast<__nv_bfloat16*>(preact); p.ldp = ldp;
     p.flags = flags;
+    p.a_fmt = p.b_fmt = 0;
+    p.scale_a = p.scale_b = nullptr;
     if (max_ctas <= 0) max_ctas = num_sms();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define LME_DISPATCH(BN_, ST_)                                                          \
@@ -433,6 +462,39 @@ extern "C" int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const
     if (BN == 128) LME_DISPATCH(128, 6);
     LME_DISPATCH(256, 4);
 #undef LME_DISPATCH
+}
+
+// C[M,N] = (A[M,K] * B[N,K]^T) * scale_a * scale_b with 1-byte e4m3 / e5m2 operands, both K-major.
+extern "C" int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void* B, int b_fmt, long long ldb,
+                            const float* scale_a, const float* scale_b, void* C, long long ldc, int M, int N, int K,
+                            int flags, const void* bias, const void* residual, long long ldr, void* preact,
+                            long long ldp, int max_ctas, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return LME_OK;
+    if ((N % 8) || (lda % 16) || (ldb % 16) || (ldc % 4) || (K % 16)) return LME_ERR_SHAPE;
+    if ((flags & LME_GEMM_SWIGLU) && (N % 16)) return LME_ERR_SHAPE;
+    if ((a_fmt | b_fmt) & ~1) return LME_ERR_SHAPE;
+    if (scale_a == nullptr || scale_b == nullptr) return LME_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_2d(&ta, A, K, M, lda, 128, BM, 1);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tb, B, K, N, ldb, 128, BN, 1);
+    if (rc) return rc;
+    GemmArgs p;
+    p.M = M; p.N = N; p.K = K;
+    p.C = C; p.ldc = ldc;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+    p.preact = static_cast<__nv_bfloat16*>(preact); p.ldp = ldp;
+    p.flags = flags;
+    p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+    p.scale_a = scale_a; p.scale_b = scale_b;
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (BN == 128) return launch_gemm<128, 6, false, false, true>(ta, tb, p, max_ctas, st);
+    return launch_gemm<256, 4, false, false, true>(ta, tb, p, max_ctas, st);
 }
 
 extern "C" int lme_read_status(unsigned int* out8, int clear) {

@@ -94,6 +94,7 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--sustained", action="store_true", help="time ~1.5 s back-to-back loops (power-limited clocks)")
     ap.add_argument("--impl", default=None, choices=["1cta", "2cta"])
+    ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
     args = ap.parse_args()
     peaks = _peaks()
     T = 8192
@@ -109,6 +110,9 @@ def main():
     ]
     if args.quick:
         shapes = shapes[:3]
+    if args.only is not None:
+        shapes = [s for s in shapes if s[0] == args.only]
+        assert shapes, f"no shape named {args.only!r}"
     rows = []
     for name, M, N, K, a_mn, b_mn, kw in shapes:
         r = bench_gemm(M, N, K, a_mn, b_mn, sustained=args.sustained, impl=args.impl, **kw)
