@@ -376,6 +376,13 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
     cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
+    // The encode call is a driver entry point and needs a current context.  A thread that has made no runtime
+    // call yet (an autograd worker whose first op is this GEMM) has none bound: bind the primary context once.
+    thread_local bool context_bound = false;
+    if (!context_bound) {
+        cudaFree(nullptr);
+        context_bound = true;
+    }
     CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                      const_cast<void*>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -29,6 +29,21 @@ int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, const void*
                        void* C, long long ldc, int M, int N, int K, int flags, const void* bias,
                        const void* residual, long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
 
+// C[M, N] = (A[M, K] * B[N, K]^T) * scale_a[0] * scale_b[0]: 1-byte e4m3 (fmt 0) / e5m2 (fmt 1) operands, both
+// K-major, fp32 accumulation in TMEM; same flags and fused epilogue as lme_gemm_bf16.  K, lda, ldb % 16 == 0.
+int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void* B, int b_fmt, long long ldb,
+                 const float* scale_a, const float* scale_b, void* C, long long ldc, int M, int N, int K, int flags,
+                 const void* bias, const void* residual, long long ldr, void* preact, long long ldp, int max_ctas,
+                 void* stream);
+
+// max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
+int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
+
+// Tensor-wise scaled cast of a bf16 [rows, cols] matrix to 8 bits with scale fmax / amax[0]; writes q [rows, cols]
+// and / or its transpose qt [cols, rows] (either may be null) and scale_inv[0] = amax / fmax.
+int lme_fp8_quantize(const void* x, int rows, int cols, long long ldx, const float* amax, int fmt, void* q,
+                     long long ldq, void* qt, long long ldqt, float* scale_inv, void* stream);
+
 // Copies the 8-word device status block to the host (synchronising copy); optionally clears it.
 int lme_read_status(unsigned int* out8, int clear);
 

@@ -3,4 +3,5 @@
 #include "kernels/gemm.cu"
 #include "kernels/gemm2cta.cu"
 #include "kernels/elementwise.cu"
+#include "kernels/fp8.cu"
 #include "kernels/noalloc.cu"

@@ -57,6 +57,9 @@ def cuda_lib() -> ctypes.CDLL:
         sigs = {
             "lme_gemm_bf16": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
             "lme_gemm_bf16_2cta": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
+            "lme_gemm_fp8": [P, I, L, P, I, L, P, P, P, L, I, I, I, I, P, P, L, P, L, I, P],
+            "lme_fp8_amax": [P, L, P, P],
+            "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],
             "lme_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
             "lme_rmsnorm_bwd_partial_rows": [I],

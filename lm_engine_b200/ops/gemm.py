@@ -186,6 +186,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
            residual: torch.Tensor | None = None) -> torch.Tensor:
     """``F.linear`` with an optional fused residual add; tcgen05 GEMMs on CUDA bf16, PyTorch elsewhere."""
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        if getattr(weight, "fp8", False):
+            from . import fp8
+
+            if fp8.fp8_eligible(x, weight):
+                return fp8.linear_fp8(x, weight, bias, residual)
         return _Linear.apply(x, weight, bias, residual)
     y = torch.nn.functional.linear(x, weight, bias)
     return y if residual is None else y + residual
@@ -227,6 +232,11 @@ class _LinearSwiGLU(torch.autograd.Function):
 def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``up * silu(gate)`` of the packed projection ``x W^T`` (gate/up interleaved along the output features)."""
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.size(0) % 16 == 0:
+        if getattr(weight, "fp8", False):
+            from . import fp8
+
+            if fp8.fp8_eligible(x, weight):
+                return fp8.linear_swiglu_fp8(x, weight)
         return _LinearSwiGLU.apply(x, weight)
     from .activation import swiglu_packed
 

@@ -88,12 +88,31 @@ def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, **kw
             "cublas_tflops": fl / t_ref / 1e12}
 
 
+def bench_gemm_fp8(M, N, K, sustained=False):
+    """8-bit GEMM (pre-quantised operands) and the quantiser feeding it, on one forward-shaped problem."""
+    from . import fp8
+
+    dev = "cuda"
+    n_pool = max(2, min(8, int(300e6 // (M * K + N * K + 2 * M * N)) + 1))
+    xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(n_pool)]
+    ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) for _ in range(n_pool)]
+    xq = [fp8.quantize(x, fp8.E4M3) for x in xs]
+    wq = [fp8.quantize(w, fp8.E4M3) for w in ws]
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    timer = _sustained if sustained else _time
+    t = timer(lambda i: fp8.gemm_fp8(xq[i].q, 0, xq[i].scale_inv, wq[i].q, 0, wq[i].scale_inv, out=out), n_pool)
+    tq = _time(lambda i: fp8.quantize(xs[i], fp8.E4M3, transposed=True), n_pool)
+    return {"M": M, "N": N, "K": K, "ms": t * 1e3, "tflops": 2.0 * M * N * K / t / 1e12, "quantize_ms": tq * 1e3,
+            "quantize_gbs": M * K * 4 / tq / 1e9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--sustained", action="store_true", help="time ~1.5 s back-to-back loops (power-limited clocks)")
     ap.add_argument("--impl", default=None, choices=["1cta", "2cta"])
+    ap.add_argument("--fp8", action="store_true", help="also time the 8-bit GEMM and its quantiser")
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
     args = ap.parse_args()
     peaks = _peaks()
@@ -122,6 +141,15 @@ def main():
         print(f"{name:16s} M={M:6d} N={N:6d} K={K:6d}  ours {r['ms']:8.3f} ms {r['tflops']:7.1f} TF "
               f"({100 * r['frac_of_peak']:5.1f}% of {peaks['source']} peak)   cuBLAS {r['cublas_ms']:8.3f} ms "
               f"{r['cublas_tflops']:7.1f} TF", flush=True)
+    if args.fp8:
+        for name, M, N, K, a_mn, b_mn, kw in shapes:
+            if a_mn or b_mn or kw:
+                continue
+            r = bench_gemm_fp8(M, N, K, sustained=args.sustained)
+            r["name"] = name + " fp8"
+            rows.append(r)
+            print(f"{name:16s} fp8 e4m3  M={M:6d} N={N:6d} K={K:6d}  {r['ms']:8.3f} ms {r['tflops']:7.1f} TF   "
+                  f"quantize(+transpose) {r['quantize_ms']:7.3f} ms {r['quantize_gbs']:6.0f} GB/s", flush=True)
     st = _lib.read_status()
     print("device status:", st)
     if args.json:
