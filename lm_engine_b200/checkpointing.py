@@ -120,10 +120,11 @@ def model_state_dict(model_container: ModelContainer, which: str = "master") -> 
             for k, v in wrapper.model.state_dict().items():
                 out[f"model.{k}"] = v
             continue
-        for u in eng.units:
+        for u in eng.all_units:
             full = eng.gather_full(u, which)
             for s in u.slots:
-                out[f"model.{s.name}"] = _to_dtensor(eng, full[s.offset:s.offset + s.numel].view(s.shape), s.param)
+                out[f"model.{s.name}"] = _to_dtensor(
+                    eng, eng._slot_full(s, full[s.offset:s.offset + s.numel].view(s.shape)), s.param)
     return out
 
 
@@ -136,7 +137,7 @@ def load_model_state_dict(model_container: ModelContainer, state: dict[str, torc
                                           strict=False)
             continue
         plain = {}
-        for u in eng.units:
+        for u in eng.all_units:
             for s in u.slots:
                 key = f"model.{s.name}"
                 if key in state:
@@ -155,13 +156,13 @@ def optimizer_state_dict(model_container: ModelContainer, optimizer_container: O
         eng = wrapper.engine
         groups = {g["name"]: g for g in opt.param_groups}
         a = opt.class_args
-        for u in eng.units:
+        for u in eng.all_units:
             m, v = eng.gather_full(u, "exp_avg"), eng.gather_full(u, "exp_avg_sq")
             for s in u.slots:
                 fqn = f"model.{s.name}"
                 sl = slice(s.offset, s.offset + s.numel)
-                out[f"state.{fqn}.exp_avg"] = _to_dtensor(eng, m[sl].view(s.shape), s.param)
-                out[f"state.{fqn}.exp_avg_sq"] = _to_dtensor(eng, v[sl].view(s.shape), s.param)
+                out[f"state.{fqn}.exp_avg"] = _to_dtensor(eng, eng._slot_full(s, m[sl].view(s.shape)), s.param)
+                out[f"state.{fqn}.exp_avg_sq"] = _to_dtensor(eng, eng._slot_full(s, v[sl].view(s.shape)), s.param)
                 out[f"state.{fqn}.step"] = torch.tensor(float(eng.step_count))
                 g = groups.get(s.group, groups["normal"])
                 hyper = {"lr": g["lr"], "betas": tuple(a.get("betas", (0.9, 0.999))), "eps": a.get("eps", 1e-8),
@@ -177,7 +178,7 @@ def load_optimizer_state_dict(model_container, optimizer_container, state: dict)
         eng = wrapper.engine
         for which in ("exp_avg", "exp_avg_sq"):
             plain = {}
-            for u in eng.units:
+            for u in eng.all_units:
                 for s in u.slots:
                     key = f"state.model.{s.name}.{which}"
                     if key in state:
@@ -187,7 +188,7 @@ def load_optimizer_state_dict(model_container, optimizer_container, state: dict)
         if steps:
             eng.step_count = int(max(steps))
         for g in opt.param_groups:
-            for u in eng.units:
+            for u in eng.all_units:
                 for s in u.slots:
                     if s.group == g["name"] and f"param_groups.model.{s.name}.lr" in state:
                         g["lr"] = state[f"param_groups.model.{s.name}.lr"]

@@ -67,15 +67,35 @@ def _flatten_args(args: tuple):
 
 
 def _install_unit_forward(engine: FSDPEngine, module: nn.Module, unit_name: str) -> None:
+    """Routes ``module.forward`` through the engine.  Auxiliary (router) losses produced inside the unit are returned
+    as one more output of the unit and re-added to the accumulator outside: the accumulator must only ever hold
+    tensors of the outer autograd graph, else the final loss would back-propagate into a unit's private graph behind
+    the engine's back (and a checkpointed unit would lose the term altogether)."""
+    from .models.aux_loss import add_aux_loss, swap_aux_loss
+
     inner = module.forward
 
     def forward(*args, **kwargs):
         tensors, rebuild = _flatten_args(args)
+        info = {}
 
         def fn(*ts):
-            return inner(*rebuild(ts), **kwargs)
+            outer = swap_aux_loss(0)
+            try:
+                out = inner(*rebuild(ts), **kwargs)
+            finally:
+                aux = swap_aux_loss(outer)
+            info["tuple"] = isinstance(out, tuple)
+            info["aux"] = isinstance(aux, torch.Tensor)
+            if not info["aux"]:
+                return out
+            return (*out, aux) if info["tuple"] else (out, aux)
 
-        return engine.run_unit(unit_name, fn, *tensors)
+        out = engine.run_unit(unit_name, fn, *tensors)
+        if info.get("aux"):
+            add_aux_loss(out[-1])
+            out = out[:-1] if info["tuple"] else out[0]
+        return out
 
     module.forward = forward
 

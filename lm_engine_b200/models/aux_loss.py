@@ -19,3 +19,11 @@ def add_aux_loss(value: torch.Tensor | float) -> None:
 
 def get_aux_loss() -> torch.Tensor | float:
     return _AUX
+
+
+def swap_aux_loss(value: torch.Tensor | float) -> torch.Tensor | float:
+    """Replaces the accumulator and returns the previous one (a sharded unit collects its own share, which then
+    leaves the unit as an explicit output so that autograd sees it on the outer graph)."""
+    global _AUX
+    old, _AUX = _AUX, value
+    return old

@@ -288,7 +288,16 @@ class CausalLM(nn.Module):
             if not manager.has_tensor(name):
                 continue
             dim = getattr(p, "tp_shard_dim", None)
-            if dim is None or ProcessGroupManager.get_tensor_parallel_world_size() == 1:
+            ep_dim = getattr(p, "ep_shard_dim", None)
+            if ep_dim is not None and ProcessGroupManager.get_expert_parallel_world_size() > 1:
+                # experts are split over the expert-parallel ranks (never combined with a tensor-parallel split)
+                sl = manager.get_slice(name)
+                n = p.size(ep_dim)
+                lo = ProcessGroupManager.get_expert_parallel_rank() * n
+                idx = [slice(None)] * len(sl.get_shape())
+                idx[ep_dim] = slice(lo, lo + n)
+                t = sl[tuple(idx)]
+            elif dim is None or ProcessGroupManager.get_tensor_parallel_world_size() == 1:
                 t = manager.get_tensor(name)
             else:
                 sl = manager.get_slice(name)

@@ -109,6 +109,9 @@ class RowParallelLinear(ParameterizedLinear):
         mark_tp_shard(self.weight, 1, (out_features, in_features))
         if self.bias is not None:
             mark_tp_shard(self.bias, None)
+            # added after the reduce-scatter, i.e. to this rank's slice of the sequence only: its gradient is a
+            # partial sum that the sharding runtime all-reduces over the tensor-parallel group
+            self.bias.sequence_parallel_grad = sequence_parallel and tp > 1
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         if self.tp_world_size == 1:

@@ -42,7 +42,7 @@ class ShardedOptimizer:
     def _build_torch_optimizer(self) -> None:
         groups: dict[str, list[nn.Parameter]] = {g["name"]: [] for g in self.param_groups}
         self._aliases: list[tuple[nn.Parameter, torch.Tensor, torch.Tensor]] = []
-        for u in self.engine.units:
+        for u in self.engine.all_units:
             for g in u.local_group_ranges():
                 sl = slice(g.start, g.end)
                 p = nn.Parameter(u.master[sl])
@@ -84,11 +84,12 @@ class ShardedOptimizer:
         for p, u, sl in self._aliases:
             u.lp_shard[sl].copy_(u.master[sl])
             p.grad = None
-        if e.stage in (1, 2) and e.world > 1:
+        if e.stage in (1, 2):
             import torch.distributed as dist
 
-            for u in e.units:
-                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=e.shard_group)
+            for u in e.all_units:
+                if u.world > 1:
+                    dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
         return e.grad_norm
 
     def state_dict(self) -> dict:

@@ -61,9 +61,17 @@ class ShardedUnit:
 
     def __init__(self, name: str, modules: list[nn.Module], prefixes: list[str], device: torch.device,
                  compute_dtype: torch.dtype, grad_dtype: torch.dtype, shard_world: int, shard_rank: int,
-                 shard_params: bool, shard_state: bool, use_mup_group: bool) -> None:
+                 shard_params: bool, shard_state: bool, use_mup_group: bool, group=None, replica_group=None,
+                 param_filter: Callable[[nn.Parameter], bool] | None = None, is_expert: bool = False) -> None:
         self.name = name
         self.modules = modules
+        # group that shards this unit (the data-parallel sharding group; for expert-parallel parameters the ranks
+        # that hold the same experts) and the group that replicates it (HSDP)
+        self.group, self.replica_group, self.is_expert = group, replica_group, is_expert
+        self.children: list[ShardedUnit] = []   # expert-parallel parameters of the same modules
+        self.peer_shards = None
+        self.grad_post_scale = 1.0
+        self.grad_scaled = False
         self.device, self.compute_dtype, self.grad_dtype = device, compute_dtype, grad_dtype
         self.world, self.rank = shard_world, shard_rank
         self.shard_params = shard_params and shard_world > 1
@@ -73,7 +81,7 @@ class ShardedUnit:
         seen = set()
         for prefix, m in zip(prefixes, modules):
             for n, p in m.named_parameters():
-                if id(p) in seen:
+                if id(p) in seen or (param_filter is not None and not param_filter(p)):
                     continue
                 seen.add(id(p))
                 named.append((f"{prefix}.{n}" if prefix else n, p))
@@ -245,13 +253,43 @@ class FSDPEngine:
         self.checkpoint_units = checkpoint_units or set()
         self.preserve_rng = preserve_rng
         self.is_cuda = self.device.type == "cuda"
-        self.units: list[ShardedUnit] = []
+        # Expert-parallel parameters differ between the ranks of the expert-parallel group, so they are sharded /
+        # reduced over the ranks that own the same experts only; they form a child unit of their block.
+        self.ep_group = ProcessGroupManager.get_expert_parallel_group()
+        self.ep_world = ProcessGroupManager.get_expert_parallel_world_size()
+        edp_group = ProcessGroupManager.get_expert_data_parallel_group() if self.ep_world > 1 else None
+        edp_world = dist.get_world_size(edp_group) if edp_group is not None else 1
+        edp_rank = dist.get_rank(edp_group) if edp_group is not None else 0
+
+        def is_expert_param(p: nn.Parameter) -> bool:
+            return self.ep_world > 1 and getattr(p, "ep_shard_dim", None) is not None
+
+        self.units: list[ShardedUnit] = []        # execution order (prefetch neighbours)
+        self.all_units: list[ShardedUnit] = []    # + expert children, for everything that walks the state
         for name, modules, prefixes in units:
-            self.units.append(ShardedUnit(name, modules, prefixes, self.device, compute_dtype, self.grad_dtype,
-                                          self.world, self.rank, shard_params=stage == 3, shard_state=stage >= 1,
-                                          use_mup_group=use_mup_group))
-        self.by_name = {u.name: u for u in self.units}
-        covered = {id(s.param) for u in self.units for s in u.slots}
+            u = ShardedUnit(name, modules, prefixes, self.device, compute_dtype, self.grad_dtype, self.world,
+                            self.rank, shard_params=stage == 3, shard_state=stage >= 1, use_mup_group=use_mup_group,
+                            group=self.shard_group, replica_group=self.replica_group,
+                            param_filter=lambda p: not is_expert_param(p))
+            self.units.append(u)
+            self.all_units.append(u)
+            if any(is_expert_param(p) for m in modules for p in m.parameters()):
+                assert self.replica_group is None or stage == 0, "expert parallel with HSDP is not supported"
+                sharded = stage >= 1 and edp_world > 1
+                c = ShardedUnit(name + ".experts", modules, prefixes, self.device, compute_dtype, self.grad_dtype,
+                                edp_world if sharded else 1, edp_rank if sharded else 0, shard_params=stage == 3,
+                                shard_state=stage >= 1, use_mup_group=use_mup_group,
+                                group=edp_group if sharded else None,
+                                replica_group=edp_group if (not sharded and edp_world > 1) else None,
+                                param_filter=is_expert_param, is_expert=True)
+                # every rank of the expert-parallel group adds the tokens it sent here, each weighted for the mean
+                # over its own micro-batch: the mean over all data-parallel ranks needs 1 / ep on top of the
+                # average over the ranks that replicate these experts
+                c.grad_post_scale = 1.0 / self.ep_world
+                u.children.append(c)
+                self.all_units.append(c)
+        self.by_name = {u.name: u for u in self.all_units}
+        covered = {id(s.param) for u in self.all_units for s in u.slots}
         missing = [n for n, p in model.named_parameters() if id(p) not in covered]
         assert not missing, f"parameters not covered by any unit: {missing[:5]}"
         self._materialize(init_fn, seed)
@@ -272,6 +310,7 @@ class FSDPEngine:
         self._fence_word = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._inflight: dict[str, torch.Tensor] = {}
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.sumsq_experts = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
         self.step_count = 0
@@ -292,7 +331,8 @@ class FSDPEngine:
         """Gives every unit real storage: parameters are (re)initialised in fp32 into a temporary full buffer, the
         fp32 master slice and the bf16 copy are cut from it."""
         tp_rank = ProcessGroupManager.get_tensor_parallel_rank()
-        for ui, u in enumerate(self.units):
+        ep_rank = ProcessGroupManager.get_expert_parallel_rank() if self.ep_world > 1 else 0
+        for ui, u in enumerate(self.all_units):
             full = torch.zeros(u.numel, dtype=torch.float32, device=self.device)
             meta = any(s.param.is_meta for s in u.slots)
             old = {id(s.param): s.param.data for s in u.slots} if not meta else {}
@@ -305,13 +345,19 @@ class FSDPEngine:
                 s.param.data = view
             if meta:
                 # keyed by the unit's global name, so that a pipeline split initialises the same weights
-                gen_seed = (seed + zlib.crc32(u.name.encode()) + 104729 * tp_rank) % (2 ** 63)
+                gen_seed = (seed + zlib.crc32(u.name.encode()) + 104729 * tp_rank
+                            + (1299709 * ep_rank if u.is_expert else 0)) % (2 ** 63)
+                mine = {id(s.param) for s in u.slots}
                 devs = [self.device] if self.is_cuda else []
                 with torch.random.fork_rng(devices=devs):
                     torch.manual_seed(gen_seed)
                     for m in u.modules:
                         for sub in m.modules():
-                            if hasattr(sub, "reset_parameters"):
+                            # only modules that directly own a parameter of this unit (a block's expert weights
+                            # live in a child unit that is initialised on its own turn)
+                            own = [p for p in sub._parameters.values() if p is not None]
+                            if hasattr(sub, "reset_parameters") and (not own or any(id(p) in mine for p in own)) \
+                                    and (own or not u.is_expert):
                                 sub.reset_parameters()
                     if init_fn is not None:
                         init_fn(u)
@@ -363,8 +409,8 @@ class FSDPEngine:
                 dist.broadcast(s.param.data, src=src, group=tp_group)
 
     def _setup_grad_buffers(self) -> None:
-        for u in self.units:
-            if self.world == 1 or self.stage == 0:
+        for u in self.all_units:
+            if u.world == 1 or self.stage == 0:
                 # the unreduced buffer is the final gradient
                 g = torch.zeros(u.numel, dtype=self.grad_dtype, device=self.device)
                 u.bind_grads(g)
@@ -389,7 +435,7 @@ class FSDPEngine:
 
             return hook
 
-        for u in self.units:
+        for u in self.all_units:
             for s in u.slots:
                 s.param.register_post_accumulate_grad_hook(make_hook())
 
@@ -443,31 +489,38 @@ class FSDPEngine:
         return bufs[i % 2]
 
     # ------------------------------------------------------------------ gather / reduce
-    def _all_gather(self, u: ShardedUnit) -> None:
-        """Starts the all-gather of ``u`` (side stream on CUDA) unless it is already gathered or in flight."""
+    def _all_gather(self, u: ShardedUnit, for_graph: bool = False) -> None:
+        """Starts the all-gather of ``u`` (side stream on CUDA) unless it is already gathered or in flight.
+        ``for_graph``: the gathered weights feed a forward pass whose autograd graph outlives the unit's forward."""
         if u.unsharded or u.name in self._inflight:
             return
-        buf = self._take(self._param_pool, "p", u, self.compute_dtype)
+        if for_graph and u.name not in self.checkpoint_units:
+            # This forward records an autograd graph that lives until the unit's backward, and ops may save views
+            # of the gathered weights in it.  A pooled buffer would be overwritten by the next unit's gather in the
+            # meantime, so such a gather gets storage of its own (released with the graph).
+            buf = torch.empty(u.numel, dtype=self.compute_dtype, device=self.device)
+        else:
+            buf = self._take(self._param_pool, "p", u, self.compute_dtype)
         if self.is_cuda:
             self.ag_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.ag_stream):
-                if self.copy_engine_gather:
+                if self.copy_engine_gather and u.peer_shards is not None:
                     S = u.shard_size
-                    for i in range(self.world):   # own shard first, then the peers in a rank-rotated order
-                        p = (self.rank + i) % self.world
+                    for i in range(u.world):   # own shard first, then the peers in a rank-rotated order
+                        p = (u.rank + i) % u.world
                         buf[p * S:(p + 1) * S].copy_(u.peer_shards[p], non_blocking=True)
                 else:
-                    dist.all_gather_into_tensor(buf, u.lp_shard, group=self.shard_group)
+                    dist.all_gather_into_tensor(buf, u.lp_shard, group=u.group)
                 u.ag_event = torch.cuda.Event()
                 u.ag_event.record(self.ag_stream)
         else:
-            dist.all_gather_into_tensor(buf, u.lp_shard, group=self.shard_group)
+            dist.all_gather_into_tensor(buf, u.lp_shard, group=u.group)
         self._inflight[u.name] = buf
 
-    def _wait_gather(self, u: ShardedUnit) -> None:
+    def _wait_gather(self, u: ShardedUnit, for_graph: bool = False) -> None:
         if u.unsharded:
             return
-        self._all_gather(u)
+        self._all_gather(u, for_graph)
         buf = self._inflight.pop(u.name)
         if self.is_cuda and u.ag_event is not None:
             torch.cuda.current_stream().wait_event(u.ag_event)
@@ -487,25 +540,36 @@ class FSDPEngine:
         return self.units[i] if 0 <= i < len(self.units) else None
 
     # ------------------------------------------------------------------ hooks called by _UnitFunction
+    @staticmethod
+    def _family(u: ShardedUnit | None) -> tuple[ShardedUnit, ...]:
+        return () if u is None else (u, *u.children)
+
     def pre_forward(self, u: ShardedUnit, training: bool) -> None:
-        if training:
-            u.pending_backward += 1
-        self._wait_gather(u)
-        nxt = self._neighbour(u, +1)
-        if nxt is not None and nxt.shard_params:
-            self._all_gather(nxt)
+        for x in self._family(u):
+            if training:
+                x.pending_backward += 1
+            self._wait_gather(x, for_graph=training)
+        for x in self._family(self._neighbour(u, +1)):
+            if x.shard_params:
+                self._all_gather(x, for_graph=training)
 
     def post_forward(self, u: ShardedUnit, training: bool) -> None:
         # the last unit's backward starts right after its forward: keep it gathered
         if u.keep_unsharded or (training and u is self.units[-1] and not self.pipeline_mode):
             return
-        self._reshard(u)
+        for x in self._family(u):
+            self._reshard(x)
 
     def pre_backward(self, u: ShardedUnit) -> None:
-        self._wait_gather(u)
-        prv = self._neighbour(u, -1)
-        if prv is not None and prv.shard_params:
-            self._all_gather(prv)
+        for x in self._family(u):
+            self._wait_gather(x)
+        for x in self._family(self._neighbour(u, -1)):
+            if x.shard_params:
+                self._all_gather(x)
+        for x in self._family(u):
+            self._bind_grad_buffer(x)
+
+    def _bind_grad_buffer(self, u: ShardedUnit) -> None:
         if u.main_grad is None:
             buf = self._take(self._grad_pool, "g", u, self.grad_dtype)
             # the buffer may still be read by the reduce-scatter of the unit that used it last (two units ago)
@@ -520,12 +584,13 @@ class FSDPEngine:
                 s.param.main_grad_stale = True
 
     def post_backward(self, u: ShardedUnit) -> None:
-        u.pending_backward -= 1
-        if u.pending_backward > 0 and not self.pipeline_mode:
-            return  # the unit ran more than once in forward (tied embedding / LM head): reduce after the last use
-        self._reduce_grads(u)
-        if not u.keep_unsharded:
-            self._reshard(u)
+        for x in self._family(u):
+            x.pending_backward -= 1
+            if x.pending_backward > 0 and not self.pipeline_mode:
+                continue  # the unit ran more than once in forward (tied embedding / LM head): reduce after the last
+            self._reduce_grads(x)
+            if not u.keep_unsharded:
+                self._reshard(x)
 
     def _reduce_grads(self, u: ShardedUnit) -> None:
         tp_group = ProcessGroupManager.get_tensor_parallel_group()
@@ -533,36 +598,37 @@ class FSDPEngine:
             for s in u.slots:
                 if getattr(s.param, "sequence_parallel_grad", False):
                     dist.all_reduce(s.param.main_grad, group=tp_group)
-        if self.world == 1 and self.replica_group is None:
+        if u.world == 1 and u.replica_group is None:
             u.grad_ready = True
             return
         full = u.main_grad
         for sl in u.slots:   # parameters that received no gradient in this pass
-            if getattr(sl.param, "main_grad_stale", False) and self.world > 1 and self.stage != 0:
+            if getattr(sl.param, "main_grad_stale", False) and u.world > 1 and self.stage != 0:
                 sl.param.main_grad.zero_()
                 sl.param.main_grad_stale = False
         avg = dist.ReduceOp.AVG if self.is_cuda else dist.ReduceOp.SUM
-        dp_total = ProcessGroupManager.get_data_parallel_world_size()
+        # ranks that hold a copy of these parameters (all data-parallel ranks; for experts, the expert replicas)
+        dp_total = u.world * (dist.get_world_size(u.replica_group) if u.replica_group is not None else 1)
 
         def run() -> None:
-            if self.stage == 0 or self.world == 1:
-                if self.replica_group is not None:
+            if self.stage == 0 or u.world == 1:
+                if u.replica_group is not None:
                     if not self.is_cuda:
                         full.div_(dp_total)
-                    dist.all_reduce(full, op=avg, group=self.replica_group)
+                    dist.all_reduce(full, op=avg, group=u.replica_group)
                 return
             out = torch.empty(u.shard_size, dtype=full.dtype, device=self.device)
             if self.is_cuda:
-                dist.reduce_scatter_tensor(out, full, op=avg, group=self.shard_group)
+                dist.reduce_scatter_tensor(out, full, op=avg, group=u.group)
             else:
                 tmp = full / dp_total
-                dist.all_reduce(tmp, group=self.shard_group)
+                dist.all_reduce(tmp, group=u.group)
                 out.copy_(tmp[u.rank * u.shard_size:(u.rank + 1) * u.shard_size])
-            if self.replica_group is not None:
+            if u.replica_group is not None:
                 if self.is_cuda:
-                    dist.all_reduce(out, op=avg, group=self.replica_group)
+                    dist.all_reduce(out, op=avg, group=u.replica_group)
                 else:
-                    dist.all_reduce(out, group=self.replica_group)
+                    dist.all_reduce(out, group=u.replica_group)
             if u.grad_shard_fresh:
                 u.grad_shard.copy_(out)
                 u.grad_shard_fresh = False
@@ -578,7 +644,7 @@ class FSDPEngine:
                 self._buffer_events[full.data_ptr()] = u.rs_event
         else:
             run()
-        if self.stage != 0 and self.world > 1:
+        if self.stage != 0 and u.world > 1:
             u.main_grad = None
             for s in u.slots:
                 s.param.main_grad = None
@@ -600,8 +666,9 @@ class FSDPEngine:
         """Starts a new accumulation window.  Persistent gradient buffers (single shard / ZeRO-0) are not cleared:
         every parameter is flagged so that its first gradient write of the step overwrites instead of accumulating;
         parameters that received no gradient are cleared in :meth:`finish_backward`."""
-        lazy = self.world == 1 or self.stage == 0
-        for u in self.units:
+        for u in self.all_units:
+            lazy = u.world == 1 or self.stage == 0
+            u.grad_scaled = False
             if lazy and u.main_grad is not None:
                 for s in u.slots:
                     s.param.main_grad_stale = True
@@ -613,7 +680,7 @@ class FSDPEngine:
 
     def finish_backward(self) -> None:
         """Joins the reduction stream; call once after the last ``backward`` of a step."""
-        for u in self.units:
+        for u in self.all_units:
             for s in u.slots:
                 if getattr(s.param, "main_grad_stale", False):
                     mg = getattr(s.param, "main_grad", None)
@@ -623,10 +690,13 @@ class FSDPEngine:
         if self.is_cuda:
             torch.cuda.current_stream().wait_stream(self.rs_stream)
             torch.cuda.current_stream().wait_stream(self.ag_stream)
-        for u in self.units:
+        for u in self.all_units:
             if u.grad_shard_fresh and u.main_grad is None and u.grad_shard is not None:
                 u.grad_shard.zero_()
             u.grad_shard_fresh = False if u.main_grad is None else u.grad_shard_fresh
+            if u.grad_post_scale != 1.0 and not u.grad_scaled:
+                u.grad_shard.mul_(u.grad_post_scale)
+                u.grad_scaled = True
 
     @torch.no_grad()
     def clip_and_step(self, *, lr: float, lr_by_group: dict[str, float] | None = None, betas=(0.9, 0.95),
@@ -645,15 +715,15 @@ class FSDPEngine:
                 self.sumsq.add_(extra_sumsq)
         ops.clip_coef_(self.sumsq, max_grad_norm, self.grad_norm, self.clip_coef)
         lr_by_group = lr_by_group or {}
-        for u in self.units:
+        for u in self.all_units:
             for g in u.local_group_ranges():
                 sl = slice(g.start, g.end)
                 ops.adamw_step(u.master[sl], u.exp_avg[sl], u.exp_avg_sq[sl], u.grad_shard[sl], u.lp_shard[sl],
                                lr=lr_by_group.get(g.name, lr), betas=betas, eps=eps,
                                weight_decay=0.0 if g.name == "no_weight_decay" else weight_decay,
                                step=self.step_count, gscale=self.clip_coef)
-            if self.stage in (1, 2) and self.world > 1:
-                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=self.shard_group)
+            if self.stage in (1, 2) and u.world > 1:
+                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
         self._cross_rank_fence()
         return self.grad_norm
 
@@ -663,9 +733,18 @@ class FSDPEngine:
         the sharding and tensor-parallel groups; over the pipeline group too when asked)."""
         self.finish_backward()
         first = True
-        for u in self.units:
-            ops.sumsq_(u.grad_shard, self.sumsq, accumulate=not first)
-            first = False
+        for u in self.all_units:
+            if not u.is_expert:
+                ops.sumsq_(u.grad_shard, self.sumsq, accumulate=not first)
+                first = False
+        experts = [u for u in self.all_units if u.is_expert]
+        if experts:
+            # distinct experts on every rank of the expert-parallel group; shards over the expert replicas
+            for i, u in enumerate(experts):
+                ops.sumsq_(u.grad_shard, self.sumsq_experts, accumulate=i > 0)
+            if experts[0].group is not None:
+                dist.all_reduce(self.sumsq_experts, group=experts[0].group)
+            dist.all_reduce(self.sumsq_experts, group=self.ep_group)
         self._reduce_norm(include_pipeline_group)
         return self.sumsq
 
@@ -673,12 +752,14 @@ class FSDPEngine:
         """Sum of squares over every group that holds a distinct piece of the model."""
         if self.stage >= 1 and self.shard_group is not None:
             dist.all_reduce(self.sumsq, group=self.shard_group)
+        if self.ep_world > 1:
+            self.sumsq.add_(self.sumsq_experts)
         tp = ProcessGroupManager.get_tensor_parallel_group()
         if tp is not None:
             # replicated parameters were counted tp times; their share is small and the reference counts DTensor
             # replicas once, so subtract the surplus
             rep = torch.zeros(1, dtype=torch.float32, device=self.device)
-            for u in self.units:
+            for u in self.all_units:
                 for s in u.slots:
                     if getattr(s.param, "tp_shard_dim", None) is None:
                         lo = max(s.offset, u.state_lo) - u.state_lo
@@ -703,25 +784,41 @@ class FSDPEngine:
         if not u.shard_state:
             return t.float().clone()
         out = torch.empty(u.numel, dtype=t.dtype, device=self.device)
-        dist.all_gather_into_tensor(out, t.contiguous(), group=self.shard_group)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=u.group)
         return out.float()
+
+    def _slot_full(self, s: "_Slot", local: torch.Tensor) -> torch.Tensor:
+        """Expert-parallel parameters: the tensor over all experts (concatenated over the expert-parallel group)."""
+        dim = getattr(s.param, "ep_shard_dim", None)
+        if self.ep_world == 1 or dim is None:
+            return local
+        parts = [torch.empty_like(local) for _ in range(self.ep_world)]
+        dist.all_gather(parts, local.contiguous(), group=self.ep_group)
+        return torch.cat(parts, dim=dim)
+
+    def _slot_local(self, s: "_Slot", full: torch.Tensor) -> torch.Tensor:
+        dim = getattr(s.param, "ep_shard_dim", None)
+        if self.ep_world == 1 or dim is None or full.size(dim) == s.shape[dim]:
+            return full
+        return full.chunk(self.ep_world, dim=dim)[ProcessGroupManager.get_expert_parallel_rank()]
 
     @torch.no_grad()
     def full_state_dict(self, which: str = "master") -> dict[str, torch.Tensor]:
         out = {}
-        for u in self.units:
+        for u in self.all_units:
             full = self.gather_full(u, which)
             for s in u.slots:
-                out[s.name] = full[s.offset:s.offset + s.numel].view(s.shape).clone()
+                out[s.name] = self._slot_full(s, full[s.offset:s.offset + s.numel].view(s.shape).clone())
         return out
 
     @torch.no_grad()
     def load_full_state_dict(self, sd: dict[str, torch.Tensor], which: str = "master") -> None:
-        for u in self.units:
+        for u in self.all_units:
             full = self.gather_full(u, which)
             for s in u.slots:
                 if s.name in sd:
-                    full[s.offset:s.offset + s.numel].copy_(sd[s.name].reshape(-1).to(full.device))
+                    full[s.offset:s.offset + s.numel].copy_(
+                        self._slot_local(s, sd[s.name]).reshape(-1).to(full.device))
             piece = full[u.state_lo:u.state_hi]
             {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq}[which].copy_(piece)
             if which == "master":
@@ -733,4 +830,4 @@ class FSDPEngine:
             self._cross_rank_fence()
 
     def num_parameters(self) -> int:
-        return sum(s.numel for u in self.units for s in u.slots)
+        return sum(s.numel for u in self.all_units for s in u.slots)

@@ -37,7 +37,8 @@ def _all_gather_dim(x: torch.Tensor, dim: int, group) -> torch.Tensor:
         dist.all_gather_into_tensor(out, x, group=group)
         return out
     parts = torch.empty((world, *x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(parts, x, group=group)
+    # flat view: the gloo backend only takes the concatenated output form
+    dist.all_gather_into_tensor(parts.view(-1, *x.shape[1:]) if x.dim() > 0 else parts, x, group=group)
     return torch.cat(list(parts.unbind(0)), dim=dim)
 
 
