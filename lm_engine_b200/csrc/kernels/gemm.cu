@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "../lme_api.h"
 
+#include "gather.cuh"
+
 #include <mutex>
 #include <stdio.h>
 
@@ -174,11 +176,14 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row,
 
 // F8: operands are 1-byte e4m3 / e5m2, K-major; a 128-byte swizzle row then holds 128 elements of K and one MMA
 // consumes 32 of them, so the byte geometry of the pipeline is identical to the bf16 one.
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false>
+// GATHER: the first g.n_copy CTAs of the grid pull an operand's rows from the peers (gather.cuh) while the others
+// multiply; the TMA producer waits for the segments under each operand tile.
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs p) {
+                 const GemmArgs p, const __grid_constant__ GatherArgs g) {
     static_assert(!F8 || (!A_MN && !B_MN), "8-bit operands are K-major");
+    static_assert(!GATHER || (!A_MN && !B_MN), "gathered operands are K-major");
     constexpr int BKE = F8 ? 2 * BK : BK;  // K elements per pipeline stage
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
@@ -189,6 +194,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t* tempty_bar = tfull_bar + 2;
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tempty_bar + 2);
 
+    const int n_copy = GATHER ? g.n_copy : 0;
+    if (GATHER && static_cast<int>(blockIdx.x) < n_copy) {
+        gather_copy_cta(g, smem, blockIdx.x);
+        return;
+    }
+    const int cta = blockIdx.x - n_copy, n_cta = gridDim.x - n_copy;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
@@ -223,10 +234,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
                 int mb, nb;
                 tile_coords(tile, p, mb, nb);
+                if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
                 const int m0 = mb * BM, n0 = nb * BN;
+                if (GATHER) {
+                    const bool arrived = g.which == 0 ? gather_wait_rows(g, m0, BM, p.M)
+                                                      : gather_wait_rows(g, n0, BN, p.N);
+                    if (!arrived) { ok = false; break; }
+                }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -260,7 +277,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       : make_idesc(1, 1, A_MN, B_MN, BM, BN);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++tcount) {
                 const int acc = tcount & 1;
                 const uint32_t aph = (tcount >> 1) & 1;
                 if (!mbar_wait(&tempty_bar[acc], aph ^ 1, 200 + acc)) { ok = false; break; }
@@ -300,9 +317,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool swiglu = p.flags & LME_GEMM_SWIGLU;
         float dequant = 1.0f;
         if (F8) dequant = __ldg(p.scale_a) * __ldg(p.scale_b);
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++tcount) {
             int mb, nb;
             tile_coords(tile, p, mb, nb);
+            if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
             if (!mbar_wait(&tfull_bar[acc], aph, 400 + acc)) { ok = false; break; }
@@ -406,11 +424,12 @@ static int num_sms() {
     return g_num_sms;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p, int max_ctas,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const GatherArgs* gather = nullptr) {
     using L = SmemLayout<BN, STAGES>;
-    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8>;
+    static_assert(!GATHER || L::TILES_BYTES >= GATHER_SLOTS * GATHER_SEG_BYTES, "copy CTAs reuse the tile ring");
+    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8, GATHER>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
@@ -421,8 +440,20 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p
     p.tiles_n = (p.N + BN - 1) / BN;
     p.group_m = 8;
     int tiles = p.tiles_m * p.tiles_n;
+    GatherArgs g;
+    if (GATHER) {
+        g = *gather;
+        // every CTA of this grid must be resident at once (the multiplying CTAs wait for the copy CTAs)
+        int gemm_ctas = max_ctas - g.n_copy;
+        if (gemm_ctas < 1) return LME_ERR_SHAPE;
+        if (tiles < gemm_ctas) gemm_ctas = tiles;
+        kern<<<gemm_ctas + g.n_copy, 192, L::TOTAL, stream>>>(ta, tb, p, g);
+        return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+    }
+    g.enabled = 0;
+    g.n_copy = 0;
     int grid = tiles < max_ctas ? tiles : max_ctas;
-    kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, p);
+    kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, p, g);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 
@@ -502,6 +533,68 @@ extern "C" int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (BN == 128) return launch_gemm<128, 6, false, false, true>(ta, tb, p, max_ctas, st);
     return launch_gemm<256, 4, false, false, true>(ta, tb, p, max_ctas, st);
+}
+
+// C[M, N] = A_gathered[M, K] * B[N, K]^T where the rows of A are the concatenation, in rank order, of `world`
+// contributions of shard_bytes each.  This rank's contribution is `local_src`; the peers' arrive through the
+// symmetric staging buffers `stage[r]` (already offset to the slot of this call) and are written to `A_gathered`
+// (local) by copy CTAs of the same grid while the other CTAs multiply the rows that are there.
+//   pads[r]   : int32 signal pad (16 words) of rank r in symmetric memory
+//   ready     : local int32, world * ceil(shard_bytes / 32 KB) words, never reset (compared against seq)
+//   counters  : local uint32[2], zero before the first call
+//   seq       : 1, 2, 3, ... per call on this set of buffers (the same on every rank)
+extern "C" int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, long long ldb, void* C,
+                                         long long ldc, int M, int N, int K, int flags, const void* bias,
+                                         const void* residual, long long ldr, void* preact, long long ldp,
+                                         const void* local_src, void* const* stage, int* const* pads, int* ready,
+                                         unsigned int* counters, long long shard_bytes, int rank, int world,
+                                         int seq, int n_copy, int max_ctas, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return LME_OK;
+    if ((N % 8) || (lda % 8) || (ldb % 8) || (ldc % 4)) return LME_ERR_SHAPE;
+    if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world || seq < 1 || n_copy < 1)
+        return LME_ERR_SHAPE;
+    if (lda != K || shard_bytes * world != static_cast<long long>(M) * K * 2 || (shard_bytes % 16))
+        return LME_ERR_SHAPE;   // the gathered operand is dense and splits evenly
+    if ((reinterpret_cast<uintptr_t>(A_gathered) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+         reinterpret_cast<uintptr_t>(local_src)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16_2d(&ta, A_gathered, K, M, lda, 64, BM);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
+    if (rc) return rc;
+    GemmArgs p;
+    p.M = M; p.N = N; p.K = K;
+    p.C = C; p.ldc = ldc;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+    p.preact = static_cast<__nv_bfloat16*>(preact); p.ldp = ldp;
+    p.flags = flags;
+    p.a_fmt = p.b_fmt = 0;
+    p.scale_a = p.scale_b = nullptr;
+    GatherArgs g;
+    g.enabled = 1;
+    g.rank = rank; g.world = world; g.n_copy = n_copy; g.seq = seq;
+    g.shard_bytes = shard_bytes;
+    g.operand_off = 0;
+    g.row_bytes = lda * 2;
+    g.rows_per_tile = BM;
+    g.which = 0;
+    const int tiles_m = (M + BM - 1) / BM;
+    g.rotate_tiles = static_cast<int>((static_cast<long long>(rank) * tiles_m) / world);
+    g.local_src = static_cast<const uint8_t*>(local_src);
+    for (int r = 0; r < GATHER_MAX_RANKS; ++r) {
+        g.stage[r] = r < world ? static_cast<uint8_t*>(stage[r]) : nullptr;
+        g.pad[r] = r < world ? pads[r] : nullptr;
+    }
+    g.dst = static_cast<uint8_t*>(A_gathered);
+    g.ready = ready;
+    g.counters = counters;
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (BN == 128) return launch_gemm<128, 6, false, false, false, true>(ta, tb, p, max_ctas, st, &g);
+    return launch_gemm<256, 4, false, false, false, true>(ta, tb, p, max_ctas, st, &g);
 }
 
 extern "C" int lme_read_status(unsigned int* out8, int clear) {

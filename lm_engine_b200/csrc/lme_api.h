@@ -36,6 +36,18 @@ int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void* B, int b_f
                  const void* bias, const void* residual, long long ldr, void* preact, long long ldp, int max_ctas,
                  void* stream);
 
+// All-gather fused into the GEMM: C = A_gathered * B^T where A_gathered [M, K] (local, written by this call) is the
+// concatenation in rank order of `world` contributions of shard_bytes each.  Copy CTAs of the GEMM's own grid move
+// this rank's contribution (local_src) and the peers' (through the symmetric staging buffers stage[r]) with bulk
+// asynchronous copies over NVLink while the other CTAs multiply the rows that have arrived.  pads[r]: 16-word int32
+// signal pad of rank r in symmetric memory; ready / counters: local scratch words (see kernels/gather.cuh);
+// seq = 1, 2, ... per call on one set of buffers, the same on every rank.  All waits are bounded.
+int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                              int M, int N, int K, int flags, const void* bias, const void* residual, long long ldr,
+                              void* preact, long long ldp, const void* local_src, void* const* stage,
+                              int* const* pads, int* ready, unsigned int* counters, long long shard_bytes, int rank,
+                              int world, int seq, int n_copy, int max_ctas, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

@@ -1,0 +1,77 @@
+"""Fused all-gather -> GEMM over NVLink peer memory on 2 GPUs (child processes, NVLS off): results against a plain
+all-gather followed by an fp32 matmul, over several calls so that both staging slots and the flag protocol cycle."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lm_engine_b200.ops import _lib
+        from lm_engine_b200.parallel.symm import all_gather_matmul
+
+        errs = []
+        for (t, K, N), calls in (((512, 1024, 768), 5), ((4096, 4096, 6144), 3), ((384, 256, 264), 2)):
+            w = (torch.randn(N, K, device="cuda", generator=torch.Generator("cuda").manual_seed(7)) * 0.05
+                 ).to(torch.bfloat16)
+            for c in range(calls):
+                g = torch.Generator("cuda").manual_seed(100 * rank + c)
+                x = torch.randn(t, K, device="cuda", generator=g).to(torch.bfloat16)
+                y, xg = all_gather_matmul(x, w, dist.group.WORLD)
+                ref_x = torch.empty(world * t, K, device="cuda", dtype=torch.bfloat16)
+                dist.all_gather_into_tensor(ref_x, x)
+                ref = ref_x.float() @ w.float().t()
+                errs.append(float((xg != ref_x).sum()))
+                errs.append(float((y.float() - ref).abs().max() / ref.abs().max()))
+        torch.cuda.synchronize()
+        q.put((rank, "ok", (errs, _lib.read_status())))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_all_gather_matmul_two_gpus():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    try:
+        for _ in range(2):
+            rank, status, payload = q.get(timeout=240)
+            assert status == "ok", payload
+            res[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    for rank, (errs, status) in res.items():
+        assert status[0] == 0, status
+        for i in range(0, len(errs), 2):
+            assert errs[i] == 0, f"rank {rank}: gathered operand differs ({errs[i]} elements)"
+            assert errs[i + 1] < 1e-2, f"rank {rank}: GEMM error {errs[i + 1]}"
