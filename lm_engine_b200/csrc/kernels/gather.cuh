@@ -8,11 +8,9 @@
 // under an operand tile before loading it.
 //
 // Cross-rank protocol (all words live in symmetric memory, zero at start, `seq` grows by one per call):
-//   own contribution  -> stage[rank][seq & 1] (symmetric), once the peers' done[] words show they finished reading
-//                        the previous use of that slot (call seq - 2)
-//   sig[rank] := seq     written into every peer's pad after the stage is complete: "rank's data for seq is there"
+//   own contribution  -> stage[rank][seq & 1] (symmetric) by a device-to-device copy ahead of the kernel
+//   sig[rank] := seq     written into every peer's pad when the kernel starts: "rank's data for seq is there"
 //   pull from peer p     after our pad shows sig[p] >= seq
-//   done[rank] := seq    written into every peer's pad after all pulls of this call are complete
 // Every wait is bounded (LME_WAIT_LIMIT_NS); on expiry the status word is set and the CTA returns, which makes the
 // GEMM CTAs run into their own bounded waits and return as well.
 #pragma once
@@ -24,6 +22,7 @@ static constexpr int GATHER_SEG_SHIFT = 15;                 // 32 KB segments
 static constexpr int GATHER_SEG_BYTES = 1 << GATHER_SEG_SHIFT;
 static constexpr int GATHER_SLOTS = 6;
 static constexpr int GATHER_LAG = 4;                        // loads in flight ahead of the store stage
+static constexpr int GATHER_FLAG_LAG = 3;                   // stores allowed in flight behind a published flag
 
 // layout of the int32 signal pad of one rank (symmetric memory)
 static constexpr int PAD_SIG = 0;                           // [8]  sig[src]: src published its stage for call n
@@ -39,12 +38,16 @@ struct GatherArgs {
     int rows_per_tile;          // BM (A gathered) or BN (B gathered)
     int which;                  // 0: rows of A arrive, 1: rows of B arrive
     int rotate_tiles;           // m-tile rotation so that locally available rows are multiplied first
-    const uint8_t* local_src;   // this rank's contribution, any local memory
+    const uint8_t* local_src;   // this rank's contribution (the GEMM reads its own rows from here)
     uint8_t* stage[GATHER_MAX_RANKS];   // slot-selected staging buffer of every rank ([rank] = ours)
     uint8_t* dst;               // local gathered buffer, world * shard_bytes
     int* ready;                 // local, one word per segment of dst
     int* pad[GATHER_MAX_RANKS];         // signal pad of every rank ([rank] = ours)
     unsigned int* counters;     // local, 2 words: copy-CTA arrival counters (monotonic)
+    int local_row0, local_rows; // rows of the gathered operand that are this rank's own (read from local_src)
+    int flag_every;             // publish readiness every this many segments of a copy CTA
+    int seg_shift;              // log2 of the bytes covered by one ready word (15 with copy CTAs; the chunk size
+                                // when copy engines deliver the data and the stream writes the words)
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -120,7 +123,7 @@ __device__ __forceinline__ void bulk_wait_all() {
 // Runs on ONE thread.  Returns false on a timed-out wait.
 __device__ bool gather_copy_range(uint8_t* smem, uint64_t* bars, uint32_t& ring_it, const uint8_t* src,
                                   uint8_t* dst_a, uint8_t* dst_b, long long bytes, int* ready, int seq, int cta,
-                                  int n_cta) {
+                                  int n_cta, int flag_every) {
     const int nseg = static_cast<int>((bytes + GATHER_SEG_BYTES - 1) >> GATHER_SEG_SHIFT);
     const int mine = (nseg - cta + n_cta - 1) / n_cta;      // segments cta, cta + n_cta, ...
     if (mine <= 0) return true;
@@ -152,12 +155,12 @@ __device__ bool gather_copy_range(uint8_t* smem, uint64_t* bars, uint32_t& ring_
             bulk_s2g(dst_a + off, smem + slot * GATHER_SEG_BYTES, seg_bytes(s));
             if (dst_b != nullptr) bulk_s2g(dst_b + off, smem + slot * GATHER_SEG_BYTES, seg_bytes(s));
             bulk_commit();
-            if (ready != nullptr && j >= 1) {
-                bulk_wait_all<1>();   // everything but the group just committed is complete
-                fence_proxy_async_all();
-                __threadfence();
-                st_release_gpu(&ready[seg_of(j - 1)], seq);
-                flagged = j;
+            if (ready != nullptr && j >= GATHER_FLAG_LAG && ((j - GATHER_FLAG_LAG + 1) % flag_every) == 0) {
+                // all but the newest groups are complete (wait_group makes their writes visible to this thread, the
+                // release below publishes them): flags trail the stores so that the ring never drains
+                bulk_wait_all<GATHER_FLAG_LAG>();
+                for (int f = flagged; f <= j - GATHER_FLAG_LAG; ++f) st_release_gpu(&ready[seg_of(f)], seq);
+                flagged = j - GATHER_FLAG_LAG + 1;
             }
         }
     }
@@ -180,33 +183,23 @@ __device__ void gather_copy_cta(const GatherArgs& g, uint8_t* smem, int cta) {
     uint32_t ring_it = 0;
     int* my_pad = g.pad[g.rank];
     const int nseg_shard = static_cast<int>((g.shard_bytes + GATHER_SEG_BYTES - 1) >> GATHER_SEG_SHIFT);
-    // 0. the staging slot was last used by call seq - 2: every peer must have finished reading it
-    for (int p = 0; p < g.world; ++p)
-        if (p != g.rank && !wait_flag_sys(&my_pad[PAD_DONE + p], g.seq - 2, 800 + p)) return;
-    // 1. own contribution -> staging (for the peers) and -> its place in the gathered buffer
-    if (!gather_copy_range(smem, bars, ring_it, g.local_src, g.dst + g.rank * g.shard_bytes, g.stage[g.rank],
-                           g.shard_bytes, g.ready + g.rank * nseg_shard, g.seq, cta, g.n_copy))
-        return;
-    // all copy CTAs have written their part of the stage -> publish
-    const unsigned int target = static_cast<unsigned int>(g.seq) * g.n_copy;
-    if (atomicAdd(&g.counters[0], 1u) + 1u == target) {
+    // 1. This rank's contribution was copied into its staging slot before this kernel (stream order), so it can be
+    //    announced right away.  Two slots need no "done" handshake before that copy overwrites one: the slot was
+    //    last read by the peers in call seq - 2, and in call seq - 1 this rank waited for every peer's sig, which a
+    //    peer only sends from the kernel that follows its call seq - 2 in stream order.
+    if (cta == 0) {
         __threadfence_system();
         for (int p = 0; p < g.world; ++p)
             if (p != g.rank) st_release_sys(&g.pad[p][PAD_SIG + g.rank], g.seq);
     }
-    // 2. pull the peers, nearest-rank-first rotation so that the peers are read evenly
+    // 2. pull the peers, nearest rank first, so that every peer is read by one rank at a time
     for (int i = 1; i < g.world; ++i) {
         const int p = (g.rank + i) % g.world;
         if (!wait_flag_sys(&my_pad[PAD_SIG + p], g.seq, 820 + p)) return;
+        fence_proxy_async_all();   // the bulk (async proxy) reads below are ordered after the acquire above
         if (!gather_copy_range(smem, bars, ring_it, g.stage[p], g.dst + p * g.shard_bytes, nullptr, g.shard_bytes,
-                               g.ready + p * nseg_shard, g.seq, cta, g.n_copy))
+                               g.ready + p * nseg_shard, g.seq, cta, g.n_copy, g.flag_every))
             return;
-    }
-    // 3. tell the peers that their staging slot is free again
-    if (atomicAdd(&g.counters[1], 1u) + 1u == target) {
-        __threadfence_system();
-        for (int p = 0; p < g.world; ++p)
-            if (p != g.rank) st_release_sys(&g.pad[p][PAD_DONE + g.rank], g.seq);
     }
 }
 
@@ -217,18 +210,46 @@ __device__ __forceinline__ bool gather_wait_rows(const GatherArgs& g, int r0, in
     const long long lo = g.operand_off + static_cast<long long>(r0) * g.row_bytes;
     const long long hi = g.operand_off + static_cast<long long>(r1) * g.row_bytes - 1;
     // segment numbering is per shard (a shard's last segment may be partial)
-    const int nseg_shard = static_cast<int>((g.shard_bytes + GATHER_SEG_BYTES - 1) >> GATHER_SEG_SHIFT);
+    const long long seg_bytes = 1ll << g.seg_shift;
+    const int nseg_shard = static_cast<int>((g.shard_bytes + seg_bytes - 1) >> g.seg_shift);
     for (long long b = lo; b <= hi;) {
         const int shard = static_cast<int>(b / g.shard_bytes);
         const long long in = b - shard * g.shard_bytes;
-        const int seg = static_cast<int>(in >> GATHER_SEG_SHIFT);
+        const int seg = static_cast<int>(in >> g.seg_shift);
         if (!wait_flag_gpu(&g.ready[shard * nseg_shard + seg], g.seq, 900)) return false;
-        long long next = shard * g.shard_bytes + (static_cast<long long>(seg + 1) << GATHER_SEG_SHIFT);
+        long long next = shard * g.shard_bytes + (static_cast<long long>(seg + 1) << g.seg_shift);
         const long long shard_end = (shard + 1) * g.shard_bytes;
         b = next < shard_end ? next : shard_end;
     }
     fence_proxy_async_all();
     return true;
 }
+
+// Announces this rank's staging slot to the peers (one thread).
+__global__ void gather_signal_kernel(GatherArgs g) {
+    __threadfence_system();
+    for (int p = 0; p < g.world; ++p)
+        if (p != g.rank) st_release_sys(&g.pad[p][PAD_SIG + g.rank], g.seq);
+}
+// Holds a stream until peer `src` has announced call `seq` (one thread, bounded: on expiry the status word is set
+// and the stream continues, so the copies behind it read a stale slot but nothing hangs).
+__global__ void gather_wait_peer_kernel(const int* word, int seq, unsigned int id) { wait_flag_sys(word, seq, id); }
+
+// ----------------------------------------------------------------------------------------------------------------
+// GEMM -> reduce-scatter fused into the epilogue.  Every rank multiplies its K-slice for all M rows; the rows are
+// owned by the ranks in equal blocks.  Tiles of rows owned by a peer are stored (bf16) straight into the owner's
+// receive slab over NVLink, followed by a per-(tile, warp) arrival flag; tiles of own rows are multiplied last, and
+// their epilogue adds the partial results that the peers have delivered meanwhile, then bias / residual, and writes
+// the final output.  No separate reduction pass, no extra CTAs.
+// Two slab slots (seq & 1) need no "done" handshake: a rank overwrites a peer's slot of call seq - 2 only after its
+// own call seq - 1 consumed that peer's flags of call seq - 1, which the peer wrote after finishing call seq - 2.
+struct RsArgs {
+    int enabled, rank, world, seq;
+    int rows_per_rank, tiles_per_rank;   // rows_per_rank is a multiple of the tile height
+    int rotate;                          // m-tile rotation: rows of rank + 1 first, own rows last
+    long long slab_ld;                   // N
+    uint8_t* slab[GATHER_MAX_RANKS];     // slot-selected receive slab of every rank: [src][rows_per_rank][N] bf16
+    int* flags[GATHER_MAX_RANKS];        // arrival flags of every rank: [src][tiles_per_rank][tiles_n][4]
+};
 
 }  // namespace lme

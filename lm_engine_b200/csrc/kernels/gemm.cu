@@ -21,6 +21,7 @@
 #include "gather.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 #include <stdio.h>
 
 namespace lme {
@@ -178,12 +179,15 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row,
 // consumes 32 of them, so the byte geometry of the pipeline is identical to the bf16 one.
 // GATHER: the first g.n_copy CTAs of the grid pull an operand's rows from the peers (gather.cuh) while the others
 // multiply; the TMA producer waits for the segments under each operand tile.
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false>
+// RS: the epilogue reduce-scatters the product over the ranks (RsArgs in gather.cuh).
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false, bool RS = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs p, const __grid_constant__ GatherArgs g) {
+                 const GemmArgs p, const __grid_constant__ GatherArgs g,
+                 const __grid_constant__ CUtensorMap tmLocal, const __grid_constant__ RsArgs rs) {
+    static_assert(!(GATHER && RS), "one fused collective per kernel");
     static_assert(!F8 || (!A_MN && !B_MN), "8-bit operands are K-major");
-    static_assert(!GATHER || (!A_MN && !B_MN), "gathered operands are K-major");
+    static_assert(!GATHER || !A_MN, "the gathered operand is K-major");
     constexpr int BKE = F8 ? 2 * BK : BK;  // K elements per pipeline stage
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
@@ -238,11 +242,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 int mb, nb;
                 tile_coords(tile, p, mb, nb);
                 if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
+                if (RS) mb = (mb + rs.rotate) % p.tiles_m;
                 const int m0 = mb * BM, n0 = nb * BN;
+                // rows that are entirely this rank's own contribution are read where they already are
+                bool own_rows = false;
                 if (GATHER) {
-                    const bool arrived = g.which == 0 ? gather_wait_rows(g, m0, BM, p.M)
-                                                      : gather_wait_rows(g, n0, BN, p.N);
-                    if (!arrived) { ok = false; break; }
+                    own_rows = g.which == 0 && m0 >= g.local_row0 && m0 + BM <= g.local_row0 + g.local_rows;
+                    if (!own_rows) {
+                        const bool arrived = g.which == 0 ? gather_wait_rows(g, m0, BM, p.M)
+                                                          : gather_wait_rows(g, n0, BN, p.N);
+                        if (!arrived) { ok = false; break; }
+                    }
                 }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -256,6 +266,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c)
                             tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[s], m0 + c * 64, k0);
+                    } else if (GATHER && own_rows) {
+                        tma_load_2d(sa, &tmLocal, &full_bar[s], k0, m0 - g.local_row0);
                     } else {
                         tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
                     }
@@ -321,6 +333,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int mb, nb;
             tile_coords(tile, p, mb, nb);
             if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
+            if (RS) mb = (mb + rs.rotate) % p.tiles_m;
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
             if (!mbar_wait(&tfull_bar[acc], aph, 400 + acc)) { ok = false; break; }
@@ -328,6 +341,109 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int row = mb * BM + q * 32 + lane;
             const bool row_ok = row < p.M;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+            if (RS) {
+                const int owner = mb / rs.tiles_per_rank;
+                const int lmt = mb - owner * rs.tiles_per_rank;
+                const int lrow = lmt * BM + q * 32 + lane;   // row inside the owner's block
+                if (owner != rs.rank) {
+                    // A peer's rows: bf16 partial product into the owner's slab, then the arrival flag.  The
+                    // accumulator arrives one row per lane; it is turned through shared memory (16-byte chunks
+                    // XOR-swizzled by row) so that a store instruction covers two full 256-byte row pieces: NVLink
+                    // then carries full-size write packets instead of 32 scattered 16-byte ones.
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(rs.slab[owner]) +
+                                         (static_cast<long long>(rs.rank) * rs.rows_per_rank + lmt * BM + q * 32) *
+                                             rs.slab_ld;
+                    uint8_t* wst = smem + L::TILES_BYTES + 1024 + q * 8192;
+#pragma unroll 1
+                    for (int half = 0; half < BN / 128; ++half) {
+#pragma unroll 1
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(taddr + (half * 4 + c4) * 32, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+                                o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                                o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                                o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                                const int phys = (c4 * 4 + i) ^ (lane & 15);
+                                *reinterpret_cast<uint4*>(wst + lane * 256 + phys * 16) = o;
+                            }
+                        }
+                        __syncwarp();
+                        const int k = lane & 15;
+                        const int col = nb * BN + half * 128 + k * 8;
+#pragma unroll 4
+                        for (int rr = 0; rr < 16; ++rr) {
+                            const int rw = rr * 2 + (lane >> 4);
+                            const uint4 v = *reinterpret_cast<const uint4*>(wst + rw * 256 + ((k ^ (rw & 15)) * 16));
+                            if (col < p.N) *reinterpret_cast<uint4*>(dst + rw * rs.slab_ld + col) = v;
+                        }
+                        __syncwarp();
+                    }
+                    tc_fence_before();
+                    __threadfence_system();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&tempty_bar[acc]);
+                        st_release_sys(&rs.flags[owner][((rs.rank * rs.tiles_per_rank + lmt) * p.tiles_n + nb) * 4 + q],
+                                       rs.seq);
+                    }
+                    continue;
+                }
+                // own rows: the peers' partial products must have arrived
+                int arrived = 1;
+                if (lane == 0) {
+                    for (int src = 0; src < rs.world && arrived; ++src)
+                        if (src != rs.rank)
+                            arrived = wait_flag_sys(
+                                &rs.flags[rs.rank][((src * rs.tiles_per_rank + lmt) * p.tiles_n + nb) * 4 + q], rs.seq,
+                                840 + src);
+                }
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                if (!arrived) { ok = false; break; }
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    const int col0 = nb * BN + c * 32;
+                    if (col0 < p.N) {
+                        for (int src = 0; src < rs.world; ++src) {
+                            if (src == rs.rank) continue;
+                            const __nv_bfloat16* part = reinterpret_cast<const __nv_bfloat16*>(rs.slab[rs.rank]) +
+                                (static_cast<long long>(src) * rs.rows_per_rank + lrow) * rs.slab_ld + col0;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                if (col0 + i < p.N) {
+                                    uint4 b = *reinterpret_cast<const uint4*>(part + i);
+                                    float2 f;
+                                    f = unpack_bf16x2(b.x);
+                                    r[i] = __float_as_uint(__uint_as_float(r[i]) + f.x);
+                                    r[i + 1] = __float_as_uint(__uint_as_float(r[i + 1]) + f.y);
+                                    f = unpack_bf16x2(b.y);
+                                    r[i + 2] = __float_as_uint(__uint_as_float(r[i + 2]) + f.x);
+                                    r[i + 3] = __float_as_uint(__uint_as_float(r[i + 3]) + f.y);
+                                    f = unpack_bf16x2(b.z);
+                                    r[i + 4] = __float_as_uint(__uint_as_float(r[i + 4]) + f.x);
+                                    r[i + 5] = __float_as_uint(__uint_as_float(r[i + 5]) + f.y);
+                                    f = unpack_bf16x2(b.w);
+                                    r[i + 6] = __float_as_uint(__uint_as_float(r[i + 6]) + f.x);
+                                    r[i + 7] = __float_as_uint(__uint_as_float(r[i + 7]) + f.y);
+                                }
+                            }
+                        }
+                        epilogue_store(r, lrow, col0, p, out_f32, accumulate, swiglu);
+                    }
+                    __syncwarp();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+                continue;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
@@ -424,15 +540,19 @@ static int num_sms() {
     return g_num_sms;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false, bool RS = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p, int max_ctas,
-                       cudaStream_t stream, const GatherArgs* gather = nullptr) {
+                       cudaStream_t stream, const GatherArgs* gather = nullptr,
+                       const CUtensorMap* tlocal = nullptr, const RsArgs* scatter = nullptr) {
     using L = SmemLayout<BN, STAGES>;
     static_assert(!GATHER || L::TILES_BYTES >= GATHER_SLOTS * GATHER_SEG_BYTES, "copy CTAs reuse the tile ring");
-    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8, GATHER>;
+    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8, GATHER, RS>;
+    // RS: + 4 x 8 KB behind the barriers, where the epilogue warps turn their tiles for coalesced peer stores
+    constexpr int SMEM = L::TOTAL + (RS ? 1024 + 4 * 8192 : 0);
+    static_assert(SMEM <= 232448, "dynamic shared memory of one CTA");
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return LME_ERR_LAUNCH;
         configured = true;
     }
@@ -441,19 +561,22 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p
     p.group_m = 8;
     int tiles = p.tiles_m * p.tiles_n;
     GatherArgs g;
+    RsArgs rs;
+    rs.enabled = 0;
+    if (RS) rs = *scatter;
     if (GATHER) {
         g = *gather;
         // every CTA of this grid must be resident at once (the multiplying CTAs wait for the copy CTAs)
         int gemm_ctas = max_ctas - g.n_copy;
         if (gemm_ctas < 1) return LME_ERR_SHAPE;
         if (tiles < gemm_ctas) gemm_ctas = tiles;
-        kern<<<gemm_ctas + g.n_copy, 192, L::TOTAL, stream>>>(ta, tb, p, g);
+        kern<<<gemm_ctas + g.n_copy, 192, SMEM, stream>>>(ta, tb, p, g, *tlocal, rs);
         return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
     }
     g.enabled = 0;
     g.n_copy = 0;
     int grid = tiles < max_ctas ? tiles : max_ctas;
-    kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, p, g);
+    kern<<<grid, 192, SMEM, stream>>>(ta, tb, p, g, ta, rs);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 
@@ -543,15 +666,16 @@ extern "C" int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void*
 //   ready     : local int32, world * ceil(shard_bytes / 32 KB) words, never reset (compared against seq)
 //   counters  : local uint32[2], zero before the first call
 //   seq       : 1, 2, 3, ... per call on this set of buffers (the same on every rank)
-extern "C" int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, long long ldb, void* C,
+extern "C" int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, int b_mn_major,
+                                         long long ldb, void* C,
                                          long long ldc, int M, int N, int K, int flags, const void* bias,
                                          const void* residual, long long ldr, void* preact, long long ldp,
                                          const void* local_src, void* const* stage, int* const* pads, int* ready,
                                          unsigned int* counters, long long shard_bytes, int rank, int world,
-                                         int seq, int n_copy, int max_ctas, void* stream) {
+                                         int seq, int n_copy, int seg_shift, int max_ctas, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0) return LME_OK;
     if ((N % 8) || (lda % 8) || (ldb % 8) || (ldc % 4)) return LME_ERR_SHAPE;
-    if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world || seq < 1 || n_copy < 1)
+    if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world || seq < 1 || n_copy < 0)
         return LME_ERR_SHAPE;
     if (lda != K || shard_bytes * world != static_cast<long long>(M) * K * 2 || (shard_bytes % 16))
         return LME_ERR_SHAPE;   // the gathered operand is dense and splits evenly
@@ -562,7 +686,7 @@ extern "C" int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const 
     CUtensorMap ta, tb;
     int rc = make_tmap_bf16_2d(&ta, A_gathered, K, M, lda, 64, BM);
     if (rc) return rc;
-    rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
+    rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK) : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
     if (rc) return rc;
     GemmArgs p;
     p.M = M; p.N = N; p.K = K;
@@ -591,10 +715,111 @@ extern "C" int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const 
     g.dst = static_cast<uint8_t*>(A_gathered);
     g.ready = ready;
     g.counters = counters;
+    g.local_rows = M / world;
+    g.local_row0 = rank * g.local_rows;
+    g.seg_shift = n_copy > 0 ? GATHER_SEG_SHIFT : seg_shift;
+    if (g.seg_shift < 12 || g.seg_shift > 30) return LME_ERR_SHAPE;
+    g.flag_every = 4;
+    if (const char* e = getenv("LME_GATHER_FLAG_EVERY")) g.flag_every = atoi(e) > 0 ? atoi(e) : 4;
+    CUtensorMap tl;
+    rc = make_tmap_bf16_2d(&tl, local_src, K, g.local_rows, lda, 64, BM);
+    if (rc) return rc;
     if (max_ctas <= 0) max_ctas = num_sms();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (BN == 128) return launch_gemm<128, 6, false, false, false, true>(ta, tb, p, max_ctas, st, &g);
-    return launch_gemm<256, 4, false, false, false, true>(ta, tb, p, max_ctas, st, &g);
+    if (b_mn_major) {
+        if (BN == 128) return launch_gemm<128, 6, false, true, false, true>(ta, tb, p, max_ctas, st, &g, &tl);
+        return launch_gemm<256, 4, false, true, false, true>(ta, tb, p, max_ctas, st, &g, &tl);
+    }
+    if (BN == 128) return launch_gemm<128, 6, false, false, false, true>(ta, tb, p, max_ctas, st, &g, &tl);
+    return launch_gemm<256, 4, false, false, false, true>(ta, tb, p, max_ctas, st, &g, &tl);
+}
+
+// out[M / world, N] = sum over ranks of (A[M, K] * B[N, K]^T)[rows of this rank] (+ bias) (+ residual): the
+// reduce-scatter runs inside the GEMM epilogue (RsArgs in kernels/gather.cuh).  slabs[r] / flags[r]: receive slab
+// (already offset to the slot of this call) and arrival flags of rank r in symmetric memory.  M / world must be a
+// multiple of 128.  seq = 1, 2, ... per call on one set of buffers.
+extern "C" int lme_gemm_bf16_reduce_scatter(const void* A, long long lda, const void* B, int b_mn_major,
+                                            long long ldb, void* out,
+                                            long long ldo, int M, int N, int K, const void* bias,
+                                            const void* residual, long long ldr, void* const* slabs,
+                                            int* const* flags, int rank, int world, int seq, int max_ctas,
+                                            void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return LME_OK;
+    if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 4)) return LME_ERR_SHAPE;
+    if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world || seq < 1) return LME_ERR_SHAPE;
+    if (M % (world * BM)) return LME_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16_2d(&ta, A, K, M, lda, 64, BM);
+    if (rc) return rc;
+    rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK) : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
+    if (rc) return rc;
+    GemmArgs p;
+    p.M = M; p.N = N; p.K = K;
+    p.C = out; p.ldc = ldo;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+    p.preact = nullptr; p.ldp = 0;
+    p.flags = 0;
+    p.a_fmt = p.b_fmt = 0;
+    p.scale_a = p.scale_b = nullptr;
+    RsArgs rs;
+    rs.enabled = 1;
+    rs.rank = rank; rs.world = world; rs.seq = seq;
+    rs.rows_per_rank = M / world;
+    rs.tiles_per_rank = rs.rows_per_rank / BM;
+    rs.rotate = ((rank + 1) % world) * rs.tiles_per_rank;
+    rs.slab_ld = N;
+    for (int r = 0; r < GATHER_MAX_RANKS; ++r) {
+        rs.slab[r] = r < world ? static_cast<uint8_t*>(slabs[r]) : nullptr;
+        rs.flags[r] = r < world ? flags[r] : nullptr;
+    }
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (b_mn_major) {
+        if (BN == 128)
+            return launch_gemm<128, 6, false, true, false, false, true>(ta, tb, p, max_ctas, st, nullptr, nullptr,
+                                                                         &rs);
+        return launch_gemm<256, 4, false, true, false, false, true>(ta, tb, p, max_ctas, st, nullptr, nullptr, &rs);
+    }
+    if (BN == 128)
+        return launch_gemm<128, 6, false, false, false, false, true>(ta, tb, p, max_ctas, st, nullptr, nullptr, &rs);
+    return launch_gemm<256, 4, false, false, false, false, true>(ta, tb, p, max_ctas, st, nullptr, nullptr, &rs);
+}
+
+// Stream-side pieces of the copy-engine-fed all-gather (n_copy == 0 above): announce the staging slot to the peers;
+// hold a stream until a peer has announced; write a readiness word from the stream itself (a stream memory
+// operation, no kernel, so it progresses while persistent GEMM CTAs occupy every SM).
+extern "C" int lme_gather_signal(int* const* pads, int rank, int world, int seq, void* stream) {
+    GatherArgs g;
+    g.rank = rank; g.world = world; g.seq = seq;
+    for (int r = 0; r < GATHER_MAX_RANKS; ++r) g.pad[r] = r < world ? pads[r] : nullptr;
+    gather_signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(g);
+    return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+}
+extern "C" int lme_gather_wait_peer(const int* pad, int src, int seq, void* stream) {
+    gather_wait_peer_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(pad + PAD_SIG + src, seq, 860 + src);
+    return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+}
+typedef CUresult (*WriteValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+extern "C" int lme_stream_write_words(int* words, int count, int value, void* stream) {
+    static WriteValue32Fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<WriteValue32Fn>(f);
+    });
+    if (!fn) return LME_ERR_DRIVER;
+    for (int i = 0; i < count; ++i)
+        if (fn(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(words + i), static_cast<cuuint32_t>(value),
+               0) != CUDA_SUCCESS)
+            return LME_ERR_LAUNCH;
+    return LME_OK;
 }
 
 extern "C" int lme_read_status(unsigned int* out8, int clear) {

@@ -42,11 +42,30 @@ int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void* B, int b_f
 // asynchronous copies over NVLink while the other CTAs multiply the rows that have arrived.  pads[r]: 16-word int32
 // signal pad of rank r in symmetric memory; ready / counters: local scratch words (see kernels/gather.cuh);
 // seq = 1, 2, ... per call on one set of buffers, the same on every rank.  All waits are bounded.
-int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, long long ldb, void* C, long long ldc,
+int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, int b_mn_major, long long ldb, void* C,
+                              long long ldc,
                               int M, int N, int K, int flags, const void* bias, const void* residual, long long ldr,
                               void* preact, long long ldp, const void* local_src, void* const* stage,
                               int* const* pads, int* ready, unsigned int* counters, long long shard_bytes, int rank,
-                              int world, int seq, int n_copy, int max_ctas, void* stream);
+                              int world, int seq, int n_copy, int seg_shift, int max_ctas, void* stream);
+
+// With n_copy == 0 the peers' rows are delivered by copy engines instead (device-to-device copies on a side stream,
+// each followed by lme_stream_write_words on the `ready` word of that chunk of 1 << seg_shift bytes); the GEMM only
+// waits for the words.  lme_gather_signal announces this rank's staging slot; lme_gather_wait_peer holds a stream
+// (bounded) until a peer's announcement for `seq` is in this rank's pad.
+int lme_gather_signal(int* const* pads, int rank, int world, int seq, void* stream);
+int lme_gather_wait_peer(const int* pad, int src, int seq, void* stream);
+int lme_stream_write_words(int* words, int count, int value, void* stream);
+
+// Reduce-scatter fused into the GEMM epilogue: out[M / world, N] = sum over ranks of (A * B^T)[rows of this rank]
+// (+ bias) (+ residual).  Tiles of a peer's rows are stored into that peer's receive slab over NVLink with an
+// arrival flag; own rows are multiplied last and their epilogue adds what the peers delivered.  slabs[r] / flags[r]:
+// slab (slot of this call) and flag words of rank r in symmetric memory; M / world % 128 == 0; seq = 1, 2, ...
+int lme_gemm_bf16_reduce_scatter(const void* A, long long lda, const void* B, int b_mn_major, long long ldb, void* out,
+                                 long long ldo,
+                                 int M, int N, int K, const void* bias, const void* residual, long long ldr,
+                                 void* const* slabs, int* const* flags, int rank, int world, int seq, int max_ctas,
+                                 void* stream);
 
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);

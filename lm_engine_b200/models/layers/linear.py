@@ -22,6 +22,20 @@ from ...parameter import (
 from ...utils import divide_if_divisible
 
 
+def _fused_tp(x: torch.Tensor, padding_free: bool, world: int, gathered: bool) -> bool:
+    """Fused collective kernels apply under ``use_async_tensor_parallel`` to activations whose sequence-parallel
+    shards concatenate along rows: packed ``[T, H]`` or batch 1 (a ``[B > 1, S, H]`` batch would interleave the
+    ranks' rows per batch entry and takes the two-step path)."""
+    if not ProcessGroupManager.use_async_tensor_parallel():
+        return False
+    if not (x.dim() == 2 or padding_free or x.size(0) == 1):
+        return False
+    from ...parallel.symm import fused_tp_eligible
+
+    rows = x.numel() // x.size(-1)
+    return fused_tp_eligible(x, rows // world if gathered else rows, world)
+
+
 class ParameterizedLinear(nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = True, std: float | None = None,
                  device=None, dtype=None) -> None:
@@ -84,6 +98,16 @@ class ColumnParallelLinear(ParameterizedLinear):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         if self.tp_world_size > 1:
+            if self.sequence_parallel and residual is None and _fused_tp(x, self.use_padding_free_transformer,
+                                                                         self.tp_world_size, gathered=False):
+                # all-gather fused into the GEMM (copy CTAs pull the peers' rows over NVLink while the others multiply)
+                from ...parallel import symm
+
+                shape = x.shape
+                y = symm.all_gather_linear(x.reshape(-1, shape[-1]), self.weight, self.bias,
+                                           ProcessGroupManager.get_tensor_parallel_group())
+                lead = (shape[0] * self.tp_world_size,) if x.dim() == 2 else (shape[0], shape[1] * self.tp_world_size)
+                return y.view(*lead, self.weight.size(0))
             if self.sequence_parallel:
                 x = tp_comm.gather_from_sequence_parallel(x, tp_comm.seq_dim(x, self.use_padding_free_transformer))
             else:
@@ -116,6 +140,17 @@ class RowParallelLinear(ParameterizedLinear):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         if self.tp_world_size == 1:
             return ops.linear(x, self.weight, self.bias, residual)
+        if self.sequence_parallel and _fused_tp(x, self.use_padding_free_transformer, self.tp_world_size,
+                                                gathered=True):
+            # reduce-scatter (+ bias + residual) fused into the GEMM epilogue over NVLink peer stores
+            from ...parallel import symm
+
+            shape = x.shape
+            r2 = residual.reshape(-1, self.weight.size(0)) if residual is not None else None
+            y = symm.linear_reduce_scatter(x.reshape(-1, shape[-1]), self.weight, self.bias, r2,
+                                           ProcessGroupManager.get_tensor_parallel_group())
+            lead = (shape[0] // self.tp_world_size,) if x.dim() == 2 else (shape[0], shape[1] // self.tp_world_size)
+            return y.view(*lead, self.weight.size(0))
         y = ops.linear(x, self.weight, None, None)
         if self.sequence_parallel:
             y = tp_comm.scatter_to_sequence_parallel(y, tp_comm.seq_dim(y, self.use_padding_free_transformer))

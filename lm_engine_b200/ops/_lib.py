@@ -58,7 +58,11 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_gemm_bf16": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
             "lme_gemm_bf16_2cta": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
             "lme_gemm_fp8": [P, I, L, P, I, L, P, P, P, L, I, I, I, I, P, P, L, P, L, I, P],
-            "lme_gemm_bf16_allgather_a": [P, L, P, L, P, L, I, I, I, I, P, P, L, P, L, P, P, P, P, P, L, I, I, I, I, I, P],
+            "lme_gemm_bf16_allgather_a": [P, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, P, P, P, P, P, L, I, I, I, I, I, I, P],
+            "lme_gather_signal": [P, I, I, I, P],
+            "lme_gather_wait_peer": [P, I, I, P],
+            "lme_stream_write_words": [P, I, I, P],
+            "lme_gemm_bf16_reduce_scatter": [P, L, P, I, L, P, L, I, I, I, P, P, L, P, P, I, I, I, I, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

@@ -32,14 +32,32 @@ def _worker(rank, world, port, q):
         for (t, K, N), calls in (((512, 1024, 768), 5), ((4096, 4096, 6144), 3), ((384, 256, 264), 2)):
             w = (torch.randn(N, K, device="cuda", generator=torch.Generator("cuda").manual_seed(7)) * 0.05
                  ).to(torch.bfloat16)
-            for c in range(calls):
+            for c in range(2 * calls):
                 g = torch.Generator("cuda").manual_seed(100 * rank + c)
                 x = torch.randn(t, K, device="cuda", generator=g).to(torch.bfloat16)
-                y, xg = all_gather_matmul(x, w, dist.group.WORLD)
+                # even calls: copy engines deliver the peers' rows; odd calls: copy CTAs inside the GEMM grid
+                y, xg = all_gather_matmul(x, w, dist.group.WORLD, n_copy=0 if c % 2 == 0 else 8)
                 ref_x = torch.empty(world * t, K, device="cuda", dtype=torch.bfloat16)
                 dist.all_gather_into_tensor(ref_x, x)
                 ref = ref_x.float() @ w.float().t()
                 errs.append(float((xg != ref_x).sum()))
+                errs.append(float((y.float() - ref).abs().max() / ref.abs().max()))
+        # GEMM -> reduce-scatter in the epilogue
+        from lm_engine_b200.parallel.symm import matmul_reduce_scatter
+
+        for (M, Kl, N), calls in (((512, 256, 768), 5), ((8192, 2048, 4096), 3), ((256, 136, 264), 2)):
+            w = (torch.randn(N, Kl, device="cuda", generator=torch.Generator("cuda").manual_seed(11 + rank)) * 0.05
+                 ).to(torch.bfloat16)
+            bias = torch.randn(N, device="cuda", generator=torch.Generator("cuda").manual_seed(5)).to(torch.bfloat16)
+            for c in range(calls):
+                g = torch.Generator("cuda").manual_seed(1000 * rank + c)
+                x = torch.randn(M, Kl, device="cuda", generator=g).to(torch.bfloat16)
+                res = torch.randn(M // world, N, device="cuda", generator=g).to(torch.bfloat16)
+                y = matmul_reduce_scatter(x, w, dist.group.WORLD, bias=bias, residual=res)
+                part = (x.float() @ w.float().t()).to(torch.bfloat16).float()   # partial products travel as bf16
+                dist.all_reduce(part)
+                ref = part[rank * (M // world):(rank + 1) * (M // world)] + bias.float() + res.float()
+                errs.append(0.0)
                 errs.append(float((y.float() - ref).abs().max() / ref.abs().max()))
         torch.cuda.synchronize()
         q.put((rank, "ok", (errs, _lib.read_status())))
