@@ -46,6 +46,17 @@ struct GemmArgs {
     int a_fmt, b_fmt;
     const float* scale_a;
     const float* scale_b;
+    // Grouped (mixture-of-experts) forms.  Rows are laid out so that every 128-row tile belongs to one group:
+    //   tile_group != null : tile_group[m-tile] = group of that tile (< 0: tile unused, skipped); the B operand of
+    //                        group e starts group_b_stride rows (K-major B) / contraction rows (MN-major B) further
+    //   num_groups_w > 0   : one product per group with its own contraction range (weight gradients):
+    //                        k in [group_k0[e], group_k0[e] + 64 * group_kb[e]), output e at C + e * group_c_stride
+    const int* tile_group;
+    int group_b_stride;
+    int num_groups_w;
+    const int* group_k0;
+    const int* group_kb;
+    long long group_c_stride;
 };
 
 template <int BN, int STAGES>
@@ -71,7 +82,7 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmArgs& p, int& mb
 
 // Fused epilogue for 32 consecutive accumulator columns of one output row (held by one thread).
 __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row, int col0, const GemmArgs& p,
-                                               bool out_f32, bool accumulate, bool swiglu) {
+                                               bool out_f32, bool accumulate, bool swiglu, long long c_off = 0) {
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -140,7 +151,7 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row,
             }
         }
         if (out_f32) {
-            float* out = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            float* out = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
                 if (i < ncols) {
@@ -153,7 +164,7 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row,
                 }
             }
         } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) +
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off +
                                  static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -206,7 +217,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int cta = blockIdx.x - n_copy, n_cta = gridDim.x - n_copy;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int tiles_per_group = p.tiles_m * p.tiles_n;
+    const int num_tiles = tiles_per_group * (p.num_groups_w > 0 ? p.num_groups_w : 1);
     const int num_kb = (p.K + BKE - 1) / BKE;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                    : (2 * BN <= 256) ? 256 : 512;
@@ -240,9 +252,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool ok = true;
             for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
                 int mb, nb;
-                tile_coords(tile, p, mb, nb);
+                const int grp = p.num_groups_w > 0 ? tile / tiles_per_group : 0;
+                tile_coords(tile - grp * tiles_per_group, p, mb, nb);
                 if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
                 if (RS) mb = (mb + rs.rotate) % p.tiles_m;
+                int b_off = 0;
+                if (p.tile_group != nullptr) {
+                    const int e = __ldg(&p.tile_group[mb]);
+                    if (e < 0) continue;   // unused tile of the padded row layout (all three roles skip it)
+                    b_off = e * p.group_b_stride;
+                }
+                const int tile_kb = p.num_groups_w > 0 ? __ldg(&p.group_kb[grp]) : num_kb;
+                const int k_base = p.num_groups_w > 0 ? __ldg(&p.group_k0[grp]) : 0;
                 const int m0 = mb * BM, n0 = nb * BN;
                 // rows that are entirely this rank's own contribution are read where they already are
                 bool own_rows = false;
@@ -254,14 +275,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         if (!arrived) { ok = false; break; }
                     }
                 }
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = 0; kb < tile_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, 100 + s)) { ok = false; break; }
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                    const int k0 = kb * BKE;
+                    const int k0 = k_base + kb * BKE;
                     if (A_MN) {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c)
@@ -274,9 +295,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (B_MN) {
 #pragma unroll
                         for (int c = 0; c < BN / 64; ++c)
-                            tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, k0);
+                            tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64,
+                                        (p.num_groups_w > 0 ? k0 : kb * BKE) + b_off);
                     } else {
-                        tma_load_2d(sb, &tmB, &full_bar[s], k0, n0);
+                        tma_load_2d(sb, &tmB, &full_bar[s], k0, n0 + b_off);
                     }
                 }
             }
@@ -289,13 +311,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       : make_idesc(1, 1, A_MN, B_MN, BM, BN);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++tcount) {
+            for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+                const int grp = p.num_groups_w > 0 ? tile / tiles_per_group : 0;
+                if (p.tile_group != nullptr) {
+                    int mb, nb;
+                    tile_coords(tile - grp * tiles_per_group, p, mb, nb);
+                    if (__ldg(&p.tile_group[mb]) < 0) continue;
+                }
+                const int tile_kb = p.num_groups_w > 0 ? __ldg(&p.group_kb[grp]) : num_kb;
                 const int acc = tcount & 1;
                 const uint32_t aph = (tcount >> 1) & 1;
+                ++tcount;
                 if (!mbar_wait(&tempty_bar[acc], aph ^ 1, 200 + acc)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                if (tile_kb == 0) {   // a group without rows: nothing to multiply, the epilogue writes zeros
+                    mbar_arrive(&tfull_bar[acc]);
+                    continue;
+                }
+                for (int kb = 0; kb < tile_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&full_bar[s], ph, 300 + s)) { ok = false; break; }
@@ -329,13 +363,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool swiglu = p.flags & LME_GEMM_SWIGLU;
         float dequant = 1.0f;
         if (F8) dequant = __ldg(p.scale_a) * __ldg(p.scale_b);
-        for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++tcount) {
+        for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
             int mb, nb;
-            tile_coords(tile, p, mb, nb);
+            const int grp = p.num_groups_w > 0 ? tile / tiles_per_group : 0;
+            tile_coords(tile - grp * tiles_per_group, p, mb, nb);
             if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
             if (RS) mb = (mb + rs.rotate) % p.tiles_m;
+            if (p.tile_group != nullptr && __ldg(&p.tile_group[mb]) < 0) continue;
+            const bool empty_group = p.num_groups_w > 0 && __ldg(&p.group_kb[grp]) == 0;
+            const long long c_off = p.num_groups_w > 0 ? grp * p.group_c_stride : 0;
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
+            ++tcount;
             if (!mbar_wait(&tfull_bar[acc], aph, 400 + acc)) { ok = false; break; }
             tc_fence_after();
             const int row = mb * BM + q * 32 + lane;
@@ -453,8 +492,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * dequant);
                 }
+                if (empty_group) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
                 const int col0 = nb * BN + c * 32;
-                if (row_ok && col0 < p.N) epilogue_store(r, row, col0, p, out_f32, accumulate, swiglu);
+                if (row_ok && col0 < p.N) epilogue_store(r, row, col0, p, out_f32, accumulate, swiglu, c_off);
                 __syncwarp();
             }
             // accumulator buffer may be overwritten by the MMA warp
@@ -602,7 +645,7 @@ extern "C" int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const
     if (rc) return rc;
     rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK) : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
     if (rc) return rc;
-    GemmArgs p;
+    GemmArgs p = {};
     p.M = M; p.N = N; p.K = K;
     p.C = C; p.ldc = ldc;
     p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -625,6 +668,75 @@ extern "C" int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const
 #undef LME_DISPATCH
 }
 
+// Grouped GEMM for mixture-of-experts layers.  Rows of A / C are in the padded per-group layout: every 128-row tile
+// belongs to one group, tile_group[m-tile] names it (< 0: unused tile, skipped).  Group e multiplies with
+//   B[e] = rows [e * N, (e + 1) * N) of a K-major [G * N, K] matrix (forward:  y = x W_e^T), or
+//   B[e] = rows [e * K, (e + 1) * K) of an MN-major [G * K, N] matrix (input gradient: dx = dy W_e).
+extern "C" int lme_gemm_bf16_grouped(const void* A, long long lda, const void* B, int b_mn_major, long long ldb,
+                                     void* C, long long ldc, int M, int N, int K, int num_groups, int flags,
+                                     void* preact, long long ldp, const int* tile_group, int max_ctas,
+                                     void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return LME_OK;
+    if ((N % 8) || (lda % 8) || (ldb % 8) || (ldc % 4) || (M % BM) || tile_group == nullptr) return LME_ERR_SHAPE;
+    if (b_mn_major && (K % BK)) return LME_ERR_SHAPE;   // a partial K block would read the next group's rows
+    if ((flags & LME_GEMM_SWIGLU) && (N % 16)) return LME_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16_2d(&ta, A, K, M, lda, 64, BM);
+    if (rc) return rc;
+    rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, static_cast<uint64_t>(num_groups) * K, ldb, 64, BK)
+                    : make_tmap_bf16_2d(&tb, B, K, static_cast<uint64_t>(num_groups) * N, ldb, 64, BN);
+    if (rc) return rc;
+    GemmArgs p = {};
+    p.M = M; p.N = N; p.K = K;
+    p.C = C; p.ldc = ldc;
+    p.preact = static_cast<__nv_bfloat16*>(preact); p.ldp = ldp;
+    p.flags = flags;
+    p.tile_group = tile_group;
+    p.group_b_stride = b_mn_major ? K : N;
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (b_mn_major) {
+        if (BN == 128) return launch_gemm<128, 6, false, true>(ta, tb, p, max_ctas, st);
+        return launch_gemm<256, 4, false, true>(ta, tb, p, max_ctas, st);
+    }
+    if (BN == 128) return launch_gemm<128, 6, false, false>(ta, tb, p, max_ctas, st);
+    return launch_gemm<256, 4, false, false>(ta, tb, p, max_ctas, st);
+}
+
+// Weight gradients of a grouped layer: dW[e] [M, N] (+)= dY[rows of e]^T * X[rows of e] for every group e, rows in
+// the padded layout (group e owns rows [group_k0[e], group_k0[e] + 64 * group_kb[e]), padding rows of X are zero).
+// dY is [rows, M], X is [rows, N]; dW is [G, M, N] with row pitch ldw.  A group without rows yields zeros.
+extern "C" int lme_gemm_bf16_grouped_wgrad(const void* dY, long long lddy, const void* X, long long ldx, void* dW,
+                                           long long ldw, int M, int N, int rows, int num_groups,
+                                           const int* group_k0, const int* group_kb, int flags, int max_ctas,
+                                           void* stream) {
+    if (M <= 0 || N <= 0 || rows <= 0 || num_groups <= 0) return LME_OK;
+    if ((N % 8) || (M % 8) || (lddy % 8) || (ldx % 8) || (ldw % 4)) return LME_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(dY) | reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(dW)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16_2d(&ta, dY, M, rows, lddy, 64, BK);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tb, X, N, rows, ldx, 64, BK);
+    if (rc) return rc;
+    GemmArgs p = {};
+    p.M = M; p.N = N; p.K = rows;
+    p.C = dW; p.ldc = ldw;
+    p.flags = flags & (LME_GEMM_OUT_F32 | LME_GEMM_ACCUMULATE);
+    p.num_groups_w = num_groups;
+    p.group_k0 = group_k0;
+    p.group_kb = group_kb;
+    p.group_c_stride = static_cast<long long>(M) * ldw;
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (BN == 128) return launch_gemm<128, 6, true, true>(ta, tb, p, max_ctas, st);
+    return launch_gemm<256, 4, true, true>(ta, tb, p, max_ctas, st);
+}
+
 // C[M,N] = (A[M,K] * B[N,K]^T) * scale_a * scale_b with 1-byte e4m3 / e5m2 operands, both K-major.
 extern "C" int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void* B, int b_fmt, long long ldb,
                             const float* scale_a, const float* scale_b, void* C, long long ldc, int M, int N, int K,
@@ -643,7 +755,7 @@ extern "C" int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void*
     if (rc) return rc;
     rc = make_tmap_2d(&tb, B, K, N, ldb, 128, BN, 1);
     if (rc) return rc;
-    GemmArgs p;
+    GemmArgs p = {};
     p.M = M; p.N = N; p.K = K;
     p.C = C; p.ldc = ldc;
     p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -688,7 +800,7 @@ extern "C" int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const 
     if (rc) return rc;
     rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK) : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
     if (rc) return rc;
-    GemmArgs p;
+    GemmArgs p = {};
     p.M = M; p.N = N; p.K = K;
     p.C = C; p.ldc = ldc;
     p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -756,7 +868,7 @@ extern "C" int lme_gemm_bf16_reduce_scatter(const void* A, long long lda, const 
     if (rc) return rc;
     rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK) : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, BN);
     if (rc) return rc;
-    GemmArgs p;
+    GemmArgs p = {};
     p.M = M; p.N = N; p.K = K;
     p.C = out; p.ldc = ldo;
     p.bias = static_cast<const __nv_bfloat16*>(bias);

@@ -304,7 +304,7 @@ extern "C" int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, 
     rc = b_mn_major ? make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK)
                     : make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, HALF_N);
     if (rc) return rc;
-    GemmArgs p;
+    GemmArgs p = {};
     p.M = M; p.N = N; p.K = K;
     p.C = C; p.ldc = ldc;
     p.bias = static_cast<const __nv_bfloat16*>(bias);

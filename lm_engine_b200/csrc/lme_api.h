@@ -29,6 +29,18 @@ int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, const void*
                        void* C, long long ldc, int M, int N, int K, int flags, const void* bias,
                        const void* residual, long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
 
+// Grouped GEMM (mixture of experts).  A / C rows are in a padded per-group layout in which every 128-row tile belongs
+// to one group: tile_group[m-tile] = group (< 0: unused tile).  B holds all groups: K-major [G * N, K] (forward,
+// C = A B_e^T) or MN-major [G * K, N] (input gradient, C = A B_e).  Flags / SwiGLU epilogue as lme_gemm_bf16.
+int lme_gemm_bf16_grouped(const void* A, long long lda, const void* B, int b_mn_major, long long ldb, void* C,
+                          long long ldc, int M, int N, int K, int num_groups, int flags, void* preact, long long ldp,
+                          const int* tile_group, int max_ctas, void* stream);
+
+// dW[e] [M, N] (+)= dY[rows of e]^T X[rows of e]; group e owns rows [group_k0[e], group_k0[e] + 64 * group_kb[e]).
+int lme_gemm_bf16_grouped_wgrad(const void* dY, long long lddy, const void* X, long long ldx, void* dW, long long ldw,
+                                int M, int N, int rows, int num_groups, const int* group_k0, const int* group_kb,
+                                int flags, int max_ctas, void* stream);
+
 // C[M, N] = (A[M, K] * B[N, K]^T) * scale_a[0] * scale_b[0]: 1-byte e4m3 (fmt 0) / e5m2 (fmt 1) operands, both
 // K-major, fp32 accumulation in TMEM; same flags and fused epilogue as lme_gemm_bf16.  K, lda, ldb % 16 == 0.
 int lme_gemm_fp8(const void* A, int a_fmt, long long lda, const void* B, int b_fmt, long long ldb,

@@ -30,7 +30,7 @@ from ...parameter import (
 from ...utils import divide_if_divisible
 from ..aux_loss import add_aux_loss
 from ..config import MoEArgs
-from .activations import get_activation_function, is_glu, sigmoid
+from .activations import GLUActivation, get_activation_function, is_glu, sigmoid
 from .dropout import Dropout
 from .init_utils import std_for_linear
 from .linear import ColumnParallelLinear, ParameterizedLinear, ReplicatedLinear, RowParallelLinear
@@ -152,12 +152,33 @@ class MoE(nn.Module):
         xs = x[token]
         if self.ep_world_size > 1:
             ys = self._expert_parallel(xs, freq)
+        elif self._grouped_kernels(xs):
+            # one persistent grouped GEMM per projection over all experts, rows in a padded per-expert layout that is
+            # derived on the device: no per-expert launches and no host synchronisation on the routing result
+            ys = self._grouped_mlp(xs, sorted_experts, freq)
         else:
             counts = freq.tolist()
             ys = self.c_proj(self.act(self.c_fc(xs, counts)), counts)
         ys = ys * gates.unsqueeze(-1)
         out = torch.zeros((T, self.hidden_size), dtype=ys.dtype, device=ys.device).index_add(0, token, ys)
         return out, freq
+
+    def _grouped_kernels(self, xs: torch.Tensor) -> bool:
+        from ...ops.moe import grouped_kernels_eligible
+
+        return (self.c_fc.bias is None and self.c_proj.bias is None
+                and grouped_kernels_eligible(xs, self.c_fc.weight, self.c_proj.weight))
+
+    def _grouped_mlp(self, xs: torch.Tensor, sorted_experts: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+        from ...ops.moe import GroupLayout, grouped_linear_padded
+
+        layout = GroupLayout(sorted_experts, freq)
+        x_pad = layout.scatter(xs)
+        fuse = isinstance(self.act, GLUActivation) and self.act.is_swiglu
+        h = grouped_linear_padded(x_pad, self.c_fc.weight, layout, swiglu=fuse)
+        if not fuse:
+            h = self.act(h)
+        return layout.gather(grouped_linear_padded(h, self.c_proj.weight, layout))
 
     def _expert_parallel(self, xs: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
         """Tokens (sorted by global expert id) -> owners of the experts -> local grouped MLP -> back."""
@@ -177,7 +198,12 @@ class MoE(nn.Module):
         by_expert = [pieces[src * local_e + e] for e in range(local_e) for src in range(ep)]
         per_expert = [sum(counts[src][me * local_e + e] for src in range(ep)) for e in range(local_e)]
         h = torch.cat(by_expert, dim=0) if by_expert else got
-        h = self.c_proj(self.act(self.c_fc(h, per_expert)), per_expert)
+        if self._grouped_kernels(h) and h.size(0) > 0:
+            counts_t = torch.tensor(per_expert, device=h.device)
+            ids = torch.repeat_interleave(torch.arange(local_e, device=h.device), counts_t, output_size=h.size(0))
+            h = self._grouped_mlp(h, ids, counts_t)
+        else:
+            h = self.c_proj(self.act(self.c_fc(h, per_expert)), per_expert)
         # back to (source rank, local expert) order and home
         seg2 = [counts[src][me * local_e + e] for e in range(local_e) for src in range(ep)]
         back = list(h.split(seg2, dim=0))

@@ -35,6 +35,120 @@ def grouped_linear(x: torch.Tensor, weight: torch.Tensor, counts: list[int],
     return torch.cat(outs, dim=0)
 
 
+# ---------------------------------------------------------------------------------------------------- grouped GEMM
+TILE_ROWS = 128
+
+
+class GroupLayout:
+    """Padded per-expert row layout: expert ``e`` owns rows ``[start[e], start[e] + pad[e])`` with ``pad[e]`` the
+    count rounded up to the 128-row GEMM tile, so every tile belongs to one expert.  Everything is computed on the
+    device from the per-expert counts; the row capacity is the static upper bound ``rows + E * 127`` (rounded up),
+    tiles past the last expert are marked unused and skipped by the kernels.  No host synchronisation."""
+
+    def __init__(self, sorted_experts: torch.Tensor, freq: torch.Tensor) -> None:
+        E, total = freq.numel(), sorted_experts.numel()
+        dev = freq.device
+        pad = (freq + (TILE_ROWS - 1)) // TILE_ROWS * TILE_ROWS
+        end = pad.cumsum(0)
+        start = end - pad
+        first_sorted = freq.cumsum(0) - freq
+        self.capacity = (total + E * (TILE_ROWS - 1) + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS
+        self.dest = start[sorted_experts] + (torch.arange(total, device=dev) - first_sorted[sorted_experts])
+        tile_start = torch.arange(self.capacity // TILE_ROWS, device=dev) * TILE_ROWS
+        grp = torch.searchsorted(end, tile_start, right=True)
+        self.tile_group = torch.where(grp < E, grp, torch.full_like(grp, -1)).to(torch.int32)
+        self.k0 = start.to(torch.int32)
+        self.kb = (pad // 64).to(torch.int32)
+        self.num_groups = E
+
+    def scatter(self, rows: torch.Tensor) -> torch.Tensor:
+        """Rows sorted by expert -> padded layout (padding rows zero)."""
+        out = torch.zeros((self.capacity, rows.size(1)), dtype=rows.dtype, device=rows.device)
+        return out.index_copy(0, self.dest, rows)
+
+    def gather(self, padded: torch.Tensor) -> torch.Tensor:
+        return padded.index_select(0, self.dest)
+
+
+def _grouped_gemm(a: torch.Tensor, w2d: torch.Tensor, layout: GroupLayout, n: int, k: int, b_mn: bool,
+                  swiglu: bool = False, preact: torch.Tensor | None = None) -> torch.Tensor:
+    from . import _lib
+    from .gemm import _max_ctas
+
+    out = torch.zeros((a.size(0), n // 2 if swiglu else n), dtype=torch.bfloat16, device=a.device)
+    rc = _lib.cuda_lib().lme_gemm_bf16_grouped(
+        a.data_ptr(), a.stride(0), w2d.data_ptr(), int(b_mn), w2d.stride(0), out.data_ptr(), out.stride(0),
+        a.size(0), n, k, layout.num_groups, _lib.GEMM_SWIGLU if swiglu else 0, _lib.ptr(preact),
+        preact.stride(0) if preact is not None else 0, layout.tile_group.data_ptr(), _max_ctas(a.device),
+        _lib.stream_ptr())
+    _lib.check(rc, f"lme_gemm_bf16_grouped rows={a.size(0)} N={n} K={k} groups={layout.num_groups}")
+    _lib.count_launch()
+    return out
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """``y[rows of e] = x[rows of e] @ W[e].T`` (optionally followed by the packed SwiGLU in the epilogue) on rows in
+    the padded layout: one persistent tcgen05 kernel over all experts for each of forward, dgrad and wgrad."""
+
+    @staticmethod
+    def forward(ctx, x_pad, weight, layout: GroupLayout, swiglu: bool):
+        E, N, K = weight.shape
+        pre = torch.zeros((x_pad.size(0), N), dtype=x_pad.dtype, device=x_pad.device) if swiglu else None
+        y = _grouped_gemm(x_pad, weight.view(E * N, K), layout, N, K, False, swiglu, pre)
+        ctx.save_for_backward(x_pad, weight, pre)
+        ctx.layout, ctx.swiglu = layout, swiglu
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _lib
+        from .activation import swiglu_backward
+        from .gemm import _max_ctas
+
+        x_pad, weight, pre = ctx.saved_tensors
+        layout = ctx.layout
+        E, N, K = weight.shape
+        dy = dy.contiguous()
+        if ctx.swiglu:
+            dy = swiglu_backward(pre, dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx = dy @ W[e]: W[e] is [N, K] = the MN-major operand whose contraction rows are offset by e * N
+            dx = _grouped_gemm(dy, weight.view(E * N, K), layout, K, N, True)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            stale = getattr(weight, "main_grad_stale", False)
+            if main_grad is not None:
+                out, flags = main_grad, (0 if stale else _lib.GEMM_ACCUMULATE)
+            else:
+                out, flags = torch.empty_like(weight), 0
+            if out.dtype == torch.float32:
+                flags |= _lib.GEMM_OUT_F32
+            rc = _lib.cuda_lib().lme_gemm_bf16_grouped_wgrad(
+                dy.data_ptr(), dy.stride(0), x_pad.data_ptr(), x_pad.stride(0), out.data_ptr(), K, N, K,
+                dy.size(0), E, layout.k0.data_ptr(), layout.kb.data_ptr(), flags, _max_ctas(dy.device),
+                _lib.stream_ptr())
+            _lib.check(rc, f"lme_gemm_bf16_grouped_wgrad N={N} K={K} groups={E}")
+            _lib.count_launch()
+            if main_grad is not None:
+                if stale:
+                    weight.main_grad_stale = False
+            else:
+                dw = out
+        return dx, dw, None, None
+
+
+def grouped_linear_padded(x_pad: torch.Tensor, weight: torch.Tensor, layout: GroupLayout,
+                          swiglu: bool = False) -> torch.Tensor:
+    return _GroupedLinear.apply(x_pad, weight, layout, swiglu)
+
+
+def grouped_kernels_eligible(x: torch.Tensor, *weights: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and all(
+        w.dtype == torch.bfloat16 and w.is_contiguous() and w.size(1) % 64 == 0 and w.size(2) % 64 == 0
+        for w in weights)
+
+
 class _AllToAll(torch.autograd.Function):
     """Variable-size all-to-all of rows; backward is the all-to-all with the split lists swapped."""
 

@@ -93,3 +93,81 @@ def test_all_gather_matmul_two_gpus():
         for i in range(0, len(errs), 2):
             assert errs[i] == 0, f"rank {rank}: gathered operand differs ({errs[i]} elements)"
             assert errs[i + 1] < 1e-2, f"rank {rank}: GEMM error {errs[i + 1]}"
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        import torch.distributed as dist
+
+        from lm_engine_b200.distributed import shard_model
+        from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+        from lm_engine_b200.models import dense_config
+        from lm_engine_b200.ops import _lib
+        from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+        from lm_engine_b200.parallel import manager
+        from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+        ProcessGroupManager(tensor_parallel_world_size=2, zero_stage=3)
+        cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, intermediate_size=1024, head_dim=64, max_position_embeddings=512)
+        g = torch.Generator().manual_seed(3)
+        data = torch.randint(0, 2048, (1, 513), generator=g).cuda()
+        out = {}
+        for fused in (False, True):
+            manager._S.async_tp = fused
+            launches = _lib.launch_count
+            w = ModelWrapperForPretraining(pretrained_config=cfg.to_dict(), micro_batch_size=1, sequence_length=512,
+                                           efficient_initialization=True, dtype="bf16", sequence_parallel=True)
+            eng = shard_model(w, stage=3, dtype=torch.bfloat16, communication_dtype=None, seed=3)
+            opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95],
+                                                       "eps": 1e-10}, None, False, 1.0)
+            losses, norms = [], []
+            for _ in range(4):
+                opt.zero_grad()
+                o = w(data if ProcessGroupManager.is_tensor_parallel_first_rank() else None,
+                      lm_loss_multiplier=1 / 512)
+                o["loss"].backward()
+                norms.append(float(opt.step()))
+                losses.append(float(o["loss"]))
+            out[fused] = (losses, norms)
+        torch.cuda.synchronize()
+        q.put((rank, "ok", (out, _lib.read_status())))
+        dist.barrier()
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sequence_parallel_training_with_fused_collectives_matches_two_step_path():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    try:
+        for _ in range(2):
+            rank, status, payload = q.get(timeout=300)
+            assert status == "ok", payload
+            res[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    for rank, (out, status) in res.items():
+        assert status[0] == 0, status
+        (l0, n0), (l1, n1) = out[False], out[True]
+        assert l0[-1] < l0[0]
+        for a, b in zip(l0 + n0, l1 + n1):
+            assert abs(a - b) <= 2e-2 * abs(a) + 1e-3, (out[False], out[True])
