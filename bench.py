@@ -31,7 +31,11 @@ MODELS = {
     "llama3-8b": (128256, 32, 4096, 32, 8, 128, 14336, 500000),
     "llama-1b": (32000, 16, 2048, 16, 8, 128, 5632, 10000),
     "tiny": (2048, 4, 256, 4, 2, 64, 1024, 10000),
+    # fine-grained mixture of experts (see MOE): dense dims as above, the MLP of every block is routed
+    "moe-64e": (32000, 16, 2048, 16, 4, 128, 1024, 10000),
 }
+# name: (experts, experts per token, shared expert intermediate size or None, router aux-loss coefficient)
+MOE = {"moe-64e": (64, 8, None, 0.01)}
 
 
 LAYERS_OVERRIDE: int | None = None   # --layers: same per-layer shapes with fewer layers (profiling captures only)
@@ -50,9 +54,18 @@ def model_config(name: str, seq: int) -> dict:
         "use_depth_scaled_init": False, "tie_word_embeddings": False,
         "sequence_mixer_blocks": [{"sequence_mixer_type": "softmax_attention", "num_attention_heads": nh,
                                    "num_key_value_heads": nkv, "head_dim": hd} for _ in range(L)],
-        "mlp_blocks": [{"mlp_type": "MLP", "intermediate_size": inter, "activation_function": "swiglu"}
-                       for _ in range(L)],
+        "mlp_blocks": [_mlp_block(name, inter) for _ in range(L)],
+        "router_aux_loss_coef": MOE[name][3] if name in MOE else 0.001,
     }
+
+
+def _mlp_block(name: str, inter: int) -> dict:
+    if name not in MOE:
+        return {"mlp_type": "MLP", "intermediate_size": inter, "activation_function": "swiglu"}
+    experts, topk, shared, _ = MOE[name]
+    return {"mlp_type": "MoE", "intermediate_size": inter, "activation_function": "swiglu", "num_experts": experts,
+            "num_experts_per_tok": topk, "shared_intermediate_size": shared, "add_bias": False,
+            "shared_expert_gating": False, "normalized_topk": True, "dropout": 0}
 
 
 def training_config(model: str, seq: int, mbs: int, steps: int, kernels: list[str], tokenizer: str | None) -> dict:

@@ -8,3 +8,4 @@ from .norm import rmsnorm, rmsnorm_reference
 from .optimizer import adamw_reference, adamw_step, clip_coef_, sumsq_
 from .rope import apply_rope_reference, qkv_split_rope, qkv_split_rope_reference
 from .attention import attention, attention_reference
+from .packing import compute_cu_seqlens_and_max_seqlen_from_attention_mask, pack_sequence, unpack_sequence
