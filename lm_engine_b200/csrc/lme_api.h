@@ -79,6 +79,15 @@ int lme_gemm_bf16_reduce_scatter(const void* A, long long lda, const void* B, in
                                  void* const* slabs, int* const* flags, int rank, int world, int seq, int max_ctas,
                                  void* stream);
 
+// Mixture-of-experts token movement on bf16 rows of H elements (H % 8 == 0); slot[t * K + k] = row of the padded
+// per-expert layout holding the k-th assignment of token t (< 0: none); w (optional) = bf16 [T, K] weights.
+//   scatter_rows : dst[slot[t,k]] = w[t,k] * src[t]      gather_reduce : dst[t] = sum_k w[t,k] * src[slot[t,k]]
+//   row_dots     : out[t,k] = <a[slot[t,k]], b[t]>
+int lme_moe_scatter_rows(const void* src, const int* slot, const void* w, void* dst, int T, int H, int K, void* stream);
+int lme_moe_gather_reduce(const void* src, const int* slot, const void* w, void* dst, int T, int H, int K,
+                          void* stream);
+int lme_moe_row_dots(const void* a, const int* slot, const void* b, void* out, int T, int H, int K, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

@@ -4,4 +4,5 @@
 #include "kernels/gemm2cta.cu"
 #include "kernels/elementwise.cu"
 #include "kernels/fp8.cu"
+#include "kernels/moe.cu"
 #include "kernels/noalloc.cu"

@@ -147,15 +147,20 @@ class MoE(nn.Module):
         with torch.no_grad():
             sorted_experts, order = selected.flatten().sort()
             freq = expert_histogram(sorted_experts, self.num_experts)
+        if self.ep_world_size == 1 and self._grouped_kernels(x) and x.size(1) % 8 == 0:
+            # Device-only path: padded per-expert layout derived from the histogram, one scatter kernel, two grouped
+            # tcgen05 GEMMs over all experts (SwiGLU fused into the first), one gather-reduce kernel for the weighted
+            # combine.  No per-expert launches, no atomics, no host synchronisation on the routing result.
+            from ...ops.moe import GroupLayout, combine_tokens, dispatch_tokens
+
+            layout = GroupLayout(sorted_experts, freq, order=order, top_k=self.top_k)
+            y_pad = self._grouped_mlp_padded(dispatch_tokens(x, layout), layout)
+            return combine_tokens(y_pad, weights.to(x.dtype), layout), freq
         token = order // self.top_k
         gates = weights.flatten()[order]
         xs = x[token]
         if self.ep_world_size > 1:
             ys = self._expert_parallel(xs, freq)
-        elif self._grouped_kernels(xs):
-            # one persistent grouped GEMM per projection over all experts, rows in a padded per-expert layout that is
-            # derived on the device: no per-expert launches and no host synchronisation on the routing result
-            ys = self._grouped_mlp(xs, sorted_experts, freq)
         else:
             counts = freq.tolist()
             ys = self.c_proj(self.act(self.c_fc(xs, counts)), counts)
@@ -169,16 +174,21 @@ class MoE(nn.Module):
         return (self.c_fc.bias is None and self.c_proj.bias is None
                 and grouped_kernels_eligible(xs, self.c_fc.weight, self.c_proj.weight))
 
-    def _grouped_mlp(self, xs: torch.Tensor, sorted_experts: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
-        from ...ops.moe import GroupLayout, grouped_linear_padded
+    def _grouped_mlp_padded(self, x_pad: torch.Tensor, layout) -> torch.Tensor:
+        from ...ops.moe import grouped_linear_padded
 
-        layout = GroupLayout(sorted_experts, freq)
-        x_pad = layout.scatter(xs)
         fuse = isinstance(self.act, GLUActivation) and self.act.is_swiglu
         h = grouped_linear_padded(x_pad, self.c_fc.weight, layout, swiglu=fuse)
         if not fuse:
             h = self.act(h)
-        return layout.gather(grouped_linear_padded(h, self.c_proj.weight, layout))
+        return grouped_linear_padded(h, self.c_proj.weight, layout)
+
+    def _grouped_mlp(self, xs: torch.Tensor, sorted_experts: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+        """Rows already sorted by expert (expert-parallel receive side)."""
+        from ...ops.moe import GroupLayout
+
+        layout = GroupLayout(sorted_experts, freq)
+        return layout.gather(self._grouped_mlp_padded(layout.scatter(xs), layout))
 
     def _expert_parallel(self, xs: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
         """Tokens (sorted by global expert id) -> owners of the experts -> local grouped MLP -> back."""

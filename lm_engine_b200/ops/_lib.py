@@ -65,6 +65,9 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_gemm_bf16_reduce_scatter": [P, L, P, I, L, P, L, I, I, I, P, P, L, P, P, I, I, I, I, P],
             "lme_gemm_bf16_grouped": [P, L, P, I, L, P, L, I, I, I, I, I, P, L, P, I, P],
             "lme_gemm_bf16_grouped_wgrad": [P, L, P, L, P, L, I, I, I, I, P, P, I, I, P],
+            "lme_moe_scatter_rows": [P, P, P, P, I, I, I, P],
+            "lme_moe_gather_reduce": [P, P, P, P, I, I, I, P],
+            "lme_moe_row_dots": [P, P, P, P, I, I, I, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

@@ -106,6 +106,60 @@ def bench_gemm_fp8(M, N, K, sustained=False):
             "quantize_gbs": M * K * 4 / tq / 1e9}
 
 
+def bench_elementwise(peaks: dict) -> list[dict]:
+    """Bandwidth-bound kernels at the 8B model's shapes: algorithmic bytes / device time against the measured copy
+    bandwidth.  Operand sets rotate through a pool larger than L2."""
+    from . import adamw_step, cross_entropy_sum, qkv_split_rope, rmsnorm, swiglu_backward
+    from . import fp8
+
+    dev, T, H, I = "cuda", 8192, 4096, 14336
+    bf = torch.bfloat16
+    pool = 3
+    rows = []
+
+    def add(name, fn, nbytes):
+        t = _time(fn, pool)
+        rows.append({"name": name, "ms": t * 1e3, "gbs": nbytes / t / 1e9,
+                     "frac_of_hbm": nbytes / t / 1e9 / peaks["hbm_gbs"]})
+        print(f"{name:28s} {t * 1e3:8.3f} ms  {nbytes / t / 1e9:7.0f} GB/s  "
+              f"({100 * rows[-1]['frac_of_hbm']:5.1f}% of {peaks['source']} copy bandwidth)", flush=True)
+
+    xs = [torch.randn(T, H, device=dev, dtype=bf) for _ in range(pool)]
+    rs = [torch.randn(T, H, device=dev, dtype=bf) for _ in range(pool)]
+    w = torch.ones(H, device=dev, dtype=bf, requires_grad=True)
+    add("rmsnorm fwd (+residual)", lambda i: rmsnorm(xs[i], w, 1e-5, rs[i]), T * H * 2 * 4)
+    ys = []
+    for i in range(pool):
+        x = xs[i].clone().requires_grad_(True)
+        y, _ = rmsnorm(x, w, 1e-5)
+        ys.append((x, y))
+    g = torch.randn(T, H, device=dev, dtype=bf)
+    add("rmsnorm bwd", lambda i: torch.autograd.grad(ys[i][1], ys[i][0], g, retain_graph=True), T * H * 2 * 3)
+    pre = [torch.randn(T, 2 * I, device=dev, dtype=bf) for _ in range(pool)]
+    dy = torch.randn(T, I, device=dev, dtype=bf)
+    add("swiglu bwd", lambda i: swiglu_backward(pre[i], dy), T * I * 2 * (2 + 1 + 2))
+    Hkv, G, D = 8, 4, 128
+    qkv = [torch.randn(T, Hkv * (G + 2) * D, device=dev, dtype=bf) for _ in range(pool)]
+    inv = 1.0 / (500000 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    fr = torch.outer(torch.arange(4096, device=dev).float(), inv)
+    cos, sin = torch.cat((fr, fr), -1).cos(), torch.cat((fr, fr), -1).sin()
+    add("qkv split + rope", lambda i: qkv_split_rope(qkv[i].view(2, 4096, -1), Hkv, G, D, cos, sin, None, 4096),
+        T * Hkv * (G + 2) * D * 2 * 2)
+    n = 218_112_000 // 2
+    ps = [(torch.randn(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev),
+           torch.randn(n, device=dev, dtype=bf), torch.empty(n, device=dev, dtype=bf)) for _ in range(2)]
+    one = torch.ones(1, device=dev)
+    add("adamw (fp32 state, bf16 grad+copy)",
+        lambda i: adamw_step(ps[i % 2][0], ps[i % 2][1], ps[i % 2][2], ps[i % 2][3], ps[i % 2][4], lr=1e-4,
+                             betas=(0.9, 0.95), eps=1e-10, weight_decay=0.1, step=3, gscale=one), n * (12 + 12 + 2 + 2))
+    V = 128256
+    lg = [torch.randn(2048, V, device=dev, dtype=bf) for _ in range(pool)]
+    lb = torch.randint(0, V, (2048,), device=dev)
+    add("cross entropy fwd (logits)", lambda i: cross_entropy_sum(lg[i], lb), 2048 * V * 2)
+    add("fp8 quantize + transpose", lambda i: fp8.quantize(xs[i], fp8.E4M3, transposed=True), T * H * (2 + 2 + 1 + 1))
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
@@ -113,9 +167,17 @@ def main():
     ap.add_argument("--sustained", action="store_true", help="time ~1.5 s back-to-back loops (power-limited clocks)")
     ap.add_argument("--impl", default=None, choices=["1cta", "2cta"])
     ap.add_argument("--fp8", action="store_true", help="also time the 8-bit GEMM and its quantiser")
+    ap.add_argument("--elementwise", action="store_true", help="time the bandwidth-bound kernels instead")
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
     args = ap.parse_args()
     peaks = _peaks()
+    if args.elementwise:
+        rows = bench_elementwise(peaks)
+        st = _lib.read_status()
+        print("device status:", st)
+        if args.json:
+            json.dump({"peaks": peaks, "elementwise": rows, "status": st}, open(args.json, "w"), indent=1)
+        return
     T = 8192
     shapes = [
         ("qkv fwd", T, 6144, 4096, False, False, {}),

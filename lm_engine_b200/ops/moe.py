@@ -45,7 +45,8 @@ class GroupLayout:
     device from the per-expert counts; the row capacity is the static upper bound ``rows + E * 127`` (rounded up),
     tiles past the last expert are marked unused and skipped by the kernels.  No host synchronisation."""
 
-    def __init__(self, sorted_experts: torch.Tensor, freq: torch.Tensor) -> None:
+    def __init__(self, sorted_experts: torch.Tensor, freq: torch.Tensor, order: torch.Tensor | None = None,
+                 top_k: int = 1) -> None:
         E, total = freq.numel(), sorted_experts.numel()
         dev = freq.device
         pad = (freq + (TILE_ROWS - 1)) // TILE_ROWS * TILE_ROWS
@@ -60,6 +61,12 @@ class GroupLayout:
         self.k0 = start.to(torch.int32)
         self.kb = (pad // 64).to(torch.int32)
         self.num_groups = E
+        # slot[t, k]: padded row of the k-th assignment of token t (``order`` maps sorted position -> t * top_k + k)
+        self.slot = None
+        if order is not None:
+            flat = torch.empty(total, dtype=torch.int32, device=dev)
+            flat.scatter_(0, order, self.dest.to(torch.int32))
+            self.slot = flat.view(total // top_k, top_k)
 
     def scatter(self, rows: torch.Tensor) -> torch.Tensor:
         """Rows sorted by expert -> padded layout (padding rows zero)."""
@@ -141,6 +148,73 @@ class _GroupedLinear(torch.autograd.Function):
 def grouped_linear_padded(x_pad: torch.Tensor, weight: torch.Tensor, layout: GroupLayout,
                           swiglu: bool = False) -> torch.Tensor:
     return _GroupedLinear.apply(x_pad, weight, layout, swiglu)
+
+
+def _rows_call(fn_name: str, src, slot, w, dst, T, H, K) -> None:
+    from . import _lib
+
+    rc = getattr(_lib.cuda_lib(), fn_name)(src.data_ptr(), slot.data_ptr(), _lib.ptr(w), dst.data_ptr(), T, H, K,
+                                            _lib.stream_ptr())
+    _lib.check(rc, f"{fn_name} T={T} H={H} K={K}")
+    _lib.count_launch()
+
+
+class _Dispatch(torch.autograd.Function):
+    """Tokens ``[T, H]`` -> padded per-expert rows (each token copied to its ``top_k`` slots); backward sums a
+    token's slots.  One pass each way, no atomics."""
+
+    @staticmethod
+    def forward(ctx, x, slot, capacity: int):
+        x = x.contiguous()
+        out = torch.zeros((capacity, x.size(1)), dtype=x.dtype, device=x.device)
+        _rows_call("lme_moe_scatter_rows", x, slot, None, out, x.size(0), x.size(1), slot.size(1))
+        ctx.slot, ctx.shape = slot, x.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dx = torch.empty(ctx.shape, dtype=g.dtype, device=g.device)
+        _rows_call("lme_moe_gather_reduce", g, ctx.slot, None, dx, ctx.shape[0], ctx.shape[1], ctx.slot.size(1))
+        return dx, None, None
+
+
+class _Combine(torch.autograd.Function):
+    """``out[t] = sum_k gates[t, k] * y_pad[slot[t, k]]``; backward scatters ``gates * dout`` to the slots and takes
+    the row dot products for the gate gradients."""
+
+    @staticmethod
+    def forward(ctx, y_pad, gates, slot):
+        y_pad, gates = y_pad.contiguous(), gates.contiguous()
+        T, K = slot.shape
+        out = torch.empty((T, y_pad.size(1)), dtype=y_pad.dtype, device=y_pad.device)
+        _rows_call("lme_moe_gather_reduce", y_pad, slot, gates, out, T, y_pad.size(1), K)
+        ctx.save_for_backward(y_pad, gates)
+        ctx.slot = slot
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y_pad, gates = ctx.saved_tensors
+        dout = dout.contiguous()
+        T, K = ctx.slot.shape
+        H = y_pad.size(1)
+        dy = dg = None
+        if ctx.needs_input_grad[0]:
+            dy = torch.zeros_like(y_pad)
+            _rows_call("lme_moe_scatter_rows", dout, ctx.slot, gates, dy, T, H, K)
+        if ctx.needs_input_grad[1]:
+            dg = torch.empty_like(gates)
+            _rows_call("lme_moe_row_dots", y_pad, ctx.slot, dout, dg, T, H, K)
+        return dy, dg, None
+
+
+def dispatch_tokens(x: torch.Tensor, layout: GroupLayout) -> torch.Tensor:
+    return _Dispatch.apply(x, layout.slot, layout.capacity)
+
+
+def combine_tokens(y_pad: torch.Tensor, gates: torch.Tensor, layout: GroupLayout) -> torch.Tensor:
+    return _Combine.apply(y_pad, gates, layout.slot)
 
 
 def grouped_kernels_eligible(x: torch.Tensor, *weights: torch.Tensor) -> bool:

@@ -91,7 +91,7 @@ def test_moe_layer_grouped_path_matches_loop_path():
 
     def run(grouped):
         moe.zero_grad()
-        moe._grouped_kernels = (lambda xs: grouped) if not grouped else MoE._grouped_kernels.__get__(moe)
+        moe._grouped_kernels = (lambda xs: False) if not grouped else MoE._grouped_kernels.__get__(moe)
         xi = x.clone().requires_grad_(True)
         y = moe(xi)
         y.float().pow(2).sum().backward()
@@ -100,3 +100,33 @@ def test_moe_layer_grouped_path_matches_loop_path():
     a, b = run(True), run(False)
     for u, v in zip(a, b):
         assert float((u.float() - v.float()).norm() / (v.float().norm() + 1e-6)) < 2e-2
+
+
+def test_dispatch_combine_kernels_match_index_ops():
+    from lm_engine_b200.ops.moe import GroupLayout, combine_tokens, dispatch_tokens
+
+    torch.manual_seed(3)
+    T, K, E, H = 300, 2, 8, 64
+    sel = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)])
+    gates = torch.rand(T, K, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    se, order = sel.flatten().sort()
+    freq = torch.bincount(se, minlength=E)
+    layout = GroupLayout(se, freq, order=order, top_k=K)
+    xp = dispatch_tokens(x, layout)
+    token = order // K
+    assert torch.equal(xp[layout.dest], x.detach()[token])
+    assert float(xp.float().abs().sum()) == pytest.approx(float(x.detach()[token].float().abs().sum()), rel=1e-6)
+    yp = (torch.randn_like(xp) * (xp.abs().sum(-1, keepdim=True) > 0)).requires_grad_(True)
+    out = combine_tokens(yp, gates, layout)
+    ref_g = gates.detach().float().requires_grad_(True)
+    ref_y = yp.detach().float().requires_grad_(True)
+    ref = torch.zeros(T, H, device="cuda").index_add(0, token, ref_y[layout.dest] * ref_g.flatten()[order][:, None])
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    do = torch.randn_like(out)
+    (out.float() * do.float()).sum().backward()
+    (ref * do.float()).sum().backward()
+    torch.testing.assert_close(yp.grad.float(), ref_y.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(gates.grad.float(), ref_g.grad, rtol=3e-2, atol=3e-2)
+    xp.backward(torch.ones_like(xp))
+    torch.testing.assert_close(x.grad.float(), torch.full_like(x, float(K)).float())
