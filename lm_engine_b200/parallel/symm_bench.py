@@ -70,7 +70,17 @@ def main() -> None:
         def floor(i):
             gemm(full, ws[i % pool], out=out)
 
-        r = {"name": name, "world": world, "M": T, "N": N, "K": K, "fused_ms": _time(fused, a.iters),
+        # numerical check of both fused forms against the two-step result
+        two_step(0)
+        want = out.float().clone()
+        errs = []
+        for nc in (0, a.copy_ctas):
+            y, xg = all_gather_matmul(xs[0], ws[0], dist.group.WORLD, n_copy=nc)
+            errs.append(float((y.float() - want).abs().max() / want.abs().max()))
+            errs.append(float((xg != full).sum()))
+        r_err = max(errs)
+        r = {"name": name, "world": world, "M": T, "N": N, "K": K, "max_err": r_err,
+             "fused_ms": _time(fused, a.iters),
              "fused_copy_ctas_ms": _time(fused_ctas, a.iters), "copy_ctas": a.copy_ctas,
              "nccl_then_gemm_ms": _time(two_step, a.iters), "gemm_only_ms": _time(floor, a.iters)}
         r["nvlink_bytes_in"] = (world - 1) * t * K * 2
@@ -79,7 +89,8 @@ def main() -> None:
         if rank == 0:
             print(f"{name:4s} M={T} N={N} K={K} world={world}: fused (copy engines feed the GEMM) {r['fused_ms']:.3f} ms "
                   f"({r['fused_tflops']:.0f} TF) | fused ({a.copy_ctas} copy CTAs in the grid) "
-                  f"{r['fused_copy_ctas_ms']:.3f} ms | NCCL all-gather + GEMM {r['nccl_then_gemm_ms']:.3f} ms | GEMM alone {r['gemm_only_ms']:.3f} ms",
+                  f"{r['fused_copy_ctas_ms']:.3f} ms | NCCL all-gather + GEMM {r['nccl_then_gemm_ms']:.3f} ms | GEMM alone {r['gemm_only_ms']:.3f} ms"
+                  f" | max err vs two-step {r['max_err']:.2e}",
                   flush=True)
     # GEMM -> reduce-scatter: row-parallel projections (contraction dim split over the ranks)
     from .symm import matmul_reduce_scatter
@@ -101,7 +112,11 @@ def main() -> None:
         def floor_rs(i):
             gemm(xs[i % pool], ws[i % pool], out=full)
 
-        r = {"name": name, "world": world, "M": T, "N": N, "K": Kl, "fused_ms": _time(fused_rs, a.iters),
+        two_step_rs(0)
+        got = matmul_reduce_scatter(xs[0], ws[0], dist.group.WORLD)
+        r_err = float((got.float() - shard.float()).abs().max() / shard.float().abs().max())
+        r = {"name": name, "world": world, "M": T, "N": N, "K": Kl, "max_err": r_err,
+             "fused_ms": _time(fused_rs, a.iters),
              "gemm_then_nccl_ms": _time(two_step_rs, a.iters), "gemm_only_ms": _time(floor_rs, a.iters)}
         r["nvlink_bytes_out"] = (world - 1) * (T // world) * N * 2
         r["fused_tflops"] = 2.0 * T * N * Kl / (r["fused_ms"] * 1e-3) / 1e12
@@ -109,7 +124,7 @@ def main() -> None:
         if rank == 0:
             print(f"{name:8s} M={T} N={N} K={Kl} world={world}: fused GEMM+reduce-scatter {r['fused_ms']:.3f} ms "
                   f"({r['fused_tflops']:.0f} TF) | GEMM + NCCL reduce-scatter {r['gemm_then_nccl_ms']:.3f} ms | "
-                  f"GEMM alone {r['gemm_only_ms']:.3f} ms", flush=True)
+                  f"GEMM alone {r['gemm_only_ms']:.3f} ms | max err vs two-step {r['max_err']:.2e}", flush=True)
     st = _lib.read_status()
     if rank == 0:
         print("device status:", st)
