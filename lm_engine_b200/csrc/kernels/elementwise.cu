@@ -148,14 +148,23 @@ __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* _
     }
 }
 
-// out[c] (+)= sum_r partial[r, c]   (fp32 out)
-__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int R, int H,
-                              int accumulate) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= H) return;
+// out[c] (+)= sum_r partial[r, c]   (fp32 out).  Block = 32 columns x 32 row lanes: every row lane sums a strided
+// subset of the rows with coalesced 128-byte loads, the lanes are combined through shared memory.
+__global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                      int R, int H, int accumulate) {
+    __shared__ float tile[32][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
-    for (int r = 0; r < R; ++r) s += partial[static_cast<long long>(r) * H + c];
-    out[c] = accumulate ? out[c] + s : s;
+    if (c < H)
+        for (int r = threadIdx.y; r < R; r += 32) s += partial[static_cast<long long>(r) * H + c];
+    tile[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < H) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) t += tile[i][threadIdx.x];
+        out[c] = accumulate ? out[c] + t : t;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------- SwiGLU
@@ -236,26 +245,39 @@ __global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
         const __nv_bfloat16* src = inverse ? split : packed;
         __nv_bfloat16* dst = inverse ? packed : split;
         float a[8];
-        load8(src + c, a);
         if (rotate && c >= r0) {
-            // partner vector in the other half of the rotary span
-            int rc = c - r0;
-            bool first = rc < half;
-            int pc = first ? c + half : c - half;
+            // The vector in the first half of the rotary span and its partner in the second half use the same
+            // angles: the thread that owns the first-half vector rotates both (one load of each vector and of the
+            // cos / sin row), the owner of the partner has nothing left to do.
+            const int rc = c - r0;
+            if (rc >= half) continue;
             float b[8];
-            load8(src + pc, b);
+            load8(src + c, a);
+            load8(src + c + half, b);
             int p = pos != nullptr ? pos[t] : static_cast<int>(t % S);
             if (p < 0 || p >= max_pos) {  // position outside the angle table: record it and leave the head unrotated
                 report_error(STATUS_BOUNDS, static_cast<unsigned int>(p));
                 store8(dst + c, a);
+                store8(dst + c + half, b);
                 continue;
             }
-            const float* cs = cos_t + static_cast<long long>(p) * rd + rc;
-            const float* sn = sin_t + static_cast<long long>(p) * rd + rc;
-            float sgn = (first ? -1.f : 1.f) * (inverse ? -1.f : 1.f);
+            const float4* cs = reinterpret_cast<const float4*>(cos_t + static_cast<long long>(p) * rd + rc);
+            const float4* sn = reinterpret_cast<const float4*>(sin_t + static_cast<long long>(p) * rd + rc);
+            const float4 c0 = __ldg(cs), c1 = __ldg(cs + 1), s0 = __ldg(sn), s1 = __ldg(sn + 1);
+            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const float sgn = inverse ? -1.f : 1.f;
+            float oa[8], ob[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a[j] = a[j] * cs[j] + sgn * b[j] * sn[j];
+            for (int j = 0; j < 8; ++j) {
+                oa[j] = a[j] * cv[j] - sgn * b[j] * sv[j];
+                ob[j] = b[j] * cv[j] + sgn * a[j] * sv[j];
+            }
+            store8(dst + c, oa);
+            store8(dst + c + half, ob);
+            continue;
         }
+        load8(src + c, a);
         store8(dst + c, a);
     }
 }
@@ -483,7 +505,7 @@ extern "C" int lme_rmsnorm_bwd(const void* dy, const void* h, const void* w, con
     else if (vecs <= 1024) rmsnorm_bwd_kernel<2><<<G, 512, 0, st>>>(DY, HH, W, rstd, DR, DX, dw_partial, T, H);
     else rmsnorm_bwd_kernel<4><<<G, 512, 0, st>>>(DY, HH, W, rstd, DR, DX, dw_partial, T, H);
     if (dw_partial != nullptr && dw != nullptr)
-        colsum_kernel<<<(H + 127) / 128, 128, 0, st>>>(dw_partial, dw, G, H, dw_accumulate);
+        colsum_kernel<<<(H + 31) / 32, dim3(32, 32), 0, st>>>(dw_partial, dw, G, H, dw_accumulate);
     return LME_LAUNCH_OK();
 }
 

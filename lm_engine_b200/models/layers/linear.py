@@ -22,7 +22,7 @@ from ...parameter import (
 from ...utils import divide_if_divisible
 
 
-def _fused_tp(x: torch.Tensor, padding_free: bool, world: int, gathered: bool) -> bool:
+def _fused_tp(x: torch.Tensor, padding_free: bool, world: int, gathered: bool, out_features: int) -> bool:
     """Fused collective kernels apply under ``use_async_tensor_parallel`` to activations whose sequence-parallel
     shards concatenate along rows: packed ``[T, H]`` or batch 1 (a ``[B > 1, S, H]`` batch would interleave the
     ranks' rows per batch entry and takes the two-step path)."""
@@ -30,10 +30,13 @@ def _fused_tp(x: torch.Tensor, padding_free: bool, world: int, gathered: bool) -
         return False
     if not (x.dim() == 2 or padding_free or x.size(0) == 1):
         return False
-    from ...parallel.symm import fused_tp_eligible
+    from ...parallel.symm import fused_tp_eligible, fused_tp_profitable
 
     rows = x.numel() // x.size(-1)
-    return fused_tp_eligible(x, rows // world if gathered else rows, world)
+    if not fused_tp_eligible(x, rows // world if gathered else rows, world):
+        return False
+    m = rows if gathered else rows * world
+    return fused_tp_profitable("reduce_scatter" if gathered else "all_gather", m, out_features, x.size(-1))
 
 
 class ParameterizedLinear(nn.Module):
@@ -99,7 +102,8 @@ class ColumnParallelLinear(ParameterizedLinear):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         if self.tp_world_size > 1:
             if self.sequence_parallel and residual is None and _fused_tp(x, self.use_padding_free_transformer,
-                                                                         self.tp_world_size, gathered=False):
+                                                                         self.tp_world_size, gathered=False,
+                                                                         out_features=self.weight.size(0)):
                 # all-gather fused into the GEMM (copy CTAs pull the peers' rows over NVLink while the others multiply)
                 from ...parallel import symm
 
@@ -141,7 +145,7 @@ class RowParallelLinear(ParameterizedLinear):
         if self.tp_world_size == 1:
             return ops.linear(x, self.weight, self.bias, residual)
         if self.sequence_parallel and _fused_tp(x, self.use_padding_free_transformer, self.tp_world_size,
-                                                gathered=True):
+                                                gathered=True, out_features=self.weight.size(0)):
             # reduce-scatter (+ bias + residual) fused into the GEMM epilogue over NVLink peer stores
             from ...parallel import symm
 

@@ -256,6 +256,20 @@ def fused_tp_eligible(x: torch.Tensor, rows_local: int, world: int) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16 and 2 <= world <= 8 and rows_local % 128 == 0
 
 
+# Measured on B200 (tp 2 / 4 / 8, 8192 tokens): the fused kernels beat "NCCL collective + GEMM" once the GEMM is long
+# enough to hide the transfer and the host-side enqueue of the chunk copies; below that the two-step path wins.
+_MIN_MNK = {"all_gather": 1.0e11, "reduce_scatter": 6.0e10}
+
+
+def fused_tp_profitable(kind: str, m: int, n: int, k: int) -> bool:
+    mode = os.environ.get("LME_FUSED_TP", "auto")
+    if mode == "always":
+        return True
+    if mode == "never":
+        return False
+    return float(m) * n * k >= _MIN_MNK[kind]
+
+
 def all_gather_linear(x, weight, bias, group):
     return _AllGatherLinear.apply(x, weight, bias, group)
 

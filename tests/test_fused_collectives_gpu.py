@@ -97,7 +97,7 @@ def test_all_gather_matmul_two_gpus():
 
 def _tp_worker(rank, world, port, q):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LME_FUSED_TP="always")
     try:
         import torch.distributed as dist
 
