@@ -106,7 +106,7 @@ def bench_gemm_fp8(M, N, K, sustained=False):
             "quantize_gbs": M * K * 4 / tq / 1e9}
 
 
-def bench_elementwise(peaks: dict) -> list[dict]:
+def bench_elementwise(peaks: dict, small: bool = False) -> list[dict]:
     """Bandwidth-bound kernels at the 8B model's shapes: algorithmic bytes / device time against the measured copy
     bandwidth.  Operand sets rotate through a pool larger than L2."""
     from . import adamw_step, cross_entropy_sum, qkv_split_rope, rmsnorm, swiglu_backward
@@ -114,7 +114,7 @@ def bench_elementwise(peaks: dict) -> list[dict]:
 
     dev, T, H, I = "cuda", 8192, 4096, 14336
     bf = torch.bfloat16
-    pool = 3
+    pool = 2 if small else 3   # small: under 2 GB on the device for profiler captures, operands still > L2
     rows = []
 
     def add(name, fn, nbytes):
@@ -145,7 +145,7 @@ def bench_elementwise(peaks: dict) -> list[dict]:
     cos, sin = torch.cat((fr, fr), -1).cos(), torch.cat((fr, fr), -1).sin()
     add("qkv split + rope", lambda i: qkv_split_rope(qkv[i].view(2, 4096, -1), Hkv, G, D, cos, sin, None, 4096),
         T * Hkv * (G + 2) * D * 2 * 2)
-    n = 218_112_000 // 2
+    n = 40_000_000 if small else 218_112_000 // 2
     ps = [(torch.randn(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev),
            torch.randn(n, device=dev, dtype=bf), torch.empty(n, device=dev, dtype=bf)) for _ in range(2)]
     one = torch.ones(1, device=dev)
@@ -153,9 +153,10 @@ def bench_elementwise(peaks: dict) -> list[dict]:
         lambda i: adamw_step(ps[i % 2][0], ps[i % 2][1], ps[i % 2][2], ps[i % 2][3], ps[i % 2][4], lr=1e-4,
                              betas=(0.9, 0.95), eps=1e-10, weight_decay=0.1, step=3, gscale=one), n * (12 + 12 + 2 + 2))
     V = 128256
-    lg = [torch.randn(2048, V, device=dev, dtype=bf) for _ in range(pool)]
-    lb = torch.randint(0, V, (2048,), device=dev)
-    add("cross entropy fwd (logits)", lambda i: cross_entropy_sum(lg[i], lb), 2048 * V * 2)
+    ce_rows = 1024 if small else 2048
+    lg = [torch.randn(ce_rows, V, device=dev, dtype=bf) for _ in range(pool)]
+    lb = torch.randint(0, V, (ce_rows,), device=dev)
+    add("cross entropy fwd (logits)", lambda i: cross_entropy_sum(lg[i], lb), ce_rows * V * 2)
     add("fp8 quantize + transpose", lambda i: fp8.quantize(xs[i], fp8.E4M3, transposed=True), T * H * (2 + 2 + 1 + 1))
     return rows
 
@@ -168,11 +169,12 @@ def main():
     ap.add_argument("--impl", default=None, choices=["1cta", "2cta"])
     ap.add_argument("--fp8", action="store_true", help="also time the 8-bit GEMM and its quantiser")
     ap.add_argument("--elementwise", action="store_true", help="time the bandwidth-bound kernels instead")
+    ap.add_argument("--small", action="store_true", help="smaller operand pools (profiler captures)")
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
     args = ap.parse_args()
     peaks = _peaks()
     if args.elementwise:
-        rows = bench_elementwise(peaks)
+        rows = bench_elementwise(peaks, small=args.small)
         st = _lib.read_status()
         print("device status:", st)
         if args.json:
