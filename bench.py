@@ -33,9 +33,13 @@ MODELS = {
     "tiny": (2048, 4, 256, 4, 2, 64, 1024, 10000),
     # fine-grained mixture of experts (see MOE): dense dims as above, the MLP of every block is routed
     "moe-64e": (32000, 16, 2048, 16, 4, 128, 1024, 10000),
+    # hybrid: three Mamba-2 (SSD) layers per softmax-attention layer (see HYBRID), no positional embedding
+    "hybrid-mamba2": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
 }
 # name: (experts, experts per token, shared expert intermediate size or None, router aux-loss coefficient)
 MOE = {"moe-64e": (64, 8, None, 0.01)}
+# name: (attention every n-th layer, state size, SSM heads, conv kernel, chunk size)
+HYBRID = {"hybrid-mamba2": (4, 128, 64, 4, 256)}
 
 
 LAYERS_OVERRIDE: int | None = None   # --layers: same per-layer shapes with fewer layers (profiling captures only)
@@ -49,14 +53,23 @@ def model_config(name: str, seq: int) -> dict:
         "model_type": "gpt_base", "vocab_size": v, "max_position_embeddings": seq, "hidden_size": h,
         "num_layers": L, "normalization_function": "rmsnorm", "layer_norm_epsilon": 1e-5,
         "initializer_range": 0.02, "bos_token_id": 0, "eos_token_id": 1, "pad_token_id": 2,
-        "position_embedding_type": "rope", "rope_theta": theta, "rope_scaling": None, "m_emb": None,
+        "position_embedding_type": "nope" if name in HYBRID else "rope", "rope_theta": theta, "rope_scaling": None, "m_emb": None,
         "m_width": None, "m_residual": None, "init_method": "normal", "embedding_init_method": "normal",
         "use_depth_scaled_init": False, "tie_word_embeddings": False,
-        "sequence_mixer_blocks": [{"sequence_mixer_type": "softmax_attention", "num_attention_heads": nh,
-                                   "num_key_value_heads": nkv, "head_dim": hd} for _ in range(L)],
+        "sequence_mixer_blocks": [_mixer_block(name, i, h, nh, nkv, hd) for i in range(L)],
         "mlp_blocks": [_mlp_block(name, inter) for _ in range(L)],
         "router_aux_loss_coef": MOE[name][3] if name in MOE else 0.001,
     }
+
+
+def _mixer_block(name: str, i: int, h: int, nh: int, nkv: int, hd: int) -> dict:
+    if name in HYBRID and (i + 1) % HYBRID[name][0] != 0:
+        _, state, heads, conv, chunk = HYBRID[name]
+        return {"sequence_mixer_type": "mamba2", "state_size": state, "intermediate_size": 2 * h, "num_heads": heads,
+                "conv_kernel_size": conv, "add_bias": False, "use_conv_bias": True, "num_groups": 1,
+                "chunk_size": chunk, "activation_function": "silu", "normalization_function": "rmsnorm"}
+    return {"sequence_mixer_type": "softmax_attention", "num_attention_heads": nh, "num_key_value_heads": nkv,
+            "head_dim": hd}
 
 
 def _mlp_block(name: str, inter: int) -> dict:

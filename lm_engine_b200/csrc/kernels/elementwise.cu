@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(512) rmsnorm_fwd_kernel(const __nv_bfloat16* _
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dres);  dw partial sums per CTA (rows strided by gridDim).
 template <int VPT>
-__global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+__global__ void __launch_bounds__(512, 3) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                    float* __restrict__ dw_partial, int T, int H) {
@@ -483,7 +483,8 @@ extern "C" int lme_rmsnorm_fwd(const void* x, const void* residual, const void* 
 }
 
 // Rows of dw_partial the backward kernel writes for a [T, H] problem (the caller sizes the scratch with it).
-extern "C" int lme_rmsnorm_bwd_partial_rows(int T) { return T < 592 ? (T < 1 ? 1 : T) : 592; }
+// 3 CTAs of 512 threads are resident per SM (40 registers per thread): one wave of 148 x 3 CTAs
+extern "C" int lme_rmsnorm_bwd_partial_rows(int T) { return T < 444 ? (T < 1 ? 1 : T) : 444; }
 
 // dw_partial: fp32 scratch [lme_rmsnorm_bwd_partial_rows(T), H] (may be null when w is null / dw not needed).
 extern "C" int lme_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,
