@@ -173,7 +173,9 @@ def run_ours(a) -> dict:
     from lm_engine_b200.train_utils import get_model_tflops, measured_peaks
     from lm_engine_b200.utils import disable_generation_cache
 
-    args = TrainingArgs(**training_config(a.model, a.seq, a.mbs, a.steps, ["fused_linear_cross_entropy"], None))
+    cfg = training_config(a.model, a.seq, a.mbs, a.steps, ["fused_linear_cross_entropy"], None)
+    cfg["mixed_precision_args"] = {"dtype": getattr(a, "dtype", "bf16")}
+    args = TrainingArgs(**cfg)
     d = args.distributed_args
     ProcessGroupManager(zero_stage=d.stage)
     world = ProcessGroupManager.get_world_size()
@@ -248,7 +250,7 @@ def run_ours(a) -> dict:
         "metric": "tokens/sec (whole job), pretraining step fwd+bwd+clip+AdamW", "value": value,
         "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic uniform-random token ids, seeded random-init weights",
+        "dtype": getattr(a, "dtype", "bf16"), "data": "synthetic uniform-random token ids, seeded random-init weights",
         "config": {"model": a.model if a.layers is None else f"{a.model}-{a.layers}layers",
                    "global_batch": world * a.mbs, "seq_len": a.seq, "parallelism": f"zero3-dp{world}", "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
                    "optimizer": "AdamW fp32 master+state", "l2": "working set per step >> 126 MB L2, no flush"},
@@ -279,6 +281,8 @@ def main() -> None:
     ap.add_argument("--mbs", type=int, default=2)
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (profiling captures on a small case; not a benchmark result)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="compute dtype of this repo's arm (the headline number is bf16; fp8 is an extra measurement)")
     a = ap.parse_args()
     global LAYERS_OVERRIDE
     LAYERS_OVERRIDE = a.layers

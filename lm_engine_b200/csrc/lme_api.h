@@ -88,6 +88,14 @@ int lme_moe_gather_reduce(const void* src, const int* slot, const void* w, void*
                           void* stream);
 int lme_moe_row_dots(const void* a, const int* slot, const void* b, void* out, int T, int H, int K, void* stream);
 
+// Depthwise causal convolution on channel-last bf16 activations x [B, S, C], weight [C, K] (K <= 8), optional bias [C]
+// and initial state init [B, C, K-1] (the inputs before t = 0); silu != 0 fuses the activation.  Backward recomputes
+// the pre-activation; dw [C, K] / dbias [C] are fp32 accumulators the caller zeroes, dinit [B, C, K-1] is written.
+int lme_causal_conv1d_fwd(const void* x, const void* w, const void* bias, const void* init, void* y, int B, int S,
+                          int C, int K, int silu, void* stream);
+int lme_causal_conv1d_bwd(const void* x, const void* w, const void* bias, const void* init, const void* dy, void* dx,
+                          float* dw, float* dbias, float* dinit, int B, int S, int C, int K, int silu, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

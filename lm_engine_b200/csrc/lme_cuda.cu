@@ -5,4 +5,5 @@
 #include "kernels/elementwise.cu"
 #include "kernels/fp8.cu"
 #include "kernels/moe.cu"
+#include "kernels/conv1d.cu"
 #include "kernels/noalloc.cu"

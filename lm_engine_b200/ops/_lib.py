@@ -68,6 +68,8 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_moe_scatter_rows": [P, P, P, P, I, I, I, P],
             "lme_moe_gather_reduce": [P, P, P, P, I, I, I, P],
             "lme_moe_row_dots": [P, P, P, P, I, I, I, P],
+            "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
+            "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

@@ -150,9 +150,18 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
     timer.start()
     window = MetricsTrackingDict({})
     step = starting_iteration
+    # host-side failure detection: per-rank heartbeat file + watchdog thread (LME_STALL_SECONDS, LME_STALL_ABORT=1
+    # ends a rank that made no progress so that the launcher can restart from the last checkpoint)
+    from .utils.watchdog import Heartbeat
+
+    heartbeat = Heartbeat(os.environ.get("LME_HEARTBEAT_DIR", os.path.join(args.save_args.save_path, "heartbeats")),
+                          ProcessGroupManager.get_global_rank(), ProcessGroupManager.get_world_size(),
+                          stall_seconds=float(os.environ.get("LME_STALL_SECONDS", "1800")), poll_seconds=30.0,
+                          abort=os.environ.get("LME_STALL_ABORT", "0") == "1").start()
     with StepProfiler(args.logging_args.torch_profiler_trace_path) as prof:
         while step < tp.num_training_steps:
             step += 1
+            heartbeat.beat(step)
             if pipeline_schedule is not None:
                 m = train_step_with_pipeline_parallel(model_container, pipeline_schedule, optimizer_container,
                                                       lr_scheduler_container, train_dataloader, ga,
@@ -196,6 +205,7 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
                                 {"consumed_samples": consumed, "cumulative_cost_usd": cumulative_cost})
                 host_t0 = time.perf_counter()
                 timer.start()
+    heartbeat.stop()
     ensure_last_checkpoint_is_saved()
 
 
