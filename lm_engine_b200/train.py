@@ -150,6 +150,10 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
     timer.start()
     window = MetricsTrackingDict({})
     step = starting_iteration
+    # metrics of every logged step also go to <save_path>/../metrics.jsonl (the sweep tool reads it)
+    from .train_utils import set_metrics_file
+
+    set_metrics_file(os.path.join(os.path.dirname(os.path.abspath(args.save_args.save_path)), "metrics.jsonl"))
     # host-side failure detection: per-rank heartbeat file + watchdog thread (LME_STALL_SECONDS, LME_STALL_ABORT=1
     # ends a rank that made no progress so that the launcher can restart from the last checkpoint)
     from .utils.watchdog import Heartbeat

@@ -38,11 +38,26 @@ def all_reduce_metrics_tracker(metrics: MetricsTrackingDict) -> MetricsTrackingD
     return MetricsTrackingDict({k: v for k, v in zip(keys, out)})
 
 
+_METRICS_FILE: str | None = None
+
+
+def set_metrics_file(path: str | None) -> None:
+    global _METRICS_FILE
+    _METRICS_FILE = path
+
+
 def track_metrics(global_step: int, experiments_tracker, metrics: MetricsTrackingDict | dict, context: str) -> None:
     d = metrics.get_dict() if isinstance(metrics, MetricsTrackingDict) else metrics
     d = {k: (v.item() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
     if experiments_tracker is not None:
         experiments_tracker.track(d, step=global_step, context=context)
+    # local record next to the checkpoints (set by the training entry point, ``LME_METRICS_FILE`` overrides): one JSON object
+    # per logged step, written by the tracking rank; the sweep tool ranks trials from it
+    path = os.environ.get("LME_METRICS_FILE", _METRICS_FILE)
+    if path and ProcessGroupManager.is_tracking_rank() and os.path.isdir(os.path.dirname(path)):
+        with open(path, "a") as f:
+            f.write(json.dumps({"context": context, "step": global_step, **{k: v for k, v in d.items()
+                                                                            if isinstance(v, (int, float))}}) + "\n")
     parts = [f"step = {global_step}"]
     for k in sorted(d):
         v = d[k]

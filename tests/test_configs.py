@@ -20,6 +20,11 @@ def test_config_parses(path):
     from lm_engine_b200.models import config_from_dict
 
     cfg = _load(path)
+    if "parameters" in cfg and "method" in cfg:          # sweep description
+        from lm_engine_b200.sweep import generate_trials
+
+        assert len(generate_trials(cfg, 4)) == 4
+        return
     if "unsharded_path" in cfg:
         UnshardingArgs(**cfg)
         return

@@ -108,3 +108,33 @@ def test_moe_group_layout_is_a_padded_partition():
     x = torch.arange(ids.numel(), dtype=torch.float32)[:, None].repeat(1, 2)
     assert torch.equal(lay.gather(lay.scatter(x)), x)
     assert lay.capacity % 128 == 0 and lay.capacity >= 512
+
+
+def test_sweep_generation_and_collection(tmp_path):
+    import json
+    import os
+
+    import yaml
+
+    from lm_engine_b200.sweep import collect, generate_trials, materialise
+
+    sweep = {"method": "grid", "parameters": {"optimizer_args.class_args.lr": {"values": [1e-4, 1e-3]},
+                                              "training_parameters.micro_batch_size": {"values": [1, 2, 4]}}}
+    trials = generate_trials(sweep, None)
+    assert len(trials) == 6
+    base = {"optimizer_args": {"class_args": {"lr": 1.0, "eps": 1e-8}}, "training_parameters": {"micro_batch_size": 8},
+            "save_args": {"save_path": "x", "save_interval": 5}}
+    paths = materialise(base, trials, str(tmp_path))
+    cfg = yaml.safe_load(open(paths[4]))
+    assert cfg["optimizer_args"]["class_args"] == {"lr": 1e-3, "eps": 1e-8}
+    assert cfg["training_parameters"]["micro_batch_size"] == 2 and cfg["save_args"]["save_interval"] == 5
+    assert cfg["save_args"]["save_path"].endswith(os.path.join("trial-4", "checkpoints"))
+    rnd = generate_trials({"method": "bayes", "parameters": {"a.b": {"distribution": "log_uniform_values",
+                                                                     "min": 1e-5, "max": 1e-2}}}, 16, seed=1)
+    assert all(1e-5 <= t["a.b"] <= 1e-2 for t in rnd) and len({t["a.b"] for t in rnd}) == 16
+    for i, v in ((0, 3.0), (3, 1.5)):
+        with open(tmp_path / f"trial-{i}" / "metrics.jsonl", "w") as f:
+            f.write(json.dumps({"context": "train", "step": 1, "lm_loss": 9.0}) + "\n")
+            f.write(json.dumps({"context": "train", "step": 2, "lm_loss": v}) + "\n")
+    ranked = collect(str(tmp_path), "train/lm_loss")
+    assert [r[0] for r in ranked] == [3, 0] and ranked[0][1] == 1.5
