@@ -592,6 +592,75 @@ extern "C" int lme_sumsq(const void* x, int is_bf16, long long n, float* partial
     sum_partials_kernel<<<1, 256, 0, st>>>(partials, grid, out, accumulate);
     return LME_LAUNCH_OK();
 }
+// out (=|+=) scale * sum_r src[r]: the local half of a reduce-scatter whose slices were pulled into local memory by
+// copy engines.  bf16 (or fp32) slices, fp32 accumulation.
+struct SlicePtrs { const void* p[8]; };
+template <typename T>
+__global__ void reduce_slices_kernel(SlicePtrs src, int nsrc, T* __restrict__ out, long long n, float scale,
+                                     int accumulate) {
+    constexpr int VEC = 16 / sizeof(T);
+    const long long nvec = n / VEC;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < nsrc; ++r) {
+            if constexpr (sizeof(T) == 2) {
+                float f[8];
+                load8(static_cast<const __nv_bfloat16*>(src.p[r]) + i * 8, f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            } else {
+                const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(src.p[r]) + i * 4);
+                acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+            }
+        }
+        if constexpr (sizeof(T) == 2) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + i * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = acc[j] * scale;
+            if (accumulate) {
+                float old[8];
+                load8(o, old);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += old[j];
+            }
+            store8(o, f);
+        } else {
+            float* o = reinterpret_cast<float*>(out) + i * 4;
+            float4 v = make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
+            if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(o);
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            *reinterpret_cast<float4*>(o) = v;
+        }
+    }
+}
+
+// n must be a multiple of 8 (bf16) / 4 (fp32) elements and every pointer 16-byte aligned.
+extern "C" int lme_reduce_slices(const void* const* src, int nsrc, void* out, long long n, int is_bf16, float scale,
+                                 int accumulate, void* stream) {
+    if (nsrc < 1 || nsrc > 8 || n < 0 || (n % (is_bf16 ? 8 : 4))) return LME_ERR_SHAPE;
+    if (n == 0) return LME_OK;
+    SlicePtrs sp;
+    for (int r = 0; r < 8; ++r) {
+        sp.p[r] = r < nsrc ? src[r] : nullptr;
+        if (r < nsrc && (reinterpret_cast<uintptr_t>(src[r]) & 15)) return LME_ERR_ALIGN;
+    }
+    if (reinterpret_cast<uintptr_t>(out) & 15) return LME_ERR_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = grid_for(n / 8 + 1, 256, 148 * 8);
+    if (is_bf16)
+        reduce_slices_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(sp, nsrc, static_cast<__nv_bfloat16*>(out), n,
+                                                                  scale, accumulate);
+    else
+        reduce_slices_kernel<float><<<grid, 256, 0, st>>>(sp, nsrc, static_cast<float*>(out), n, scale, accumulate);
+    return LME_LAUNCH_OK();
+}
+
 extern "C" int lme_clip_coef(const float* sumsq, float max_norm, float* norm_out, float* coef_out, void* stream) {
     clip_coef_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, norm_out, coef_out);
     return LME_LAUNCH_OK();

@@ -96,6 +96,11 @@ int lme_causal_conv1d_fwd(const void* x, const void* w, const void* bias, const 
 int lme_causal_conv1d_bwd(const void* x, const void* w, const void* bias, const void* init, const void* dy, void* dx,
                           float* dw, float* dbias, float* dinit, int B, int S, int C, int K, int silu, void* stream);
 
+// out (=|+=) scale * sum of nsrc <= 8 local slices of n elements (bf16 or fp32, fp32 accumulation): the reduction
+// half of a reduce-scatter whose peer slices were pulled by copy engines.
+int lme_reduce_slices(const void* const* src, int nsrc, void* out, long long n, int is_bf16, float scale,
+                      int accumulate, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

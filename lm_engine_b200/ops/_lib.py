@@ -70,6 +70,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_moe_row_dots": [P, P, P, P, I, I, I, P],
             "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
             "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+            "lme_reduce_slices": [P, I, P, L, I, F, I, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

@@ -319,11 +319,17 @@ class FSDPEngine:
         self._setup_grad_buffers()
         self._install_grad_hooks()
         self.copy_engine_gather = False
+        self.copy_engine_reduce = False
         if self.is_cuda and self.world > 1 and self.stage == 3:
             import os
 
             if os.environ.get("LME_ALLGATHER", "ce") == "ce":
                 self._setup_symmetric_shards()
+        if self.is_cuda and 1 < self.world <= 8 and self.stage >= 1:
+            import os
+
+            if os.environ.get("LME_REDUCE_SCATTER", "nccl") == "ce":
+                self._setup_symmetric_reduce()
 
     # ------------------------------------------------------------------ initialisation
     @torch.no_grad()
@@ -471,6 +477,80 @@ class FSDPEngine:
             log_rank_0(logging.WARNING, f"symmetric-memory parameter shards unavailable ({e}); using NCCL all-gather")
             self.copy_engine_gather = False
 
+    # ------------------------------------------------------------------ copy-engine gradient reduce-scatter
+    def _setup_symmetric_reduce(self) -> None:
+        """Gradient buffers of the sharded units live in symmetric memory; a reduce-scatter then is: announce the
+        buffer (one-thread kernel writing a sequence number into every peer's pad), per peer wait for its
+        announcement (bounded one-thread kernel) and pull this rank's slice of its buffer with a copy engine, then
+        one local kernel that sums the slices in fp32, scales and writes / accumulates the gradient shard.  The
+        transfer takes no SM from the backward GEMMs it overlaps with."""
+        try:
+            import ctypes
+
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self._rs_pad = symm_mem.empty(16, dtype=torch.int32, device=self.device)
+            self._rs_pad.zero_()
+            handle = symm_mem.rendezvous(self._rs_pad, self.shard_group)
+            ptrs = [handle.get_buffer(r, (16,), torch.int32, 0).data_ptr() for r in range(self.world)]
+            self._rs_pad_handle = handle
+            self._rs_pad_arr = (ctypes.c_void_p * 8)(*(ptrs + [None] * (8 - self.world)))
+            self._rs_seq = 0
+            self._rs_stage: torch.Tensor | None = None
+            self._symm_grad: dict[int, list[torch.Tensor]] = {}
+            self._last_reduced_buf: int | None = None
+            self.copy_engine_reduce = True
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.shard_group)
+        except Exception as e:  # noqa: BLE001 - symmetric memory unavailable: keep the NCCL reduce-scatter
+            import logging
+
+            from ..logging_utils import log_rank_0
+
+            log_rank_0(logging.WARNING, f"symmetric-memory gradient buffers unavailable ({e}); using NCCL")
+            self.copy_engine_reduce = False
+
+    def _ce_reduce_applies(self, u: ShardedUnit) -> bool:
+        return (self.copy_engine_reduce and u.world > 1 and u.group is self.shard_group and u.replica_group is None
+                and not u.is_expert and self.world <= 8)
+
+    def _symmetric_grad_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        buf = symm_mem.empty(numel, dtype=dtype, device=self.device)
+        handle = symm_mem.rendezvous(buf, self.shard_group)      # collective: every rank allocates in the same order
+        self._symm_grad[buf.data_ptr()] = [handle.get_buffer(r, (numel,), dtype, 0) for r in range(self.world)]
+        self._symm_grad_handles = getattr(self, "_symm_grad_handles", []) + [handle]
+        return buf
+
+    def _reduce_scatter_ce(self, u: ShardedUnit, full: torch.Tensor, scale: float) -> None:
+        """Runs on the reduction stream."""
+        import ctypes
+
+        from ..ops import _lib
+
+        lib, st = _lib.cuda_lib(), _lib.stream_ptr()
+        S, world, rank = u.shard_size, self.world, self.rank
+        peers = self._symm_grad[full.data_ptr()]
+        self._rs_seq += 1
+        seq = self._rs_seq
+        if self._rs_stage is None or self._rs_stage.size(1) < S or self._rs_stage.dtype != full.dtype:
+            cap = max(x.shard_size for x in self.units)
+            self._rs_stage = torch.empty((world - 1, cap), dtype=full.dtype, device=self.device)
+        _lib.check(lib.lme_gather_signal(self._rs_pad_arr, rank, world, seq, st), "lme_gather_signal")
+        srcs = [full[rank * S:(rank + 1) * S]]
+        for i in range(1, world):
+            p = (rank + i) % world
+            _lib.check(lib.lme_gather_wait_peer(self._rs_pad.data_ptr(), p, seq, st), "lme_gather_wait_peer")
+            stage = self._rs_stage[i - 1, :S]
+            stage.copy_(peers[p][rank * S:(rank + 1) * S], non_blocking=True)
+            srcs.append(stage)
+        arr = (ctypes.c_void_p * 8)(*([t.data_ptr() for t in srcs] + [None] * (8 - world)))
+        _lib.check(lib.lme_reduce_slices(arr, world, u.grad_shard.data_ptr(), S, int(full.dtype == torch.bfloat16),
+                                         scale, int(not u.grad_shard_fresh), st), "lme_reduce_slices")
+        _lib.count_launch(2)
+        u.grad_shard_fresh = False
+
     def _cross_rank_fence(self) -> None:
         """Orders this rank's writes to its parameter shard (optimizer step, checkpoint load) before the peers'
         next reads: a tiny all-reduce on the compute stream; the gather stream waits on the compute stream."""
@@ -481,7 +561,10 @@ class FSDPEngine:
     def _take(self, pool: dict[int, list[torch.Tensor]], kind: str, u: ShardedUnit, dtype) -> torch.Tensor:
         bufs = pool.setdefault(u.numel, [])
         if len(bufs) < 2:
-            bufs.append(torch.empty(u.numel, dtype=dtype, device=self.device))
+            if kind == "g" and self._ce_reduce_applies(u):
+                bufs.append(self._symmetric_grad_buffer(u.numel, dtype))
+            else:
+                bufs.append(torch.empty(u.numel, dtype=dtype, device=self.device))
             return bufs[-1]
         key = (kind, u.numel)
         i = self._pool_cursor.get(key, 0)
@@ -617,6 +700,9 @@ class FSDPEngine:
                         full.div_(dp_total)
                     dist.all_reduce(full, op=avg, group=u.replica_group)
                 return
+            if self.is_cuda and full.data_ptr() in getattr(self, "_symm_grad", {}):
+                self._reduce_scatter_ce(u, full, 1.0 / dp_total)
+                return
             out = torch.empty(u.shard_size, dtype=full.dtype, device=self.device)
             if self.is_cuda:
                 dist.reduce_scatter_tensor(out, full, op=avg, group=u.group)
@@ -641,7 +727,15 @@ class FSDPEngine:
                 run()
                 u.rs_event = torch.cuda.Event()
                 u.rs_event.record(self.rs_stream)
-                self._buffer_events[full.data_ptr()] = u.rs_event
+                if full.data_ptr() in getattr(self, "_symm_grad", {}):
+                    # Peers pull from this buffer too: it is free for new gradients once the NEXT reduction has
+                    # finished here (that one waited for every peer's announcement, which a peer sends after its
+                    # own pulls of this reduction, in stream order).  The step boundary is covered by the fence.
+                    if self._last_reduced_buf is not None:
+                        self._buffer_events[self._last_reduced_buf] = u.rs_event
+                    self._last_reduced_buf = full.data_ptr()
+                else:
+                    self._buffer_events[full.data_ptr()] = u.rs_event
         else:
             run()
         if self.stage != 0 and u.world > 1:
