@@ -30,16 +30,29 @@ def _make_tokenizer_dir() -> str:
     from transformers import PreTrainedTokenizerFast
 
     path = os.path.join(tempfile.gettempdir(), f"lme_ref_tok_{os.getuid()}")
-    if os.path.exists(os.path.join(path, "tokenizer.json")):
+    done = os.path.join(path, "tokenizer.json")
+    if os.path.exists(done):
         return path
+    if int(os.environ.get("LOCAL_RANK", "0")) != 0:
+        # one rank per node writes the files (published by an atomic rename); the others wait for them
+        for _ in range(600):
+            if os.path.exists(done):
+                return path
+            time.sleep(0.1)
+        raise RuntimeError("tokenizer files were not written by local rank 0")
     # special-token ids must equal the model config's bos / eos / pad ids (0 / 1 / 2): the reference asserts it
     vocab = {"<bos>": 0, "<eos>": 1, "<pad>": 2, "<unk>": 3, "a": 4, "b": 5}
     tok = Tokenizer(models.WordLevel(vocab=vocab, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Whitespace()
     fast = PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="<eos>", pad_token="<pad>",
                                    bos_token="<bos>")
-    os.makedirs(path, exist_ok=True)
-    fast.save_pretrained(path)
+    tmp = tempfile.mkdtemp(prefix="lme_ref_tok_build_")
+    fast.save_pretrained(tmp)
+    try:
+        os.replace(tmp, path)
+    except OSError:          # another launcher got there first
+        if not os.path.exists(done):
+            raise
     return path
 
 
