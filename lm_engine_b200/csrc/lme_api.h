@@ -101,6 +101,12 @@ int lme_causal_conv1d_bwd(const void* x, const void* w, const void* bias, const 
 int lme_reduce_slices(const void* const* src, int nsrc, void* out, long long n, int is_bf16, float scale,
                       int accumulate, void* stream);
 
+// Mamba-2 SSD intra-chunk helpers (L % 8 == 0, L <= 1024; BC = batch x chunks):
+//   decay_matrix: m[BC,N,L,L] = cb[BC,G,L,L] * exp(cum[BC,N,l] - cum[BC,N,s]) for s <= l else 0 (bf16; cum fp32)
+//   dcb         : dcb[BC,G,L,L] = sum over the heads of a group of dm[BC,N,L,L] * exp(cum[l] - cum[s]), s <= l
+int lme_ssd_decay_matrix(const void* cb, const float* cum, void* m, long long BC, int N, int G, int L, void* stream);
+int lme_ssd_dcb(const void* dm, const float* cum, void* dcb, long long BC, int N, int G, int L, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

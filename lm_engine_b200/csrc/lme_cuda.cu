@@ -6,4 +6,5 @@
 #include "kernels/fp8.cu"
 #include "kernels/moe.cu"
 #include "kernels/conv1d.cu"
+#include "kernels/ssd.cu"
 #include "kernels/noalloc.cu"

@@ -71,6 +71,8 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
             "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
             "lme_reduce_slices": [P, I, P, L, I, F, I, P],
+            "lme_ssd_decay_matrix": [P, P, P, L, I, I, I, P],
+            "lme_ssd_dcb": [P, P, P, L, I, I, I, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

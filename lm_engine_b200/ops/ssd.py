@@ -13,6 +13,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+FUSED_INTRA_CHUNK = True   # tests switch it off to compare the two paths
+
 
 def ssd_recurrent_step(x, dt, A, B, C, D, h):
     """One token.  x ``[b, N, P]``, dt ``[b, N]``, B/C ``[b, G, Sd]``, h ``[b, N, P, Sd]`` (fp32)."""
@@ -23,6 +25,59 @@ def ssd_recurrent_step(x, dt, A, B, C, D, h):
     h = h.float() * dA + (dt.float()[..., None] * x.float())[..., None] * Bh[:, :, None, :]
     y = (h * Ch[:, :, None, :]).sum(-1) + D.float()[None, :, None] * x.float()
     return y.to(x.dtype), h
+
+
+class _IntraChunk(torch.autograd.Function):
+    """``y[l] = sum_{s<=l} exp(cum[l]-cum[s]) CB[l,s] xdt[s]`` per (batch, chunk, head) on CUDA: the decay-masked
+    matrix is built in one kernel (bf16), the two products run as batched tensor-core GEMMs, and the backward needs
+    one more kernel (group sum of ``dM * decay``); the gradient of ``cum`` follows from ``dy . y`` and
+    ``xdt . dxdt`` without another L x L pass."""
+
+    @staticmethod
+    def forward(ctx, CB, ct, xdt):
+        # CB [b, nc, G, L, L] bf16, ct [b, nc, N, L] fp32, xdt [b, nc, N, L, P] bf16
+        from . import _lib
+
+        b, nc, G, L, _ = CB.shape
+        N, P = ct.size(2), xdt.size(-1)
+        CB, ct, xdt = CB.contiguous(), ct.contiguous(), xdt.contiguous()
+        M = torch.empty((b, nc, N, L, L), dtype=torch.bfloat16, device=CB.device)
+        _lib.check(_lib.cuda_lib().lme_ssd_decay_matrix(CB.data_ptr(), ct.data_ptr(), M.data_ptr(), b * nc, N, G, L,
+                                                        _lib.stream_ptr()), "lme_ssd_decay_matrix")
+        _lib.count_launch()
+        y = torch.bmm(M.view(-1, L, L), xdt.view(-1, L, P)).view(b, nc, N, L, P)
+        ctx.save_for_backward(M, ct, xdt, y)
+        ctx.G = G
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _lib
+
+        M, ct, xdt, y = ctx.saved_tensors
+        b, nc, N, L, P = xdt.shape
+        G = ctx.G
+        dy = dy.contiguous().to(torch.bfloat16)
+        dyv, xv = dy.view(-1, L, P), xdt.view(-1, L, P)
+        dM = torch.bmm(dyv, xv.transpose(1, 2))                          # [bcn, L, L]
+        dxdt = torch.bmm(M.view(-1, L, L).transpose(1, 2), dyv).view(b, nc, N, L, P)
+        dCB = torch.empty((b, nc, G, L, L), dtype=torch.bfloat16, device=dy.device)
+        _lib.check(_lib.cuda_lib().lme_ssd_dcb(dM.data_ptr(), ct.data_ptr(), dCB.data_ptr(), b * nc, N, G, L,
+                                               _lib.stream_ptr()), "lme_ssd_dcb")
+        _lib.count_launch()
+        dct = (dy.float() * y.float()).sum(-1) - (xdt.float() * dxdt.float()).sum(-1)   # [b, nc, N, L]
+        return dCB, dct, dxdt
+
+
+def _intra_chunk_fused(Cc, Bc, ct, xdt):
+    """CUDA path of the intra-chunk term.  Cc / Bc ``[b, nc, L, G, Sd]``, ct ``[b, nc, N, L]`` fp32,
+    xdt ``[b, nc, L, N, P]`` fp32 -> ``[b, nc, L, N, P]`` fp32."""
+    Cg = Cc.permute(0, 1, 3, 2, 4).to(torch.bfloat16)                    # [b, nc, G, L, Sd]
+    Bg = Bc.permute(0, 1, 3, 2, 4).to(torch.bfloat16)
+    CB = torch.matmul(Cg, Bg.transpose(-1, -2))                          # [b, nc, G, L, L] bf16
+    xh = xdt.permute(0, 1, 3, 2, 4).to(torch.bfloat16)                   # [b, nc, N, L, P]
+    y = _IntraChunk.apply(CB, ct, xh)
+    return y.permute(0, 1, 3, 2, 4).float()
 
 
 def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
@@ -48,14 +103,17 @@ def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
     dA = dtc * A.float()                                      # [b, nc, L, N]
     cum = torch.cumsum(dA, dim=2)
     # ---- intra-chunk: y[t] = sum_{s<=t} exp(cum[t]-cum[s]) (C_t.B_s) dt_s x_s
-    CB = torch.einsum("bclgn,bcsgn->bcgls", Cc, Bc)           # [b, nc, G, L, L]
-    CB = CB.repeat_interleave(rep, dim=2)                     # [b, nc, N, L, L]
     ct = cum.permute(0, 1, 3, 2)                              # [b, nc, N, L]
-    seg = ct[..., :, None] - ct[..., None, :]                 # cum[t] - cum[s]
-    causal = torch.ones(L, L, dtype=torch.bool, device=x.device).tril()
-    decay = torch.exp(seg.masked_fill(~causal, float("-inf")))
     xdt = xc * dtc[..., None]                                 # [b, nc, L, N, P]
-    y = torch.einsum("bcnls,bcsnp->bclnp", CB * decay, xdt)
+    if x.is_cuda and dtype == torch.bfloat16 and L % 8 == 0 and L <= 1024 and FUSED_INTRA_CHUNK:
+        y = _intra_chunk_fused(Cc, Bc, ct, xdt)
+    else:
+        CB = torch.einsum("bclgn,bcsgn->bcgls", Cc, Bc)       # [b, nc, G, L, L]
+        CB = CB.repeat_interleave(rep, dim=2)                 # [b, nc, N, L, L]
+        seg = ct[..., :, None] - ct[..., None, :]             # cum[t] - cum[s]
+        causal = torch.ones(L, L, dtype=torch.bool, device=x.device).tril()
+        decay = torch.exp(seg.masked_fill(~causal, float("-inf")))
+        y = torch.einsum("bcnls,bcsnp->bclnp", CB * decay, xdt)
     # ---- chunk summaries: S_c = sum_s exp(cum[L-1]-cum[s]) B_s (x) (dt_s x_s)
     tail = torch.exp(cum[:, :, -1:, :] - cum)                 # [b, nc, L, N]
     Bh = Bc.repeat_interleave(rep, dim=3)                     # [b, nc, L, N, Sd]
