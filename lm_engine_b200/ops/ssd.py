@@ -27,6 +27,14 @@ def ssd_recurrent_step(x, dt, A, B, C, D, h):
     return y.to(x.dtype), h
 
 
+def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """bf16 x bf16 batched product with an fp32 result (tensor cores, no rounding of the sums)."""
+    try:
+        return torch.bmm(a, b, out_dtype=torch.float32)
+    except (TypeError, RuntimeError):
+        return torch.bmm(a, b).float()
+
+
 class _IntraChunk(torch.autograd.Function):
     """``y[l] = sum_{s<=l} exp(cum[l]-cum[s]) CB[l,s] xdt[s]`` per (batch, chunk, head) on CUDA: the decay-masked
     matrix is built in one kernel (bf16), the two products run as batched tensor-core GEMMs, and the backward needs
@@ -45,7 +53,7 @@ class _IntraChunk(torch.autograd.Function):
         _lib.check(_lib.cuda_lib().lme_ssd_decay_matrix(CB.data_ptr(), ct.data_ptr(), M.data_ptr(), b * nc, N, G, L,
                                                         _lib.stream_ptr()), "lme_ssd_decay_matrix")
         _lib.count_launch()
-        y = torch.bmm(M.view(-1, L, L), xdt.view(-1, L, P)).view(b, nc, N, L, P)
+        y = _bmm_f32(M.view(-1, L, L), xdt.view(-1, L, P)).view(b, nc, N, L, P)
         ctx.save_for_backward(M, ct, xdt, y)
         ctx.G = G
         return y
@@ -57,15 +65,16 @@ class _IntraChunk(torch.autograd.Function):
         M, ct, xdt, y = ctx.saved_tensors
         b, nc, N, L, P = xdt.shape
         G = ctx.G
-        dy = dy.contiguous().to(torch.bfloat16)
+        dy32 = dy.contiguous().float()
+        dy = dy32.to(torch.bfloat16)
         dyv, xv = dy.view(-1, L, P), xdt.view(-1, L, P)
         dM = torch.bmm(dyv, xv.transpose(1, 2))                          # [bcn, L, L]
-        dxdt = torch.bmm(M.view(-1, L, L).transpose(1, 2), dyv).view(b, nc, N, L, P)
+        dxdt = _bmm_f32(M.view(-1, L, L).transpose(1, 2), dyv).view(b, nc, N, L, P)
         dCB = torch.empty((b, nc, G, L, L), dtype=torch.bfloat16, device=dy.device)
         _lib.check(_lib.cuda_lib().lme_ssd_dcb(dM.data_ptr(), ct.data_ptr(), dCB.data_ptr(), b * nc, N, G, L,
                                                _lib.stream_ptr()), "lme_ssd_dcb")
         _lib.count_launch()
-        dct = (dy.float() * y.float()).sum(-1) - (xdt.float() * dxdt.float()).sum(-1)   # [b, nc, N, L]
+        dct = (dy32 * y).sum(-1) - (xdt.float() * dxdt).sum(-1)   # [b, nc, N, L]
         return dCB, dct, dxdt
 
 
@@ -77,7 +86,7 @@ def _intra_chunk_fused(Cc, Bc, ct, xdt):
     CB = torch.matmul(Cg, Bg.transpose(-1, -2))                          # [b, nc, G, L, L] bf16
     xh = xdt.permute(0, 1, 3, 2, 4).to(torch.bfloat16)                   # [b, nc, N, L, P]
     y = _IntraChunk.apply(CB, ct, xh)
-    return y.permute(0, 1, 3, 2, 4).float()
+    return y.permute(0, 1, 3, 2, 4)
 
 
 def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
