@@ -27,6 +27,18 @@ def ssd_recurrent_step(x, dt, A, B, C, D, h):
     return y.to(x.dtype), h
 
 
+def _group_mm(a: torch.Tensor, b: torch.Tensor, lowp: bool) -> torch.Tensor:
+    """``a @ b`` over the leading (batch, chunk, group) dims with an fp32 result; bf16 operands on the tensor cores
+    when the model computes in bf16, plain fp32 otherwise."""
+    lead = a.shape[:-2]
+    a2, b2 = a.reshape(-1, *a.shape[-2:]), b.reshape(-1, *b.shape[-2:])
+    if lowp:
+        out = _bmm_f32(a2.to(torch.bfloat16).contiguous(), b2.to(torch.bfloat16).contiguous())
+    else:
+        out = torch.bmm(a2.float(), b2.float())
+    return out.view(*lead, a.size(-2), b.size(-1))
+
+
 def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """bf16 x bf16 batched product with an fp32 result (tensor cores, no rounding of the sums)."""
     try:
@@ -124,9 +136,13 @@ def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
         decay = torch.exp(seg.masked_fill(~causal, float("-inf")))
         y = torch.einsum("bcnls,bcsnp->bclnp", CB * decay, xdt)
     # ---- chunk summaries: S_c = sum_s exp(cum[L-1]-cum[s]) B_s (x) (dt_s x_s)
+    # The heads of a group share B and C, so both state products are batched GEMMs over (batch, chunk, group) with
+    # the group's heads folded into the GEMM's M / N dimension: no per-head copies of B or C are made.
+    lowp = x.is_cuda and dtype == torch.bfloat16
     tail = torch.exp(cum[:, :, -1:, :] - cum)                 # [b, nc, L, N]
-    Bh = Bc.repeat_interleave(rep, dim=3)                     # [b, nc, L, N, Sd]
-    states = torch.einsum("bcln,bclnp,bclns->bcnps", tail, xdt, Bh)
+    xw = (xdt * tail[..., None]).view(b, nc, L, G, rep * P)   # [b, nc, L, G, rep*P]
+    states = _group_mm(xw.permute(0, 1, 3, 4, 2), Bc.permute(0, 1, 3, 2, 4), lowp)   # [b, nc, G, rep*P, Sd]
+    states = states.view(b, nc, N, P, Sd)
     # ---- boundary states: h_c = exp(sum dA of chunk c-1) h_{c-1} + S_{c-1}
     h = (torch.zeros(b, N, P, Sd, dtype=torch.float32, device=x.device) if initial_state is None
          else initial_state.float())
@@ -137,8 +153,10 @@ def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
         h = h * chunk_decay[:, c, :, None, None] + states[:, c]
     h0 = torch.stack(starts, dim=1)                           # [b, nc, N, P, Sd] state at chunk start
     # ---- carried state contribution: exp(cum[t]) C_t . h_c
-    Ch = Cc.repeat_interleave(rep, dim=3)
-    y = y + torch.einsum("bclns,bcnps,bcln->bclnp", Ch, h0, torch.exp(cum))
+    hg = h0.view(b, nc, G, rep * P, Sd)
+    off = _group_mm(Cc.permute(0, 1, 3, 2, 4), hg.transpose(-1, -2), lowp)            # [b, nc, G, L, rep*P]
+    off = off.permute(0, 1, 3, 2, 4).reshape(b, nc, L, N, P)
+    y = y + off * torch.exp(cum)[..., None]
     y = y + D.float()[None, None, None, :, None] * xc
     y = y.reshape(b, nc * L, N, P)[:, :S]
     if pad:
