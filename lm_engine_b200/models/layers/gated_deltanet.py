@@ -2,15 +2,15 @@
 when negative eigenvalues are allowed), log-decay ``g = -exp(A_log) softplus(a + dt_bias)``, GQA-style repetition of
 q / k heads up to the v heads, gated delta rule with l2-normalised q / k, optional output gate, per-head RMSNorm,
 ``o_proj`` (lm_engine/modeling_utils/sequence_mixer_blocks/gated_deltanet/module.py:28-246).  The reference has no
-PyTorch path for the recurrence (it calls fla's Triton kernels); :func:`gated_delta_rule_scan` is this engine's
-statement of it."""
+PyTorch path for the recurrence (it calls fla's Triton kernels); ``ops.recurrence.gated_delta_rule`` is this engine's
+statement of it: the token recurrence for decode, the chunk-parallel (triangular-solve) form otherwise."""
 
 from __future__ import annotations
 
 import torch
 import torch.nn as nn
 
-from ...ops.recurrence import gated_delta_rule_scan
+from ...ops.recurrence import gated_delta_rule
 from ...utils import divide_if_divisible
 from ..context import AttentionMaskInfo, GenerationCache, PositionInfo, resolve_attention_and_position_info
 from .activations import silu
@@ -74,7 +74,7 @@ class GatedDeltaNet(nn.Module):
             beta = beta * 2
         g, _ = self.decay_gate(a, final_exponential=False)
         o, h = run_per_sample(
-            lambda t, st: gated_delta_rule_scan(t[0], t[1], t[2], t[3], t[4], self.attention_multiplier, st, True),
+            lambda t, st: gated_delta_rule(t[0], t[1], t[2], t[3], t[4], self.attention_multiplier, st, True),
             mask, [q, k, v, g, beta], h)
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ...ops.recurrence import linear_attention_scan
+from ...ops.recurrence import linear_attention
 from ...parameter import mark_parameter_as_mup_learning_rate
 from ...utils import divide_if_divisible
 from ..context import AttentionMaskInfo, GenerationCache, PositionInfo, resolve_attention_and_position_info
@@ -67,7 +67,7 @@ class LinearAttention(nn.Module):
         q = q.view(B, S, self.num_q_heads, self.k_head_dim)
         k = k.view(B, S, self.num_k_heads, self.k_head_dim)
         v = v.view(B, S, self.num_v_heads, self.v_head_dim)
-        y, h = run_per_sample(lambda t, st: linear_attention_scan(t[0], t[1], t[2], st, self.attention_multiplier),
+        y, h = run_per_sample(lambda t, st: linear_attention(t[0], t[1], t[2], st, self.attention_multiplier),
                               mask, [q, k, v], h)
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)

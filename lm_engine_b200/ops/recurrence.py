@@ -70,6 +70,86 @@ def m2rnn_scan(q, k, v, f, W, h0=None, gradient_clipping=None):
     return torch.stack(ys, dim=1), h
 
 
+CHUNK = 64   # time steps per block of the chunk-parallel forms below
+
+
+def linear_attention_chunked(q, k, v, h0=None, attention_multiplier: float = 1.0, chunk: int = CHUNK):
+    """Chunk-parallel form of :func:`linear_attention_scan`: inside a block ``Y = strict_tril(Q K^T) V + Q H``; the
+    state entering each block is an exclusive prefix sum of the blocks' ``K^T V`` - batched matmuls instead of one
+    tiny step per token."""
+    B, S, _, K = q.shape
+    V = v.size(-1)
+    N = max(q.size(2), k.size(2), v.size(2))
+    q, k, v = _rep(q, N, 2), _rep(k, N, 2), _rep(v, N, 2)
+    pad = (chunk - S % chunk) % chunk
+    if pad:
+        q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+    nc = (S + pad) // chunk
+    qc = q.view(B, nc, chunk, N, K).permute(0, 3, 1, 2, 4).float()      # [B, N, nc, L, K]
+    kc = k.view(B, nc, chunk, N, K).permute(0, 3, 1, 2, 4).float()
+    vc = v.view(B, nc, chunk, N, V).permute(0, 3, 1, 2, 4).float()
+    kv = kc.transpose(-1, -2) @ vc                                       # [B, N, nc, K, V]
+    h_in = torch.cumsum(kv, dim=2) - kv                                  # state before each block (without h0)
+    if h0 is not None:
+        h_in = h_in + h0.float()[:, :, None]
+    mask = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril(-1)
+    att = (qc @ kc.transpose(-1, -2)).masked_fill(~mask, 0.0)
+    y = att @ vc + qc @ h_in
+    y = y.permute(0, 2, 3, 1, 4).reshape(B, nc * chunk, N, V)[:, :S]
+    h = h_in[:, :, -1] + kv[:, :, -1]
+    return (y * attention_multiplier).to(q.dtype), h
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: bool = True, chunk: int = CHUNK):
+    """Chunk-parallel gated delta rule (same recurrence as :func:`gated_delta_rule_scan`).  With ``G`` the cumulative
+    log-decay inside a block and ``S0`` the state entering it, the per-step corrections ``u_t`` solve the unit lower
+    triangular system ``(I + strict_tril(beta_t e^{G_t - G_i} k_t.k_i)) U = beta (V - e^{G} K S0)``, so
+    ``U = W_v - W_k S0`` with ``W_v, W_k`` computed for all blocks at once; then
+    ``Y = e^{G} Q S0 + tril(e^{G_t - G_i} q_t.k_i) U`` and ``S_end = e^{G_L} S0 + (e^{G_L - G} K)^T U``.
+    Only the short loop over blocks is sequential."""
+    B, S, N, K = q.shape
+    V = v.size(-1)
+    dtype = v.dtype
+    qf, kf, vf = q.float(), k.float(), v.float()
+    if use_qk_l2norm:
+        qf = qf / (qf.norm(dim=-1, keepdim=True) + 1e-6)
+        kf = kf / (kf.norm(dim=-1, keepdim=True) + 1e-6)
+    qf = qf * (K**-0.5 if scale is None else scale)
+    gf, bf = g.float(), beta.float()
+    pad = (chunk - S % chunk) % chunk
+    if pad:   # padded steps: no decay (g = 0), no write (beta = 0)
+        qf, kf, vf = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (qf, kf, vf))
+        gf, bf = (torch.nn.functional.pad(t, (0, 0, 0, pad)) for t in (gf, bf))
+    nc, L = (S + pad) // chunk, chunk
+
+    def blocks(t):   # [B, S, N, X] -> [B, N, nc, L, X]
+        return t.view(B, nc, L, N, -1).permute(0, 3, 1, 2, 4)
+
+    qc, kc, vc = blocks(qf), blocks(kf), blocks(vf)
+    G = torch.cumsum(gf.view(B, nc, L, N).permute(0, 3, 1, 2), dim=-1)    # [B, N, nc, L]
+    bc = bf.view(B, nc, L, N).permute(0, 3, 1, 2)
+    diff = G[..., :, None] - G[..., None, :]                               # G_t - G_i
+    strict = torch.ones(L, L, dtype=torch.bool, device=q.device).tril(-1)
+    incl = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+    decay_strict = torch.exp(diff.masked_fill(~strict, float("-inf")))
+    decay_incl = torch.exp(diff.masked_fill(~incl, float("-inf")))
+    T = torch.eye(L, device=q.device) + bc[..., :, None] * decay_strict * (kc @ kc.transpose(-1, -2))
+    rhs = torch.cat((bc[..., None] * vc, (bc * torch.exp(G))[..., None] * kc), dim=-1)
+    W = torch.linalg.solve_triangular(T, rhs, upper=False, unitriangular=True)
+    Wv, Wk = W[..., :V], W[..., V:]                                        # [.., L, V], [.., L, K]
+    qk = decay_incl * (qc @ kc.transpose(-1, -2))                          # [.., L(t), L(i)]
+    eG = torch.exp(G)[..., None]
+    k_end = torch.exp(G[..., -1:, None] - G[..., None]) * kc               # e^{G_L - G_i} k_i
+    h = torch.zeros(B, N, K, V, dtype=torch.float32, device=q.device) if h0 is None else h0.float()
+    ys = []
+    for c in range(nc):
+        U = Wv[:, :, c] - Wk[:, :, c] @ h                                  # [B, N, L, V]
+        ys.append((eG[:, :, c] * qc[:, :, c]) @ h + qk[:, :, c] @ U)
+        h = torch.exp(G[:, :, c, -1])[..., None, None] * h + k_end[:, :, c].transpose(-1, -2) @ U
+    y = torch.stack(ys, dim=2).permute(0, 2, 3, 1, 4).reshape(B, nc * L, N, V)[:, :S]
+    return y.to(dtype), h
+
+
 def linear_attention_scan(q, k, v, h0=None, attention_multiplier: float = 1.0):
     """``y_t = q_t . h_{t-1}`` (state read before the update), ``h_t = h_{t-1} + k_t (x) v_t``; fp32 state."""
     B, S, _, K = q.shape
@@ -105,3 +185,16 @@ def gated_delta_rule_scan(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: 
         h = h + kf[:, s, :, :, None] * d[:, :, None, :]
         ys.append(torch.einsum("bnkv,bnk->bnv", h, qf[:, s]))
     return torch.stack(ys, dim=1).to(dtype), h
+
+
+def linear_attention(q, k, v, h0=None, attention_multiplier: float = 1.0):
+    """Token recurrence for short inputs (decode), chunk-parallel form otherwise."""
+    if q.size(1) < 8:
+        return linear_attention_scan(q, k, v, h0, attention_multiplier)
+    return linear_attention_chunked(q, k, v, h0, attention_multiplier)
+
+
+def gated_delta_rule(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: bool = True):
+    if q.size(1) < 8:
+        return gated_delta_rule_scan(q, k, v, g, beta, scale, h0, use_qk_l2norm)
+    return gated_delta_rule_chunked(q, k, v, g, beta, scale, h0, use_qk_l2norm)

@@ -1,0 +1,104 @@
+"""ZeRO-3 on 2 GPUs (copy-engine parameter all-gather over symmetric memory, NCCL reduce-scatter, and the opt-in
+copy-engine reduce-scatter) against the same global batch on 1 GPU: per-step mean loss and global gradient norm."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q, reduce_mode, total_mbs, steps):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LME_REDUCE_SCATTER=reduce_mode)
+    try:
+        import torch.distributed as dist
+
+        from lm_engine_b200.distributed import shard_model
+        from lm_engine_b200.enums import GradientCheckpointingMethod
+        from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+        from lm_engine_b200.models import dense_config
+        from lm_engine_b200.ops import _lib
+        from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+        from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+        ProcessGroupManager(zero_stage=3)
+        mbs = total_mbs // world
+        cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=3, num_attention_heads=4,
+                           num_key_value_heads=2, intermediate_size=1024, head_dim=64, max_position_embeddings=256)
+        w = ModelWrapperForPretraining(pretrained_config=cfg.to_dict(), micro_batch_size=mbs, sequence_length=256,
+                                       efficient_initialization=True, dtype="bf16")
+        eng = shard_model(w, stage=3, dtype=torch.bfloat16, communication_dtype=None,
+                          gradient_checkpointing_method=GradientCheckpointingMethod.block, seed=5)
+        opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95],
+                                                   "eps": 1e-10}, None, False, 1.0)
+        g = torch.Generator().manual_seed(11)
+        data = torch.randint(0, 2048, (steps, total_mbs, 257), generator=g)
+        losses, norms = [], []
+        for s in range(steps):
+            opt.zero_grad()
+            out = w(data[s, rank * mbs:(rank + 1) * mbs].cuda(), lm_loss_multiplier=1 / (mbs * 256))
+            out["loss"].backward()
+            norms.append(float(opt.step()))
+            losses.append(float(out["loss"]))
+        torch.cuda.synchronize()
+        info = {"ce_gather": eng.copy_engine_gather, "ce_reduce": eng.copy_engine_reduce}
+        q.put((rank, "ok", (losses, norms, _lib.read_status(), info)))
+        if world > 1:
+            dist.barrier()
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _run(world, reduce_mode, total_mbs=4, steps=4):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    try:
+        for _ in range(world):
+            rank, status, payload = q.get(timeout=300)
+            assert status == "ok", payload
+            res[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    return [res[r] for r in range(world)]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("reduce_mode", ["nccl", "ce"])
+def test_zero3_two_gpus_match_one_gpu(reduce_mode):
+    (ref_losses, ref_norms, ref_status, _), = _run(1, "nccl")
+    outs = _run(2, reduce_mode)
+    for losses, norms, status, info in outs:
+        assert status[0] == 0, status
+        assert info["ce_gather"] and info["ce_reduce"] == (reduce_mode == "ce")
+    mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
+    assert ref_losses[-1] < ref_losses[0]
+    for a, b in zip(mean, ref_losses):
+        assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)
+    for o in outs:
+        for a, b in zip(o[1], ref_norms):
+            assert abs(a - b) < 3e-2 * abs(b), (o[1], ref_norms)

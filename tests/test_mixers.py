@@ -127,3 +127,32 @@ def test_other_model_families_run_and_share_kv():
     assert any("h.0.kv_proj" in n for n in names) and not any("h.1.kv_proj" in n for n in names)
     m(x).logits.float().pow(2).mean().backward()
     assert all(p.grad is not None for p in m.parameters())
+
+
+@pytest.mark.parametrize("S", [1, 63, 64, 150])
+def test_chunk_parallel_forms_equal_the_token_recurrences(S):
+    from lm_engine_b200.ops.recurrence import (gated_delta_rule_chunked, gated_delta_rule_scan,
+                                               linear_attention_chunked, linear_attention_scan)
+
+    torch.manual_seed(S)
+    B, N, K, V = 2, 3, 8, 5
+    q, k = torch.randn(B, S, N, K, dtype=torch.float64), torch.randn(B, S, N, K, dtype=torch.float64)
+    v = torch.randn(B, S, N, V, dtype=torch.float64)
+    h0 = torch.randn(B, N, K, V)
+    y0, s0 = linear_attention_scan(q.float(), k.float(), v.float(), h0, 0.7)
+    y1, s1 = linear_attention_chunked(q.float(), k.float(), v.float(), h0, 0.7, chunk=64)
+    torch.testing.assert_close(y1, y0, rtol=2e-4, atol=2e-4)
+    torch.testing.assert_close(s1, s0, rtol=2e-4, atol=2e-4)
+    g = -torch.rand(B, S, N) * 0.2
+    beta = torch.rand(B, S, N)
+    a = [t.float().requires_grad_(True) for t in (q, k, v)]
+    b = [t.float().requires_grad_(True) for t in (q, k, v)]
+    y2, s2 = gated_delta_rule_scan(*a, g, beta, h0=h0)
+    y3, s3 = gated_delta_rule_chunked(*b, g, beta, h0=h0, chunk=64)
+    torch.testing.assert_close(y3, y2, rtol=3e-4, atol=3e-4)
+    torch.testing.assert_close(s3, s2, rtol=3e-4, atol=3e-4)
+    w = torch.randn_like(y2)
+    (y2 * w).sum().backward()
+    (y3 * w).sum().backward()
+    for x, y in zip(a, b):
+        torch.testing.assert_close(y.grad, x.grad, rtol=2e-3, atol=2e-3)
