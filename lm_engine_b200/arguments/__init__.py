@@ -202,6 +202,9 @@ class DistributedArgs(BaseArgs):
     use_async_tensor_parallel: bool = False
     # extension: expert-parallel world size for MoE layers (experts sharded, tokens exchanged by all-to-all)
     expert_parallel_world_size: int = 1
+    # extension: "ring" (K/V blocks around the cp ring), "ulysses" (all-to-all head exchange) or "auto" (ulysses
+    # whenever the head counts divide over the cp group, else ring)
+    context_parallel_attention: str = "auto"
 
     def model_post_init(self, _ctx: Any) -> None:
         if self.communication_dtype is not None:

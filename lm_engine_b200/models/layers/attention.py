@@ -144,6 +144,13 @@ class SoftmaxAttention(nn.Module):
 
         dropout = self.softmax_dropout_p if self.training else 0.0
         if ProcessGroupManager.is_context_parallel_enabled():
+            from ...parallel.ulysses import ulysses_attention, ulysses_eligible
+
+            how = ProcessGroupManager.get_context_parallel_attention()
+            cp = ProcessGroupManager.get_context_parallel_world_size()
+            if how == "ulysses" or (how == "auto" and ulysses_eligible(q.size(-2), k.size(-2), cp)):
+                return ulysses_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
+                                         sliding_window=self.sliding_window, dropout_p=dropout)
             return ring_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
                                   sliding_window=self.sliding_window)
         if packed:

@@ -34,6 +34,7 @@ class _State:
         self.groups: dict[str, Any] = {}
         self.cpu_group = None
         self.cp_lb: ContextParallelLoadBalancerMethod | None = None
+        self.cp_attention: str = "auto"
         self.async_tp = False
         self.dummy_rank: dict[str, int] = {}
         self.dummy_size: dict[str, int] = {}
@@ -57,6 +58,7 @@ class ProcessGroupManager:
         timeout_minutes: int | None = None,
         use_async_tensor_parallel: bool = False,
         expert_parallel_world_size: int = 1,
+        context_parallel_attention: str = "auto",
     ) -> None:
         _S.reset()
         rank = int(os.environ.get("RANK", "0"))
@@ -64,6 +66,8 @@ class ProcessGroupManager:
         world = int(os.environ.get("WORLD_SIZE", "1"))
         _S.rank, _S.local_rank = rank, local_rank
         _S.cp_lb = context_parallel_load_balancing_method
+        assert context_parallel_attention in ("auto", "ring", "ulysses")
+        _S.cp_attention = context_parallel_attention
         _S.async_tp = use_async_tensor_parallel
         Accelerator.set_device(local_rank)
         # optional cap on the SMs NCCL may take while its collectives overlap the persistent GEMM kernels (the GEMMs
@@ -290,6 +294,10 @@ class ProcessGroupManager:
     @staticmethod
     def get_context_parallel_load_balancing_method() -> ContextParallelLoadBalancerMethod | None:
         return _S.cp_lb
+
+    @staticmethod
+    def get_context_parallel_attention() -> str:
+        return _S.cp_attention
 
     # ------------------------------------------------------------------ expert parallel (extension)
     @staticmethod

@@ -234,7 +234,8 @@ def main(args_class: type[TrainingArgs | DistillationArgs] = TrainingArgs) -> No
         context_parallel_load_balancing_method=d.context_parallel_load_balancing_method,
         zero_stage=d.stage, timeout_minutes=d.timeout_minutes,
         use_async_tensor_parallel=d.use_async_tensor_parallel,
-        expert_parallel_world_size=d.expert_parallel_world_size)
+        expert_parallel_world_size=d.expert_parallel_world_size,
+        context_parallel_attention=d.context_parallel_attention)
     args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
     Accelerator.set_seed(args.random_args.seed)
     model_container = get_model_container(args, efficient_initialization=None, keep_in_fp32=True)

@@ -79,13 +79,16 @@ CASES = [
     ("dense", {"tensor_parallel_world_size": 2}, False),
     ("dense", {"tensor_parallel_world_size": 2}, True),
     ("bias", {"tensor_parallel_world_size": 2}, True),
-    ("dense", {"context_parallel_world_size": 2}, False),
+    ("dense", {"context_parallel_world_size": 2, "context_parallel_attention": "ring"}, False),
+    ("dense", {"context_parallel_world_size": 2, "context_parallel_attention": "ulysses"}, False),
+    ("dense", {"context_parallel_world_size": 2, "context_parallel_attention": "ulysses",
+               "context_parallel_load_balancing_method": "headtail"}, False),
     ("moe", {"expert_parallel_world_size": 2}, False),
     ("moe", {"tensor_parallel_world_size": 2}, False),
 ]
 
 
-@pytest.mark.parametrize("kind,topo,sp", CASES, ids=["tp2", "tp2-sp", "tp2-sp-bias", "cp2", "ep2", "moe-tp2"])
+@pytest.mark.parametrize("kind,topo,sp", CASES, ids=["tp2", "tp2-sp", "tp2-sp-bias", "cp2-ring", "cp2-ulysses", "cp2-ulysses-headtail", "ep2", "moe-tp2"])
 def test_parallel_training_matches_single_process(kind, topo, sp, tmp_path):
     steps, total_mbs = 3, 2
     d, (ref_loss, ref_norm, _) = _reference(kind, tmp_path, steps, total_mbs)
@@ -99,3 +102,31 @@ def test_parallel_training_matches_single_process(kind, topo, sp, tmp_path):
     np.testing.assert_allclose(loss, ref_loss, rtol=2e-4)
     for o in outs:
         np.testing.assert_allclose(o[1], ref_norm, rtol=2e-3)
+
+
+def _ulysses_rank(rank, world, method):
+    from lm_engine_b200.ops import attention
+    from lm_engine_b200.parallel.context_parallel import shard_indices
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+    from lm_engine_b200.parallel.ulysses import ulysses_attention
+
+    ProcessGroupManager(context_parallel_world_size=world, context_parallel_load_balancing_method=method)
+    g = torch.Generator().manual_seed(3)
+    B, S, Hq, Hkv, D = 2, 32, 8, 2, 16          # 2 K/V heads over 4 ranks: each K/V head is replicated twice
+    q, k, v, do = (torch.randn(B, S, h, D, generator=g, dtype=torch.float64) for h in (Hq, Hkv, Hkv, Hq))
+    full = [t.clone().requires_grad_() for t in (q, k, v)]
+    ref = attention(*full, causal=True)
+    ref.backward(do)
+    idx = shard_indices(S, world, rank, method)
+    loc = [t[:, idx].clone().requires_grad_() for t in (q, k, v)]
+    out = ulysses_attention(*loc, causal=True)
+    out.backward(do[:, idx])
+    torch.testing.assert_close(out, ref[:, idx].detach(), rtol=1e-9, atol=1e-9)
+    for a, b in zip(loc, full):
+        torch.testing.assert_close(a.grad, b.grad[:, idx], rtol=1e-9, atol=1e-9)
+    return True
+
+
+@pytest.mark.parametrize("method", [None, "headtail"])
+def test_ulysses_attention_replicated_kv_heads(method):
+    assert all(run_distributed(_ulysses_rank, 4, method))
