@@ -107,6 +107,57 @@ int lme_reduce_slices(const void* const* src, int nsrc, void* out, long long n, 
 int lme_ssd_decay_matrix(const void* cb, const float* cum, void* m, long long BC, int N, int G, int L, void* stream);
 int lme_ssd_dcb(const void* dm, const float* cum, void* dcb, long long BC, int N, int G, int L, void* stream);
 
+// Matrix-state RNN scan (kernels/m2rnn.cu).  q/k [B,S,Nq|Nk,K] and v [B,S,Nv,V] are bf16 with element strides
+// *_b (batch) and *_t (token), the K (V) values of a head contiguous; f fp32 [B,S,Nf]; W bf16 [Nw,V,V]; every head
+// count divides N and operand heads are shared by consecutive groups of N / count heads.  K % 16 == 0, V in
+// {16, 32, 64}, all bases and strides 16-byte aligned.  RB = K / 16.
+//   mode 0 forward : y_part fp32 [RB,B,S,N,V] (sum over RB = y), h_out fp32 [B,N,K,V], optional h0 (same shape),
+//                    optional ckpt fp32 [B,N,ceil(S/seg_len),K,V] = state before each segment
+//   mode 1 replay  : steps t0 .. t0+T-1 from ckpt[t0 / seg_len]; writes hprev, z bf16 [B,N,Tcap,K,V]
+//   mode 2 backward: steps t0+T-1 .. t0; reads hprev, z (overwritten with da), dy bf16 [B,S,N,V], dh fp32 [B,N,K,V]
+//                    (in: gradient of the state after step t0+T-1, out: before step t0); writes dq, dk fp32
+//                    [B,S,N,K], dv_part fp32 [RB,B,S,N,V], df_part fp32 [RB,B,S,N]; clip > 0 clamps dh every step
+typedef struct LmeM2rnnArgs {
+    const void *q, *k, *v;
+    const float* f;
+    const void* W;
+    long long q_b, q_t, k_b, k_t, v_b, v_t;
+    int B, S, N, K, V, Nq, Nk, Nv, Nf, Nw;
+    const float* h0;
+    float* h_out;
+    float* y_part;
+    float* ckpt;
+    int seg_len, t0, T, Tcap;
+    void *hprev, *z;
+    const void* dy;
+    float *dh, *dq, *dk, *dv_part, *df_part;
+    float clip;
+} LmeM2rnnArgs;
+int lme_m2rnn(const LmeM2rnnArgs* args, int mode, void* stream);
+
+// Vector-state RNN / GRU scans (kernels/rnn.cu), state h [B,N,H] per (batch, head), H in {16, 32} (RNN also 64):
+//   RNN: h_t = tanh(h_{t-1} W + x_t)
+//   GRU: f = sigmoid(h_{t-1} Wf + xf_t), r = sigmoid(h_{t-1} Wr + xr_t), z = tanh((h_{t-1} * r) W + x_t),
+//        h_t = f h_{t-1} + (1 - f) z
+// x* bf16 [B,S,Nx*,H] with element strides *_b / *_t (16-byte aligned), W* bf16 [Nw*,H,H], h0 bf16 [B,N,H] (never
+// null: zeros for a fresh state), y bf16 [B,S,N,H] (= every state, so the last step is the final state).
+//   mode 0 forward ; mode 1 backward: reads y, dy bf16 [B,S,N,H] and dh fp32 [B,N,H] (in: gradient of the final
+//   state, out: of h0); writes dx (, dxf, dxr, hr = h_{t-1} * r) bf16 [B,S,N,H]; the weight gradients are
+//   sum_t h_{t-1}^T dx_t etc., left to batched GEMMs.  clip > 0 clamps the state gradient at every step.
+typedef struct LmeRnnArgs {
+    const void *x, *xf, *xr;
+    const void *W, *Wf, *Wr;
+    long long x_b, x_t, xf_b, xf_t, xr_b, xr_t;
+    int B, S, N, H, Nx, Nxf, Nxr, Nw, Nwf, Nwr, gru, pad_;
+    const void* h0;
+    void* y;
+    const void* dy;
+    float* dh;
+    void *dx, *dxf, *dxr, *hr;
+    float clip;
+} LmeRnnArgs;
+int lme_rnn(const LmeRnnArgs* args, int mode, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

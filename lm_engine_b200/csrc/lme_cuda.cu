@@ -7,4 +7,6 @@
 #include "kernels/moe.cu"
 #include "kernels/conv1d.cu"
 #include "kernels/ssd.cu"
+#include "kernels/m2rnn.cu"
+#include "kernels/rnn.cu"
 #include "kernels/noalloc.cu"

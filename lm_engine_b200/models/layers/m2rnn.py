@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ...ops.recurrence import m2rnn_scan
+from ...ops.recurrence import m2rnn
 from ...parallel.manager import ProcessGroupManager
 from ...parallel.sequence_pipeline import sequence_pipeline
 from ...parameter import (
@@ -101,10 +101,10 @@ class M2RNN(nn.Module):
         v = v.view(B, S, self.num_v_heads, self.v_head_dim)
 
         def scan(t, st):
-            return m2rnn_scan(t[0], t[1], t[2], t[3], self.state_weight, st, self.gradient_clipping)
+            return m2rnn(t[0], t[1], t[2], t[3], self.state_weight, st, self.gradient_clipping)
 
         if cp:
-            y, h = sequence_pipeline(lambda q_, k_, v_, f_, W_, h0: m2rnn_scan(q_, k_, v_, f_, W_, h0,
+            y, h = sequence_pipeline(lambda q_, k_, v_, f_, W_, h0: m2rnn(q_, k_, v_, f_, W_, h0,
                                                                                  self.gradient_clipping),
                                      (q, k, v, f, self.state_weight),
                                      (B, self.num_heads, self.k_head_dim, self.v_head_dim))

@@ -73,6 +73,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_reduce_slices": [P, I, P, L, I, F, I, P],
             "lme_ssd_decay_matrix": [P, P, P, L, I, I, I, P],
             "lme_ssd_dcb": [P, P, P, L, I, I, I, P],
+            "lme_m2rnn": [P, I, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

@@ -198,3 +198,12 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: bool 
     if q.size(1) < 8:
         return gated_delta_rule_scan(q, k, v, g, beta, scale, h0, use_qk_l2norm)
     return gated_delta_rule_chunked(q, k, v, g, beta, scale, h0, use_qk_l2norm)
+
+
+def m2rnn(q, k, v, f, W, h0=None, gradient_clipping=None):
+    """Matrix-state RNN: the CUDA scan when the operands qualify, else :func:`m2rnn_scan`."""
+    from .m2rnn import m2rnn_cuda, m2rnn_kernel_eligible
+
+    if m2rnn_kernel_eligible(q, k, v, f, W):
+        return m2rnn_cuda(q, k, v, f, W, h0, gradient_clipping)
+    return m2rnn_scan(q, k, v, f, W, h0, gradient_clipping)

@@ -33,7 +33,7 @@ def _group_mm(a: torch.Tensor, b: torch.Tensor, lowp: bool) -> torch.Tensor:
     lead = a.shape[:-2]
     a2, b2 = a.reshape(-1, *a.shape[-2:]), b.reshape(-1, *b.shape[-2:])
     if lowp:
-        out = _bmm_f32(a2.to(torch.bfloat16).contiguous(), b2.to(torch.bfloat16).contiguous())
+        out = _BmmF32.apply(a2.to(torch.bfloat16).contiguous(), b2.to(torch.bfloat16).contiguous())
     else:
         out = torch.bmm(a2.float(), b2.float())
     return out.view(*lead, a.size(-2), b.size(-1))
@@ -45,6 +45,23 @@ def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         return torch.bmm(a, b, out_dtype=torch.float32)
     except (TypeError, RuntimeError):
         return torch.bmm(a, b).float()
+
+
+class _BmmF32(torch.autograd.Function):
+    """:func:`_bmm_f32` with its derivative (the ``out_dtype`` form of ``bmm`` has none registered)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return _bmm_f32(a, b)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        g = g.to(torch.bfloat16)
+        da = torch.bmm(g, b.transpose(1, 2)) if ctx.needs_input_grad[0] else None
+        db = torch.bmm(a.transpose(1, 2), g) if ctx.needs_input_grad[1] else None
+        return da, db
 
 
 class _IntraChunk(torch.autograd.Function):
