@@ -35,11 +35,16 @@ MODELS = {
     "moe-64e": (32000, 16, 2048, 16, 4, 128, 1024, 10000),
     # hybrid: three Mamba-2 (SSD) layers per softmax-attention layer (see HYBRID), no positional embedding
     "hybrid-mamba2": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
+    # hybrid: three matrix-state RNN layers per softmax-attention layer (see M2RNN_HYBRID)
+    "hybrid-m2rnn": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
 }
 # name: (experts, experts per token, shared expert intermediate size or None, router aux-loss coefficient)
 MOE = {"moe-64e": (64, 8, None, 0.01)}
 # name: (attention every n-th layer, state size, SSM heads, conv kernel, chunk size)
 HYBRID = {"hybrid-mamba2": (4, 128, 64, 4, 256)}
+# name: (attention every n-th layer, k head dim, v head dim, heads, conv kernel): one q / k head shared by all value
+# heads, the layout of the published M2RNN hybrids
+M2RNN_HYBRID = {"hybrid-m2rnn": (4, 64, 16, 64, 4)}
 
 
 LAYERS_OVERRIDE: int | None = None   # --layers: same per-layer shapes with fewer layers (profiling captures only)
@@ -53,7 +58,7 @@ def model_config(name: str, seq: int) -> dict:
         "model_type": "gpt_base", "vocab_size": v, "max_position_embeddings": seq, "hidden_size": h,
         "num_layers": L, "normalization_function": "rmsnorm", "layer_norm_epsilon": 1e-5,
         "initializer_range": 0.02, "bos_token_id": 0, "eos_token_id": 1, "pad_token_id": 2,
-        "position_embedding_type": "nope" if name in HYBRID else "rope", "rope_theta": theta, "rope_scaling": None, "m_emb": None,
+        "position_embedding_type": "nope" if name in HYBRID or name in M2RNN_HYBRID else "rope", "rope_theta": theta, "rope_scaling": None, "m_emb": None,
         "m_width": None, "m_residual": None, "init_method": "normal", "embedding_init_method": "normal",
         "use_depth_scaled_init": False, "tie_word_embeddings": False,
         "sequence_mixer_blocks": [_mixer_block(name, i, h, nh, nkv, hd) for i in range(L)],
@@ -68,6 +73,12 @@ def _mixer_block(name: str, i: int, h: int, nh: int, nkv: int, hd: int) -> dict:
         return {"sequence_mixer_type": "mamba2", "state_size": state, "intermediate_size": 2 * h, "num_heads": heads,
                 "conv_kernel_size": conv, "add_bias": False, "use_conv_bias": True, "num_groups": 1,
                 "chunk_size": chunk, "activation_function": "silu", "normalization_function": "rmsnorm"}
+    if name in M2RNN_HYBRID and (i + 1) % M2RNN_HYBRID[name][0] != 0:
+        _, kd, vd, heads, conv = M2RNN_HYBRID[name]
+        return {"sequence_mixer_type": "m2rnn", "k_head_dim": kd, "v_head_dim": vd, "num_q_heads": 1,
+                "num_k_heads": 1, "num_v_heads": heads, "num_f_heads": heads, "num_g_heads": heads,
+                "num_weight_heads": heads, "kernel_size": conv, "add_bias": False, "use_residual": True,
+                "activation_function": "silu", "gradient_clipping": 1.0, "normalization_function": "rmsnorm"}
     return {"sequence_mixer_type": "softmax_attention", "num_attention_heads": nh, "num_key_value_heads": nkv,
             "head_dim": hd}
 

@@ -158,6 +158,20 @@ typedef struct LmeRnnArgs {
 } LmeRnnArgs;
 int lme_rnn(const LmeRnnArgs* args, int mode, void* stream);
 
+// Row movers (kernels/rows.cu); H % 8 == 0 / row_bytes % 16 == 0, 16-byte aligned bases.
+//   embedding_fwd: out[t,:] = lo <= ids[t] < hi ? W[ids[t]-lo,:] : 0 (bf16 rows of H values)
+//   embedding_bwd: dW[v-lo,:] = sum of dy[t,:] over tokens with id v; sorted_ids ascending with order[j] the token of
+//                  sorted position j; dW must be zero on entry (rows without tokens are not touched)
+//   pack_rows / unpack_rows: left-padded [B,S,row] <-> packed [T,row] by cu_seqlens (int32 [B+1]); unpack zero-fills
+int lme_embedding_fwd(const long long* ids, const void* W, void* out, long long T, int H, long long lo, long long hi,
+                      void* stream);
+int lme_embedding_bwd(const long long* sorted_ids, const long long* order, const void* dy, void* dW, long long T,
+                      int H, long long lo, long long hi, void* stream);
+int lme_pack_rows(const void* x, const int* cu_seqlens, void* out, int B, int S, long long T, long long row_bytes,
+                  void* stream);
+int lme_unpack_rows(const void* packed, const int* cu_seqlens, void* x, int B, int S, long long row_bytes,
+                    void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

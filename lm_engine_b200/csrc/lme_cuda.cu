@@ -9,4 +9,5 @@
 #include "kernels/ssd.cu"
 #include "kernels/m2rnn.cu"
 #include "kernels/rnn.cu"
+#include "kernels/rows.cu"
 #include "kernels/noalloc.cu"

@@ -54,11 +54,11 @@ class ParameterizedEmbedding(nn.Module):
         mark_parameter_as_initialized(self.weight)
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        from ...ops.embedding import embedding
+
         if self.tp_world_size == 1:
-            return F.embedding(input_ids, self.weight)
-        inside = (input_ids >= self.vocab_start) & (input_ids < self.vocab_end)
-        local = (input_ids - self.vocab_start).masked_fill(~inside, 0)
-        x = F.embedding(local, self.weight) * inside.unsqueeze(-1).to(self.weight.dtype)
+            return embedding(input_ids, self.weight) if self.weight.is_cuda else F.embedding(input_ids, self.weight)
+        x = embedding(input_ids, self.weight, self.vocab_start, self.vocab_end)
         if self.sequence_parallel:
             return tp_comm.scatter_to_sequence_parallel(x, tp_comm.seq_dim(x, self.use_padding_free_transformer))
         return tp_comm.reduce_from_tensor_parallel(x)

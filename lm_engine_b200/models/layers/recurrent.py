@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ...ops.recurrence import gru_scan, rnn_scan
+from ...ops.recurrence import gru, rnn
 from ...parameter import (
     mark_parameter_as_initialized,
     mark_parameter_as_mup_learning_rate,
@@ -117,7 +117,7 @@ class RNN(_RecurrentBase):
         xi, g = self.input_projection(x).split((self.x_shape, self.g_shape), dim=-1)
         xi, c = self._input_branch(xi, c, mask, cache_params is not None)
         xi = xi.view(*xi.shape[:-1], -1, self.state_head_dim)
-        y, h = run_per_sample(lambda t, st: rnn_scan(t[0], self.state_weight, st, self.gradient_clipping), mask,
+        y, h = run_per_sample(lambda t, st: rnn(t[0], self.state_weight, st, self.gradient_clipping), mask,
                               [xi], h)
         return self._finish(y, g, c, h, S, cache_params)
 
@@ -152,6 +152,6 @@ class GRU(_RecurrentBase):
         d = self.state_head_dim
         xi, xf, xr = (t.view(*t.shape[:-1], -1, d) for t in (xi, xf, xr))
         W, Wf, Wr = self.state_weight.split(self.weight_heads, dim=0)
-        y, h = run_per_sample(lambda t, st: gru_scan(t[0], t[1], t[2], W, Wf, Wr, st, self.gradient_clipping), mask,
+        y, h = run_per_sample(lambda t, st: gru(t[0], t[1], t[2], W, Wf, Wr, st, self.gradient_clipping), mask,
                               [xi, xf, xr], h)
         return self._finish(y, g, c, h, S, cache_params)

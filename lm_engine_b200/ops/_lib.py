@@ -74,6 +74,11 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_ssd_decay_matrix": [P, P, P, L, I, I, I, P],
             "lme_ssd_dcb": [P, P, P, L, I, I, I, P],
             "lme_m2rnn": [P, I, P],
+            "lme_rnn": [P, I, P],
+            "lme_embedding_fwd": [P, P, P, L, I, L, L, P],
+            "lme_embedding_bwd": [P, P, P, P, L, I, L, L, P],
+            "lme_pack_rows": [P, P, P, I, I, L, L, P],
+            "lme_unpack_rows": [P, P, P, I, I, L, P],
             "lme_fp8_amax": [P, L, P, P],
             "lme_fp8_quantize": [P, I, I, L, P, I, P, L, P, L, P, P],
             "lme_read_status": [P, I],

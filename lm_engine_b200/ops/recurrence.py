@@ -207,3 +207,21 @@ def m2rnn(q, k, v, f, W, h0=None, gradient_clipping=None):
     if m2rnn_kernel_eligible(q, k, v, f, W):
         return m2rnn_cuda(q, k, v, f, W, h0, gradient_clipping)
     return m2rnn_scan(q, k, v, f, W, h0, gradient_clipping)
+
+
+def rnn(x, W, h0=None, gradient_clipping=None):
+    """Multi-head tanh RNN: the CUDA scan when the operands qualify, else :func:`rnn_scan`."""
+    from .rnn import rnn_cuda, rnn_kernel_eligible
+
+    if rnn_kernel_eligible(x):
+        return rnn_cuda(x, W, h0, gradient_clipping)
+    return rnn_scan(x, W, h0, gradient_clipping)
+
+
+def gru(x, xf, xr, W, Wf, Wr, h0=None, gradient_clipping=None):
+    """Multi-head GRU: the CUDA scan when the operands qualify, else :func:`gru_scan`."""
+    from .rnn import gru_cuda, rnn_kernel_eligible
+
+    if rnn_kernel_eligible(x, xf, xr, gru=True):
+        return gru_cuda(x, xf, xr, W, Wf, Wr, h0, gradient_clipping)
+    return gru_scan(x, xf, xr, W, Wf, Wr, h0, gradient_clipping)
