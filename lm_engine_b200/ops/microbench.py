@@ -161,8 +161,68 @@ def bench_elementwise(peaks: dict, small: bool = False) -> list[dict]:
     return rows
 
 
+def bench_recurrent(small: bool = False) -> list[dict]:
+    """Scan kernels at training shapes: ms per call and ns per time step (the scans are latency chains, so time per
+    step is the figure of merit), plus the PyTorch time loop on a 128-step prefix for scale."""
+    from . import m2rnn as m2op
+    from . import rnn as rnnop
+    from .recurrence import gru_scan, m2rnn_scan, rnn_scan
+
+    dev, bf = "cuda", torch.bfloat16
+    B, S = 2, (512 if small else 4096)
+    rows = []
+
+    def add(name, make, ref):
+        args = make(S)
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                a.requires_grad_(True)
+        fwd = _time(lambda i: make_call(name, args), 1, iters=5, warmup=2)
+
+        def both(i):
+            y, h = make_call(name, args)
+            y.backward(torch.ones_like(y))
+
+        tot = _time(both, 1, iters=5, warmup=2)
+        short = tuple(a.to(bf) if isinstance(a, torch.Tensor) else a for a in make(128))
+        loop = _time(lambda i: ref(*short), 1, iters=2, warmup=1)
+        rows.append({"name": name, "S": S, "fwd_ms": fwd * 1e3, "fwd_bwd_ms": tot * 1e3,
+                     "fwd_ns_per_step": fwd * 1e9 / S, "torch_loop_fwd_ms_at_128_steps": loop * 1e3})
+        print(f"{name:34s} S={S}  fwd {fwd * 1e3:7.3f} ms ({fwd * 1e9 / S:6.0f} ns/step)  fwd+bwd {tot * 1e3:7.3f} ms"
+              f"   PyTorch loop fwd, 128 steps: {loop * 1e3:7.2f} ms", flush=True)
+
+    def make_call(name, args):
+        if name.startswith("m2rnn"):
+            return m2op.m2rnn_cuda(*args)
+        if name.startswith("gru"):
+            return rnnop.gru_cuda(*args)
+        return rnnop.rnn_cuda(*args)
+
+    def m2(N, K, V, shared):
+        def make(s):
+            nq = 1 if shared else N
+            return (torch.randn(B, s, nq, K, device=dev).to(bf) * 0.5, torch.randn(B, s, nq, K, device=dev).to(bf) * 0.5,
+                    torch.randn(B, s, N, V, device=dev).to(bf), torch.sigmoid(torch.randn(B, s, N, device=dev) + 2),
+                    (torch.eye(V, device=dev) + 0.05 * torch.randn(N, V, V, device=dev)).to(bf), None, 1.0)
+        return make
+
+    def vec(N, H, gates):
+        def make(s):
+            xs = [torch.randn(B, s, N, H, device=dev).to(bf) for _ in range(gates)]
+            ws = [(torch.randn(N, H, H, device=dev) / H ** 0.5).to(bf) for _ in range(gates)]
+            return (*xs, *ws, None, 1.0)
+        return make
+
+    add("m2rnn K=64 V=16 N=132 (shared q,k)", m2(132, 64, 16, True), m2rnn_scan)
+    add("m2rnn K=64 V=64 N=32", m2(32, 64, 64, False), m2rnn_scan)
+    add("rnn H=16 N=128", vec(128, 16, 1), rnn_scan)
+    add("gru H=16 N=128", vec(128, 16, 3), gru_scan)
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--recurrent", action="store_true", help="time the RNN-family scan kernels instead")
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--sustained", action="store_true", help="time ~1.5 s back-to-back loops (power-limited clocks)")
@@ -173,6 +233,13 @@ def main():
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
     args = ap.parse_args()
     peaks = _peaks()
+    if args.recurrent:
+        rows = bench_recurrent(small=args.small)
+        st = _lib.read_status()
+        print("device status:", st)
+        if args.json:
+            json.dump({"recurrent": rows, "status": st}, open(args.json, "w"), indent=1)
+        return
     if args.elementwise:
         rows = bench_elementwise(peaks, small=args.small)
         st = _lib.read_status()
