@@ -1,0 +1,307 @@
+// Flash-attention forward on tcgen05 (head dim 128, bf16, causal or full, grouped K/V heads).
+//
+// One CTA owns 128 query rows of one (batch, head) and streams the K/V sequence in tiles of 128 rows:
+//   warp 0      TMA producer   Q once; K and V tiles through a 2-stage ring (separate barriers, so S = Q K^T starts
+//                              as soon as K has landed)
+//   warp 1      MMA issuer     S_j = Q K_j^T  (128 x 128 x 128, both operands K-major, accumulator in TMEM, two S
+//                              buffers so S_{j+1} is computed while the softmax warps work on S_j), then
+//                              PV_j = P_j V_j (P from shared memory, V as an MN-major operand straight from its
+//                              [kv, d] tile - no transpose anywhere)
+//   warps 2..5  softmax        thread = query row (tcgen05.ld 32x32b hands every thread its own row, so max and sum
+//                              need no shuffles): two passes over S in TMEM (max, then exp2 / sum / bf16 P written
+//                              into the 128-byte-swizzled K-major layout the MMA expects), then O = O * alpha + PV
+//                              in registers, normalised and stored at the end with the log-sum-exp.
+// TMEM: S0 | S1 | PV = 3 x 128 fp32 columns (512 allocated).  Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB,
+// P 32 KB.  Every wait is bounded (common.cuh); a CTA that starts after an error was recorded returns at once.
+//
+// Role of flash-attn's forward kernels used by the reference (lm_engine/modeling_utils/sequence_mixer_blocks/
+// softmax_attention/utils.py flash_attention; FA2 / FA3 / FA4 selection in lm_engine/kernels.py).
+namespace lme {
+namespace attn {
+
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16, 128-byte swizzle
+constexpr int TILE_BYTES = 2 * HALF_BYTES;     // 32 KB
+constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 5 * TILE_BYTES;
+constexpr int OFF_BAR = 6 * TILE_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // barriers + slack for the 1024-byte alignment of the tiles
+constexpr uint32_t TMEM_COLS = 512;
+
+struct Args {
+    __nv_bfloat16* o;
+    float* lse;
+    long long o_ld;            // row pitch of o in elements
+    int B, S_q, S_kv, Hq, Hkv, causal;
+    float scale;               // softmax scale (natural units)
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const Args p) {
+    extern __shared__ uint8_t attn_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(attn_smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;     // [2]
+    uint64_t* v_full = bars + 3;     // [2]
+    uint64_t* kv_empty = bars + 5;   // [2]
+    uint64_t* s_full = bars + 7;     // [2]
+    uint64_t* p_full = bars + 9;
+    uint64_t* pv_full = bars + 10;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* poisoned = tmem_base_smem + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x;        // long (late) query blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int q0 = qb * BM;
+    const int shift = p.S_kv - p.S_q;                  // query row i may see keys <= i + shift
+    int n_tiles = p.S_kv / BN;
+    if (p.causal) n_tiles = min(n_tiles, (q0 + BM + shift + BN - 1) / BN);
+
+    if (threadIdx.x == 0) *poisoned = lme_status[0];
+    __syncthreads();
+    if (*poisoned != 0u || n_tiles <= 0) return;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+            mbar_init(&s_full[s], 1);
+        }
+        mbar_init(p_full, 4);        // one arrival per softmax warp
+        mbar_init(pv_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int row_q = b * p.S_q + q0;
+            mbar_expect_tx(q_full, TILE_BYTES);
+            tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
+            tma_load_2d(smem + OFF_Q + HALF_BYTES, &tmQ, q_full, h * HD + 64, row_q);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) break;
+                const int row_k = b * p.S_kv + j * BN;
+                uint8_t* ks = smem + OFF_K + s * TILE_BYTES;
+                uint8_t* vs = smem + OFF_V + s * TILE_BYTES;
+                mbar_expect_tx(&k_full[s], TILE_BYTES);
+                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, row_k);
+                tma_load_2d(ks + HALF_BYTES, &tmK, &k_full[s], hk * HD + 64, row_k);
+                mbar_expect_tx(&v_full[s], TILE_BYTES);
+                tma_load_2d(vs, &tmV, &v_full[s], hk * HD, row_k);
+                tma_load_2d(vs + HALF_BYTES, &tmV, &v_full[s], hk * HD + 64, row_k);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = make_idesc(1, 1, false, false, BM, BN);
+            const uint32_t idesc_pv = make_idesc(1, 1, false, true, BM, HD);
+            const uint32_t sq = smem_u32(smem + OFF_Q), sp = smem_u32(smem + OFF_P);
+            bool ok = mbar_wait(q_full, 0, 610);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&k_full[s], (j >> 1) & 1, 620 + s)) return false;
+                tc_fence_after();
+                const uint32_t sk = smem_u32(smem + OFF_K + s * TILE_BYTES);
+                const uint32_t d = tmem_base + s * BN;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                    umma_bf16(d, make_smem_desc_sw128(sq + off, 16, 1024), make_smem_desc_sw128(sk + off, 16, 1024),
+                              idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
+                if (!mbar_wait(p_full, j & 1, 630)) { ok = false; break; }
+                if (!mbar_wait(&v_full[s], (j >> 1) & 1, 640 + s)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sv = smem_u32(smem + OFF_V + s * TILE_BYTES);
+                const uint32_t d = tmem_base + 2 * BN;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                    umma_bf16(d, make_smem_desc_sw128(sp + a_off, 16, 1024),
+                              make_smem_desc_sw128(sv + kk * (16 * 128), HALF_BYTES, 1024), idesc_pv,
+                              kk > 0 ? 1u : 0u);
+                }
+                umma_commit(pv_full);
+                umma_commit(&kv_empty[s]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int qd = warp & 3;                      // TMEM lane quadrant this warp may access
+        const int row = qd * 32 + lane;               // query row inside the tile
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+        const float sl2 = p.scale * 1.4426950408889634f;
+        const int limit = q0 + row + shift;           // last visible key of this row (causal)
+        float m = -INFINITY, l = 0.f;
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        uint8_t* prow = smem + OFF_P + row * 128;     // this row inside a 64-column half
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            if (!mbar_wait(&s_full[s], (j >> 1) & 1, 650 + s)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t ts = lane_base + s * BN;
+            const int k0 = j * BN;
+            const bool masked = p.causal && (k0 + BN - 1 > q0 + shift);
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(ts + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float v = __uint_as_float(r[i]);
+                    if (!masked || k0 + c * 32 + i <= limit) mx = fmaxf(mx, v);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            // a row with no visible key so far keeps m = -inf; exponent offsets then use 0 to stay finite
+            const float m_off = (m_new == -INFINITY) ? 0.f : m_new * sl2;
+            const float alpha = ex2(m * sl2 - m_off);
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(ts + c * 32, r);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = ex2(__uint_as_float(r[i]) * sl2 - m_off);
+                    float p1 = ex2(__uint_as_float(r[i + 1]) * sl2 - m_off);
+                    if (masked) {
+                        if (k0 + c * 32 + i > limit) p0 = 0.f;
+                        if (k0 + c * 32 + i + 1 > limit) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    packed[i >> 1] = pack_bf16x2(p0, p1);
+                }
+                // columns c*32 .. +31 = 16-byte chunks (c & 1) * 4 .. +3 of half c >> 1, XOR-swizzled by row
+                uint8_t* half = prow + (c >> 1) * HALF_BYTES;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = ((c & 1) * 4 + q4) ^ (row & 7);
+                    *reinterpret_cast<uint4*>(half + chunk * 16) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+            if (!mbar_wait(pv_full, j & 1, 660)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_base + 2 * BN + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
+            }
+            tc_fence_before();
+        }
+        if (ok) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const long long grow = static_cast<long long>(b) * p.S_q + q0 + row;
+            __nv_bfloat16* dst = p.o + grow * p.o_ld + h * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                uint4 v;
+                v.x = pack_bf16x2(o[i] * inv, o[i + 1] * inv);
+                v.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
+                v.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
+                v.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
+                *reinterpret_cast<uint4*>(dst + i) = v;
+            }
+            if (p.lse)
+                p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S_q + q0 + row] =
+                    l > 0.f ? m * p.scale + __logf(l) : -INFINITY;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace attn
+}  // namespace lme
+
+// q [B, S_q, Hq, 128], k / v [B, S_kv, Hkv, 128] bf16 with the 128 values of a head contiguous, heads contiguous
+// inside a token, token pitch ld* elements and batches back to back (pitch S * ld); o [B, S_q, Hq, 128] bf16 with
+// token pitch ldo; lse fp32 [B, Hq, S_q] or null.  S_q and S_kv are multiples of 128; causal aligns the last query
+// with the last key.
+extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                                 long long ldv, void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq,
+                                 int Hkv, int causal, float scale, void* stream) {
+    using namespace lme::attn;
+    if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % BM || S_kv % BN || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
+    if (causal && S_kv < S_q) return LME_ERR_SHAPE;
+    if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+         reinterpret_cast<uintptr_t>(o)) & 15)
+        return LME_ERR_ALIGN;
+    if ((ldq | ldk | ldv | ldo) % 8) return LME_ERR_ALIGN;
+    CUtensorMap tq, tk, tv;
+    int rc = make_tmap_bf16_2d(&tq, q, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(B) * S_q, ldq, 64, BM);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tk, k, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldk, 64, BN);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tv, v, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldv, 64, BN);
+    if (rc) return rc;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+            return LME_ERR_LAUNCH;
+        configured = true;
+    }
+    Args p;
+    p.o = static_cast<__nv_bfloat16*>(o);
+    p.lse = lse;
+    p.o_ld = ldo;
+    p.B = B; p.S_q = S_q; p.S_kv = S_kv; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+    p.scale = scale;
+    dim3 grid(S_q / BM, Hq, B);
+    attn_fwd_kernel<<<grid, 192, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+}
