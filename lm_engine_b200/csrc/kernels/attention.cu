@@ -274,7 +274,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                                  long long ldv, void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq,
                                  int Hkv, int causal, float scale, void* stream) {
-    using namespace lme::attn;
+    using lme::attn::Args;
+    using lme::attn::HD;
+    using lme::attn::SMEM_BYTES;
+    using lme::attn::attn_fwd_kernel;
+    constexpr int BM = lme::attn::BM, BN = lme::attn::BN;
     if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % BM || S_kv % BN || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
     if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
@@ -283,11 +287,11 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
         return LME_ERR_ALIGN;
     if ((ldq | ldk | ldv | ldo) % 8) return LME_ERR_ALIGN;
     CUtensorMap tq, tk, tv;
-    int rc = make_tmap_bf16_2d(&tq, q, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(B) * S_q, ldq, 64, BM);
+    int rc = lme::make_tmap_bf16_2d(&tq, q, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(B) * S_q, ldq, 64, BM);
     if (rc) return rc;
-    rc = make_tmap_bf16_2d(&tk, k, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldk, 64, BN);
+    rc = lme::make_tmap_bf16_2d(&tk, k, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldk, 64, BN);
     if (rc) return rc;
-    rc = make_tmap_bf16_2d(&tv, v, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldv, 64, BN);
+    rc = lme::make_tmap_bf16_2d(&tv, v, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldv, 64, BN);
     if (rc) return rc;
     static bool configured = false;
     if (!configured) {

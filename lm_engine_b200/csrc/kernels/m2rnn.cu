@@ -208,6 +208,11 @@ __global__ void __launch_bounds__(32) m2rnn_fwd_kernel(const LmeM2rnnArgs p) {
         cp_commit();
     };
 
+    int next_ckpt = (!SAVE && p.ckpt) ? 0 : -1;
+    float* ckpt_ptr = p.ckpt ? p.ckpt + (static_cast<long long>(w.b) * p.N + w.n) * nseg * KV + 16 * w.rb * V : nullptr;
+    // (rb, b, t_begin, n, 0) of y_part [RB, B, S, N, V]; advanced by one token per step
+    float* y_ptr = SAVE ? nullptr : p.y_part + (((static_cast<long long>(w.rb) * p.B + w.b) * p.S + t_begin) * p.N + w.n) * V;
+    const long long y_step = static_cast<long long>(p.N) * V;
     const int nchunks = (t_end - t_begin + TC - 1) / TC;
     if (nchunks > 0) issue(0);
     for (int c = 0; c < nchunks; ++c) {
@@ -222,9 +227,11 @@ __global__ void __launch_bounds__(32) m2rnn_fwd_kernel(const LmeM2rnnArgs p) {
         for (int st = 0; st < TC; ++st) {
             const int t = t_begin + c * TC + st;
             if (t >= t_end) break;
-            if (!SAVE && p.ckpt && t % p.seg_len == 0)
-                store_state<V>(p.ckpt + ((static_cast<long long>(w.b) * p.N + w.n) * nseg + t / p.seg_len) * KV + 16 * w.rb * V,
-                               w, h);
+            if (!SAVE && t == next_ckpt) {    // t_begin = 0: snapshots at 0, seg_len, 2 seg_len, ...
+                store_state<V>(ckpt_ptr, w, h);
+                ckpt_ptr += KV;
+                next_ckpt += p.seg_len;
+            }
             const float k0 = __bfloat162float(ks[stage][st][g]), k1 = __bfloat162float(ks[stage][st][g + 8]);
             const float gt = fs[stage][st];
             uint32_t a[KS][4];
@@ -281,8 +288,8 @@ __global__ void __launch_bounds__(32) m2rnn_fwd_kernel(const LmeM2rnnArgs p) {
                 int nt_out = 0;
                 bool writer = true;
                 ColReduce<NT, 16>::run(part, lane, out, nt_out, writer);
-                if (writer)
-                    *reinterpret_cast<float2*>(p.y_part + (((static_cast<long long>(w.rb) * p.B + w.b) * p.S + t) * p.N + w.n) * V + 8 * nt_out + 2 * qd) = out;
+                if (writer) *reinterpret_cast<float2*>(y_ptr + 8 * nt_out + 2 * qd) = out;
+                y_ptr += y_step;
             }
         }
         __syncwarp();

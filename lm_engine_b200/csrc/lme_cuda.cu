@@ -10,4 +10,5 @@
 #include "kernels/m2rnn.cu"
 #include "kernels/rnn.cu"
 #include "kernels/rows.cu"
+#include "kernels/attention.cu"
 #include "kernels/noalloc.cu"

@@ -220,8 +220,36 @@ def bench_recurrent(small: bool = False) -> list[dict]:
     return rows
 
 
+def bench_attention(peaks: dict, small: bool = False) -> list[dict]:
+    """Own tcgen05 attention forward against the library (cuDNN through SDPA) forward at training shapes."""
+    import torch.nn.functional as F
+
+    from .attention_cuda import flash_attention_forward
+
+    rows = []
+    for name, B, S, Hq, Hkv in ([("1b-shape", 2, 1024, 16, 8)] if small else
+                                [("8b-shape", 2, 4096, 32, 8), ("1b-shape", 2, 4096, 16, 8), ("long", 1, 16384, 32, 8)]):
+        qkv = torch.randn(B, S, (Hq + 2 * Hkv) * 128, device="cuda").to(torch.bfloat16)
+        q, k, v = (t.view(B, S, -1, 128) for t in qkv.split((Hq * 128, Hkv * 128, Hkv * 128), dim=-1))
+        scale = 128 ** -0.5
+        flops = 4 * B * Hq * S * S * 128 / 2
+        ours = _time(lambda i: flash_attention_forward(q, k, v, causal=True, softmax_scale=scale), 1)
+        qt, kt, vt = (t.transpose(1, 2) for t in (q, k, v))
+        lib = _time(lambda i: F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, scale=scale,
+                                                             enable_gqa=True), 1)
+        r = {"name": name, "B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "ms": ours * 1e3, "tflops": flops / ours / 1e12,
+             "library_ms": lib * 1e3, "library_tflops": flops / lib / 1e12,
+             "frac_of_peak": flops / ours / 1e12 / peaks["bf16_tflops"]}
+        rows.append(r)
+        print(f"attention fwd causal {name:9s} B={B} S={S} Hq={Hq} Hkv={Hkv}: ours {r['ms']:7.3f} ms {r['tflops']:6.1f} TF "
+              f"({100 * r['frac_of_peak']:4.1f}% of {peaks['source']} GEMM peak)   library {r['library_ms']:7.3f} ms "
+              f"{r['library_tflops']:6.1f} TF", flush=True)
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--attention", action="store_true", help="time the attention forward kernel instead")
     ap.add_argument("--recurrent", action="store_true", help="time the RNN-family scan kernels instead")
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
@@ -233,6 +261,13 @@ def main():
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
     args = ap.parse_args()
     peaks = _peaks()
+    if args.attention:
+        rows = bench_attention(peaks, small=args.small)
+        st = _lib.read_status()
+        print("device status:", st)
+        if args.json:
+            json.dump({"peaks": peaks, "attention": rows, "status": st}, open(args.json, "w"), indent=1)
+        return
     if args.recurrent:
         rows = bench_recurrent(small=args.small)
         st = _lib.read_status()

@@ -1,0 +1,57 @@
+"""tcgen05 flash-attention forward against the fp32 PyTorch statement: output and log-sum-exp, causal and full,
+grouped K/V heads, operands that are strided slices of one projection output."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal", [
+    (1, 128, 1, 1, False),
+    (1, 128, 1, 1, True),
+    (2, 256, 4, 2, True),
+    (1, 512, 8, 8, False),
+    (2, 640, 6, 2, True),
+])
+@pytest.mark.parametrize("fused_qkv", [False, True])
+def test_attention_forward_matches_reference(B, S, Hq, Hkv, causal, fused_qkv):
+    from lm_engine_b200.ops import _lib
+    from lm_engine_b200.ops.attention import attention_reference
+    from lm_engine_b200.ops.attention_cuda import flash_attention_forward
+
+    torch.manual_seed(0)
+    D = 128
+    if fused_qkv:
+        qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+        q, k, v = (t.view(B, S, -1, D) for t in qkv.split((Hq * D, Hkv * D, Hkv * D), dim=-1))
+    else:
+        q = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+        k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
+        v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
+    scale = D ** -0.5
+    out, lse = flash_attention_forward(q, k, v, causal=causal, softmax_scale=scale, return_lse=True)
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    ref, ref_lse = attention_reference(q.float(), k.float(), v.float(), causal=causal, softmax_scale=scale,
+                                       return_lse=True)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lse, ref_lse.transpose(1, 2), rtol=1e-3, atol=1e-3)    # ours is [B, Hq, Sq]
+
+
+def test_dispatcher_uses_kernel_only_without_grad(monkeypatch):
+    from lm_engine_b200.ops import attention_cuda
+    from lm_engine_b200.ops.attention import attention
+
+    monkeypatch.setenv("LME_ATTENTION", "own")
+    q = torch.randn(1, 256, 2, 128, device="cuda").to(torch.bfloat16)
+    calls = []
+    real = attention_cuda.flash_attention_forward
+    monkeypatch.setattr(attention_cuda, "flash_attention_forward", lambda *a, **k: calls.append(1) or real(*a, **k))
+    with torch.no_grad():
+        a = attention(q, q, q, causal=True)
+    assert calls == [1]
+    qg = q.clone().requires_grad_(True)
+    b = attention(qg, qg, qg, causal=True)
+    assert calls == [1]                       # the gradient path stays on the library kernel
+    torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2)
