@@ -8,10 +8,12 @@
 //                              PV_j = P_j V_j (P from shared memory, V as an MN-major operand straight from its
 //                              [kv, d] tile - no transpose anywhere)
 //   warps 2..5  softmax        thread = query row (tcgen05.ld 32x32b hands every thread its own row, so max and sum
-//                              need no shuffles): two passes over S in TMEM (max, then exp2 / sum / bf16 P written
-//                              into the 128-byte-swizzled K-major layout the MMA expects), then O = O * alpha + PV
-//                              in registers, normalised and stored at the end with the log-sum-exp.
-// TMEM: S0 | S1 | PV = 3 x 128 fp32 columns (512 allocated).  Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB,
+//                              need no shuffles): one pass over S from TMEM (max, exp2, sum, bf16 P written
+//                              into the 128-byte-swizzled K-major layout the MMA expects).  O accumulates in TMEM
+//                              across tiles (the PV products add into it); the exponents are taken against a
+//                              maximum that trails the true one by at most 2^8, so the rescale of O - a TMEM
+//                              read-modify-write - runs only on the few tiles where the maximum jumps.
+// TMEM: S0 | S1 | O = 3 x 128 fp32 columns (512 allocated).  Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB,
 // P 32 KB.  Every wait is bounded (common.cuh); a CTA that starts after an error was recorded returns at once.
 //
 // Role of flash-attn's forward kernels used by the reference (lm_engine/modeling_utils/sequence_mixer_blocks/
@@ -150,7 +152,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
                     umma_bf16(d, make_smem_desc_sw128(sp + a_off, 16, 1024),
                               make_smem_desc_sw128(sv + kk * (16 * 128), HALF_BYTES, 1024), idesc_pv,
-                              kk > 0 ? 1u : 0u);
+                              (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(pv_full);
                 umma_commit(&kv_empty[s]);
@@ -161,52 +163,70 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int qd = warp & 3;                      // TMEM lane quadrant this warp may access
         const int row = qd * 32 + lane;               // query row inside the tile
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+        const uint32_t to = lane_base + 2 * BN;       // the O accumulator
         const float sl2 = p.scale * 1.4426950408889634f;
         const int limit = q0 + row + shift;           // last visible key of this row (causal)
+        // m is the maximum the exponents are taken against.  It follows the true row maximum lazily: O (in TMEM) and
+        // l are rescaled only when the maximum grew by more than 2^8, so P stays below 256 and most tiles skip the
+        // read-modify-write of O altogether.
         float m = -INFINITY, l = 0.f;
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
         uint8_t* prow = smem + OFF_P + row * 128;     // this row inside a 64-column half
         bool ok = true;
+        // every wait is voted on: the tcgen05.ld / st below are warp-collective, so the warp leaves together
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
-            if (!mbar_wait(&s_full[s], (j >> 1) & 1, 650 + s)) { ok = false; break; }
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (j >> 1) & 1, 650 + s));
+            if (!ok) break;
             tc_fence_after();
             const uint32_t ts = lane_base + s * BN;
             const int k0 = j * BN;
             const bool masked = p.causal && (k0 + BN - 1 > q0 + shift);
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, r[c]);
+            tmem_ld_wait();
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(ts + c * 32, r);
-                tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float v = __uint_as_float(r[i]);
-                    if (!masked || k0 + c * 32 + i <= limit) mx = fmaxf(mx, v);
+                    if (masked && k0 + c * 32 + i > limit) r[c][i] = 0xff800000u;   // -inf: exp2 gives 0
+                    mx = fmaxf(mx, __uint_as_float(r[c][i]));
+                }
+            const float m_new = fmaxf(m, mx);
+            if (j == 0) {
+                m = m_new;
+            } else {
+                // PV_{j-1} has to be complete before P is overwritten and before O may be touched
+                ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (j - 1) & 1, 660));
+                if (!ok) break;
+                tc_fence_after();
+                const bool need = (m_new - m) * sl2 > 8.f;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float alpha = need ? ex2((m - m_new) * sl2) : 1.f;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t t[32];
+                        tmem_ld_32x32(to + c * 32, t);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+                        tmem_st_32x32(to + c * 32, t);
+                    }
+                    tmem_st_wait();
+                    l *= alpha;
+                    if (need) m = m_new;
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            // a row with no visible key so far keeps m = -inf; exponent offsets then use 0 to stay finite
-            const float m_off = (m_new == -INFINITY) ? 0.f : m_new * sl2;
-            const float alpha = ex2(m * sl2 - m_off);
+            const float m_off = (m == -INFINITY) ? 0.f : m * sl2;
             float sum = 0.f;
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(ts + c * 32, r);
-                tmem_ld_wait();
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = ex2(__uint_as_float(r[i]) * sl2 - m_off);
-                    float p1 = ex2(__uint_as_float(r[i + 1]) * sl2 - m_off);
-                    if (masked) {
-                        if (k0 + c * 32 + i > limit) p0 = 0.f;
-                        if (k0 + c * 32 + i + 1 > limit) p1 = 0.f;
-                    }
+                    const float p0 = ex2(fmaf(__uint_as_float(r[c][i]), sl2, -m_off));
+                    const float p1 = ex2(fmaf(__uint_as_float(r[c][i + 1]), sl2, -m_off));
                     sum += p0 + p1;
                     packed[i >> 1] = pack_bf16x2(p0, p1);
                 }
@@ -219,36 +239,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                 }
             }
-            l = l * alpha + sum;
-            m = m_new;
+            l += sum;
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
-            if (!mbar_wait(pv_full, j & 1, 660)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(lane_base + 2 * BN + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
-            }
-            tc_fence_before();
         }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (n_tiles - 1) & 1, 670));
         if (ok) {
+            tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const long long grow = static_cast<long long>(b) * p.S_q + q0 + row;
             __nv_bfloat16* dst = p.o + grow * p.o_ld + h * HD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t t[32];
+                tmem_ld_32x32(to + c * 32, t);
+                tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < HD; i += 8) {
-                uint4 v;
-                v.x = pack_bf16x2(o[i] * inv, o[i + 1] * inv);
-                v.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
-                v.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
-                v.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
-                *reinterpret_cast<uint4*>(dst + i) = v;
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v;
+                    v.x = pack_bf16x2(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
+                    v.y = pack_bf16x2(__uint_as_float(t[i + 2]) * inv, __uint_as_float(t[i + 3]) * inv);
+                    v.z = pack_bf16x2(__uint_as_float(t[i + 4]) * inv, __uint_as_float(t[i + 5]) * inv);
+                    v.w = pack_bf16x2(__uint_as_float(t[i + 6]) * inv, __uint_as_float(t[i + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+                }
             }
             if (p.lse)
                 p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S_q + q0 + row] =
