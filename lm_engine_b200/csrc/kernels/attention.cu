@@ -1,33 +1,38 @@
 // Flash-attention forward on tcgen05 (head dim 128, bf16, causal or full, grouped K/V heads).
 //
-// One CTA owns 128 query rows of one (batch, head) and streams the K/V sequence in tiles of 128 rows:
+// One CTA owns 128 query rows of one (batch, head) and streams the K/V sequence in tiles of 64 rows:
 //   warp 0      TMA producer   Q once; K and V tiles through a 2-stage ring (separate barriers, so S = Q K^T starts
 //                              as soon as K has landed)
-//   warp 1      MMA issuer     S_j = Q K_j^T  (128 x 128 x 128, both operands K-major, accumulator in TMEM, two S
+//   warp 1      MMA issuer     S_j = Q K_j^T  (128 x 64 x 128, both operands K-major, accumulator in TMEM, two S
 //                              buffers so S_{j+1} is computed while the softmax warps work on S_j), then
-//                              PV_j = P_j V_j (P from shared memory, V as an MN-major operand straight from its
+//                              O += P_j V_j (P from shared memory, V as an MN-major operand straight from its
 //                              [kv, d] tile - no transpose anywhere)
 //   warps 2..5  softmax        thread = query row (tcgen05.ld 32x32b hands every thread its own row, so max and sum
 //                              need no shuffles): one pass over S from TMEM (max, exp2, sum, bf16 P written
 //                              into the 128-byte-swizzled K-major layout the MMA expects).  O accumulates in TMEM
-//                              across tiles (the PV products add into it); the exponents are taken against a
-//                              maximum that trails the true one by at most 2^8, so the rescale of O - a TMEM
-//                              read-modify-write - runs only on the few tiles where the maximum jumps.
-// TMEM: S0 | S1 | O = 3 x 128 fp32 columns (512 allocated).  Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB,
-// P 32 KB.  Every wait is bounded (common.cuh); a CTA that starts after an error was recorded returns at once.
+//                              across tiles; the exponents are taken against a maximum that trails the true one by
+//                              at most 2^8, so the rescale of O - a TMEM read-modify-write - runs only on the few
+//                              tiles where the maximum jumps.
+// TMEM: S0 | S1 (64 columns each) | O (128) = 256 columns.  Shared memory: Q 32 KB, K 2 x 16 KB, V 2 x 16 KB,
+// P 16 KB = 112 KB, so TWO CTAs share an SM (and its 512 TMEM columns): while one CTA's softmax warps keep the
+// MUFU / FMA pipes busy the other's MMAs and loads proceed.  Every wait is bounded (common.cuh); a CTA that starts
+// after an error was recorded returns at once.
 //
 // Role of flash-attn's forward kernels used by the reference (lm_engine/modeling_utils/sequence_mixer_blocks/
 // softmax_attention/utils.py flash_attention; FA2 / FA3 / FA4 selection in lm_engine/kernels.py).
 namespace lme {
 namespace attn {
 
-constexpr int BM = 128, BN = 128, HD = 128;
-constexpr int HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16, 128-byte swizzle
-constexpr int TILE_BYTES = 2 * HALF_BYTES;     // 32 KB
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 5 * TILE_BYTES;
-constexpr int OFF_BAR = 6 * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // barriers + slack for the 1024-byte alignment of the tiles
-constexpr uint32_t TMEM_COLS = 512;
+constexpr int BM = 128, BN = 64, HD = 128;
+constexpr int Q_HALF = BM * 128;               // 128 rows x 64 bf16 (one 128-byte swizzled half of the head dim)
+constexpr int KV_HALF = BN * 128;              // 64 rows x 64 bf16
+constexpr int Q_BYTES = 2 * Q_HALF, KV_BYTES = 2 * KV_HALF, P_BYTES = BM * BN * 2;
+constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
+constexpr int OFF_BAR = OFF_P + P_BYTES;
+// 112 KB of tiles + barriers: two CTAs share an SM, so the softmax of one overlaps the other's MMAs and waits
+constexpr int SMEM_BYTES = OFF_BAR + 128;
+constexpr uint32_t TMEM_COLS = 256;            // S0 | S1 (64 columns each) | O (128)
+constexpr uint32_t TM_S = 0, TM_O = 128;
 
 struct Args {
     __nv_bfloat16* o;
@@ -43,11 +48,10 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const Args p) {
-    extern __shared__ uint8_t attn_smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(attn_smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];      // the swizzled tiles need 1024-byte alignment (checked)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;     // [2]
@@ -57,7 +61,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint64_t* p_full = bars + 9;
     uint64_t* pv_full = bars + 10;
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
-    uint32_t* poisoned = tmem_base_smem + 1;
+    uint32_t* poisoned = tmem_base_smem + 1;   // bars + 12 .. 13 of the 16 words reserved
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = gridDim.x - 1 - blockIdx.x;        // long (late) query blocks first
@@ -68,7 +72,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int n_tiles = p.S_kv / BN;
     if (p.causal) n_tiles = min(n_tiles, (q0 + BM + shift + BN - 1) / BN);
 
-    if (threadIdx.x == 0) *poisoned = lme_status[0];
+    if (threadIdx.x == 0) {
+        *poisoned = lme_status[0];
+        if (smem_u32(smem) & 1023u) {
+            report_error(STATUS_BOUNDS, 680);
+            *poisoned = 1u;
+        }
+    }
     __syncthreads();
     if (*poisoned != 0u || n_tiles <= 0) return;
 
@@ -99,21 +109,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (warp == 0) {
         if (lane == 0) {
             const int row_q = b * p.S_q + q0;
-            mbar_expect_tx(q_full, TILE_BYTES);
+            mbar_expect_tx(q_full, Q_BYTES);
             tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
-            tma_load_2d(smem + OFF_Q + HALF_BYTES, &tmQ, q_full, h * HD + 64, row_q);
+            tma_load_2d(smem + OFF_Q + Q_HALF, &tmQ, q_full, h * HD + 64, row_q);
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j & 1;
                 if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) break;
                 const int row_k = b * p.S_kv + j * BN;
-                uint8_t* ks = smem + OFF_K + s * TILE_BYTES;
-                uint8_t* vs = smem + OFF_V + s * TILE_BYTES;
-                mbar_expect_tx(&k_full[s], TILE_BYTES);
+                uint8_t* ks = smem + OFF_K + s * KV_BYTES;
+                uint8_t* vs = smem + OFF_V + s * KV_BYTES;
+                mbar_expect_tx(&k_full[s], KV_BYTES);
                 tma_load_2d(ks, &tmK, &k_full[s], hk * HD, row_k);
-                tma_load_2d(ks + HALF_BYTES, &tmK, &k_full[s], hk * HD + 64, row_k);
-                mbar_expect_tx(&v_full[s], TILE_BYTES);
+                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, row_k);
+                mbar_expect_tx(&v_full[s], KV_BYTES);
                 tma_load_2d(vs, &tmV, &v_full[s], hk * HD, row_k);
-                tma_load_2d(vs + HALF_BYTES, &tmV, &v_full[s], hk * HD + 64, row_k);
+                tma_load_2d(vs + KV_HALF, &tmV, &v_full[s], hk * HD + 64, row_k);
             }
         }
         __syncwarp();
@@ -127,12 +137,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const int s = j & 1;
                 if (!mbar_wait(&k_full[s], (j >> 1) & 1, 620 + s)) return false;
                 tc_fence_after();
-                const uint32_t sk = smem_u32(smem + OFF_K + s * TILE_BYTES);
-                const uint32_t d = tmem_base + s * BN;
+                const uint32_t sk = smem_u32(smem + OFF_K + s * KV_BYTES);
+                const uint32_t d = tmem_base + TM_S + s * BN;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    umma_bf16(d, make_smem_desc_sw128(sq + off, 16, 1024), make_smem_desc_sw128(sk + off, 16, 1024),
+                    const uint32_t qoff = (kk >> 2) * Q_HALF + (kk & 3) * 32;
+                    const uint32_t koff = (kk >> 2) * KV_HALF + (kk & 3) * 32;
+                    umma_bf16(d, make_smem_desc_sw128(sq + qoff, 16, 1024), make_smem_desc_sw128(sk + koff, 16, 1024),
                               idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[s]);
@@ -145,13 +156,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!mbar_wait(p_full, j & 1, 630)) { ok = false; break; }
                 if (!mbar_wait(&v_full[s], (j >> 1) & 1, 640 + s)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t sv = smem_u32(smem + OFF_V + s * TILE_BYTES);
-                const uint32_t d = tmem_base + 2 * BN;
+                const uint32_t sv = smem_u32(smem + OFF_V + s * KV_BYTES);
+                const uint32_t d = tmem_base + TM_O;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    umma_bf16(d, make_smem_desc_sw128(sp + a_off, 16, 1024),
-                              make_smem_desc_sw128(sv + kk * (16 * 128), HALF_BYTES, 1024), idesc_pv,
+                    // P: one 64-column half, 32 bytes per k-step.  V: 16 key rows per k-step, the two 64-wide
+                    // halves of the head dim KV_HALF bytes apart
+                    umma_bf16(d, make_smem_desc_sw128(sp + kk * 32, 16, 1024),
+                              make_smem_desc_sw128(sv + kk * (16 * 128), KV_HALF, 1024), idesc_pv,
                               (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(pv_full);
@@ -163,14 +175,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int qd = warp & 3;                      // TMEM lane quadrant this warp may access
         const int row = qd * 32 + lane;               // query row inside the tile
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
-        const uint32_t to = lane_base + 2 * BN;       // the O accumulator
+        const uint32_t to = lane_base + TM_O;         // the O accumulator
         const float sl2 = p.scale * 1.4426950408889634f;
         const int limit = q0 + row + shift;           // last visible key of this row (causal)
         // m is the maximum the exponents are taken against.  It follows the true row maximum lazily: O (in TMEM) and
         // l are rescaled only when the maximum grew by more than 2^8, so P stays below 256 and most tiles skip the
         // read-modify-write of O altogether.
         float m = -INFINITY, l = 0.f;
-        uint8_t* prow = smem + OFF_P + row * 128;     // this row inside a 64-column half
+        uint8_t* prow = smem + OFF_P + row * 128;     // this row of the 128 x 64 P tile
         bool ok = true;
         // every wait is voted on: the tcgen05.ld / st below are warp-collective, so the warp leaves together
         for (int j = 0; j < n_tiles; ++j) {
@@ -178,16 +190,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (j >> 1) & 1, 650 + s));
             if (!ok) break;
             tc_fence_after();
-            const uint32_t ts = lane_base + s * BN;
+            const uint32_t ts = lane_base + TM_S + s * BN;
             const int k0 = j * BN;
             const bool masked = p.causal && (k0 + BN - 1 > q0 + shift);
-            uint32_t r[4][32];
+            uint32_t r[BN / 32][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, r[c]);
+            for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32(ts + c * 32, r[c]);
             tmem_ld_wait();
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < BN / 32; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     if (masked && k0 + c * 32 + i > limit) r[c][i] = 0xff800000u;   // -inf: exp2 gives 0
@@ -221,7 +233,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float m_off = (m == -INFINITY) ? 0.f : m * sl2;
             float sum = 0.f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < BN / 32; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -230,12 +242,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     sum += p0 + p1;
                     packed[i >> 1] = pack_bf16x2(p0, p1);
                 }
-                // columns c*32 .. +31 = 16-byte chunks (c & 1) * 4 .. +3 of half c >> 1, XOR-swizzled by row
-                uint8_t* half = prow + (c >> 1) * HALF_BYTES;
+                // columns c*32 .. +31 = 16-byte chunks c * 4 .. +3 of the row, XOR-swizzled by row
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 1) * 4 + q4) ^ (row & 7);
-                    *reinterpret_cast<uint4*>(half + chunk * 16) =
+                    const int chunk = (c * 4 + q4) ^ (row & 7);
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) =
                         make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                 }
             }
@@ -313,6 +324,7 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     if (!configured) {
         if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
             return LME_ERR_LAUNCH;
+        cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         configured = true;
     }
     Args p;
