@@ -1,8 +1,7 @@
 // Flash-attention forward on tcgen05 (head dim 128, bf16, causal or full, grouped K/V heads).
 //
 // One CTA owns 128 query rows of one (batch, head) and streams the K/V sequence in tiles of 64 rows:
-//   warp 0      TMA producer   Q once; K and V tiles through a 2-stage ring (separate barriers, so S = Q K^T starts
-//                              as soon as K has landed)
+//   warp 0      TMA producer   Q once; K tiles through a 2-stage ring, V through one stage
 //   warp 1      MMA issuer     S_j = Q K_j^T  (128 x 64 x 128, both operands K-major, accumulator in TMEM, two S
 //                              buffers so S_{j+1} is computed while the softmax warps work on S_j), then
 //                              O += P_j V_j (P from shared memory, V as an MN-major operand straight from its
@@ -13,8 +12,8 @@
 //                              across tiles; the exponents are taken against a maximum that trails the true one by
 //                              at most 2^8, so the rescale of O - a TMEM read-modify-write - runs only on the few
 //                              tiles where the maximum jumps.
-// TMEM: S0 | S1 (64 columns each) | O (128) = 256 columns.  Shared memory: Q 32 KB, K 2 x 16 KB, V 2 x 16 KB,
-// P 16 KB = 112 KB, so TWO CTAs share an SM (and its 512 TMEM columns): while one CTA's softmax warps keep the
+// TMEM: S0 | S1 (64 columns each) | O (128) = 256 columns.  Shared memory: Q 32 KB, K 2 x 16 KB, V 16 KB,
+// P 2 x 16 KB = 112 KB, so TWO CTAs share an SM (and its 512 TMEM columns): while one CTA's softmax warps keep the
 // MUFU / FMA pipes busy the other's MMAs and loads proceed.  Every wait is bounded (common.cuh); a CTA that starts
 // after an error was recorded returns at once.
 //
@@ -27,8 +26,10 @@ constexpr int BM = 128, BN = 64, HD = 128;
 constexpr int Q_HALF = BM * 128;               // 128 rows x 64 bf16 (one 128-byte swizzled half of the head dim)
 constexpr int KV_HALF = BN * 128;              // 64 rows x 64 bf16
 constexpr int Q_BYTES = 2 * Q_HALF, KV_BYTES = 2 * KV_HALF, P_BYTES = BM * BN * 2;
-constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;
+// K has a 2-stage ring (the next S product is issued a tile ahead), V one stage (it is needed a whole softmax after
+// the previous P V product released it), P two buffers (the softmax warps never wait for the MMA that reads P)
+constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + KV_BYTES;
+constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
 // 112 KB of tiles + barriers: two CTAs share an SM, so the softmax of one overlaps the other's MMAs and waits
 constexpr int SMEM_BYTES = OFF_BAR + 128;
 constexpr uint32_t TMEM_COLS = 256;            // S0 | S1 (64 columns each) | O (128)
@@ -53,15 +54,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmV, const Args p) {
     extern __shared__ __align__(1024) uint8_t smem[];      // the swizzled tiles need 1024-byte alignment (checked)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    // Barriers that can be one completion ahead of their waiter come in pairs indexed by tile parity: a single
+    // barrier whose phase ran two completions ahead would show the waiter the parity it is still waiting for.
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;     // [2]
-    uint64_t* v_full = bars + 3;     // [2]
-    uint64_t* kv_empty = bars + 5;   // [2]
+    uint64_t* k_empty = bars + 3;    // [2]
+    uint64_t* v_full = bars + 5;
+    uint64_t* v_empty = bars + 6;
     uint64_t* s_full = bars + 7;     // [2]
-    uint64_t* p_full = bars + 9;
-    uint64_t* pv_full = bars + 10;
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
-    uint32_t* poisoned = tmem_base_smem + 1;   // bars + 12 .. 13 of the 16 words reserved
+    uint64_t* p_full = bars + 9;     // [2]
+    uint64_t* pv_full = bars + 11;   // [2]
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 13);
+    uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = gridDim.x - 1 - blockIdx.x;        // long (late) query blocks first
@@ -89,12 +93,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1);
-            mbar_init(&v_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_empty[s], 1);
             mbar_init(&s_full[s], 1);
+            mbar_init(&p_full[s], 4);    // one arrival per softmax warp
+            mbar_init(&pv_full[s], 1);
         }
-        mbar_init(p_full, 4);        // one arrival per softmax warp
-        mbar_init(pv_full, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -112,18 +117,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_expect_tx(q_full, Q_BYTES);
             tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
             tma_load_2d(smem + OFF_Q + Q_HALF, &tmQ, q_full, h * HD + 64, row_q);
-            for (int j = 0; j < n_tiles; ++j) {
+            auto load_k = [&](int j) -> bool {
                 const int s = j & 1;
-                if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) break;
-                const int row_k = b * p.S_kv + j * BN;
+                if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) return false;
                 uint8_t* ks = smem + OFF_K + s * KV_BYTES;
-                uint8_t* vs = smem + OFF_V + s * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
-                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, row_k);
-                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, row_k);
-                mbar_expect_tx(&v_full[s], KV_BYTES);
-                tma_load_2d(vs, &tmV, &v_full[s], hk * HD, row_k);
-                tma_load_2d(vs + KV_HALF, &tmV, &v_full[s], hk * HD + 64, row_k);
+                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, b * p.S_kv + j * BN);
+                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, b * p.S_kv + j * BN);
+                return true;
+            };
+            bool ok = load_k(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                // K runs one tile ahead of V so that the wait for V's single stage never delays the next S product
+                if (j + 1 < n_tiles && !load_k(j + 1)) break;
+                if (!mbar_wait(v_empty, (j & 1) ^ 1, 605)) break;
+                uint8_t* vs = smem + OFF_V;
+                mbar_expect_tx(v_full, KV_BYTES);
+                tma_load_2d(vs, &tmV, v_full, hk * HD, b * p.S_kv + j * BN);
+                tma_load_2d(vs + KV_HALF, &tmV, v_full, hk * HD + 64, b * p.S_kv + j * BN);
             }
         }
         __syncwarp();
@@ -131,7 +142,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(1, 1, false, false, BM, BN);
             const uint32_t idesc_pv = make_idesc(1, 1, false, true, BM, HD);
-            const uint32_t sq = smem_u32(smem + OFF_Q), sp = smem_u32(smem + OFF_P);
+            const uint32_t sq = smem_u32(smem + OFF_Q);
             bool ok = mbar_wait(q_full, 0, 610);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j & 1;
@@ -147,16 +158,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                               idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[s]);
+                umma_commit(&k_empty[s]);
                 return true;
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j & 1;
                 if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
-                if (!mbar_wait(p_full, j & 1, 630)) { ok = false; break; }
-                if (!mbar_wait(&v_full[s], (j >> 1) & 1, 640 + s)) { ok = false; break; }
+                if (!mbar_wait(&p_full[s], (j >> 1) & 1, 630 + s)) { ok = false; break; }
+                if (!mbar_wait(v_full, j & 1, 640)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t sv = smem_u32(smem + OFF_V + s * KV_BYTES);
+                const uint32_t sv = smem_u32(smem + OFF_V);
+                const uint32_t sp = smem_u32(smem + OFF_P + s * P_BYTES);
                 const uint32_t d = tmem_base + TM_O;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
@@ -166,8 +179,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                               make_smem_desc_sw128(sv + kk * (16 * 128), KV_HALF, 1024), idesc_pv,
                               (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(pv_full);
-                umma_commit(&kv_empty[s]);
+                umma_commit(&pv_full[s]);
+                umma_commit(v_empty);
             }
         }
         __syncwarp();
@@ -182,7 +195,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // l are rescaled only when the maximum grew by more than 2^8, so P stays below 256 and most tiles skip the
         // read-modify-write of O altogether.
         float m = -INFINITY, l = 0.f;
-        uint8_t* prow = smem + OFF_P + row * 128;     // this row of the 128 x 64 P tile
+        uint8_t* prow0 = smem + OFF_P + row * 128;    // this row of the 128 x 64 P tile (buffer 0)
         bool ok = true;
         // every wait is voted on: the tcgen05.ld / st below are warp-collective, so the warp leaves together
         for (int j = 0; j < n_tiles; ++j) {
@@ -206,15 +219,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     mx = fmaxf(mx, __uint_as_float(r[c][i]));
                 }
             const float m_new = fmaxf(m, mx);
+            if (j >= 2) {   // this P buffer was last read by the P V product of tile j - 2
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[s], ((j >> 1) - 1) & 1, 655 + s));
+                if (!ok) break;
+            }
             if (j == 0) {
                 m = m_new;
             } else {
-                // PV_{j-1} has to be complete before P is overwritten and before O may be touched
-                ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (j - 1) & 1, 660));
-                if (!ok) break;
-                tc_fence_after();
                 const bool need = (m_new - m) * sl2 > 8.f;
                 if (__any_sync(0xffffffffu, need)) {
+                    // O may only be touched when every earlier P V product has completed
+                    ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1, 660));
+                    if (!ok) break;
+                    tc_fence_after();
                     const float alpha = need ? ex2((m - m_new) * sl2) : 1.f;
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
@@ -246,7 +263,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const int chunk = (c * 4 + q4) ^ (row & 7);
-                    *reinterpret_cast<uint4*>(prow + chunk * 16) =
+                    *reinterpret_cast<uint4*>(prow0 + s * P_BYTES + chunk * 16) =
                         make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                 }
             }
@@ -254,9 +271,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(&p_full[s]);
         }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (n_tiles - 1) & 1, 670));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 670));
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
