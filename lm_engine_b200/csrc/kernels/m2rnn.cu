@@ -99,6 +99,13 @@ struct ColReduce {
     }
 };
 
+// transposes an 8 x 8 block of 16-bit values held as a fragment (lane (g, qd) holds row g, columns 2qd, 2qd+1)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
 __device__ __forceinline__ float quad_sum(float x) {
     x += __shfl_xor_sync(0xffffffffu, x, 1);
     x += __shfl_xor_sync(0xffffffffu, x, 2);
@@ -345,6 +352,13 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
     }
     float dh[NT][4];
     load_state<V>(p.dh + w.state_off, w, dh);
+    // dW of this warp's rows over this launch's steps, accumulator layout: [m-tile of i][n-tile of j]
+    constexpr bool DW_IN_KERNEL = V <= 32;
+    float dWacc[DW_IN_KERNEL ? KS : 1][DW_IN_KERNEL ? NT : 1][4];
+#pragma unroll
+    for (int mt = 0; mt < (DW_IN_KERNEL ? KS : 1); ++mt)
+#pragma unroll
+        for (int nt = 0; nt < (DW_IN_KERNEL ? NT : 1); ++nt) dWacc[mt][nt][0] = dWacc[mt][nt][1] = dWacc[mt][nt][2] = dWacc[mt][nt][3] = 0.f;
 
     const int t_begin = p.t0, t_end = p.t0 + p.T;
     auto issue = [&](int c) {
@@ -395,13 +409,16 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
             float dq0 = 0.f, dq1 = 0.f, dk0 = 0.f, dk1 = 0.f, dfp = 0.f;
             float dvp[NT][2], acc[NT][4];
             uint32_t a[KS][4];
+            uint32_t hraw[NT][2];
             __nv_bfloat16* zout = zrec + (t - p.t0) * rec_step + g * V + 2 * qd;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const float2 dyv = unpack2(*reinterpret_cast<const uint32_t*>(&sm.dy[stage][st][8 * nt + 2 * qd]));
                 const float2 vv = unpack2(*reinterpret_cast<const uint32_t*>(&sm.v[stage][st][8 * nt + 2 * qd]));
-                const float2 hp01 = unpack2(*reinterpret_cast<const uint32_t*>(&sm.hp[stage][st][g][8 * nt + 2 * qd]));
-                const float2 hp23 = unpack2(*reinterpret_cast<const uint32_t*>(&sm.hp[stage][st][g + 8][8 * nt + 2 * qd]));
+                hraw[nt][0] = *reinterpret_cast<const uint32_t*>(&sm.hp[stage][st][g][8 * nt + 2 * qd]);
+                hraw[nt][1] = *reinterpret_cast<const uint32_t*>(&sm.hp[stage][st][g + 8][8 * nt + 2 * qd]);
+                const float2 hp01 = unpack2(hraw[nt][0]);
+                const float2 hp23 = unpack2(hraw[nt][1]);
                 const float2 z01 = unpack2(*reinterpret_cast<const uint32_t*>(&sm.z[stage][st][g][8 * nt + 2 * qd]));
                 const float2 z23 = unpack2(*reinterpret_cast<const uint32_t*>(&sm.z[stage][st][g + 8][8 * nt + 2 * qd]));
                 const float hpv[4] = {hp01.x, hp01.y, hp23.x, hp23.y};
@@ -425,10 +442,32 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
                 dvp[nt][0] = k0 * da[0] + k1 * da[2];
                 dvp[nt][1] = k0 * da[1] + k1 * da[3];
                 const uint32_t p01 = pack2(da[0], da[1]), p23 = pack2(da[2], da[3]);
-                *reinterpret_cast<uint32_t*>(zout + 8 * nt) = p01;
-                *reinterpret_cast<uint32_t*>(zout + 8 * V + 8 * nt) = p23;
+                if (!DW_IN_KERNEL) {      // the caller forms dW = sum h_{t-1}^T da_t from the records
+                    *reinterpret_cast<uint32_t*>(zout + 8 * nt) = p01;
+                    *reinterpret_cast<uint32_t*>(zout + 8 * V + 8 * nt) = p23;
+                }
                 a[nt >> 1][(nt & 1) * 2] = p01;
                 a[nt >> 1][(nt & 1) * 2 + 1] = p23;
+            }
+            if (DW_IN_KERNEL) {
+                // dW[i][j] += sum_rows h_{t-1}[row][i] da[row][j]: both operands are the register pairs above with
+                // their 8 x 8 blocks transposed (rows become the contraction index)
+                uint32_t bt[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    bt[nt][0] = movmatrix_trans(a[nt >> 1][(nt & 1) * 2]);
+                    bt[nt][1] = movmatrix_trans(a[nt >> 1][(nt & 1) * 2 + 1]);
+                }
+#pragma unroll
+                for (int mt = 0; mt < KS; ++mt) {
+                    uint32_t at[4];
+                    at[0] = movmatrix_trans(hraw[2 * mt][0]);
+                    at[1] = movmatrix_trans(hraw[2 * mt + 1][0]);
+                    at[2] = movmatrix_trans(hraw[2 * mt][1]);
+                    at[3] = movmatrix_trans(hraw[2 * mt + 1][1]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma16816(dWacc[DW_IN_KERNEL ? mt : 0][DW_IN_KERNEL ? nt : 0], at, bt[nt][0], bt[nt][1]);
+                }
             }
             dq0 = quad_sum(dq0), dq1 = quad_sum(dq1), dk0 = quad_sum(dk0), dk1 = quad_sum(dk1);
             if (qd == 0) {
@@ -460,6 +499,20 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
         __syncwarp();
     }
     store_state<V>(p.dh + w.state_off, w, dh);
+    if (DW_IN_KERNEL) {
+        // dW_part [B, N, RB, V, V] accumulates over the launches of one backward pass (the caller zeroes it)
+        float* out = p.dW_part + ((static_cast<long long>(w.b) * p.N + w.n) * (p.K / 16) + w.rb) * V * V;
+#pragma unroll
+        for (int mt = 0; mt < KS; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float2* lo = reinterpret_cast<float2*>(out + (16 * mt + g) * V + 8 * nt + 2 * qd);
+                float2* hi = reinterpret_cast<float2*>(out + (16 * mt + g + 8) * V + 8 * nt + 2 * qd);
+                float2 a0 = *lo, a1 = *hi;
+                a0.x += dWacc[mt][nt][0], a0.y += dWacc[mt][nt][1], a1.x += dWacc[mt][nt][2], a1.y += dWacc[mt][nt][3];
+                *lo = a0, *hi = a1;
+            }
+    }
 }
 
 template <int V>

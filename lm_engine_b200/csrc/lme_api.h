@@ -116,7 +116,8 @@ int lme_ssd_dcb(const void* dm, const float* cum, void* dcb, long long BC, int N
 //   mode 1 replay  : steps t0 .. t0+T-1 from ckpt[t0 / seg_len]; writes hprev, z bf16 [B,N,Tcap,K,V]
 //   mode 2 backward: steps t0+T-1 .. t0; reads hprev, z (overwritten with da), dy bf16 [B,S,N,V], dh fp32 [B,N,K,V]
 //                    (in: gradient of the state after step t0+T-1, out: before step t0); writes dq, dk fp32
-//                    [B,S,N,K], dv_part fp32 [RB,B,S,N,V], df_part fp32 [RB,B,S,N]; clip > 0 clamps dh every step
+//                    [B,S,N,K], dv_part fp32 [RB,B,S,N,V], df_part fp32 [RB,B,S,N]; clip > 0 clamps dh every step.
+//                    V = 64: z is overwritten with da for the caller's dW GEMM; V <= 32: dW_part is accumulated
 typedef struct LmeM2rnnArgs {
     const void *q, *k, *v;
     const float* f;
@@ -132,6 +133,7 @@ typedef struct LmeM2rnnArgs {
     const void* dy;
     float *dh, *dq, *dk, *dv_part, *df_part;
     float clip;
+    float* dW_part;   // V <= 32: fp32 [B,N,RB,V,V], += sum_t h_{t-1}^T da_t of each launch (hprev / z stay inputs only)
 } LmeM2rnnArgs;
 int lme_m2rnn(const LmeM2rnnArgs* args, int mode, void* stream);
 

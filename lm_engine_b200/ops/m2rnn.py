@@ -24,7 +24,7 @@ class _Args(ctypes.Structure):
                 + [(n, c_void_p) for n in ("h0", "h_out", "y_part", "ckpt")]
                 + [(n, c_int) for n in ("seg_len", "t0", "T", "Tcap")]
                 + [(n, c_void_p) for n in ("hprev", "z", "dy", "dh", "dq", "dk", "dv_part", "df_part")]
-                + [("clip", c_float)])
+                + [("clip", c_float), ("dW_part", c_void_p)])
 
 
 def m2rnn_kernel_eligible(q, k, v, f, W) -> bool:
@@ -112,20 +112,26 @@ class _M2RNN(torch.autograd.Function):
         df_part = torch.empty((RB, B, S, N), dtype=torch.float32, device=dev)
         hprev = torch.empty((B, N, seg, K, V), dtype=torch.bfloat16, device=dev)
         z = torch.empty_like(hprev)
+        in_kernel_dw = V <= 32      # the backward kernel accumulates dW itself; V = 64 leaves it to a batched GEMM
         dW = torch.zeros((N, V, V), dtype=torch.float32, device=dev)
+        dW_part = torch.zeros((B, N, RB, V, V), dtype=torch.float32, device=dev) if in_kernel_dw else None
         a = _Args()
         _fill(a, q, k, v, f32, Wb, N)
         a.ckpt, a.seg_len, a.Tcap = ckpt.data_ptr(), seg, seg
         a.hprev, a.z, a.dy, a.dh = hprev.data_ptr(), z.data_ptr(), dy.data_ptr(), dh.data_ptr()
         a.dq, a.dk, a.dv_part, a.df_part = dq.data_ptr(), dk.data_ptr(), dv_part.data_ptr(), df_part.data_ptr()
         a.clip = float(clip) if clip is not None else 0.0
+        a.dW_part = dW_part.data_ptr() if in_kernel_dw else None
         for s in reversed(range((S + seg - 1) // seg)):
             a.t0, a.T = s * seg, min(seg, S - s * seg)
             _launch(a, 1, f"lme_m2rnn replay t0={a.t0} T={a.T}")
             _launch(a, 2, f"lme_m2rnn backward t0={a.t0} T={a.T}")
-            hp = hprev[:, :, :a.T].reshape(B * N, a.T * K, V)
-            da = z[:, :, :a.T].reshape(B * N, a.T * K, V)
-            dW += _bmm_f32(hp.transpose(1, 2), da).view(B, N, V, V).sum(0)
+            if not in_kernel_dw:
+                hp = hprev[:, :, :a.T].reshape(B * N, a.T * K, V)
+                da = z[:, :, :a.T].reshape(B * N, a.T * K, V)
+                dW += _bmm_f32(hp.transpose(1, 2), da).view(B, N, V, V).sum(0)
+        if in_kernel_dw:
+            dW = dW_part.sum((0, 2))
 
         def fold(t: torch.Tensor, heads: int, dtype) -> torch.Tensor:      # [B, S, N, ...] -> [B, S, heads, ...]
             if heads != N:
