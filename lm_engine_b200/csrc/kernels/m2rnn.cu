@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(32) m2rnn_fwd_kernel(const LmeM2rnnArgs p) {
         cp_commit();
     };
 
+    const long long rec0 = SAVE ? ((static_cast<long long>(w.b) * p.N + w.n) * p.Tcap * p.K + 16 * w.rb + g) * V + 2 * qd : 0;
     int next_ckpt = (!SAVE && p.ckpt) ? 0 : -1;
     float* ckpt_ptr = p.ckpt ? p.ckpt + (static_cast<long long>(w.b) * p.N + w.n) * nseg * KV + 16 * w.rb * V : nullptr;
     // (rb, b, t_begin, n, 0) of y_part [RB, B, S, N, V]; advanced by one token per step
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(32) m2rnn_fwd_kernel(const LmeM2rnnArgs p) {
                 a[s][3] = pack2(h[2 * s + 1][2], h[2 * s + 1][3]);
             }
             // element offset of (row g, column 2 qd) of this step's 16 x V tile in the [B, N, Tcap, K, V] records
-            const long long rec = (((static_cast<long long>(w.b) * p.N + w.n) * p.Tcap + (t - p.t0)) * p.K + 16 * w.rb + g) * V + 2 * qd;
+            const long long rec = rec0 + static_cast<long long>(t - t_begin) * KV;
             if (SAVE) {
                 __nv_bfloat16* hp = static_cast<__nv_bfloat16*>(p.hprev) + rec;
 #pragma unroll
@@ -389,6 +390,12 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
         cp_commit();
     };
 
+    // output pointers of the last step of this launch; they walk backwards with the scan
+    const long long qk_step = static_cast<long long>(p.N) * p.K;
+    float* dq_ptr = p.dq + ((static_cast<long long>(w.b) * p.S + (t_end - 1)) * p.N + w.n) * p.K + 16 * w.rb + g;
+    float* dk_ptr = p.dk + (dq_ptr - p.dq);
+    float* df_ptr = p.df_part + ((static_cast<long long>(w.rb) * p.B + w.b) * p.S + (t_end - 1)) * p.N + w.n;
+    float* dv_ptr = p.dv_part + (df_ptr - p.df_part) * V;
     const int nchunks = (t_end - t_begin + TC - 1) / TC;
     if (nchunks > 0) issue(nchunks - 1);
     for (int c = nchunks - 1; c >= 0; --c) {
@@ -470,23 +477,21 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
                 }
             }
             dq0 = quad_sum(dq0), dq1 = quad_sum(dq1), dk0 = quad_sum(dk0), dk1 = quad_sum(dk1);
-            if (qd == 0) {
-                const long long o = ((static_cast<long long>(w.b) * p.S + t) * p.N + w.n) * p.K + 16 * w.rb + g;
-                p.dq[o] = dq0, p.dq[o + 8] = dq1, p.dk[o] = dk0, p.dk[o + 8] = dk1;
-            }
+            if (qd == 0) dq_ptr[0] = dq0, dq_ptr[8] = dq1, dk_ptr[0] = dk0, dk_ptr[8] = dk1;
+            dq_ptr -= qk_step, dk_ptr -= qk_step;
             dfp = quad_sum(dfp);
             dfp += __shfl_xor_sync(0xffffffffu, dfp, 4);
             dfp += __shfl_xor_sync(0xffffffffu, dfp, 8);
             dfp += __shfl_xor_sync(0xffffffffu, dfp, 16);
-            const long long po = ((static_cast<long long>(w.rb) * p.B + w.b) * p.S + t) * p.N + w.n;
-            if (lane == 0) p.df_part[po] = dfp;
+            if (lane == 0) *df_ptr = dfp;
             {
                 float2 out;
                 int nt_out = 0;
                 bool writer = true;
                 ColReduce<NT, 16>::run(dvp, lane, out, nt_out, writer);
-                if (writer) *reinterpret_cast<float2*>(p.dv_part + po * V + 8 * nt_out + 2 * qd) = out;
+                if (writer) *reinterpret_cast<float2*>(dv_ptr + 8 * nt_out + 2 * qd) = out;
             }
+            df_ptr -= p.N, dv_ptr -= static_cast<long long>(p.N) * V;
 #pragma unroll
             for (int s = 0; s < KS; ++s)
 #pragma unroll
