@@ -1,0 +1,580 @@
+// Flash-attention backward on tcgen05, as two kernels without atomics (head dim 128, bf16, causal or full, GQA):
+//
+//   attn_dq_kernel   one CTA per 128 query rows of one (batch, head); streams K/V in tiles of 64 rows like the
+//                    forward kernel:  S = Q K^T, dP = dO V^T (TMEM), dS = P (dP - delta) scale with
+//                    P = exp2(S scale log2e - lse log2e) recomputed from the saved log-sum-exp (no running maximum),
+//                    dQ += dS K (K's tile read a second time as an MN-major operand).
+//   attn_dkv_kernel  one CTA per 128 key rows of one (batch, kv head); streams the query rows of every query head
+//                    of its group in tiles of 64, in the TRANSPOSED orientation so that a thread owns a key row:
+//                    S^T = K Q^T, dP^T = V dO^T, P^T and dS^T written as K-major operands,
+//                    dV += P^T dO, dK += dS^T Q (Q and dO tiles read a second time as MN-major operands).
+// Recomputing S and dP in both kernels costs 7 tile products per (query, key) tile pair instead of 5, and buys
+// ownership: every output row has exactly one writer, so there is no atomic accumulation of dQ and the result is
+// deterministic.  delta = rowsum(dO * O) comes from the caller.
+//
+// Warp roles, barriers and bounded waits follow attention.cu (warp 0 TMA, warp 1 MMA issuer, warps 2..5 one row
+// per thread); barriers that can run one completion ahead of their waiter are paired by tile parity.
+//
+// Role of flash-attn's backward kernels used by the reference (lm_engine/modeling_utils/sequence_mixer_blocks/
+// softmax_attention/utils.py flash_attention).
+namespace lme {
+namespace attn_bwd {
+
+using attn::ex2;
+
+constexpr int HD = 128;
+constexpr int ROWS = 128;                      // rows owned by a CTA (queries in dq, keys in dkv)
+constexpr int TN = 64;                         // streamed tile rows
+constexpr int BIG_HALF = ROWS * 128;           // 128 rows x 64 bf16, one swizzled half of the head dim: 16 KB
+constexpr int SMALL_HALF = TN * 128;           // 64 rows x 64 bf16: 8 KB
+constexpr int BIG = 2 * BIG_HALF, SMALL = 2 * SMALL_HALF;
+constexpr int PT = ROWS * TN * 2;              // a 128 x 64 bf16 operand written by the row threads: 16 KB
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct DqArgs {
+    __nv_bfloat16* dq;
+    long long dq_ld;
+    const float* lse;        // [B, Hq, S_q] natural log
+    const float* delta;      // [B, Hq, S_q]
+    int B, S_q, S_kv, Hq, Hkv, causal;
+    float scale;
+};
+
+// row r of a 128 x 64 K-major operand tile: 16-byte chunk c (8 columns) lands at chunk c ^ (r & 7)
+__device__ __forceinline__ void store_row_chunk(uint8_t* tile, int row, int chunk, uint4 v) {
+    *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+
+namespace dq {
+constexpr int OFF_Q = 0, OFF_DO = BIG, OFF_K = 2 * BIG, OFF_V = OFF_K + 2 * SMALL, OFF_DS = OFF_V + 2 * SMALL;
+constexpr int OFF_BAR = OFF_DS + 2 * PT;
+constexpr int SMEM_BYTES = OFF_BAR + 256;
+constexpr uint32_t TMEM_COLS = 512;            // S0 S1 | dP0 dP1 (64 each) | dQ (128)
+constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256;
+}  // namespace dq
+
+__global__ void __launch_bounds__(192, 1)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const DqArgs p) {
+    using namespace dq;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* q_full = bars + 0;
+    uint64_t* kv_full = bars + 1;    // [2]
+    uint64_t* kv_empty = bars + 3;   // [2]
+    uint64_t* sdp_full = bars + 5;   // [2]
+    uint64_t* ds_full = bars + 7;    // [2]
+    uint64_t* dq_done = bars + 9;    // [2]
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* poisoned = tmem_base_smem + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int q0 = qb * ROWS;
+    const int shift = p.S_kv - p.S_q;
+    int n_tiles = p.S_kv / TN;
+    if (p.causal) n_tiles = min(n_tiles, (q0 + ROWS + shift + TN - 1) / TN);
+
+    if (threadIdx.x == 0) {
+        *poisoned = lme_status[0];
+        if (smem_u32(smem) & 1023u) {
+            report_error(STATUS_BOUNDS, 780);
+            *poisoned = 1u;
+        }
+    }
+    __syncthreads();
+    if (*poisoned != 0u || n_tiles <= 0) return;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmDO);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+            mbar_init(&sdp_full[s], 1);
+            mbar_init(&ds_full[s], 4);
+            mbar_init(&dq_done[s], 1);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int row_q = b * p.S_q + q0;
+            mbar_expect_tx(q_full, 2 * BIG);
+            tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
+            tma_load_2d(smem + OFF_Q + BIG_HALF, &tmQ, q_full, h * HD + 64, row_q);
+            tma_load_2d(smem + OFF_DO, &tmDO, q_full, h * HD, row_q);
+            tma_load_2d(smem + OFF_DO + BIG_HALF, &tmDO, q_full, h * HD + 64, row_q);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, 700 + s)) break;
+                const int row_k = b * p.S_kv + j * TN;
+                uint8_t* ks = smem + OFF_K + s * SMALL;
+                uint8_t* vs = smem + OFF_V + s * SMALL;
+                mbar_expect_tx(&kv_full[s], 2 * SMALL);
+                tma_load_2d(ks, &tmK, &kv_full[s], hk * HD, row_k);
+                tma_load_2d(ks + SMALL_HALF, &tmK, &kv_full[s], hk * HD + 64, row_k);
+                tma_load_2d(vs, &tmV, &kv_full[s], hk * HD, row_k);
+                tma_load_2d(vs + SMALL_HALF, &tmV, &kv_full[s], hk * HD + 64, row_k);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = make_idesc(1, 1, false, false, ROWS, TN);      // 128 x 64, both K-major
+            const uint32_t idesc_dq = make_idesc(1, 1, false, true, ROWS, HD);      // 128 x 128, B MN-major
+            const uint32_t sq = smem_u32(smem + OFF_Q), sdo = smem_u32(smem + OFF_DO);
+            bool ok = mbar_wait(q_full, 0, 710);
+            auto issue_sdp = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&kv_full[s], (j >> 1) & 1, 720 + s)) return false;
+                tc_fence_after();
+                const uint32_t sk = smem_u32(smem + OFF_K + s * SMALL), sv = smem_u32(smem + OFF_V + s * SMALL);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t big = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+                    const uint32_t small = (kk >> 2) * SMALL_HALF + (kk & 3) * 32;
+                    umma_bf16(tmem_base + TM_S + s * TN, make_smem_desc_sw128(sq + big, 16, 1024),
+                              make_smem_desc_sw128(sk + small, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t big = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+                    const uint32_t small = (kk >> 2) * SMALL_HALF + (kk & 3) * 32;
+                    umma_bf16(tmem_base + TM_DP + s * TN, make_smem_desc_sw128(sdo + big, 16, 1024),
+                              make_smem_desc_sw128(sv + small, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&sdp_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_sdp(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                if (j + 1 < n_tiles && !issue_sdp(j + 1)) { ok = false; break; }
+                if (!mbar_wait(&ds_full[s], (j >> 1) & 1, 730 + s)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sds = smem_u32(smem + OFF_DS + s * PT);
+                const uint32_t sk = smem_u32(smem + OFF_K + s * SMALL);
+#pragma unroll
+                for (int kk = 0; kk < TN / 16; ++kk)
+                    umma_bf16(tmem_base + TM_DQ, make_smem_desc_sw128(sds + kk * 32, 16, 1024),
+                              make_smem_desc_sw128(sk + kk * (16 * 128), SMALL_HALF, 1024), idesc_dq,
+                              (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&dq_done[s]);
+                umma_commit(&kv_empty[s]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int qd = warp & 3;
+        const int row = qd * 32 + lane;
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        const int limit = q0 + row + shift;
+        const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_q + q0 + row;
+        const float lse2 = p.lse[stat] * LOG2E;
+        const float delta = p.delta[stat];
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (j >> 1) & 1, 750 + s));
+            if (!ok) break;
+            tc_fence_after();
+            const int k0 = j * TN;
+            const bool masked = p.causal && (k0 + TN - 1 > q0 + shift);
+            uint32_t sv[2][32], dp[2][32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                tmem_ld_32x32(lane_base + TM_S + s * TN + c * 32, sv[c]);
+                tmem_ld_32x32(lane_base + TM_DP + s * TN + c * 32, dp[c]);
+            }
+            tmem_ld_wait();
+            if (j >= 2) {   // this dS buffer was last read by the dQ product of tile j - 2
+                ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[s], ((j >> 1) - 1) & 1, 755 + s));
+                if (!ok) break;
+            }
+            uint8_t* tile = smem + OFF_DS + s * PT;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float d0 = ex2(fmaf(__uint_as_float(sv[c][i]), sl2, -lse2)) * (__uint_as_float(dp[c][i]) - delta) * p.scale;
+                    float d1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), sl2, -lse2)) * (__uint_as_float(dp[c][i + 1]) - delta) * p.scale;
+                    if (masked) {
+                        if (k0 + c * 32 + i > limit) d0 = 0.f;
+                        if (k0 + c * 32 + i + 1 > limit) d1 = 0.f;
+                    }
+                    packed[i >> 1] = pack_bf16x2(d0, d1);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    store_row_chunk(tile, row, c * 4 + q4,
+                                    make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]));
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ds_full[s]);
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 770));
+        if (ok) {
+            tc_fence_after();
+            __nv_bfloat16* dst = p.dq + (static_cast<long long>(b) * p.S_q + q0 + row) * p.dq_ld + h * HD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t t[32];
+                tmem_ld_32x32(lane_base + TM_DQ + c * 32, t);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v;
+                    v.x = pack_bf16x2(__uint_as_float(t[i]), __uint_as_float(t[i + 1]));
+                    v.y = pack_bf16x2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3]));
+                    v.z = pack_bf16x2(__uint_as_float(t[i + 4]), __uint_as_float(t[i + 5]));
+                    v.w = pack_bf16x2(__uint_as_float(t[i + 6]), __uint_as_float(t[i + 7]));
+                    *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, dq::TMEM_COLS);
+    }
+}
+
+
+struct DkvArgs {
+    __nv_bfloat16 *dk, *dv;
+    long long dk_ld, dv_ld;
+    const float* lse;        // [B, Hq, S_q] natural log
+    const float* delta;      // [B, Hq, S_q]
+    int B, S_q, S_kv, Hq, Hkv, causal;
+    float scale;
+};
+
+namespace dkv {
+constexpr int OFF_K = 0, OFF_V = BIG, OFF_Q = 2 * BIG, OFF_DO = OFF_Q + 2 * SMALL, OFF_PT = OFF_DO + 2 * SMALL;
+constexpr int OFF_DST = OFF_PT + 2 * PT, OFF_STAT = OFF_DST + 2 * PT;     // stats: 2 stages x (64 lse + 64 delta)
+constexpr int STAT_BYTES = 2 * TN * 4;
+constexpr int OFF_BAR = OFF_STAT + 2 * STAT_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 256;
+constexpr uint32_t TMEM_COLS = 512;            // S^T0 S^T1 | dP^T0 dP^T1 (64 each) | dV (128) | dK (128)
+constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 384;
+}  // namespace dkv
+
+__global__ void __launch_bounds__(192, 1)
+attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const DkvArgs p) {
+    using namespace dkv;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* kv_full = bars + 0;
+    uint64_t* qdo_full = bars + 1;   // [2]
+    uint64_t* qdo_empty = bars + 3;  // [2]
+    uint64_t* sdp_full = bars + 5;   // [2]
+    uint64_t* pds_full = bars + 7;   // [2]
+    uint64_t* acc_done = bars + 9;   // [2]
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* poisoned = tmem_base_smem + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int G = p.Hq / p.Hkv;
+    const int k0 = kb * ROWS;
+    const int shift = p.S_kv - p.S_q;
+    const int nq = p.S_q / TN;
+    // first query tile with a row that sees key k0: 64 i + 63 + shift >= k0
+    const int i_start = p.causal ? max(0, (k0 - shift) / TN) : 0;
+    const int per_g = nq - i_start;
+    const int n_it = per_g > 0 ? G * per_g : 0;
+
+    if (threadIdx.x == 0) {
+        *poisoned = lme_status[0];
+        if (smem_u32(smem) & 1023u) {
+            report_error(STATUS_BOUNDS, 880);
+            *poisoned = 1u;
+        }
+    }
+    __syncthreads();
+    if (*poisoned != 0u) return;
+    if (n_it <= 0) {        // no query sees these keys: their gradients are zero
+        if (warp >= 2) {
+            const int row = (warp & 3) * 32 + lane;
+            const long long grow = static_cast<long long>(b) * p.S_kv + k0 + row;
+            for (int i = 0; i < HD; i += 8) {
+                *reinterpret_cast<uint4*>(p.dk + grow * p.dk_ld + hk * HD + i) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(p.dv + grow * p.dv_ld + hk * HD + i) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmDO);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        mbar_init(kv_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&qdo_full[s], 1);
+            mbar_init(&qdo_empty[s], 1);
+            mbar_init(&sdp_full[s], 1);
+            mbar_init(&pds_full[s], 4);
+            mbar_init(&acc_done[s], 1);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int row_k = b * p.S_kv + k0;
+            mbar_expect_tx(kv_full, 2 * BIG);
+            tma_load_2d(smem + OFF_K, &tmK, kv_full, hk * HD, row_k);
+            tma_load_2d(smem + OFF_K + BIG_HALF, &tmK, kv_full, hk * HD + 64, row_k);
+            tma_load_2d(smem + OFF_V, &tmV, kv_full, hk * HD, row_k);
+            tma_load_2d(smem + OFF_V + BIG_HALF, &tmV, kv_full, hk * HD + 64, row_k);
+            for (int it = 0; it < n_it; ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(&qdo_empty[s], ((it >> 1) & 1) ^ 1, 800 + s)) break;
+                const int h = hk * G + it / per_g, i = i_start + it % per_g;
+                const int row_q = b * p.S_q + i * TN;
+                uint8_t* qs = smem + OFF_Q + s * SMALL;
+                uint8_t* dos = smem + OFF_DO + s * SMALL;
+                float* st = reinterpret_cast<float*>(smem + OFF_STAT + s * STAT_BYTES);
+                const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_q + i * TN;
+                mbar_expect_tx(&qdo_full[s], 2 * SMALL + STAT_BYTES);
+                tma_load_2d(qs, &tmQ, &qdo_full[s], h * HD, row_q);
+                tma_load_2d(qs + SMALL_HALF, &tmQ, &qdo_full[s], h * HD + 64, row_q);
+                tma_load_2d(dos, &tmDO, &qdo_full[s], h * HD, row_q);
+                tma_load_2d(dos + SMALL_HALF, &tmDO, &qdo_full[s], h * HD + 64, row_q);
+                bulk_g2s(st, p.lse + stat, TN * 4, &qdo_full[s]);
+                bulk_g2s(st + TN, p.delta + stat, TN * 4, &qdo_full[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = make_idesc(1, 1, false, false, ROWS, TN);
+            const uint32_t idesc_acc = make_idesc(1, 1, false, true, ROWS, HD);
+            const uint32_t sk = smem_u32(smem + OFF_K), sv = smem_u32(smem + OFF_V);
+            bool ok = mbar_wait(kv_full, 0, 810);
+            auto issue_sdp = [&](int it) -> bool {
+                const int s = it & 1;
+                if (!mbar_wait(&qdo_full[s], (it >> 1) & 1, 820 + s)) return false;
+                tc_fence_after();
+                const uint32_t sq = smem_u32(smem + OFF_Q + s * SMALL), sdo = smem_u32(smem + OFF_DO + s * SMALL);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t big = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+                    const uint32_t small = (kk >> 2) * SMALL_HALF + (kk & 3) * 32;
+                    umma_bf16(tmem_base + TM_S + s * TN, make_smem_desc_sw128(sk + big, 16, 1024),
+                              make_smem_desc_sw128(sq + small, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t big = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+                    const uint32_t small = (kk >> 2) * SMALL_HALF + (kk & 3) * 32;
+                    umma_bf16(tmem_base + TM_DP + s * TN, make_smem_desc_sw128(sv + big, 16, 1024),
+                              make_smem_desc_sw128(sdo + small, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&sdp_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_sdp(0);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int s = it & 1;
+                if (it + 1 < n_it && !issue_sdp(it + 1)) { ok = false; break; }
+                if (!mbar_wait(&pds_full[s], (it >> 1) & 1, 830 + s)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t spt = smem_u32(smem + OFF_PT + s * PT), sdst = smem_u32(smem + OFF_DST + s * PT);
+                const uint32_t sq = smem_u32(smem + OFF_Q + s * SMALL), sdo = smem_u32(smem + OFF_DO + s * SMALL);
+#pragma unroll
+                for (int kk = 0; kk < TN / 16; ++kk)
+                    umma_bf16(tmem_base + TM_DV, make_smem_desc_sw128(spt + kk * 32, 16, 1024),
+                              make_smem_desc_sw128(sdo + kk * (16 * 128), SMALL_HALF, 1024), idesc_acc,
+                              (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < TN / 16; ++kk)
+                    umma_bf16(tmem_base + TM_DK, make_smem_desc_sw128(sdst + kk * 32, 16, 1024),
+                              make_smem_desc_sw128(sq + kk * (16 * 128), SMALL_HALF, 1024), idesc_acc,
+                              (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&acc_done[s]);
+                umma_commit(&qdo_empty[s]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int qd = warp & 3;
+        const int row = qd * 32 + lane;               // key row inside the tile
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        const int kr = k0 + row;
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it & 1;
+            const int i = i_start + it % per_g;
+            // the statistics of this tile were written by the bulk copies that complete qdo_full
+            ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[s], (it >> 1) & 1, 845 + s));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (it >> 1) & 1, 850 + s));
+            if (!ok) break;
+            tc_fence_after();
+            const bool masked = p.causal && (i * TN + shift < k0 + ROWS - 1);
+            uint32_t sv[2][32], dp[2][32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                tmem_ld_32x32(lane_base + TM_S + s * TN + c * 32, sv[c]);
+                tmem_ld_32x32(lane_base + TM_DP + s * TN + c * 32, dp[c]);
+            }
+            tmem_ld_wait();
+            if (it >= 2) {   // these operand buffers were last read by the products of iteration it - 2
+                ok = __all_sync(0xffffffffu, mbar_wait(&acc_done[s], ((it >> 1) - 1) & 1, 855 + s));
+                if (!ok) break;
+            }
+            const float* st = reinterpret_cast<const float*>(smem + OFF_STAT + s * STAT_BYTES);
+            uint8_t* pt = smem + OFF_PT + s * PT;
+            uint8_t* dst = smem + OFF_DST + s * PT;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t pp[16], dd[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int col = c * 32 + e;
+                    float p0 = ex2(fmaf(__uint_as_float(sv[c][e]), sl2, -st[col] * LOG2E));
+                    float p1 = ex2(fmaf(__uint_as_float(sv[c][e + 1]), sl2, -st[col + 1] * LOG2E));
+                    if (masked) {
+                        if (kr > i * TN + col + shift) p0 = 0.f;
+                        if (kr > i * TN + col + 1 + shift) p1 = 0.f;
+                    }
+                    const float d0 = p0 * (__uint_as_float(dp[c][e]) - st[TN + col]) * p.scale;
+                    const float d1 = p1 * (__uint_as_float(dp[c][e + 1]) - st[TN + col + 1]) * p.scale;
+                    pp[e >> 1] = pack_bf16x2(p0, p1);
+                    dd[e >> 1] = pack_bf16x2(d0, d1);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    store_row_chunk(pt, row, c * 4 + q4, make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]));
+                    store_row_chunk(dst, row, c * 4 + q4, make_uint4(dd[4 * q4], dd[4 * q4 + 1], dd[4 * q4 + 2], dd[4 * q4 + 3]));
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pds_full[s]);
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&acc_done[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, 870));
+        if (ok) {
+            tc_fence_after();
+            const long long grow = static_cast<long long>(b) * p.S_kv + kr;
+            __nv_bfloat16* dvp = p.dv + grow * p.dv_ld + hk * HD;
+            __nv_bfloat16* dkp = p.dk + grow * p.dk_ld + hk * HD;
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+                uint32_t t[32];
+                tmem_ld_32x32(lane_base + TM_DV + c * 32, t);     // columns 256 .. 511: dV then dK
+                tmem_ld_wait();
+                __nv_bfloat16* o = (c < 4 ? dvp : dkp) + (c & 3) * 32;
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                    uint4 v;
+                    v.x = pack_bf16x2(__uint_as_float(t[e]), __uint_as_float(t[e + 1]));
+                    v.y = pack_bf16x2(__uint_as_float(t[e + 2]), __uint_as_float(t[e + 3]));
+                    v.z = pack_bf16x2(__uint_as_float(t[e + 4]), __uint_as_float(t[e + 5]));
+                    v.w = pack_bf16x2(__uint_as_float(t[e + 6]), __uint_as_float(t[e + 7]));
+                    *reinterpret_cast<uint4*>(o + e) = v;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, dkv::TMEM_COLS);
+    }
+}
+
+}  // namespace attn_bwd
+}  // namespace lme
+
+// Gradients of lme_attention_fwd.  q / k / v / dout / out layouts as there (token pitches ld*), lse and delta fp32
+// [B, Hq, S_q] (delta = rowsum(dout * out)); dq [B, S_q, Hq, 128], dk / dv [B, S_kv, Hkv, 128] bf16, written whole.
+extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                                 long long ldv, const void* dout, long long lddo, const float* lse,
+                                 const float* delta, void* dq, long long lddq, void* dk, long long lddk, void* dv,
+                                 long long lddv, int B, int S_q, int S_kv, int Hq, int Hkv, int causal, float scale,
+                                 void* stream) {
+    using namespace lme::attn_bwd;
+    if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % ROWS || S_kv % ROWS || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
+    if (causal && S_kv < S_q) return LME_ERR_SHAPE;
+    if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                           reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+                           reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(delta);
+    if (ptrs & 15) return LME_ERR_ALIGN;
+    if ((ldq | ldk | ldv | lddo | lddq | lddk | lddv) % 8) return LME_ERR_ALIGN;
+    const uint64_t wq = static_cast<uint64_t>(Hq) * HD, wk = static_cast<uint64_t>(Hkv) * HD;
+    const uint64_t rq = static_cast<uint64_t>(B) * S_q, rk = static_cast<uint64_t>(B) * S_kv;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM_BYTES) != cudaSuccess)
+            return LME_ERR_LAUNCH;
+        configured = true;
+    }
+    int rc;
+    {   // dQ: Q and dO in 128-row boxes, K and V in 64-row boxes
+        CUtensorMap tq, tdo, tk, tv;
+        if ((rc = lme::make_tmap_bf16_2d(&tq, q, wq, rq, ldq, 64, ROWS))) return rc;
+        if ((rc = lme::make_tmap_bf16_2d(&tdo, dout, wq, rq, lddo, 64, ROWS))) return rc;
+        if ((rc = lme::make_tmap_bf16_2d(&tk, k, wk, rk, ldk, 64, TN))) return rc;
+        if ((rc = lme::make_tmap_bf16_2d(&tv, v, wk, rk, ldv, 64, TN))) return rc;
+        DqArgs a;
+        a.dq = static_cast<__nv_bfloat16*>(dq); a.dq_ld = lddq; a.lse = lse; a.delta = delta;
+        a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.scale = scale;
+        attn_dq_kernel<<<dim3(S_q / ROWS, Hq, B), 192, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
+    }
+    {   // dK, dV: K and V in 128-row boxes, Q and dO in 64-row boxes
+        CUtensorMap tq, tdo, tk, tv;
+        if ((rc = lme::make_tmap_bf16_2d(&tq, q, wq, rq, ldq, 64, TN))) return rc;
+        if ((rc = lme::make_tmap_bf16_2d(&tdo, dout, wq, rq, lddo, 64, TN))) return rc;
+        if ((rc = lme::make_tmap_bf16_2d(&tk, k, wk, rk, ldk, 64, ROWS))) return rc;
+        if ((rc = lme::make_tmap_bf16_2d(&tv, v, wk, rk, ldv, 64, ROWS))) return rc;
+        DkvArgs a;
+        a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv); a.dk_ld = lddk; a.dv_ld = lddv;
+        a.lse = lse; a.delta = delta;
+        a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.scale = scale;
+        attn_dkv_kernel<<<dim3(S_kv / ROWS, Hkv, B), 192, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
+    }
+    return LME_OK;
+}

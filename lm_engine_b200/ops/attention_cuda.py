@@ -1,10 +1,9 @@
-"""Binding of the tcgen05 flash-attention forward kernel (csrc/kernels/attention.cu): head dim 128, bf16, causal or
-full, grouped K/V heads, log-sum-exp output.
+"""Binding of the tcgen05 flash-attention kernels (csrc/kernels/attention.cu, attention_bwd.cu): head dim 128, bf16,
+causal or full, grouped K/V heads; forward with log-sum-exp output, backward as a dQ kernel and a dK / dV kernel
+that own their output rows (no atomics, deterministic).
 
-There is no backward kernel yet, so the dispatcher in :mod:`lm_engine_b200.ops.attention` takes this path only where
-no gradient is recorded - evaluation, generation prefill, and the first forward pass of a block under activation
-checkpointing (which runs under ``no_grad``; the recomputation and the backward use the library kernel) - and only
-when ``LME_ATTENTION=own`` asks for it: it is not yet faster than the library forward."""
+The kernels are opt-in (``LME_ATTENTION=own``): they are not yet as fast as the library kernels the default path
+calls (cuDNN through ``scaled_dot_product_attention``)."""
 
 from __future__ import annotations
 
@@ -29,11 +28,9 @@ def shapes_supported(q, k, v) -> bool:
 def supports(q, k, v, *, causal, sliding_window, attention_mask, cu_seqlens, dropout_p) -> bool:
     if not enabled() or not shapes_supported(q, k, v):
         return False
-    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
     if causal and q.size(1) != k.size(1):
         return False
-    return (not needs_grad and attention_mask is None and dropout_p == 0 and sliding_window is None
-            and cu_seqlens is None)
+    return attention_mask is None and dropout_p == 0 and sliding_window is None and cu_seqlens is None
 
 
 def _token_major(t: torch.Tensor) -> torch.Tensor:
@@ -58,6 +55,40 @@ def flash_attention_forward(q, k, v, *, causal: bool, softmax_scale: float, retu
     return (out, lse) if return_lse else out
 
 
+def flash_attention_backward(dout, q, k, v, out, lse, *, causal: bool, softmax_scale: float):
+    """Returns ``(dq, dk, dv)`` (contiguous ``[B, S, H, 128]``) for operands laid out as in the forward call."""
+    q, k, v, dout = _token_major(q), _token_major(k), _token_major(v), _token_major(dout)
+    B, Sq, Hq, D = q.shape
+    Skv, Hkv = k.size(1), k.size(2)
+    delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()          # [B, Hq, Sq]
+    dq, dk, dv = torch.empty_like(out), k.new_empty((B, Skv, Hkv, D)), k.new_empty((B, Skv, Hkv, D))
+    _lib.check(_lib.cuda_lib().lme_attention_bwd(
+        q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(), v.stride(1), dout.data_ptr(),
+        dout.stride(1), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), Hq * D, dk.data_ptr(), Hkv * D,
+        dv.data_ptr(), Hkv * D, B, Sq, Skv, Hq, Hkv, int(causal), float(softmax_scale), _lib.stream_ptr()),
+        f"lme_attention_bwd B={B} Sq={Sq} Skv={Skv} Hq={Hq} Hkv={Hkv}")
+    _lib.count_launch(2)
+    return dq, dk, dv
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal: bool, scale: float):
+        out, lse = flash_attention_forward(q, k, v, causal=causal, softmax_scale=scale, return_lse=True)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        causal, scale = ctx.cfg
+        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, causal=causal, softmax_scale=scale)
+        return dq, dk, dv, None, None
+
+
 def flash_attention(q, k, v, *, causal, softmax_scale, sliding_window=None, cu_seqlens=None, max_seqlen=None):
     assert sliding_window is None and cu_seqlens is None
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _FlashAttention.apply(q, k, v, bool(causal), float(softmax_scale))
     return flash_attention_forward(q, k, v, causal=causal, softmax_scale=softmax_scale)
