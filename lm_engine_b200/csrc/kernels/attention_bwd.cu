@@ -12,8 +12,8 @@
 // ownership: every output row has exactly one writer, so there is no atomic accumulation of dQ and the result is
 // deterministic.  delta = rowsum(dO * O) comes from the caller.
 //
-// Warp roles, barriers and bounded waits follow attention.cu (warp 0 TMA, warp 1 MMA issuer, warps 2..5 one row
-// per thread); barriers that can run one completion ahead of their waiter are paired by tile parity.
+// Warp roles, barriers and bounded waits follow attention.cu (warp 0 TMA, warp 1 MMA issuer, warps 2..9 one row
+// and half of the streamed columns per thread); barriers that can run one completion ahead of their waiter are paired by tile parity.
 //
 // Role of flash-attn's backward kernels used by the reference (lm_engine/modeling_utils/sequence_mixer_blocks/
 // softmax_attention/utils.py flash_attention).
@@ -46,26 +46,29 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* tile, int row, int chun
 }
 
 namespace dq {
-constexpr int OFF_Q = 0, OFF_DO = BIG, OFF_K = 2 * BIG, OFF_V = OFF_K + 2 * SMALL, OFF_DS = OFF_V + 2 * SMALL;
+// The K/V ring is deeper than the double buffering of S / dP / dS: a stage is held from its load until the dQ
+// product of its tile has read K, so two stages would leave the next load no time to arrive.
+constexpr int NS = 4;
+constexpr int OFF_Q = 0, OFF_DO = BIG, OFF_K = 2 * BIG, OFF_V = OFF_K + NS * SMALL, OFF_DS = OFF_V + NS * SMALL;
 constexpr int OFF_BAR = OFF_DS + 2 * PT;
 constexpr int SMEM_BYTES = OFF_BAR + 256;
 constexpr uint32_t TMEM_COLS = 512;            // S0 S1 | dP0 dP1 (64 each) | dQ (128)
 constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256;
 }  // namespace dq
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const DqArgs p) {
     using namespace dq;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* q_full = bars + 0;
-    uint64_t* kv_full = bars + 1;    // [2]
-    uint64_t* kv_empty = bars + 3;   // [2]
-    uint64_t* sdp_full = bars + 5;   // [2]
-    uint64_t* ds_full = bars + 7;    // [2]
-    uint64_t* dq_done = bars + 9;    // [2]
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* kv_full = bars + 1;    // [NS]
+    uint64_t* kv_empty = bars + 5;   // [NS]
+    uint64_t* sdp_full = bars + 9;   // [2]
+    uint64_t* ds_full = bars + 11;   // [2]
+    uint64_t* dq_done = bars + 13;   // [2]
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 16);
     uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -93,11 +96,13 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&kv_full[s], 1);
             mbar_init(&kv_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(&sdp_full[s], 1);
-            mbar_init(&ds_full[s], 4);
+            mbar_init(&ds_full[s], 8);     // one arrival per row warp
             mbar_init(&dq_done[s], 1);
         }
         fence_barrier_init();
@@ -120,8 +125,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tma_load_2d(smem + OFF_DO, &tmDO, q_full, h * HD, row_q);
             tma_load_2d(smem + OFF_DO + BIG_HALF, &tmDO, q_full, h * HD + 64, row_q);
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, 700 + s)) break;
+                const int s = j % NS;
+                if (!mbar_wait(&kv_empty[s], ((j / NS) & 1) ^ 1, 700 + s)) break;
                 const int row_k = b * p.S_kv + j * TN;
                 uint8_t* ks = smem + OFF_K + s * SMALL;
                 uint8_t* vs = smem + OFF_V + s * SMALL;
@@ -140,10 +145,10 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const uint32_t sq = smem_u32(smem + OFF_Q), sdo = smem_u32(smem + OFF_DO);
             bool ok = mbar_wait(q_full, 0, 710);
             auto issue_sdp = [&](int j) -> bool {
-                const int s = j & 1;
-                if (!mbar_wait(&kv_full[s], (j >> 1) & 1, 720 + s)) return false;
+                const int s = j & 1, st = j % NS;
+                if (!mbar_wait(&kv_full[st], (j / NS) & 1, 720 + st)) return false;
                 tc_fence_after();
-                const uint32_t sk = smem_u32(smem + OFF_K + s * SMALL), sv = smem_u32(smem + OFF_V + s * SMALL);
+                const uint32_t sk = smem_u32(smem + OFF_K + st * SMALL), sv = smem_u32(smem + OFF_V + st * SMALL);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t big = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
@@ -168,19 +173,22 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (!mbar_wait(&ds_full[s], (j >> 1) & 1, 730 + s)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t sds = smem_u32(smem + OFF_DS + s * PT);
-                const uint32_t sk = smem_u32(smem + OFF_K + s * SMALL);
+                const uint32_t sk = smem_u32(smem + OFF_K + (j % NS) * SMALL);
 #pragma unroll
                 for (int kk = 0; kk < TN / 16; ++kk)
                     umma_bf16(tmem_base + TM_DQ, make_smem_desc_sw128(sds + kk * 32, 16, 1024),
                               make_smem_desc_sw128(sk + kk * (16 * 128), SMALL_HALF, 1024), idesc_dq,
                               (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&dq_done[s]);
-                umma_commit(&kv_empty[s]);
+                umma_commit(&kv_empty[j % NS]);
             }
         }
         __syncwarp();
     } else {
+        // eight row warps: warps w and w + 4 share TMEM quadrant w & 3 and each take 32 of the 64 streamed columns
+        // (no row statistics are formed here, so the two halves of a row never talk to each other)
         const int qd = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = qd * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
         const float sl2 = p.scale * LOG2E;
@@ -196,34 +204,30 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tc_fence_after();
             const int k0 = j * TN;
             const bool masked = p.causal && (k0 + TN - 1 > q0 + shift);
-            uint32_t sv[2][32], dp[2][32];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                tmem_ld_32x32(lane_base + TM_S + s * TN + c * 32, sv[c]);
-                tmem_ld_32x32(lane_base + TM_DP + s * TN + c * 32, dp[c]);
-            }
+            uint32_t sv[32], dp[32];
+            tmem_ld_32x32(lane_base + TM_S + s * TN + half * 32, sv);
+            tmem_ld_32x32(lane_base + TM_DP + s * TN + half * 32, dp);
             tmem_ld_wait();
             if (j >= 2) {   // this dS buffer was last read by the dQ product of tile j - 2
                 ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[s], ((j >> 1) - 1) & 1, 755 + s));
                 if (!ok) break;
             }
             uint8_t* tile = smem + OFF_DS + s * PT;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float d0 = ex2(fmaf(__uint_as_float(sv[c][i]), sl2, -lse2)) * (__uint_as_float(dp[c][i]) - delta) * p.scale;
-                    float d1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), sl2, -lse2)) * (__uint_as_float(dp[c][i + 1]) - delta) * p.scale;
+                    float d0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, -lse2)) * (__uint_as_float(dp[i]) - delta) * p.scale;
+                    float d1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2)) * (__uint_as_float(dp[i + 1]) - delta) * p.scale;
                     if (masked) {
-                        if (k0 + c * 32 + i > limit) d0 = 0.f;
-                        if (k0 + c * 32 + i + 1 > limit) d1 = 0.f;
+                        if (k0 + half * 32 + i > limit) d0 = 0.f;
+                        if (k0 + half * 32 + i + 1 > limit) d1 = 0.f;
                     }
                     packed[i >> 1] = pack_bf16x2(d0, d1);
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
-                    store_row_chunk(tile, row, c * 4 + q4,
+                    store_row_chunk(tile, row, half * 4 + q4,
                                     make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]));
             }
             fence_proxy_async_smem();
@@ -236,7 +240,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tc_fence_after();
             __nv_bfloat16* dst = p.dq + (static_cast<long long>(b) * p.S_q + q0 + row) * p.dq_ld + h * HD;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 2 * half; c < 2 * half + 2; ++c) {
                 uint32_t t[32];
                 tmem_ld_32x32(lane_base + TM_DQ + c * 32, t);
                 tmem_ld_wait();
@@ -272,28 +276,29 @@ struct DkvArgs {
 };
 
 namespace dkv {
-constexpr int OFF_K = 0, OFF_V = BIG, OFF_Q = 2 * BIG, OFF_DO = OFF_Q + 2 * SMALL, OFF_PT = OFF_DO + 2 * SMALL;
-constexpr int OFF_DST = OFF_PT + 2 * PT, OFF_STAT = OFF_DST + 2 * PT;     // stats: 2 stages x (64 lse + 64 delta)
+constexpr int NS = 3;       // Q / dO / statistics ring (a stage is held until dV and dK of its tile are done)
+constexpr int OFF_K = 0, OFF_V = BIG, OFF_Q = 2 * BIG, OFF_DO = OFF_Q + NS * SMALL, OFF_PT = OFF_DO + NS * SMALL;
+constexpr int OFF_DST = OFF_PT + 2 * PT, OFF_STAT = OFF_DST + 2 * PT;     // stats: NS stages x (64 lse + 64 delta)
 constexpr int STAT_BYTES = 2 * TN * 4;
-constexpr int OFF_BAR = OFF_STAT + 2 * STAT_BYTES;
+constexpr int OFF_BAR = OFF_STAT + NS * STAT_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256;
 constexpr uint32_t TMEM_COLS = 512;            // S^T0 S^T1 | dP^T0 dP^T1 (64 each) | dV (128) | dK (128)
 constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 384;
 }  // namespace dkv
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const DkvArgs p) {
     using namespace dkv;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* kv_full = bars + 0;
-    uint64_t* qdo_full = bars + 1;   // [2]
-    uint64_t* qdo_empty = bars + 3;  // [2]
-    uint64_t* sdp_full = bars + 5;   // [2]
-    uint64_t* pds_full = bars + 7;   // [2]
-    uint64_t* acc_done = bars + 9;   // [2]
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* qdo_full = bars + 1;   // [NS]
+    uint64_t* qdo_empty = bars + 4;  // [NS]
+    uint64_t* sdp_full = bars + 7;   // [2]
+    uint64_t* pds_full = bars + 9;   // [2]
+    uint64_t* acc_done = bars + 11;  // [2]
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 14);
     uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -317,7 +322,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     if (*poisoned != 0u) return;
     if (n_it <= 0) {        // no query sees these keys: their gradients are zero
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 6) {
             const int row = (warp & 3) * 32 + lane;
             const long long grow = static_cast<long long>(b) * p.S_kv + k0 + row;
             for (int i = 0; i < HD; i += 8) {
@@ -334,11 +339,13 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
         mbar_init(kv_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&qdo_full[s], 1);
             mbar_init(&qdo_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(&sdp_full[s], 1);
-            mbar_init(&pds_full[s], 4);
+            mbar_init(&pds_full[s], 8);    // one arrival per row warp
             mbar_init(&acc_done[s], 1);
         }
         fence_barrier_init();
@@ -361,8 +368,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tma_load_2d(smem + OFF_V, &tmV, kv_full, hk * HD, row_k);
             tma_load_2d(smem + OFF_V + BIG_HALF, &tmV, kv_full, hk * HD + 64, row_k);
             for (int it = 0; it < n_it; ++it) {
-                const int s = it & 1;
-                if (!mbar_wait(&qdo_empty[s], ((it >> 1) & 1) ^ 1, 800 + s)) break;
+                const int s = it % NS;
+                if (!mbar_wait(&qdo_empty[s], ((it / NS) & 1) ^ 1, 800 + s)) break;
                 const int h = hk * G + it / per_g, i = i_start + it % per_g;
                 const int row_q = b * p.S_q + i * TN;
                 uint8_t* qs = smem + OFF_Q + s * SMALL;
@@ -386,10 +393,10 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint32_t sk = smem_u32(smem + OFF_K), sv = smem_u32(smem + OFF_V);
             bool ok = mbar_wait(kv_full, 0, 810);
             auto issue_sdp = [&](int it) -> bool {
-                const int s = it & 1;
-                if (!mbar_wait(&qdo_full[s], (it >> 1) & 1, 820 + s)) return false;
+                const int s = it & 1, st = it % NS;
+                if (!mbar_wait(&qdo_full[st], (it / NS) & 1, 820 + st)) return false;
                 tc_fence_after();
-                const uint32_t sq = smem_u32(smem + OFF_Q + s * SMALL), sdo = smem_u32(smem + OFF_DO + s * SMALL);
+                const uint32_t sq = smem_u32(smem + OFF_Q + st * SMALL), sdo = smem_u32(smem + OFF_DO + st * SMALL);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t big = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
@@ -414,7 +421,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!mbar_wait(&pds_full[s], (it >> 1) & 1, 830 + s)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t spt = smem_u32(smem + OFF_PT + s * PT), sdst = smem_u32(smem + OFF_DST + s * PT);
-                const uint32_t sq = smem_u32(smem + OFF_Q + s * SMALL), sdo = smem_u32(smem + OFF_DO + s * SMALL);
+                const uint32_t sq = smem_u32(smem + OFF_Q + (it % NS) * SMALL), sdo = smem_u32(smem + OFF_DO + (it % NS) * SMALL);
 #pragma unroll
                 for (int kk = 0; kk < TN / 16; ++kk)
                     umma_bf16(tmem_base + TM_DV, make_smem_desc_sw128(spt + kk * 32, 16, 1024),
@@ -426,12 +433,13 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                               make_smem_desc_sw128(sq + kk * (16 * 128), SMALL_HALF, 1024), idesc_acc,
                               (it > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&acc_done[s]);
-                umma_commit(&qdo_empty[s]);
+                umma_commit(&qdo_empty[it % NS]);
             }
         }
         __syncwarp();
     } else {
         const int qd = warp & 3;
+        const int half = (warp - 2) >> 2;             // which 32 of the 64 streamed query columns this warp takes
         const int row = qd * 32 + lane;               // key row inside the tile
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
         const float sl2 = p.scale * LOG2E;
@@ -441,46 +449,42 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int s = it & 1;
             const int i = i_start + it % per_g;
             // the statistics of this tile were written by the bulk copies that complete qdo_full
-            ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[s], (it >> 1) & 1, 845 + s));
+            ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[it % NS], (it / NS) & 1, 845));
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (it >> 1) & 1, 850 + s));
             if (!ok) break;
             tc_fence_after();
             const bool masked = p.causal && (i * TN + shift < k0 + ROWS - 1);
-            uint32_t sv[2][32], dp[2][32];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                tmem_ld_32x32(lane_base + TM_S + s * TN + c * 32, sv[c]);
-                tmem_ld_32x32(lane_base + TM_DP + s * TN + c * 32, dp[c]);
-            }
+            uint32_t sv[32], dp[32];
+            tmem_ld_32x32(lane_base + TM_S + s * TN + half * 32, sv);
+            tmem_ld_32x32(lane_base + TM_DP + s * TN + half * 32, dp);
             tmem_ld_wait();
             if (it >= 2) {   // these operand buffers were last read by the products of iteration it - 2
                 ok = __all_sync(0xffffffffu, mbar_wait(&acc_done[s], ((it >> 1) - 1) & 1, 855 + s));
                 if (!ok) break;
             }
-            const float* st = reinterpret_cast<const float*>(smem + OFF_STAT + s * STAT_BYTES);
+            const float* st = reinterpret_cast<const float*>(smem + OFF_STAT + (it % NS) * STAT_BYTES);
             uint8_t* pt = smem + OFF_PT + s * PT;
             uint8_t* dst = smem + OFF_DST + s * PT;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            {
                 uint32_t pp[16], dd[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    const int col = c * 32 + e;
-                    float p0 = ex2(fmaf(__uint_as_float(sv[c][e]), sl2, -st[col] * LOG2E));
-                    float p1 = ex2(fmaf(__uint_as_float(sv[c][e + 1]), sl2, -st[col + 1] * LOG2E));
+                    const int col = half * 32 + e;
+                    float p0 = ex2(fmaf(__uint_as_float(sv[e]), sl2, -st[col] * LOG2E));
+                    float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), sl2, -st[col + 1] * LOG2E));
                     if (masked) {
                         if (kr > i * TN + col + shift) p0 = 0.f;
                         if (kr > i * TN + col + 1 + shift) p1 = 0.f;
                     }
-                    const float d0 = p0 * (__uint_as_float(dp[c][e]) - st[TN + col]) * p.scale;
-                    const float d1 = p1 * (__uint_as_float(dp[c][e + 1]) - st[TN + col + 1]) * p.scale;
+                    const float d0 = p0 * (__uint_as_float(dp[e]) - st[TN + col]) * p.scale;
+                    const float d1 = p1 * (__uint_as_float(dp[e + 1]) - st[TN + col + 1]) * p.scale;
                     pp[e >> 1] = pack_bf16x2(p0, p1);
                     dd[e >> 1] = pack_bf16x2(d0, d1);
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    store_row_chunk(pt, row, c * 4 + q4, make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]));
-                    store_row_chunk(dst, row, c * 4 + q4, make_uint4(dd[4 * q4], dd[4 * q4 + 1], dd[4 * q4 + 2], dd[4 * q4 + 3]));
+                    store_row_chunk(pt, row, half * 4 + q4, make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]));
+                    store_row_chunk(dst, row, half * 4 + q4, make_uint4(dd[4 * q4], dd[4 * q4 + 1], dd[4 * q4 + 2], dd[4 * q4 + 3]));
                 }
             }
             fence_proxy_async_smem();
@@ -495,7 +499,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             __nv_bfloat16* dvp = p.dv + grow * p.dv_ld + hk * HD;
             __nv_bfloat16* dkp = p.dk + grow * p.dk_ld + hk * HD;
 #pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 4 * half; c < 4 * half + 4; ++c) {      // warps of half 0 store dV, of half 1 dK
                 uint32_t t[32];
                 tmem_ld_32x32(lane_base + TM_DV + c * 32, t);     // columns 256 .. 511: dV then dK
                 tmem_ld_wait();
@@ -560,7 +564,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         DqArgs a;
         a.dq = static_cast<__nv_bfloat16*>(dq); a.dq_ld = lddq; a.lse = lse; a.delta = delta;
         a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.scale = scale;
-        attn_dq_kernel<<<dim3(S_q / ROWS, Hq, B), 192, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        attn_dq_kernel<<<dim3(S_q / ROWS, Hq, B), 320, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     {   // dK, dV: K and V in 128-row boxes, Q and dO in 64-row boxes
@@ -573,7 +577,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv); a.dk_ld = lddk; a.dv_ld = lddv;
         a.lse = lse; a.delta = delta;
         a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.scale = scale;
-        attn_dkv_kernel<<<dim3(S_kv / ROWS, Hkv, B), 192, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        attn_dkv_kernel<<<dim3(S_kv / ROWS, Hkv, B), 320, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     return LME_OK;

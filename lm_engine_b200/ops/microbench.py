@@ -240,10 +240,24 @@ def bench_attention(peaks: dict, small: bool = False) -> list[dict]:
         r = {"name": name, "B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "ms": ours * 1e3, "tflops": flops / ours / 1e12,
              "library_ms": lib * 1e3, "library_tflops": flops / lib / 1e12,
              "frac_of_peak": flops / ours / 1e12 / peaks["bf16_tflops"]}
-        rows.append(r)
         print(f"attention fwd causal {name:9s} B={B} S={S} Hq={Hq} Hkv={Hkv}: ours {r['ms']:7.3f} ms {r['tflops']:6.1f} TF "
               f"({100 * r['frac_of_peak']:4.1f}% of {peaks['source']} GEMM peak)   library {r['library_ms']:7.3f} ms "
               f"{r['library_tflops']:6.1f} TF", flush=True)
+        # backward alone (2.5x the forward FLOPs by the usual count: 5 products against 2)
+        from .attention_cuda import flash_attention_backward
+
+        out, lse = flash_attention_forward(q, k, v, causal=True, softmax_scale=scale, return_lse=True)
+        dout = torch.randn_like(out)
+        bwd = _time(lambda i: flash_attention_backward(dout, q, k, v, out, lse, causal=True, softmax_scale=scale), 1)
+        ql, kl, vl = (t.detach().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+        ol = F.scaled_dot_product_attention(ql, kl, vl, is_causal=True, scale=scale, enable_gqa=True)
+        dl = dout.transpose(1, 2)
+        lib_bwd = _time(lambda i: torch.autograd.grad(ol, (ql, kl, vl), dl, retain_graph=True), 1)
+        r.update({"bwd_ms": bwd * 1e3, "bwd_tflops": 2.5 * flops / bwd / 1e12, "library_bwd_ms": lib_bwd * 1e3,
+                  "library_bwd_tflops": 2.5 * flops / lib_bwd / 1e12})
+        rows.append(r)
+        print(f"attention bwd causal {name:9s}: ours {r['bwd_ms']:7.3f} ms {r['bwd_tflops']:6.1f} TF (incl. the delta "
+              f"pass)   library {r['library_bwd_ms']:7.3f} ms {r['library_bwd_tflops']:6.1f} TF", flush=True)
     return rows
 
 
