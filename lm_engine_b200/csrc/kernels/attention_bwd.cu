@@ -266,6 +266,22 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 }
 
 
+// delta[b, h, s] = sum_d dout[b, s, h, d] * out[b, s, h, d]: one warp per (token, head) row of 128 values
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long lddo, const __nv_bfloat16* __restrict__ out,
+                  long long ldo, float* __restrict__ delta, long long tokens, int S, int H) {
+    const long long rowi = blockIdx.x * 8ll + (threadIdx.x >> 5);     // token * H + h
+    if (rowi >= tokens * H) return;
+    const int lane = threadIdx.x & 31;
+    const long long tok = rowi / H;
+    const int h = static_cast<int>(rowi % H);
+    const uint2 a = *reinterpret_cast<const uint2*>(dout + tok * lddo + h * HD + lane * 4);
+    const uint2 c = *reinterpret_cast<const uint2*>(out + tok * ldo + h * HD + lane * 4);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y);
+    const float v = warp_sum(a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y);
+    if (lane == 0) delta[((tok / S) * H + h) * S + tok % S] = v;
+}
+
 struct DkvArgs {
     __nv_bfloat16 *dk, *dv;
     long long dk_ld, dv_ld;
@@ -528,11 +544,12 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }  // namespace attn_bwd
 }  // namespace lme
 
-// Gradients of lme_attention_fwd.  q / k / v / dout / out layouts as there (token pitches ld*), lse and delta fp32
-// [B, Hq, S_q] (delta = rowsum(dout * out)); dq [B, S_q, Hq, 128], dk / dv [B, S_kv, Hkv, 128] bf16, written whole.
+// Gradients of lme_attention_fwd.  q / k / v / dout / out layouts as there (token pitches ld*), lse fp32
+// [B, Hq, S_q]; delta is fp32 scratch of the same shape (filled here with rowsum(dout * out));
+// dq [B, S_q, Hq, 128], dk / dv [B, S_kv, Hkv, 128] bf16, written whole.
 extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
-                                 long long ldv, const void* dout, long long lddo, const float* lse,
-                                 const float* delta, void* dq, long long lddq, void* dk, long long lddk, void* dv,
+                                 long long ldv, const void* dout, long long lddo, const void* out, long long ldo,
+                                 const float* lse, float* delta, void* dq, long long lddq, void* dk, long long lddk, void* dv,
                                  long long lddv, int B, int S_q, int S_kv, int Hq, int Hkv, int causal, float scale,
                                  void* stream) {
     using namespace lme::attn_bwd;
@@ -553,6 +570,14 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
             cudaFuncSetAttribute(attn_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM_BYTES) != cudaSuccess)
             return LME_ERR_LAUNCH;
         configured = true;
+    }
+    if ((reinterpret_cast<uintptr_t>(out) & 15) || ldo % 8) return LME_ERR_ALIGN;
+    {
+        const long long rows = static_cast<long long>(B) * S_q * Hq;
+        attn_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(dout), lddo, static_cast<const __nv_bfloat16*>(out), ldo, delta,
+            static_cast<long long>(B) * S_q, S_q, Hq);
+        if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     int rc;
     {   // dQ: Q and dO in 128-row boxes, K and V in 64-row boxes

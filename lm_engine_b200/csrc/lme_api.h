@@ -183,10 +183,12 @@ int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk
                       float scale, void* stream);
 
 // Gradients of lme_attention_fwd (kernels/attention_bwd.cu; two kernels, no atomics, deterministic).  dout and out
-// laid out like q; lse and delta = rowsum(dout * out) fp32 [B,Hq,S_q]; dq [B,S_q,Hq,128], dk / dv [B,S_kv,Hkv,128]
-// bf16 with token pitches ldd*, written whole.  S_q and S_kv multiples of 128.
+// laid out like q; lse fp32 [B,Hq,S_q]; delta fp32 scratch of that shape (receives rowsum(dout * out));
+// dq [B,S_q,Hq,128], dk / dv [B,S_kv,Hkv,128] bf16 with token pitches ldd*, written whole.  S_q and S_kv multiples
+// of 128.
 int lme_attention_bwd(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
-                      const void* dout, long long lddo, const float* lse, const float* delta, void* dq,
+                      const void* dout, long long lddo, const void* out, long long ldo, const float* lse,
+                      float* delta, void* dq,
                       long long lddq, void* dk, long long lddk, void* dv, long long lddv, int B, int S_q, int S_kv,
                       int Hq, int Hkv, int causal, float scale, void* stream);
 

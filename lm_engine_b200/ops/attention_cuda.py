@@ -60,14 +60,15 @@ def flash_attention_backward(dout, q, k, v, out, lse, *, causal: bool, softmax_s
     q, k, v, dout = _token_major(q), _token_major(k), _token_major(v), _token_major(dout)
     B, Sq, Hq, D = q.shape
     Skv, Hkv = k.size(1), k.size(2)
-    delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()          # [B, Hq, Sq]
-    dq, dk, dv = torch.empty_like(out), k.new_empty((B, Skv, Hkv, D)), k.new_empty((B, Skv, Hkv, D))
+    out = _token_major(out)
+    delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)             # rowsum(dout * out), filled by the call
+    dq, dk, dv = q.new_empty((B, Sq, Hq, D)), k.new_empty((B, Skv, Hkv, D)), k.new_empty((B, Skv, Hkv, D))
     _lib.check(_lib.cuda_lib().lme_attention_bwd(
         q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(), v.stride(1), dout.data_ptr(),
-        dout.stride(1), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), Hq * D, dk.data_ptr(), Hkv * D,
+        dout.stride(1), out.data_ptr(), out.stride(1), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), Hq * D, dk.data_ptr(), Hkv * D,
         dv.data_ptr(), Hkv * D, B, Sq, Skv, Hq, Hkv, int(causal), float(softmax_scale), _lib.stream_ptr()),
         f"lme_attention_bwd B={B} Sq={Sq} Skv={Skv} Hq={Hq} Hkv={Hkv}")
-    _lib.count_launch(2)
+    _lib.count_launch(3)
     return dq, dk, dv
 
 
