@@ -40,6 +40,7 @@ struct Args {
     float* lse;
     long long o_ld;            // row pitch of o in elements
     int B, S_q, S_kv, Hq, Hkv, causal;
+    int window;                // > 0 (with causal): query i sees keys in (i + shift - window, i + shift]
     float scale;               // softmax scale (natural units)
 };
 
@@ -75,6 +76,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int shift = p.S_kv - p.S_q;                  // query row i may see keys <= i + shift
     int n_tiles = p.S_kv / BN;
     if (p.causal) n_tiles = min(n_tiles, (q0 + BM + shift + BN - 1) / BN);
+    // a sliding window also skips the tiles before the first key the first row sees; j below counts from there
+    const int j_begin = (p.causal && p.window > 0) ? max(0, (q0 + shift - p.window + 1) / BN) : 0;
+    n_tiles -= j_begin;
 
     if (threadIdx.x == 0) {
         *poisoned = lme_status[0];
@@ -122,8 +126,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) return false;
                 uint8_t* ks = smem + OFF_K + s * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
-                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, b * p.S_kv + j * BN);
-                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, b * p.S_kv + j * BN);
+                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, b * p.S_kv + (j_begin + j) * BN);
+                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, b * p.S_kv + (j_begin + j) * BN);
                 return true;
             };
             bool ok = load_k(0);
@@ -133,8 +137,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!mbar_wait(v_empty, (j & 1) ^ 1, 605)) break;
                 uint8_t* vs = smem + OFF_V;
                 mbar_expect_tx(v_full, KV_BYTES);
-                tma_load_2d(vs, &tmV, v_full, hk * HD, b * p.S_kv + j * BN);
-                tma_load_2d(vs + KV_HALF, &tmV, v_full, hk * HD + 64, b * p.S_kv + j * BN);
+                tma_load_2d(vs, &tmV, v_full, hk * HD, b * p.S_kv + (j_begin + j) * BN);
+                tma_load_2d(vs + KV_HALF, &tmV, v_full, hk * HD + 64, b * p.S_kv + (j_begin + j) * BN);
             }
         }
         __syncwarp();
@@ -191,6 +195,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t to = lane_base + TM_O;         // the O accumulator
         const float sl2 = p.scale * 1.4426950408889634f;
         const int limit = q0 + row + shift;           // last visible key of this row (causal)
+        const int low = p.window > 0 ? limit - p.window : -1;   // last key below this row's window
         // m is the maximum the exponents are taken against.  It follows the true row maximum lazily: O (in TMEM) and
         // l are rescaled only when the maximum grew by more than 2^8, so P stays below 256 and most tiles skip the
         // read-modify-write of O altogether.
@@ -204,8 +209,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             const uint32_t ts = lane_base + TM_S + s * BN;
-            const int k0 = j * BN;
-            const bool masked = p.causal && (k0 + BN - 1 > q0 + shift);
+            const int k0 = (j_begin + j) * BN;
+            // the tile crosses the causal diagonal of some row, or the lower edge of some row's window
+            const bool masked = p.causal && (k0 + BN - 1 > q0 + shift ||
+                                             (p.window > 0 && k0 <= q0 + BM - 1 + shift - p.window));
             uint32_t r[BN / 32][32];
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32(ts + c * 32, r[c]);
@@ -215,7 +222,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int c = 0; c < BN / 32; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    if (masked && k0 + c * 32 + i > limit) r[c][i] = 0xff800000u;   // -inf: exp2 gives 0
+                    if (masked && (k0 + c * 32 + i > limit || k0 + c * 32 + i <= low)) r[c][i] = 0xff800000u;   // -inf: exp2 gives 0
                     mx = fmaxf(mx, __uint_as_float(r[c][i]));
                 }
             const float m_new = fmaxf(m, mx);
@@ -314,10 +321,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // q [B, S_q, Hq, 128], k / v [B, S_kv, Hkv, 128] bf16 with the 128 values of a head contiguous, heads contiguous
 // inside a token, token pitch ld* elements and batches back to back (pitch S * ld); o [B, S_q, Hq, 128] bf16 with
 // token pitch ldo; lse fp32 [B, Hq, S_q] or null.  S_q and S_kv are multiples of 128; causal aligns the last query
-// with the last key.
+// with the last key; window > 0 (causal only) keeps the last `window` visible keys of every query.
 extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                                  long long ldv, void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq,
-                                 int Hkv, int causal, float scale, void* stream) {
+                                 int Hkv, int causal, int window, float scale, void* stream) {
     using lme::attn::Args;
     using lme::attn::HD;
     using lme::attn::SMEM_BYTES;
@@ -325,6 +332,7 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     constexpr int BM = lme::attn::BM, BN = lme::attn::BN;
     if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % BM || S_kv % BN || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
+    if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
     if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(o)) & 15)
@@ -348,7 +356,7 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     p.o = static_cast<__nv_bfloat16*>(o);
     p.lse = lse;
     p.o_ld = ldo;
-    p.B = B; p.S_q = S_q; p.S_kv = S_kv; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+    p.B = B; p.S_q = S_q; p.S_kv = S_kv; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.window = window;
     p.scale = scale;
     dim3 grid(S_q / BM, Hq, B);
     attn_fwd_kernel<<<grid, 192, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);

@@ -36,7 +36,7 @@ struct DqArgs {
     long long dq_ld;
     const float* lse;        // [B, Hq, S_q] natural log
     const float* delta;      // [B, Hq, S_q]
-    int B, S_q, S_kv, Hq, Hkv, causal;
+    int B, S_q, S_kv, Hq, Hkv, causal, window;
     float scale;
 };
 
@@ -79,6 +79,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int shift = p.S_kv - p.S_q;
     int n_tiles = p.S_kv / TN;
     if (p.causal) n_tiles = min(n_tiles, (q0 + ROWS + shift + TN - 1) / TN);
+    // sliding window: skip the tiles before the first key the first row sees; j below counts from there
+    const int j_begin = (p.causal && p.window > 0) ? max(0, (q0 + shift - p.window + 1) / TN) : 0;
+    n_tiles -= j_begin;
 
     if (threadIdx.x == 0) {
         *poisoned = lme_status[0];
@@ -127,7 +130,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % NS;
                 if (!mbar_wait(&kv_empty[s], ((j / NS) & 1) ^ 1, 700 + s)) break;
-                const int row_k = b * p.S_kv + j * TN;
+                const int row_k = b * p.S_kv + (j_begin + j) * TN;
                 uint8_t* ks = smem + OFF_K + s * SMALL;
                 uint8_t* vs = smem + OFF_V + s * SMALL;
                 mbar_expect_tx(&kv_full[s], 2 * SMALL);
@@ -193,6 +196,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
         const float sl2 = p.scale * LOG2E;
         const int limit = q0 + row + shift;
+        const int low = p.window > 0 ? limit - p.window : -1;
         const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_q + q0 + row;
         const float lse2 = p.lse[stat] * LOG2E;
         const float delta = p.delta[stat];
@@ -202,8 +206,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (j >> 1) & 1, 750 + s));
             if (!ok) break;
             tc_fence_after();
-            const int k0 = j * TN;
-            const bool masked = p.causal && (k0 + TN - 1 > q0 + shift);
+            const int k0 = (j_begin + j) * TN;
+            const bool masked = p.causal && (k0 + TN - 1 > q0 + shift ||
+                                             (p.window > 0 && k0 <= q0 + ROWS - 1 + shift - p.window));
             uint32_t sv[32], dp[32];
             tmem_ld_32x32(lane_base + TM_S + s * TN + half * 32, sv);
             tmem_ld_32x32(lane_base + TM_DP + s * TN + half * 32, dp);
@@ -220,8 +225,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     float d0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, -lse2)) * (__uint_as_float(dp[i]) - delta) * p.scale;
                     float d1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2)) * (__uint_as_float(dp[i + 1]) - delta) * p.scale;
                     if (masked) {
-                        if (k0 + half * 32 + i > limit) d0 = 0.f;
-                        if (k0 + half * 32 + i + 1 > limit) d1 = 0.f;
+                        if (k0 + half * 32 + i > limit || k0 + half * 32 + i <= low) d0 = 0.f;
+                        if (k0 + half * 32 + i + 1 > limit || k0 + half * 32 + i + 1 <= low) d1 = 0.f;
                     }
                     packed[i >> 1] = pack_bf16x2(d0, d1);
                 }
@@ -287,7 +292,7 @@ struct DkvArgs {
     long long dk_ld, dv_ld;
     const float* lse;        // [B, Hq, S_q] natural log
     const float* delta;      // [B, Hq, S_q]
-    int B, S_q, S_kv, Hq, Hkv, causal;
+    int B, S_q, S_kv, Hq, Hkv, causal, window;
     float scale;
 };
 
@@ -325,7 +330,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int nq = p.S_q / TN;
     // first query tile with a row that sees key k0: 64 i + 63 + shift >= k0
     const int i_start = p.causal ? max(0, (k0 - shift) / TN) : 0;
-    const int per_g = nq - i_start;
+    // sliding window: the last query that sees key k0 + 127 is k0 + 127 - shift + window - 1
+    const int i_end = (p.causal && p.window > 0) ? min(nq, (k0 + ROWS - 1 - shift + p.window - 1) / TN + 1) : nq;
+    const int per_g = i_end - i_start;
     const int n_it = per_g > 0 ? G * per_g : 0;
 
     if (threadIdx.x == 0) {
@@ -469,7 +476,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (it >> 1) & 1, 850 + s));
             if (!ok) break;
             tc_fence_after();
-            const bool masked = p.causal && (i * TN + shift < k0 + ROWS - 1);
+            const bool masked = p.causal && (i * TN + shift < k0 + ROWS - 1 ||
+                                             (p.window > 0 && i * TN + TN - 1 + shift >= k0 + p.window));
             uint32_t sv[32], dp[32];
             tmem_ld_32x32(lane_base + TM_S + s * TN + half * 32, sv);
             tmem_ld_32x32(lane_base + TM_DP + s * TN + half * 32, dp);
@@ -489,8 +497,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     float p0 = ex2(fmaf(__uint_as_float(sv[e]), sl2, -st[col] * LOG2E));
                     float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), sl2, -st[col + 1] * LOG2E));
                     if (masked) {
-                        if (kr > i * TN + col + shift) p0 = 0.f;
-                        if (kr > i * TN + col + 1 + shift) p1 = 0.f;
+                        const int qv = i * TN + col + shift;          // key limit of query column `col`
+                        if (kr > qv || (p.window > 0 && kr <= qv - p.window)) p0 = 0.f;
+                        if (kr > qv + 1 || (p.window > 0 && kr <= qv + 1 - p.window)) p1 = 0.f;
                     }
                     const float d0 = p0 * (__uint_as_float(dp[e]) - st[TN + col]) * p.scale;
                     const float d1 = p1 * (__uint_as_float(dp[e + 1]) - st[TN + col + 1]) * p.scale;
@@ -550,11 +559,12 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                                  long long ldv, const void* dout, long long lddo, const void* out, long long ldo,
                                  const float* lse, float* delta, void* dq, long long lddq, void* dk, long long lddk, void* dv,
-                                 long long lddv, int B, int S_q, int S_kv, int Hq, int Hkv, int causal, float scale,
-                                 void* stream) {
+                                 long long lddv, int B, int S_q, int S_kv, int Hq, int Hkv, int causal, int window,
+                                 float scale, void* stream) {
     using namespace lme::attn_bwd;
     if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % ROWS || S_kv % ROWS || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
+    if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
     if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                            reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
@@ -588,7 +598,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         if ((rc = lme::make_tmap_bf16_2d(&tv, v, wk, rk, ldv, 64, TN))) return rc;
         DqArgs a;
         a.dq = static_cast<__nv_bfloat16*>(dq); a.dq_ld = lddq; a.lse = lse; a.delta = delta;
-        a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.scale = scale;
+        a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.window = window; a.scale = scale;
         attn_dq_kernel<<<dim3(S_q / ROWS, Hq, B), 320, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
@@ -601,7 +611,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         DkvArgs a;
         a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv); a.dk_ld = lddk; a.dv_ld = lddv;
         a.lse = lse; a.delta = delta;
-        a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.scale = scale;
+        a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.window = window; a.scale = scale;
         attn_dkv_kernel<<<dim3(S_kv / ROWS, Hkv, B), 320, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }

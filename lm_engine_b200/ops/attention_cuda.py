@@ -26,11 +26,13 @@ def shapes_supported(q, k, v) -> bool:
 
 
 def supports(q, k, v, *, causal, sliding_window, attention_mask, cu_seqlens, dropout_p) -> bool:
-    if not enabled() or not shapes_supported(q, k, v):
+    """The switch selects these kernels; causal sliding-window attention takes them regardless, because the library
+    path has no windowed kernel and the alternative materialises the full score matrix."""
+    if not shapes_supported(q, k, v) or attention_mask is not None or dropout_p != 0 or cu_seqlens is not None:
         return False
-    if causal and q.size(1) != k.size(1):
-        return False
-    return attention_mask is None and dropout_p == 0 and sliding_window is None and cu_seqlens is None
+    if sliding_window is not None:
+        return bool(causal)
+    return enabled() and (not causal or q.size(1) == k.size(1))
 
 
 def _token_major(t: torch.Tensor) -> torch.Tensor:
@@ -41,7 +43,8 @@ def _token_major(t: torch.Tensor) -> torch.Tensor:
     return t if ok else t.contiguous()
 
 
-def flash_attention_forward(q, k, v, *, causal: bool, softmax_scale: float, return_lse: bool = False):
+def flash_attention_forward(q, k, v, *, causal: bool, softmax_scale: float, return_lse: bool = False,
+                            sliding_window: int | None = None):
     q, k, v = _token_major(q), _token_major(k), _token_major(v)
     B, Sq, Hq, D = q.shape
     Skv, Hkv = k.size(1), k.size(2)
@@ -49,13 +52,15 @@ def flash_attention_forward(q, k, v, *, causal: bool, softmax_scale: float, retu
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device) if return_lse else None
     _lib.check(_lib.cuda_lib().lme_attention_fwd(q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(),
                                                  v.stride(1), out.data_ptr(), Hq * D, _lib.ptr(lse), B, Sq, Skv, Hq,
-                                                 Hkv, int(causal), float(softmax_scale), _lib.stream_ptr()),
+                                                 Hkv, int(causal), int(sliding_window or 0), float(softmax_scale),
+                                                 _lib.stream_ptr()),
                f"lme_attention_fwd B={B} Sq={Sq} Skv={Skv} Hq={Hq} Hkv={Hkv}")
     _lib.count_launch()
     return (out, lse) if return_lse else out
 
 
-def flash_attention_backward(dout, q, k, v, out, lse, *, causal: bool, softmax_scale: float):
+def flash_attention_backward(dout, q, k, v, out, lse, *, causal: bool, softmax_scale: float,
+                             sliding_window: int | None = None):
     """Returns ``(dq, dk, dv)`` (contiguous ``[B, S, H, 128]``) for operands laid out as in the forward call."""
     q, k, v, dout = _token_major(q), _token_major(k), _token_major(v), _token_major(dout)
     B, Sq, Hq, D = q.shape
@@ -66,7 +71,8 @@ def flash_attention_backward(dout, q, k, v, out, lse, *, causal: bool, softmax_s
     _lib.check(_lib.cuda_lib().lme_attention_bwd(
         q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(), v.stride(1), dout.data_ptr(),
         dout.stride(1), out.data_ptr(), out.stride(1), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), Hq * D, dk.data_ptr(), Hkv * D,
-        dv.data_ptr(), Hkv * D, B, Sq, Skv, Hq, Hkv, int(causal), float(softmax_scale), _lib.stream_ptr()),
+        dv.data_ptr(), Hkv * D, B, Sq, Skv, Hq, Hkv, int(causal), int(sliding_window or 0), float(softmax_scale),
+        _lib.stream_ptr()),
         f"lme_attention_bwd B={B} Sq={Sq} Skv={Skv} Hq={Hq} Hkv={Hkv}")
     _lib.count_launch(3)
     return dq, dk, dv
@@ -74,22 +80,24 @@ def flash_attention_backward(dout, q, k, v, out, lse, *, causal: bool, softmax_s
 
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal: bool, scale: float):
-        out, lse = flash_attention_forward(q, k, v, causal=causal, softmax_scale=scale, return_lse=True)
+    def forward(ctx, q, k, v, causal: bool, scale: float, window: int | None = None):
+        out, lse = flash_attention_forward(q, k, v, causal=causal, softmax_scale=scale, return_lse=True,
+                                           sliding_window=window)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.cfg = (causal, scale)
+        ctx.cfg = (causal, scale, window)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        causal, scale = ctx.cfg
-        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, causal=causal, softmax_scale=scale)
-        return dq, dk, dv, None, None
+        causal, scale, window = ctx.cfg
+        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, causal=causal, softmax_scale=scale,
+                                              sliding_window=window)
+        return dq, dk, dv, None, None, None
 
 
 def flash_attention(q, k, v, *, causal, softmax_scale, sliding_window=None, cu_seqlens=None, max_seqlen=None):
-    assert sliding_window is None and cu_seqlens is None
+    assert cu_seqlens is None
     if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        return _FlashAttention.apply(q, k, v, bool(causal), float(softmax_scale))
-    return flash_attention_forward(q, k, v, causal=causal, softmax_scale=softmax_scale)
+        return _FlashAttention.apply(q, k, v, bool(causal), float(softmax_scale), sliding_window)
+    return flash_attention_forward(q, k, v, causal=causal, softmax_scale=softmax_scale, sliding_window=sliding_window)

@@ -73,6 +73,36 @@ def test_attention_backward_matches_reference(B, S, Hq, Hkv, causal):
         assert err < 2e-2, (name, err)
 
 
+@pytest.mark.parametrize("B,S,Hq,Hkv,window", [(1, 256, 2, 1, 64), (2, 640, 4, 2, 200), (1, 512, 2, 2, 129),
+                                                  (1, 384, 2, 2, 1000)])
+def test_sliding_window_matches_reference(B, S, Hq, Hkv, window):
+    """Causal sliding-window attention takes the kernels without the switch (forward and every gradient)."""
+    from lm_engine_b200.ops import _lib
+    from lm_engine_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(2)
+    D = 128
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    ref_in = qkv.detach().float().requires_grad_(True)
+
+    def split(t):
+        return [x.view(B, S, -1, D) for x in t.split((Hq * D, Hkv * D, Hkv * D), dim=-1)]
+
+    launches = _lib.launch_count
+    out = attention(*split(qkv), causal=True, sliding_window=window)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    assert _lib.launch_count >= launches + 4              # forward + delta + dQ + dK/dV: the kernels ran
+    ref = attention_reference(*split(ref_in), causal=True, sliding_window=window)
+    ref.backward(dout.float())
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for name, a, b in zip("qkv", split(qkv.grad.float()), split(ref_in.grad)):
+        err = float((a - b).norm() / (b.norm() + 1e-6))
+        assert err < 2e-2, (name, err)
+
+
 def test_dispatcher_follows_the_switch(monkeypatch):
     from lm_engine_b200.ops import attention_cuda
     from lm_engine_b200.ops.attention import attention
