@@ -41,6 +41,8 @@ struct Args {
     long long o_ld;            // row pitch of o in elements
     int B, S_q, S_kv, Hq, Hkv, causal;
     int window;                // > 0 (with causal): query i sees keys in (i + shift - window, i + shift]
+    const int* cu_seqlens;     // packed sequences: tokens of sequence b are rows cu[b] .. cu[b+1]-1 (self-attention)
+    int S_pad;                 // row pitch of lse: S_q, or the padded maximum length for packed sequences
     float scale;               // softmax scale (natural units)
 };
 
@@ -73,9 +75,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.Hq / p.Hkv);
     const int q0 = qb * BM;
-    const int shift = p.S_kv - p.S_q;                  // query row i may see keys <= i + shift
-    int n_tiles = p.S_kv / BN;
+    // rows of this sequence in the token-major operands, and its lengths
+    int tok_q = b * p.S_q, tok_k = b * p.S_kv, len_q = p.S_q, len_k = p.S_kv;
+    if (p.cu_seqlens != nullptr) {
+        tok_q = tok_k = p.cu_seqlens[b];
+        len_q = len_k = p.cu_seqlens[b + 1] - tok_q;
+    }
+    const int shift = len_k - len_q;                   // query row i may see keys <= i + shift
+    int n_tiles = (len_k + BN - 1) / BN;
     if (p.causal) n_tiles = min(n_tiles, (q0 + BM + shift + BN - 1) / BN);
+    if (q0 >= len_q) n_tiles = 0;                      // a query block past the end of a packed sequence
     // a sliding window also skips the tiles before the first key the first row sees; j below counts from there
     const int j_begin = (p.causal && p.window > 0) ? max(0, (q0 + shift - p.window + 1) / BN) : 0;
     n_tiles -= j_begin;
@@ -117,7 +126,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     if (warp == 0) {
         if (lane == 0) {
-            const int row_q = b * p.S_q + q0;
+            const int row_q = tok_q + q0;
             mbar_expect_tx(q_full, Q_BYTES);
             tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
             tma_load_2d(smem + OFF_Q + Q_HALF, &tmQ, q_full, h * HD + 64, row_q);
@@ -126,8 +135,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) return false;
                 uint8_t* ks = smem + OFF_K + s * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
-                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, b * p.S_kv + (j_begin + j) * BN);
-                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, b * p.S_kv + (j_begin + j) * BN);
+                tma_load_2d(ks, &tmK, &k_full[s], hk * HD, tok_k + (j_begin + j) * BN);
+                tma_load_2d(ks + KV_HALF, &tmK, &k_full[s], hk * HD + 64, tok_k + (j_begin + j) * BN);
                 return true;
             };
             bool ok = load_k(0);
@@ -137,8 +146,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!mbar_wait(v_empty, (j & 1) ^ 1, 605)) break;
                 uint8_t* vs = smem + OFF_V;
                 mbar_expect_tx(v_full, KV_BYTES);
-                tma_load_2d(vs, &tmV, v_full, hk * HD, b * p.S_kv + (j_begin + j) * BN);
-                tma_load_2d(vs + KV_HALF, &tmV, v_full, hk * HD + 64, b * p.S_kv + (j_begin + j) * BN);
+                tma_load_2d(vs, &tmV, v_full, hk * HD, tok_k + (j_begin + j) * BN);
+                tma_load_2d(vs + KV_HALF, &tmV, v_full, hk * HD + 64, tok_k + (j_begin + j) * BN);
             }
         }
         __syncwarp();
@@ -194,8 +203,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
         const uint32_t to = lane_base + TM_O;         // the O accumulator
         const float sl2 = p.scale * 1.4426950408889634f;
-        const int limit = q0 + row + shift;           // last visible key of this row (causal)
-        const int low = p.window > 0 ? limit - p.window : -1;   // last key below this row's window
+        // last visible key of this row: the causal diagonal and / or the end of the (packed) sequence
+        const int limit = p.causal ? min(q0 + row + shift, len_k - 1) : len_k - 1;
+        const int low = p.window > 0 ? q0 + row + shift - p.window : -1;   // last key below this row's window
         // m is the maximum the exponents are taken against.  It follows the true row maximum lazily: O (in TMEM) and
         // l are rescaled only when the maximum grew by more than 2^8, so P stays below 256 and most tiles skip the
         // read-modify-write of O altogether.
@@ -211,8 +221,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint32_t ts = lane_base + TM_S + s * BN;
             const int k0 = (j_begin + j) * BN;
             // the tile crosses the causal diagonal of some row, or the lower edge of some row's window
-            const bool masked = p.causal && (k0 + BN - 1 > q0 + shift ||
-                                             (p.window > 0 && k0 <= q0 + BM - 1 + shift - p.window));
+            const bool masked = k0 + BN > len_k ||
+                                (p.causal && (k0 + BN - 1 > q0 + shift ||
+                                              (p.window > 0 && k0 <= q0 + BM - 1 + shift - p.window)));
             uint32_t r[BN / 32][32];
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32(ts + c * 32, r[c]);
@@ -282,9 +293,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 670));
         if (ok) {
+            const bool valid = q0 + row < len_q;    // tcgen05.ld is warp-collective: only the stores are predicated
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            const long long grow = static_cast<long long>(b) * p.S_q + q0 + row;
+            const long long grow = static_cast<long long>(tok_q) + q0 + row;
             __nv_bfloat16* dst = p.o + grow * p.o_ld + h * HD;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -298,11 +310,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     v.y = pack_bf16x2(__uint_as_float(t[i + 2]) * inv, __uint_as_float(t[i + 3]) * inv);
                     v.z = pack_bf16x2(__uint_as_float(t[i + 4]) * inv, __uint_as_float(t[i + 5]) * inv);
                     v.w = pack_bf16x2(__uint_as_float(t[i + 6]) * inv, __uint_as_float(t[i + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+                    if (valid) *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
                 }
             }
-            if (p.lse)
-                p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S_q + q0 + row] =
+            if (p.lse && valid)
+                p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S_pad + q0 + row] =
                     l > 0.f ? m * p.scale + __logf(l) : -INFINITY;
         }
     }
@@ -322,15 +334,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // inside a token, token pitch ld* elements and batches back to back (pitch S * ld); o [B, S_q, Hq, 128] bf16 with
 // token pitch ldo; lse fp32 [B, Hq, S_q] or null.  S_q and S_kv are multiples of 128; causal aligns the last query
 // with the last key; window > 0 (causal only) keeps the last `window` visible keys of every query.
+// Packed sequences: cu_seqlens (int32 [B + 1], device) with q / k / v / o as [total_tokens, H, 128], S_q = S_kv = the
+// longest sequence and lse [B, Hq, S_pad], S_pad = S_q rounded up to 128.
 extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                                  long long ldv, void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq,
-                                 int Hkv, int causal, int window, float scale, void* stream) {
+                                 int Hkv, int causal, int window, float scale, const int* cu_seqlens,
+                                 long long total_tokens, void* stream) {
     using lme::attn::Args;
     using lme::attn::HD;
     using lme::attn::SMEM_BYTES;
     using lme::attn::attn_fwd_kernel;
     constexpr int BM = lme::attn::BM, BN = lme::attn::BN;
-    if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % BM || S_kv % BN || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
+    if (B <= 0 || S_q <= 0 || S_kv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
+    // packed sequences (cu_seqlens): B sequences, S_q = S_kv = the longest one, any lengths; else multiples of 128
+    if (cu_seqlens ? (S_q != S_kv || total_tokens <= 0) : (S_q % BM || S_kv % BM)) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
     if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
     if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
@@ -339,11 +356,13 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
         return LME_ERR_ALIGN;
     if ((ldq | ldk | ldv | ldo) % 8) return LME_ERR_ALIGN;
     CUtensorMap tq, tk, tv;
-    int rc = lme::make_tmap_bf16_2d(&tq, q, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(B) * S_q, ldq, 64, BM);
+    const uint64_t rows_q = cu_seqlens ? static_cast<uint64_t>(total_tokens) : static_cast<uint64_t>(B) * S_q;
+    const uint64_t rows_k = cu_seqlens ? static_cast<uint64_t>(total_tokens) : static_cast<uint64_t>(B) * S_kv;
+    int rc = lme::make_tmap_bf16_2d(&tq, q, static_cast<uint64_t>(Hq) * HD, rows_q, ldq, 64, BM);
     if (rc) return rc;
-    rc = lme::make_tmap_bf16_2d(&tk, k, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldk, 64, BN);
+    rc = lme::make_tmap_bf16_2d(&tk, k, static_cast<uint64_t>(Hkv) * HD, rows_k, ldk, 64, BN);
     if (rc) return rc;
-    rc = lme::make_tmap_bf16_2d(&tv, v, static_cast<uint64_t>(Hkv) * HD, static_cast<uint64_t>(B) * S_kv, ldv, 64, BN);
+    rc = lme::make_tmap_bf16_2d(&tv, v, static_cast<uint64_t>(Hkv) * HD, rows_k, ldv, 64, BN);
     if (rc) return rc;
     static bool configured = false;
     if (!configured) {
@@ -357,8 +376,10 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     p.lse = lse;
     p.o_ld = ldo;
     p.B = B; p.S_q = S_q; p.S_kv = S_kv; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.window = window;
+    p.cu_seqlens = cu_seqlens;
+    p.S_pad = (S_q + BM - 1) / BM * BM;
     p.scale = scale;
-    dim3 grid(S_q / BM, Hq, B);
+    dim3 grid((S_q + BM - 1) / BM, Hq, B);
     attn_fwd_kernel<<<grid, 192, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }

@@ -38,6 +38,8 @@ struct DqArgs {
     const float* delta;      // [B, Hq, S_q]
     int B, S_q, S_kv, Hq, Hkv, causal, window;
     float scale;
+    const int* cu_seqlens;   // packed sequences (self-attention): rows cu[b] .. cu[b+1]-1; null = [B, S] batches
+    int S_pad;               // row pitch of lse / delta
 };
 
 // row r of a 128 x 64 K-major operand tile: 16-byte chunk c (8 columns) lands at chunk c ^ (r & 7)
@@ -76,9 +78,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.Hq / p.Hkv);
     const int q0 = qb * ROWS;
-    const int shift = p.S_kv - p.S_q;
-    int n_tiles = p.S_kv / TN;
+    int tok_q = b * p.S_q, tok_k = b * p.S_kv, len_q = p.S_q, len_k = p.S_kv;
+    if (p.cu_seqlens != nullptr) {
+        tok_q = tok_k = p.cu_seqlens[b];
+        len_q = len_k = p.cu_seqlens[b + 1] - tok_q;
+    }
+    const int shift = len_k - len_q;
+    int n_tiles = (len_k + TN - 1) / TN;
     if (p.causal) n_tiles = min(n_tiles, (q0 + ROWS + shift + TN - 1) / TN);
+    if (q0 >= len_q) n_tiles = 0;
     // sliding window: skip the tiles before the first key the first row sees; j below counts from there
     const int j_begin = (p.causal && p.window > 0) ? max(0, (q0 + shift - p.window + 1) / TN) : 0;
     n_tiles -= j_begin;
@@ -121,7 +129,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            const int row_q = b * p.S_q + q0;
+            const int row_q = tok_q + q0;
             mbar_expect_tx(q_full, 2 * BIG);
             tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
             tma_load_2d(smem + OFF_Q + BIG_HALF, &tmQ, q_full, h * HD + 64, row_q);
@@ -130,7 +138,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % NS;
                 if (!mbar_wait(&kv_empty[s], ((j / NS) & 1) ^ 1, 700 + s)) break;
-                const int row_k = b * p.S_kv + (j_begin + j) * TN;
+                const int row_k = tok_k + (j_begin + j) * TN;
                 uint8_t* ks = smem + OFF_K + s * SMALL;
                 uint8_t* vs = smem + OFF_V + s * SMALL;
                 mbar_expect_tx(&kv_full[s], 2 * SMALL);
@@ -195,9 +203,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int row = qd * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
         const float sl2 = p.scale * LOG2E;
-        const int limit = q0 + row + shift;
-        const int low = p.window > 0 ? limit - p.window : -1;
-        const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_q + q0 + row;
+        const int limit = p.causal ? min(q0 + row + shift, len_k - 1) : len_k - 1;
+        const int low = p.window > 0 ? q0 + row + shift - p.window : -1;
+        const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_pad + q0 + row;
         const float lse2 = p.lse[stat] * LOG2E;
         const float delta = p.delta[stat];
         bool ok = true;
@@ -207,8 +215,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (!ok) break;
             tc_fence_after();
             const int k0 = (j_begin + j) * TN;
-            const bool masked = p.causal && (k0 + TN - 1 > q0 + shift ||
-                                             (p.window > 0 && k0 <= q0 + ROWS - 1 + shift - p.window));
+            const bool masked = k0 + TN > len_k ||
+                                (p.causal && (k0 + TN - 1 > q0 + shift ||
+                                              (p.window > 0 && k0 <= q0 + ROWS - 1 + shift - p.window)));
             uint32_t sv[32], dp[32];
             tmem_ld_32x32(lane_base + TM_S + s * TN + half * 32, sv);
             tmem_ld_32x32(lane_base + TM_DP + s * TN + half * 32, dp);
@@ -243,7 +252,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 770));
         if (ok) {
             tc_fence_after();
-            __nv_bfloat16* dst = p.dq + (static_cast<long long>(b) * p.S_q + q0 + row) * p.dq_ld + h * HD;
+            const bool valid = q0 + row < len_q;    // the loads below are warp-collective: only stores are predicated
+            __nv_bfloat16* dst = p.dq + (static_cast<long long>(tok_q) + q0 + row) * p.dq_ld + h * HD;
 #pragma unroll 1
             for (int c = 2 * half; c < 2 * half + 2; ++c) {
                 uint32_t t[32];
@@ -256,7 +266,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     v.y = pack_bf16x2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3]));
                     v.z = pack_bf16x2(__uint_as_float(t[i + 4]), __uint_as_float(t[i + 5]));
                     v.w = pack_bf16x2(__uint_as_float(t[i + 6]), __uint_as_float(t[i + 7]));
-                    *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+                    if (valid) *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
                 }
             }
         }
@@ -271,20 +281,31 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 }
 
 
-// delta[b, h, s] = sum_d dout[b, s, h, d] * out[b, s, h, d]: one warp per (token, head) row of 128 values
+// delta[b, h, s] = sum_d dout[tok, h, d] * out[tok, h, d] with tok = b S + s (or cu[b] + s for packed sequences, 0
+// past the end of a sequence): one warp per (b, s, h)
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long lddo, const __nv_bfloat16* __restrict__ out,
-                  long long ldo, float* __restrict__ delta, long long tokens, int S, int H) {
-    const long long rowi = blockIdx.x * 8ll + (threadIdx.x >> 5);     // token * H + h
-    if (rowi >= tokens * H) return;
+                  long long ldo, float* __restrict__ delta, int B, int S, int S_pad, int H,
+                  const int* __restrict__ cu) {
+    const long long rowi = blockIdx.x * 8ll + (threadIdx.x >> 5);     // (b * S_pad + s) * H + h
+    if (rowi >= static_cast<long long>(B) * S_pad * H) return;
     const int lane = threadIdx.x & 31;
-    const long long tok = rowi / H;
     const int h = static_cast<int>(rowi % H);
-    const uint2 a = *reinterpret_cast<const uint2*>(dout + tok * lddo + h * HD + lane * 4);
-    const uint2 c = *reinterpret_cast<const uint2*>(out + tok * ldo + h * HD + lane * 4);
-    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y);
-    const float v = warp_sum(a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y);
-    if (lane == 0) delta[((tok / S) * H + h) * S + tok % S] = v;
+    const int sidx = static_cast<int>((rowi / H) % S_pad), b = static_cast<int>(rowi / H / S_pad);
+    long long tok = static_cast<long long>(b) * S + sidx;
+    int len = S;
+    if (cu != nullptr) {
+        tok = cu[b] + sidx;
+        len = cu[b + 1] - cu[b];
+    }
+    float v = 0.f;
+    if (sidx < len) {
+        const uint2 a = *reinterpret_cast<const uint2*>(dout + tok * lddo + h * HD + lane * 4);
+        const uint2 c = *reinterpret_cast<const uint2*>(out + tok * ldo + h * HD + lane * 4);
+        const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y);
+        v = warp_sum(a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y);
+    }
+    if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S_pad + sidx] = v;
 }
 
 struct DkvArgs {
@@ -294,6 +315,8 @@ struct DkvArgs {
     const float* delta;      // [B, Hq, S_q]
     int B, S_q, S_kv, Hq, Hkv, causal, window;
     float scale;
+    const int* cu_seqlens;   // packed sequences (self-attention): rows cu[b] .. cu[b+1]-1; null = [B, S] batches
+    int S_pad;               // row pitch of lse / delta
 };
 
 namespace dkv {
@@ -326,14 +349,19 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int G = p.Hq / p.Hkv;
     const int k0 = kb * ROWS;
-    const int shift = p.S_kv - p.S_q;
-    const int nq = p.S_q / TN;
+    int tok_q = b * p.S_q, tok_k = b * p.S_kv, len_q = p.S_q, len_k = p.S_kv;
+    if (p.cu_seqlens != nullptr) {
+        tok_q = tok_k = p.cu_seqlens[b];
+        len_q = len_k = p.cu_seqlens[b + 1] - tok_q;
+    }
+    const int shift = len_k - len_q;
+    const int nq = (len_q + TN - 1) / TN;
     // first query tile with a row that sees key k0: 64 i + 63 + shift >= k0
     const int i_start = p.causal ? max(0, (k0 - shift) / TN) : 0;
     // sliding window: the last query that sees key k0 + 127 is k0 + 127 - shift + window - 1
     const int i_end = (p.causal && p.window > 0) ? min(nq, (k0 + ROWS - 1 - shift + p.window - 1) / TN + 1) : nq;
     const int per_g = i_end - i_start;
-    const int n_it = per_g > 0 ? G * per_g : 0;
+    const int n_it = (per_g > 0 && k0 < len_k) ? G * per_g : 0;
 
     if (threadIdx.x == 0) {
         *poisoned = lme_status[0];
@@ -347,8 +375,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (n_it <= 0) {        // no query sees these keys: their gradients are zero
         if (warp >= 2 && warp < 6) {
             const int row = (warp & 3) * 32 + lane;
-            const long long grow = static_cast<long long>(b) * p.S_kv + k0 + row;
-            for (int i = 0; i < HD; i += 8) {
+            const long long grow = static_cast<long long>(tok_k) + k0 + row;
+            for (int i = 0; i < HD && k0 + row < len_k; i += 8) {
                 *reinterpret_cast<uint4*>(p.dk + grow * p.dk_ld + hk * HD + i) = make_uint4(0u, 0u, 0u, 0u);
                 *reinterpret_cast<uint4*>(p.dv + grow * p.dv_ld + hk * HD + i) = make_uint4(0u, 0u, 0u, 0u);
             }
@@ -384,7 +412,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     if (warp == 0) {
         if (lane == 0) {
-            const int row_k = b * p.S_kv + k0;
+            const int row_k = tok_k + k0;
             mbar_expect_tx(kv_full, 2 * BIG);
             tma_load_2d(smem + OFF_K, &tmK, kv_full, hk * HD, row_k);
             tma_load_2d(smem + OFF_K + BIG_HALF, &tmK, kv_full, hk * HD + 64, row_k);
@@ -394,11 +422,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const int s = it % NS;
                 if (!mbar_wait(&qdo_empty[s], ((it / NS) & 1) ^ 1, 800 + s)) break;
                 const int h = hk * G + it / per_g, i = i_start + it % per_g;
-                const int row_q = b * p.S_q + i * TN;
+                const int row_q = tok_q + i * TN;
                 uint8_t* qs = smem + OFF_Q + s * SMALL;
                 uint8_t* dos = smem + OFF_DO + s * SMALL;
                 float* st = reinterpret_cast<float*>(smem + OFF_STAT + s * STAT_BYTES);
-                const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_q + i * TN;
+                const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.S_pad + i * TN;
                 mbar_expect_tx(&qdo_full[s], 2 * SMALL + STAT_BYTES);
                 tma_load_2d(qs, &tmQ, &qdo_full[s], h * HD, row_q);
                 tma_load_2d(qs + SMALL_HALF, &tmQ, &qdo_full[s], h * HD + 64, row_q);
@@ -476,8 +504,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (it >> 1) & 1, 850 + s));
             if (!ok) break;
             tc_fence_after();
-            const bool masked = p.causal && (i * TN + shift < k0 + ROWS - 1 ||
-                                             (p.window > 0 && i * TN + TN - 1 + shift >= k0 + p.window));
+            const bool masked = i * TN + TN > len_q ||
+                                (p.causal && (i * TN + shift < k0 + ROWS - 1 ||
+                                              (p.window > 0 && i * TN + TN - 1 + shift >= k0 + p.window)));
             uint32_t sv[32], dp[32];
             tmem_ld_32x32(lane_base + TM_S + s * TN + half * 32, sv);
             tmem_ld_32x32(lane_base + TM_DP + s * TN + half * 32, dp);
@@ -497,9 +526,10 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     float p0 = ex2(fmaf(__uint_as_float(sv[e]), sl2, -st[col] * LOG2E));
                     float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), sl2, -st[col + 1] * LOG2E));
                     if (masked) {
-                        const int qv = i * TN + col + shift;          // key limit of query column `col`
-                        if (kr > qv || (p.window > 0 && kr <= qv - p.window)) p0 = 0.f;
-                        if (kr > qv + 1 || (p.window > 0 && kr <= qv + 1 - p.window)) p1 = 0.f;
+                        const int qc = i * TN + col;                  // query of this column; it sees keys <= qc + shift
+                        const int qv = qc + shift;
+                        if (qc >= len_q || (p.causal && (kr > qv || (p.window > 0 && kr <= qv - p.window)))) p0 = 0.f;
+                        if (qc + 1 >= len_q || (p.causal && (kr > qv + 1 || (p.window > 0 && kr <= qv + 1 - p.window)))) p1 = 0.f;
                     }
                     const float d0 = p0 * (__uint_as_float(dp[e]) - st[TN + col]) * p.scale;
                     const float d1 = p1 * (__uint_as_float(dp[e + 1]) - st[TN + col + 1]) * p.scale;
@@ -520,7 +550,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&acc_done[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, 870));
         if (ok) {
             tc_fence_after();
-            const long long grow = static_cast<long long>(b) * p.S_kv + kr;
+            const bool valid = kr < len_k;
+            const long long grow = static_cast<long long>(tok_k) + kr;
             __nv_bfloat16* dvp = p.dv + grow * p.dv_ld + hk * HD;
             __nv_bfloat16* dkp = p.dk + grow * p.dk_ld + hk * HD;
 #pragma unroll 1
@@ -536,7 +567,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     v.y = pack_bf16x2(__uint_as_float(t[e + 2]), __uint_as_float(t[e + 3]));
                     v.z = pack_bf16x2(__uint_as_float(t[e + 4]), __uint_as_float(t[e + 5]));
                     v.w = pack_bf16x2(__uint_as_float(t[e + 6]), __uint_as_float(t[e + 7]));
-                    *reinterpret_cast<uint4*>(o + e) = v;
+                    if (valid) *reinterpret_cast<uint4*>(o + e) = v;
                 }
             }
         }
@@ -560,9 +591,10 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
                                  long long ldv, const void* dout, long long lddo, const void* out, long long ldo,
                                  const float* lse, float* delta, void* dq, long long lddq, void* dk, long long lddk, void* dv,
                                  long long lddv, int B, int S_q, int S_kv, int Hq, int Hkv, int causal, int window,
-                                 float scale, void* stream) {
+                                 float scale, const int* cu_seqlens, long long total_tokens, void* stream) {
     using namespace lme::attn_bwd;
-    if (B <= 0 || S_q <= 0 || S_kv <= 0 || S_q % ROWS || S_kv % ROWS || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
+    if (B <= 0 || S_q <= 0 || S_kv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return LME_ERR_SHAPE;
+    if (cu_seqlens ? (S_q != S_kv || total_tokens <= 0) : (S_q % ROWS || S_kv % ROWS)) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
     if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
     if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
@@ -572,7 +604,9 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
     if (ptrs & 15) return LME_ERR_ALIGN;
     if ((ldq | ldk | ldv | lddo | lddq | lddk | lddv) % 8) return LME_ERR_ALIGN;
     const uint64_t wq = static_cast<uint64_t>(Hq) * HD, wk = static_cast<uint64_t>(Hkv) * HD;
-    const uint64_t rq = static_cast<uint64_t>(B) * S_q, rk = static_cast<uint64_t>(B) * S_kv;
+    const uint64_t rq = cu_seqlens ? static_cast<uint64_t>(total_tokens) : static_cast<uint64_t>(B) * S_q;
+    const uint64_t rk = cu_seqlens ? static_cast<uint64_t>(total_tokens) : static_cast<uint64_t>(B) * S_kv;
+    const int S_pad = (S_q + ROWS - 1) / ROWS * ROWS;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     static bool configured = false;
     if (!configured) {
@@ -583,10 +617,10 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
     }
     if ((reinterpret_cast<uintptr_t>(out) & 15) || ldo % 8) return LME_ERR_ALIGN;
     {
-        const long long rows = static_cast<long long>(B) * S_q * Hq;
+        const long long rows = static_cast<long long>(B) * S_pad * Hq;
         attn_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(dout), lddo, static_cast<const __nv_bfloat16*>(out), ldo, delta,
-            static_cast<long long>(B) * S_q, S_q, Hq);
+            static_cast<const __nv_bfloat16*>(dout), lddo, static_cast<const __nv_bfloat16*>(out), ldo, delta, B, S_q,
+            S_pad, Hq, cu_seqlens);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     int rc;
@@ -599,7 +633,8 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         DqArgs a;
         a.dq = static_cast<__nv_bfloat16*>(dq); a.dq_ld = lddq; a.lse = lse; a.delta = delta;
         a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.window = window; a.scale = scale;
-        attn_dq_kernel<<<dim3(S_q / ROWS, Hq, B), 320, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        a.cu_seqlens = cu_seqlens; a.S_pad = S_pad;
+        attn_dq_kernel<<<dim3((S_q + ROWS - 1) / ROWS, Hq, B), 320, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     {   // dK, dV: K and V in 128-row boxes, Q and dO in 64-row boxes
@@ -612,7 +647,8 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv); a.dk_ld = lddk; a.dv_ld = lddv;
         a.lse = lse; a.delta = delta;
         a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.window = window; a.scale = scale;
-        attn_dkv_kernel<<<dim3(S_kv / ROWS, Hkv, B), 320, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        a.cu_seqlens = cu_seqlens; a.S_pad = S_pad;
+        attn_dkv_kernel<<<dim3((S_kv + ROWS - 1) / ROWS, Hkv, B), 320, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     return LME_OK;

@@ -178,10 +178,12 @@ int lme_unpack_rows(const void* packed, const int* cu_seqlens, void* x, int B, i
 // q [B,S_q,Hq,128], k / v [B,S_kv,Hkv,128] with token pitch ld* elements (heads contiguous inside a token, batches
 // back to back); o [B,S_q,Hq,128] with token pitch ldo; lse fp32 [B,Hq,S_q] or null.  causal aligns the last query
 // with the last key; window > 0 (causal only) is a sliding window: query i sees its last `window` visible keys.
-// scale multiplies q.k before the softmax.
+// scale multiplies q.k before the softmax.  Packed sequences: cu_seqlens (int32 [B+1], device) with q / k / v / o
+// as [total_tokens, H, 128], S_q = S_kv = the longest sequence (any lengths), lse [B,Hq,S_pad], S_pad = S_q rounded
+// up to 128; cu_seqlens null = batches.
 int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
                       void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq, int Hkv, int causal,
-                      int window, float scale, void* stream);
+                      int window, float scale, const int* cu_seqlens, long long total_tokens, void* stream);
 
 // Gradients of lme_attention_fwd (kernels/attention_bwd.cu; two kernels, no atomics, deterministic).  dout and out
 // laid out like q; lse fp32 [B,Hq,S_q]; delta fp32 scratch of that shape (receives rowsum(dout * out));
@@ -191,7 +193,8 @@ int lme_attention_bwd(const void* q, long long ldq, const void* k, long long ldk
                       const void* dout, long long lddo, const void* out, long long ldo, const float* lse,
                       float* delta, void* dq,
                       long long lddq, void* dk, long long lddk, void* dv, long long lddv, int B, int S_q, int S_kv,
-                      int Hq, int Hkv, int causal, int window, float scale, void* stream);
+                      int Hq, int Hkv, int causal, int window, float scale, const int* cu_seqlens,
+                      long long total_tokens, void* stream);
 
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);

@@ -75,8 +75,8 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_ssd_dcb": [P, P, P, L, I, I, I, P],
             "lme_m2rnn": [P, I, P],
             "lme_rnn": [P, I, P],
-            "lme_attention_fwd": [P, L, P, L, P, L, P, L, P, I, I, I, I, I, I, I, F, P],
-            "lme_attention_bwd": [P, L, P, L, P, L, P, L, P, L, P, P, P, L, P, L, P, L, I, I, I, I, I, I, I, F, P],
+            "lme_attention_fwd": [P, L, P, L, P, L, P, L, P, I, I, I, I, I, I, I, F, P, L, P],
+            "lme_attention_bwd": [P, L, P, L, P, L, P, L, P, L, P, P, P, L, P, L, P, L, I, I, I, I, I, I, I, F, P, L, P],
             "lme_embedding_fwd": [P, P, P, L, I, L, L, P],
             "lme_embedding_bwd": [P, P, P, P, L, I, L, L, P],
             "lme_pack_rows": [P, P, P, I, I, L, L, P],

@@ -75,6 +75,31 @@ def _sdpa(q, k, v, causal, scale, dropout_p):
     return out.transpose(1, 2)
 
 
+def _flash_attn_varlen_usable(q: torch.Tensor) -> bool:
+    if q.dtype not in (torch.bfloat16, torch.float16) or q.size(-1) > 256:
+        return False
+    try:
+        import flash_attn  # noqa: F401
+    except Exception:  # noqa: BLE001
+        return False
+    return True
+
+
+def _flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale, sliding_window, dropout_p):
+    """Packed sequences on the GPU through the flash-attn library kernel (what the reference calls for its
+    padding-free path, lm_engine/modeling_utils/sequence_mixer_blocks/softmax_attention/utils.py); the PyTorch
+    statement would loop over the sequences and materialise their score matrices."""
+    from flash_attn import flash_attn_varlen_func
+
+    cu = cu_seqlens.to(torch.int32)
+    if max_seqlen is None:
+        max_seqlen = int((cu[1:] - cu[:-1]).max())
+    window = (-1, -1) if sliding_window is None else ((sliding_window - 1, 0) if causal
+                                                      else (sliding_window - 1, sliding_window - 1))
+    return flash_attn_varlen_func(q.contiguous(), k.contiguous(), v.contiguous(), cu, cu, max_seqlen, max_seqlen,
+                                  dropout_p=dropout_p, softmax_scale=scale, causal=causal, window_size=window)
+
+
 def attention(q, k, v, *, causal=True, softmax_scale=None, sliding_window=None, attention_mask=None,
               cu_seqlens=None, max_seqlen=None, dropout_p=0.0):
     """Returns ``[B, Sq, Hq, D]`` (or packed ``[T, Hq, D]``)."""
@@ -88,6 +113,8 @@ def attention(q, k, v, *, causal=True, softmax_scale=None, sliding_window=None, 
         return attention_cuda.flash_attention(q, k, v, causal=causal, softmax_scale=scale,
                                               sliding_window=sliding_window, cu_seqlens=cu_seqlens,
                                               max_seqlen=max_seqlen)
+    if cu_seqlens is not None and q.is_cuda and attention_mask is None and _flash_attn_varlen_usable(q):
+        return _flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale, sliding_window, dropout_p)
     plain = sliding_window is None and attention_mask is None and cu_seqlens is None
     if plain and (q.size(1) == k.size(1) or not causal):
         return _sdpa(q, k, v, causal, scale, dropout_p)

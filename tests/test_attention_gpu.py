@@ -103,6 +103,41 @@ def test_sliding_window_matches_reference(B, S, Hq, Hkv, window):
         assert err < 2e-2, (name, err)
 
 
+@pytest.mark.parametrize("window", [None, 48])
+@pytest.mark.parametrize("own,D", [(False, 64), (True, 128)])
+def test_packed_sequences_on_gpu_match_reference(window, own, D, monkeypatch):
+    """cu_seqlens attention on the GPU - the library varlen kernel by default, the tcgen05 kernels under the switch -
+    against the per-sequence PyTorch statement."""
+    from lm_engine_b200.ops import _lib
+    from lm_engine_b200.ops.attention import attention, attention_reference
+
+    if own:
+        monkeypatch.setenv("LME_ATTENTION", "own")
+    else:
+        monkeypatch.delenv("LME_ATTENTION", raising=False)
+    torch.manual_seed(4)
+    Hq, Hkv = 4, 2
+    launches = _lib.launch_count
+    lens = [37, 128, 5, 200]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    T = sum(lens)
+    q = torch.randn(T, Hq, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    k = torch.randn(T, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(T, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    out = attention(q, k, v, causal=True, sliding_window=window, cu_seqlens=cu, max_seqlen=max(lens))
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref = attention_reference(*ref_in, causal=True, sliding_window=window, cu_seqlens=cu)
+    ref.backward(dout.float())
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    assert (_lib.launch_count >= launches + 4) == own
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for a, b in zip((q, k, v), ref_in):
+        assert float((a.grad.float() - b.grad).norm() / (b.grad.norm() + 1e-6)) < 2e-2
+
+
 def test_dispatcher_follows_the_switch(monkeypatch):
     from lm_engine_b200.ops import attention_cuda
     from lm_engine_b200.ops.attention import attention
