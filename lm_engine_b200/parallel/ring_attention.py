@@ -7,8 +7,10 @@ global token positions, which makes contiguous and head-tail sharding (and slidi
 blocks that a causal mask would zero entirely are skipped.
 
 Role of lm_engine/modeling_utils/sequence_mixer_blocks/softmax_attention/ring_attention.py:41-538 (which wraps
-flash-attn kernels in a Python ring over all-to-all); here the per-block math is
-:func:`block_attention_forward` / :func:`block_attention_backward`.
+flash-attn kernels in a Python ring over all-to-all); here the per-block math is the tcgen05 attention kernels
+(:func:`kernel_block_forward` / :func:`kernel_block_backward`, one launch per pair of position runs) when the block
+decomposes into whole runs of 128-row multiples, else the PyTorch statements :func:`block_attention_forward` /
+:func:`block_attention_backward`.
 """
 
 from __future__ import annotations
@@ -104,6 +106,99 @@ def _block_needed(qpos, kpos, causal, window) -> bool:
     return True
 
 
+def shard_runs(seq_len: int, cp: int, rank: int, method) -> list[tuple[int, int]]:
+    """The shard of ``rank`` as (first position, length) runs, in shard order: one run for contiguous sharding,
+    two for head-tail (host-side twin of :func:`shard_indices`)."""
+    from ..enums import ContextParallelLoadBalancerMethod
+
+    if method == ContextParallelLoadBalancerMethod.headtail:
+        c = seq_len // (2 * cp)
+        return [(rank * c, c), ((2 * cp - 1 - rank) * c, c)]
+    c = seq_len // cp
+    return [(rank * c, c)]
+
+
+def _relation(qrun: tuple[int, int], krun: tuple[int, int], causal: bool) -> str | None:
+    """How a run of keys relates to a run of queries: every key visible, the causal diagonal, nothing visible, or
+    ``None`` for a partial overlap the kernels have no mask for."""
+    if not causal:
+        return "full"
+    (qs, ql), (ks, kl) = qrun, krun
+    if ks + kl - 1 <= qs:
+        return "full"
+    if ks == qs and kl == ql:
+        return "causal"
+    if ks > qs + ql - 1:
+        return "skip"
+    return None
+
+
+def kernel_blocks_usable(q: torch.Tensor, k: torch.Tensor, qruns, kruns, causal: bool, window) -> bool:
+    """The tcgen05 attention kernels (ops/attention_cuda.py) serve a block when it decomposes into whole runs."""
+    from ..ops import attention_cuda
+
+    if window is not None or not q.is_cuda or q.dtype != torch.bfloat16 or q.size(-1) != 128:
+        return False
+    if any(length % 128 for _, length in list(qruns) + list(kruns)):
+        return False
+    if any(_relation(a, b, causal) is None for a in qruns for b in kruns):
+        return False
+    return attention_cuda.shapes_supported(q[:, :128], k[:, :128], k[:, :128])
+
+
+def kernel_block_forward(q, k, v, qruns, kruns, scale, causal):
+    """:func:`block_attention_forward` on the attention kernels: one launch per (query run, key run) pair that has
+    visible keys, merged per query run by their log-sum-exps."""
+    from ..ops.attention_cuda import flash_attention_forward
+
+    B, Sq, Hq, D = q.shape
+    out = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=q.device)
+    lse = torch.full((B, Sq, Hq), float("-inf"), dtype=torch.float32, device=q.device)
+    qo = 0
+    for qrun in qruns:
+        o_run = l_run = None
+        ko = 0
+        for krun in kruns:
+            rel = _relation(qrun, krun, causal)
+            if rel != "skip":
+                o_b, l_b = flash_attention_forward(q[:, qo:qo + qrun[1]], k[:, ko:ko + krun[1]], v[:, ko:ko + krun[1]],
+                                                   causal=rel == "causal", softmax_scale=scale, return_lse=True)
+                o_run, l_run = merge_partial(o_run, l_run, o_b.float(), l_b.transpose(1, 2))
+            ko += krun[1]
+        if o_run is not None:
+            out[:, qo:qo + qrun[1]] = o_run
+            lse[:, qo:qo + qrun[1]] = l_run
+        qo += qrun[1]
+    return out, lse
+
+
+def kernel_block_backward(do, q, k, v, out, lse, qruns, kruns, scale, causal):
+    """:func:`block_attention_backward` on the attention kernels (global ``out`` / ``lse``)."""
+    from ..ops.attention_cuda import flash_attention_backward
+
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    do16, out16 = do.to(q.dtype), out.to(q.dtype)
+    qo = 0
+    for qrun in qruns:
+        qs = slice(qo, qo + qrun[1])
+        l_run = lse[:, qs].transpose(1, 2).contiguous()
+        ko = 0
+        for krun in kruns:
+            rel = _relation(qrun, krun, causal)
+            ks = slice(ko, ko + krun[1])
+            if rel != "skip":
+                dq_b, dk_b, dv_b = flash_attention_backward(do16[:, qs], q[:, qs], k[:, ks], v[:, ks], out16[:, qs],
+                                                            l_run, causal=rel == "causal", softmax_scale=scale)
+                dq[:, qs] += dq_b
+                dk[:, ks] += dk_b
+                dv[:, ks] += dv_b
+            ko += krun[1]
+        qo += qrun[1]
+    return dq, dk, dv
+
+
 def _rotate(t: torch.Tensor, group, shift: int = 1) -> tuple[torch.Tensor, list]:
     """Starts sending ``t`` to rank+shift and receiving from rank-shift; returns (recv buffer, work handles)."""
     world, r = dist.get_world_size(group), dist.get_rank(group)
@@ -119,6 +214,7 @@ class _RingAttention(torch.autograd.Function):
     def forward(ctx, q, k, v, scale, causal, window, group, method, seq_len):
         cp, r = dist.get_world_size(group), dist.get_rank(group)
         pos = [shard_indices(seq_len, cp, j, method, device=q.device) for j in range(cp)]
+        runs = [shard_runs(seq_len, cp, j, method) for j in range(cp)]
         out = lse = None
         kv = torch.stack((k, v)).contiguous()
         for step in range(cp):
@@ -126,7 +222,11 @@ class _RingAttention(torch.autograd.Function):
             if step < cp - 1:
                 nxt, works = _rotate(kv, group)
             src = (r - step) % cp
-            if _block_needed(pos[r], pos[src], causal, window):
+            if kernel_blocks_usable(q, kv[0], runs[r], runs[src], causal, window):
+                if any(_relation(a, b, causal) != "skip" for a in runs[r] for b in runs[src]):
+                    o_b, l_b = kernel_block_forward(q, kv[0], kv[1], runs[r], runs[src], scale, causal)
+                    out, lse = merge_partial(out, lse, o_b, l_b)
+            elif _block_needed(pos[r], pos[src], causal, window):
                 o_b, l_b = block_attention_forward(q, kv[0], kv[1], pos[r], pos[src], scale, causal, window)
                 out, lse = merge_partial(out, lse, o_b, l_b)
             if works is not None:
@@ -143,6 +243,7 @@ class _RingAttention(torch.autograd.Function):
         scale, causal, window, group, method, seq_len = ctx.cfg
         cp, r = dist.get_world_size(group), dist.get_rank(group)
         pos = [shard_indices(seq_len, cp, j, method, device=q.device) for j in range(cp)]
+        runs = [shard_runs(seq_len, cp, j, method) for j in range(cp)]
         dq = torch.zeros_like(q, dtype=torch.float32)
         kv = torch.stack((k, v)).contiguous()
         dkv = torch.zeros_like(kv, dtype=torch.float32)
@@ -151,12 +252,16 @@ class _RingAttention(torch.autograd.Function):
             nxt_kv = works = None
             if step < cp - 1:
                 nxt_kv, works = _rotate(kv, group)
-            if _block_needed(pos[r], pos[src], causal, window):
-                dq_b, dk_b, dv_b = block_attention_backward(do, q, kv[0], kv[1], out, lse, pos[r], pos[src], scale,
-                                                            causal, window)
-                dq += dq_b
-                dkv[0] += dk_b
-                dkv[1] += dv_b
+            blk = None
+            if kernel_blocks_usable(q, kv[0], runs[r], runs[src], causal, window):
+                if any(_relation(a, b, causal) != "skip" for a in runs[r] for b in runs[src]):
+                    blk = kernel_block_backward(do, q, kv[0], kv[1], out, lse, runs[r], runs[src], scale, causal)
+            elif _block_needed(pos[r], pos[src], causal, window):
+                blk = block_attention_backward(do, q, kv[0], kv[1], out, lse, pos[r], pos[src], scale, causal, window)
+            if blk is not None:
+                dq += blk[0]
+                dkv[0] += blk[1]
+                dkv[1] += blk[2]
             if works is not None:
                 for w in works:
                     w.wait()

@@ -156,3 +156,44 @@ def test_dispatcher_follows_the_switch(monkeypatch):
     b.sum().backward()
     assert qg.grad is not None and torch.isfinite(qg.grad.float()).all()
     torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("method", [None, "headtail"])
+def test_ring_attention_blocks_on_kernels_match_block_math(method):
+    """The per-block forward / backward of context-parallel ring attention on the attention kernels against the
+    PyTorch block statements, for every (query rank, key rank) pair of a 2-way split (no process group needed)."""
+    from lm_engine_b200.ops.attention import attention_reference
+    from lm_engine_b200.parallel import ring_attention as ra
+    from lm_engine_b200.parallel.context_parallel import shard_indices
+
+    torch.manual_seed(5)
+    B, S, Hq, Hkv, D, cp = 1, 1024, 4, 2, 128, 2
+    scale = D ** -0.5
+    q = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
+    do = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+    out_full, lse_full = attention_reference(q.float(), k.float(), v.float(), causal=True, softmax_scale=scale,
+                                             return_lse=True)                       # [B,S,Hq,D], [B,S,Hq]
+    pos = [shard_indices(S, cp, j, method, device="cuda") for j in range(cp)]
+    runs = [ra.shard_runs(S, cp, j, method) for j in range(cp)]
+    for j in range(cp):
+        assert torch.equal(torch.cat([torch.arange(a, a + n, device="cuda") for a, n in runs[j]]), pos[j])
+    for r in range(cp):
+        for src in range(cp):
+            qs, ks, vs = q[:, pos[r]], k[:, pos[src]], v[:, pos[src]]
+            assert ra.kernel_blocks_usable(qs, ks, runs[r], runs[src], True, None)
+            if not ra._block_needed(pos[r], pos[src], True, None):
+                assert all(ra._relation(a, b, True) == "skip" for a in runs[r] for b in runs[src])
+                continue
+            o_k, l_k = ra.kernel_block_forward(qs, ks, vs, runs[r], runs[src], scale, True)
+            o_r, l_r = ra.block_attention_forward(qs, ks, vs, pos[r], pos[src], scale, True, None)
+            seen = ~torch.isinf(l_r)
+            assert torch.equal(seen, ~torch.isinf(l_k))
+            torch.testing.assert_close(l_k[seen], l_r[seen], rtol=1e-3, atol=1e-3)
+            torch.testing.assert_close(o_k[seen], o_r[seen], rtol=2e-2, atol=2e-2)
+            args = (do[:, pos[r]], qs, ks, vs, out_full[:, pos[r]], lse_full[:, pos[r]])
+            g_k = ra.kernel_block_backward(*args, runs[r], runs[src], scale, True)
+            g_r = ra.block_attention_backward(*args, pos[r], pos[src], scale, True, None)
+            for a, b in zip(g_k, g_r):
+                assert float((a - b).norm() / (b.norm() + 1e-6)) < 2e-2

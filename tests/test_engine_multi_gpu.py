@@ -103,7 +103,7 @@ def test_zero3_two_gpus_match_one_gpu(reduce_mode):
             assert abs(a - b) < 3e-2 * abs(b), (o[1], ref_norms)
 
 
-def _ulysses_worker(rank, world, port, q, method):
+def _cp_attention_worker(rank, world, port, q, method, algo):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     try:
@@ -112,6 +112,7 @@ def _ulysses_worker(rank, world, port, q, method):
         from lm_engine_b200.ops import attention
         from lm_engine_b200.parallel.context_parallel import shard_indices
         from lm_engine_b200.parallel.manager import ProcessGroupManager
+        from lm_engine_b200.parallel.ring_attention import ring_attention
         from lm_engine_b200.parallel.ulysses import ulysses_attention
 
         ProcessGroupManager(context_parallel_world_size=world, context_parallel_load_balancing_method=method)
@@ -123,7 +124,7 @@ def _ulysses_worker(rank, world, port, q, method):
         ref.backward(do)
         idx = shard_indices(S, world, rank, method, device="cuda")
         loc = [t[:, idx].clone().requires_grad_() for t in (q_, k_, v_)]
-        out = ulysses_attention(*loc, causal=True)
+        out = (ulysses_attention if algo == "ulysses" else ring_attention)(*loc, causal=True)
         out.backward(do[:, idx])
         torch.cuda.synchronize()
         err = [float((out.float() - ref[:, idx].float()).abs().max())]
@@ -143,11 +144,14 @@ def _ulysses_worker(rank, world, port, q, method):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("method", [None, "headtail"])
-def test_ulysses_attention_two_gpus(method):
+@pytest.mark.parametrize("algo", ["ulysses", "ring"])
+def test_context_parallel_attention_two_gpus(method, algo):
+    """Head-exchange and ring attention (the latter on the tcgen05 block kernels: 512 tokens split 2 ways gives
+    runs of 256 / 128 rows) against single-GPU attention, outputs and gradients."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _port()
-    procs = [ctx.Process(target=_ulysses_worker, args=(r, 2, port, q, method)) for r in range(2)]
+    procs = [ctx.Process(target=_cp_attention_worker, args=(r, 2, port, q, method, algo)) for r in range(2)]
     for p in procs:
         p.start()
     try:
