@@ -127,8 +127,10 @@ def _cp_attention_worker(rank, world, port, q, method, algo):
         out = (ulysses_attention if algo == "ulysses" else ring_attention)(*loc, causal=True)
         out.backward(do[:, idx])
         torch.cuda.synchronize()
-        err = [float((out.float() - ref[:, idx].float()).abs().max())]
-        err += [float((a.grad.float() - b.grad[:, idx].float()).abs().max()) for a, b in zip(loc, full)]
+        def rel(a, b):
+            return float((a.detach().float() - b.detach().float()).norm() / (b.detach().float().norm() + 1e-6))
+
+        err = [rel(out, ref[:, idx])] + [rel(a.grad, b.grad[:, idx]) for a, b in zip(loc, full)]
         q.put((rank, "ok", err))
         dist.barrier()
     except Exception:  # noqa: BLE001
@@ -158,7 +160,7 @@ def test_context_parallel_attention_two_gpus(method, algo):
         for _ in range(2):
             rank, status, payload = q.get(timeout=300)
             assert status == "ok", payload
-            assert max(payload) < 5e-2, payload     # bf16 outputs and gradients of O(1) magnitude
+            assert max(payload) < 2e-2, payload     # relative error of the output and of dq, dk, dv
     finally:
         for p in procs:
             p.join(timeout=30)
