@@ -55,7 +55,13 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, ac
     A = a.t() if a_mn else a
     B = b.t() if b_mn else b
     out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
-    acc = A.float() @ B.float().t()
+    if A.is_cuda and A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16:
+        try:        # library GEMM on the tensor cores with an fp32 result (shapes the tcgen05 kernel does not take)
+            acc = torch.mm(A, B.t(), out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            acc = torch.mm(A, B.t()).float()
+    else:
+        acc = A.float() @ B.float().t()
     if bias is not None:
         acc = acc + bias.float()
     if swiglu:
@@ -104,6 +110,14 @@ def gemm(
     if K != Kb:
         raise ValueError(f"gemm: contraction mismatch {K} vs {Kb}")
     n_out = N // 2 if swiglu else N
+    # the kernel moves operands with TMA: leading dimensions and N in units of 16 bytes.  Other shapes (an output
+    # width that is not a multiple of 8, e.g. a projection that carries one scalar gate per head) take the library
+    # GEMM with the same epilogue semantics.
+    if (N % 8 or (swiglu and N % 16) or a.stride(0) % 8 or b.stride(0) % 8
+            or (out is not None and (out.stride(1) != 1 or out.stride(0) % 4))
+            or (residual is not None and residual.stride(0) % 8) or (preact is not None and preact.stride(0) % 8)):
+        return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
+                              bias=bias, residual=residual, swiglu=swiglu, preact=preact)
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype or torch.bfloat16, device=a.device)
     elif out.stride(1) != 1 or out.shape != (M, n_out):

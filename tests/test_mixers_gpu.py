@@ -1,0 +1,69 @@
+"""Small models of every recurrent mixer family on the GPU in bf16 (CUDA scan / conv / SSD kernels inside the layers)
+against the same weights in fp32 on the CPU (PyTorch statements): logits and parameter gradients."""
+
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ATTN = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2)
+MIXERS = {
+    "rnn": dict(sequence_mixer_type="rnn", state_head_dim=16, num_input_heads=2, num_weight_heads=4, add_bias=False,
+                normalization_function="rmsnorm", gradient_clipping=1.0, kernel_size=None,
+                activation_function="tanh"),
+    "gru": dict(sequence_mixer_type="gru", state_head_dim=16, num_input_heads=4, num_forget_input_heads=2,
+                num_reset_input_heads=1, num_weight_heads=2, num_forget_weight_heads=4, num_reset_weight_heads=1,
+                add_bias=True, normalization_function="rmsnorm", gradient_clipping=None, kernel_size=4,
+                activation_function="silu"),
+    "m2rnn": dict(sequence_mixer_type="m2rnn", k_head_dim=16, v_head_dim=16, num_q_heads=1, num_k_heads=1,
+                  num_v_heads=4, num_f_heads=4, num_g_heads=4, num_weight_heads=2, use_residual=True, kernel_size=4,
+                  activation_function="silu", add_bias=False, gradient_clipping=1.0,
+                  normalization_function="rmsnorm"),
+    "mamba2": dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=128, num_heads=4,
+                   conv_kernel_size=4, activation_function="silu", num_groups=1, chunk_size=16,
+                   normalization_function="rmsnorm"),
+}
+
+
+def _config(mixer):
+    return dict(model_type="gpt_base", vocab_size=256, max_position_embeddings=128, hidden_size=64, num_layers=2,
+                normalization_function="rmsnorm", layer_norm_epsilon=1e-5, initializer_range=0.05, bos_token_id=0,
+                eos_token_id=1, pad_token_id=2, position_embedding_type="nope", rope_theta=10000, rope_scaling=None,
+                m_emb=None, m_width=None, m_residual=None, init_method="normal", embedding_init_method="normal",
+                use_depth_scaled_init=False, tie_word_embeddings=False, sequence_mixer_blocks=[mixer, dict(ATTN)],
+                mlp_blocks=[dict(mlp_type="MLP", intermediate_size=128, activation_function="swiglu")
+                            for _ in range(2)])
+
+
+@pytest.mark.parametrize("family", sorted(MIXERS))
+def test_recurrent_family_on_gpu_matches_cpu_fp32(family):
+    from lm_engine_b200.models import build_model, config_from_dict
+    from lm_engine_b200.ops import _lib
+
+    torch.manual_seed(0)
+    cpu = build_model(config_from_dict(_config(MIXERS[family])))
+    # weights that survive the bf16 cast exactly, so that both models start from the same point
+    with torch.no_grad():
+        for p in cpu.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    gpu = copy.deepcopy(cpu).to(device="cuda", dtype=torch.bfloat16)
+    x = torch.randint(0, 256, (2, 96), generator=torch.Generator().manual_seed(1))
+    launches = _lib.launch_count
+    out_g = gpu(x.cuda()).logits
+    out_c = cpu(x).logits
+    out_g.float().pow(2).mean().backward()
+    out_c.pow(2).mean().backward()
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    assert _lib.launch_count > launches                       # the layers ran on the kernels
+    err = float((out_g.float().cpu() - out_c).norm() / out_c.norm())
+    assert err < 3e-2, err
+    bad = []
+    for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
+        ref = pc.grad
+        e = float((pg.grad.float().cpu() - ref).norm() / (ref.norm() + 1e-8))
+        if e > 8e-2 and float(ref.norm()) > 1e-6:
+            bad.append((n, round(e, 3)))
+    assert not bad, bad
