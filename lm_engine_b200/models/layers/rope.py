@@ -40,8 +40,9 @@ class RoPE(nn.Module):
 
     def tables(self, seq_len: int) -> tuple[torch.Tensor, torch.Tensor]:
         """Full fp32 ``[>= seq_len, head_dim]`` tables (grown on demand)."""
-        if seq_len > self.max_seq_len_cached:
-            self._build(seq_len)
+        # a module-wide ``.to(dtype)`` also casts these buffers; the angles are needed (and read by the kernels) in fp32
+        if seq_len > self.max_seq_len_cached or self.cos_cached.dtype != torch.float32:
+            self._build(max(seq_len, self.max_seq_len_cached))
         return self.cos_cached, self.sin_cached
 
     def forward(self, seq_len: int) -> tuple[torch.Tensor, torch.Tensor]:

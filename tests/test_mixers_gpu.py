@@ -1,4 +1,4 @@
-"""Small models of every recurrent mixer family on the GPU in bf16 (CUDA scan / conv / SSD kernels inside the layers)
+"""Small models of every mixer / block family on the GPU in bf16 (the CUDA kernels inside the layers)
 against the same weights in fp32 on the CPU (PyTorch statements): logits and parameter gradients."""
 
 import copy
@@ -27,23 +27,53 @@ MIXERS = {
 }
 
 
-def _config(mixer):
-    return dict(model_type="gpt_base", vocab_size=256, max_position_embeddings=128, hidden_size=64, num_layers=2,
+def _config(mixer, model_type="gpt_base", mlp=None, **extra):
+    d = _base(mixer, model_type, mlp)
+    d.update(extra)
+    return d
+
+
+def _base(mixer, model_type, mlp):
+    mlp = mlp or dict(mlp_type="MLP", intermediate_size=128, activation_function="swiglu")
+    return dict(model_type=model_type, vocab_size=256, max_position_embeddings=128, hidden_size=64, num_layers=2,
                 normalization_function="rmsnorm", layer_norm_epsilon=1e-5, initializer_range=0.05, bos_token_id=0,
                 eos_token_id=1, pad_token_id=2, position_embedding_type="nope", rope_theta=10000, rope_scaling=None,
                 m_emb=None, m_width=None, m_residual=None, init_method="normal", embedding_init_method="normal",
                 use_depth_scaled_init=False, tie_word_embeddings=False, sequence_mixer_blocks=[mixer, dict(ATTN)],
-                mlp_blocks=[dict(mlp_type="MLP", intermediate_size=128, activation_function="swiglu")
-                            for _ in range(2)])
+                mlp_blocks=[dict(mlp) for _ in range(2)])
 
 
-@pytest.mark.parametrize("family", sorted(MIXERS))
-def test_recurrent_family_on_gpu_matches_cpu_fp32(family):
+GDN = dict(sequence_mixer_type="gated_deltanet", k_head_dim=16, v_head_dim=32, num_k_heads=2, num_v_heads=4,
+           use_gate=True, attention_multiplier=None, allow_neg_eigval=True, kernel_size=4)
+MOE = dict(mlp_type="MoE", intermediate_size=64, num_experts=4, num_experts_per_tok=2, activation_function="swiglu",
+           shared_intermediate_size=64, add_bias=False)
+LINATT = dict(sequence_mixer_type="linear_attention", k_head_dim=16, v_head_dim=16, num_q_heads=2, num_k_heads=2,
+              num_v_heads=4, num_g_heads=4, kernel_size=4, activation_function="silu", add_bias=False,
+              normalization_function="rmsnorm", attention_multiplier=None)
+OTHER = {
+    "gated_deltanet": dict(mixer=GDN),
+    "linear_attention": dict(mixer=LINATT),
+    "moe": dict(mixer=dict(ATTN), mlp=MOE, router_aux_loss_coef=0.01),
+    "rope": dict(mixer=dict(ATTN), position_embedding_type="rope", rope_dim=16),
+    "palm": dict(mixer=dict(ATTN), model_type="palm", position_embedding_type="rope", rope_dim=16),
+    "ladder_residual": dict(mixer=dict(ATTN), model_type="ladder_residual", position_embedding_type="rope",
+                            rope_dim=16),
+    "crosslayer": dict(mixer=dict(ATTN), model_type="gpt_crosslayer", sharing_pattern=[0, 0],
+                       position_embedding_type="rope", rope_dim=16),
+    "layernorm_bias": dict(mixer=dict(ATTN, add_bias=True), normalization_function="layernorm",
+                           mlp=dict(mlp_type="MLP", intermediate_size=128, activation_function="gelu_pytorch_tanh",
+                                    add_bias=True)),
+}
+
+
+@pytest.mark.parametrize("family", sorted(MIXERS) + sorted(OTHER))
+def test_model_family_on_gpu_matches_cpu_fp32(family):
     from lm_engine_b200.models import build_model, config_from_dict
     from lm_engine_b200.ops import _lib
 
     torch.manual_seed(0)
-    cpu = build_model(config_from_dict(_config(MIXERS[family])))
+    cfg = _config(MIXERS[family]) if family in MIXERS else _config(**OTHER[family])
+    cpu = build_model(config_from_dict(cfg))
     # weights that survive the bf16 cast exactly, so that both models start from the same point
     with torch.no_grad():
         for p in cpu.parameters():
