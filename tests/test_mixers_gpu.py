@@ -97,3 +97,34 @@ def test_model_family_on_gpu_matches_cpu_fp32(family):
         if e > 8e-2 and float(ref.norm()) > 1e-6:
             bad.append((n, round(e, 3)))
     assert not bad, bad
+
+
+CACHED = ["rnn", "gru", "m2rnn", "mamba2", "gated_deltanet", "linear_attention", "rope"]
+
+
+@pytest.mark.parametrize("family", CACHED)
+def test_prefill_and_decode_with_the_cache_match_the_full_forward(family):
+    """On the GPU in bf16: prefilling 64 tokens and decoding the next 8 one at a time (the kernels' carried states:
+    scans with an initial state, conv state, KV cache) gives the logits of one forward over all 72 tokens."""
+    from lm_engine_b200.models import build_model, config_from_dict
+    from lm_engine_b200.models.context import GenerationCache
+    from lm_engine_b200.ops import _lib
+
+    torch.manual_seed(0)
+    cfg = _config(MIXERS[family]) if family in MIXERS else _config(**OTHER[family])
+    model = build_model(config_from_dict(cfg)).to(device="cuda", dtype=torch.bfloat16).eval()
+    x = torch.randint(0, 256, (2, 72), generator=torch.Generator().manual_seed(2)).cuda()
+    with torch.no_grad():
+        full = model(x).logits.float()
+        out = model(x[:, :64], cache_params=GenerationCache())
+        steps = [out.logits[:, -1].float()]
+        for t in range(64, 71):
+            out = model(x[:, t:t + 1], cache_params=out.cache_params)
+            steps.append(out.logits[:, -1].float())
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    got = torch.stack(steps, dim=1)                       # logits that predict tokens 64 .. 71
+    want = full[:, 63:71]
+    err = float((got - want).norm() / want.norm())
+    assert err < 3e-2, err
+
