@@ -128,3 +128,29 @@ def test_prefill_and_decode_with_the_cache_match_the_full_forward(family):
     err = float((got - want).norm() / want.norm())
     assert err < 3e-2, err
 
+
+
+@pytest.mark.parametrize("family", CACHED)
+def test_left_padded_prefill_matches_the_unpadded_sample(family):
+    """A left-padded row of a batch (attention mask, prefill with a cache) gives the logits of the same tokens run
+    alone: padding reaches neither the attention nor the recurrent states / convolution windows."""
+    from lm_engine_b200.models import build_model, config_from_dict
+    from lm_engine_b200.models.context import AttentionMaskInfo, GenerationCache
+    from lm_engine_b200.ops import _lib
+
+    torch.manual_seed(0)
+    cfg = _config(MIXERS[family]) if family in MIXERS else _config(**OTHER[family])
+    model = build_model(config_from_dict(cfg)).to(device="cuda", dtype=torch.bfloat16).eval()
+    g = torch.Generator().manual_seed(3)
+    short, long = torch.randint(3, 256, (1, 40), generator=g).cuda(), torch.randint(3, 256, (1, 64), generator=g).cuda()
+    batch = torch.cat((torch.cat((torch.full((1, 24), 2, device="cuda"), short), 1), long))
+    mask = torch.ones_like(batch)
+    mask[0, :24] = 0
+    with torch.no_grad():
+        alone = model(short, cache_params=GenerationCache()).logits.float()
+        both = model(batch, cache_params=GenerationCache(),
+                     attention_mask_info=AttentionMaskInfo(attention_mask=mask)).logits.float()
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    err = float((both[0, 24:] - alone[0]).norm() / alone[0].norm())
+    assert err < 3e-2, err
