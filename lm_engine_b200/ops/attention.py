@@ -115,6 +115,13 @@ def attention(q, k, v, *, causal=True, softmax_scale=None, sliding_window=None, 
                                               max_seqlen=max_seqlen)
     if cu_seqlens is not None and q.is_cuda and attention_mask is None and _flash_attn_varlen_usable(q):
         return _flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale, sliding_window, dropout_p)
+    if (sliding_window is not None and q.is_cuda and attention_mask is None and cu_seqlens is None
+            and (q.size(1) == k.size(1) or not causal) and _flash_attn_varlen_usable(q)):
+        # windows the tcgen05 kernels do not take (head dim != 128, ragged lengths): the library's windowed kernel
+        from flash_attn import flash_attn_func
+
+        window = (sliding_window - 1, 0) if causal else (sliding_window - 1, sliding_window - 1)
+        return flash_attn_func(q, k, v, dropout_p=dropout_p, softmax_scale=scale, causal=causal, window_size=window)
     plain = sliding_window is None and attention_mask is None and cu_seqlens is None
     if plain and (q.size(1) == k.size(1) or not causal):
         return _sdpa(q, k, v, causal, scale, dropout_p)

@@ -138,6 +138,27 @@ def test_packed_sequences_on_gpu_match_reference(window, own, D, monkeypatch):
         assert float((a.grad.float() - b.grad).norm() / (b.grad.norm() + 1e-6)) < 2e-2
 
 
+def test_sliding_window_with_other_head_dims_uses_the_library_kernel():
+    from lm_engine_b200.ops import _lib
+    from lm_engine_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(6)
+    q = torch.randn(2, 200, 4, 64, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    k = torch.randn(2, 200, 2, 64, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(2, 200, 2, 64, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    launches = _lib.launch_count
+    out = attention(q, k, v, causal=True, sliding_window=50)
+    assert _lib.launch_count == launches                    # head dim 64: not our kernels
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref = attention_reference(*ref_in, causal=True, sliding_window=50)
+    ref.backward(dout.float())
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for a, b in zip((q, k, v), ref_in):
+        assert float((a.grad.float() - b.grad).norm() / (b.grad.norm() + 1e-6)) < 2e-2
+
+
 def test_dispatcher_follows_the_switch(monkeypatch):
     from lm_engine_b200.ops import attention_cuda
     from lm_engine_b200.ops.attention import attention
