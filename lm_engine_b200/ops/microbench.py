@@ -213,6 +213,34 @@ def bench_recurrent(small: bool = False) -> list[dict]:
             return (*xs, *ws, None, 1.0)
         return make
 
+    # the chunk-parallel PyTorch forms (batched matmuls + triangular solve) at the published gated-delta-net layout
+    from .recurrence import gated_delta_rule, linear_attention
+
+    def chunked(name, fn, make_args):
+        args = make_args()
+        for a in args:
+            if isinstance(a, torch.Tensor) and a.is_floating_point():
+                a.requires_grad_(True)
+        fwd = _time(lambda i: fn(*args), 1, iters=5, warmup=2)
+
+        def both(i):
+            y, _ = fn(*args)
+            y.backward(torch.ones_like(y))
+
+        tot = _time(both, 1, iters=5, warmup=2)
+        rows.append({"name": name, "S": S, "fwd_ms": fwd * 1e3, "fwd_bwd_ms": tot * 1e3})
+        print(f"{name:34s} S={S}  fwd {fwd * 1e3:7.3f} ms  fwd+bwd {tot * 1e3:7.3f} ms   (chunk-parallel PyTorch ops)",
+              flush=True)
+
+    def gdn_args():
+        N, K, V = 3, 256, 512
+        return (torch.randn(B, S, N, K, device=dev).to(bf), torch.randn(B, S, N, K, device=dev).to(bf),
+                torch.randn(B, S, N, V, device=dev).to(bf), -torch.rand(B, S, N, device=dev) * 0.1,
+                torch.rand(B, S, N, device=dev))
+
+    chunked("gated delta rule K=256 V=512 N=3", gated_delta_rule, gdn_args)
+    chunked("linear attention K=64 V=64 N=32", linear_attention,
+            lambda: tuple(torch.randn(B, S, 32, 64, device=dev).to(bf) * 0.3 for _ in range(3)))
     add("m2rnn K=64 V=16 N=132 (shared q,k)", m2(132, 64, 16, True), m2rnn_scan)
     add("m2rnn K=64 V=64 N=32", m2(32, 64, 64, False), m2rnn_scan)
     add("rnn H=16 N=128", vec(128, 16, 1), rnn_scan)

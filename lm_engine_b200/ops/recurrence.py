@@ -71,6 +71,7 @@ def m2rnn_scan(q, k, v, f, W, h0=None, gradient_clipping=None):
 
 
 CHUNK = 64   # time steps per block of the chunk-parallel forms below
+LONG_CHUNK = 256
 
 
 def linear_attention_chunked(q, k, v, h0=None, attention_multiplier: float = 1.0, chunk: int = CHUNK):
@@ -197,7 +198,10 @@ def linear_attention(q, k, v, h0=None, attention_multiplier: float = 1.0):
 def gated_delta_rule(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: bool = True):
     if q.size(1) < 8:
         return gated_delta_rule_scan(q, k, v, g, beta, scale, h0, use_qk_l2norm)
-    return gated_delta_rule_chunked(q, k, v, g, beta, scale, h0, use_qk_l2norm)
+    # the loop over blocks is the sequential (launch-bound) part and the block-local work is cheap: long sequences
+    # take large blocks (the intra-block cost grows with the block length, the number of loop trips falls with it)
+    chunk = LONG_CHUNK if q.size(1) >= 4 * LONG_CHUNK else CHUNK
+    return gated_delta_rule_chunked(q, k, v, g, beta, scale, h0, use_qk_l2norm, chunk=chunk)
 
 
 def m2rnn(q, k, v, f, W, h0=None, gradient_clipping=None):

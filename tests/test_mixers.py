@@ -156,3 +156,26 @@ def test_chunk_parallel_forms_equal_the_token_recurrences(S):
     (y3 * w).sum().backward()
     for x, y in zip(a, b):
         torch.testing.assert_close(y.grad, x.grad, rtol=2e-3, atol=2e-3)
+
+
+def test_gated_delta_rule_large_blocks_equal_the_token_recurrence():
+    """Long sequences run the chunk-parallel form with 256-step blocks (fewer sequential block steps)."""
+    from lm_engine_b200.ops import recurrence as rec
+
+    torch.manual_seed(7)
+    B, S, N, K, V = 1, 4 * rec.LONG_CHUNK + 37, 2, 8, 6
+    q, k = torch.randn(B, S, N, K), torch.randn(B, S, N, K)
+    v = torch.randn(B, S, N, V)
+    g = -torch.rand(B, S, N) * 0.05
+    beta = torch.rand(B, S, N)
+    a = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    b = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    y2, s2 = rec.gated_delta_rule_scan(*a, g, beta)
+    y3, s3 = rec.gated_delta_rule(*b, g, beta)          # dispatcher: S >= 4 * LONG_CHUNK takes the large blocks
+    torch.testing.assert_close(y3, y2, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(s3, s2, rtol=1e-3, atol=1e-3)
+    w = torch.randn_like(y2)
+    (y2 * w).sum().backward()
+    (y3 * w).sum().backward()
+    for x, y in zip(a, b):
+        torch.testing.assert_close(y.grad, x.grad, rtol=5e-3, atol=5e-3)
