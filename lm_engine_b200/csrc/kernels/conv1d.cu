@@ -11,7 +11,7 @@
 namespace lme {
 
 static constexpr int CONV_MAX_K = 8;
-static constexpr int CONV_CHUNK = 64;
+static constexpr int CONV_CHUNK = 32;
 
 __device__ __forceinline__ void conv_load_row(const __nv_bfloat16* x, const __nv_bfloat16* init, long long b, int t,
                                               int S, int C, int K, int c, float (&out)[8]) {
@@ -31,11 +31,13 @@ __device__ __forceinline__ void conv_load_row(const __nv_bfloat16* x, const __nv
     }
 }
 
-template <int KM>
+// EXACT: the filter has exactly KM taps, so every `j < K` test and tap select below folds at compile time
+template <int KM, bool EXACT>
 __global__ void __launch_bounds__(128)
 causal_conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                          const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ init,
-                         __nv_bfloat16* __restrict__ y, int B, int S, int C, int K, int silu) {
+                         __nv_bfloat16* __restrict__ y, int B, int S, int C, int K_, int silu) {
+    const int K = EXACT ? KM : K_;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= C) return;
     const int t0 = blockIdx.y * CONV_CHUNK;
@@ -123,13 +125,14 @@ __device__ __forceinline__ void conv_dz(const __nv_bfloat16* x, const __nv_bfloa
     }
 }
 
-template <int KM>
+template <int KM, bool EXACT>
 __global__ void __launch_bounds__(128)
 causal_conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                          const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ init,
                          const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
                          float* __restrict__ dw, float* __restrict__ dbias, float* __restrict__ dinit, int B, int S,
-                         int C, int K, int silu) {
+                         int C, int K_, int silu) {
+    const int K = EXACT ? KM : K_;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= C) return;
     const int t0 = blockIdx.y * CONV_CHUNK;
@@ -249,8 +252,9 @@ extern "C" int lme_causal_conv1d_fwd(const void* x, const void* w, const void* b
     auto IN = static_cast<const __nv_bfloat16*>(init);
     auto Y = static_cast<__nv_bfloat16*>(y);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (K <= 4) causal_conv1d_fwd_kernel<4><<<grid, 128, 0, st>>>(X, W, BI, IN, Y, B, S, C, K, silu);
-    else causal_conv1d_fwd_kernel<CONV_MAX_K><<<grid, 128, 0, st>>>(X, W, BI, IN, Y, B, S, C, K, silu);
+    if (K == 4) causal_conv1d_fwd_kernel<4, true><<<grid, 128, 0, st>>>(X, W, BI, IN, Y, B, S, C, K, silu);
+    else if (K < 4) causal_conv1d_fwd_kernel<4, false><<<grid, 128, 0, st>>>(X, W, BI, IN, Y, B, S, C, K, silu);
+    else causal_conv1d_fwd_kernel<CONV_MAX_K, false><<<grid, 128, 0, st>>>(X, W, BI, IN, Y, B, S, C, K, silu);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 
@@ -271,10 +275,12 @@ extern "C" int lme_causal_conv1d_bwd(const void* x, const void* w, const void* b
     auto DY = static_cast<const __nv_bfloat16*>(dy);
     auto DX = static_cast<__nv_bfloat16*>(dx);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (K <= 4)
-        causal_conv1d_bwd_kernel<4><<<grid, 128, 0, st>>>(X, W, BI, IN, DY, DX, dw, dbias, dinit, B, S, C, K, silu);
+    if (K == 4)
+        causal_conv1d_bwd_kernel<4, true><<<grid, 128, 0, st>>>(X, W, BI, IN, DY, DX, dw, dbias, dinit, B, S, C, K, silu);
+    else if (K < 4)
+        causal_conv1d_bwd_kernel<4, false><<<grid, 128, 0, st>>>(X, W, BI, IN, DY, DX, dw, dbias, dinit, B, S, C, K, silu);
     else
-        causal_conv1d_bwd_kernel<CONV_MAX_K><<<grid, 128, 0, st>>>(X, W, BI, IN, DY, DX, dw, dbias, dinit, B, S, C, K,
-                                                                   silu);
+        causal_conv1d_bwd_kernel<CONV_MAX_K, false><<<grid, 128, 0, st>>>(X, W, BI, IN, DY, DX, dw, dbias, dinit, B, S, C,
+                                                                          K, silu);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
