@@ -166,3 +166,112 @@ def test_context_parallel_attention_two_gpus(method, algo):
             p.join(timeout=30)
             if p.is_alive():
                 p.kill()
+
+
+def _pp_worker(rank, world, port, q, stages, schedule, M):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        import torch.distributed as dist
+
+        from lm_engine_b200.containers import ModelContainer
+        from lm_engine_b200.distributed import shard_model
+        from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+        from lm_engine_b200.models import dense_config
+        from lm_engine_b200.ops import _lib
+        from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+        from lm_engine_b200.parallel.manager import ProcessGroupManager
+        from lm_engine_b200.parallel.pipeline_parallel import PipelineSchedule
+
+        mbs, seq, steps = 2, 256, 3
+        ProcessGroupManager(zero_stage=3, pipeline_parallel_world_size=world)
+        cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=4, num_attention_heads=4,
+                           num_key_value_heads=2, intermediate_size=1024, head_dim=64,
+                           max_position_embeddings=seq).to_dict()
+        if world > 1:
+            ids = ProcessGroupManager.topology().pipeline_stage_ids(ProcessGroupManager.get_pipeline_parallel_rank(),
+                                                                    stages)
+            ws = [ModelWrapperForPretraining(pretrained_config=cfg, micro_batch_size=mbs, sequence_length=seq,
+                                             efficient_initialization=True, dtype="bf16",
+                                             num_pipeline_stages=stages, pipeline_stage_id=i) for i in ids]
+        else:
+            ws = [ModelWrapperForPretraining(pretrained_config=cfg, micro_batch_size=mbs, sequence_length=seq,
+                                             efficient_initialization=True, dtype="bf16")]
+        mc = ModelContainer(ws)
+        opts = []
+        for w in ws:
+            e = shard_model(w, stage=3, dtype=torch.bfloat16, communication_dtype=None, seed=3)
+            opts.append(ShardedOptimizer(e, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95],
+                                                           "eps": 1e-10}, None, False, 1.0))
+        data = torch.randint(0, 2048, (steps, M * mbs, seq + 1), generator=torch.Generator().manual_seed(9)).cuda()
+        losses, norms = [], []
+        sched = PipelineSchedule(mc, schedule, stages, M, mbs, seq, torch.bfloat16, False) if world > 1 else None
+        for s in range(steps):
+            for o in opts:
+                o.zero_grad()
+            if sched is not None:
+                totals = sched.step(data[s])
+                total = sum(w.engine.local_sumsq().clone() for w in ws)
+                dist.all_reduce(total, group=ProcessGroupManager.get_pipeline_parallel_group())
+                for o in opts:
+                    n = o.step(total_sumsq=total)
+                losses.append(float(totals["loss"]) if totals is not None else None)
+            else:
+                acc = 0.0
+                for mb in data[s].chunk(M):
+                    out = ws[0](mb, lm_loss_multiplier=1 / (mbs * seq))
+                    (out["loss"] / M).backward()
+                    acc += float(out["loss"].detach()) / M
+                n = opts[0].step()
+                losses.append(acc)
+            norms.append(float(n))
+        torch.cuda.synchronize()
+        q.put((rank, "ok", (losses, norms, _lib.read_status())))
+        if world > 1:
+            dist.barrier()
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _spawn(world, target, *args):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q, *args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    try:
+        for _ in range(world):
+            rank, status, payload = q.get(timeout=300)
+            assert status == "ok", payload
+            res[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    return [res[r] for r in range(world)]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("stages,schedule,M", [(2, "1F1B", 4), (4, "Interleaved1F1B", 4)])
+def test_pipeline_parallel_two_gpus_match_one_gpu(stages, schedule, M):
+    """Two pipeline ranks over NCCL (batched isend / irecv per tick) in bf16 against the same micro-batches on one
+    GPU: loss of the last stage and the global gradient norm per step."""
+    (ref_losses, ref_norms, _), = _spawn(1, _pp_worker, 1, None, M)
+    outs = _spawn(2, _pp_worker, stages, schedule, M)
+    last = outs[(stages - 1) % 2]
+    for a, b in zip(last[0], ref_losses):
+        assert abs(a - b) < 1.5e-2 * abs(b), (last[0], ref_losses)
+    for losses, norms, status in outs:
+        assert status[0] == 0, status
+        for a, b in zip(norms, ref_norms):
+            assert abs(a - b) < 3e-2 * abs(b), (norms, ref_norms)
