@@ -17,7 +17,19 @@ def _port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q, reduce_mode, total_mbs, steps):
+def _moe_config():
+    from lm_engine_b200.models import dense_config
+
+    cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                       intermediate_size=1024, head_dim=64, max_position_embeddings=256).to_dict()
+    cfg["mlp_blocks"] = [{"mlp_type": "MoE", "intermediate_size": 256, "num_experts": 4, "num_experts_per_tok": 2,
+                          "activation_function": "swiglu", "shared_intermediate_size": None, "add_bias": False}
+                         for _ in range(3)]
+    cfg["router_aux_loss_coef"] = 0.01
+    return cfg
+
+
+def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_dir=None):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LME_REDUCE_SCATTER=reduce_mode)
     try:
@@ -31,12 +43,17 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps):
         from lm_engine_b200.optimization.optimizer import ShardedOptimizer
         from lm_engine_b200.parallel.manager import ProcessGroupManager
 
-        ProcessGroupManager(zero_stage=3)
+        ProcessGroupManager(zero_stage=3, expert_parallel_world_size=ep if world > 1 else 1)
         mbs = total_mbs // world
         cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=3, num_attention_heads=4,
-                           num_key_value_heads=2, intermediate_size=1024, head_dim=64, max_position_embeddings=256)
-        w = ModelWrapperForPretraining(pretrained_config=cfg.to_dict(), micro_batch_size=mbs, sequence_length=256,
-                                       efficient_initialization=True, dtype="bf16")
+                           num_key_value_heads=2, intermediate_size=1024, head_dim=64,
+                           max_position_embeddings=256).to_dict()
+        if weights_dir is not None:     # the same saved weights on every topology (experts are sliced on load)
+            w = ModelWrapperForPretraining(model_name=weights_dir, micro_batch_size=mbs, sequence_length=256,
+                                           dtype="bf16")
+        else:
+            w = ModelWrapperForPretraining(pretrained_config=cfg, micro_batch_size=mbs, sequence_length=256,
+                                           efficient_initialization=True, dtype="bf16")
         eng = shard_model(w, stage=3, dtype=torch.bfloat16, communication_dtype=None,
                           gradient_checkpointing_method=GradientCheckpointingMethod.block, seed=5)
         opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95],
@@ -66,11 +83,12 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps):
             dist.destroy_process_group()
 
 
-def _run(world, reduce_mode, total_mbs=4, steps=4):
+def _run(world, reduce_mode, total_mbs=4, steps=4, ep=1, weights_dir=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps, ep, weights_dir))
+             for r in range(world)]
     for p in procs:
         p.start()
     res = {}
@@ -101,6 +119,34 @@ def test_zero3_two_gpus_match_one_gpu(reduce_mode):
     for o in outs:
         for a, b in zip(o[1], ref_norms):
             assert abs(a - b) < 3e-2 * abs(b), (o[1], ref_norms)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_two_gpus_match_one_gpu(tmp_path):
+    """Mixture of experts with the experts split over 2 GPUs (NCCL all-to-all of token rows, grouped GEMM kernels,
+    expert parameter units reduced over their replica group) against all experts on one GPU."""
+    from lm_engine_b200.models import build_model, config_from_dict
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+    from lm_engine_b200.utils import SafeTensorsWeightsManager
+
+    ProcessGroupManager.destroy_process_groups()
+    ProcessGroupManager(zero_stage=3)
+    torch.manual_seed(5)
+    cfg = config_from_dict(_moe_config())
+    model = build_model(cfg)
+    d = str(tmp_path / "weights")
+    cfg.save_pretrained(d)
+    SafeTensorsWeightsManager.save_state_dict(model.state_dict(), d)
+    ProcessGroupManager.destroy_process_groups()
+    (ref_losses, ref_norms, _, _), = _run(1, "nccl", ep=2, weights_dir=d)
+    outs = _run(2, "nccl", ep=2, weights_dir=d)
+    mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
+    for a, b in zip(mean, ref_losses):
+        assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)
+    for losses, norms, status, _ in outs:
+        assert status[0] == 0, status
+        for a, b in zip(norms, ref_norms):
+            assert abs(a - b) < 4e-2 * abs(b), (norms, ref_norms)
 
 
 def _cp_attention_worker(rank, world, port, q, method, algo):
