@@ -29,7 +29,23 @@ def _moe_config():
     return cfg
 
 
-def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_dir=None):
+def _hybrid_config():
+    from lm_engine_b200.models import dense_config
+
+    cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                       intermediate_size=1024, head_dim=64, max_position_embeddings=256).to_dict()
+    cfg["position_embedding_type"] = "nope"
+    cfg["sequence_mixer_blocks"] = [
+        dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=512, num_heads=8, conv_kernel_size=4,
+             activation_function="silu", num_groups=1, chunk_size=32, normalization_function="rmsnorm"),
+        dict(sequence_mixer_type="m2rnn", k_head_dim=16, v_head_dim=16, num_q_heads=1, num_k_heads=1, num_v_heads=8,
+             num_f_heads=8, num_g_heads=8, num_weight_heads=8, use_residual=True, kernel_size=4,
+             activation_function="silu", add_bias=False, gradient_clipping=1.0, normalization_function="rmsnorm"),
+        dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, head_dim=64)]
+    return cfg
+
+
+def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_dir=None, cp=1):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LME_REDUCE_SCATTER=reduce_mode)
     try:
@@ -43,8 +59,10 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_d
         from lm_engine_b200.optimization.optimizer import ShardedOptimizer
         from lm_engine_b200.parallel.manager import ProcessGroupManager
 
-        ProcessGroupManager(zero_stage=3, expert_parallel_world_size=ep if world > 1 else 1)
-        mbs = total_mbs // world
+        ProcessGroupManager(zero_stage=3, expert_parallel_world_size=ep if world > 1 else 1,
+                            context_parallel_world_size=cp if world > 1 else 1)
+        shards = cp if world > 1 else 1                  # context-parallel ranks share the batch and split the tokens
+        mbs = total_mbs // (world // shards)
         cfg = dense_config(vocab_size=2048, hidden_size=256, num_layers=3, num_attention_heads=4,
                            num_key_value_heads=2, intermediate_size=1024, head_dim=64,
                            max_position_embeddings=256).to_dict()
@@ -63,7 +81,8 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_d
         losses, norms = [], []
         for s in range(steps):
             opt.zero_grad()
-            out = w(data[s, rank * mbs:(rank + 1) * mbs].cuda(), lm_loss_multiplier=1 / (mbs * 256))
+            dl_rank = rank // shards
+            out = w(data[s, dl_rank * mbs:(dl_rank + 1) * mbs].cuda(), lm_loss_multiplier=1 / (mbs * 256 / shards))
             out["loss"].backward()
             norms.append(float(opt.step()))
             losses.append(float(out["loss"]))
@@ -83,11 +102,11 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_d
             dist.destroy_process_group()
 
 
-def _run(world, reduce_mode, total_mbs=4, steps=4, ep=1, weights_dir=None):
+def _run(world, reduce_mode, total_mbs=4, steps=4, ep=1, weights_dir=None, cp=1):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps, ep, weights_dir))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps, ep, weights_dir, cp))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -140,6 +159,39 @@ def test_expert_parallel_two_gpus_match_one_gpu(tmp_path):
     ProcessGroupManager.destroy_process_groups()
     (ref_losses, ref_norms, _, _), = _run(1, "nccl", ep=2, weights_dir=d)
     outs = _run(2, "nccl", ep=2, weights_dir=d)
+    mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
+    for a, b in zip(mean, ref_losses):
+        assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)
+    for losses, norms, status, _ in outs:
+        assert status[0] == 0, status
+        for a, b in zip(norms, ref_norms):
+            assert abs(a - b) < 4e-2 * abs(b), (norms, ref_norms)
+
+
+def _save_weights(config: dict, path) -> str:
+    from lm_engine_b200.models import build_model, config_from_dict
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+    from lm_engine_b200.utils import SafeTensorsWeightsManager
+
+    ProcessGroupManager.destroy_process_groups()
+    ProcessGroupManager(zero_stage=3)
+    torch.manual_seed(5)
+    cfg = config_from_dict(config)
+    model = build_model(cfg)
+    cfg.save_pretrained(str(path))
+    SafeTensorsWeightsManager.save_state_dict(model.state_dict(), str(path))
+    ProcessGroupManager.destroy_process_groups()
+    return str(path)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_context_parallel_hybrid_two_gpus_match_one_gpu(tmp_path):
+    """Mamba-2, M2RNN and attention layers with the sequence split over 2 GPUs: the SSD prefix over ranks, the
+    scan kernels' carried state and its gradient through the sequence pipeline, the convolution halo, and the
+    head-exchange attention, against the whole sequence on one GPU."""
+    d = _save_weights(_hybrid_config(), tmp_path / "weights")
+    (ref_losses, ref_norms, _, _), = _run(1, "nccl", weights_dir=d, cp=2)
+    outs = _run(2, "nccl", weights_dir=d, cp=2)
     mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
     for a, b in zip(mean, ref_losses):
         assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)

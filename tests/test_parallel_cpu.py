@@ -21,6 +21,15 @@ def _config(kind: str) -> dict:
                             "activation_function": "swiglu", "shared_intermediate_size": 64, "add_bias": False}
                            for _ in range(2)]
         d["router_aux_loss_coef"] = 0.01
+    if kind == "hybrid":     # recurrent mixers whose state (and convolution window) crosses the sequence shards
+        d["sequence_mixer_blocks"] = [
+            dict(sequence_mixer_type="mamba2", state_size=8, intermediate_size=128, num_heads=4, conv_kernel_size=4,
+                 activation_function="silu", num_groups=1, chunk_size=8, normalization_function="rmsnorm"),
+            dict(sequence_mixer_type="m2rnn", k_head_dim=4, v_head_dim=8, num_q_heads=2, num_k_heads=2, num_v_heads=4,
+                 num_f_heads=4, num_g_heads=4, num_weight_heads=4, use_residual=True, kernel_size=4,
+                 activation_function="silu", add_bias=False, gradient_clipping=None,
+                 normalization_function="rmsnorm")]
+        d["position_embedding_type"] = "nope"
     if kind == "bias":
         for b in d["sequence_mixer_blocks"] + d["mlp_blocks"]:
             b["add_bias"] = True
@@ -83,12 +92,13 @@ CASES = [
     ("dense", {"context_parallel_world_size": 2, "context_parallel_attention": "ulysses"}, False),
     ("dense", {"context_parallel_world_size": 2, "context_parallel_attention": "ulysses",
                "context_parallel_load_balancing_method": "headtail"}, False),
+    ("hybrid", {"context_parallel_world_size": 2}, False),
     ("moe", {"expert_parallel_world_size": 2}, False),
     ("moe", {"tensor_parallel_world_size": 2}, False),
 ]
 
 
-@pytest.mark.parametrize("kind,topo,sp", CASES, ids=["tp2", "tp2-sp", "tp2-sp-bias", "cp2-ring", "cp2-ulysses", "cp2-ulysses-headtail", "ep2", "moe-tp2"])
+@pytest.mark.parametrize("kind,topo,sp", CASES, ids=["tp2", "tp2-sp", "tp2-sp-bias", "cp2-ring", "cp2-ulysses", "cp2-ulysses-headtail", "cp2-hybrid", "ep2", "moe-tp2"])
 def test_parallel_training_matches_single_process(kind, topo, sp, tmp_path):
     steps, total_mbs = 3, 2
     d, (ref_loss, ref_norm, _) = _reference(kind, tmp_path, steps, total_mbs)
