@@ -94,6 +94,136 @@ ssd_dcb_kernel(const __nv_bfloat16* __restrict__ dm, const float* __restrict__ c
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ scan glue
+// The element-wise passes around the products of the chunked scan, one kernel per direction instead of a chain of
+// PyTorch ops over [tokens, heads, P] fp32 tensors (BC = batch x chunks, rows l of a chunk, heads n, P values):
+//   prep     xh [BC,N,L,P]  = x[BC,L,N,P] * dt[BC,L,N]                         (operand of the intra-chunk product)
+//            xwT[BC,N,P,L]  = x * dt * tail[BC,L,N], transposed                 (operand of the chunk-state product)
+//   prep^T   dx = dt (dxh + tail dxwT^T),  ddt = sum_p x (dxh + tail dxwT^T),  dtail = dt sum_p x dxwT^T
+//   combine  y[BC,L,N,P] = yin[BC,N,L,P] + off[BC,G,L,rep*P] * ecum[BC,L,N] + D[n] * x
+//   combine^T dyin = dy, doff = dy * ecum, decum = sum_p dy off, dDp[BC,L,N] = sum_p dy x, dx = D dy
+// One block handles 32 rows of one (BC, n); a warp owns a row at a time (coalesced along P); the transposed operand
+// goes through a padded shared-memory tile so that both its reads and writes are coalesced.
+constexpr int GLUE_ROWS = 32;
+
+template <int P>
+__global__ void __launch_bounds__(256)
+ssd_prep_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dt, const float* __restrict__ tail,
+                __nv_bfloat16* __restrict__ xh, __nv_bfloat16* __restrict__ xwT, int N, int L) {
+    __shared__ float tile[GLUE_ROWS][P + 1];
+    const int l0 = blockIdx.x * GLUE_ROWS, n = blockIdx.y;
+    const long long bc = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < GLUE_ROWS; r += 8) {
+        const int l = l0 + r;
+        const long long tok = (bc * L + l) * N + n;
+        const float d = dt[tok], tl = tail[tok];
+        const __nv_bfloat16* xr = x + tok * P;
+        __nv_bfloat16* hr = xh + ((bc * N + n) * L + l) * P;
+#pragma unroll
+        for (int p = lane; p < P; p += 32) {
+            const float v = __bfloat162float(xr[p]) * d;
+            hr[p] = __float2bfloat16(v);
+            tile[r][p] = v * tl;
+        }
+    }
+    __syncthreads();
+    __nv_bfloat16* wt = xwT + (bc * N + n) * static_cast<long long>(P) * L + l0;
+    for (int p = warp; p < P; p += 8) wt[static_cast<long long>(p) * L + lane] = __float2bfloat16(tile[lane][p]);
+}
+
+template <int P>
+__global__ void __launch_bounds__(256)
+ssd_prep_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dt, const float* __restrict__ tail,
+                    const float* __restrict__ dxh, const __nv_bfloat16* __restrict__ dxwT,
+                    __nv_bfloat16* __restrict__ dx, float* __restrict__ ddt, float* __restrict__ dtail, int N, int L) {
+    __shared__ float tile[GLUE_ROWS][P + 1];
+    const int l0 = blockIdx.x * GLUE_ROWS, n = blockIdx.y;
+    const long long bc = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const __nv_bfloat16* wt = dxwT + (bc * N + n) * static_cast<long long>(P) * L + l0;
+    for (int p = warp; p < P; p += 8) tile[lane][p] = __bfloat162float(wt[static_cast<long long>(p) * L + lane]);
+    __syncthreads();
+    for (int r = warp; r < GLUE_ROWS; r += 8) {
+        const int l = l0 + r;
+        const long long tok = (bc * L + l) * N + n;
+        const float d = dt[tok], tl = tail[tok];
+        const __nv_bfloat16* xr = x + tok * P;
+        const float* gh = dxh + ((bc * N + n) * L + l) * P;
+        __nv_bfloat16* dxr = dx + tok * P;
+        float s_dt = 0.f, s_tail = 0.f;
+#pragma unroll
+        for (int p = lane; p < P; p += 32) {
+            const float w = tile[r][p], xv = __bfloat162float(xr[p]);
+            const float g = gh[p] + tl * w;
+            dxr[p] = __float2bfloat16(d * g);
+            s_dt += xv * g;
+            s_tail += xv * w;
+        }
+        s_dt = warp_sum(s_dt);
+        s_tail = warp_sum(s_tail);
+        if (lane == 0) {
+            ddt[tok] = s_dt;
+            dtail[tok] = d * s_tail;
+        }
+    }
+}
+
+// one warp per (bc, l, n) row
+template <int P>
+__global__ void __launch_bounds__(256)
+ssd_combine_kernel(const float* __restrict__ yin, const float* __restrict__ off, const float* __restrict__ ecum,
+                   const float* __restrict__ D, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                   long long rows, int N, int L, int G) {
+    const long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);       // (bc * L + l) * N + n
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const int n = static_cast<int>(row % N), l = static_cast<int>((row / N) % L);
+    const long long bc = row / N / L;
+    const int rep = N / G, g = n / rep, r = n % rep;
+    const float e = ecum[row], dn = D[n];
+    const float* yi = yin + ((bc * N + n) * L + l) * P;
+    const float* of = off + ((bc * G + g) * L + l) * static_cast<long long>(rep) * P + r * P;
+#pragma unroll
+    for (int p = lane; p < P; p += 32)
+        y[row * P + p] = __float2bfloat16(yi[p] + of[p] * e + dn * __bfloat162float(x[row * P + p]));
+}
+
+template <int P>
+__global__ void __launch_bounds__(256)
+ssd_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ off,
+                       const float* __restrict__ ecum, const float* __restrict__ D,
+                       const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ dyin,
+                       __nv_bfloat16* __restrict__ doff, float* __restrict__ decum, float* __restrict__ dDp,
+                       __nv_bfloat16* __restrict__ dx, long long rows, int N, int L, int G) {
+    const long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const int n = static_cast<int>(row % N), l = static_cast<int>((row / N) % L);
+    const long long bc = row / N / L;
+    const int rep = N / G, g = n / rep, r = n % rep;
+    const float e = ecum[row], dn = D[n];
+    const long long o_in = ((bc * N + n) * L + l) * P;
+    const long long o_off = ((bc * G + g) * L + l) * static_cast<long long>(rep) * P + r * P;
+    float s_e = 0.f, s_d = 0.f;
+#pragma unroll
+    for (int p = lane; p < P; p += 32) {
+        const float gy = __bfloat162float(dy[row * P + p]);
+        dyin[o_in + p] = dy[row * P + p];
+        doff[o_off + p] = __float2bfloat16(gy * e);
+        dx[row * P + p] = __float2bfloat16(dn * gy);
+        s_e += gy * off[o_off + p];
+        s_d += gy * __bfloat162float(x[row * P + p]);
+    }
+    s_e = warp_sum(s_e);
+    s_d = warp_sum(s_d);
+    if (lane == 0) {
+        decum[row] = s_e;
+        dDp[row] = s_d;
+    }
+}
+
 }  // namespace lme
 
 using namespace lme;
@@ -127,5 +257,50 @@ extern "C" int lme_ssd_dcb(const void* dm, const float* cum, void* dcb, long lon
     if (L <= 256) ssd_dcb_kernel<1><<<grid, 256, 0, st>>>(DM, cum, DC, rows, N, G, L);
     else if (L <= 512) ssd_dcb_kernel<2><<<grid, 256, 0, st>>>(DM, cum, DC, rows, N, G, L);
     else ssd_dcb_kernel<4><<<grid, 256, 0, st>>>(DM, cum, DC, rows, N, G, L);
+    return LME_LAUNCH_OK();
+}
+
+// Scan glue (see the kernels): BC = batch x chunks, L % 32 == 0, P in {32, 64, 128}, N % G == 0.  mode 0 = forward,
+// 1 = backward; unused pointers of a mode may be null.
+extern "C" int lme_ssd_prep(const void* x, const float* dt, const float* tail, void* xh, void* xwT,
+                            const float* dxh, const void* dxwT, void* dx, float* ddt, float* dtail, long long BC,
+                            int N, int L, int P, int mode, void* stream) {
+    if (BC <= 0) return LME_OK;
+    if (L % lme::GLUE_ROWS || BC > 65535 || N > 65535) return LME_ERR_SHAPE;
+    dim3 grid(L / lme::GLUE_ROWS, N, static_cast<unsigned>(BC));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto X = static_cast<const __nv_bfloat16*>(x);
+#define LME_PREP(PP)                                                                                                  \
+    if (mode == 0)                                                                                                    \
+        ssd_prep_kernel<PP><<<grid, 256, 0, st>>>(X, dt, tail, static_cast<__nv_bfloat16*>(xh),                       \
+                                                  static_cast<__nv_bfloat16*>(xwT), N, L);                           \
+    else                                                                                                              \
+        ssd_prep_bwd_kernel<PP><<<grid, 256, 0, st>>>(X, dt, tail, dxh, static_cast<const __nv_bfloat16*>(dxwT),      \
+                                                      static_cast<__nv_bfloat16*>(dx), ddt, dtail, N, L);
+    if (P == 32) { LME_PREP(32) } else if (P == 64) { LME_PREP(64) } else if (P == 128) { LME_PREP(128) } else return LME_ERR_SHAPE;
+#undef LME_PREP
+    return LME_LAUNCH_OK();
+}
+
+extern "C" int lme_ssd_combine(const float* yin, const float* off, const float* ecum, const float* D, const void* x,
+                               void* y, const void* dy, void* dyin, void* doff, float* decum, float* dDp, void* dx,
+                               long long BC, int N, int L, int G, int P, int mode, void* stream) {
+    if (BC <= 0) return LME_OK;
+    if (N % G) return LME_ERR_SHAPE;
+    const long long rows = BC * L * N;
+    const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto X = static_cast<const __nv_bfloat16*>(x);
+#define LME_COMB(PP)                                                                                                  \
+    if (mode == 0)                                                                                                    \
+        ssd_combine_kernel<PP><<<grid, 256, 0, st>>>(yin, off, ecum, D, X, static_cast<__nv_bfloat16*>(y), rows, N,  \
+                                                     L, G);                                                           \
+    else                                                                                                              \
+        ssd_combine_bwd_kernel<PP><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), off, ecum, D, X,      \
+                                                         static_cast<__nv_bfloat16*>(dyin),                           \
+                                                         static_cast<__nv_bfloat16*>(doff), decum, dDp,               \
+                                                         static_cast<__nv_bfloat16*>(dx), rows, N, L, G);
+    if (P == 32) { LME_COMB(32) } else if (P == 64) { LME_COMB(64) } else if (P == 128) { LME_COMB(128) } else return LME_ERR_SHAPE;
+#undef LME_COMB
     return LME_LAUNCH_OK();
 }

@@ -196,6 +196,18 @@ int lme_attention_bwd(const void* q, long long ldq, const void* k, long long ldk
                       int Hq, int Hkv, int causal, int window, float scale, const int* cu_seqlens,
                       long long total_tokens, void* stream);
 
+// Element-wise glue of the chunked SSD scan (kernels/ssd.cu), BC = batch x chunks, L % 32 == 0, P in {32, 64, 128}:
+//   prep    (mode 0) xh[BC,N,L,P] = x[BC,L,N,P] dt[BC,L,N];  xwT[BC,N,P,L] = x dt tail, transposed          (bf16)
+//           (mode 1) dx, ddt, dtail from dxh (fp32 [BC,N,L,P]) and dxwT (bf16 [BC,N,P,L])
+//   combine (mode 0) y[BC,L,N,P] = yin[BC,N,L,P] + off[BC,G,L,(N/G)P] ecum[BC,L,N] + D[n] x                 (bf16 out)
+//           (mode 1) dyin, doff (bf16), decum, dDp[BC,L,N] (fp32 row sums of dy x), dx = D dy
+int lme_ssd_prep(const void* x, const float* dt, const float* tail, void* xh, void* xwT, const float* dxh,
+                 const void* dxwT, void* dx, float* ddt, float* dtail, long long BC, int N, int L, int P, int mode,
+                 void* stream);
+int lme_ssd_combine(const float* yin, const float* off, const float* ecum, const float* D, const void* x, void* y,
+                    const void* dy, void* dyin, void* doff, float* decum, float* dDp, void* dx, long long BC, int N,
+                    int L, int G, int P, int mode, void* stream);
+
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);
 

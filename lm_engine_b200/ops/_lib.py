@@ -73,6 +73,8 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_reduce_slices": [P, I, P, L, I, F, I, P],
             "lme_ssd_decay_matrix": [P, P, P, L, I, I, I, P],
             "lme_ssd_dcb": [P, P, P, L, I, I, I, P],
+            "lme_ssd_prep": [P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, P],
+            "lme_ssd_combine": [P, P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
             "lme_m2rnn": [P, I, P],
             "lme_rnn": [P, I, P],
             "lme_attention_fwd": [P, L, P, L, P, L, P, L, P, I, I, I, I, I, I, I, F, P, L, P],

@@ -107,6 +107,91 @@ class _IntraChunk(torch.autograd.Function):
         return dCB, dct, dxdt
 
 
+class _ScanPrep(torch.autograd.Function):
+    """``xh[b,c,n,l,:] = x dt`` and ``xwT[b,c,n,:,l] = x dt tail`` (bf16 operands of the intra-chunk and the
+    chunk-state products) from ``x [b, nc, L, N, P]`` bf16 and ``dt``, ``tail [b, nc, L, N]`` fp32, in one kernel;
+    one more for all three gradients."""
+
+    @staticmethod
+    def forward(ctx, x, dt, tail):
+        from . import _lib
+
+        b, nc, L, N, P = x.shape
+        x, dt, tail = x.contiguous(), dt.contiguous(), tail.contiguous()
+        xh = torch.empty((b, nc, N, L, P), dtype=torch.bfloat16, device=x.device)
+        xwT = torch.empty((b, nc, N, P, L), dtype=torch.bfloat16, device=x.device)
+        _lib.check(_lib.cuda_lib().lme_ssd_prep(x.data_ptr(), dt.data_ptr(), tail.data_ptr(), xh.data_ptr(),
+                                                xwT.data_ptr(), None, None, None, None, None, b * nc, N, L, P, 0,
+                                                _lib.stream_ptr()), "lme_ssd_prep")
+        _lib.count_launch()
+        ctx.save_for_backward(x, dt, tail)
+        return xh, xwT
+
+    @staticmethod
+    def backward(ctx, dxh, dxwT):
+        from . import _lib
+
+        x, dt, tail = ctx.saved_tensors
+        b, nc, L, N, P = x.shape
+        dxh = (torch.zeros((b, nc, N, L, P), dtype=torch.float32, device=x.device) if dxh is None
+               else dxh.float().contiguous())
+        dxwT = (torch.zeros((b, nc, N, P, L), dtype=torch.bfloat16, device=x.device) if dxwT is None
+                else dxwT.to(torch.bfloat16).contiguous())
+        dx = torch.empty_like(x)
+        ddt, dtail = torch.empty_like(dt), torch.empty_like(tail)
+        _lib.check(_lib.cuda_lib().lme_ssd_prep(x.data_ptr(), dt.data_ptr(), tail.data_ptr(), None, None,
+                                                dxh.data_ptr(), dxwT.data_ptr(), dx.data_ptr(), ddt.data_ptr(),
+                                                dtail.data_ptr(), b * nc, N, L, P, 1, _lib.stream_ptr()),
+                   "lme_ssd_prep(backward)")
+        _lib.count_launch()
+        return dx, ddt, dtail
+
+
+class _ScanCombine(torch.autograd.Function):
+    """``y = yin^T + off ecum + D x`` in bf16 ``[b, nc, L, N, P]`` from the intra-chunk result ``yin [b,nc,N,L,P]``,
+    the carried-state product ``off [b,nc,G,L,(N/G) P]`` (both fp32), ``ecum [b,nc,L,N]``, ``D [N]`` and ``x``."""
+
+    @staticmethod
+    def forward(ctx, yin, off, ecum, D, x):
+        from . import _lib
+
+        b, nc, L, N, P = x.shape
+        G = off.size(2)
+        yin, off, ecum, D, x = yin.contiguous(), off.contiguous(), ecum.contiguous(), D.contiguous(), x.contiguous()
+        y = torch.empty_like(x)
+        _lib.check(_lib.cuda_lib().lme_ssd_combine(yin.data_ptr(), off.data_ptr(), ecum.data_ptr(), D.data_ptr(),
+                                                   x.data_ptr(), y.data_ptr(), None, None, None, None, None, None,
+                                                   b * nc, N, L, G, P, 0, _lib.stream_ptr()), "lme_ssd_combine")
+        _lib.count_launch()
+        ctx.save_for_backward(off, ecum, D, x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _lib
+
+        off, ecum, D, x = ctx.saved_tensors
+        b, nc, L, N, P = x.shape
+        G = off.size(2)
+        dy = dy.to(torch.bfloat16).contiguous()
+        dyin = torch.empty((b, nc, N, L, P), dtype=torch.bfloat16, device=x.device)
+        doff = torch.empty(off.shape, dtype=torch.bfloat16, device=x.device)
+        decum = torch.empty_like(ecum)
+        dDp = torch.empty_like(ecum)
+        dx = torch.empty_like(x)
+        _lib.check(_lib.cuda_lib().lme_ssd_combine(None, off.data_ptr(), ecum.data_ptr(), D.data_ptr(), x.data_ptr(),
+                                                   None, dy.data_ptr(), dyin.data_ptr(), doff.data_ptr(),
+                                                   decum.data_ptr(), dDp.data_ptr(), dx.data_ptr(), b * nc, N, L, G,
+                                                   P, 1, _lib.stream_ptr()), "lme_ssd_combine(backward)")
+        _lib.count_launch()
+        return dyin, doff, decum, dDp.sum((0, 1, 2)), dx
+
+
+def scan_glue_eligible(x: torch.Tensor, L: int) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and L % 32 == 0 and L <= 1024 and x.size(-1) in (32, 64, 128)
+            and FUSED_INTRA_CHUNK)
+
+
 def _intra_chunk_fused(Cc, Bc, ct, xdt):
     """CUDA path of the intra-chunk term.  Cc / Bc ``[b, nc, L, G, Sd]``, ct ``[b, nc, N, L]`` fp32,
     xdt ``[b, nc, L, N, P]`` fp32 -> ``[b, nc, L, N, P]`` fp32."""
@@ -126,20 +211,24 @@ def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
     dtype = x.dtype
     L = chunk_size
     pad = (L - S % L) % L
-    xf, dtf, Bf, Cf = x.float(), dt.float(), B.float(), C.float()
+    kernels = scan_glue_eligible(x, L)          # then x is consumed in bf16 by the glue kernels: no fp32 copy of it
+    xf, dtf, Bf, Cf = (None if kernels else x.float()), dt.float(), B.float(), C.float()
     if pad:
-        xf = torch.nn.functional.pad(xf, (0, 0, 0, 0, 0, pad))
+        if not kernels:
+            xf = torch.nn.functional.pad(xf, (0, 0, 0, 0, 0, pad))
         dtf = torch.nn.functional.pad(dtf, (0, 0, 0, pad))
         Bf = torch.nn.functional.pad(Bf, (0, 0, 0, 0, 0, pad))
         Cf = torch.nn.functional.pad(Cf, (0, 0, 0, 0, 0, pad))
     nc = (S + pad) // L
-    xc = xf.view(b, nc, L, N, P)
+    xc = None if kernels else xf.view(b, nc, L, N, P)
     dtc = dtf.view(b, nc, L, N)
     Bc = Bf.view(b, nc, L, G, Sd)
     Cc = Cf.view(b, nc, L, G, Sd)
     rep = N // G
     dA = dtc * A.float()                                      # [b, nc, L, N]
     cum = torch.cumsum(dA, dim=2)
+    if kernels:
+        return _chunk_scan_kernels(x, pad, dtc, cum, Bc, Cc, D, initial_state, b, S, nc, L, N, P, G, Sd)
     # ---- intra-chunk: y[t] = sum_{s<=t} exp(cum[t]-cum[s]) (C_t.B_s) dt_s x_s
     ct = cum.permute(0, 1, 3, 2)                              # [b, nc, N, L]
     xdt = xc * dtc[..., None]                                 # [b, nc, L, N, P]
@@ -180,6 +269,36 @@ def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
         # padded steps have dt = 0: decay 1, no input, so ``h`` already is the state after the last real token
         pass
     return y.to(dtype), h
+
+
+def _chunk_scan_kernels(x, pad, dtc, cum, Bc, Cc, D, initial_state, b, S, nc, L, N, P, G, Sd):
+    """The CUDA composition of :func:`ssd_chunk_scan`: the element-wise passes are two kernels (:class:`_ScanPrep`,
+    :class:`_ScanCombine`), the L x L part is :class:`_IntraChunk`, the products are batched tensor-core GEMMs; only
+    per-(token, head) scalars (decays) and the short loop over chunk boundaries stay PyTorch ops."""
+    rep = N // G
+    xb = torch.nn.functional.pad(x, (0, 0, 0, 0, 0, pad)) if pad else x
+    xc = xb.reshape(b, nc, L, N, P)
+    tail = torch.exp(cum[:, :, -1:, :] - cum)                 # [b, nc, L, N]
+    xh, xwT = _ScanPrep.apply(xc, dtc, tail)
+    # intra-chunk
+    Cg = Cc.permute(0, 1, 3, 2, 4).to(torch.bfloat16).contiguous()        # [b, nc, G, L, Sd]
+    Bg = Bc.permute(0, 1, 3, 2, 4).to(torch.bfloat16).contiguous()
+    CB = torch.matmul(Cg, Bg.transpose(-1, -2))                          # [b, nc, G, L, L]
+    yin = _IntraChunk.apply(CB, cum.permute(0, 1, 3, 2), xh)             # [b, nc, N, L, P] fp32
+    # chunk summaries S_c [b, nc, G, rep*P, Sd] (the heads of a group folded into the GEMM's M dimension)
+    states = _BmmF32.apply(xwT.view(b * nc * G, rep * P, L), Bg.view(b * nc * G, L, Sd)).view(b, nc, N, P, Sd)
+    h = (torch.zeros(b, N, P, Sd, dtype=torch.float32, device=x.device) if initial_state is None
+         else initial_state.float())
+    chunk_decay = torch.exp(cum[:, :, -1, :])                 # [b, nc, N]
+    starts = []
+    for c in range(nc):
+        starts.append(h)
+        h = h * chunk_decay[:, c, :, None, None] + states[:, c]
+    h0 = torch.stack(starts, dim=1)                           # [b, nc, N, P, Sd]
+    hgT = h0.view(b * nc * G, rep * P, Sd).transpose(1, 2).to(torch.bfloat16).contiguous()
+    off = _BmmF32.apply(Cg.view(b * nc * G, L, Sd), hgT).view(b, nc, G, L, rep * P)
+    y = _ScanCombine.apply(yin, off, torch.exp(cum), D.float(), xc)
+    return y.reshape(b, nc * L, N, P)[:, :S], h
 
 
 def ssd_context_parallel_initial_state(final_zero_init: torch.Tensor, total_decay: torch.Tensor, group) -> torch.Tensor:
