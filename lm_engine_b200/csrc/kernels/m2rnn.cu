@@ -232,6 +232,9 @@ __global__ void __launch_bounds__(32) m2rnn_fwd_kernel(const LmeM2rnnArgs p) {
         }
         __syncwarp();
         const int stage = c & 1;
+        // two steps per trip (small states): the output reduction and stores of one step overlap the dependent
+        // product -> tanh chain of the next
+#pragma unroll(V <= 32 ? 2 : 1)
         for (int st = 0; st < TC; ++st) {
             const int t = t_begin + c * TC + st;
             if (t >= t_end) break;
@@ -407,6 +410,7 @@ __global__ void __launch_bounds__(32) m2rnn_bwd_kernel(const LmeM2rnnArgs p) {
         }
         __syncwarp();
         const int stage = c & 1;
+#pragma unroll(V <= 32 ? 2 : 1)
         for (int st = TC - 1; st >= 0; --st) {
             const int t = t_begin + c * TC + st;
             if (t >= t_end) continue;
