@@ -86,3 +86,36 @@ def test_embedding_and_packing_fall_back_on_cpu():
     packed = pack_sequence(x, cu)
     assert packed.shape == (5, 4) and torch.equal(packed[:2], x[0, 1:])
     assert torch.equal(unpack_sequence(packed, cu, (2, 3, 4))[0, 0], torch.zeros(4))
+
+
+def test_argument_structs_match_the_c_header(tmp_path):
+    """The ctypes mirrors of the scan kernels' argument structs have the size and field offsets the C header gives
+    them (compiled with the host compiler; no GPU or nvcc involved)."""
+    import ctypes
+    import os
+    import shutil
+    import subprocess
+
+    from lm_engine_b200.ops import m2rnn, rnn
+
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        pytest.skip("no host C++ compiler")
+    header = os.path.join(os.path.dirname(m2rnn.__file__), "..", "csrc", "lme_api.h")
+    src = tmp_path / "probe.cpp"
+    src.write_text('#include <cstdio>\n#include <cstddef>\n#include "%s"\n' % os.path.abspath(header) + '''
+int main() {
+    printf("%zu %zu %zu %zu %zu\\n", sizeof(LmeM2rnnArgs), offsetof(LmeM2rnnArgs, h0), offsetof(LmeM2rnnArgs, hprev),
+           offsetof(LmeM2rnnArgs, clip), offsetof(LmeM2rnnArgs, dW_part));
+    printf("%zu %zu %zu %zu\\n", sizeof(LmeRnnArgs), offsetof(LmeRnnArgs, h0), offsetof(LmeRnnArgs, hr),
+           offsetof(LmeRnnArgs, clip));
+    return 0;
+}
+''')
+    exe = tmp_path / "probe"
+    subprocess.run([cxx, "-std=c++17", str(src), "-o", str(exe)], check=True)
+    lines = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    a, b = m2rnn._Args, rnn._Args
+    assert [int(v) for v in lines[0].split()] == [ctypes.sizeof(a), a.h0.offset, a.hprev.offset, a.clip.offset,
+                                                  a.dW_part.offset]
+    assert [int(v) for v in lines[1].split()] == [ctypes.sizeof(b), b.h0.offset, b.hr.offset, b.clip.offset]
