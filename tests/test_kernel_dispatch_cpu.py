@@ -119,3 +119,27 @@ int main() {
     assert [int(v) for v in lines[0].split()] == [ctypes.sizeof(a), a.h0.offset, a.hprev.offset, a.clip.offset,
                                                   a.dW_part.offset]
     assert [int(v) for v in lines[1].split()] == [ctypes.sizeof(b), b.h0.offset, b.hr.offset, b.clip.offset]
+
+
+def test_ctypes_signatures_have_the_arity_of_the_header():
+    """Every entry point bound in ops/_lib.py is declared in csrc/lme_api.h with the same number of parameters."""
+    import os
+    import re
+
+    from lm_engine_b200.ops import _lib
+
+    header = open(os.path.join(os.path.dirname(_lib.__file__), "..", "csrc", "lme_api.h")).read()
+    header = re.sub(r"//[^\n]*", "", header)
+    declared = {}
+    for m in re.finditer(r"\bint\s+(lme_\w+)\s*\(([^;{]*?)\)\s*;", header, flags=re.S):
+        params = m.group(2).strip()
+        declared[m.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+    source = open(_lib.__file__).read()
+    bound = {}
+    for m in re.finditer(r'"(lme_\w+)":\s*\[([^\]]*)\]', source):
+        bound[m.group(1)] = len([a for a in m.group(2).split(",") if a.strip()])
+    assert len(bound) > 30
+    missing = sorted(set(bound) - set(declared))
+    assert not missing, missing
+    wrong = {k: (bound[k], declared[k]) for k in bound if bound[k] != declared[k]}
+    assert not wrong, wrong
