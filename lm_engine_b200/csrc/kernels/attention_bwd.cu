@@ -520,21 +520,30 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             uint8_t* dst = smem + OFF_DST + s * PT;
             {
                 uint32_t pp[16], dd[16];
+                // the statistics are the same for every lane: read them as 16-byte broadcasts, four columns at a time
+                const float4* lse4 = reinterpret_cast<const float4*>(st + half * 32);
+                const float4* del4 = reinterpret_cast<const float4*>(st + TN + half * 32);
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int col = half * 32 + e;
-                    float p0 = ex2(fmaf(__uint_as_float(sv[e]), sl2, -st[col] * LOG2E));
-                    float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), sl2, -st[col + 1] * LOG2E));
-                    if (masked) {
-                        const int qc = i * TN + col;                  // query of this column; it sees keys <= qc + shift
-                        const int qv = qc + shift;
-                        if (qc >= len_q || (p.causal && (kr > qv || (p.window > 0 && kr <= qv - p.window)))) p0 = 0.f;
-                        if (qc + 1 >= len_q || (p.causal && (kr > qv + 1 || (p.window > 0 && kr <= qv + 1 - p.window)))) p1 = 0.f;
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 l4 = lse4[e4], d4 = del4[e4];
+                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int e = e4 * 4 + h2 * 2;
+                        const int col = half * 32 + e;
+                        float p0 = ex2(fmaf(__uint_as_float(sv[e]), sl2, -ls[h2 * 2] * LOG2E));
+                        float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), sl2, -ls[h2 * 2 + 1] * LOG2E));
+                        if (masked) {
+                            const int qc = i * TN + col;              // query of this column; it sees keys <= qc + shift
+                            const int qv = qc + shift;
+                            if (qc >= len_q || (p.causal && (kr > qv || (p.window > 0 && kr <= qv - p.window)))) p0 = 0.f;
+                            if (qc + 1 >= len_q || (p.causal && (kr > qv + 1 || (p.window > 0 && kr <= qv + 1 - p.window)))) p1 = 0.f;
+                        }
+                        const float d0 = p0 * (__uint_as_float(dp[e]) - ds[h2 * 2]) * p.scale;
+                        const float d1 = p1 * (__uint_as_float(dp[e + 1]) - ds[h2 * 2 + 1]) * p.scale;
+                        pp[e >> 1] = pack_bf16x2(p0, p1);
+                        dd[e >> 1] = pack_bf16x2(d0, d1);
                     }
-                    const float d0 = p0 * (__uint_as_float(dp[e]) - st[TN + col]) * p.scale;
-                    const float d1 = p1 * (__uint_as_float(dp[e + 1]) - st[TN + col + 1]) * p.scale;
-                    pp[e >> 1] = pack_bf16x2(p0, p1);
-                    dd[e >> 1] = pack_bf16x2(d0, d1);
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
