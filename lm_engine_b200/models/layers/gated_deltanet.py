@@ -19,6 +19,7 @@ from .decay_gate import SoftplusDecayGate
 from .init_utils import std_for_linear
 from .linear import ParameterizedLinear
 from .norm import get_normalization_function
+from .packed import PackedBatch
 from .recurrent import run_per_sample
 
 
@@ -27,7 +28,7 @@ class GatedDeltaNet(nn.Module):
                  m_width, num_layers: int, use_depth_scaled_init: bool, use_padding_free_transformer: bool = False,
                  layer_norm_epsilon: float = 1e-5) -> None:
         super().__init__()
-        assert not use_padding_free_transformer
+        self.use_padding_free_transformer = use_padding_free_transformer
         self.allow_neg_eigval, self.use_gate, self.layer_idx = config.allow_neg_eigval, config.use_gate, layer_idx
         self.num_k_heads, self.num_v_heads = config.num_k_heads, config.num_v_heads
         self.k_head_dim, self.v_head_dim = config.k_head_dim, config.v_head_dim
@@ -50,8 +51,9 @@ class GatedDeltaNet(nn.Module):
     def forward(self, hidden_states, cache_params: GenerationCache | None = None,
                 attention_mask_info: AttentionMaskInfo | None = None, position_info: PositionInfo | None = None):
         info, _ = resolve_attention_and_position_info(attention_mask_info, position_info)
-        mask = info.recurrent_mask(cache_params)
-        B, S = hidden_states.shape[:2]
+        layout = PackedBatch.of(self.use_padding_free_transformer, info, hidden_states, cache_params)
+        mask = layout.mask if layout is not None else info.recurrent_mask(cache_params)
+        B, S = (layout.num_sequences, layout.max_seqlen) if layout is not None else hidden_states.shape[:2]
         c = h = None
         if cache_params is not None:
             c, h = cache_params.get(self.layer_idx, "conv"), cache_params.get(self.layer_idx, "state")
@@ -61,6 +63,8 @@ class GatedDeltaNet(nn.Module):
             a, b, gate = ab.split((self.num_v_heads, self.num_v_heads, self.value_dim), dim=-1)
         else:
             a, b = ab.chunk(2, dim=-1)
+        if layout is not None:
+            qkv, a, b = layout.unpack(qkv), layout.unpack(a), layout.unpack(b)
         qkv, c = self.qkv_conv1d(qkv, c, mask, output_state=cache_params is not None)
         q, k, v = qkv.split((self.key_dim, self.key_dim, self.value_dim), dim=-1)
         q = q.view(B, S, -1, self.k_head_dim)
@@ -76,10 +80,12 @@ class GatedDeltaNet(nn.Module):
         o, h = run_per_sample(
             lambda t, st: gated_delta_rule(t[0], t[1], t[2], t[3], t[4], self.attention_multiplier, st, True),
             mask, [q, k, v, g, beta], h)
+        if layout is not None:
+            o = layout.pack(o)
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)
             cache_params.update(self.layer_idx, "state", h, GenerationCache.REPLACE)
         if self.use_gate:
-            o = o * silu(gate.view(B, S, -1, self.v_head_dim))
+            o = o * silu(gate.view(*o.shape[:-2], -1, self.v_head_dim))
         o = self.o_norm(o)
         return self.o_proj(o.flatten(-2, -1))

@@ -16,6 +16,7 @@ from .conv import DepthwiseCausalConvolution
 from .init_utils import std_for_linear
 from .linear import ParameterizedLinear
 from .norm import get_normalization_function
+from .packed import PackedBatch
 from .recurrent import run_per_sample
 
 
@@ -24,7 +25,7 @@ class LinearAttention(nn.Module):
                  num_layers: int, layer_idx: int, use_depth_scaled_init: bool,
                  use_padding_free_transformer: bool = False, layer_norm_epsilon: float = 1e-5) -> None:
         super().__init__()
-        assert not use_padding_free_transformer, "packed inputs need the CUDA recurrence kernels"
+        self.use_padding_free_transformer = use_padding_free_transformer
         self.k_head_dim, self.v_head_dim, self.layer_idx = config.k_head_dim, config.v_head_dim, layer_idx
         self.kernel_size, self.activation_string = config.kernel_size, config.activation_function
         self.num_q_heads, self.num_k_heads = config.num_q_heads, config.num_k_heads
@@ -55,12 +56,15 @@ class LinearAttention(nn.Module):
     def forward(self, x, cache_params: GenerationCache | None = None,
                 attention_mask_info: AttentionMaskInfo | None = None, position_info: PositionInfo | None = None):
         info, _ = resolve_attention_and_position_info(attention_mask_info, position_info)
-        mask = info.recurrent_mask(cache_params)
-        B, S = x.shape[:2]
+        layout = PackedBatch.of(self.use_padding_free_transformer, info, x, cache_params)
+        mask = layout.mask if layout is not None else info.recurrent_mask(cache_params)
+        B, S = (layout.num_sequences, layout.max_seqlen) if layout is not None else x.shape[:2]
         c = h = None
         if cache_params is not None:
             c, h = cache_params.get(self.layer_idx, "conv"), cache_params.get(self.layer_idx, "state")
         xc, g = self.input_projection(x).split((self.conv_dim, self.g_shape), dim=-1)
+        if layout is not None:
+            xc = layout.unpack(xc)
         if self.kernel_size is not None:
             xc, c = self.conv1d(xc, c, mask, output_state=cache_params is not None)
         q, k, v = xc.split((self.q_shape, self.k_shape, self.v_shape), dim=-1)
@@ -69,6 +73,8 @@ class LinearAttention(nn.Module):
         v = v.view(B, S, self.num_v_heads, self.v_head_dim)
         y, h = run_per_sample(lambda t, st: linear_attention(t[0], t[1], t[2], st, self.attention_multiplier),
                               mask, [q, k, v], h)
+        if layout is not None:
+            y = layout.pack(y)
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)
             cache_params.update(self.layer_idx, "state", h, GenerationCache.REPLACE)

@@ -23,6 +23,7 @@ from .decay_gate import SoftplusDecayGate
 from .init_utils import std_for_linear
 from .linear import ParameterizedLinear
 from .norm import get_normalization_function
+from .packed import PackedBatch
 from .recurrent import run_per_sample
 
 
@@ -31,7 +32,7 @@ class M2RNN(nn.Module):
                  num_layers: int, layer_idx: int, use_depth_scaled_init: bool,
                  use_padding_free_transformer: bool = False, layer_norm_epsilon: float = 1e-5) -> None:
         super().__init__()
-        assert not use_padding_free_transformer, "packed inputs need the CUDA recurrence kernels"
+        self.use_padding_free_transformer = use_padding_free_transformer
         self.k_head_dim, self.v_head_dim, self.layer_idx = config.k_head_dim, config.v_head_dim, layer_idx
         self.kernel_size, self.activation_string = config.kernel_size, config.activation_function
         self.gradient_clipping, self.use_residual = config.gradient_clipping, config.use_residual
@@ -82,8 +83,9 @@ class M2RNN(nn.Module):
     def forward(self, x, cache_params: GenerationCache | None = None,
                 attention_mask_info: AttentionMaskInfo | None = None, position_info: PositionInfo | None = None):
         info, _ = resolve_attention_and_position_info(attention_mask_info, position_info)
-        mask = info.recurrent_mask(cache_params)
-        B, S = x.shape[:2]
+        layout = PackedBatch.of(self.use_padding_free_transformer, info, x, cache_params)
+        mask = layout.mask if layout is not None else info.recurrent_mask(cache_params)
+        B, S = (layout.num_sequences, layout.max_seqlen) if layout is not None else x.shape[:2]
         cp = ProcessGroupManager.is_context_parallel_enabled()
         if cp:
             assert cache_params is None and mask is None
@@ -93,6 +95,8 @@ class M2RNN(nn.Module):
             c, h = cache_params.get(self.layer_idx, "conv"), cache_params.get(self.layer_idx, "state")
         xc, f, g = self.input_projection(x).split((self.conv_dim, self.num_f_heads, self.g_shape), dim=-1)
         f, _ = self.decay_gate(f, final_exponential=True, output_dtype=f.dtype)
+        if layout is not None:
+            xc, f = layout.unpack(xc), layout.unpack(f)
         if self.kernel_size is not None:
             xc, c = self.conv1d(xc, c, mask, output_state=cache_params is not None)
         q, k, v = xc.split((self.q_shape, self.k_shape, self.v_shape), dim=-1)
@@ -112,6 +116,8 @@ class M2RNN(nn.Module):
             y, h = run_per_sample(scan, mask, [q, k, v, f], h)
         if self.use_residual:
             y = y + v.repeat_interleave(self.num_heads // self.num_v_heads, dim=2) * self.D
+        if layout is not None:
+            y = layout.pack(y)
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)
             cache_params.update(self.layer_idx, "state", h, GenerationCache.REPLACE)

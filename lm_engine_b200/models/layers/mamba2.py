@@ -24,6 +24,7 @@ from .decay_gate import SoftplusDecayGate
 from .init_utils import std_for_linear
 from .linear import ParameterizedLinear
 from .norm import get_normalization_function
+from .packed import PackedBatch
 
 
 class Mamba2(nn.Module):
@@ -31,6 +32,7 @@ class Mamba2(nn.Module):
                  m_width: float | None, init_method: str, num_layers: int, layer_idx: int,
                  use_depth_scaled_init: bool = False, use_padding_free_transformer: bool = False) -> None:
         super().__init__()
+        self.use_padding_free_transformer = use_padding_free_transformer
         self.num_heads, self.hidden_size = config.num_heads, hidden_size
         self.ssm_state_size, self.num_groups = config.state_size, config.num_groups
         self.intermediate_size, self.layer_idx = config.intermediate_size, layer_idx
@@ -63,15 +65,21 @@ class Mamba2(nn.Module):
                 attention_mask_info: AttentionMaskInfo | None = None,
                 position_info: PositionInfo | None = None) -> torch.Tensor:
         info, _ = resolve_attention_and_position_info(attention_mask_info, position_info)
-        assert info.cu_seqlens is None
-        mask = info.recurrent_mask(cache_params)
-        x = apply_mask_to_padding_states(x, mask)
-        b, S, _ = x.shape
+        layout = PackedBatch.of(self.use_padding_free_transformer, info, x, cache_params)
+        if layout is not None:
+            mask, b, S = layout.mask, layout.num_sequences, layout.max_seqlen
+        else:
+            assert info.cu_seqlens is None
+            mask = info.recurrent_mask(cache_params)
+            x = apply_mask_to_padding_states(x, mask)
+            b, S, _ = x.shape
         I, G, Sd, N, P = self.intermediate_size, self.num_groups, self.ssm_state_size, self.num_heads, self.head_dim
         c = h = None
         if cache_params is not None:
             c, h = cache_params.get(self.layer_idx, "conv"), cache_params.get(self.layer_idx, "ssm")
         gate, xBC, dt = self.in_proj(x).split((I, self.conv_dim, N), dim=-1)
+        if layout is not None:
+            xBC, dt = layout.unpack(xBC), layout.unpack(dt)
         xBC, c = self.conv1d(xBC, c, mask, output_state=cache_params is not None)
         A = -torch.exp(self.decay_gate.A_log.float())
         dt = self.decay_gate.get_dt(dt, *self.time_step_limit)
@@ -93,5 +101,8 @@ class Mamba2(nn.Module):
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)
             cache_params.update(self.layer_idx, "ssm", h, GenerationCache.REPLACE)
-        y = y.reshape(b, S, I) * silu(gate)
+        y = y.reshape(b, S, I)
+        if layout is not None:
+            y = layout.pack(y)
+        y = y * silu(gate)
         return self.out_proj(self.norm(y))

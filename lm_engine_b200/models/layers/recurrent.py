@@ -20,13 +20,20 @@ from .conv import DepthwiseCausalConvolution
 from .init_utils import std_for_linear
 from .linear import ParameterizedLinear
 from .norm import get_normalization_function
+from .packed import PackedBatch
 
 
 def run_per_sample(fn, mask: torch.Tensor | None, tensors: list[torch.Tensor], state):
-    """Runs ``fn(tensors, state) -> (y, state)`` on the un-padded suffix of every sample of a left-padded batch
-    (what pack -> kernel -> unpack does in the reference); identity wrapper when there is no padding."""
+    """``fn(tensors, state) -> (y, state)`` on a left-padded batch so that every sample sees only its own tokens
+    (what pack -> kernel -> unpack does in the reference); identity wrapper when there is no padding.  Only a padded
+    batch that also carries a state is run sample by sample."""
     if mask is None:
         return fn(tensors, state)
+    if state is None:
+        # zero inputs and a zero state keep every recurrence here at zero through the padding in front of a sample,
+        # so the whole batch runs as one scan
+        keep = [mask.view(*mask.shape, *([1] * (t.dim() - 2))).to(t.dtype) for t in tensors]
+        return fn([t * m for t, m in zip(tensors, keep)], None)
     B, S = mask.shape
     ys, hs = [], []
     for b in range(B):
@@ -41,7 +48,7 @@ def run_per_sample(fn, mask: torch.Tensor | None, tensors: list[torch.Tensor], s
 class _RecurrentBase(nn.Module):
     def _common(self, hidden_size, config, init_method, initializer_range, m_width, num_layers, layer_idx,
                 use_depth_scaled_init, use_padding_free_transformer, in_width: int) -> None:
-        assert not use_padding_free_transformer, "packed inputs need the CUDA recurrence kernels"
+        self.use_padding_free_transformer = use_padding_free_transformer
         self.layer_idx = layer_idx
         self.gradient_clipping = config.gradient_clipping
         self.state_head_dim = config.state_head_dim
@@ -109,16 +116,21 @@ class RNN(_RecurrentBase):
     def forward(self, x, cache_params: GenerationCache | None = None,
                 attention_mask_info: AttentionMaskInfo | None = None, position_info: PositionInfo | None = None):
         info, _ = resolve_attention_and_position_info(attention_mask_info, position_info)
-        mask = info.recurrent_mask(cache_params)
-        S = x.size(1)
+        layout = PackedBatch.of(self.use_padding_free_transformer, info, x, cache_params)
+        mask = layout.mask if layout is not None else info.recurrent_mask(cache_params)
+        S = x.size(-2)
         c = h = None
         if cache_params is not None:
             c, h = cache_params.get(self.layer_idx, "conv"), cache_params.get(self.layer_idx, "state")
         xi, g = self.input_projection(x).split((self.x_shape, self.g_shape), dim=-1)
+        if layout is not None:
+            xi = layout.unpack(xi)
         xi, c = self._input_branch(xi, c, mask, cache_params is not None)
         xi = xi.view(*xi.shape[:-1], -1, self.state_head_dim)
         y, h = run_per_sample(lambda t, st: rnn(t[0], self.state_weight, st, self.gradient_clipping), mask,
                               [xi], h)
+        if layout is not None:
+            y = layout.pack(y)
         return self._finish(y, g, c, h, S, cache_params)
 
 
@@ -142,16 +154,21 @@ class GRU(_RecurrentBase):
     def forward(self, x, cache_params: GenerationCache | None = None,
                 attention_mask_info: AttentionMaskInfo | None = None, position_info: PositionInfo | None = None):
         info, _ = resolve_attention_and_position_info(attention_mask_info, position_info)
-        mask = info.recurrent_mask(cache_params)
-        S = x.size(1)
+        layout = PackedBatch.of(self.use_padding_free_transformer, info, x, cache_params)
+        mask = layout.mask if layout is not None else info.recurrent_mask(cache_params)
+        S = x.size(-2)
         c = h = None
         if cache_params is not None:
             c, h = cache_params.get(self.layer_idx, "conv"), cache_params.get(self.layer_idx, "state")
         xi, xf, xr, g = self.input_projection(x).split(self.splits, dim=-1)
+        if layout is not None:
+            xi, xf, xr = layout.unpack(xi), layout.unpack(xf), layout.unpack(xr)
         xi, c = self._input_branch(xi, c, mask, cache_params is not None)
         d = self.state_head_dim
         xi, xf, xr = (t.view(*t.shape[:-1], -1, d) for t in (xi, xf, xr))
         W, Wf, Wr = self.state_weight.split(self.weight_heads, dim=0)
         y, h = run_per_sample(lambda t, st: gru(t[0], t[1], t[2], W, Wf, Wr, st, self.gradient_clipping), mask,
                               [xi, xf, xr], h)
+        if layout is not None:
+            y = layout.pack(y)
         return self._finish(y, g, c, h, S, cache_params)
