@@ -37,7 +37,7 @@ def _config(kind: str) -> dict:
     return d
 
 
-def _train(rank, world, kind, topo, weights_dir, steps, total_mbs, sequence_parallel=False):
+def _train(rank, world, kind, topo, weights_dir, steps, total_mbs, sequence_parallel=False, padding_free=False):
     from lm_engine_b200.distributed import shard_model
     from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
     from lm_engine_b200.optimization.optimizer import ShardedOptimizer
@@ -48,7 +48,7 @@ def _train(rank, world, kind, topo, weights_dir, steps, total_mbs, sequence_para
     dl_rank = ProcessGroupManager.get_data_loading_rank()
     mbs = total_mbs // dl_world
     w = ModelWrapperForPretraining(model_name=weights_dir, micro_batch_size=mbs, sequence_length=SEQ,
-                                   sequence_parallel=sequence_parallel)
+                                   sequence_parallel=sequence_parallel, use_padding_free_transformer=padding_free)
     eng = shard_model(w, stage=3, dtype=torch.float32, communication_dtype=None, seed=1)
     opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 2e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "eps": 1e-10},
                            None, False, 1.0)
@@ -140,3 +140,16 @@ def _ulysses_rank(rank, world, method):
 @pytest.mark.parametrize("method", [None, "headtail"])
 def test_ulysses_attention_replicated_kv_heads(method):
     assert all(run_distributed(_ulysses_rank, 4, method))
+
+
+@pytest.mark.parametrize("kind,topo,sp", [("dense", {"tensor_parallel_world_size": 2}, True), ("hybrid", {}, False)],
+                         ids=["tp2-sp", "dp2-hybrid"])
+def test_padding_free_training_matches_the_batched_layout(kind, topo, sp, tmp_path):
+    """Packed tokens [mbs * S] + cu_seqlens on two ranks against the [mbs, S] layout in one process."""
+    steps, total_mbs = 3, 2
+    d, (ref_loss, ref_norm, _) = _reference(kind, tmp_path, steps, total_mbs)
+    outs = run_distributed(_train, 2, kind, topo, d, steps, total_mbs, sp, True)
+    loss = outs[0][0] if outs[0][2] == 1 else [sum(o[0][s] for o in outs) / len(outs) for s in range(steps)]
+    np.testing.assert_allclose(loss, ref_loss, rtol=2e-4)
+    for o in outs:
+        np.testing.assert_allclose(o[1], ref_norm, rtol=2e-3)
