@@ -29,7 +29,6 @@ import subprocess
 
 import numpy as np
 import torch
-import torch.distributed as dist
 import torch.distributed.checkpoint as dcp
 import yaml
 from torch.distributed.tensor import DTensor, Replicate, Shard
@@ -38,7 +37,7 @@ from .accelerator import Accelerator
 from .arguments import DistillationArgs, TrainingArgs, UnshardingArgs
 from .containers import LRSchedulerContainer, ModelContainer, OptimizerContainer
 from .logging_utils import log_rank_0
-from .parallel.manager import ProcessGroupManager, run_rank_n
+from .parallel.manager import ProcessGroupManager
 from .utils import load_yaml, string_to_torch_dtype
 
 _KILLSWITCH = "KILLSWITCH"

@@ -18,7 +18,6 @@ mixed precision, efficient (meta-device) initialisation, and the pipeline schedu
 from __future__ import annotations
 
 import logging
-from typing import Callable
 
 import torch
 import torch.nn as nn
@@ -28,7 +27,6 @@ from .containers import ModelContainer
 from .enums import GradientCheckpointingMethod, ParamsGroupMethod
 from .logging_utils import log_rank_0
 from .parallel.fsdp import FSDPEngine
-from .parallel.manager import ProcessGroupManager
 from .utils import string_to_torch_dtype
 
 

@@ -13,7 +13,6 @@ import os
 import torch
 import torch.nn as nn
 
-from ..enums import Kernel
 from ..kernels import is_fused_linear_cross_entropy_enabled
 from ..logging_utils import log_rank_0
 from ..loss import get_autoregressive_language_modeling_loss, is_aux_loss_zero

@@ -14,7 +14,7 @@ import torch.nn as nn
 from .config import CommonConfig
 from .context import AttentionMaskInfo, GenerationCache, PositionInfo
 from .layers.mlp import MLP
-from .layers.norm import RMSNorm, get_normalization_function
+from .layers.norm import get_normalization_function
 
 
 def get_sequence_mixer(config: CommonConfig, causal: bool, use_padding_free_transformer: bool, layer_idx: int,

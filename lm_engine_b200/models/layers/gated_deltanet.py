@@ -7,7 +7,6 @@ statement of it: the token recurrence for decode, the chunk-parallel (triangular
 
 from __future__ import annotations
 
-import torch
 import torch.nn as nn
 
 from ...ops.recurrence import gated_delta_rule

@@ -4,7 +4,6 @@ module.py:29-206)."""
 
 from __future__ import annotations
 
-import torch
 import torch.nn as nn
 
 from ...ops.recurrence import linear_attention

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..containers import BackwardHookOptimizerContainer, ModelContainer, OptimizerContainer
+from ..containers import ModelContainer, OptimizerContainer
 from ..enums import ParamsGroupMethod
 from ..parallel.fsdp import FSDPEngine
 

@@ -19,9 +19,8 @@ Stages: 0 = replicate everything (DDP); 1/2 = shard optimizer state and gradient
 
 from __future__ import annotations
 
-import math
 import zlib
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable
 
 import torch
