@@ -71,8 +71,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = gridDim.x - 1 - blockIdx.x;        // long (late) query blocks first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // blocks are handed out x first: x runs over (head, batch) and y over the query blocks, late (long) ones first,
+    // so the longest blocks of ALL heads start first and the short ones fill the tail; neighbours in x share K / V
+    const int qb = gridDim.y - 1 - blockIdx.y;
+    const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
     const int hk = h / (p.Hq / p.Hkv);
     const int q0 = qb * BM;
     // rows of this sequence in the token-major operands, and its lengths
@@ -350,7 +352,7 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     if (cu_seqlens ? (S_q != S_kv || total_tokens <= 0) : (S_q % BM || S_kv % BM)) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
     if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
-    if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
+    if (B > 65535 || Hq > 65535 || (S_q + BM - 1) / BM > 65535) return LME_ERR_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(o)) & 15)
         return LME_ERR_ALIGN;
@@ -379,7 +381,7 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     p.cu_seqlens = cu_seqlens;
     p.S_pad = (S_q + BM - 1) / BM * BM;
     p.scale = scale;
-    dim3 grid((S_q + BM - 1) / BM, Hq, B);
+    dim3 grid(static_cast<unsigned>(Hq) * B, (S_q + BM - 1) / BM, 1);
     attn_fwd_kernel<<<grid, 192, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }

@@ -74,8 +74,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = gridDim.x - 1 - blockIdx.x;
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int qb = gridDim.y - 1 - blockIdx.y;        // x = (head, batch), y = query blocks, long ones first
+    const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
     const int hk = h / (p.Hq / p.Hkv);
     const int q0 = qb * ROWS;
     int tok_q = b * p.S_q, tok_k = b * p.S_kv, len_q = p.S_q, len_k = p.S_kv;
@@ -346,7 +346,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int kb = blockIdx.y;                         // x = (K/V head, batch), y = key blocks, long (early) ones first
+    const int hk = blockIdx.x % p.Hkv, b = blockIdx.x / p.Hkv;
     const int G = p.Hq / p.Hkv;
     const int k0 = kb * ROWS;
     int tok_q = b * p.S_q, tok_k = b * p.S_kv, len_q = p.S_q, len_k = p.S_kv;
@@ -606,7 +607,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
     if (cu_seqlens ? (S_q != S_kv || total_tokens <= 0) : (S_q % ROWS || S_kv % ROWS)) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
     if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
-    if (B > 65535 || Hq > 65535) return LME_ERR_TOO_LARGE;
+    if (B > 65535 || Hq > 65535 || (S_kv + ROWS - 1) / ROWS > 65535) return LME_ERR_TOO_LARGE;
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                            reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
                            reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(delta);
@@ -643,7 +644,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         a.dq = static_cast<__nv_bfloat16*>(dq); a.dq_ld = lddq; a.lse = lse; a.delta = delta;
         a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.window = window; a.scale = scale;
         a.cu_seqlens = cu_seqlens; a.S_pad = S_pad;
-        attn_dq_kernel<<<dim3((S_q + ROWS - 1) / ROWS, Hq, B), 320, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        attn_dq_kernel<<<dim3(static_cast<unsigned>(Hq) * B, (S_q + ROWS - 1) / ROWS, 1), 320, dq::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     {   // dK, dV: K and V in 128-row boxes, Q and dO in 64-row boxes
@@ -657,7 +658,7 @@ extern "C" int lme_attention_bwd(const void* q, long long ldq, const void* k, lo
         a.lse = lse; a.delta = delta;
         a.B = B; a.S_q = S_q; a.S_kv = S_kv; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal; a.window = window; a.scale = scale;
         a.cu_seqlens = cu_seqlens; a.S_pad = S_pad;
-        attn_dkv_kernel<<<dim3((S_kv + ROWS - 1) / ROWS, Hkv, B), 320, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
+        attn_dkv_kernel<<<dim3(static_cast<unsigned>(Hkv) * B, (S_kv + ROWS - 1) / ROWS, 1), 320, dkv::SMEM_BYTES, st>>>(tq, tdo, tk, tv, a);
         if (cudaGetLastError() != cudaSuccess) return LME_ERR_LAUNCH;
     }
     return LME_OK;
