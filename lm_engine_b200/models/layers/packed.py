@@ -34,7 +34,11 @@ class PackedBatch:
             return None
         assert cache_params is None, "packed inputs are a training layout: no generation cache"
         assert x.dim() == 2, "padding-free mixers take packed tokens [T, H]"
-        return cls(info.cu_seqlens, info.max_seqlen, x.size(0))
+        cached = getattr(info, "_packed_batch", None)      # one layout per forward pass, shared by the layers
+        if cached is None or cached.total_tokens != x.size(0) or cached.cu_seqlens is not info.cu_seqlens:
+            cached = cls(info.cu_seqlens, info.max_seqlen, x.size(0))
+            info._packed_batch = cached
+        return cached
 
     def unpack(self, t: torch.Tensor) -> torch.Tensor:
         """[T, ...] -> [num_sequences, max_seqlen, ...], zeros in front of the shorter sequences."""
