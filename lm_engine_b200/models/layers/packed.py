@@ -24,8 +24,14 @@ class PackedBatch:
         lengths = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
         self.max_seqlen = int(max_seqlen) if max_seqlen is not None else int(lengths.max())
         self.total_tokens = total_tokens
-        steps = torch.arange(self.max_seqlen, device=cu_seqlens.device)
-        self.mask = (steps[None, :] >= (self.max_seqlen - lengths)[:, None]).to(torch.int64)   # left-padded
+        assert self.total_tokens <= self.num_sequences * self.max_seqlen, "max_seqlen is smaller than a sequence"
+        # every sequence as long as the longest one: the packed rows already are the batch, nothing is padded
+        self.dense = total_tokens == self.num_sequences * self.max_seqlen
+        if self.dense:
+            self.mask = None
+        else:
+            steps = torch.arange(self.max_seqlen, device=cu_seqlens.device)
+            self.mask = (steps[None, :] >= (self.max_seqlen - lengths)[:, None]).to(torch.int64)   # left-padded
 
     @classmethod
     def of(cls, enabled: bool, info, x: torch.Tensor, cache_params) -> "PackedBatch | None":
@@ -42,7 +48,10 @@ class PackedBatch:
 
     def unpack(self, t: torch.Tensor) -> torch.Tensor:
         """[T, ...] -> [num_sequences, max_seqlen, ...], zeros in front of the shorter sequences."""
-        return unpack_sequence(t, self.cu_seqlens, (self.num_sequences, self.max_seqlen, *t.shape[1:]))
+        shape = (self.num_sequences, self.max_seqlen, *t.shape[1:])
+        return t.reshape(shape) if self.dense else unpack_sequence(t, self.cu_seqlens, shape)
 
     def pack(self, t: torch.Tensor) -> torch.Tensor:
+        if self.dense:
+            return t.reshape(self.total_tokens, *t.shape[2:])
         return pack_sequence(t, self.cu_seqlens, self.total_tokens)
