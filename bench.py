@@ -33,13 +33,16 @@ MODELS = {
     "tiny": (2048, 4, 256, 4, 2, 64, 1024, 10000),
     # fine-grained mixture of experts (see MOE): dense dims as above, the MLP of every block is routed
     "moe-64e": (32000, 16, 2048, 16, 4, 128, 1024, 10000),
+    # the mixture-of-experts target config: 24 layers, 64 SwiGLU-1024 experts, top-8, aux 0.01, micro batch 4 per GPU,
+    # experts split over all N GPUs (expert parallel = N) with ZeRO-3 for the rest
+    "moe-ep8": (50304, 24, 2048, 16, 4, 128, 1024, 10000),
     # hybrid: three Mamba-2 (SSD) layers per softmax-attention layer (see HYBRID), no positional embedding
     "hybrid-mamba2": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
     # hybrid: three matrix-state RNN layers per softmax-attention layer (see M2RNN_HYBRID)
     "hybrid-m2rnn": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
 }
 # name: (experts, experts per token, shared expert intermediate size or None, router aux-loss coefficient)
-MOE = {"moe-64e": (64, 8, None, 0.01)}
+MOE = {"moe-64e": (64, 8, None, 0.01), "moe-ep8": (64, 8, None, 0.01)}
 # name: (attention every n-th layer, state size, SSM heads, conv kernel, chunk size)
 HYBRID = {"hybrid-mamba2": (4, 128, 64, 4, 256)}
 # name: (attention every n-th layer, k head dim, v head dim, heads, conv kernel): one q / k head shared by all value
@@ -186,9 +189,12 @@ def run_ours(a) -> dict:
 
     cfg = training_config(a.model, a.seq, a.mbs, a.steps, ["fused_linear_cross_entropy"], None)
     cfg["mixed_precision_args"] = {"dtype": getattr(a, "dtype", "bf16")}
+    env_world = int(os.environ.get("WORLD_SIZE", "1"))
+    ep = env_world if a.model == "moe-ep8" and MOE[a.model][0] % env_world == 0 else 1
+    cfg["distributed_args"]["expert_parallel_world_size"] = ep
     args = TrainingArgs(**cfg)
     d = args.distributed_args
-    ProcessGroupManager(zero_stage=d.stage)
+    ProcessGroupManager(zero_stage=d.stage, expert_parallel_world_size=ep)
     world = ProcessGroupManager.get_world_size()
     rank = ProcessGroupManager.get_global_rank()
     args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
@@ -207,7 +213,8 @@ def run_ours(a) -> dict:
                                        world=ProcessGroupManager.get_data_loading_world_size(), seed=1234)
 
     def step(loader):
-        return train_step_without_pipeline_parallel(models, opts, scheds, loader, 1, 1.0, reduce_metrics=False)
+        # metrics are averaged over the data-parallel ranks and read back every step, as in the reference's step
+        return train_step_without_pipeline_parallel(models, opts, scheds, loader, 1, 1.0, reduce_metrics=True)
 
     def barrier():
         if dist.is_initialized():
@@ -263,7 +270,7 @@ def run_ours(a) -> dict:
         "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": getattr(a, "dtype", "bf16"), "data": "synthetic uniform-random token ids, seeded random-init weights",
         "config": {"model": a.model if a.layers is None else f"{a.model}-{a.layers}layers",
-                   "global_batch": world * a.mbs, "seq_len": a.seq, "parallelism": f"zero3-dp{world}", "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
+                   "global_batch": world * a.mbs, "seq_len": a.seq, "parallelism": f"fsdp2-zero3-dp{world}" + (f"-ep{ep}" if ep > 1 else ""), "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
                    "optimizer": "AdamW fp32 master+state", "l2": "working set per step >> 126 MB L2, no flush"},
         "tokens_per_sec_per_gpu": value / world,
         "model_tflops_per_gpu": tfl / (dev_ms * 1e-3 / a.steps) / world,
@@ -277,8 +284,52 @@ def run_ours(a) -> dict:
         "device_status": status[:4],
         "impl": "lm_engine_b200",
     }
+    if world > 1:
+        out["multi_gpu_check"] = multi_gpu_check(world, rank, device)
     ProcessGroupManager.destroy_process_groups()
     return out if rank == 0 else None
+
+
+def multi_gpu_check(world: int, rank: int, device) -> dict:
+    """Outside the timed region: one step of a small dense model (2 blocks, hidden 1024) sharded over all ranks
+    (ZeRO-3: parameter gathers, the gradient reduce-scatter, the sharded norm) against the same global batch computed
+    by every rank alone on replicated weights.  Both start from the same seeded weights; the mean loss and the global
+    gradient norm of the two have to agree to bf16 accuracy."""
+    import torch
+    import torch.distributed as dist
+
+    from lm_engine_b200.distributed import shard_model
+    from lm_engine_b200.enums import GradientCheckpointingMethod
+    from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+    from lm_engine_b200.models import dense_config
+    from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+
+    seq = 1024
+    cfg = dense_config(vocab_size=8192, hidden_size=1024, num_layers=2, num_attention_heads=8, num_key_value_heads=4,
+                       intermediate_size=4096, head_dim=128, max_position_embeddings=seq).to_dict()
+    tokens = torch.randint(0, 8192, (world, seq + 1), generator=torch.Generator().manual_seed(77)).to(device)
+    res = {}
+    for name, stage, batch in (("sharded", 3, tokens[rank:rank + 1]), ("replicated", 0, tokens)):
+        w = ModelWrapperForPretraining(pretrained_config=cfg, micro_batch_size=batch.size(0), sequence_length=seq,
+                                       efficient_initialization=True, dtype="bf16")
+        eng = shard_model(w, stage=stage, dtype=torch.bfloat16, communication_dtype=None,
+                          gradient_checkpointing_method=GradientCheckpointingMethod.block, seed=7)
+        opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-4, "weight_decay": 0.0, "betas": [0.9, 0.95],
+                                                   "eps": 1e-10}, None, False, 1.0)
+        opt.zero_grad()
+        loss = w(batch, lm_loss_multiplier=1 / (batch.size(0) * seq))["loss"]
+        loss.backward()
+        norm = opt.step()
+        t = torch.stack([loss.detach().float().reshape(()), norm.float().reshape(())])
+        if stage == 3:
+            dist.all_reduce(t[:1])
+            t[0] /= world
+        res[name] = t.tolist()
+        del w, eng, opt
+    return {"loss_sharded": res["sharded"][0], "loss_replicated": res["replicated"][0],
+            "grad_norm_sharded": res["sharded"][1], "grad_norm_replicated": res["replicated"][1],
+            "loss_abs_diff": abs(res["sharded"][0] - res["replicated"][0]),
+            "grad_norm_rel_diff": abs(res["sharded"][1] - res["replicated"][1]) / max(res["replicated"][1], 1e-12)}
 
 
 def main() -> None:
@@ -289,7 +340,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
     ap.add_argument("--seq", type=int, default=4096)
-    ap.add_argument("--mbs", type=int, default=2)
+    ap.add_argument("--mbs", type=int, default=None, help="micro batch per GPU (default 2; 4 for the MoE models)")
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (profiling captures on a small case; not a benchmark result)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
@@ -297,6 +348,8 @@ def main() -> None:
     a = ap.parse_args()
     global LAYERS_OVERRIDE
     LAYERS_OVERRIDE = a.layers
+    if a.mbs is None:
+        a.mbs = 4 if a.model in MOE else 2
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if a.gpus != world:
         if world == 1 and a.gpus > 1:

@@ -71,7 +71,9 @@ def _needs_build(target: str, stamp: str) -> bool:
 def build_cuda(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OUT, exist_ok=True)
     target = os.path.join(OUT, "liblme_cuda.so")
-    deps = _sources("kernels", (".cu", ".cuh")) + [os.path.join(CSRC, "lme_cuda.cu"), os.path.join(CSRC, "lme_api.h")]
+    # every kernel file plus every header and source directly under csrc/ (lme_api.h, lme_noalloc.h, lme_cuda.cu)
+    deps = _sources("kernels", (".cu", ".cuh")) + [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC))
+                                                   if f.endswith((".h", ".cu", ".cuh"))]
     stamp = _tree_hash(deps)
     if force or _needs_build(target, stamp):
         cmd = [_nvcc(), *NVCC_FLAGS, "-o", target, os.path.join(CSRC, "lme_cuda.cu")]

@@ -147,22 +147,53 @@ def load_model_state_dict(model_container: ModelContainer, state: dict[str, torc
 _GROUP_KEYS = ("lr", "betas", "eps", "weight_decay", "initial_lr")
 
 
-def optimizer_state_dict(model_container: ModelContainer, optimizer_container: OptimizerContainer) -> dict:
+def _optimizer_keeps_step(opt) -> bool:
+    """Whether the wrapped torch optimizer class tracks a per-parameter ``step`` (SGD does not)."""
+    return getattr(opt, "class_name", "") not in ("TorchSGD",)
+
+
+def _saved_optimizer_state_names(checkpoint_id: str, prefix: str = "state.") -> tuple[set[str], set[str]]:
+    """Names of the per-element and of the scalar optimizer-state entries in a saved checkpoint (a fresh torch
+    optimizer has no state yet, so the template to load into is shaped after what was saved)."""
+    from torch.distributed.checkpoint import FileSystemReader
+
+    tensors, scalars = set(), set()
+    for k, md in FileSystemReader(checkpoint_id).read_metadata().state_dict_metadata.items():
+        if not k.startswith(prefix + "state.model."):
+            continue
+        which = k.rpartition(".")[2]
+        size = getattr(md, "size", None)
+        (scalars if size is not None and len(size) == 0 else tensors).add(which)
+    return tensors, scalars
+
+
+def optimizer_state_dict(model_container: ModelContainer, optimizer_container: OptimizerContainer,
+                         saved_names: tuple[set[str], set[str]] | None = None) -> dict:
     """Flattened optimizer state in torch's ``flatten_optimizer_state_dict`` key scheme:
-    ``state.<fqn>.{exp_avg,exp_avg_sq,step}`` and ``param_groups.<fqn>.<hyper-parameter>``."""
+    ``state.<fqn>.{exp_avg,exp_avg_sq,step}`` and ``param_groups.<fqn>.<hyper-parameter>``.  ``saved_names``
+    (per-element names, scalar names) adds entries that a checkpoint holds but this optimizer has not created yet."""
     out: dict = {}
     for wrapper, opt in zip(model_container, optimizer_container):
         eng = wrapper.engine
         groups = {g["name"]: g for g in opt.param_groups}
         a = opt.class_args
+        # fused AdamW: the moments are the engine's own shards; any other optimizer class keeps its per-element
+        # state (momentum_buffer, exp_avg, square_avg, max_exp_avg_sq, ...) inside the wrapped torch optimizer
+        fused = getattr(opt, "fused", True)
+        keys = ["exp_avg", "exp_avg_sq"] if fused else opt.tensor_state_keys()
+        scalars = {"step": float(eng.step_count)} if fused else {"step": float(eng.step_count), **opt.scalar_state()}
+        if saved_names is not None and not fused:
+            keys = sorted(set(keys) | saved_names[0])
+            scalars = {**{k: 0.0 for k in saved_names[1]}, **scalars}
         for u in eng.all_units:
-            m, v = eng.gather_full(u, "exp_avg"), eng.gather_full(u, "exp_avg_sq")
+            fulls = {k: eng.gather_full(u, k if fused else opt.unit_state(u, k)) for k in keys}
             for s in u.slots:
                 fqn = f"model.{s.name}"
                 sl = slice(s.offset, s.offset + s.numel)
-                out[f"state.{fqn}.exp_avg"] = _to_dtensor(eng, eng._slot_full(s, m[sl].view(s.shape)), s.param)
-                out[f"state.{fqn}.exp_avg_sq"] = _to_dtensor(eng, eng._slot_full(s, v[sl].view(s.shape)), s.param)
-                out[f"state.{fqn}.step"] = torch.tensor(float(eng.step_count))
+                for k, full in fulls.items():
+                    out[f"state.{fqn}.{k}"] = _to_dtensor(eng, eng._slot_full(s, full[sl].view(s.shape)), s.param)
+                for k, v in scalars.items():
+                    out[f"state.{fqn}.{k}"] = torch.tensor(v)
                 g = groups.get(s.group, groups["normal"])
                 hyper = {"lr": g["lr"], "betas": tuple(a.get("betas", (0.9, 0.999))), "eps": a.get("eps", 1e-8),
                          "weight_decay": 0.0 if s.group == "no_weight_decay" else a.get("weight_decay", 1e-2),
@@ -175,14 +206,30 @@ def optimizer_state_dict(model_container: ModelContainer, optimizer_container: O
 def load_optimizer_state_dict(model_container, optimizer_container, state: dict) -> None:
     for wrapper, opt in zip(model_container, optimizer_container):
         eng = wrapper.engine
-        for which in ("exp_avg", "exp_avg_sq"):
-            plain = {}
-            for u in eng.all_units:
-                for s in u.slots:
-                    key = f"state.model.{s.name}.{which}"
-                    if key in state:
-                        plain[s.name] = _from_saved(state[key], eng)
-            eng.load_full_state_dict(plain, which)
+        fused = getattr(opt, "fused", True)
+        names = {s.name for u in eng.all_units for s in u.slots}
+        found: dict[str, dict[str, torch.Tensor]] = {}       # state key -> slot name -> saved value
+        for k, v in state.items():
+            if k.startswith("state.model."):
+                name, _, which = k[len("state.model."):].rpartition(".")
+                if name in names:
+                    found.setdefault(which, {})[name] = v
+        if fused:
+            for which in ("exp_avg", "exp_avg_sq"):
+                plain = {n: _from_saved(v, eng) for n, v in found.get(which, {}).items()}
+                eng.load_full_state_dict(plain, which)
+        else:
+            scalars = {}
+            for which, by_slot in found.items():
+                first = next(iter(by_slot.values()))
+                if not isinstance(first, DTensor) and first.numel() == 1:
+                    if which != "step" or which in opt.scalar_state() or _optimizer_keeps_step(opt):
+                        scalars[which] = float(first)
+                    continue
+                plain = {n: _from_saved(v, eng) for n, v in by_slot.items()}
+                for u in eng.all_units:
+                    opt.set_unit_state(u, which, eng.local_piece_from_slots(u, plain, opt.unit_state(u, which)))
+            opt.set_scalar_state(scalars)
         steps = [float(v) for k, v in state.items() if k.endswith(".step")]
         if steps:
             eng.step_count = int(max(steps))
@@ -290,7 +337,9 @@ def load_checkpoint_for_training(args: TrainingArgs, args_class: type[TrainingAr
     if saved_args.save_args.async_checkpointing:
         state = {"model": model_state_dict(model_container)}
         if la.load_optimizer:
-            state["optimizer"] = optimizer_state_dict(model_container, optimizer_container)
+            state["optimizer"] = optimizer_state_dict(
+                model_container, optimizer_container,
+                _saved_optimizer_state_names(os.path.join(base, "model_optimizer"), "state.optimizer."))
         wrapped = {"state": state}
         dcp.load(wrapped, checkpoint_id=os.path.join(base, "model_optimizer"))
         load_model_state_dict(model_container, wrapped["state"]["model"])
@@ -301,7 +350,9 @@ def load_checkpoint_for_training(args: TrainingArgs, args_class: type[TrainingAr
         dcp.load(wrapped, checkpoint_id=os.path.join(base, "model"))
         load_model_state_dict(model_container, wrapped["state"])
         if la.load_optimizer:
-            wrapped = {"state": optimizer_state_dict(model_container, optimizer_container)}
+            wrapped = {"state": optimizer_state_dict(
+                model_container, optimizer_container,
+                _saved_optimizer_state_names(os.path.join(base, "optimizer"), "state."))}
             dcp.load(wrapped, checkpoint_id=os.path.join(base, "optimizer"))
             load_optimizer_state_dict(model_container, optimizer_container, wrapped["state"])
     if la.load_lr_scheduler:

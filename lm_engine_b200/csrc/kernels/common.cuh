@@ -19,6 +19,9 @@ namespace lme {
 
 // status[0]: first error code (0 = ok), status[1]: detail (e.g. barrier id), status[2]: block, status[3]: count
 __device__ unsigned int lme_status[8];  // one translation unit: lme_cuda.cu includes every kernel file
+// limit of the waits on words that another GPU writes (lme_set_peer_wait_limit_ms); waits inside one GPU keep
+// LME_WAIT_LIMIT_NS
+__device__ unsigned long long lme_peer_wait_ns = LME_WAIT_LIMIT_NS;
 
 enum StatusCode : unsigned int {
     STATUS_OK = 0,

@@ -484,7 +484,9 @@ extern "C" int lme_rmsnorm_fwd(const void* x, const void* residual, const void* 
 
 // Rows of dw_partial the backward kernel writes for a [T, H] problem (the caller sizes the scratch with it).
 // 3 CTAs of 512 threads are resident per SM (40 registers per thread): one wave of 148 x 3 CTAs
-extern "C" int lme_rmsnorm_bwd_partial_rows(int T) { return T < 444 ? (T < 1 ? 1 : T) : 444; }
+extern "C" int lme_rmsnorm_bwd_partial_rows(int T) {
+    return T < LME_RMSNORM_BWD_MAX_PARTIAL_ROWS ? (T < 1 ? 1 : T) : LME_RMSNORM_BWD_MAX_PARTIAL_ROWS;
+}
 
 // dw_partial: fp32 scratch [lme_rmsnorm_bwd_partial_rows(T), H] (may be null when w is null / dw not needed).
 extern "C" int lme_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,

@@ -72,10 +72,11 @@ __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.pr
 __device__ __forceinline__ bool wait_flag_sys(const int* p, int want, unsigned int id) {
     if (ld_acquire_sys(p) >= want) return true;
     uint64_t t0 = globaltimer_ns();
+    const uint64_t limit = lme_peer_wait_ns;
     uint32_t spins = 0;
     while (ld_acquire_sys(p) < want) {
         __nanosleep(64);
-        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > LME_WAIT_LIMIT_NS) {
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > limit) {
             report_error(STATUS_FLAG_TIMEOUT, id);
             return false;
         }

@@ -101,6 +101,20 @@ int lme_causal_conv1d_bwd(const void* x, const void* w, const void* bias, const 
 int lme_reduce_slices(const void* const* src, int nsrc, void* out, long long n, int is_bf16, float scale,
                       int accumulate, void* stream);
 
+// Gradient reduce-scatter in one kernel: out[n] (=|+=) scale * sum over ranks of this rank's slice of every rank's
+// buffer (symmetric memory; src[r] = the slice inside rank r's buffer as mapped here, [rank] local), fp32 sums in
+// rank order, plus one partial sum of squares of the written values per CTA (partials[ctas], may be null).
+// mc_src != null: the slice's multicast mapping, read with multimem.ld_reduce (the switch adds) instead of
+// `world` peer loads.  pads[r]: 16-word int32 signal pad of rank r; seq = 1, 2, ... per call, the same on every
+// rank.  The kernel announces this rank's buffer, waits (bounded) for every peer's announcement, then reads.
+int lme_reduce_scatter_peers(const void* const* src, int* const* pads, const void* mc_src, int rank, int world,
+                             int seq, void* out, long long n, int is_bf16, float scale, int accumulate,
+                             float* partials, int ctas, void* stream);
+// out[0] (+)= sum of n floats in a fixed order
+int lme_sum_partials(const float* partials, int n, float* out, int accumulate, void* stream);
+// limit of the device-side waits on words written by another GPU (default 2000 ms)
+int lme_set_peer_wait_limit_ms(long long ms);
+
 // Mamba-2 SSD intra-chunk helpers (L % 8 == 0, L <= 1024; BC = batch x chunks):
 //   decay_matrix: m[BC,N,L,L] = cb[BC,G,L,L] * exp(cum[BC,N,l] - cum[BC,N,s]) for s <= l else 0 (bf16; cum fp32)
 //   dcb         : dcb[BC,G,L,L] = sum over the heads of a group of dm[BC,N,L,L] * exp(cum[l] - cum[s]), s <= l
@@ -223,6 +237,9 @@ int lme_read_status(unsigned int* out8, int clear);
 // y = rmsnorm(x (+ residual)) * w; h_out (optional) receives x + residual; rstd (optional) the per-row 1/rms.
 int lme_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out, float* rstd, int T,
                     int H, float eps, void* stream);
+// rows of the weight-gradient scratch that lme_rmsnorm_bwd writes for T rows: min(max(T, 1), 444), one per CTA of
+// a single wave (148 SMs x 3 resident CTAs)
+#define LME_RMSNORM_BWD_MAX_PARTIAL_ROWS 444
 int lme_rmsnorm_bwd_partial_rows(int T);
 // dx = d rmsnorm / d h  (+ dres); dw (fp32, optional accumulate) via the fp32 scratch dw_partial
 // [lme_rmsnorm_bwd_partial_rows(T), H].

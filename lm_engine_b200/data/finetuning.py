@@ -201,15 +201,42 @@ def collate_fn(batch: list[dict], use_output: bool, loss_mask: LossMask, eos_tok
     return out
 
 
+class _LoaderIterator:
+    """Iterator over a dataloader (endless when ``infinite``) that still exposes the loader's ``state_dict`` /
+    ``load_state_dict``, so that a checkpoint can record and restore the sampler position.  Restoring takes effect
+    on the first ``next`` (the underlying iterator is created lazily)."""
+
+    def __init__(self, loader, infinite: bool) -> None:
+        self.loader, self.infinite = loader, infinite
+        self._it = None
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        if self._it is None:
+            self._it = iter(self.loader)
+        try:
+            return next(self._it)
+        except StopIteration:
+            if not self.infinite:
+                raise
+            self._it = iter(self.loader)
+            return next(self._it)
+
+    def state_dict(self) -> dict:
+        return self.loader.state_dict() if hasattr(self.loader, "state_dict") else {}
+
+    def load_state_dict(self, sd: dict) -> None:
+        if hasattr(self.loader, "load_state_dict"):
+            self.loader.load_state_dict(sd)
+        self._it = None
+
+
 def custom_iterator(x: Iterable | None, infinite: bool):
     if x is None:
         return None
-
-    def forever(q):
-        while True:
-            yield from q
-
-    return forever(x) if infinite else iter(x)
+    return _LoaderIterator(x, infinite)
 
 
 def get_finetuning_dataloader(args, tokenizer, split: str | DatasetSplit = "train"):

@@ -79,6 +79,8 @@ class BlendedDistributedSampler(torch.utils.data.DistributedSampler):
 
     def __iter__(self):
         while True:
+            # the permutation of this epoch is drawn from here: a resume inside the epoch must redraw the same one
+            self._epoch_generator_state = self.generator.get_state()
             idx = self._epoch_indices()
             mine = idx[self.rank::self.num_replicas]
             for i in mine[self.index:]:
@@ -91,7 +93,9 @@ class BlendedDistributedSampler(torch.utils.data.DistributedSampler):
         return self.num_samples_total // self.num_replicas
 
     def state_dict(self) -> dict:
-        return {"epoch": self.epoch, "index": self.index, "generator": self.generator.get_state()}
+        state = getattr(self, "_epoch_generator_state", None)
+        return {"epoch": self.epoch, "index": self.index,
+                "generator": state if state is not None else self.generator.get_state()}
 
     def load_state_dict(self, sd: dict) -> None:
         self.epoch, self.index = sd["epoch"], sd["index"]

@@ -71,6 +71,9 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
             "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
             "lme_reduce_slices": [P, I, P, L, I, F, I, P],
+            "lme_reduce_scatter_peers": [P, P, P, I, I, I, P, L, I, F, I, P, I, P],
+            "lme_sum_partials": [P, I, P, I, P],
+            "lme_set_peer_wait_limit_ms": [L],
             "lme_ssd_decay_matrix": [P, P, P, L, I, I, I, P],
             "lme_ssd_dcb": [P, P, P, L, I, I, I, P],
             "lme_ssd_prep": [P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, P],

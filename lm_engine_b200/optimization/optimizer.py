@@ -90,7 +90,53 @@ class ShardedOptimizer:
             for u in e.all_units:
                 if u.world > 1:
                     dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
+        # the peers read this rank's parameter shard for the next step's gathers: order the update before them
+        e._cross_rank_fence()
         return e.grad_norm
+
+    # ------------------------------------------------------------------ state of the torch optimizers, per unit
+    def tensor_state_keys(self) -> list[str]:
+        """Names of the per-element state tensors that the wrapped ``torch.optim`` class keeps (``momentum_buffer``,
+        ``exp_avg``, ``square_avg``, ...); empty before the first step of a fresh optimizer."""
+        keys: list[str] = []
+        if self._torch_opt is None:
+            return keys
+        for p, _, _ in self._aliases:
+            for k, v in self._torch_opt.state.get(p, {}).items():
+                if isinstance(v, torch.Tensor) and v.numel() == p.numel() and v.numel() > 1 and k not in keys:
+                    keys.append(k)
+        return sorted(keys)
+
+    def scalar_state(self) -> dict[str, float]:
+        """Scalar entries (``step`` and the like), the same for every parameter."""
+        out: dict[str, float] = {}
+        if self._torch_opt is None:
+            return out
+        for p, _, _ in self._aliases:
+            for k, v in self._torch_opt.state.get(p, {}).items():
+                if isinstance(v, (int, float)) or (isinstance(v, torch.Tensor) and v.numel() == 1 and p.numel() > 1):
+                    out.setdefault(k, float(v))
+        return out
+
+    def unit_state(self, u, key: str) -> torch.Tensor:
+        """Local fp32 slice (the unit's optimizer-state range of this rank) of state tensor ``key``."""
+        flat = torch.zeros(u.state_hi - u.state_lo, dtype=torch.float32, device=u.master.device)
+        for p, pu, sl in self._aliases:
+            if pu is u:
+                v = self._torch_opt.state.get(p, {}).get(key)
+                if v is not None:
+                    flat[sl].copy_(v.reshape(-1))
+        return flat
+
+    def set_unit_state(self, u, key: str, flat: torch.Tensor) -> None:
+        for p, pu, sl in self._aliases:
+            if pu is u:
+                self._torch_opt.state[p][key] = flat[sl].clone().view_as(p)
+
+    def set_scalar_state(self, scalars: dict[str, float]) -> None:
+        for p, _, _ in self._aliases:
+            for k, v in scalars.items():
+                self._torch_opt.state[p][k] = torch.tensor(float(v), dtype=torch.float32)
 
     def state_dict(self) -> dict:
         sd = {"step": self.engine.step_count, "param_groups": [dict(g) for g in self.param_groups]}

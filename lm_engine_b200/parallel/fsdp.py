@@ -324,11 +324,21 @@ class FSDPEngine:
 
             if os.environ.get("LME_ALLGATHER", "ce") == "ce":
                 self._setup_symmetric_shards()
+        # Gradient reduce-scatter: "fused" (default) = one kernel of ours per unit that reads the peers' buffers over
+        # NVLink, averages, writes the shard and the partial squared norm; "nvls" = the same kernel reading through
+        # the switch (multimem.ld_reduce); "ce" = copy-engine pulls + a local sum; "nccl" = the library collective.
+        self.reduce_mode = "nccl"
+        self.fused_reduce_ctas = 0
         if self.is_cuda and 1 < self.world <= 8 and self.stage >= 1:
             import os
 
-            if os.environ.get("LME_REDUCE_SCATTER", "nccl") == "ce":
+            mode = os.environ.get("LME_REDUCE_SCATTER", "fused")
+            if mode in ("fused", "nvls", "ce"):
                 self._setup_symmetric_reduce()
+                if self.copy_engine_reduce:
+                    self.reduce_mode = mode
+                    self.fused_reduce_ctas = int(os.environ.get("LME_RS_CTAS", "48"))
+                    self.copy_engine_reduce = mode == "ce"
 
     # ------------------------------------------------------------------ initialisation
     @torch.no_grad()
@@ -485,6 +495,7 @@ class FSDPEngine:
         transfer takes no SM from the backward GEMMs it overlaps with."""
         try:
             import ctypes
+            import os
 
             import torch.distributed._symmetric_memory as symm_mem
 
@@ -497,8 +508,17 @@ class FSDPEngine:
             self._rs_seq = 0
             self._rs_stage: torch.Tensor | None = None
             self._symm_grad: dict[int, list[torch.Tensor]] = {}
+            self._symm_grad_mc: dict[int, int] = {}            # buffer -> multicast address (0: none)
+            self._rs_args: dict[tuple[int, int], tuple] = {}   # (buffer, shard size) -> pointer arrays
+            self._rs_partials: torch.Tensor | None = None
+            self._rs_partial_slot: dict[str, int] = {}
             self._last_reduced_buf: int | None = None
             self.copy_engine_reduce = True
+            from ..ops import _lib
+
+            # ranks drift apart by seconds around evaluation, checkpoints and first-step allocations
+            _lib.check(_lib.cuda_lib().lme_set_peer_wait_limit_ms(int(os.environ.get("LME_PEER_WAIT_MS", "60000"))),
+                       "lme_set_peer_wait_limit_ms")
             torch.cuda.synchronize(self.device)
             dist.barrier(group=self.shard_group)
         except Exception as e:  # noqa: BLE001 - symmetric memory unavailable: keep the NCCL reduce-scatter
@@ -510,8 +530,9 @@ class FSDPEngine:
             self.copy_engine_reduce = False
 
     def _ce_reduce_applies(self, u: ShardedUnit) -> bool:
-        return (self.copy_engine_reduce and u.world > 1 and u.group is self.shard_group and u.replica_group is None
-                and not u.is_expert and self.world <= 8)
+        """Units whose gradient buffers live in symmetric memory (reduced by our own kernel or by copy engines)."""
+        return (self.reduce_mode != "nccl" and u.world > 1 and u.group is self.shard_group
+                and u.replica_group is None and not u.is_expert and self.world <= 8)
 
     def _symmetric_grad_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         import torch.distributed._symmetric_memory as symm_mem
@@ -519,6 +540,13 @@ class FSDPEngine:
         buf = symm_mem.empty(numel, dtype=dtype, device=self.device)
         handle = symm_mem.rendezvous(buf, self.shard_group)      # collective: every rank allocates in the same order
         self._symm_grad[buf.data_ptr()] = [handle.get_buffer(r, (numel,), dtype, 0) for r in range(self.world)]
+        mc = 0
+        if self.reduce_mode == "nvls":
+            try:
+                mc = int(handle.multicast_ptr or 0)
+            except Exception:  # noqa: BLE001 - no NVLS mapping on this machine
+                mc = 0
+        self._symm_grad_mc[buf.data_ptr()] = mc
         self._symm_grad_handles = getattr(self, "_symm_grad_handles", []) + [handle]
         return buf
 
@@ -548,6 +576,38 @@ class FSDPEngine:
         _lib.check(lib.lme_reduce_slices(arr, world, u.grad_shard.data_ptr(), S, int(full.dtype == torch.bfloat16),
                                          scale, int(not u.grad_shard_fresh), st), "lme_reduce_slices")
         _lib.count_launch(2)
+        u.grad_shard_fresh = False
+
+    def _reduce_scatter_fused(self, u: ShardedUnit, full: torch.Tensor, scale: float) -> None:
+        """One launch on the reduction stream: announce this rank's buffer, wait (bounded) for the peers', read this
+        rank's slice of every buffer over NVLink, average in fp32, write / accumulate the gradient shard and leave
+        the partial sums of squares for the gradient norm."""
+        import ctypes
+
+        from ..ops import _lib
+
+        S, world, rank = u.shard_size, self.world, self.rank
+        key = (full.data_ptr(), S)
+        args = self._rs_args.get(key)
+        if args is None:
+            peers = self._symm_grad[full.data_ptr()]
+            esz = full.element_size()
+            srcs = (ctypes.c_void_p * 8)(*([peers[p].data_ptr() + rank * S * esz for p in range(world)]
+                                           + [None] * (8 - world)))
+            mc = self._symm_grad_mc.get(full.data_ptr(), 0)
+            args = self._rs_args[key] = (srcs, (mc + rank * S * esz) if mc else None)
+        srcs, mc_src = args
+        ctas = self.fused_reduce_ctas
+        if self._rs_partials is None:
+            self._rs_partial_stride = ctas
+            self._rs_partials = torch.zeros(len(self.all_units) * ctas, dtype=torch.float32, device=self.device)
+        slot = self._rs_partial_slot.setdefault(u.name, len(self._rs_partial_slot))
+        self._rs_seq += 1
+        _lib.check(_lib.cuda_lib().lme_reduce_scatter_peers(
+            srcs, self._rs_pad_arr, mc_src, rank, world, self._rs_seq, u.grad_shard.data_ptr(), S,
+            int(full.dtype == torch.bfloat16), scale, int(not u.grad_shard_fresh),
+            self._rs_partials.data_ptr() + slot * ctas * 4, ctas, _lib.stream_ptr()), "lme_reduce_scatter_peers")
+        _lib.count_launch()
         u.grad_shard_fresh = False
 
     def _cross_rank_fence(self) -> None:
@@ -700,7 +760,10 @@ class FSDPEngine:
                     dist.all_reduce(full, op=avg, group=u.replica_group)
                 return
             if self.is_cuda and full.data_ptr() in getattr(self, "_symm_grad", {}):
-                self._reduce_scatter_ce(u, full, 1.0 / dp_total)
+                if self.reduce_mode == "ce":
+                    self._reduce_scatter_ce(u, full, 1.0 / dp_total)
+                else:
+                    self._reduce_scatter_fused(u, full, 1.0 / dp_total)
                 return
             out = torch.empty(u.shard_size, dtype=full.dtype, device=self.device)
             if self.is_cuda:
@@ -786,6 +849,10 @@ class FSDPEngine:
         for u in self.all_units:
             if u.grad_shard_fresh and u.main_grad is None and u.grad_shard is not None:
                 u.grad_shard.zero_()
+                slot = getattr(self, "_rs_partial_slot", {}).get(u.name)
+                if slot is not None:
+                    c = self._rs_partial_stride
+                    self._rs_partials[slot * c:(slot + 1) * c].zero_()
             u.grad_shard_fresh = False if u.main_grad is None else u.grad_shard_fresh
             if u.grad_post_scale != 1.0 and not u.grad_scaled:
                 u.grad_shard.mul_(u.grad_post_scale)
@@ -826,8 +893,19 @@ class FSDPEngine:
         the sharding and tensor-parallel groups; over the pipeline group too when asked)."""
         self.finish_backward()
         first = True
+        fused = getattr(self, "_rs_partial_slot", {})
+        if fused:
+            # the reduce-scatter kernels left per-CTA sums of squares of every shard they wrote: one launch adds them
+            from ..ops import _lib
+
+            _lib.check(_lib.cuda_lib().lme_sum_partials(self._rs_partials.data_ptr(),
+                                                        len(fused) * self._rs_partial_stride,
+                                                        self.sumsq.data_ptr(), 0, _lib.stream_ptr()),
+                       "lme_sum_partials")
+            _lib.count_launch()
+            first = False
         for u in self.all_units:
-            if not u.is_expert:
+            if not u.is_expert and u.name not in fused:
                 ops.sumsq_(u.grad_shard, self.sumsq, accumulate=not first)
                 first = False
         experts = [u for u in self.all_units if u.is_expert]
@@ -872,8 +950,8 @@ class FSDPEngine:
     @torch.no_grad()
     def gather_full(self, u: ShardedUnit, which: str = "master") -> torch.Tensor:
         """Full fp32 flat tensor of ``master`` / ``exp_avg`` / ``exp_avg_sq`` / ``grad`` on every rank."""
-        t = {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq,
-             "grad": u.grad_shard}[which]
+        t = which if isinstance(which, torch.Tensor) else {
+            "master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq, "grad": u.grad_shard}[which]
         if not u.shard_state:
             return t.float().clone()
         out = torch.empty(u.numel, dtype=t.dtype, device=self.device)
@@ -921,6 +999,16 @@ class FSDPEngine:
                     u.flat_param.copy_(full)
         if which == "master":
             self._cross_rank_fence()
+
+    @torch.no_grad()
+    def local_piece_from_slots(self, u: ShardedUnit, sd: dict[str, torch.Tensor], local: torch.Tensor) -> torch.Tensor:
+        """This rank's state slice of unit ``u`` after replacing the slots named in ``sd`` (full tensors) inside
+        the unit-wide tensor whose local slice is ``local`` (used for optimizer state that is not the engine's own)."""
+        full = self.gather_full(u, local)
+        for s in u.slots:
+            if s.name in sd:
+                full[s.offset:s.offset + s.numel].copy_(self._slot_local(s, sd[s.name]).reshape(-1).to(full.device))
+        return full[u.state_lo:u.state_hi].clone()
 
     def num_parameters(self) -> int:
         return sum(s.numel for u in self.all_units for s in u.slots)

@@ -27,7 +27,8 @@ from .kernels import enable_kernels
 from .logging_utils import ExperimentsTracker, MetricsTrackingDict, StepProfiler, log_environment, log_rank_0
 from .logging_utils.profiler import DeviceTimer
 from .parallel.manager import ProcessGroupManager
-from .train_utils import all_reduce_metrics_tracker, get_model_tflops, mfu, track_metrics
+from .train_utils import (all_reduce_metrics_tracker, check_device_status, get_model_tflops, mfu,
+                          track_metrics)
 from .utils import disable_generation_cache, setup_tf32
 
 
@@ -158,14 +159,23 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
     # ends a rank that made no progress so that the launcher can restart from the last checkpoint)
     from .utils.watchdog import Heartbeat
 
+    from .utils.watchdog import abort_is_safe
+
+    want_abort = os.environ.get("LME_STALL_ABORT", "0") == "1"
+    if want_abort and not abort_is_safe():
+        log_rank_0(logging.WARNING, "LME_STALL_ABORT=1 ignored: ending a rank whose memory is bound to an NVLink "
+                   "multicast object faults its peers; set NCCL_NVLS_ENABLE=0 (and no LME_REDUCE_SCATTER=nvls), "
+                   "or stop the job through the KILLSWITCH file")
+        want_abort = False
     heartbeat = Heartbeat(os.environ.get("LME_HEARTBEAT_DIR", os.path.join(args.save_args.save_path, "heartbeats")),
                           ProcessGroupManager.get_global_rank(), ProcessGroupManager.get_world_size(),
                           stall_seconds=float(os.environ.get("LME_STALL_SECONDS", "1800")), poll_seconds=30.0,
-                          abort=os.environ.get("LME_STALL_ABORT", "0") == "1").start()
+                          abort=want_abort).start()
+    device_status = None
     with StepProfiler(args.logging_args.torch_profiler_trace_path) as prof:
         while step < tp.num_training_steps:
             step += 1
-            heartbeat.beat(step)
+            heartbeat.beat(step, device_status)
             if pipeline_schedule is not None:
                 m = train_step_with_pipeline_parallel(model_container, pipeline_schedule, optimizer_container,
                                                       lr_scheduler_container, train_dataloader, ga,
@@ -176,6 +186,9 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
                     tp.gradient_clipping,
                     sync_every_gradient_accumulation_step=d.sync_every_gradient_accumulation_step,
                     tuning_method=args.tuning_args.tuning_method)
+            # the metric reduction above read values back, so the device is idle: one look at the status block tells
+            # whether any bounded wait of the step (peer flags of the fused collectives, mbarriers) ran out
+            device_status = check_device_status(step)
             window = window + m
             consumed += tp.global_batch_size
             prof.step()
@@ -211,6 +224,14 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
                 timer.start()
     heartbeat.stop()
     ensure_last_checkpoint_is_saved()
+
+
+def resumed_consumed_samples(args, metadata: dict | None) -> int:
+    """Samples that the pretraining loaders skip on a resume: the checkpoint's count, or 0 when the checkpoint's
+    data position is not wanted (``load_args.load_dataloader_state: false``; lm_engine/train.py:702-707)."""
+    if metadata is None or args.load_args is None or not args.load_args.load_dataloader_state:
+        return 0
+    return int(metadata.get("consumed_samples", 0))
 
 
 def main(args_class: type[TrainingArgs | DistillationArgs] = TrainingArgs) -> None:
@@ -250,13 +271,19 @@ def main(args_class: type[TrainingArgs | DistillationArgs] = TrainingArgs) -> No
         args.training_parameters.num_training_steps, ls.lr_decay_style, ls.lr_decay_factor,
         ls.extra_lr_scheduler_args)
     starting_iteration, metadata, tracker_state = 0, None, None
+    finetuning = args.tuning_args.tuning_method == TuningMethod.full_finetuning
+    train_dl = None
+    if finetuning:
+        # built before the checkpoint is read, so that the saved sampler position is restored into it (the
+        # reference does the same, lm_engine/train.py:719-728); the pretraining loaders are built afterwards from
+        # the number of consumed samples instead
+        train_dl = get_finetuning_dataloader(args, model_container[0].tokenizer, split="train")
     if args.load_args is not None:
         starting_iteration, metadata, tracker_state = load_checkpoint_for_training(
-            args, args_class, model_container, optimizer_container, lr_scheduler_container, None)
-    consumed = 0 if metadata is None else metadata.get("consumed_samples", 0)
+            args, args_class, model_container, optimizer_container, lr_scheduler_container, train_dl)
+    consumed = resumed_consumed_samples(args, metadata)
     val_names: list[str] = []
-    if args.tuning_args.tuning_method == TuningMethod.full_finetuning:
-        train_dl = get_finetuning_dataloader(args, model_container[0].tokenizer, split="train")
+    if finetuning:
         val_dls = [get_finetuning_dataloader(args, model_container[0].tokenizer, split="val")] \
             if args.training_parameters.eval_during_training else []
         test_dls = []

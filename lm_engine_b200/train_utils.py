@@ -38,6 +38,33 @@ def all_reduce_metrics_tracker(metrics: MetricsTrackingDict) -> MetricsTrackingD
     return MetricsTrackingDict({k: v for k, v in zip(keys, out)})
 
 
+class DeviceWaitExpired(RuntimeError):
+    """A bounded device-side wait of the kernel library ran out: data that a kernel expected never arrived."""
+
+
+def read_device_status() -> list[int] | None:
+    """The kernel library's status block (``None`` without a GPU).  Word 0 != 0: a wait on a peer's flag or on an
+    mbarrier expired and the kernel went on without the data it waited for."""
+    if not torch.cuda.is_available():
+        return None
+    from .ops import _lib
+
+    return _lib.read_status(clear=False)
+
+
+def check_device_status(step: int, status: list[int] | None = None) -> list[int] | None:
+    """Called once per optimizer step, right after the metrics were read back (the device is idle then).  Raises when
+    a device-side wait expired during the step: its results were computed from rows that never arrived, so the job
+    must not go on training on them (the launcher restarts from the last checkpoint)."""
+    status = read_device_status() if status is None else status
+    if status is not None and status[0] != 0:
+        raise DeviceWaitExpired(
+            f"step {step}: device status {status[:4]} (code {status[0]}: 1 = mbarrier wait, 2 = peer flag wait, "
+            f"3 = bounds; detail {status[1]}, block {status[2]}, count {status[3]}): a bounded wait expired, the "
+            f"step's results are not valid")
+    return status
+
+
 _METRICS_FILE: str | None = None
 
 

@@ -31,6 +31,14 @@ def _path(directory: str, rank: int) -> str:
     return os.path.join(directory, f"heartbeat-{rank}.json")
 
 
+def abort_is_safe(environ=None) -> bool:
+    """Ending a rank from the watchdog thread (``os._exit``) is only allowed when no memory of that rank can be bound
+    to an NVLink multicast object: NCCL's in-switch reductions off and the gradient reduce-scatter on plain peer
+    loads.  Otherwise the rank has to leave between steps (KILLSWITCH, process-group timeout)."""
+    env = os.environ if environ is None else environ
+    return env.get("NCCL_NVLS_ENABLE", "") == "0" and env.get("LME_REDUCE_SCATTER", "fused") != "nvls"
+
+
 class Heartbeat:
     def __init__(self, directory: str, rank: int, world_size: int, stall_seconds: float = 600.0,
                  poll_seconds: float = 10.0, abort: bool = False, on_stall=None) -> None:

@@ -32,17 +32,19 @@ def _args(save_path, load_path=None, stage=3):
     return TrainingArgs(**d)
 
 
-def _build(args):
+def _build(args, optimizer="TorchAdamW", optimizer_args=None, init_groups=True):
     from lm_engine_b200.distributed import wrap_model_container_for_distributed_training
     from lm_engine_b200.model_wrapper import get_model_container
     from lm_engine_b200.optimization import get_optimizer_container, get_scheduler_container
     from lm_engine_b200.parallel.manager import ProcessGroupManager
 
-    ProcessGroupManager(zero_stage=args.distributed_args.stage)
+    if init_groups:
+        ProcessGroupManager(zero_stage=args.distributed_args.stage)
     args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
     models = get_model_container(args)
     models, _ = wrap_model_container_for_distributed_training(args, models)
-    opts = get_optimizer_container("TorchAdamW", args.optimizer_args.class_args, models, None, max_grad_norm=1.0)
+    opts = get_optimizer_container(optimizer, optimizer_args or args.optimizer_args.class_args, models, None,
+                                   max_grad_norm=1.0)
     ls = args.lr_scheduler_args
     scheds = get_scheduler_container(models, opts, ls.num_warmup_steps, 0, None, 20, ls.lr_decay_style,
                                      ls.lr_decay_factor, {})
@@ -146,3 +148,42 @@ def test_two_rank_checkpoint_reshards_to_one(tmp_path):
     for k, v in outs[0].items():
         assert np.array_equal(got[k].numpy(), v), k
     assert models[0].engine.step_count == 2
+
+
+def _resume_with_torch_optimizer(rank, world, path, optimizer, optimizer_args):
+    """3 steps, save, 3 more steps; then fresh objects, load, the same 3 steps: identical losses and norms."""
+    from lm_engine_b200.arguments import TrainingArgs
+    from lm_engine_b200.checkpointing import load_checkpoint_for_training, save_checkpoint
+
+    args = _args(path)
+    models, opts, scheds = _build(args, optimizer, optimizer_args)
+    assert not opts[0].fused
+    data = _data(6, rank, world)
+    _steps(models, opts, scheds, data[:3])
+    save_checkpoint(args, models, opts, scheds, None, None, 3, {})
+    cont = _steps(models, opts, scheds, data[3:])
+    args2 = _args(path, load_path=path)
+    args2.random_args.seed = 999
+    models2, opts2, scheds2 = _build(args2, optimizer, optimizer_args, init_groups=False)
+    load_checkpoint_for_training(args2, TrainingArgs, models2, opts2, scheds2, None)
+    resumed = _steps(models2, opts2, scheds2, data[3:])
+    return cont, resumed
+
+
+def test_resume_keeps_momentum_of_sgd_on_two_ranks(tmp_path):
+    """The optimizers other than the fused AdamW keep their state inside a wrapped torch optimizer; a checkpoint
+    must carry it (SGD's momentum buffer here), otherwise the first steps after a resume differ."""
+    outs = run_distributed(_resume_with_torch_optimizer, 2, str(tmp_path / "ckpt"), "TorchSGD",
+                           {"lr": 1e-2, "momentum": 0.9, "weight_decay": 0.0})
+    for cont, resumed in outs:
+        assert resumed == cont, (resumed, cont)
+
+
+def test_resume_keeps_amsgrad_state(tmp_path):
+    cont, resumed = _resume_with_torch_optimizer(0, 1, str(tmp_path / "ckpt"), "TorchAdamW",
+                                                 {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95],
+                                                  "eps": 1e-10, "amsgrad": True})
+    assert resumed == cont, (resumed, cont)
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    ProcessGroupManager.destroy_process_groups()

@@ -152,3 +152,51 @@ def test_collate_left_pads_and_masks():
     pf = collate_fn([dict(b) for b in batch], True, LossMask.output_only, 0, True)
     assert pf["cu_seqlens"].tolist() == [0, 4, 6] and pf["max_seqlen"] == 4
     assert pf["labels"].tolist() == [-100, -100, 7, 8, -100, 2]
+
+
+def test_finetuning_dataloader_resumes_inside_an_epoch(tmp_path):
+    """Save in the middle of an epoch, build a fresh dataloader, restore: the next batches are the ones the first
+    loader goes on to produce (also across the epoch boundary, where a new permutation is drawn)."""
+    import torch
+
+    from lm_engine_b200.arguments import TrainingArgs
+    from lm_engine_b200.data import get_finetuning_dataloader
+    from lm_engine_b200.models import dense_config
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+    from lm_engine_b200.train import resumed_consumed_samples
+
+    ProcessGroupManager.destroy_process_groups()
+    ProcessGroupManager()
+    cfg = dense_config(vocab_size=512, hidden_size=64, num_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                       intermediate_size=128, max_position_embeddings=32).to_dict()
+    args = TrainingArgs(
+        model_args={"pretrained_config": cfg}, tuning_args={"tuning_method": "full_finetuning"},
+        optimizer_args={"class_args": {"lr": 1e-3}}, lr_scheduler_args={"lr_decay_style": "cosine"},
+        datasets=[{"class_name": "DebugDataset", "data_name": "debug", "max_input_tokens": 4, "max_output_tokens": 4,
+                   "class_args": {"num_examples": 37, "static_examples": False, "token_id": 5}}],
+        save_args={"save_path": str(tmp_path), "save_interval": 100},
+        training_parameters={"num_training_steps": 20, "micro_batch_size": 4, "gradient_accumulation_steps": 1,
+                             "eval_during_training": False},
+        load_args={"load_path": str(tmp_path)})
+
+    class _Tok:
+        eos_token_id = 1
+        pad_token_id = 2
+
+    def first_tokens(batch):
+        return batch["input_ids"][:, 0].tolist()
+
+    a = get_finetuning_dataloader(args, _Tok(), split="train")
+    seen = [first_tokens(next(a)) for _ in range(5)]
+    torch.save(a.state_dict(), tmp_path / "dl.pt")
+    cont = [first_tokens(next(a)) for _ in range(12)]           # runs over the end of the epoch (37 examples / 4)
+    b = get_finetuning_dataloader(args, _Tok(), split="train")
+    b.load_state_dict(torch.load(tmp_path / "dl.pt", weights_only=False))
+    resumed = [first_tokens(next(b)) for _ in range(12)]
+    assert resumed == cont
+    assert len({x for row in seen + cont[:4] for x in row}) == 36      # 9 batches of one epoch: no repeats
+    # load_dataloader_state: false drops the checkpoint's data position for the pretraining loaders too
+    assert resumed_consumed_samples(args, {"consumed_samples": 96}) == 96
+    args.load_args.load_dataloader_state = False
+    assert resumed_consumed_samples(args, {"consumed_samples": 96}) == 0
+    ProcessGroupManager.destroy_process_groups()

@@ -1,5 +1,6 @@
-"""ZeRO-3 on 2 GPUs (copy-engine parameter all-gather over symmetric memory, NCCL reduce-scatter, and the opt-in
-copy-engine reduce-scatter) against the same global batch on 1 GPU: per-step mean loss and global gradient norm."""
+"""ZeRO-3 on 2 GPUs (copy-engine parameter all-gather over symmetric memory; gradient reduce-scatter by the fused
+peer-load kernel, its in-switch variant, copy engines, or NCCL) against the same global batch on 1 GPU: per-step mean
+loss and global gradient norm."""
 
 import os
 import socket
@@ -87,7 +88,9 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_d
             norms.append(float(opt.step()))
             losses.append(float(out["loss"]))
         torch.cuda.synchronize()
-        info = {"ce_gather": eng.copy_engine_gather, "ce_reduce": eng.copy_engine_reduce}
+        info = {"ce_gather": eng.copy_engine_gather, "ce_reduce": eng.copy_engine_reduce,
+                "reduce_mode": eng.reduce_mode,
+                "multicast": any(getattr(eng, "_symm_grad_mc", {}).values())}
         q.put((rank, "ok", (losses, norms, _lib.read_status(), info)))
         if world > 1:
             dist.barrier()
@@ -125,13 +128,16 @@ def _run(world, reduce_mode, total_mbs=4, steps=4, ep=1, weights_dir=None, cp=1)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("reduce_mode", ["nccl", "ce"])
+@pytest.mark.parametrize("reduce_mode", ["fused", "nvls", "nccl", "ce"])
 def test_zero3_two_gpus_match_one_gpu(reduce_mode):
     (ref_losses, ref_norms, ref_status, _), = _run(1, "nccl")
     outs = _run(2, reduce_mode)
     for losses, norms, status, info in outs:
         assert status[0] == 0, status
         assert info["ce_gather"] and info["ce_reduce"] == (reduce_mode == "ce")
+        assert info["reduce_mode"] == reduce_mode
+        if reduce_mode == "nvls" and not info["multicast"]:
+            pytest.skip("no multicast mapping on this machine: the kernel ran on plain peer loads")
     mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
     for a, b in zip(mean, ref_losses):
         assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)

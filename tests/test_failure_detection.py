@@ -103,3 +103,70 @@ def test_damaged_checkpoints_fail_loudly(tmp_path, monkeypatch):
     with pytest.raises(BaseException):   # torch's CheckpointException derives from BaseException
         main(TrainingArgs)
     ProcessGroupManager.destroy_process_groups()
+
+
+def test_expired_device_wait_stops_training():
+    """The training loop looks at the kernel library's status block once per step; a non-zero first word (a bounded
+    wait ran out: the step used rows that never arrived) must raise instead of training on."""
+    from lm_engine_b200.train_utils import DeviceWaitExpired, check_device_status
+
+    assert check_device_status(3, [0, 0, 0, 0, 0, 0, 0, 0]) == [0, 0, 0, 0, 0, 0, 0, 0]
+    with pytest.raises(DeviceWaitExpired) as e:
+        check_device_status(7, [2, 861, 0, 5, 0, 0, 0, 0])      # peer flag wait of source rank 1
+    assert "step 7" in str(e.value) and "861" in str(e.value)
+
+
+def test_train_loop_reads_status_every_step(monkeypatch, tmp_path):
+    """With a faked status reader that reports an expired wait on the second step, `train` stops on that step and
+    the heartbeat file of the first step carries the status words."""
+    import json
+
+    import lm_engine_b200.train as train_mod
+    from lm_engine_b200.train_utils import DeviceWaitExpired
+
+    calls = {"n": 0}
+
+    def fake_check(step, status=None):
+        calls["n"] += 1
+        st = [0] * 8 if calls["n"] < 2 else [2, 861, 0, 1, 0, 0, 0, 0]
+        if st[0]:
+            raise DeviceWaitExpired(f"step {step}")
+        return st
+
+    monkeypatch.setattr(train_mod, "check_device_status", fake_check)
+    monkeypatch.setattr(train_mod, "train_step_without_pipeline_parallel",
+                        lambda *a, **k: train_mod.MetricsTrackingDict({"loss": 1.0}))
+
+    class _NS:
+        def __init__(self, **kw):
+            self.__dict__.update(kw)
+
+    args = _NS(training_parameters=_NS(gradient_accumulation_steps=1, micro_batch_size=1, global_batch_size=1,
+                                       num_training_steps=5, gradient_clipping=1.0, eval_during_training=False,
+                                       eval_interval=None),
+               distributed_args=_NS(gradient_checkpointing_method=None, gradient_checkpointing_args={},
+                                    sync_every_gradient_accumulation_step=False),
+               datasets=[_NS(class_args={})], logging_args=_NS(log_interval=100, cost_per_accelerator_per_hour=None,
+                                                             torch_profiler_trace_path=None),
+               save_args=_NS(save_path=str(tmp_path / "ckpt"), save_interval=10**9),
+               tuning_args=_NS(tuning_method=None))
+
+    class _Models(list):
+        def train(self):
+            return self
+
+    monkeypatch.setenv("LME_HEARTBEAT_DIR", str(tmp_path / "hb"))
+    with pytest.raises(DeviceWaitExpired):
+        train_mod.train(args, _Models([_NS(config=None)]), None, None, None, None, None, None, None)
+    assert calls["n"] == 2
+    rec = json.load(open(tmp_path / "hb" / "heartbeat-0.json"))
+    assert rec["step"] == 2 and rec["device_status"] == [0] * 8
+
+
+def test_watchdog_abort_requires_nvls_off():
+    from lm_engine_b200.utils.watchdog import abort_is_safe
+
+    assert not abort_is_safe({})                                             # NCCL decides by itself: may bind NVLS
+    assert not abort_is_safe({"NCCL_NVLS_ENABLE": "1"})
+    assert abort_is_safe({"NCCL_NVLS_ENABLE": "0"})
+    assert not abort_is_safe({"NCCL_NVLS_ENABLE": "0", "LME_REDUCE_SCATTER": "nvls"})

@@ -15,7 +15,8 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-STATIC_SCRATCH_FLOATS = 592 * 4096
+MAX_PARTIAL_ROWS = 444                      # LME_RMSNORM_BWD_MAX_PARTIAL_ROWS
+STATIC_SCRATCH_FLOATS = MAX_PARTIAL_ROWS * 4096
 ERR_TOO_LARGE = -6
 
 
@@ -71,15 +72,18 @@ def _run_pair(T, H, seed):
 
 
 def test_two_calls_in_a_row_match_the_regular_entry_point():
-    _run_pair(T=1000, H=4096, seed=1)   # fills the whole built-in workspace (592 rows x 4096)
+    _run_pair(T=1000, H=4096, seed=1)   # 444 partial rows x 4096: uses the built-in workspace to the last float
     _run_pair(T=37, H=1024, seed=2)     # smaller problem right after: stale workspace contents must not leak
 
 
-def test_rejects_problems_beyond_the_builtin_workspace():
-    _, static_fn = _symbols()
-    T, H = 4096, 8192                   # needs 592 * 8192 floats
-    assert 592 * H > STATIC_SCRATCH_FLOATS
+def test_accepts_up_to_the_capacity_and_rejects_beyond_it():
+    lib, static_fn = _symbols()
+    assert lib.lme_rmsnorm_bwd_partial_rows(10**6) == MAX_PARTIAL_ROWS
+    _run_pair(T=222, H=8192, seed=3)    # a wider row with fewer rows: 222 * 8192 == 444 * 4096, still accepted
     z = torch.zeros(8, device="cuda")
-    rc = static_fn(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), z.data_ptr(), 0, T, H,
-                   torch.cuda.current_stream().cuda_stream)
-    assert rc == ERR_TOO_LARGE          # refused before anything is launched
+    stream = torch.cuda.current_stream().cuda_stream
+    for T, H in ((444, 4104), (4096, 8192), (223, 8192)):      # one vector, twice, one row beyond the capacity
+        assert lib.lme_rmsnorm_bwd_partial_rows(T) * H > STATIC_SCRATCH_FLOATS
+        rc = static_fn(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), z.data_ptr(), 0,
+                       T, H, stream)
+        assert rc == ERR_TOO_LARGE      # refused before anything is launched
