@@ -281,6 +281,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, 100 + s)) { ok = false; break; }
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
+                    if (p.flags & LME_GEMM_PROBE_NO_LOAD) {   // timing probe: the stage is declared full as it is
+                        mbar_arrive(&full_bar[s]);
+                        continue;
+                    }
                     mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
                     const int k0 = k_base + kb * BKE;
                     if (A_MN) {
@@ -336,6 +340,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
                     const uint32_t sb = sa + L::A_BYTES;
+                    if (p.flags & LME_GEMM_PROBE_NO_MMA) {    // timing probe: the stage is released unread
+                        mbar_arrive(&empty_bar[s]);
+                        continue;
+                    }
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // K-major: step 16 elements (32 bytes) inside the swizzled 128-byte row.

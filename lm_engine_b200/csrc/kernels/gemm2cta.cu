@@ -145,6 +145,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, 1100 + s)) { ok = false; break; }
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
+                    if (p.flags & LME_GEMM_PROBE_NO_LOAD) {   // timing probe: the stage is declared full as it is
+                        if (leader) mbar_arrive(&full_bar[s]);
+                        continue;
+                    }
                     if (leader) mbar_expect_tx(&full_bar[s], 2 * L::STAGE_BYTES);
                     const uint32_t bar = map_to_cta(&full_bar[s], 0);
                     const int k0 = kb * BK;
@@ -185,6 +189,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
                     const uint32_t sb = sa + L::A_BYTES;
+                    if (p.flags & LME_GEMM_PROBE_NO_MMA) {    // timing probe: the stage is released unread
+                        mbar_arrive(&empty_bar[s]);
+                        mbar_arrive_remote(map_to_cta(&empty_bar[s], 1));
+                        continue;
+                    }
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         const uint64_t da = A_MN ? make_smem_desc_sw128(sa + kk * (UMMA_K * 128), BK * 128, 1024)

@@ -17,6 +17,10 @@ extern "C" {
 #define LME_GEMM_OUT_F32 1
 #define LME_GEMM_ACCUMULATE 2
 #define LME_GEMM_SWIGLU 4
+// timing probes for the micro-benchmarks (results are meaningless): the TMA producer declares every stage full
+// without loading it / the MMA issuer releases every stage without multiplying it
+#define LME_GEMM_PROBE_NO_LOAD 64
+#define LME_GEMM_PROBE_NO_MMA 128
 
 // C[M,N] (+)= A x B^T (+ bias) (+ residual); operands K-major ([rows, K]) or MN-major ([K, rows]).
 // ld* are row pitches in elements.  With LME_GEMM_SWIGLU, C is [M, N/2] and `preact` (optional) gets [M, N].

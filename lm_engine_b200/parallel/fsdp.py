@@ -328,7 +328,7 @@ class FSDPEngine:
         # NVLink, averages, writes the shard and the partial squared norm; "nvls" = the same kernel reading through
         # the switch (multimem.ld_reduce); "ce" = copy-engine pulls + a local sum; "nccl" = the library collective.
         self.reduce_mode = "nccl"
-        self.fused_reduce_ctas = 0
+        self.fused_reduce_ctas = self.fused_reduce_tail_ctas = 0
         if self.is_cuda and 1 < self.world <= 8 and self.stage >= 1:
             import os
 
@@ -338,6 +338,7 @@ class FSDPEngine:
                 if self.copy_engine_reduce:
                     self.reduce_mode = mode
                     self.fused_reduce_ctas = int(os.environ.get("LME_RS_CTAS", "48"))
+                    self.fused_reduce_tail_ctas = int(os.environ.get("LME_RS_TAIL_CTAS", "296"))
                     self.copy_engine_reduce = mode == "ce"
 
     # ------------------------------------------------------------------ initialisation
@@ -597,16 +598,21 @@ class FSDPEngine:
             mc = self._symm_grad_mc.get(full.data_ptr(), 0)
             args = self._rs_args[key] = (srcs, (mc + rank * S * esz) if mc else None)
         srcs, mc_src = args
-        ctas = self.fused_reduce_ctas
+        # The reduction of the unit whose backward runs last (the first unit of the model) has nothing left to hide
+        # behind: it gets enough CTAs to run at link rate.  The others share the SMs with the backward GEMMs and
+        # have a whole unit's backward of time, so they stay small.
+        tail = u is self.units[0]
+        ctas = self.fused_reduce_tail_ctas if tail else self.fused_reduce_ctas
+        stride = max(self.fused_reduce_tail_ctas, self.fused_reduce_ctas)
         if self._rs_partials is None:
-            self._rs_partial_stride = ctas
-            self._rs_partials = torch.zeros(len(self.all_units) * ctas, dtype=torch.float32, device=self.device)
+            self._rs_partial_stride = stride
+            self._rs_partials = torch.zeros(len(self.all_units) * stride, dtype=torch.float32, device=self.device)
         slot = self._rs_partial_slot.setdefault(u.name, len(self._rs_partial_slot))
         self._rs_seq += 1
         _lib.check(_lib.cuda_lib().lme_reduce_scatter_peers(
             srcs, self._rs_pad_arr, mc_src, rank, world, self._rs_seq, u.grad_shard.data_ptr(), S,
             int(full.dtype == torch.bfloat16), scale, int(not u.grad_shard_fresh),
-            self._rs_partials.data_ptr() + slot * ctas * 4, ctas, _lib.stream_ptr()), "lme_reduce_scatter_peers")
+            self._rs_partials.data_ptr() + slot * stride * 4, ctas, _lib.stream_ptr()), "lme_reduce_scatter_peers")
         _lib.count_launch()
         u.grad_shard_fresh = False
 
@@ -619,8 +625,16 @@ class FSDPEngine:
     # ------------------------------------------------------------------ buffer pools
     def _take(self, pool: dict[int, list[torch.Tensor]], kind: str, u: ShardedUnit, dtype) -> torch.Tensor:
         bufs = pool.setdefault(u.numel, [])
-        if len(bufs) < 2:
-            if kind == "g" and self._ce_reduce_applies(u):
+        symmetric = kind == "g" and self._ce_reduce_applies(u)
+        # A gradient buffer that the peers read is free again only once the reduction AFTER its own has finished
+        # here (see _reduce_grads).  With two buffers the backward pass of unit i - 2 would then wait for the
+        # reduction of unit i - 1, which has only just been issued: nothing would overlap.  A third buffer moves
+        # that wait one unit back.
+        depth = 2
+        if symmetric:   # units of a size that occurs once or twice per step never meet that wait: one buffer each
+            depth = min(3, sum(1 for x in self.all_units if x.numel == u.numel and self._ce_reduce_applies(x)))
+        if len(bufs) < depth:
+            if symmetric:
                 bufs.append(self._symmetric_grad_buffer(u.numel, dtype))
             else:
                 bufs.append(torch.empty(u.numel, dtype=dtype, device=self.device))
@@ -628,7 +642,7 @@ class FSDPEngine:
         key = (kind, u.numel)
         i = self._pool_cursor.get(key, 0)
         self._pool_cursor[key] = i + 1
-        return bufs[i % 2]
+        return bufs[i % depth]
 
     # ------------------------------------------------------------------ gather / reduce
     def _all_gather(self, u: ShardedUnit, for_graph: bool = False) -> None:
@@ -686,14 +700,27 @@ class FSDPEngine:
     def _family(u: ShardedUnit | None) -> tuple[ShardedUnit, ...]:
         return () if u is None else (u, *u.children)
 
+    # a unit below this many elements (a lone norm) runs for a few microseconds: the gather of the unit behind it
+    # would not be hidden, so prefetching looks one unit further
+    _TINY_UNIT = 1 << 20
+
+    def _prefetch(self, u: ShardedUnit, step: int, for_graph: bool) -> None:
+        """Starts the gathers of the unit(s) that run after ``u`` (``step`` +1: forward order, -1: backward)."""
+        nxt = self._neighbour(u, step)
+        for x in self._family(nxt):
+            if x.shard_params:
+                self._all_gather(x, for_graph)
+        if nxt is not None and nxt.numel < self._TINY_UNIT:
+            for x in self._family(self._neighbour(nxt, step)):
+                if x.shard_params:
+                    self._all_gather(x, for_graph)
+
     def pre_forward(self, u: ShardedUnit, training: bool) -> None:
         for x in self._family(u):
             if training:
                 x.pending_backward += 1
             self._wait_gather(x, for_graph=training)
-        for x in self._family(self._neighbour(u, +1)):
-            if x.shard_params:
-                self._all_gather(x, for_graph=training)
+        self._prefetch(u, +1, for_graph=training)
 
     def post_forward(self, u: ShardedUnit, training: bool) -> None:
         # the last unit's backward starts right after its forward: keep it gathered
@@ -705,9 +732,7 @@ class FSDPEngine:
     def pre_backward(self, u: ShardedUnit) -> None:
         for x in self._family(u):
             self._wait_gather(x)
-        for x in self._family(self._neighbour(u, -1)):
-            if x.shard_params:
-                self._all_gather(x)
+        self._prefetch(u, -1, for_graph=False)
         for x in self._family(u):
             self._bind_grad_buffer(x)
 
@@ -885,7 +910,20 @@ class FSDPEngine:
             if self.stage in (1, 2) and u.world > 1:
                 dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
         self._cross_rank_fence()
+        self.prefetch_first_units()
         return self.grad_norm
+
+    def prefetch_first_units(self) -> None:
+        """Starts the parameter gathers of the first units of the next forward pass right behind the optimizer step
+        (every rank's update is complete after the fence), so that they run under the step's host-side tail
+        (metric reduction, read-back, next batch) instead of in front of the first kernel of the next step."""
+        if self.stage != 3 or not self.is_cuda or self.world == 1 or self.pipeline_mode or not self.units:
+            return
+        first = self.units[0]
+        for x in self._family(first):
+            if x.shard_params:
+                self._all_gather(x, for_graph=True)
+        self._prefetch(first, +1, for_graph=True)
 
     @torch.no_grad()
     def local_sumsq(self, include_pipeline_group: bool = False) -> torch.Tensor:
@@ -998,6 +1036,11 @@ class FSDPEngine:
                 else:
                     u.flat_param.copy_(full)
         if which == "master":
+            # gathers started before the load hold the old weights
+            if self._inflight:
+                if self.is_cuda:
+                    torch.cuda.synchronize(self.device)
+                self._inflight.clear()
             self._cross_rank_fence()
 
     @torch.no_grad()
