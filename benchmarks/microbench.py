@@ -1,6 +1,6 @@
 """Micro-benchmarks of the hand-written kernels against their roofline.
 
-    python -m lm_engine_b200.ops.microbench [--json out.json] [--quick]
+    python -m benchmarks.microbench [--json out.json] [--quick]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, operands rotated through a pool larger than
 the 126 MB L2 so every timed launch reads cold data.  GEMM throughput is reported next to ``torch.matmul`` (cuBLAS)
@@ -15,11 +15,11 @@ import os
 
 import torch
 
-from . import _lib, gemm
+from lm_engine_b200.ops import _lib, gemm
 
 
 def _peaks() -> dict:
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     path = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
@@ -66,7 +66,7 @@ def _sustained(fn, n_pool: int, seconds: float = 1.5) -> float:
     return e1.elapsed_time(e2) * 1e-3 / half
 
 
-def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, **kw):
+def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, probe=0, **kw):
     dev = "cuda"
     bytes_per = 2 * (M * K + N * K + M * N)
     n_pool = max(2, min(8, int(300e6 // bytes_per) + 1))
@@ -74,7 +74,7 @@ def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, **kw
     Bs = [torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16) for _ in range(n_pool)]
     out = torch.empty((M, N // 2 if kw.get("swiglu") else N), device=dev, dtype=torch.bfloat16)
     timer = _sustained if sustained else _time
-    t_ours = timer(lambda i: gemm(As[i], Bs[i], a_mn=a_mn, b_mn=b_mn, out=out, impl=impl, **kw), n_pool)
+    t_ours = timer(lambda i: gemm(As[i], Bs[i], a_mn=a_mn, b_mn=b_mn, out=out, impl=impl, probe=probe, **kw), n_pool)
 
     def ref(i):
         A = As[i].t() if a_mn else As[i]
@@ -90,7 +90,7 @@ def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, **kw
 
 def bench_gemm_fp8(M, N, K, sustained=False):
     """8-bit GEMM (pre-quantised operands) and the quantiser feeding it, on one forward-shaped problem."""
-    from . import fp8
+    from lm_engine_b200.ops import fp8
 
     dev = "cuda"
     n_pool = max(2, min(8, int(300e6 // (M * K + N * K + 2 * M * N)) + 1))
@@ -109,8 +109,8 @@ def bench_gemm_fp8(M, N, K, sustained=False):
 def bench_elementwise(peaks: dict, small: bool = False) -> list[dict]:
     """Bandwidth-bound kernels at the 8B model's shapes: algorithmic bytes / device time against the measured copy
     bandwidth.  Operand sets rotate through a pool larger than L2."""
-    from . import adamw_step, cross_entropy_sum, qkv_split_rope, rmsnorm, swiglu_backward
-    from . import fp8
+    from lm_engine_b200.ops import adamw_step, cross_entropy_sum, qkv_split_rope, rmsnorm, swiglu_backward
+    from lm_engine_b200.ops import fp8
 
     dev, T, H, I = "cuda", 8192, 4096, 14336
     bf = torch.bfloat16
@@ -164,9 +164,9 @@ def bench_elementwise(peaks: dict, small: bool = False) -> list[dict]:
 def bench_recurrent(small: bool = False) -> list[dict]:
     """Scan kernels at training shapes: ms per call and ns per time step (the scans are latency chains, so time per
     step is the figure of merit), plus the PyTorch time loop on a 128-step prefix for scale."""
-    from . import m2rnn as m2op
-    from . import rnn as rnnop
-    from .recurrence import gru_scan, m2rnn_scan, rnn_scan
+    from lm_engine_b200.ops import m2rnn as m2op
+    from lm_engine_b200.ops import rnn as rnnop
+    from lm_engine_b200.ops.recurrence import gru_scan, m2rnn_scan, rnn_scan
 
     dev, bf = "cuda", torch.bfloat16
     B, S = 2, (512 if small else 4096)
@@ -214,7 +214,7 @@ def bench_recurrent(small: bool = False) -> list[dict]:
         return make
 
     # the chunk-parallel PyTorch forms (batched matmuls + triangular solve) at the published gated-delta-net layout
-    from .recurrence import gated_delta_rule, linear_attention
+    from lm_engine_b200.ops.recurrence import gated_delta_rule, linear_attention
 
     def chunked(name, fn, make_args):
         args = make_args()
@@ -252,7 +252,7 @@ def bench_attention(peaks: dict, small: bool = False) -> list[dict]:
     """Own tcgen05 attention forward against the library (cuDNN through SDPA) forward at training shapes."""
     import torch.nn.functional as F
 
-    from .attention_cuda import flash_attention_forward
+    from lm_engine_b200.ops.attention_cuda import flash_attention_forward
 
     rows = []
     for name, B, S, Hq, Hkv in ([("capture", 1, 8192, 8, 2)] if small else
@@ -301,6 +301,8 @@ def main():
     ap.add_argument("--elementwise", action="store_true", help="time the bandwidth-bound kernels instead")
     ap.add_argument("--small", action="store_true", help="smaller operand pools (profiler captures)")
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
+    ap.add_argument("--probe", default=None, choices=["noload", "nomma"],
+                    help="GEMM timing probe: skip the operand loads (tensor-pipe ceiling) or the MMAs (load ceiling)")
     args = ap.parse_args()
     peaks = _peaks()
     if args.attention:
@@ -342,7 +344,8 @@ def main():
         assert shapes, f"no shape named {args.only!r}"
     rows = []
     for name, M, N, K, a_mn, b_mn, kw in shapes:
-        r = bench_gemm(M, N, K, a_mn, b_mn, sustained=args.sustained, impl=args.impl, **kw)
+        r = bench_gemm(M, N, K, a_mn, b_mn, sustained=args.sustained, impl=args.impl,
+                       probe={"noload": 64, "nomma": 128, None: 0}[args.probe], **kw)
         r["name"] = name
         r["frac_of_peak"] = r["tflops"] / peaks["bf16_tflops_sustained" if args.sustained else "bf16_tflops"]
         rows.append(r)

@@ -1,7 +1,7 @@
 """Times the fused all-gather -> GEMM kernel against its two-step equivalent (NCCL all-gather, then the same GEMM)
 and against the GEMM alone on an already gathered operand (the floor).  One process per GPU::
 
-    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m lm_engine_b200.parallel.symm_bench
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m benchmarks.symm_bench
 
 Device time by CUDA events around ``iters`` back-to-back calls after warm-up, max over ranks; operands rotate through a
 pool larger than L2.
@@ -16,9 +16,9 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..ops import _lib
-from ..ops.gemm import gemm
-from .symm import all_gather_matmul
+from lm_engine_b200.ops import _lib
+from lm_engine_b200.ops.gemm import gemm
+from lm_engine_b200.parallel.symm import all_gather_matmul
 
 
 def _time(fn, iters: int, warmup: int = 3) -> float:
@@ -93,7 +93,7 @@ def main() -> None:
                   f" | max err vs two-step {r['max_err']:.2e}",
                   flush=True)
     # GEMM -> reduce-scatter: row-parallel projections (contraction dim split over the ranks)
-    from .symm import matmul_reduce_scatter
+    from lm_engine_b200.parallel.symm import matmul_reduce_scatter
 
     for name, K_full, N in (("attn-out", 4096, 4096), ("fc2", 14336, 4096)):
         Kl, pool = K_full // world, 4

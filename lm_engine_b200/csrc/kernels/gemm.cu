@@ -57,6 +57,10 @@ struct GemmArgs {
     const int* group_k0;
     const int* group_kb;
     long long group_c_stride;
+    // Batched form (BATCHED kernels): `batch` independent products; the operands are addressed through 3-D tensor
+    // maps whose outermost coordinate is the batch index, output b starts batch_c_stride elements further.
+    int batch;
+    long long batch_c_stride;
 };
 
 template <int BN, int STAGES>
@@ -191,7 +195,8 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&r)[32], int row,
 // GATHER: the first g.n_copy CTAs of the grid pull an operand's rows from the peers (gather.cuh) while the others
 // multiply; the TMA producer waits for the segments under each operand tile.
 // RS: the epilogue reduce-scatters the product over the ranks (RsArgs in gather.cuh).
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false, bool RS = false>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false, bool RS = false,
+          bool BATCHED = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs p, const __grid_constant__ GatherArgs g,
@@ -199,6 +204,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     static_assert(!(GATHER && RS), "one fused collective per kernel");
     static_assert(!F8 || (!A_MN && !B_MN), "8-bit operands are K-major");
     static_assert(!GATHER || !A_MN, "the gathered operand is K-major");
+    static_assert(!BATCHED || (!F8 && !GATHER && !RS), "the batched form is the plain bf16 product");
     constexpr int BKE = F8 ? 2 * BK : BK;  // K elements per pipeline stage
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
@@ -218,7 +224,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int tiles_per_group = p.tiles_m * p.tiles_n;
-    const int num_tiles = tiles_per_group * (p.num_groups_w > 0 ? p.num_groups_w : 1);
+    const int num_tiles = tiles_per_group * (BATCHED ? p.batch : (p.num_groups_w > 0 ? p.num_groups_w : 1));
     const int num_kb = (p.K + BKE - 1) / BKE;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                    : (2 * BN <= 256) ? 256 : 512;
@@ -252,7 +258,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool ok = true;
             for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
                 int mb, nb;
-                const int grp = p.num_groups_w > 0 ? tile / tiles_per_group : 0;
+                const int grp = (BATCHED || p.num_groups_w > 0) ? tile / tiles_per_group : 0;
                 tile_coords(tile - grp * tiles_per_group, p, mb, nb);
                 if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
                 if (RS) mb = (mb + rs.rotate) % p.tiles_m;
@@ -287,6 +293,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
                     const int k0 = k_base + kb * BKE;
+                    if (BATCHED) {
+                        // 3-D maps: (inner, rows, batch); rows beyond a batch's extent read zeros
+                        if (A_MN) {
+#pragma unroll
+                            for (int c = 0; c < BM / 64; ++c)
+                                tma_load_3d(sa + c * (BK * 128), &tmA, &full_bar[s], m0 + c * 64, k0, grp);
+                        } else {
+                            tma_load_3d(sa, &tmA, &full_bar[s], k0, m0, grp);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int c = 0; c < BN / 64; ++c)
+                                tma_load_3d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, k0, grp);
+                        } else {
+                            tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, grp);
+                        }
+                        continue;
+                    }
                     if (A_MN) {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c)
@@ -373,13 +397,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (F8) dequant = __ldg(p.scale_a) * __ldg(p.scale_b);
         for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
             int mb, nb;
-            const int grp = p.num_groups_w > 0 ? tile / tiles_per_group : 0;
+            const int grp = (BATCHED || p.num_groups_w > 0) ? tile / tiles_per_group : 0;
             tile_coords(tile - grp * tiles_per_group, p, mb, nb);
             if (GATHER) mb = (mb + g.rotate_tiles) % p.tiles_m;
             if (RS) mb = (mb + rs.rotate) % p.tiles_m;
             if (p.tile_group != nullptr && __ldg(&p.tile_group[mb]) < 0) continue;
             const bool empty_group = p.num_groups_w > 0 && __ldg(&p.group_kb[grp]) == 0;
-            const long long c_off = p.num_groups_w > 0 ? grp * p.group_c_stride : 0;
+            const long long c_off = BATCHED ? grp * p.batch_c_stride
+                                            : (p.num_groups_w > 0 ? grp * p.group_c_stride : 0);
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
             ++tcount;
@@ -581,6 +606,34 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
     return LME_OK;
 }
 
+// 3-D bf16 tensor map (inner, rows, batch): row pitch `ld` and batch pitch `batch_ld` in elements, box
+// [box_inner x box_rows x 1], 128-byte swizzle.
+int make_tmap_bf16_3d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t ld,
+                      uint64_t batch_ld, uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return LME_ERR_DRIVER;
+    cuuint64_t dims[3] = {inner, rows, batch};
+    cuuint64_t strides[2] = {ld * 2, batch_ld * 2};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    thread_local bool context_bound = false;
+    if (!context_bound) {
+        cudaFree(nullptr);
+        context_bound = true;
+    }
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        fprintf(stderr, "lme: cuTensorMapEncodeTiled (3-D) failed (CUresult %d): ptr=%p inner=%llu rows=%llu batch=%llu "
+                "ld=%llu batch_ld=%llu\n", static_cast<int>(r), ptr, static_cast<unsigned long long>(inner),
+                static_cast<unsigned long long>(rows), static_cast<unsigned long long>(batch),
+                static_cast<unsigned long long>(ld), static_cast<unsigned long long>(batch_ld));
+        return LME_ERR_TMAP;
+    }
+    return LME_OK;
+}
+
 static int g_num_sms = 0;
 static int num_sms() {
     if (g_num_sms == 0) {
@@ -591,13 +644,14 @@ static int num_sms() {
     return g_num_sms;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false, bool RS = false>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool F8 = false, bool GATHER = false, bool RS = false,
+          bool BATCHED = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p, int max_ctas,
                        cudaStream_t stream, const GatherArgs* gather = nullptr,
                        const CUtensorMap* tlocal = nullptr, const RsArgs* scatter = nullptr) {
     using L = SmemLayout<BN, STAGES>;
     static_assert(!GATHER || L::TILES_BYTES >= GATHER_SLOTS * GATHER_SEG_BYTES, "copy CTAs reuse the tile ring");
-    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8, GATHER, RS>;
+    auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, F8, GATHER, RS, BATCHED>;
     // RS: + 4 x 8 KB behind the barriers, where the epilogue warps turn their tiles for coalesced peer stores
     constexpr int SMEM = L::TOTAL + (RS ? 1024 + 4 * 8192 : 0);
     static_assert(SMEM <= 232448, "dynamic shared memory of one CTA");
@@ -610,7 +664,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
     p.group_m = 8;
-    int tiles = p.tiles_m * p.tiles_n;
+    int tiles = p.tiles_m * p.tiles_n * (BATCHED ? p.batch : 1);
     GatherArgs g;
     RsArgs rs;
     rs.enabled = 0;
@@ -670,6 +724,53 @@ extern "C" int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const
         if (a_mn_major) return launch_gemm<BN_, ST_, true, false>(ta, tb, p, max_ctas, st);                \
         if (b_mn_major) return launch_gemm<BN_, ST_, false, true>(ta, tb, p, max_ctas, st);                \
         return launch_gemm<BN_, ST_, false, false>(ta, tb, p, max_ctas, st);                               \
+    } while (0)
+    if (BN == 128) LME_DISPATCH(128, 6);
+    LME_DISPATCH(256, 4);
+#undef LME_DISPATCH
+}
+
+// Batched GEMM: C[b] (+)= A[b] x B[b]^T for b < batch.  Operand b of A / B starts a_batch_ld / b_batch_ld elements
+// after operand b - 1 (row pitches lda / ldb), either layout per operand as in lme_gemm_bf16; C[b] at
+// C + b * c_batch_ld.  Flags: LME_GEMM_OUT_F32, LME_GEMM_ACCUMULATE.
+extern "C" int lme_gemm_bf16_batched(const void* A, int a_mn_major, long long lda, long long a_batch_ld,
+                                     const void* B, int b_mn_major, long long ldb, long long b_batch_ld, void* C,
+                                     long long ldc, long long c_batch_ld, int batch, int M, int N, int K, int flags,
+                                     int max_ctas, void* stream) {
+    if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return LME_OK;
+    if ((N % 8) || (lda % 8) || (ldb % 8) || (a_batch_ld % 8) || (b_batch_ld % 8) || (ldc % 4) || (c_batch_ld % 4))
+        return LME_ERR_SHAPE;
+    if (flags & ~(LME_GEMM_OUT_F32 | LME_GEMM_ACCUMULATE)) return LME_ERR_SHAPE;
+    // the innermost extent of a tensor map is a multiple of 16 bytes
+    if ((a_mn_major ? M : K) % 8 || (b_mn_major ? N : K) % 8) return LME_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+        return LME_ERR_ALIGN;
+    const int BN = (N <= 128) ? 128 : 256;
+    CUtensorMap ta, tb;
+    int rc;
+    rc = a_mn_major ? make_tmap_bf16_3d(&ta, A, M, K, batch, lda, a_batch_ld, 64, BK)
+                    : make_tmap_bf16_3d(&ta, A, K, M, batch, lda, a_batch_ld, 64, BM);
+    if (rc) return rc;
+    rc = b_mn_major ? make_tmap_bf16_3d(&tb, B, N, K, batch, ldb, b_batch_ld, 64, BK)
+                    : make_tmap_bf16_3d(&tb, B, K, N, batch, ldb, b_batch_ld, 64, BN);
+    if (rc) return rc;
+    GemmArgs p = {};
+    p.M = M; p.N = N; p.K = K;
+    p.C = C; p.ldc = ldc;
+    p.flags = flags;
+    p.batch = batch;
+    p.batch_c_stride = c_batch_ld;
+    if (max_ctas <= 0) max_ctas = num_sms();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define LME_DISPATCH(BN_, ST_)                                                                              \
+    do {                                                                                                    \
+        if (a_mn_major && b_mn_major)                                                                       \
+            return launch_gemm<BN_, ST_, true, true, false, false, false, true>(ta, tb, p, max_ctas, st);   \
+        if (a_mn_major)                                                                                     \
+            return launch_gemm<BN_, ST_, true, false, false, false, false, true>(ta, tb, p, max_ctas, st);  \
+        if (b_mn_major)                                                                                     \
+            return launch_gemm<BN_, ST_, false, true, false, false, false, true>(ta, tb, p, max_ctas, st);  \
+        return launch_gemm<BN_, ST_, false, false, false, false, false, true>(ta, tb, p, max_ctas, st);     \
     } while (0)
     if (BN == 128) LME_DISPATCH(128, 6);
     LME_DISPATCH(256, 4);

@@ -304,3 +304,113 @@ extern "C" int lme_ssd_combine(const float* yin, const float* off, const float* 
 #undef LME_COMB
     return LME_LAUNCH_OK();
 }
+
+// ----------------------------------------------------------------------------------------------------------------
+// Chunk-boundary recurrence of the SSD scan:  h_0 = h_init,  h_{c+1} = decay[c] * h_c + S_c  per (batch, head), where
+// S_c [P * Sd] is the summary of chunk c and decay[c] = exp(sum of dt A over the chunk).  The forward kernel walks the
+// chunks once and writes the state at every chunk start (bf16: the operand of the carried-state product; optionally
+// fp32 for the backward pass) and the final state; the backward kernel walks them in reverse:
+//   dS_c = g,   d decay[c] = <g, h_c>,   g <- decay[c] * g + dh_c        (g starts as d h_final, ends as d h_init)
+// One CTA per (batch, head); the P * Sd state elements are spread over its threads, 4 per thread and pass.
+namespace lme {
+
+// E = P * Sd (multiple of 4).  states / h0_f32 / dh0 / dstates: [B, NC, N, E];  decay / ddecay: [B, NC, N].
+__global__ void __launch_bounds__(256)
+ssd_boundary_fwd_kernel(const float* __restrict__ states, const float* __restrict__ decay,
+                        const float* __restrict__ h_init, __nv_bfloat16* __restrict__ h0_bf16,
+                        float* __restrict__ h0_f32, float* __restrict__ h_final, int NC, int N, int E) {
+    const int b = blockIdx.x / N, n = blockIdx.x % N;
+    for (int e = threadIdx.x * 4; e < E; e += blockDim.x * 4) {
+        float4 h = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (h_init != nullptr) h = *reinterpret_cast<const float4*>(h_init + (static_cast<long long>(b) * N + n) * E + e);
+        for (int c = 0; c < NC; ++c) {
+            const long long row = (static_cast<long long>(b) * NC + c) * N + n;
+            const long long off = row * E + e;
+            uint2 o;
+            o.x = pack_bf16x2(h.x, h.y);
+            o.y = pack_bf16x2(h.z, h.w);
+            *reinterpret_cast<uint2*>(h0_bf16 + off) = o;
+            if (h0_f32 != nullptr) *reinterpret_cast<float4*>(h0_f32 + off) = h;
+            const float d = __ldg(decay + row);
+            const float4 s = *reinterpret_cast<const float4*>(states + off);
+            h.x = h.x * d + s.x; h.y = h.y * d + s.y; h.z = h.z * d + s.z; h.w = h.w * d + s.w;
+        }
+        *reinterpret_cast<float4*>(h_final + (static_cast<long long>(b) * N + n) * E + e) = h;
+    }
+}
+
+// blockDim.x * 4 >= E is not required: every thread keeps its running gradient per owned 4-vector in registers for
+// up to MAXV vectors (E <= 256 threads * 4 * MAXV).
+template <int MAXV>
+__global__ void __launch_bounds__(256)
+ssd_boundary_bwd_kernel(const float* __restrict__ dh0, const float* __restrict__ dh_final,
+                        const float* __restrict__ h0_f32, const float* __restrict__ decay,
+                        float* __restrict__ dstates, float* __restrict__ ddecay, float* __restrict__ dh_init, int NC,
+                        int N, int E) {
+    __shared__ float red[32];
+    const int b = blockIdx.x / N, n = blockIdx.x % N;
+    float4 g[MAXV];
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+        const int e = (v * blockDim.x + threadIdx.x) * 4;
+        g[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < E && dh_final != nullptr)
+            g[v] = *reinterpret_cast<const float4*>(dh_final + (static_cast<long long>(b) * N + n) * E + e);
+    }
+    for (int c = NC - 1; c >= 0; --c) {
+        const long long row = (static_cast<long long>(b) * NC + c) * N + n;
+        const float d = __ldg(decay + row);
+        float dot = 0.f;
+#pragma unroll
+        for (int v = 0; v < MAXV; ++v) {
+            const int e = (v * blockDim.x + threadIdx.x) * 4;
+            if (e < E) {
+                const long long off = row * E + e;
+                *reinterpret_cast<float4*>(dstates + off) = g[v];
+                const float4 h = *reinterpret_cast<const float4*>(h0_f32 + off);
+                dot += g[v].x * h.x + g[v].y * h.y + g[v].z * h.z + g[v].w * h.w;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (dh0 != nullptr) a = *reinterpret_cast<const float4*>(dh0 + off);
+                g[v].x = g[v].x * d + a.x; g[v].y = g[v].y * d + a.y;
+                g[v].z = g[v].z * d + a.z; g[v].w = g[v].w * d + a.w;
+            }
+        }
+        dot = block_sum(dot, red);
+        if (threadIdx.x == 0) ddecay[row] = dot;
+    }
+    if (dh_init != nullptr) {
+#pragma unroll
+        for (int v = 0; v < MAXV; ++v) {
+            const int e = (v * blockDim.x + threadIdx.x) * 4;
+            if (e < E) *reinterpret_cast<float4*>(dh_init + (static_cast<long long>(b) * N + n) * E + e) = g[v];
+        }
+    }
+}
+
+}  // namespace lme
+
+extern "C" int lme_ssd_boundary_fwd(const float* states, const float* decay, const float* h_init, void* h0_bf16,
+                                    float* h0_f32, float* h_final, int B, int NC, int N, int E, void* stream) {
+    if (B <= 0 || NC <= 0 || N <= 0 || E <= 0 || (E % 4)) return LME_ERR_SHAPE;
+    lme::ssd_boundary_fwd_kernel<<<B * N, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        states, decay, h_init, static_cast<__nv_bfloat16*>(h0_bf16), h0_f32, h_final, NC, N, E);
+    return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+}
+
+extern "C" int lme_ssd_boundary_bwd(const float* dh0, const float* dh_final, const float* h0_f32, const float* decay,
+                                    float* dstates, float* ddecay, float* dh_init, int B, int NC, int N, int E,
+                                    void* stream) {
+    if (B <= 0 || NC <= 0 || N <= 0 || E <= 0 || (E % 4) || E > 256 * 4 * 16) return LME_ERR_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int vecs = (E / 4 + 255) / 256;
+    if (vecs <= 2)
+        lme::ssd_boundary_bwd_kernel<2><<<B * N, 256, 0, st>>>(dh0, dh_final, h0_f32, decay, dstates, ddecay, dh_init,
+                                                              NC, N, E);
+    else if (vecs <= 8)
+        lme::ssd_boundary_bwd_kernel<8><<<B * N, 256, 0, st>>>(dh0, dh_final, h0_f32, decay, dstates, ddecay, dh_init,
+                                                              NC, N, E);
+    else
+        lme::ssd_boundary_bwd_kernel<16><<<B * N, 256, 0, st>>>(dh0, dh_final, h0_f32, decay, dstates, ddecay,
+                                                               dh_init, NC, N, E);
+    return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
+}

@@ -33,6 +33,12 @@ int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, const void*
                        void* C, long long ldc, int M, int N, int K, int flags, const void* bias,
                        const void* residual, long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
 
+// Batched form: C[b] (+)= A[b] x B[b]^T for b < batch; operand / output b starts *_batch_ld elements after b - 1.
+// Flags: LME_GEMM_OUT_F32, LME_GEMM_ACCUMULATE.  Rows past M / N of a batch read as zeros (3-D tensor maps).
+int lme_gemm_bf16_batched(const void* A, int a_mn_major, long long lda, long long a_batch_ld, const void* B,
+                          int b_mn_major, long long ldb, long long b_batch_ld, void* C, long long ldc,
+                          long long c_batch_ld, int batch, int M, int N, int K, int flags, int max_ctas, void* stream);
+
 // Grouped GEMM (mixture of experts).  A / C rows are in a padded per-group layout in which every 128-row tile belongs
 // to one group: tile_group[m-tile] = group (< 0: unused tile).  B holds all groups: K-major [G * N, K] (forward,
 // C = A B_e^T) or MN-major [G * K, N] (input gradient, C = A B_e).  Flags / SwiGLU epilogue as lme_gemm_bf16.
@@ -225,6 +231,14 @@ int lme_ssd_prep(const void* x, const float* dt, const float* tail, void* xh, vo
 int lme_ssd_combine(const float* yin, const float* off, const float* ecum, const float* D, const void* x, void* y,
                     const void* dy, void* dyin, void* doff, float* decum, float* dDp, void* dx, long long BC, int N,
                     int L, int G, int P, int mode, void* stream);
+// Chunk-boundary recurrence h_{c+1} = decay[c] h_c + states[c] per (batch, head), E = P * Sd elements (E % 4 == 0):
+// forward writes the state at every chunk start (bf16, and fp32 when h0_f32 != null) and the final state; backward
+// (E <= 16384) returns dstates, ddecay and (optionally) dh_init from dh0 / dh_final (either may be null).
+int lme_ssd_boundary_fwd(const float* states, const float* decay, const float* h_init, void* h0_bf16, float* h0_f32,
+                         float* h_final, int B, int NC, int N, int E, void* stream);
+int lme_ssd_boundary_bwd(const float* dh0, const float* dh_final, const float* h0_f32, const float* decay,
+                         float* dstates, float* ddecay, float* dh_init, int B, int NC, int N, int E, void* stream);
+
 
 // max |x| of n bf16 values, max-combined into *amax (which must hold 0 or an earlier running maximum).
 int lme_fp8_amax(const void* x, long long n, float* amax, void* stream);

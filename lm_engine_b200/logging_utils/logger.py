@@ -49,6 +49,18 @@ def warn_rank_0(msg: str) -> None:
     log_rank_0(logging.WARNING, msg)
 
 
+_WARNED: set[str] = set()
+
+
+def warn_once(key: str, msg: str) -> None:
+    """One warning per process and ``key`` on the first rank: used where an op leaves its hand-written kernel for
+    a library kernel or a PyTorch statement, so that such a change of speed is visible in the log."""
+    if key in _WARNED:
+        return
+    _WARNED.add(key)
+    log_rank_0(logging.WARNING, msg)
+
+
 def print_rank_0(*args, **kwargs) -> None:
     if _rank() == 0:
         print(*args, **kwargs)

@@ -73,6 +73,11 @@ class SoftmaxAttention(nn.Module):
         self.attention_gate = config.attention_gate
         self.exclusive_self_attention = config.exclusive_self_attention
         self.sliding_window = config.sliding_window
+        # The reference hands (sliding_window, sliding_window) to flash-attn as the window, i.e. a causal query
+        # attends to itself and the `sliding_window` keys before it: sliding_window + 1 keys
+        # (softmax_attention/flash_attention.py:128-130).  The ops of this repository count the attended keys, so
+        # the layer passes one more: a checkpoint trained by either engine gives the same logits in the other.
+        self._attended_keys = None if config.sliding_window is None else config.sliding_window + 1
         if config.attention_multiplier_method == INVERSE_SQRT:
             self.attention_multiplier = 1 / math.sqrt(self.head_dim)
         elif config.attention_multiplier_method == INVERSE:
@@ -150,15 +155,15 @@ class SoftmaxAttention(nn.Module):
             cp = ProcessGroupManager.get_context_parallel_world_size()
             if how == "ulysses" or (how == "auto" and ulysses_eligible(q.size(-2), k.size(-2), cp)):
                 return ulysses_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
-                                         sliding_window=self.sliding_window, dropout_p=dropout)
+                                         sliding_window=self._attended_keys, dropout_p=dropout)
             return ring_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
-                                  sliding_window=self.sliding_window)
+                                  sliding_window=self._attended_keys)
         if packed:
             return ops.attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
-                                 sliding_window=self.sliding_window, cu_seqlens=info.cu_seqlens,
+                                 sliding_window=self._attended_keys, cu_seqlens=info.cu_seqlens,
                                  max_seqlen=info.max_seqlen, dropout_p=dropout)
         return ops.attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
-                             sliding_window=self.sliding_window, attention_mask=info.attention_mask,
+                             sliding_window=self._attended_keys, attention_mask=info.attention_mask,
                              dropout_p=dropout)
 
     @staticmethod

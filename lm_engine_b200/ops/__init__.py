@@ -3,7 +3,7 @@ is both the CPU path and the numerical oracle of the tests."""
 
 from .activation import swiglu_backward, swiglu_packed, swiglu_packed_reference
 from .cross_entropy import cross_entropy_sum
-from .gemm import gemm, gemm_reference, linear, linear_swiglu
+from .gemm import bmm, bmm_reference, gemm, gemm_reference, linear, linear_swiglu
 from .norm import rmsnorm, rmsnorm_reference
 from .optimizer import adamw_reference, adamw_step, clip_coef_, sumsq_
 from .rope import apply_rope_reference, qkv_split_rope, qkv_split_rope_reference

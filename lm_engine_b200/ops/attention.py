@@ -113,6 +113,14 @@ def attention(q, k, v, *, causal=True, softmax_scale=None, sliding_window=None, 
         return attention_cuda.flash_attention(q, k, v, causal=causal, softmax_scale=scale,
                                               sliding_window=sliding_window, cu_seqlens=cu_seqlens,
                                               max_seqlen=max_seqlen)
+    if q.is_cuda:
+        from ..logging_utils.logger import warn_once
+
+        why = attention_cuda.why_unsupported(q, k, v, causal=causal, sliding_window=sliding_window,
+                                             attention_mask=attention_mask, cu_seqlens=cu_seqlens,
+                                             dropout_p=dropout_p)
+        warn_once(f"attention-fallback-{why}", f"attention: the tcgen05 kernels do not take this case ({why}); "
+                  "it runs on a library kernel or on the PyTorch statement")
     if cu_seqlens is not None and q.is_cuda and attention_mask is None and _flash_attn_varlen_usable(q):
         return _flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale, sliding_window, dropout_p)
     if (sliding_window is not None and q.is_cuda and attention_mask is None and cu_seqlens is None

@@ -44,6 +44,26 @@ def supports(q, k, v, *, causal, sliding_window, attention_mask, cu_seqlens, dro
     return enabled() and (not causal or q.size(1) == k.size(1))
 
 
+def why_unsupported(q, k, v, *, causal, sliding_window, attention_mask, cu_seqlens, dropout_p) -> str:
+    """Short reason why :func:`supports` said no (for the one-time fallback warning)."""
+    packed = cu_seqlens is not None
+    if q.size(-1) != 128 or v.size(-1) != 128:
+        return f"head dim {q.size(-1)}"
+    if q.dtype != torch.bfloat16:
+        return f"dtype {q.dtype}"
+    if attention_mask is not None:
+        return "padding mask"
+    if dropout_p != 0:
+        return "dropout"
+    if sliding_window is not None and not causal:
+        return "non-causal window"
+    if not shapes_supported(q, k, v, packed):
+        return "sequence length not a multiple of 128" if not packed else "packed layout"
+    if not enabled():
+        return "library kernels are the default, LME_ATTENTION=own selects the tcgen05 kernels"
+    return "query / key lengths differ"
+
+
 def _token_major(t: torch.Tensor) -> torch.Tensor:
     """[B, S, H, 128] with heads contiguous inside a token and batches back to back (any token pitch), else a copy."""
     B, S, H, D = t.shape

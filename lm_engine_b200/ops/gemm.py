@@ -97,7 +97,10 @@ def gemm(
     preact: torch.Tensor | None = None,
     max_ctas: int = 0,
     impl: str | None = None,
+    probe: int = 0,
 ) -> torch.Tensor:
+    """``probe``: timing-probe flags of the micro-benchmarks (64: stages are never loaded, 128: never multiplied);
+    the result is meaningless with either."""
     if not (a.is_cuda and a.dtype == torch.bfloat16):
         return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
                               bias=bias, residual=residual, swiglu=swiglu, preact=preact)
@@ -116,6 +119,10 @@ def gemm(
     if (N % 8 or (swiglu and N % 16) or a.stride(0) % 8 or b.stride(0) % 8
             or (out is not None and (out.stride(1) != 1 or out.stride(0) % 4))
             or (residual is not None and residual.stride(0) % 8) or (preact is not None and preact.stride(0) % 8)):
+        from ..logging_utils.logger import warn_once
+
+        warn_once(f"gemm-library-{N}-{K}", f"gemm: M={M} N={N} K={K} (strides {a.stride(0)}, {b.stride(0)}) does "
+                  "not meet the 16-byte rule of the TMA operand loads; this product runs on the library GEMM")
         return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
                               bias=bias, residual=residual, swiglu=swiglu, preact=preact)
     if out is None:
@@ -124,7 +131,7 @@ def gemm(
         raise ValueError("gemm: out must be a row-major [M, N] tensor")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise TypeError("gemm: out must be bf16 or fp32")
-    flags = 0
+    flags = int(probe) & 192
     if out.dtype == torch.float32:
         flags |= _lib.GEMM_OUT_F32
     if accumulate:
@@ -255,3 +262,96 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     from .activation import swiglu_packed
 
     return swiglu_packed(torch.nn.functional.linear(x, weight))
+
+
+# ---------------------------------------------------------------------------------------------- batched products
+def _batched_operand(t: torch.Tensor) -> torch.Tensor:
+    """3-D bf16 operand with unit inner stride and row / batch pitches that TMA accepts (multiples of 16 bytes)."""
+    if t.dim() != 3:
+        raise ValueError("bmm operands must be 3-D")
+    if t.dtype != torch.bfloat16:
+        t = t.to(torch.bfloat16)
+    if (t.stride(2) != 1 or t.stride(1) % 8 or t.stride(0) % 8 or t.stride(1) < t.size(2) or t.data_ptr() % 16
+            or (t.size(0) > 1 and t.stride(0) < t.size(1) * t.stride(1))):
+        t = t.contiguous()
+    return t
+
+
+def bmm_reference(a, b, *, a_mn=False, b_mn=False, out_dtype=torch.float32):
+    A = a.transpose(1, 2) if a_mn else a
+    B = b if b_mn else b.transpose(1, 2)
+    return torch.bmm(A.float(), B.float()).to(out_dtype)
+
+
+def _bmm_kernel(a, b, a_mn, b_mn, out_dtype):
+    a, b = _batched_operand(a), _batched_operand(b)
+    batch = a.size(0)
+    K, M = (a.size(1), a.size(2)) if a_mn else (a.size(2), a.size(1))
+    Kb, N = (b.size(1), b.size(2)) if b_mn else (b.size(2), b.size(1))
+    if K != Kb or b.size(0) != batch:
+        raise ValueError(f"bmm: shapes {tuple(a.shape)} (a_mn={a_mn}) x {tuple(b.shape)} (b_mn={b_mn}) do not match")
+    out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+    if batch == 0 or M == 0 or N == 0:
+        return out
+    flags = _lib.GEMM_OUT_F32 if out_dtype == torch.float32 else 0
+    rc = _lib.cuda_lib().lme_gemm_bf16_batched(
+        a.data_ptr(), int(a_mn), a.stride(1), a.stride(0), b.data_ptr(), int(b_mn), b.stride(1), b.stride(0),
+        out.data_ptr(), out.stride(1), out.stride(0), batch, M, N, K, flags, _max_ctas(a.device), _lib.stream_ptr())
+    _lib.check(rc, f"lme_gemm_bf16_batched batch={batch} M={M} N={N} K={K}")
+    _lib.count_launch()
+    return out
+
+
+def _bmm_kernel_usable(a, b, a_mn, b_mn) -> bool:
+    if not (a.is_cuda and a.dim() == 3 and b.dim() == 3):
+        return False
+    K, M = (a.size(1), a.size(2)) if a_mn else (a.size(2), a.size(1))
+    N = b.size(2) if b_mn else b.size(1)
+    # innermost extents of the tensor maps and the output pitch in units of 16 bytes
+    return N % 8 == 0 and (M if a_mn else K) % 8 == 0 and (N if b_mn else K) % 8 == 0
+
+
+class _Bmm(torch.autograd.Function):
+    """``C[i] = A[i] B[i]^T`` over a batch on the tcgen05 GEMM (3-D tensor maps), fp32 or bf16 result; the two
+    gradients are the same kernel with the layouts swapped, so no operand is ever transposed in memory."""
+
+    @staticmethod
+    def forward(ctx, a, b, a_mn, b_mn, out_dtype):
+        ctx.save_for_backward(a, b)
+        ctx.cfg = (a_mn, b_mn)
+        return _bmm_kernel(a, b, a_mn, b_mn, out_dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        a_mn, b_mn = ctx.cfg
+        g = g.to(torch.bfloat16)
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            # dA = dC B  (stored like A: [M, K], or [K, M] when A is MN-major)
+            da = (_bmm_kernel(b, g, not b_mn, False, torch.bfloat16) if a_mn
+                  else _bmm_kernel(g, b, False, not b_mn, torch.bfloat16)).to(a.dtype)
+        if ctx.needs_input_grad[1]:
+            # dB = dC^T A  (stored like B: [N, K], or [K, N] when B is MN-major)
+            db = (_bmm_kernel(a, g, not a_mn, True, torch.bfloat16) if b_mn
+                  else _bmm_kernel(g, a, True, not a_mn, torch.bfloat16)).to(b.dtype)
+        return da, db, None, None, None
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+        out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Batched ``C[i, M, N] = sum_k A_i(m, k) B_i(n, k)``: ``a`` is ``[batch, M, K]`` (or ``[batch, K, M]`` with
+    ``a_mn``), ``b`` is ``[batch, N, K]`` (or ``[batch, K, N]`` with ``b_mn``); bf16 operands, fp32 accumulation.
+    Differentiable.  Shapes that the TMA loads cannot take run as a PyTorch statement."""
+    if not _bmm_kernel_usable(a, b, a_mn, b_mn):
+        if a.is_cuda:
+            from ..logging_utils.logger import warn_once
+
+            warn_once(f"bmm-library-{tuple(a.shape[1:])}-{tuple(b.shape[1:])}",
+                      f"bmm: operands {tuple(a.shape)} x {tuple(b.shape)} do not meet the 16-byte rule of the TMA "
+                      "loads; this product runs on the library GEMM")
+            A = a.transpose(1, 2) if a_mn else a
+            B = b if b_mn else b.transpose(1, 2)
+            return torch.bmm(A.to(torch.bfloat16), B.to(torch.bfloat16)).to(out_dtype)
+        return bmm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype)
+    return _Bmm.apply(a, b, a_mn, b_mn, out_dtype)

@@ -29,39 +29,17 @@ def ssd_recurrent_step(x, dt, A, B, C, D, h):
 
 def _group_mm(a: torch.Tensor, b: torch.Tensor, lowp: bool) -> torch.Tensor:
     """``a @ b`` over the leading (batch, chunk, group) dims with an fp32 result; bf16 operands on the tensor cores
-    when the model computes in bf16, plain fp32 otherwise."""
+    (the batched tcgen05 GEMM, ``b`` read as its MN-major operand) when the model computes in bf16, plain fp32
+    otherwise."""
     lead = a.shape[:-2]
     a2, b2 = a.reshape(-1, *a.shape[-2:]), b.reshape(-1, *b.shape[-2:])
     if lowp:
-        out = _BmmF32.apply(a2.to(torch.bfloat16).contiguous(), b2.to(torch.bfloat16).contiguous())
+        from .gemm import bmm
+
+        out = bmm(a2.to(torch.bfloat16), b2.to(torch.bfloat16), b_mn=True)
     else:
         out = torch.bmm(a2.float(), b2.float())
     return out.view(*lead, a.size(-2), b.size(-1))
-
-
-def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """bf16 x bf16 batched product with an fp32 result (tensor cores, no rounding of the sums)."""
-    try:
-        return torch.bmm(a, b, out_dtype=torch.float32)
-    except (TypeError, RuntimeError):
-        return torch.bmm(a, b).float()
-
-
-class _BmmF32(torch.autograd.Function):
-    """:func:`_bmm_f32` with its derivative (the ``out_dtype`` form of ``bmm`` has none registered)."""
-
-    @staticmethod
-    def forward(ctx, a, b):
-        ctx.save_for_backward(a, b)
-        return _bmm_f32(a, b)
-
-    @staticmethod
-    def backward(ctx, g):
-        a, b = ctx.saved_tensors
-        g = g.to(torch.bfloat16)
-        da = torch.bmm(g, b.transpose(1, 2)) if ctx.needs_input_grad[0] else None
-        db = torch.bmm(a.transpose(1, 2), g) if ctx.needs_input_grad[1] else None
-        return da, db
 
 
 class _IntraChunk(torch.autograd.Function):
@@ -82,7 +60,10 @@ class _IntraChunk(torch.autograd.Function):
         _lib.check(_lib.cuda_lib().lme_ssd_decay_matrix(CB.data_ptr(), ct.data_ptr(), M.data_ptr(), b * nc, N, G, L,
                                                         _lib.stream_ptr()), "lme_ssd_decay_matrix")
         _lib.count_launch()
-        y = _bmm_f32(M.view(-1, L, L), xdt.view(-1, L, P)).view(b, nc, N, L, P)
+        from .gemm import _bmm_kernel
+
+        # y = M xdt: M is [l, s] (K-major), xdt is [s, P] = [K, N] (MN-major)
+        y = _bmm_kernel(M.view(-1, L, L), xdt.view(-1, L, P), False, True, torch.float32).view(b, nc, N, L, P)
         ctx.save_for_backward(M, ct, xdt, y)
         ctx.G = G
         return y
@@ -97,8 +78,11 @@ class _IntraChunk(torch.autograd.Function):
         dy32 = dy.contiguous().float()
         dy = dy32.to(torch.bfloat16)
         dyv, xv = dy.view(-1, L, P), xdt.view(-1, L, P)
-        dM = torch.bmm(dyv, xv.transpose(1, 2))                          # [bcn, L, L]
-        dxdt = _bmm_f32(M.view(-1, L, L).transpose(1, 2), dyv).view(b, nc, N, L, P)
+        from .gemm import _bmm_kernel
+
+        dM = _bmm_kernel(dyv, xv, False, False, torch.bfloat16)          # dy xdt^T  [bcn, L, L]
+        # M^T dy: M read as the MN-major A operand, dy [l, P] = [K, N] as the MN-major B operand
+        dxdt = _bmm_kernel(M.view(-1, L, L), dyv, True, True, torch.float32).view(b, nc, N, L, P)
         dCB = torch.empty((b, nc, G, L, L), dtype=torch.bfloat16, device=dy.device)
         _lib.check(_lib.cuda_lib().lme_ssd_dcb(dM.data_ptr(), ct.data_ptr(), dCB.data_ptr(), b * nc, N, G, L,
                                                _lib.stream_ptr()), "lme_ssd_dcb")
@@ -187,6 +171,50 @@ class _ScanCombine(torch.autograd.Function):
         return dyin, doff, decum, dDp.sum((0, 1, 2)), dx
 
 
+class _BoundaryScan(torch.autograd.Function):
+    """``h_{c+1} = decay[c] h_c + S_c`` over the chunks of every (batch, head) in one kernel each way.  Returns the
+    state at every chunk start in bf16 (``[b, nc, N, P, Sd]``, the operand of the carried-state product) and the
+    final state in fp32."""
+
+    @staticmethod
+    def forward(ctx, states, decay, h_init):
+        from . import _lib
+
+        b, nc, N, P, Sd = states.shape
+        states, decay = states.contiguous(), decay.contiguous()
+        h_init = None if h_init is None else h_init.float().contiguous()
+        h0 = torch.empty((b, nc, N, P, Sd), dtype=torch.bfloat16, device=states.device)
+        keep = torch.is_grad_enabled() and (states.requires_grad or decay.requires_grad
+                                            or (h_init is not None and h_init.requires_grad))
+        h0f = torch.empty((b, nc, N, P, Sd), dtype=torch.float32, device=states.device) if keep else None
+        hf = torch.empty((b, N, P, Sd), dtype=torch.float32, device=states.device)
+        _lib.check(_lib.cuda_lib().lme_ssd_boundary_fwd(states.data_ptr(), decay.data_ptr(), _lib.ptr(h_init),
+                                                        h0.data_ptr(), _lib.ptr(h0f), hf.data_ptr(), b, nc, N,
+                                                        P * Sd, _lib.stream_ptr()), "lme_ssd_boundary_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(h0f, decay)
+        ctx.has_init = h_init is not None
+        return h0, hf
+
+    @staticmethod
+    def backward(ctx, dh0, dhf):
+        from . import _lib
+
+        h0f, decay = ctx.saved_tensors
+        b, nc, N, P, Sd = h0f.shape
+        dh0 = None if dh0 is None else dh0.float().contiguous()
+        dhf = None if dhf is None else dhf.float().contiguous()
+        dstates = torch.empty_like(h0f)
+        ddecay = torch.empty_like(decay)
+        dinit = torch.empty((b, N, P, Sd), dtype=torch.float32, device=h0f.device) if ctx.has_init else None
+        _lib.check(_lib.cuda_lib().lme_ssd_boundary_bwd(_lib.ptr(dh0), _lib.ptr(dhf), h0f.data_ptr(),
+                                                        decay.data_ptr(), dstates.data_ptr(), ddecay.data_ptr(),
+                                                        _lib.ptr(dinit), b, nc, N, P * Sd, _lib.stream_ptr()),
+                   "lme_ssd_boundary_bwd")
+        _lib.count_launch()
+        return dstates, ddecay, dinit
+
+
 def scan_glue_eligible(x: torch.Tensor, L: int) -> bool:
     return (x.is_cuda and x.dtype == torch.bfloat16 and L % 32 == 0 and L <= 1024 and x.size(-1) in (32, 64, 128)
             and FUSED_INTRA_CHUNK)
@@ -197,7 +225,10 @@ def _intra_chunk_fused(Cc, Bc, ct, xdt):
     xdt ``[b, nc, L, N, P]`` fp32 -> ``[b, nc, L, N, P]`` fp32."""
     Cg = Cc.permute(0, 1, 3, 2, 4).to(torch.bfloat16)                    # [b, nc, G, L, Sd]
     Bg = Bc.permute(0, 1, 3, 2, 4).to(torch.bfloat16)
-    CB = torch.matmul(Cg, Bg.transpose(-1, -2))                          # [b, nc, G, L, L] bf16
+    from .gemm import bmm
+
+    CB = bmm(Cg.reshape(-1, *Cg.shape[-2:]), Bg.reshape(-1, *Bg.shape[-2:]),
+             out_dtype=torch.bfloat16).view(*Cg.shape[:-1], Cg.size(-2))  # [b, nc, G, L, L] bf16
     xh = xdt.permute(0, 1, 3, 2, 4).to(torch.bfloat16)                   # [b, nc, N, L, P]
     y = _IntraChunk.apply(CB, ct, xh)
     return y.permute(0, 1, 3, 2, 4)
@@ -273,8 +304,9 @@ def ssd_chunk_scan(x, dt, A, B, C, D, chunk_size: int, initial_state=None):
 
 def _chunk_scan_kernels(x, pad, dtc, cum, Bc, Cc, D, initial_state, b, S, nc, L, N, P, G, Sd):
     """The CUDA composition of :func:`ssd_chunk_scan`: the element-wise passes are two kernels (:class:`_ScanPrep`,
-    :class:`_ScanCombine`), the L x L part is :class:`_IntraChunk`, the products are batched tensor-core GEMMs; only
-    per-(token, head) scalars (decays) and the short loop over chunk boundaries stay PyTorch ops."""
+    :class:`_ScanCombine`), the L x L part is :class:`_IntraChunk`, every product is the batched tcgen05 GEMM
+    (:func:`lm_engine_b200.ops.gemm.bmm`), the recurrence over chunk boundaries is :class:`_BoundaryScan`; only
+    per-(token, head) scalars (decays, their cumulative sums) stay PyTorch ops."""
     rep = N // G
     xb = torch.nn.functional.pad(x, (0, 0, 0, 0, 0, pad)) if pad else x
     xc = xb.reshape(b, nc, L, N, P)
@@ -283,20 +315,18 @@ def _chunk_scan_kernels(x, pad, dtc, cum, Bc, Cc, D, initial_state, b, S, nc, L,
     # intra-chunk
     Cg = Cc.permute(0, 1, 3, 2, 4).to(torch.bfloat16).contiguous()        # [b, nc, G, L, Sd]
     Bg = Bc.permute(0, 1, 3, 2, 4).to(torch.bfloat16).contiguous()
-    CB = torch.matmul(Cg, Bg.transpose(-1, -2))                          # [b, nc, G, L, L]
+    from .gemm import bmm
+
+    CB = bmm(Cg.view(b * nc * G, L, Sd), Bg.view(b * nc * G, L, Sd),
+             out_dtype=torch.bfloat16).view(b, nc, G, L, L)              # C B^T per (batch, chunk, group)
     yin = _IntraChunk.apply(CB, cum.permute(0, 1, 3, 2), xh)             # [b, nc, N, L, P] fp32
-    # chunk summaries S_c [b, nc, G, rep*P, Sd] (the heads of a group folded into the GEMM's M dimension)
-    states = _BmmF32.apply(xwT.view(b * nc * G, rep * P, L), Bg.view(b * nc * G, L, Sd)).view(b, nc, N, P, Sd)
-    h = (torch.zeros(b, N, P, Sd, dtype=torch.float32, device=x.device) if initial_state is None
-         else initial_state.float())
+    # chunk summaries S_c [b, nc, G, rep*P, Sd] (the heads of a group folded into the GEMM's M dimension);
+    # B_c is [L, Sd] = [K, N]: the MN-major operand
+    states = bmm(xwT.view(b * nc * G, rep * P, L), Bg.view(b * nc * G, L, Sd), b_mn=True).view(b, nc, N, P, Sd)
     chunk_decay = torch.exp(cum[:, :, -1, :])                 # [b, nc, N]
-    starts = []
-    for c in range(nc):
-        starts.append(h)
-        h = h * chunk_decay[:, c, :, None, None] + states[:, c]
-    h0 = torch.stack(starts, dim=1)                           # [b, nc, N, P, Sd]
-    hgT = h0.view(b * nc * G, rep * P, Sd).transpose(1, 2).to(torch.bfloat16).contiguous()
-    off = _BmmF32.apply(Cg.view(b * nc * G, L, Sd), hgT).view(b, nc, G, L, rep * P)
+    h0, h = _BoundaryScan.apply(states, chunk_decay, initial_state)      # [b, nc, N, P, Sd] bf16, [b, N, P, Sd]
+    # carried-state contribution C_t . h_c: the states [rep*P, Sd] are the K-major B operand as they are
+    off = bmm(Cg.view(b * nc * G, L, Sd), h0.view(b * nc * G, rep * P, Sd)).view(b, nc, G, L, rep * P)
     y = _ScanCombine.apply(yin, off, torch.exp(cum), D.float(), xc)
     return y.reshape(b, nc * L, N, P)[:, :S], h
 

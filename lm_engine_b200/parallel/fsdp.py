@@ -630,7 +630,8 @@ class FSDPEngine:
         # here (see _reduce_grads).  With two buffers the backward pass of unit i - 2 would then wait for the
         # reduction of unit i - 1, which has only just been issued: nothing would overlap.  A third buffer moves
         # that wait one unit back.
-        depth = 2
+        # gathered parameters: the running unit plus up to two prefetched ones (see _prefetch) are live at once
+        depth = 3 if kind == "p" else 2
         if symmetric:   # units of a size that occurs once or twice per step never meet that wait: one buffer each
             depth = min(3, sum(1 for x in self.all_units if x.numel == u.numel and self._ce_reduce_applies(x)))
         if len(bufs) < depth:

@@ -227,6 +227,12 @@ class _RingAttention(torch.autograd.Function):
                     o_b, l_b = kernel_block_forward(q, kv[0], kv[1], runs[r], runs[src], scale, causal)
                     out, lse = merge_partial(out, lse, o_b, l_b)
             elif _block_needed(pos[r], pos[src], causal, window):
+                if q.is_cuda:
+                    from ..logging_utils.logger import warn_once
+
+                    warn_once("ring-attention-pytorch-block", "ring attention: a block is windowed, not bf16 with "
+                              "head dim 128, or not made of 128-row runs; it runs as a PyTorch statement that "
+                              "materialises its fp32 score matrix")
                 o_b, l_b = block_attention_forward(q, kv[0], kv[1], pos[r], pos[src], scale, causal, window)
                 out, lse = merge_partial(out, lse, o_b, l_b)
             if works is not None:
@@ -247,6 +253,7 @@ class _RingAttention(torch.autograd.Function):
         dq = torch.zeros_like(q, dtype=torch.float32)
         kv = torch.stack((k, v)).contiguous()
         dkv = torch.zeros_like(kv, dtype=torch.float32)
+        dkv_works = None        # rotation of the dK / dV accumulators started in the previous step
         for step in range(cp):
             src = (r - step) % cp
             nxt_kv = works = None
@@ -258,6 +265,11 @@ class _RingAttention(torch.autograd.Function):
                     blk = kernel_block_backward(do, q, kv[0], kv[1], out, lse, runs[r], runs[src], scale, causal)
             elif _block_needed(pos[r], pos[src], causal, window):
                 blk = block_attention_backward(do, q, kv[0], kv[1], out, lse, pos[r], pos[src], scale, causal, window)
+            # the accumulators of the previous step were sent on while this block was computed (the reference
+            # awaits its dK / dV rotation after the block as well, ring_attention.py:202-434)
+            if dkv_works is not None:
+                for w in dkv_works:
+                    w.wait()
             if blk is not None:
                 dq += blk[0]
                 dkv[0] += blk[1]
@@ -267,9 +279,9 @@ class _RingAttention(torch.autograd.Function):
                     w.wait()
                 kv = nxt_kv
             # the accumulators travel with their K/V block; after cp hops they are back at the owner
-            dkv, w2 = _rotate(dkv, group)
-            for w in w2:
-                w.wait()
+            dkv, dkv_works = _rotate(dkv, group)
+        for w in dkv_works:
+            w.wait()
         return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None, None, None
 
 

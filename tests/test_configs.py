@@ -52,3 +52,39 @@ def test_tiny_config_trains(tmp_path, monkeypatch):
     main(TrainingArgs)
     ProcessGroupManager.destroy_process_groups()
     assert os.path.isfile(tmp_path / "ckpt" / "latest_checkpointed_iteration.json")
+
+
+_REF_CONFIGS = os.path.join(os.path.dirname(ROOT), "baseline", "_ref", "configs")
+
+
+@pytest.mark.skipif(not os.path.isdir(_REF_CONFIGS), reason="no copy of the reference project's configs/ under baseline/_ref")
+def test_every_reference_config_parses():
+    """The YAML schema is the public surface shared with the reference project: each of its own example configs
+    (training, finetuning, distillation, unsharding, sweeps, research models) has to load through this repository's
+    argument classes, and every model description in them has to build a config object."""
+    from lm_engine_b200.arguments import DistillationArgs, TrainingArgs, UnshardingArgs
+    from lm_engine_b200.models import config_from_dict
+
+    paths = sorted(glob.glob(os.path.join(_REF_CONFIGS, "**", "*.yml"), recursive=True))
+    assert len(paths) >= 40
+    parsed = models = 0
+    for path in paths:
+        cfg = _load(path)
+        if not isinstance(cfg, dict):
+            continue
+        if "parameters" in cfg and "method" in cfg:            # W&B sweep description
+            continue
+        if "unsharded_path" in cfg:
+            UnshardingArgs(**cfg)
+            parsed += 1
+            continue
+        if "model_args" not in cfg:
+            continue
+        args = (DistillationArgs if "teacher_args" in cfg else TrainingArgs)(**cfg)
+        parsed += 1
+        pc = args.model_args.pretrained_config
+        if pc is not None:
+            c = config_from_dict(pc)
+            assert len(c.sequence_mixer_blocks) == c.num_layers == len(c.mlp_blocks), path
+            models += 1
+    assert parsed >= 40 and models >= 38, (parsed, models)

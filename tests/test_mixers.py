@@ -239,3 +239,23 @@ def test_left_padded_batch_runs_as_one_scan():
         torch.testing.assert_close(y[b:b + 1, 9 - n:], yb)
         torch.testing.assert_close(h[b:b + 1], hb)
         assert y[b, :9 - n].abs().max().item() == 0 if n < 9 else True
+
+
+def test_sliding_window_counts_keys_like_the_reference():
+    """``sliding_window = w`` lets a causal query see itself and the w keys before it (the reference passes
+    (w, w) to flash-attn): moving a token w + 1 positions back must not change the last position's output, moving
+    one w positions back must."""
+    torch.manual_seed(0)
+    w = 3
+    cfg = config_from_dict(_base(1, [dict(sequence_mixer_type="softmax_attention", num_attention_heads=4,
+                                          num_key_value_heads=2, sliding_window=w)]))
+    model = build_model(cfg).eval()
+    ids = torch.randint(3, 256, (1, 12))
+    with torch.no_grad():
+        base = model(input_ids=ids).logits[0, -1]
+        far = ids.clone()
+        far[0, 11 - (w + 1)] = (far[0, 11 - (w + 1)] + 7) % 256         # outside the window of position 11
+        near = ids.clone()
+        near[0, 11 - w] = (near[0, 11 - w] + 7) % 256                   # the oldest key inside it
+        assert torch.allclose(model(input_ids=far).logits[0, -1], base, atol=1e-6)
+        assert not torch.allclose(model(input_ids=near).logits[0, -1], base, atol=1e-4)
