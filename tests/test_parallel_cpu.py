@@ -153,3 +153,26 @@ def test_padding_free_training_matches_the_batched_layout(kind, topo, sp, tmp_pa
     np.testing.assert_allclose(loss, ref_loss, rtol=2e-4)
     for o in outs:
         np.testing.assert_allclose(o[1], ref_norm, rtol=2e-3)
+
+
+CASES_4_RANKS = [
+    ("dense", {"tensor_parallel_world_size": 2}, True),                                      # TP2 + SP x ZeRO-3 over 2
+    ("dense", {"context_parallel_world_size": 2, "context_parallel_attention": "ring"}, False),      # CP2 x ZeRO-3 over 2
+    ("dense", {"tensor_parallel_world_size": 2, "context_parallel_world_size": 2}, False),   # TP2 x CP2
+    ("moe", {"expert_parallel_world_size": 2}, False),                                       # EP2, experts replicated x2
+    ("hybrid", {"context_parallel_world_size": 2}, False),                                   # recurrent CP2 x ZeRO-3 over 2
+]
+
+
+@pytest.mark.parametrize("kind,topo,sp", CASES_4_RANKS,
+                         ids=["tp2-sp-x-dp2", "cp2-ring-x-dp2", "tp2-x-cp2", "ep2-x-dp2", "cp2-hybrid-x-dp2"])
+def test_composed_meshes_on_four_ranks_match_single_process(kind, topo, sp, tmp_path):
+    """Two parallel dimensions at once on 4 gloo ranks (the reference tests TP x PP x ZeRO combinations the same
+    way, tests/dcp/dcp_test.py): loss and gradient norm of every step against one process."""
+    steps, total_mbs = 3, 4          # expert parallelism alone leaves 4 data-parallel ranks: one sample each
+    d, (ref_loss, ref_norm, _) = _reference(kind, tmp_path, steps, total_mbs)
+    outs = run_distributed(_train, 4, kind, topo, d, steps, total_mbs, sp, timeout=600)
+    loss = [sum(o[0][s] for o in outs) / len(outs) for s in range(steps)]
+    np.testing.assert_allclose(loss, ref_loss, rtol=3e-4)
+    for o in outs:
+        np.testing.assert_allclose(o[1], ref_norm, rtol=3e-3)
