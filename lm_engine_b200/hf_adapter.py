@@ -3,8 +3,9 @@
 
 ``LLMAdapter_HF.from_pretrained(path, config=...)`` loads either a safetensors directory or, when ``path`` holds
 ``latest_checkpointed_iteration.json``, a sharded training checkpoint that is unsharded on the fly.
-``generate`` decodes greedily or samples (temperature / top-k / top-p) for left-padded batches and stops rows at
-``eos_token_id``; ``forward`` returns ``loss`` (mean, shifted) / ``logits`` / ``past_key_values`` under the field
+``generate`` is Hugging Face's (the adapter is a ``PreTrainedModel`` + ``GenerationMixin``); ``generate_simple``
+decodes greedily or samples (temperature / top-k / top-p) for left-padded batches and stops rows at
+``eos_token_id`` without that machinery; ``forward`` returns ``loss`` (mean, shifted) / ``logits`` / ``past_key_values`` under the field
 names Hugging Face evaluation code expects.  The adapter is for single-stage, padded (not packed) inference.
 """
 
@@ -37,18 +38,98 @@ def get_causal_lm_class(model_type: str):
     return _get_class(model_type)
 
 
-@dataclass
-class AdapterOutput:
-    loss: torch.Tensor | None = None
-    logits: torch.Tensor | None = None
-    past_key_values: GenerationCache | None = None
+try:    # the adapter is a transformers model when that package is importable, else a plain module
+    from transformers import GenerationMixin, PretrainedConfig, PreTrainedModel
+    from transformers.utils import ModelOutput
+
+    _HAVE_TRANSFORMERS = True
+except Exception:  # noqa: BLE001
+    _HAVE_TRANSFORMERS = False
+    GenerationMixin = object
+    PreTrainedModel = nn.Module
+    PretrainedConfig = object
+    ModelOutput = object
 
 
-class LLMAdapter_HF(nn.Module):
+if _HAVE_TRANSFORMERS:
+
+    @dataclass
+    class AdapterOutput(ModelOutput):
+        """``loss`` / ``logits`` / ``past_key_values`` under the names ``GenerationMixin`` looks for."""
+
+        loss: torch.Tensor | None = None
+        logits: torch.Tensor | None = None
+        past_key_values: GenerationCache | None = None
+
+    class LLMAdapterConfig(PretrainedConfig):
+        """What ``PreTrainedModel`` / ``GenerationMixin`` read from a config (token ids, sizes), filled from the
+        package's own :class:`CommonConfig`; the full model description travels along as ``common``."""
+
+        model_type = "lm_engine_b200_adapter"
+
+        def __init__(self, common: dict | None = None, **kwargs) -> None:
+            common = dict(common or {})
+            self.common = common
+            for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
+                kwargs.setdefault(k, common.get(k))
+            self.vocab_size = common.get("vocab_size")
+            self.hidden_size = common.get("hidden_size")
+            self.num_hidden_layers = common.get("num_layers")
+            self.max_position_embeddings = common.get("max_position_embeddings")
+            kwargs.setdefault("tie_word_embeddings", bool(common.get("tie_word_embeddings", False)))
+            super().__init__(**kwargs)
+
+        @classmethod
+        def from_common_config(cls, config: CommonConfig) -> "LLMAdapterConfig":
+            return cls(common=config.to_dict())
+
+else:
+
+    @dataclass
+    class AdapterOutput:
+        loss: torch.Tensor | None = None
+        logits: torch.Tensor | None = None
+        past_key_values: GenerationCache | None = None
+
+
+class LLMAdapter_HF(PreTrainedModel, GenerationMixin):
+    """``transformers.PreTrainedModel`` + ``GenerationMixin`` around an already built ``CausalLM`` of this package, so
+    that ``model.generate(...)`` with the Hugging Face arguments (beam search, logits processors, stopping criteria,
+    streamers), ``transformers.pipeline`` and evaluation harnesses work unchanged (lm_engine/hf_adapter.py:107-272).
+    The cache is the package's own :class:`GenerationCache`; :meth:`generate_simple` is a dependency-free greedy /
+    sampling loop over the same ``forward``."""
+
+    if _HAVE_TRANSFORMERS:
+        config_class = LLMAdapterConfig
+        base_model_prefix = "model"
+        main_input_name = "input_ids"
+        _supports_cache_class = False
+
     def __init__(self, model: nn.Module) -> None:
-        super().__init__()
+        if _HAVE_TRANSFORMERS:
+            super().__init__(LLMAdapterConfig.from_common_config(model.config))
+        else:
+            super().__init__()
+            self.config = model.config
         self.model = model
-        self.config = model.config
+        self.common_config = model.config
+
+    @classmethod
+    def _supports_default_dynamic_cache(cls) -> bool:
+        # the models create their own cache on the first forward call; generate() must not build a DynamicCache
+        return False
+
+    def prepare_inputs_for_generation(self, input_ids, past_key_values=None, attention_mask=None, **kwargs) -> dict:
+        """One decoding step's inputs: the whole prompt on the first call, the newest token afterwards; positions
+        count the real tokens of a left-padded row."""
+        if attention_mask is None:
+            attention_mask = torch.ones_like(input_ids)
+        pos = (attention_mask.long().cumsum(-1) - 1).clamp_min(0)
+        use_cache = kwargs.get("use_cache", True)
+        if past_key_values is not None and use_cache:
+            input_ids, pos = input_ids[:, -1:], pos[:, -1:]
+        return {"input_ids": input_ids, "attention_mask": attention_mask, "position_ids": pos,
+                "past_key_values": past_key_values if use_cache else None, "use_cache": use_cache}
 
     # ------------------------------------------------------------------ construction / IO
     @classmethod
@@ -133,8 +214,8 @@ class LLMAdapter_HF(nn.Module):
         return AdapterOutput(loss=loss, logits=out.logits, past_key_values=out.cache_params)
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None,
-                 max_new_tokens: int = 20, do_sample: bool = False, temperature: float = 1.0,
+    def generate_simple(self, input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None,
+                        max_new_tokens: int = 20, do_sample: bool = False, temperature: float = 1.0,
                  top_k: int | None = None, top_p: float | None = None, eos_token_id: int | None = None,
                  pad_token_id: int | None = None, generator: torch.Generator | None = None,
                  use_cache: bool = True, **_ignored) -> torch.Tensor:
@@ -142,9 +223,10 @@ class LLMAdapter_HF(nn.Module):
         finished rows keep emitting ``pad_token_id``."""
         was_training = self.model.training
         self.model.eval()
-        eos = self.config.eos_token_id if eos_token_id is None else eos_token_id
-        pad = pad_token_id if pad_token_id is not None else (self.config.pad_token_id
-                                                             if self.config.pad_token_id is not None else eos)
+        cfg = self.common_config
+        eos = cfg.eos_token_id if eos_token_id is None else eos_token_id
+        pad = pad_token_id if pad_token_id is not None else (cfg.pad_token_id if cfg.pad_token_id is not None
+                                                             else eos)
         B = input_ids.size(0)
         if attention_mask is None:
             attention_mask = torch.ones_like(input_ids)
@@ -192,15 +274,21 @@ def _sample(logits: torch.Tensor, temperature: float, top_k: int | None, top_p: 
 
 
 def register_model_classes() -> None:
-    """Registers the architectures with ``transformers.AutoConfig`` when that package is importable, so that
-    ``AutoConfig.from_pretrained`` resolves ``model_type`` of exported checkpoints.  Models are built by this module."""
-    try:
-        from transformers import AutoConfig, PretrainedConfig
-    except Exception:  # noqa: BLE001
+    """Registers the architectures with ``transformers``' Auto classes when that package is importable:
+    ``AutoConfig`` resolves the ``model_type`` of exported checkpoints, and ``AutoModelForCausalLM`` maps the
+    adapter's config to :class:`LLMAdapter_HF`."""
+    if not _HAVE_TRANSFORMERS:
         return
+    from transformers import AutoConfig, AutoModelForCausalLM
+
     for mt in _CUSTOM_MODEL_TYPES:
         shim = type(f"{mt}_Config", (PretrainedConfig,), {"model_type": mt})
         try:
             AutoConfig.register(mt, shim)
         except ValueError:
             pass
+    try:
+        AutoConfig.register(LLMAdapterConfig.model_type, LLMAdapterConfig)
+        AutoModelForCausalLM.register(LLMAdapterConfig, LLMAdapter_HF)
+    except ValueError:
+        pass

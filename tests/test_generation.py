@@ -28,27 +28,27 @@ def _adapter(kind="dense", seed=0):
 def test_cached_generation_equals_recompute(kind):
     m = _adapter(kind)
     ids = torch.randint(3, VOCAB, (2, 7))
-    a = m.generate(ids, max_new_tokens=6, use_cache=True, eos_token_id=-1)
-    b = m.generate(ids, max_new_tokens=6, use_cache=False, eos_token_id=-1)
+    a = m.generate_simple(ids, max_new_tokens=6, use_cache=True, eos_token_id=-1)
+    b = m.generate_simple(ids, max_new_tokens=6, use_cache=False, eos_token_id=-1)
     assert a.shape == (2, 13) and torch.equal(a, b)
 
 
 def test_left_padding_does_not_change_the_continuation():
     m = _adapter()
     short, long = torch.randint(3, VOCAB, (1, 4)), torch.randint(3, VOCAB, (1, 9))
-    alone = m.generate(short, max_new_tokens=5, eos_token_id=-1)[0, 4:]
+    alone = m.generate_simple(short, max_new_tokens=5, eos_token_id=-1)[0, 4:]
     batch = torch.cat((torch.cat((torch.full((1, 5), 2), short), 1), long))
     mask = torch.ones_like(batch)
     mask[0, :5] = 0
-    both = m.generate(batch, attention_mask=mask, max_new_tokens=5, eos_token_id=-1)
+    both = m.generate_simple(batch, attention_mask=mask, max_new_tokens=5, eos_token_id=-1)
     assert torch.equal(both[0, 9:], alone)
 
 
 def test_eos_stops_rows_and_pads():
     m = _adapter()
     ids = torch.randint(3, VOCAB, (2, 5))
-    first = m.generate(ids, max_new_tokens=1, eos_token_id=-1)[:, -1]
-    out = m.generate(ids, max_new_tokens=4, eos_token_id=int(first[0]), pad_token_id=0)
+    first = m.generate_simple(ids, max_new_tokens=1, eos_token_id=-1)[:, -1]
+    out = m.generate_simple(ids, max_new_tokens=4, eos_token_id=int(first[0]), pad_token_id=0)
     assert out[0, 5] == first[0] and (out[0, 6:] == 0).all()
 
 
@@ -74,3 +74,26 @@ def test_sampling_filters():
     flat = torch.zeros(256, 5)
     s = _sample(flat, 1.0, 2, None, g)
     assert s.max() <= 4 and len(s.unique()) <= 5
+
+
+def test_hugging_face_generate_matches_the_simple_loop():
+    """The adapter is a transformers ``PreTrainedModel`` + ``GenerationMixin``: its inherited ``generate`` (greedy, with
+    the package's own cache, left-padded batch) produces the tokens of the dependency-free loop, and beam search
+    runs through the same forward."""
+    transformers = pytest.importorskip("transformers")
+    m = _adapter()
+    assert isinstance(m, transformers.PreTrainedModel) and isinstance(m, transformers.GenerationMixin)
+    torch.manual_seed(1)
+    ids = torch.randint(3, VOCAB, (2, 7))
+    mask = torch.ones_like(ids)
+    mask[1, :3] = 0                                    # second row is left-padded
+    want = m.generate_simple(ids, attention_mask=mask, max_new_tokens=6, eos_token_id=-1)
+    got = m.generate(input_ids=ids, attention_mask=mask, max_new_tokens=6, do_sample=False, eos_token_id=None,
+                     pad_token_id=0)
+    assert torch.equal(got, want)
+    no_cache = m.generate(input_ids=ids, attention_mask=mask, max_new_tokens=6, do_sample=False, eos_token_id=None,
+                          pad_token_id=0, use_cache=False)
+    assert torch.equal(no_cache, want)
+    beams = m.generate(input_ids=ids[:1], max_new_tokens=4, num_beams=3, do_sample=False, eos_token_id=None,
+                       pad_token_id=0)
+    assert beams.shape == (1, 11)
