@@ -130,14 +130,15 @@ def _checkpointed_units(model: nn.Module, method, ckpt_args: dict) -> set[str]:
 
 def shard_model(wrapper, *, stage: int, dtype: torch.dtype, communication_dtype: torch.dtype | None,
                 gradient_checkpointing_method=None, gradient_checkpointing_args: dict | None = None,
-                use_mup_group: bool = False, seed: int = 0, device: torch.device | None = None) -> FSDPEngine:
+                use_mup_group: bool = False, seed: int = 0, device: torch.device | None = None,
+                cpu_offload: bool = False) -> FSDPEngine:
     model = wrapper.model
     units = build_units(model)
     ckpt = _checkpointed_units(model, gradient_checkpointing_method, gradient_checkpointing_args or {})
     has_dropout = any(isinstance(m, nn.Dropout) and m.p > 0 for m in model.modules())
     engine = FSDPEngine(model, units, stage=stage, compute_dtype=dtype, grad_dtype=communication_dtype or dtype,
                         device=device, use_mup_group=use_mup_group, checkpoint_units=ckpt, preserve_rng=has_dropout,
-                        seed=seed)
+                        seed=seed, cpu_offload=cpu_offload)
     tr = model.transformer
     for name, mods, _ in units:
         for m in mods:
@@ -173,13 +174,14 @@ def wrap_model_container_for_distributed_training(args: TrainingArgs | Distillat
     if d.torch_compile:
         log_rank_0(logging.WARNING, "torch_compile is ignored: kernels are hand-written, nothing is traced")
     if d.cpu_offload:
-        log_rank_0(logging.WARNING, "cpu_offload is ignored: optimizer state stays in HBM (180 GB per GPU)")
+        log_rank_0(logging.WARNING, "cpu_offload: fp32 master weights and AdamW moments are kept in pinned host "
+                   "memory and updated on the host (slow; a B200 holds the state of a 10B-parameter model in HBM)")
     for wrapper in model_container:
         shard_model(wrapper, stage=d.stage, dtype=dtype, communication_dtype=comm,
                     gradient_checkpointing_method=d.gradient_checkpointing_method,
                     gradient_checkpointing_args=d.gradient_checkpointing_args,
                     use_mup_group=args.optimizer_args.params_group_method == ParamsGroupMethod.mup,
-                    seed=args.random_args.seed)
+                    seed=args.random_args.seed, cpu_offload=bool(d.cpu_offload))
         if dtype_name == "fp8":
             from .fp8 import convert_to_fp8_training
 

@@ -25,19 +25,32 @@ class ShardedOptimizer:
     """Optimizer facade with ``param_groups`` (for LR schedulers), ``step``, ``zero_grad`` and state dicts."""
 
     def __init__(self, engine: FSDPEngine, class_name: str, class_args: dict, m_width: float | None,
-                 use_mup: bool, max_grad_norm: float | None) -> None:
+                 use_mup: bool, max_grad_norm: float | None, step_in_backward: bool = False) -> None:
         if class_name not in _TORCH_OPTIMIZERS:
             raise ValueError(f"invalid class_name ({class_name}) for optimizer")
         self.engine, self.class_name, self.class_args = engine, class_name, dict(class_args)
         self.max_grad_norm = max_grad_norm
+        self.step_in_backward = step_in_backward
         lr = class_args["lr"]
         self.param_groups = [{"name": "normal", "lr": lr}, {"name": "no_weight_decay", "lr": lr, "weight_decay": 0}]
         if use_mup:
             self.param_groups.append({"name": "mup", "lr": lr / m_width})
         self.fused = class_name == "TorchAdamW" and set(class_args) <= {"lr", "weight_decay", "betas", "eps"}
         self._torch_opt = None
+        if getattr(engine, "cpu_offload", False) and (not self.fused or step_in_backward):
+            raise NotImplementedError("cpu_offload is implemented for TorchAdamW (lr / weight_decay / betas / eps) "
+                                      "stepping after the backward pass")
         if not self.fused:
             self._build_torch_optimizer()
+        if step_in_backward:
+            # The reference steps a per-parameter optimizer from a post-accumulate-grad hook
+            # (lm_engine/optimization/optimizer.py:70-83): the update of a parameter overlaps the backward pass of
+            # the layers in front of it, and there is no global gradient norm to clip by.  Here the update of a
+            # unit's shard runs on the reduction stream right behind the unit's gradient reduction.
+            if not self.fused:
+                raise NotImplementedError("use_optimizer_with_backward_hook is implemented for TorchAdamW with "
+                                          "lr / weight_decay / betas / eps only")
+            engine.post_reduce_hook = self._step_unit
 
     def _build_torch_optimizer(self) -> None:
         groups: dict[str, list[nn.Parameter]] = {g["name"]: [] for g in self.param_groups}
@@ -58,12 +71,49 @@ class ShardedOptimizer:
 
     def zero_grad(self) -> None:
         self.engine.zero_grad()
+        if self.step_in_backward:
+            self.engine.step_count += 1     # the units step during the backward pass that follows
+
+    @torch.no_grad()
+    def _step_unit(self, u) -> None:
+        from .. import ops
+
+        e, a = self.engine, self.class_args
+        lrs = {g["name"]: g["lr"] for g in self.param_groups}
+        if u.grad_post_scale != 1.0:
+            u.grad_shard.mul_(u.grad_post_scale)
+        for g in u.local_group_ranges():
+            sl = slice(g.start, g.end)
+            ops.adamw_step(u.master[sl], u.exp_avg[sl], u.exp_avg_sq[sl], u.grad_shard[sl], u.lp_shard[sl],
+                           lr=lrs.get(g.name, lrs["normal"]), betas=tuple(a.get("betas", (0.9, 0.999))),
+                           eps=a.get("eps", 1e-8),
+                           weight_decay=0.0 if g.name == "no_weight_decay" else a.get("weight_decay", 1e-2),
+                           step=e.step_count, gscale=None)
+        u.grad_scaled = True
+        if u.main_grad is None:
+            u.grad_shard_fresh = True       # the next reduction of this unit starts a new gradient
+        else:
+            for s in u.slots:
+                s.param.main_grad_stale = True
 
     @torch.no_grad()
     def step(self, total_sumsq: torch.Tensor | None = None) -> torch.Tensor:
         e = self.engine
         lrs = {g["name"]: g["lr"] for g in self.param_groups}
         a = self.class_args
+        if self.step_in_backward:
+            # every unit has stepped behind its reduction; join, republish the parameters, no norm to report
+            e.finish_backward()
+            if e.stage in (1, 2):
+                import torch.distributed as dist
+
+                for u in e.all_units:
+                    if u.world > 1:
+                        dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
+            e._cross_rank_fence()
+            e.prefetch_first_units()
+            e.grad_norm.zero_()
+            return e.grad_norm
         if self.fused:
             return e.clip_and_step(lr=lrs["normal"], lr_by_group=lrs, betas=tuple(a.get("betas", (0.9, 0.999))),
                                    eps=a.get("eps", 1e-8), weight_decay=a.get("weight_decay", 1e-2),
@@ -156,13 +206,12 @@ def get_optimizer_container(optimizer_class_name: str, optimizer_class_args: dic
                             params_group_method: ParamsGroupMethod | None,
                             use_optimizer_with_backward_hook: bool = False,
                             max_grad_norm: float | None = 1.0) -> OptimizerContainer:
-    if use_optimizer_with_backward_hook:
-        raise NotImplementedError("optimizer-in-backward is not supported by the sharded flat-buffer runtime")
     opts = []
     for wrapper in model_container:
         engine = wrapper.engine
         assert engine is not None, "wrap_model_container_for_distributed_training must run before the optimizer"
         opts.append(ShardedOptimizer(engine, optimizer_class_name, optimizer_class_args,
                                      getattr(wrapper.config, "m_width", None),
-                                     params_group_method == ParamsGroupMethod.mup, max_grad_norm))
+                                     params_group_method == ParamsGroupMethod.mup, max_grad_norm,
+                                     step_in_backward=use_optimizer_with_backward_hook))
     return OptimizerContainer(opts)

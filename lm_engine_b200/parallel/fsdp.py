@@ -61,7 +61,8 @@ class ShardedUnit:
     def __init__(self, name: str, modules: list[nn.Module], prefixes: list[str], device: torch.device,
                  compute_dtype: torch.dtype, grad_dtype: torch.dtype, shard_world: int, shard_rank: int,
                  shard_params: bool, shard_state: bool, use_mup_group: bool, group=None, replica_group=None,
-                 param_filter: Callable[[nn.Parameter], bool] | None = None, is_expert: bool = False) -> None:
+                 param_filter: Callable[[nn.Parameter], bool] | None = None, is_expert: bool = False,
+                 state_device: torch.device | None = None) -> None:
         self.name = name
         self.modules = modules
         # group that shards this unit (the data-parallel sharding group; for expert-parallel parameters the ranks
@@ -124,9 +125,12 @@ class ShardedUnit:
         self.state_hi = self.state_lo + (self.shard_size if self.shard_state else self.numel)
         # ---- storage
         n_state = self.state_hi - self.state_lo
-        self.master = torch.zeros(n_state, dtype=torch.float32, device=device)
-        self.exp_avg = torch.zeros(n_state, dtype=torch.float32, device=device)
-        self.exp_avg_sq = torch.zeros(n_state, dtype=torch.float32, device=device)
+        # optimizer state lives on `state_device` (pinned host memory with cpu_offload, else the compute device)
+        sdev = state_device or device
+        pin = sdev.type == "cpu" and device.type == "cuda"
+        self.master = torch.zeros(n_state, dtype=torch.float32, device=sdev, pin_memory=pin)
+        self.exp_avg = torch.zeros(n_state, dtype=torch.float32, device=sdev, pin_memory=pin)
+        self.exp_avg_sq = torch.zeros(n_state, dtype=torch.float32, device=sdev, pin_memory=pin)
         self.grad_shard: torch.Tensor | None = None   # reduced gradient of [state_lo, state_hi)
         if self.shard_params:
             self.lp_shard = torch.zeros(self.shard_size, dtype=compute_dtype, device=device)
@@ -237,9 +241,11 @@ class FSDPEngine:
                  compute_dtype: torch.dtype = torch.bfloat16, grad_dtype: torch.dtype | None = None,
                  device: torch.device | None = None, use_mup_group: bool = False,
                  checkpoint_units: set[str] | None = None, preserve_rng: bool = False,
-                 init_fn: Callable[[nn.Module], None] | None = None, seed: int = 0) -> None:
+                 init_fn: Callable[[nn.Module], None] | None = None, seed: int = 0,
+                 cpu_offload: bool = False) -> None:
         assert stage in (0, 1, 2, 3)
         self.model, self.stage = model, stage
+        self.cpu_offload = cpu_offload
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                                  else torch.device("cpu"))
         self.compute_dtype = compute_dtype
@@ -263,13 +269,14 @@ class FSDPEngine:
         def is_expert_param(p: nn.Parameter) -> bool:
             return self.ep_world > 1 and getattr(p, "ep_shard_dim", None) is not None
 
+        state_device = torch.device("cpu") if cpu_offload else None
         self.units: list[ShardedUnit] = []        # execution order (prefetch neighbours)
         self.all_units: list[ShardedUnit] = []    # + expert children, for everything that walks the state
         for name, modules, prefixes in units:
             u = ShardedUnit(name, modules, prefixes, self.device, compute_dtype, self.grad_dtype, self.world,
                             self.rank, shard_params=stage == 3, shard_state=stage >= 1, use_mup_group=use_mup_group,
                             group=self.shard_group, replica_group=self.replica_group,
-                            param_filter=lambda p: not is_expert_param(p))
+                            param_filter=lambda p: not is_expert_param(p), state_device=state_device)
             self.units.append(u)
             self.all_units.append(u)
             if any(is_expert_param(p) for m in modules for p in m.parameters()):
@@ -280,7 +287,7 @@ class FSDPEngine:
                                 shard_state=stage >= 1, use_mup_group=use_mup_group,
                                 group=edp_group if sharded else None,
                                 replica_group=edp_group if (not sharded and edp_world > 1) else None,
-                                param_filter=is_expert_param, is_expert=True)
+                                param_filter=is_expert_param, is_expert=True, state_device=state_device)
                 # every rank of the expert-parallel group adds the tokens it sent here, each weighted for the mean
                 # over its own micro-batch: the mean over all data-parallel ranks needs 1 / ep on top of the
                 # average over the ranks that replicate these experts
@@ -315,6 +322,7 @@ class FSDPEngine:
         self.step_count = 0
         self.micro_step = 0
         self.pipeline_mode = False   # several micro-batches in flight: reshard / reduce after every pass
+        self.post_reduce_hook: Callable[[ShardedUnit], None] | None = None   # optimizer-in-backward
         self._setup_grad_buffers()
         self._install_grad_hooks()
         self.copy_engine_gather = False
@@ -768,6 +776,8 @@ class FSDPEngine:
                     dist.all_reduce(s.param.main_grad, group=tp_group)
         if u.world == 1 and u.replica_group is None:
             u.grad_ready = True
+            if self.post_reduce_hook is not None and u.pending_backward <= 0:
+                self.post_reduce_hook(u)
             return
         full = u.main_grad
         for sl in u.slots:   # parameters that received no gradient in this pass
@@ -824,8 +834,12 @@ class FSDPEngine:
                     self._last_reduced_buf = full.data_ptr()
                 else:
                     self._buffer_events[full.data_ptr()] = u.rs_event
+                if self.post_reduce_hook is not None:
+                    self.post_reduce_hook(u)       # optimizer step of this unit, behind its reduction
         else:
             run()
+            if self.post_reduce_hook is not None:
+                self.post_reduce_hook(u)
         if self.stage != 0 and u.world > 1:
             u.main_grad = None
             for s in u.slots:
@@ -901,6 +915,11 @@ class FSDPEngine:
                 self.sumsq.add_(extra_sumsq)
         ops.clip_coef_(self.sumsq, max_grad_norm, self.grad_norm, self.clip_coef)
         lr_by_group = lr_by_group or {}
+        if self.cpu_offload and self.is_cuda:
+            self._offloaded_step(lr, lr_by_group, betas, eps, weight_decay)
+            self._cross_rank_fence()
+            self.prefetch_first_units()
+            return self.grad_norm
         for u in self.all_units:
             for g in u.local_group_ranges():
                 sl = slice(g.start, g.end)
@@ -913,6 +932,25 @@ class FSDPEngine:
         self._cross_rank_fence()
         self.prefetch_first_units()
         return self.grad_norm
+
+    def _offloaded_step(self, lr, lr_by_group, betas, eps, weight_decay) -> None:
+        """``cpu_offload`` (lm_engine/distributed.py:334,343 passes a CPUOffloadPolicy to FSDP-2): the fp32 master
+        weights and both moments stay in pinned host memory.  Per unit the reduced gradient shard is copied to the
+        host, AdamW runs there, and the refreshed low-precision shard is copied back.  Slow by construction (PCIe
+        and host arithmetic); meant for models whose optimizer state does not fit next to the activations."""
+        from ..ops.optimizer import adamw_reference
+
+        coef = float(self.clip_coef)                      # one read-back of the clip coefficient per step
+        for u in self.all_units:
+            g_host = u.grad_shard.to("cpu", non_blocking=False).float()
+            for g in u.local_group_ranges():
+                sl = slice(g.start, g.end)
+                adamw_reference(u.master[sl], u.exp_avg[sl], u.exp_avg_sq[sl], g_host[sl] * coef, None,
+                                lr_by_group.get(g.name, lr), betas[0], betas[1], eps,
+                                0.0 if g.name == "no_weight_decay" else weight_decay, self.step_count)
+            u.lp_shard.copy_(u.master, non_blocking=True)
+            if self.stage in (1, 2) and u.world > 1:
+                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
 
     def prefetch_first_units(self) -> None:
         """Starts the parameter gathers of the first units of the next forward pass right behind the optimizer step
@@ -991,6 +1029,8 @@ class FSDPEngine:
         """Full fp32 flat tensor of ``master`` / ``exp_avg`` / ``exp_avg_sq`` / ``grad`` on every rank."""
         t = which if isinstance(which, torch.Tensor) else {
             "master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq, "grad": u.grad_shard}[which]
+        if t.device != self.device:       # offloaded optimizer state
+            t = t.to(self.device)
         if not u.shard_state:
             return t.float().clone()
         out = torch.empty(u.numel, dtype=t.dtype, device=self.device)

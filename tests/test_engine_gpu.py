@@ -6,7 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(dtype):
+def _setup(dtype, cpu_offload=False, step_in_backward=False, max_grad_norm=1.0):
     from lm_engine_b200.distributed import shard_model
     from lm_engine_b200.enums import GradientCheckpointingMethod
     from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
@@ -18,9 +18,10 @@ def _setup(dtype):
     w = ModelWrapperForPretraining(pretrained_config=cfg.to_dict(), micro_batch_size=2, sequence_length=256,
                                    efficient_initialization=True, dtype="bf16")
     eng = shard_model(w, stage=3, dtype=dtype, communication_dtype=None,
-                      gradient_checkpointing_method=GradientCheckpointingMethod.block, seed=3)
+                      gradient_checkpointing_method=GradientCheckpointingMethod.block, seed=3,
+                      cpu_offload=cpu_offload)
     opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "eps": 1e-10},
-                           None, False, 1.0)
+                           None, False, max_grad_norm, step_in_backward=step_in_backward)
     return cfg, w, eng, opt
 
 
@@ -92,3 +93,35 @@ def test_bf16_training_tracks_fp32_reference():
     assert losses[-1] < losses[0] - 0.5, losses
     for a, b in zip(losses, ref_losses):
         assert abs(a - b) < 0.05 * max(1.0, b), (losses, ref_losses)
+
+
+def _run_steps(n, **kw):
+    cfg, w, eng, opt = _setup(torch.bfloat16, **kw)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    fixed = torch.randint(0, 2048, (2, 257), device="cuda", generator=g)
+    losses = []
+    for _ in range(n):
+        opt.zero_grad()
+        out = w(fixed, lm_loss_multiplier=1 / 512)
+        out["loss"].backward()
+        opt.step()
+        losses.append(float(out["loss"]))
+    return losses, eng
+
+
+def test_cpu_offloaded_optimizer_state_follows_the_device_step():
+    """`cpu_offload`: master weights and AdamW moments in pinned host memory, updated there; the trajectory is the
+    device one up to the rounding of the host arithmetic."""
+    base, _ = _run_steps(5)
+    off, eng = _run_steps(5, cpu_offload=True)
+    assert all(u.master.device.type == "cpu" and u.master.is_pinned() for u in eng.all_units)
+    for a, b in zip(off, base):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (off, base)
+
+
+def test_optimizer_in_backward_on_the_reduction_stream():
+    """Stepping each unit behind its gradient reduction (no clipping) equals the step after the backward pass."""
+    base, _ = _run_steps(5, max_grad_norm=None)
+    hooked, _ = _run_steps(5, max_grad_norm=None, step_in_backward=True)
+    for a, b in zip(hooked, base):
+        assert abs(a - b) < 1e-3 * max(1.0, abs(b)), (hooked, base)

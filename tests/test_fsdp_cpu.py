@@ -114,3 +114,51 @@ def test_fused_linear_cross_entropy_under_zero3(tied):
         assert abs(l0 - l1) < 1e-5
         for k in g0:
             assert np.allclose(g0[k], g1[k], atol=1e-6, rtol=1e-4), k
+
+
+def _in_backward_run(rank, world, in_backward):
+    import torch
+
+    from lm_engine_b200.distributed import shard_model
+    from lm_engine_b200.model_wrapper import ModelWrapperForPretraining
+    from lm_engine_b200.models import dense_config
+    from lm_engine_b200.optimization.optimizer import ShardedOptimizer
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    ProcessGroupManager(zero_stage=3)
+    cfg = dense_config(vocab_size=128, hidden_size=32, num_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                       intermediate_size=64, max_position_embeddings=16).to_dict()
+    w = ModelWrapperForPretraining(pretrained_config=cfg, micro_batch_size=2, sequence_length=16,
+                                   efficient_initialization=True)
+    eng = shard_model(w, stage=3, dtype=torch.float32, communication_dtype=None, seed=1)
+    opt = ShardedOptimizer(eng, "TorchAdamW", {"lr": 1e-2, "weight_decay": 0.1, "betas": [0.9, 0.95], "eps": 1e-8},
+                           None, False, None, step_in_backward=in_backward)
+    data = torch.randint(0, 128, (4, 2 * world, 17), generator=torch.Generator().manual_seed(3))
+    losses = []
+    for s in range(4):
+        opt.zero_grad()
+        out = w(data[s, 2 * rank:2 * rank + 2], lm_loss_multiplier=1 / 32)
+        out["loss"].backward()
+        opt.step()
+        losses.append(float(out["loss"].detach()))
+    return losses, {k: v.cpu().numpy().copy() for k, v in eng.full_state_dict().items()}
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_optimizer_in_backward_equals_step_after_backward(world):
+    """Without clipping, stepping every unit right behind its gradient reduction (the reference's
+    `use_optimizer_with_backward_hook`) gives the weights of the ordinary step after the whole backward pass."""
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    runs = []
+    for mode in (False, True):
+        if world == 1:
+            ProcessGroupManager.destroy_process_groups()
+            runs.append([_in_backward_run(0, 1, mode)])
+            ProcessGroupManager.destroy_process_groups()
+        else:
+            runs.append(run_distributed(_in_backward_run, world, mode))
+    for (la, pa), (lb, pb) in zip(*runs):
+        assert la == lb
+        for k in pa:
+            assert np.array_equal(pa[k], pb[k]), k
