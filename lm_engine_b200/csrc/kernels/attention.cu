@@ -44,6 +44,12 @@ struct Args {
     const int* cu_seqlens;     // packed sequences: tokens of sequence b are rows cu[b] .. cu[b+1]-1 (self-attention)
     int S_pad;                 // row pitch of lse: S_q, or the padded maximum length for packed sequences
     float scale;               // softmax scale (natural units)
+    // K / V rows that arrive while the kernel runs (context parallelism: the peers' key / value chunks are copied
+    // into this GPU's K / V buffers by copy engines, and the stream writes kv_seq into one word per chunk once a
+    // chunk is complete).  The producer waits (bounded) for the word of a tile's chunk before loading the tile;
+    // chunk = key row / kv_chunk_rows (a multiple of 64), one set of words per batch entry.  null: no waiting.
+    const int* kv_ready;
+    int kv_chunk_rows, kv_chunks, kv_seq;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -132,8 +138,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_expect_tx(q_full, Q_BYTES);
             tma_load_2d(smem + OFF_Q, &tmQ, q_full, h * HD, row_q);
             tma_load_2d(smem + OFF_Q + Q_HALF, &tmQ, q_full, h * HD + 64, row_q);
+            int chunk_seen = -1;    // K / V chunks up to this one have been waited for (tiles run in key order)
+            auto wait_chunk = [&](int j) -> bool {
+                if (p.kv_ready == nullptr) return true;
+                const int c = ((j_begin + j) * BN) / p.kv_chunk_rows;
+                if (c <= chunk_seen) return true;
+                for (int cc = max(chunk_seen + 1, (j_begin * BN) / p.kv_chunk_rows); cc <= c; ++cc)
+                    // the word follows a peer's progress: the limit of the cross-GPU waits applies
+                    if (!wait_flag_sys(&p.kv_ready[b * p.kv_chunks + cc], p.kv_seq, 650)) return false;
+                fence_proxy_async_all();   // the TMA (async proxy) loads below are ordered after the acquire
+                chunk_seen = c;
+                return true;
+            };
             auto load_k = [&](int j) -> bool {
                 const int s = j & 1;
+                if (!wait_chunk(j)) return false;
                 if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) return false;
                 uint8_t* ks = smem + OFF_K + s * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
@@ -338,10 +357,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // with the last key; window > 0 (causal only) keeps the last `window` visible keys of every query.
 // Packed sequences: cu_seqlens (int32 [B + 1], device) with q / k / v / o as [total_tokens, H, 128], S_q = S_kv = the
 // longest sequence and lse [B, Hq, S_pad], S_pad = S_q rounded up to 128.
+// kv_ready != null: K / V chunks of kv_chunk_rows rows (a multiple of 64) become valid while the kernel runs; word
+// [b * chunks + c] of kv_ready holds kv_seq once chunk c of batch entry b is complete (see Args).
 extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                                  long long ldv, void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq,
                                  int Hkv, int causal, int window, float scale, const int* cu_seqlens,
-                                 long long total_tokens, void* stream) {
+                                 long long total_tokens, const int* kv_ready, int kv_chunk_rows, int kv_seq,
+                                 void* stream) {
     using lme::attn::Args;
     using lme::attn::HD;
     using lme::attn::SMEM_BYTES;
@@ -352,6 +374,7 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     if (cu_seqlens ? (S_q != S_kv || total_tokens <= 0) : (S_q % BM || S_kv % BM)) return LME_ERR_SHAPE;
     if (causal && S_kv < S_q) return LME_ERR_SHAPE;
     if (window < 0 || (window > 0 && !causal)) return LME_ERR_SHAPE;
+    if (kv_ready != nullptr && (cu_seqlens != nullptr || kv_chunk_rows <= 0 || kv_chunk_rows % BN)) return LME_ERR_SHAPE;
     if (B > 65535 || Hq > 65535 || (S_q + BM - 1) / BM > 65535) return LME_ERR_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(o)) & 15)
@@ -381,6 +404,10 @@ extern "C" int lme_attention_fwd(const void* q, long long ldq, const void* k, lo
     p.cu_seqlens = cu_seqlens;
     p.S_pad = (S_q + BM - 1) / BM * BM;
     p.scale = scale;
+    p.kv_ready = kv_ready;
+    p.kv_chunk_rows = kv_ready ? kv_chunk_rows : 1;
+    p.kv_chunks = kv_ready ? (S_kv + kv_chunk_rows - 1) / kv_chunk_rows : 0;
+    p.kv_seq = kv_seq;
     dim3 grid(static_cast<unsigned>(Hq) * B, (S_q + BM - 1) / BM, 1);
     attn_fwd_kernel<<<grid, 192, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;

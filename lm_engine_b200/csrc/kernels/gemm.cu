@@ -1043,6 +1043,27 @@ extern "C" int lme_stream_write_words(int* words, int count, int value, void* st
     return LME_OK;
 }
 
+// Holds `stream` until *word >= value (a stream memory operation: no kernel, so it needs no SM while other kernels
+// of this GPU wait for what the stream delivers afterwards).  Not bounded by itself: the kernels that consume the
+// delivery have bounded waits and report a missing peer through the status block.
+typedef CUresult (*WaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+extern "C" int lme_stream_wait_word(const int* word, int value, void* stream) {
+    static WaitValue32Fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<WaitValue32Fn>(f);
+    });
+    if (!fn) return LME_ERR_DRIVER;
+    return fn(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(word), static_cast<cuuint32_t>(value),
+              CU_STREAM_WAIT_VALUE_GEQ) == CUDA_SUCCESS
+               ? LME_OK
+               : LME_ERR_LAUNCH;
+}
+
 extern "C" int lme_read_status(unsigned int* out8, int clear) {
     unsigned int h[8];
     if (cudaMemcpyFromSymbol(h, lme_status, sizeof(h)) != cudaSuccess) return LME_ERR_LAUNCH;

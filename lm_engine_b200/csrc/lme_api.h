@@ -78,6 +78,8 @@ int lme_gemm_bf16_allgather_a(void* A_gathered, long long lda, const void* B, in
 int lme_gather_signal(int* const* pads, int rank, int world, int seq, void* stream);
 int lme_gather_wait_peer(const int* pad, int src, int seq, void* stream);
 int lme_stream_write_words(int* words, int count, int value, void* stream);
+// holds the stream until *word >= value (stream memory operation, takes no SM; not bounded by itself)
+int lme_stream_wait_word(const int* word, int value, void* stream);
 
 // Reduce-scatter fused into the GEMM epilogue: out[M / world, N] = sum over ranks of (A * B^T)[rows of this rank]
 // (+ bias) (+ residual).  Tiles of a peer's rows are stored into that peer's receive slab over NVLink with an
@@ -205,9 +207,13 @@ int lme_unpack_rows(const void* packed, const int* cu_seqlens, void* x, int B, i
 // scale multiplies q.k before the softmax.  Packed sequences: cu_seqlens (int32 [B+1], device) with q / k / v / o
 // as [total_tokens, H, 128], S_q = S_kv = the longest sequence (any lengths), lse [B,Hq,S_pad], S_pad = S_q rounded
 // up to 128; cu_seqlens null = batches.
+// kv_ready != null (batches only): chunks of kv_chunk_rows key / value rows (a multiple of 64) become valid while the
+// kernel runs - word [b * chunks + c] of kv_ready holds kv_seq once chunk c of batch entry b is complete (written by
+// the stream that copied it in); the kernel's loader waits, bounded, for the word of a tile's chunk.
 int lme_attention_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
                       void* o, long long ldo, float* lse, int B, int S_q, int S_kv, int Hq, int Hkv, int causal,
-                      int window, float scale, const int* cu_seqlens, long long total_tokens, void* stream);
+                      int window, float scale, const int* cu_seqlens, long long total_tokens, const int* kv_ready,
+                      int kv_chunk_rows, int kv_seq, void* stream);
 
 // Gradients of lme_attention_fwd (kernels/attention_bwd.cu; two kernels, no atomics, deterministic).  dout and out
 // laid out like q; lse fp32 [B,Hq,S_q]; delta fp32 scratch of that shape (receives rowsum(dout * out));

@@ -156,6 +156,13 @@ class SoftmaxAttention(nn.Module):
             if how == "ulysses" or (how == "auto" and ulysses_eligible(q.size(-2), k.size(-2), cp)):
                 return ulysses_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
                                          sliding_window=self._attended_keys, dropout_p=dropout)
+            from ...parallel import gathered_attention as gathered
+
+            method = ProcessGroupManager.get_context_parallel_load_balancing_method()
+            if how in ("auto", "gathered") and dropout == 0 and gathered.eligible(q, k, self.causal,
+                                                                                  self._attended_keys, method):
+                # the K / V exchange runs inside the attention kernel (copy engines + readiness words)
+                return gathered.gathered_kv_attention(q, k, v, softmax_scale=self.attention_multiplier)
             return ring_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
                                   sliding_window=self._attended_keys)
         if packed:

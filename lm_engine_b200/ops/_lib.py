@@ -62,6 +62,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_gather_signal": [P, I, I, I, P],
             "lme_gather_wait_peer": [P, I, I, P],
             "lme_stream_write_words": [P, I, I, P],
+            "lme_stream_wait_word": [P, I, P],
             "lme_gemm_bf16_reduce_scatter": [P, L, P, I, L, P, L, I, I, I, P, P, L, P, P, I, I, I, I, P],
             "lme_gemm_bf16_grouped": [P, L, P, I, L, P, L, I, I, I, I, I, P, L, P, I, P],
             "lme_gemm_bf16_grouped_wgrad": [P, L, P, L, P, L, I, I, I, I, P, P, I, I, P],
@@ -83,7 +84,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_gemm_bf16_batched": [P, I, L, L, P, I, L, L, P, L, L, I, I, I, I, I, I, P],
             "lme_m2rnn": [P, I, P],
             "lme_rnn": [P, I, P],
-            "lme_attention_fwd": [P, L, P, L, P, L, P, L, P, I, I, I, I, I, I, I, F, P, L, P],
+            "lme_attention_fwd": [P, L, P, L, P, L, P, L, P, I, I, I, I, I, I, I, F, P, L, P, I, I, P],
             "lme_attention_bwd": [P, L, P, L, P, L, P, L, P, L, P, P, P, L, P, L, P, L, I, I, I, I, I, I, I, F, P, L, P],
             "lme_embedding_fwd": [P, P, P, L, I, L, L, P],
             "lme_embedding_bwd": [P, P, P, P, L, I, L, L, P],

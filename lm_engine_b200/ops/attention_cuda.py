@@ -83,9 +83,11 @@ def _padded(n: int) -> int:
 
 def flash_attention_forward(q, k, v, *, causal: bool, softmax_scale: float, return_lse: bool = False,
                             sliding_window: int | None = None, cu_seqlens: torch.Tensor | None = None,
-                            max_seqlen: int | None = None):
+                            max_seqlen: int | None = None, kv_ready: torch.Tensor | None = None,
+                            kv_chunk_rows: int = 0, kv_seq: int = 0):
     """Batches ``[B, S, H, 128]``, or packed sequences ``[T, H, 128]`` with ``cu_seqlens`` (then the log-sum-exp is
-    ``[sequences, Hq, padded max length]``)."""
+    ``[sequences, Hq, padded max length]``).  ``kv_ready`` (int32 ``[B, chunks]``): chunks of ``kv_chunk_rows`` key /
+    value rows are still arriving; the kernel waits for ``kv_seq`` in a chunk's word before it loads from it."""
     packed = cu_seqlens is not None
     if packed:
         cu = cu_seqlens.to(torch.int32).contiguous()
@@ -106,7 +108,8 @@ def flash_attention_forward(q, k, v, *, causal: bool, softmax_scale: float, retu
     _lib.check(_lib.cuda_lib().lme_attention_fwd(q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(),
                                                  v.stride(1), out.data_ptr(), Hq * D, _lib.ptr(lse), B, Sq, Skv, Hq,
                                                  Hkv, int(causal), int(sliding_window or 0), float(softmax_scale),
-                                                 _lib.ptr(cu), T, _lib.stream_ptr()),
+                                                 _lib.ptr(cu), T, _lib.ptr(kv_ready), int(kv_chunk_rows),
+                                                 int(kv_seq), _lib.stream_ptr()),
                f"lme_attention_fwd B={B} Sq={Sq} Skv={Skv} Hq={Hq} Hkv={Hkv} packed={packed}")
     _lib.count_launch()
     return (out, lse) if return_lse else out

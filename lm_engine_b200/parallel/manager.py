@@ -66,7 +66,9 @@ class ProcessGroupManager:
         world = int(os.environ.get("WORLD_SIZE", "1"))
         _S.rank, _S.local_rank = rank, local_rank
         _S.cp_lb = context_parallel_load_balancing_method
-        assert context_parallel_attention in ("auto", "ring", "ulysses")
+        # "gathered": K / V exchange inside the attention kernel; "ring": blocks around a ring; "ulysses": head
+        # exchange; "auto": ulysses when the heads divide, else gathered when the kernel takes the shapes, else ring
+        assert context_parallel_attention in ("auto", "ring", "ulysses", "gathered")
         _S.cp_attention = context_parallel_attention
         _S.async_tp = use_async_tensor_parallel
         Accelerator.set_device(local_rank)

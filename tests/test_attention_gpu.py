@@ -218,3 +218,25 @@ def test_ring_attention_blocks_on_kernels_match_block_math(method):
             g_r = ra.block_attention_backward(*args, pos[r], pos[src], scale, True, None)
             for a, b in zip(g_k, g_r):
                 assert float((a - b).norm() / (b.norm() + 1e-6)) < 2e-2
+
+
+def test_forward_waits_for_chunk_readiness_words():
+    """Keys / values that "arrive" in chunks: with every chunk's word already at the sequence number the kernel gives
+    the plain result; the words are only read (no other launch is waited for)."""
+    from lm_engine_b200.ops import _lib
+    from lm_engine_b200.ops.attention import attention_reference
+    from lm_engine_b200.ops.attention_cuda import flash_attention_forward
+
+    g = torch.Generator(device="cuda").manual_seed(4)
+    B, Sq, Skv, Hq, Hkv = 1, 256, 768, 4, 2
+    q = torch.randn(B, Sq, Hq, 128, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Skv, Hkv, 128, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Skv, Hkv, 128, device="cuda", generator=g).to(torch.bfloat16)
+    ready = torch.full((B, 3), 7, dtype=torch.int32, device="cuda")       # 3 chunks of 256 rows, all announced
+    out, lse = flash_attention_forward(q, k, v, causal=True, softmax_scale=128 ** -0.5, return_lse=True,
+                                       kv_ready=ready[0], kv_chunk_rows=256, kv_seq=7)
+    ref, ref_lse = attention_reference(q, k, v, causal=True, softmax_scale=128 ** -0.5, return_lse=True)
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    assert float((out.float() - ref.float()).norm() / ref.float().norm()) < 1e-2
+    assert torch.allclose(lse, ref_lse.transpose(1, 2), atol=2e-2, rtol=1e-3)

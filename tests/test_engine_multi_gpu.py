@@ -228,13 +228,25 @@ def _cp_attention_worker(rank, world, port, q, method, algo):
         ref.backward(do)
         idx = shard_indices(S, world, rank, method, device="cuda")
         loc = [t[:, idx].clone().requires_grad_() for t in (q_, k_, v_)]
-        out = (ulysses_attention if algo == "ulysses" else ring_attention)(*loc, causal=True)
+        if algo == "gathered":
+            from lm_engine_b200.parallel.gathered_attention import eligible, gathered_kv_attention
+
+            assert eligible(loc[0], loc[1], True, None, method)
+            out = gathered_kv_attention(*loc)
+            out.backward(do[:, idx])
+            loc = [t.detach().clone().requires_grad_() for t in loc]      # a second call: slots and sequence numbers
+            out = gathered_kv_attention(*loc)
+        else:
+            out = (ulysses_attention if algo == "ulysses" else ring_attention)(*loc, causal=True)
         out.backward(do[:, idx])
         torch.cuda.synchronize()
         def rel(a, b):
             return float((a.detach().float() - b.detach().float()).norm() / (b.detach().float().norm() + 1e-6))
 
+        from lm_engine_b200.ops import _lib
+
         err = [rel(out, ref[:, idx])] + [rel(a.grad, b.grad[:, idx]) for a, b in zip(loc, full)]
+        err.append(float(_lib.read_status()[0]))
         q.put((rank, "ok", err))
         dist.barrier()
     except Exception:  # noqa: BLE001
@@ -250,10 +262,12 @@ def _cp_attention_worker(rank, world, port, q, method, algo):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("method", [None, "headtail"])
-@pytest.mark.parametrize("algo", ["ulysses", "ring"])
+@pytest.mark.parametrize("algo", ["ulysses", "ring", "gathered"])
 def test_context_parallel_attention_two_gpus(method, algo):
-    """Head-exchange and ring attention (the latter on the tcgen05 block kernels: 512 tokens split 2 ways gives
-    runs of 256 / 128 rows) against single-GPU attention, outputs and gradients."""
+    """Head-exchange, ring attention (on the tcgen05 block kernels: 512 tokens split 2 ways gives runs of 256 / 128
+    rows) and the gathered form (K / V chunks arrive by copy engines while ONE attention launch per query run waits
+    for their readiness words; dK / dV summed by the peer-load reduce-scatter kernel) against single-GPU attention,
+    outputs and gradients."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _port()
@@ -264,7 +278,8 @@ def test_context_parallel_attention_two_gpus(method, algo):
         for _ in range(2):
             rank, status, payload = q.get(timeout=300)
             assert status == "ok", payload
-            assert max(payload) < 2e-2, payload     # relative error of the output and of dq, dk, dv
+            assert payload[-1] == 0, payload        # no bounded wait expired
+            assert max(payload[:-1]) < 2e-2, payload     # relative error of the output and of dq, dk, dv
     finally:
         for p in procs:
             p.join(timeout=30)
