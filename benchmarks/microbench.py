@@ -363,6 +363,8 @@ def main():
                   f"quantize(+transpose) {r['quantize_ms']:7.3f} ms {r['quantize_gbs']:6.0f} GB/s", flush=True)
     st = _lib.read_status()
     print("device status:", st)
+    if args.impl == "2cta":
+        print("resident CTA pairs of the 2-CTA grid:", _lib.cuda_lib().lme_gemm_2cta_resident_pairs())
     if args.json:
         json.dump({"peaks": peaks, "gemm": rows, "status": st}, open(args.json, "w"), indent=1)
 

@@ -259,6 +259,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
 }
 
+static int g_last_max_clusters = -1;   // what the occupancy query said for the last 2-CTA launch (diagnostics)
+
 template <int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& p, int max_ctas,
                             cudaStream_t stream) {
@@ -279,6 +281,7 @@ static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, GemmAr
         }
         max_clusters = n;
     }
+    g_last_max_clusters = max_clusters;
     p.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
     p.tiles_n = (p.N + BN2 - 1) / BN2;
     p.group_m = 4;
@@ -292,6 +295,10 @@ static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, GemmAr
 }  // namespace lme
 
 using namespace lme;
+
+// Number of CTA pairs that can be resident at once according to cudaOccupancyMaxActiveClusters (-1 before the first
+// 2-CTA launch): the persistent grid of lme_gemm_bf16_2cta is that many pairs.
+extern "C" int lme_gemm_2cta_resident_pairs() { return lme::g_last_max_clusters; }
 
 // Same contract as lme_gemm_bf16; N <= 128 is forwarded to the one-SM kernel.
 extern "C" int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, const void* B, int b_mn_major,

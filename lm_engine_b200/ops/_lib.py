@@ -81,6 +81,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_ssd_combine": [P, P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
             "lme_ssd_boundary_fwd": [P, P, P, P, P, P, I, I, I, I, P],
             "lme_ssd_boundary_bwd": [P, P, P, P, P, P, P, I, I, I, I, P],
+            "lme_gemm_2cta_resident_pairs": [],
             "lme_gemm_bf16_batched": [P, I, L, L, P, I, L, L, P, L, L, I, I, I, I, I, I, P],
             "lme_m2rnn": [P, I, P],
             "lme_rnn": [P, I, P],

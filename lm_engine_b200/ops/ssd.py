@@ -184,8 +184,7 @@ class _BoundaryScan(torch.autograd.Function):
         states, decay = states.contiguous(), decay.contiguous()
         h_init = None if h_init is None else h_init.float().contiguous()
         h0 = torch.empty((b, nc, N, P, Sd), dtype=torch.bfloat16, device=states.device)
-        keep = torch.is_grad_enabled() and (states.requires_grad or decay.requires_grad
-                                            or (h_init is not None and h_init.requires_grad))
+        keep = any(ctx.needs_input_grad)      # the backward pass walks the fp32 states
         h0f = torch.empty((b, nc, N, P, Sd), dtype=torch.float32, device=states.device) if keep else None
         hf = torch.empty((b, N, P, Sd), dtype=torch.float32, device=states.device)
         _lib.check(_lib.cuda_lib().lme_ssd_boundary_fwd(states.data_ptr(), decay.data_ptr(), _lib.ptr(h_init),

@@ -58,7 +58,8 @@ def test_boundary_scan_matches_loop(with_init):
     decay = (torch.rand(b, nc, N, device="cuda", generator=g) * 0.9 + 0.05).requires_grad_(True)
     init = torch.randn(b, N, P, Sd, device="cuda", generator=g, requires_grad=True) if with_init else None
     h0, hf = _BoundaryScan.apply(states, decay, init)
-    w0 = torch.randn(h0.shape, device="cuda", generator=g)
+    # h0 is a bf16 output, so autograd hands its gradient over in bf16: use weights that bf16 represents exactly
+    w0 = torch.randn(h0.shape, device="cuda", generator=g).to(torch.bfloat16).float()
     wf = torch.randn(hf.shape, device="cuda", generator=g)
     ((h0.float() * w0).sum() + (hf * wf).sum()).backward()
     got = [states.grad.clone(), decay.grad.clone(), None if init is None else init.grad.clone()]
