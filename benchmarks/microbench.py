@@ -301,7 +301,7 @@ def main():
     ap.add_argument("--elementwise", action="store_true", help="time the bandwidth-bound kernels instead")
     ap.add_argument("--small", action="store_true", help="smaller operand pools (profiler captures)")
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
-    ap.add_argument("--probe", default=None, choices=["noload", "nomma"],
+    ap.add_argument("--probe", default=None, choices=["noload", "nomma", "mmaonly", "mmacommit"],
                     help="GEMM timing probe: skip the operand loads (tensor-pipe ceiling) or the MMAs (load ceiling)")
     args = ap.parse_args()
     peaks = _peaks()
@@ -345,7 +345,7 @@ def main():
     rows = []
     for name, M, N, K, a_mn, b_mn, kw in shapes:
         r = bench_gemm(M, N, K, a_mn, b_mn, sustained=args.sustained, impl=args.impl,
-                       probe={"noload": 64, "nomma": 128, None: 0}[args.probe], **kw)
+                       probe={"noload": 64, "nomma": 128, "mmaonly": 256, "mmacommit": 512, None: 0}[args.probe], **kw)
         r["name"] = name
         r["frac_of_peak"] = r["tflops"] / peaks["bf16_tflops_sustained" if args.sustained else "bf16_tflops"]
         rows.append(r)

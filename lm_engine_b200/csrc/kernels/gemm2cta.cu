@@ -60,6 +60,16 @@ __device__ __forceinline__ void umma_commit_2cta(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
                  : "memory");
 }
+// the same arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, from one instruction (a
+// signal multicast, no data moves): the two separate commits it replaces each held up the issuing thread
+__device__ __forceinline__ void umma_commit_2cta_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"(mask)
+        : "memory");
+}
 // per-CTA tile load whose completion is counted on a barrier that may live in the pair's other CTA
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
                                                  int x, int y) {
@@ -135,6 +145,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             uint32_t it = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                if (p.flags & 768) break;   // timing probes without stage hand-over: nothing to produce
                 int mb2, nb;
                 tile_coords(tile, p, mb2, nb);
                 const int m0 = (mb2 * 2 + static_cast<int>(rank)) * BM;
@@ -185,7 +196,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(&full_bar[s], ph, 1300 + s)) { ok = false; break; }
+                    // probes 256 / 512: MMAs on whatever the stage holds, no full-barrier wait (512: but with the
+                    // per-stage commit, which then signals barriers nobody waits for)
+                    if (!(p.flags & 768) && !mbar_wait(&full_bar[s], ph, 1300 + s)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
                     const uint32_t sb = sa + L::A_BYTES;
@@ -203,13 +216,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         umma_bf16_2cta(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
                     }
                     // the stage is free in both CTAs once these MMAs have read it
-                    umma_commit_2cta(smem_u32(&empty_bar[s]));
-                    umma_commit_2cta(map_to_cta(&empty_bar[s], 1));
+                    if (!(p.flags & 256)) umma_commit_2cta_pair(&empty_bar[s]);
                 }
-                if (ok) {
-                    umma_commit_2cta(smem_u32(&tfull_bar[acc]));
-                    umma_commit_2cta(map_to_cta(&tfull_bar[acc], 1));
-                }
+                if (ok) umma_commit_2cta_pair(&tfull_bar[acc]);
             }
         }
         __syncwarp();
@@ -284,7 +293,8 @@ static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, GemmAr
     g_last_max_clusters = max_clusters;
     p.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
     p.tiles_n = (p.N + BN2 - 1) / BN2;
-    p.group_m = 4;
+    static const int group_m_env = [] { const char* e = getenv("LME_GEMM2_GROUP_M"); return e ? atoi(e) : 0; }();
+    p.group_m = group_m_env > 0 ? group_m_env : 4;
     int tiles = p.tiles_m * p.tiles_n;
     int clusters = tiles < max_clusters ? tiles : max_clusters;
     if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
@@ -328,8 +338,11 @@ extern "C" int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, 
     p.preact = static_cast<__nv_bfloat16*>(preact); p.ldp = ldp;
     p.flags = flags;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    static const int stages_env = [] { const char* e = getenv("LME_GEMM2_STAGES"); return e ? atoi(e) : 6; }();
     if (a_mn_major && b_mn_major) return launch_gemm_2cta<6, true, true>(ta, tb, p, max_ctas, st);
     if (a_mn_major) return launch_gemm_2cta<6, true, false>(ta, tb, p, max_ctas, st);
     if (b_mn_major) return launch_gemm_2cta<6, false, true>(ta, tb, p, max_ctas, st);
+    if (stages_env == 7) return launch_gemm_2cta<7, false, false>(ta, tb, p, max_ctas, st);
+    if (stages_env == 4) return launch_gemm_2cta<4, false, false>(ta, tb, p, max_ctas, st);
     return launch_gemm_2cta<6, false, false>(ta, tb, p, max_ctas, st);
 }

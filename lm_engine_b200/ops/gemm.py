@@ -131,7 +131,7 @@ def gemm(
         raise ValueError("gemm: out must be a row-major [M, N] tensor")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise TypeError("gemm: out must be bf16 or fp32")
-    flags = int(probe) & 192
+    flags = int(probe) & 960
     if out.dtype == torch.float32:
         flags |= _lib.GEMM_OUT_F32
     if accumulate:

@@ -5,10 +5,14 @@ the same modules with ``fully_shard``, lm_engine/distributed.py:303-385).  Per u
 
 * ``flat_param``  compute-dtype (bf16) buffer holding every parameter of the unit back to back, ordered by optimizer
   group; module parameters are views into it.  ZeRO-3 keeps only this rank's slice between uses and all-gathers the
-  rest into one of two rotating buffers just before the unit runs (next unit prefetched on a side stream).
+  rest into one of three rotating buffers just before the unit runs (the next unit - and the one behind it when the
+  next is a lone norm - is prefetched on a side stream by copy engines out of symmetric memory; the first units of a
+  step are prefetched right behind the optimizer step).
 * ``main_grad``   gradient buffer of the same layout.  The wgrad GEMM epilogue accumulates straight into it (see
   :mod:`lm_engine_b200.ops.gemm`); other parameters' ``.grad`` are folded in by a hook.  After the unit's backward it
-  is reduce-scattered (all-reduced for ZeRO-0) on a side stream, overlapped with the backward of the next unit.
+  is reduce-scattered on a side stream, overlapped with the backward of the next unit: by ONE kernel of this
+  library that reads the peers' buffers over NVLink, averages in fp32, writes the shard and leaves the partial sums
+  of squares of the gradient norm (csrc/kernels/reduce_scatter.cu), or by NCCL (HSDP, expert units, ZeRO-0).
 * ``master / exp_avg / exp_avg_sq``  fp32 shards, updated by one fused AdamW launch per optimizer group that also
   refreshes the bf16 slice; the squared gradient norm is reduced on the device and the clip coefficient is read by
   the AdamW kernel from device memory, so a step never synchronises with the host.
