@@ -100,6 +100,28 @@ def _to_dtensor(engine, local_full: torch.Tensor, param: torch.nn.Parameter) -> 
     return local_full.clone()
 
 
+def _chunk_dtensor(engine, chunk: torch.Tensor, param: torch.nn.Parameter, shape: torch.Size) -> torch.Tensor:
+    """``Shard(0)`` DTensor over the sharding group from this rank's block of rows (see ``FSDPEngine.row_chunks``)."""
+    mesh = ProcessGroupManager.get_device_mesh("fsdp")
+    stride = torch.empty(shape, device="meta").stride()
+    return DTensor.from_local(chunk.contiguous(), mesh, [Shard(0)], run_check=False, shape=shape, stride=stride)
+
+
+def _unit_state_tensors(eng, u, which) -> dict[str, torch.Tensor]:
+    """Checkpoint-layout tensors (name -> DTensor / tensor) of one unit's state ``which``: row blocks exchanged
+    point to point where the layout allows it, else cut from the gathered unit."""
+    out = {}
+    if eng.can_exchange_row_chunks(u) and all(len(s.shape) >= 1 for s in u.slots):
+        chunks = eng.row_chunks(u, which)
+        for s in u.slots:
+            out[s.name] = _chunk_dtensor(eng, chunks[s.name], s.param, s.shape)
+        return out
+    full = eng.gather_full(u, which)
+    for s in u.slots:
+        out[s.name] = _to_dtensor(eng, eng._slot_full(s, full[s.offset:s.offset + s.numel].view(s.shape)), s.param)
+    return out
+
+
 def _from_saved(value: torch.Tensor, engine) -> torch.Tensor:
     """Inverse of :func:`_to_dtensor`: the full per-TP-rank tensor."""
     if isinstance(value, DTensor):
@@ -120,10 +142,8 @@ def model_state_dict(model_container: ModelContainer, which: str = "master") -> 
                 out[f"model.{k}"] = v
             continue
         for u in eng.all_units:
-            full = eng.gather_full(u, which)
-            for s in u.slots:
-                out[f"model.{s.name}"] = _to_dtensor(
-                    eng, eng._slot_full(s, full[s.offset:s.offset + s.numel].view(s.shape)), s.param)
+            for name, t in _unit_state_tensors(eng, u, which).items():
+                out[f"model.{name}"] = t
     return out
 
 
@@ -186,12 +206,11 @@ def optimizer_state_dict(model_container: ModelContainer, optimizer_container: O
             keys = sorted(set(keys) | saved_names[0])
             scalars = {**{k: 0.0 for k in saved_names[1]}, **scalars}
         for u in eng.all_units:
-            fulls = {k: eng.gather_full(u, k if fused else opt.unit_state(u, k)) for k in keys}
+            states = {k: _unit_state_tensors(eng, u, k if fused else opt.unit_state(u, k)) for k in keys}
             for s in u.slots:
                 fqn = f"model.{s.name}"
-                sl = slice(s.offset, s.offset + s.numel)
-                for k, full in fulls.items():
-                    out[f"state.{fqn}.{k}"] = _to_dtensor(eng, eng._slot_full(s, full[sl].view(s.shape)), s.param)
+                for k, by_name in states.items():
+                    out[f"state.{fqn}.{k}"] = by_name[s.name]
                 for k, v in scalars.items():
                     out[f"state.{fqn}.{k}"] = torch.tensor(v)
                 g = groups.get(s.group, groups["normal"])

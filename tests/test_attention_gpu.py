@@ -240,3 +240,68 @@ def test_forward_waits_for_chunk_readiness_words():
     assert _lib.read_status()[0] == 0
     assert float((out.float() - ref.float()).norm() / ref.float().norm()) < 1e-2
     assert torch.allclose(lse, ref_lse.transpose(1, 2), atol=2e-2, rtol=1e-3)
+
+
+def _fp32_attention_by_head_groups(q, k, v, causal, scale, do=None):
+    """fp32 oracle at large shapes: one K/V head (and its query heads) at a time so that the score matrices fit."""
+    B, S, Hq, D = q.shape
+    Hkv = k.size(2)
+    G = Hq // Hkv
+    outs, grads = [], []
+    for h in range(Hkv):
+        qh = q[:, :, h * G:(h + 1) * G].float().requires_grad_(do is not None)
+        kh = k[:, :, h:h + 1].float().requires_grad_(do is not None)
+        vh = v[:, :, h:h + 1].float().requires_grad_(do is not None)
+        from lm_engine_b200.ops.attention import attention_reference
+
+        o = attention_reference(qh, kh, vh, causal=causal, softmax_scale=scale)
+        if do is not None:
+            o.backward(do[:, :, h * G:(h + 1) * G].float())
+            grads.append((qh.grad, kh.grad, vh.grad))
+        outs.append(o.detach())
+    out = torch.cat(outs, dim=2)
+    if do is None:
+        return out, None
+    return out, tuple(torch.cat([g[i] for g in grads], dim=2) for i in range(3))
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(2, 4096, 32, 8), (1, 16384, 8, 2)])
+def test_attention_at_training_shapes(B, S, Hq, Hkv):
+    """The Llama-3-8B attention shape (more query blocks than one wave of CTAs, so the longest-first block order and
+    the second wave are exercised) and a 16k sequence, forward and backward against the fp32 statement."""
+    from lm_engine_b200.ops import _lib
+    from lm_engine_b200.ops.attention_cuda import _FlashAttention
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    D, scale = 128, 128 ** -0.5
+    q, k, v = (torch.randn(B, S, h, D, device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+               for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, D, device="cuda", generator=g).to(torch.bfloat16)
+    out = _FlashAttention.apply(q, k, v, True, scale)
+    out.backward(do)
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    ref, (dq, dk, dv) = _fp32_attention_by_head_groups(q.detach(), k.detach(), v.detach(), True, scale, do)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-9))
+
+    assert rel(out, ref) < 1e-2
+    assert rel(q.grad, dq) < 2e-2 and rel(k.grad, dk) < 2e-2 and rel(v.grad, dv) < 2e-2
+
+
+def test_attention_kernels_are_deterministic():
+    """No atomics anywhere: two runs on the same inputs give the same bits, forward and backward."""
+    from lm_engine_b200.ops.attention_cuda import _FlashAttention
+
+    g = torch.Generator(device="cuda").manual_seed(12)
+    q, k, v = (torch.randn(2, 1024, h, 128, device="cuda", generator=g).to(torch.bfloat16) for h in (8, 2, 2))
+    do = torch.randn(2, 1024, 8, 128, device="cuda", generator=g).to(torch.bfloat16)
+    runs = []
+    for _ in range(2):
+        a, b, c = (t.clone().requires_grad_(True) for t in (q, k, v))
+        out = _FlashAttention.apply(a, b, c, True, 128 ** -0.5)
+        out.backward(do)
+        runs.append((out.detach(), a.grad, b.grad, c.grad))
+    for x, y in zip(*runs):
+        assert torch.equal(x, y)
