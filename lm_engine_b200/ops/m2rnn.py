@@ -95,7 +95,7 @@ class _M2RNN(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, dh_out):
-        from .ssd import _bmm_f32
+        from .gemm import _bmm_kernel
 
         q, k, v, f32, Wb, ckpt = ctx.saved_tensors
         N, seg, clip, has_h0, f_dtype, W_dtype, h0_dtype = ctx.meta
@@ -129,7 +129,8 @@ class _M2RNN(torch.autograd.Function):
             if not in_kernel_dw:
                 hp = hprev[:, :, :a.T].reshape(B * N, a.T * K, V)
                 da = z[:, :, :a.T].reshape(B * N, a.T * K, V)
-                dW += _bmm_f32(hp.transpose(1, 2), da).view(B, N, V, V).sum(0)
+                # h^T da over the segment's steps and state rows: both read as MN-major operands where they are
+                dW += _bmm_kernel(hp, da, True, True, torch.float32).view(B, N, V, V).sum(0)
         if in_kernel_dw:
             dW = dW_part.sum((0, 2))
 

@@ -39,12 +39,13 @@ def _launch(a: _Args, mode: int, what: str) -> None:
 
 def _weight_grad(left: torch.Tensor, right: torch.Tensor, heads: int) -> torch.Tensor:
     """``sum_{b,s} left[b,s,n,:]^T right[b,s,n,:]`` per head ``[N, H, H]`` fp32, folded to ``heads`` weight heads."""
-    from .ssd import _bmm_f32
+    from .gemm import _bmm_kernel
 
     B, S, N, H = left.shape
-    lt = left.permute(2, 3, 0, 1).reshape(N, H, B * S)
+    # per head: left^T right over the B * S steps: both operands are read as [steps, H] = MN-major (no transposes)
+    lt = left.permute(2, 0, 1, 3).reshape(N, B * S, H)
     rt = right.permute(2, 0, 1, 3).reshape(N, B * S, H)
-    dW = _bmm_f32(lt, rt)
+    dW = _bmm_kernel(lt, rt, True, True, torch.float32)
     return dW if heads == N else dW.view(heads, N // heads, H, H).sum(1)
 
 
