@@ -66,7 +66,7 @@ def _sustained(fn, n_pool: int, seconds: float = 1.5) -> float:
     return e1.elapsed_time(e2) * 1e-3 / half
 
 
-def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, probe=0, **kw):
+def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, probe=0, **kw):
     dev = "cuda"
     bytes_per = 2 * (M * K + N * K + M * N)
     n_pool = max(2, min(8, int(300e6 // bytes_per) + 1))
@@ -74,7 +74,7 @@ def bench_gemm(M, N, K, a_mn=False, b_mn=False, sustained=False, impl=None, prob
     Bs = [torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16) for _ in range(n_pool)]
     out = torch.empty((M, N // 2 if kw.get("swiglu") else N), device=dev, dtype=torch.bfloat16)
     timer = _sustained if sustained else _time
-    t_ours = timer(lambda i: gemm(As[i], Bs[i], a_mn=a_mn, b_mn=b_mn, out=out, impl=impl, probe=probe, **kw), n_pool)
+    t_ours = timer(lambda i: gemm(As[i], Bs[i], a_mn=a_mn, b_mn=b_mn, out=out, probe=probe, **kw), n_pool)
 
     def ref(i):
         A = As[i].t() if a_mn else As[i]
@@ -296,12 +296,11 @@ def main():
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--sustained", action="store_true", help="time ~1.5 s back-to-back loops (power-limited clocks)")
-    ap.add_argument("--impl", default=None, choices=["1cta", "2cta"])
     ap.add_argument("--fp8", action="store_true", help="also time the 8-bit GEMM and its quantiser")
     ap.add_argument("--elementwise", action="store_true", help="time the bandwidth-bound kernels instead")
     ap.add_argument("--small", action="store_true", help="smaller operand pools (profiler captures)")
     ap.add_argument("--only", default=None, help="run the one shape with this name (small profiler captures)")
-    ap.add_argument("--probe", default=None, choices=["noload", "nomma", "mmaonly", "mmacommit"],
+    ap.add_argument("--probe", default=None, choices=["noload", "nomma"],
                     help="GEMM timing probe: skip the operand loads (tensor-pipe ceiling) or the MMAs (load ceiling)")
     args = ap.parse_args()
     peaks = _peaks()
@@ -344,8 +343,8 @@ def main():
         assert shapes, f"no shape named {args.only!r}"
     rows = []
     for name, M, N, K, a_mn, b_mn, kw in shapes:
-        r = bench_gemm(M, N, K, a_mn, b_mn, sustained=args.sustained, impl=args.impl,
-                       probe={"noload": 64, "nomma": 128, "mmaonly": 256, "mmacommit": 512, None: 0}[args.probe], **kw)
+        r = bench_gemm(M, N, K, a_mn, b_mn, sustained=args.sustained,
+                       probe={"noload": 64, "nomma": 128, None: 0}[args.probe], **kw)
         r["name"] = name
         r["frac_of_peak"] = r["tflops"] / peaks["bf16_tflops_sustained" if args.sustained else "bf16_tflops"]
         rows.append(r)
@@ -363,8 +362,6 @@ def main():
                   f"quantize(+transpose) {r['quantize_ms']:7.3f} ms {r['quantize_gbs']:6.0f} GB/s", flush=True)
     st = _lib.read_status()
     print("device status:", st)
-    if args.impl == "2cta":
-        print("resident CTA pairs of the 2-CTA grid:", _lib.cuda_lib().lme_gemm_2cta_resident_pairs())
     if args.json:
         json.dump({"peaks": peaks, "gemm": rows, "status": st}, open(args.json, "w"), indent=1)
 

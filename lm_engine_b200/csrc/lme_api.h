@@ -28,13 +28,6 @@ int lme_gemm_bf16(const void* A, int a_mn_major, long long lda, const void* B, i
                   void* C, long long ldc, int M, int N, int K, int flags, const void* bias, const void* residual,
                   long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
 
-// Same contract, computed by pairs of CTAs (thread-block clusters of 2, tcgen05.mma.cta_group::2, 256 x 256 tiles).
-int lme_gemm_bf16_2cta(const void* A, int a_mn_major, long long lda, const void* B, int b_mn_major, long long ldb,
-                       void* C, long long ldc, int M, int N, int K, int flags, const void* bias,
-                       const void* residual, long long ldr, void* preact, long long ldp, int max_ctas, void* stream);
-
-// resident CTA pairs of the 2-CTA kernel's persistent grid (-1 before its first launch)
-int lme_gemm_2cta_resident_pairs(void);
 
 // Batched form: C[b] (+)= A[b] x B[b]^T for b < batch; operand / output b starts *_batch_ld elements after b - 1.
 // Flags: LME_GEMM_OUT_F32, LME_GEMM_ACCUMULATE.  Rows past M / N of a batch read as zeros (3-D tensor maps).

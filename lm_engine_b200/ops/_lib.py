@@ -56,7 +56,6 @@ def cuda_lib() -> ctypes.CDLL:
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         sigs = {
             "lme_gemm_bf16": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
-            "lme_gemm_bf16_2cta": [P, I, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, I, P],
             "lme_gemm_fp8": [P, I, L, P, I, L, P, P, P, L, I, I, I, I, P, P, L, P, L, I, P],
             "lme_gemm_bf16_allgather_a": [P, L, P, I, L, P, L, I, I, I, I, P, P, L, P, L, P, P, P, P, P, L, I, I, I, I, I, I, P],
             "lme_gather_signal": [P, I, I, I, P],
@@ -81,7 +80,6 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_ssd_combine": [P, P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
             "lme_ssd_boundary_fwd": [P, P, P, P, P, P, I, I, I, I, P],
             "lme_ssd_boundary_bwd": [P, P, P, P, P, P, P, I, I, I, I, P],
-            "lme_gemm_2cta_resident_pairs": [],
             "lme_gemm_bf16_batched": [P, I, L, L, P, I, L, L, P, L, L, I, I, I, I, I, I, P],
             "lme_m2rnn": [P, I, P],
             "lme_rnn": [P, I, P],

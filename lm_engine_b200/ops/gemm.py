@@ -23,8 +23,6 @@ import torch
 
 from . import _lib
 
-# "1cta": one CTA per 128 x 256 tile; "2cta": CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2)
-DEFAULT_IMPL = os.environ.get("LME_GEMM", "1cta")
 # SMs left free for communication kernels that run concurrently with the persistent GEMMs (set by the sharding
 # runtime when collectives overlap compute).  A persistent kernel that cannot place all of its CTAs at once would
 # otherwise wait for the collective to release its SMs.
@@ -96,7 +94,6 @@ def gemm(
     swiglu: bool = False,
     preact: torch.Tensor | None = None,
     max_ctas: int = 0,
-    impl: str | None = None,
     probe: int = 0,
 ) -> torch.Tensor:
     """``probe``: timing-probe flags of the micro-benchmarks (64: stages are never loaded, 128: never multiplied);
@@ -131,7 +128,7 @@ def gemm(
         raise ValueError("gemm: out must be a row-major [M, N] tensor")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise TypeError("gemm: out must be bf16 or fp32")
-    flags = int(probe) & 960
+    flags = int(probe) & 192
     if out.dtype == torch.float32:
         flags |= _lib.GEMM_OUT_F32
     if accumulate:
@@ -146,8 +143,7 @@ def gemm(
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
         raise ValueError("gemm: bias must be a contiguous bf16 [N] tensor")
     lib = _lib.cuda_lib()
-    fn = lib.lme_gemm_bf16_2cta if (impl or DEFAULT_IMPL) == "2cta" else lib.lme_gemm_bf16
-    rc = fn(
+    rc = lib.lme_gemm_bf16(
         a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0),
         M, N, K, flags, _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
         _lib.ptr(preact), preact.stride(0) if preact is not None else 0, max_ctas or _max_ctas(a.device),
