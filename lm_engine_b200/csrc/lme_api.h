@@ -96,6 +96,23 @@ int lme_moe_gather_reduce(const void* src, const int* slot, const void* w, void*
                           void* stream);
 int lme_moe_row_dots(const void* a, const int* slot, const void* b, void* out, int T, int H, int K, void* stream);
 
+// Router: top-k selection fused with the softmax on bf16 logits [T, E] (E <= 512, K <= 32), one warp per token.
+// normalized != 0: weights = softmax over the K selected logits; else softmax over all experts read at the selected
+// ones (lse [T] fp32 receives the row log-sum-exp the backward call needs).  selected is int64 [T, K], descending,
+// the lower index first among equal logits.  The backward call writes every element of dlogits [T, E].
+int lme_moe_topk_softmax_fwd(const void* logits, int T, int E, int K, int normalized, void* weights,
+                             long long* selected, float* lse, void* stream);
+int lme_moe_topk_softmax_bwd(const void* logits, const long long* selected, const void* dw, const float* lse, int T,
+                             int E, int K, int normalized, void* dlogits, void* stream);
+
+// Padded per-expert row layout from the unsorted selection (total = T * K entries, E <= 1024): freq[e] = count,
+// k0[e] = first row (multiple of 128), kb[e] = padded rows / 64, tile_group[tile] = expert of a 128-row tile or -1,
+// slot[i] = row of assignment i (assignments of an expert keep their index order; < 0 for an id outside [0, E)).
+// ntiles * 128 >= total + 127 * E.  scratch holds lme_moe_route_chunks(total) * E ints.
+int lme_moe_route_chunks(int total);
+int lme_moe_route_layout(const long long* selected, int total, int E, int* scratch, long long* freq, int* k0, int* kb,
+                         int* tile_group, int ntiles, int* slot, void* stream);
+
 // Depthwise causal convolution on channel-last bf16 activations x [B, S, C], weight [C, K] (K <= 8), optional bias [C]
 // and initial state init [B, C, K-1] (the inputs before t = 0); silu != 0 fuses the activation.  Backward recomputes
 // the pre-activation; dw [C, K] / dbias [C] are fp32 accumulators the caller zeroes, dinit [B, C, K-1] is written.

@@ -133,6 +133,11 @@ class MoE(nn.Module):
 
     def _route(self, x: torch.Tensor):
         logits = self.gate(x)
+        from ...ops.moe import topk_softmax, topk_softmax_eligible
+
+        if topk_softmax_eligible(logits, self.top_k):
+            w, sel = topk_softmax(logits, self.top_k, self.normalized_topk)
+            return logits, w, sel
         if self.normalized_topk:
             w, sel = self._topk(logits)
             w = F.softmax(w.float(), dim=-1).type_as(x)
@@ -144,18 +149,20 @@ class MoE(nn.Module):
     # ------------------------------------------------------------------ experts
     def _experts(self, x: torch.Tensor, weights: torch.Tensor, selected: torch.Tensor):
         T = x.size(0)
+        if (self.ep_world_size == 1 and self._grouped_kernels(x) and x.size(1) % 8 == 0
+                and self.num_experts <= 1024 and selected.numel() > 0):
+            # Device-only path: padded per-expert layout from a counting sort of the selection (three small kernels),
+            # one scatter kernel, two grouped tcgen05 GEMMs over all experts (SwiGLU fused into the first), one
+            # gather-reduce kernel for the weighted combine.  No per-expert launches, no atomics, no host
+            # synchronisation on the routing result.
+            from ...ops.moe import GroupLayout, combine_tokens, dispatch_tokens
+
+            layout = GroupLayout.from_selection(selected, self.num_experts)
+            y_pad = self._grouped_mlp_padded(dispatch_tokens(x, layout), layout)
+            return combine_tokens(y_pad, weights.to(x.dtype), layout), layout.freq
         with torch.no_grad():
             sorted_experts, order = selected.flatten().sort()
             freq = expert_histogram(sorted_experts, self.num_experts)
-        if self.ep_world_size == 1 and self._grouped_kernels(x) and x.size(1) % 8 == 0:
-            # Device-only path: padded per-expert layout derived from the histogram, one scatter kernel, two grouped
-            # tcgen05 GEMMs over all experts (SwiGLU fused into the first), one gather-reduce kernel for the weighted
-            # combine.  No per-expert launches, no atomics, no host synchronisation on the routing result.
-            from ...ops.moe import GroupLayout, combine_tokens, dispatch_tokens
-
-            layout = GroupLayout(sorted_experts, freq, order=order, top_k=self.top_k)
-            y_pad = self._grouped_mlp_padded(dispatch_tokens(x, layout), layout)
-            return combine_tokens(y_pad, weights.to(x.dtype), layout), freq
         token = order // self.top_k
         gates = weights.flatten()[order]
         xs = x[token]

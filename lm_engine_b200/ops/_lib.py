@@ -68,6 +68,10 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_moe_scatter_rows": [P, P, P, P, I, I, I, P],
             "lme_moe_gather_reduce": [P, P, P, P, I, I, I, P],
             "lme_moe_row_dots": [P, P, P, P, I, I, I, P],
+            "lme_moe_topk_softmax_fwd": [P, I, I, I, I, P, P, P, P],
+            "lme_moe_topk_softmax_bwd": [P, P, P, P, I, I, I, I, P, P],
+            "lme_moe_route_chunks": [I],
+            "lme_moe_route_layout": [P, I, I, P, P, P, P, P, I, P, P],
             "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
             "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
             "lme_reduce_slices": [P, I, P, L, I, F, I, P],

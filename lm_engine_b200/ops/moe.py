@@ -68,6 +68,33 @@ class GroupLayout:
             flat.scatter_(0, order, self.dest.to(torch.int32))
             self.slot = flat.view(total // top_k, top_k)
 
+    @classmethod
+    def from_selection(cls, selected: torch.Tensor, num_experts: int) -> "GroupLayout":
+        """The same layout straight from the unsorted ``selected [T, K]`` (int64, CUDA): three small kernels (per-CTA
+        histograms, one scan, stable ranks) instead of a sort, a histogram, two scans, a search and a scatter.
+        ``freq`` (int64 ``[E]``) is filled as a by-product; ``dest`` is not (the layout is reached through ``slot``)."""
+        from . import _lib
+
+        sel = selected.contiguous()
+        total, dev = sel.numel(), sel.device
+        self = cls.__new__(cls)
+        self.capacity = (total + num_experts * (TILE_ROWS - 1) + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS
+        ntiles = self.capacity // TILE_ROWS
+        lib = _lib.cuda_lib()
+        ints = torch.empty(lib.lme_moe_route_chunks(total) * num_experts + 2 * num_experts + ntiles + total,
+                           dtype=torch.int32, device=dev)
+        scratch, self.k0, self.kb, self.tile_group, flat = ints.split(
+            [ints.numel() - 2 * num_experts - ntiles - total, num_experts, num_experts, ntiles, total])
+        self.freq = torch.empty(num_experts, dtype=torch.int64, device=dev)
+        _lib.check(lib.lme_moe_route_layout(sel.data_ptr(), total, num_experts, scratch.data_ptr(),
+                                            self.freq.data_ptr(), self.k0.data_ptr(), self.kb.data_ptr(),
+                                            self.tile_group.data_ptr(), ntiles, flat.data_ptr(), _lib.stream_ptr()),
+                   f"lme_moe_route_layout total={total} E={num_experts}")
+        _lib.count_launch(3)
+        self.num_groups, self.dest = num_experts, None
+        self.slot = flat.view(selected.shape)
+        return self
+
     def scatter(self, rows: torch.Tensor) -> torch.Tensor:
         """Rows sorted by expert -> padded layout (padding rows zero)."""
         out = torch.zeros((self.capacity, rows.size(1)), dtype=rows.dtype, device=rows.device)
@@ -207,6 +234,55 @@ class _Combine(torch.autograd.Function):
             dg = torch.empty_like(gates)
             _rows_call("lme_moe_row_dots", y_pad, ctx.slot, dout, dg, T, H, K)
         return dy, dg, None
+
+
+class _TopKSoftmax(torch.autograd.Function):
+    """Router weights and selection in one kernel each way (one warp per token): top-k of the logits, softmax over
+    the selected ones (``normalized``) or over all experts."""
+
+    @staticmethod
+    def forward(ctx, logits, k: int, normalized: bool):
+        from . import _lib
+
+        logits = logits.contiguous()
+        T, E = logits.shape
+        w = torch.empty((T, k), dtype=logits.dtype, device=logits.device)
+        sel = torch.empty((T, k), dtype=torch.int64, device=logits.device)
+        lse = None if normalized else torch.empty(T, dtype=torch.float32, device=logits.device)
+        _lib.check(_lib.cuda_lib().lme_moe_topk_softmax_fwd(logits.data_ptr(), T, E, k, int(normalized), w.data_ptr(),
+                                                            sel.data_ptr(), _lib.ptr(lse), _lib.stream_ptr()),
+                   f"lme_moe_topk_softmax_fwd T={T} E={E} K={k}")
+        _lib.count_launch()
+        ctx.save_for_backward(logits, sel, *([] if lse is None else [lse]))
+        ctx.normalized = normalized
+        ctx.mark_non_differentiable(sel)
+        return w, sel
+
+    @staticmethod
+    def backward(ctx, dw, _dsel):
+        from . import _lib
+
+        logits, sel, *rest = ctx.saved_tensors
+        T, E = logits.shape
+        dl = torch.empty_like(logits)
+        dw = dw.contiguous()
+        _lib.check(_lib.cuda_lib().lme_moe_topk_softmax_bwd(logits.data_ptr(), sel.data_ptr(), dw.data_ptr(),
+                                                            _lib.ptr(rest[0] if rest else None), T, E, sel.size(1),
+                                                            int(ctx.normalized), dl.data_ptr(), _lib.stream_ptr()),
+                   f"lme_moe_topk_softmax_bwd T={T} E={E} K={sel.size(1)}")
+        _lib.count_launch()
+        return dl, None, None
+
+
+def topk_softmax_eligible(logits: torch.Tensor, k: int) -> bool:
+    return (logits.is_cuda and logits.dtype == torch.bfloat16 and logits.dim() == 2 and k <= 32
+            and k <= logits.size(1) <= 512)
+
+
+def topk_softmax(logits: torch.Tensor, k: int, normalized: bool):
+    """``(weights [T, k] in the logits' dtype, selected [T, k] int64)`` of the router
+    (role of lm_engine/modeling_utils/mlp_blocks/moe/__init__.py's top-k + softmax in either order)."""
+    return _TopKSoftmax.apply(logits, k, normalized)
 
 
 def dispatch_tokens(x: torch.Tensor, layout: GroupLayout) -> torch.Tensor:

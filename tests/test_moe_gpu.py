@@ -130,3 +130,50 @@ def test_dispatch_combine_kernels_match_index_ops():
     torch.testing.assert_close(gates.grad.float(), ref_g.grad, rtol=3e-2, atol=3e-2)
     xp.backward(torch.ones_like(xp))
     torch.testing.assert_close(x.grad.float(), torch.full_like(x, float(K)).float())
+
+
+@pytest.mark.parametrize("T,K,E", [(300, 2, 8), (5000, 8, 64), (7, 1, 3), (4096, 4, 1000)])
+def test_route_layout_kernels_match_sort_based_layout(T, K, E):
+    """The counting-sort layout equals the one derived from a stable sort, entry by entry."""
+    from lm_engine_b200.ops.moe import GroupLayout
+
+    torch.manual_seed(T + K)
+    sel = torch.randint(0, E, (T, K), device="cuda")
+    if E > 4:
+        sel[sel == 2] = 3                       # an empty expert
+    se, order = sel.flatten().sort(stable=True)
+    freq = torch.bincount(se, minlength=E)
+    ref = GroupLayout(se, freq, order=order, top_k=K)
+    got = GroupLayout.from_selection(sel, E)
+    assert got.capacity == ref.capacity
+    assert torch.equal(got.freq, freq)
+    assert torch.equal(got.k0, ref.k0) and torch.equal(got.kb, ref.kb)
+    assert torch.equal(got.tile_group, ref.tile_group)
+    assert torch.equal(got.slot, ref.slot)
+
+
+@pytest.mark.parametrize("normalized", [True, False])
+@pytest.mark.parametrize("T,E,K", [(1000, 64, 8), (33, 8, 2), (257, 500, 1), (64, 40, 32)])
+def test_topk_softmax_kernel_matches_fp32_reference(normalized, T, E, K):
+    from lm_engine_b200.ops.moe import topk_softmax
+
+    torch.manual_seed(E + K)
+    # distinct bf16 values in a row, so that the selection has no ties
+    base = torch.stack([torch.randperm(E, device="cuda") for _ in range(T)]).float()
+    logits = ((base - E / 2) * (8.0 / E)).to(torch.bfloat16)
+    if E > 256:
+        logits = (base - E / 2).to(torch.bfloat16)                 # integers below 256 are exact in bf16
+    lg = logits.clone().requires_grad_(True)
+    w, sel = topk_softmax(lg, K, normalized)
+    ref_l = logits.float().requires_grad_(True)
+    if normalized:
+        rv, rs = ref_l.topk(K, dim=-1)
+        rw = torch.softmax(rv, dim=-1)
+    else:
+        rw, rs = torch.softmax(ref_l, dim=-1).topk(K, dim=-1)
+    assert torch.equal(sel, rs)
+    torch.testing.assert_close(w.float(), rw, rtol=1e-2, atol=1e-3)
+    dw = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    w.backward(dw)
+    rw.backward(dw.float())
+    torch.testing.assert_close(lg.grad.float(), ref_l.grad, rtol=2e-2, atol=2e-3)
