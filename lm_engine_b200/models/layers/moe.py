@@ -160,6 +160,15 @@ class MoE(nn.Module):
             layout = GroupLayout.from_selection(selected, self.num_experts)
             y_pad = self._grouped_mlp_padded(dispatch_tokens(x, layout), layout)
             return combine_tokens(y_pad, weights.to(x.dtype), layout), layout.freq
+        if self.ep_world_size > 1 and self._grouped_kernels(x) and not self.use_padding_free_transformer:
+            # Expert parallel on peer memory: rows are pushed into / pulled from the owners' symmetric slabs by
+            # kernels, the counts stay on the devices, the experts run as two grouped GEMMs on the landed rows.
+            from ...parallel import expert_exchange
+
+            group = ProcessGroupManager.get_expert_parallel_group()
+            if expert_exchange.eligible(x, selected, self.num_experts, group):
+                return expert_exchange.expert_parallel_mlp(x, weights, selected, self.num_experts, group,
+                                                           self._grouped_mlp_padded)
         with torch.no_grad():
             sorted_experts, order = selected.flatten().sort()
             freq = expert_histogram(sorted_experts, self.num_experts)

@@ -71,6 +71,15 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_moe_topk_softmax_fwd": [P, I, I, I, I, P, P, P, P],
             "lme_moe_topk_softmax_bwd": [P, P, P, P, I, I, I, I, P, P],
             "lme_moe_route_chunks": [I],
+            "lme_ep_flag_words": [],
+            "lme_ep_publish_counts": [P, P, P, I, I, I, I, P],
+            "lme_ep_bases": [P, P, I, I, I, I, I, P, P, P, P, P, P],
+            "lme_ep_dest": [P, P, P, P, I, I, I, I, P, P],
+            "lme_ep_push_rows": [P, P, P, P, I, I, I, P, I, I, I, P],
+            "lme_ep_zero_tail_rows": [P, P, P, P, I, I, P],
+            "lme_ep_wait": [P, I, I, I, P],
+            "lme_ep_signal_done": [P, I, I, I, P],
+            "lme_ep_pull_rows": [P, P, P, I, I, I, I, I, P],
             "lme_moe_route_layout": [P, I, I, P, P, P, P, P, I, P, P],
             "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
             "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],

@@ -60,8 +60,9 @@ def check_device_status(step: int, status: list[int] | None = None) -> list[int]
     if status is not None and status[0] != 0:
         raise DeviceWaitExpired(
             f"step {step}: device status {status[:4]} (code {status[0]}: 1 = mbarrier wait, 2 = peer flag wait, "
-            f"3 = bounds; detail {status[1]}, block {status[2]}, count {status[3]}): a bounded wait expired, the "
-            f"step's results are not valid")
+            f"3 = bounds; detail {status[1]}, block {status[2]}, count {status[3]}): a bounded wait expired or, with "
+            f"code 3 and detail 1200 + rank, the expert-parallel landing slab of that rank overflowed (raise "
+            f"LME_EP_CAPACITY_FACTOR); the step's results are not valid")
     return status
 
 

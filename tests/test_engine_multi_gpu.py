@@ -46,9 +46,10 @@ def _hybrid_config():
     return cfg
 
 
-def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_dir=None, cp=1):
+def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_dir=None, cp=1, ep_exchange="peer"):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LME_REDUCE_SCATTER=reduce_mode)
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LME_REDUCE_SCATTER=reduce_mode,
+                      LME_EP_EXCHANGE=ep_exchange)
     try:
         import torch.distributed as dist
 
@@ -105,11 +106,12 @@ def _worker(rank, world, port, q, reduce_mode, total_mbs, steps, ep=1, weights_d
             dist.destroy_process_group()
 
 
-def _run(world, reduce_mode, total_mbs=4, steps=4, ep=1, weights_dir=None, cp=1):
+def _run(world, reduce_mode, total_mbs=4, steps=4, ep=1, weights_dir=None, cp=1, ep_exchange="peer"):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps, ep, weights_dir, cp))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, reduce_mode, total_mbs, steps, ep, weights_dir, cp,
+                                                 ep_exchange))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -147,9 +149,11 @@ def test_zero3_two_gpus_match_one_gpu(reduce_mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_two_gpus_match_one_gpu(tmp_path):
-    """Mixture of experts with the experts split over 2 GPUs (NCCL all-to-all of token rows, grouped GEMM kernels,
-    expert parameter units reduced over their replica group) against all experts on one GPU."""
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_expert_parallel_two_gpus_match_one_gpu(tmp_path, exchange):
+    """Mixture of experts with the experts split over 2 GPUs (token rows exchanged by the peer-memory kernels or by
+    NCCL all-to-all, grouped GEMM kernels, expert parameter units reduced over their replica group) against all
+    experts on one GPU."""
     from lm_engine_b200.models import build_model, config_from_dict
     from lm_engine_b200.parallel.manager import ProcessGroupManager
     from lm_engine_b200.utils import SafeTensorsWeightsManager
@@ -164,7 +168,7 @@ def test_expert_parallel_two_gpus_match_one_gpu(tmp_path):
     SafeTensorsWeightsManager.save_state_dict(model.state_dict(), d)
     ProcessGroupManager.destroy_process_groups()
     (ref_losses, ref_norms, _, _), = _run(1, "nccl", ep=2, weights_dir=d)
-    outs = _run(2, "nccl", ep=2, weights_dir=d)
+    outs = _run(2, "nccl", ep=2, weights_dir=d, ep_exchange=exchange)
     mean = [(outs[0][0][s] + outs[1][0][s]) / 2 for s in range(len(ref_losses))]
     for a, b in zip(mean, ref_losses):
         assert abs(a - b) < 1.5e-2 * abs(b), (mean, ref_losses)
