@@ -194,10 +194,11 @@ class MoE(nn.Module):
         from ...ops.moe import grouped_linear_padded
 
         fuse = isinstance(self.act, GLUActivation) and self.act.is_swiglu
-        h = grouped_linear_padded(x_pad, self.c_fc.weight, layout, swiglu=fuse)
+        h = grouped_linear_padded(x_pad, self.c_fc.weight, layout, swiglu=fuse,
+                                  dgrad_out=getattr(layout, "input_grad_buffer", None))
         if not fuse:
             h = self.act(h)
-        return grouped_linear_padded(h, self.c_proj.weight, layout)
+        return grouped_linear_padded(h, self.c_proj.weight, layout, out=getattr(layout, "output_buffer", None))
 
     def _grouped_mlp(self, xs: torch.Tensor, sorted_experts: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
         """Rows already sorted by expert (expert-parallel receive side)."""

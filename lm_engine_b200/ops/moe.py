@@ -105,11 +105,18 @@ class GroupLayout:
 
 
 def _grouped_gemm(a: torch.Tensor, w2d: torch.Tensor, layout: GroupLayout, n: int, k: int, b_mn: bool,
-                  swiglu: bool = False, preact: torch.Tensor | None = None) -> torch.Tensor:
+                  swiglu: bool = False, preact: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out`` (optional): a buffer of the result's shape to write into; rows of tiles without an expert keep what
+    they held."""
     from . import _lib
     from .gemm import _max_ctas
 
-    out = torch.zeros((a.size(0), n // 2 if swiglu else n), dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        out = torch.zeros((a.size(0), n // 2 if swiglu else n), dtype=torch.bfloat16, device=a.device)
+    else:
+        assert out.shape == (a.size(0), n // 2 if swiglu else n) and out.dtype == torch.bfloat16
+        out = out.view(out.shape)          # a new tensor object per call: autograd hangs its node on the object
     rc = _lib.cuda_lib().lme_gemm_bf16_grouped(
         a.data_ptr(), a.stride(0), w2d.data_ptr(), int(b_mn), w2d.stride(0), out.data_ptr(), out.stride(0),
         a.size(0), n, k, layout.num_groups, _lib.GEMM_SWIGLU if swiglu else 0, _lib.ptr(preact),
@@ -125,12 +132,12 @@ class _GroupedLinear(torch.autograd.Function):
     the padded layout: one persistent tcgen05 kernel over all experts for each of forward, dgrad and wgrad."""
 
     @staticmethod
-    def forward(ctx, x_pad, weight, layout: GroupLayout, swiglu: bool):
+    def forward(ctx, x_pad, weight, layout: GroupLayout, swiglu: bool, out=None, dgrad_out=None):
         E, N, K = weight.shape
         pre = torch.zeros((x_pad.size(0), N), dtype=x_pad.dtype, device=x_pad.device) if swiglu else None
-        y = _grouped_gemm(x_pad, weight.view(E * N, K), layout, N, K, False, swiglu, pre)
+        y = _grouped_gemm(x_pad, weight.view(E * N, K), layout, N, K, False, swiglu, pre, out=out)
         ctx.save_for_backward(x_pad, weight, pre)
-        ctx.layout, ctx.swiglu = layout, swiglu
+        ctx.layout, ctx.swiglu, ctx.dgrad_out = layout, swiglu, dgrad_out
         return y
 
     @staticmethod
@@ -148,7 +155,7 @@ class _GroupedLinear(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dx = dy @ W[e]: W[e] is [N, K] = the MN-major operand whose contraction rows are offset by e * N
-            dx = _grouped_gemm(dy, weight.view(E * N, K), layout, K, N, True)
+            dx = _grouped_gemm(dy, weight.view(E * N, K), layout, K, N, True, out=ctx.dgrad_out)
         if ctx.needs_input_grad[1]:
             main_grad = getattr(weight, "main_grad", None)
             stale = getattr(weight, "main_grad_stale", False)
@@ -169,12 +176,14 @@ class _GroupedLinear(torch.autograd.Function):
                     weight.main_grad_stale = False
             else:
                 dw = out
-        return dx, dw, None, None
+        return dx, dw, None, None, None, None
 
 
-def grouped_linear_padded(x_pad: torch.Tensor, weight: torch.Tensor, layout: GroupLayout,
-                          swiglu: bool = False) -> torch.Tensor:
-    return _GroupedLinear.apply(x_pad, weight, layout, swiglu)
+def grouped_linear_padded(x_pad: torch.Tensor, weight: torch.Tensor, layout: GroupLayout, swiglu: bool = False,
+                          out: torch.Tensor | None = None, dgrad_out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out`` / ``dgrad_out``: buffers that receive the result / the input gradient (the expert-parallel exchange
+    passes its output slabs, so that the rows are published where the kernels wrote them)."""
+    return _GroupedLinear.apply(x_pad, weight, layout, swiglu, out, dgrad_out)
 
 
 def _rows_call(fn_name: str, src, slot, w, dst, T, H, K) -> None:

@@ -13,8 +13,8 @@ One layer call (csrc/kernels/ep_exchange.cu documents the flags):
 * ``_Dispatch``: rows are pushed into the owners' landing slabs; the owner zeroes the tails of its experts' last
   tiles, waits for the arrival flags and takes a private copy (the slab is reused by the next layer);
 * the grouped tcgen05 GEMMs run on the owner's rows exactly as without expert parallelism;
-* ``_Collect``: the owner publishes its output slab, the sources pull their rows back; the router-weighted sum is the
-  ordinary combine kernel on the local rows.
+* ``_Collect``: the owner publishes its output slab (the last GEMM wrote into it), the sources pull their rows back;
+  the router-weighted sum is the ordinary combine kernel on the local rows.
 
 The backward pass mirrors it on a second pair of slabs.  The landing slabs hold ``capacity_factor * tokens * top_k``
 rows (``LME_EP_CAPACITY_FACTOR``, default 2, at most the group size = the worst case): a static bound is the price
@@ -138,6 +138,8 @@ class RankBuffers:
         own = GroupLayout.__new__(GroupLayout)
         own.capacity, own.num_groups, own.k0, own.kb, own.tile_group = self.cap, Le, k0, kb, tile_group
         own.slot = own.dest = None
+        # the last expert GEMM and the first one's input-gradient GEMM write straight into the slabs the peers pull from
+        own.output_buffer, own.input_grad_buffer = self.y_out, self.dx_out
         plan.owner_layout = own
         return plan
 
@@ -169,7 +171,9 @@ class RankBuffers:
 
     def publish_output(self, rows: torch.Tensor, forward: bool, seq: int) -> None:
         _, out, pad, _ = self._dir(forward)
-        getattr(self, out).copy_(rows)
+        slab = getattr(self, out)
+        if rows.data_ptr() != slab.data_ptr():
+            slab.copy_(rows)
         _lib.check(_lib.cuda_lib().lme_ep_signal_done(self.arr[pad], self.rank, self.world, seq, _lib.stream_ptr()),
                    "lme_ep_signal_done")
         _lib.count_launch()
