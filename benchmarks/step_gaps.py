@@ -27,6 +27,8 @@ def main() -> None:
     ap.add_argument("--mbs", type=int, default=2)
     ap.add_argument("--out", default=os.path.join(os.environ.get("TMPDIR", "/tmp"), "lme_step_trace.json"))
     ap.add_argument("--top", type=int, default=30)
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel group size (mixture-of-experts models)")
+    ap.add_argument("--kernels", type=int, default=4, help="kernel names listed per stream, by total time")
     a = ap.parse_args()
 
     import torch
@@ -45,8 +47,10 @@ def main() -> None:
     from lm_engine_b200.utils import disable_generation_cache
 
     bench.LAYERS_OVERRIDE = a.layers
-    args = TrainingArgs(**bench.training_config(a.model, a.seq, a.mbs, 1, ["fused_linear_cross_entropy"], None))
-    ProcessGroupManager(zero_stage=3)
+    cfg = bench.training_config(a.model, a.seq, a.mbs, 1, ["fused_linear_cross_entropy"], None)
+    cfg["distributed_args"]["expert_parallel_world_size"] = a.ep
+    args = TrainingArgs(**cfg)
+    ProcessGroupManager(zero_stage=3, expert_parallel_world_size=a.ep)
     rank, world = ProcessGroupManager.get_global_rank(), ProcessGroupManager.get_world_size()
     args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
     models = get_model_container(args)
@@ -93,7 +97,7 @@ def main() -> None:
             names = collections.Counter()
             for e in v:
                 names[e["name"].split("<")[0].split("(")[0][:60]] += e["dur"]
-            print(f"stream {s}: n={len(v)} busy_us={busy[s]:.0f}", [(k, round(d)) for k, d in names.most_common(4)])
+            print(f"stream {s}: n={len(v)} busy_us={busy[s]:.0f}", [(k, round(d)) for k, d in names.most_common(a.kernels)])
         v = sorted(streams[main_stream], key=lambda e: e["ts"])
         gaps = [(n["ts"] - (p["ts"] + p["dur"]), p["name"][:50], n["name"][:50], p["ts"] - t0)
                 for p, n in zip(v, v[1:]) if n["ts"] - (p["ts"] + p["dur"]) > 3]

@@ -3,25 +3,30 @@
 // mixture-of-experts layer (lm_engine/modeling_utils/mlp_blocks/moe/module.py:276-291 in the reference keeps every
 // expert on every rank; its expert-parallel relatives use an all-to-all of rows with host-side split sizes).
 //
-// Every rank owns E / world consecutive experts and a landing slab of `cap` rows in symmetric memory.  One round:
+// Every rank owns E / world consecutive experts.  All row traffic is PULLED with 16-byte peer loads (measured here:
+// peer loads reach 0.8 of the peer-copy rate from such kernels, scattered peer stores of rows 0.47); only 8-byte table
+// entries and flags are stored into peer memory.  One round:
 //   1. counts   every rank stores its per-expert counts into every peer's count table, then a flag (CNT).
 //   2. bases    every rank waits for all CNT flags and derives, from the same table, the SAME padded per-expert
 //               layout of every owner: expert e of owner r starts at k0_r[e] (multiple of 128 rows); the rows of
 //               source s inside it start after those of sources < s.  The rank keeps the tables of its own experts
 //               (tile -> expert, k0, kb) and, for its role as a source, the first row of each expert at its owner.
-//   3. push     each token row is stored straight into the owners' slabs (16-byte peer stores); the last CTA to
-//               finish publishes the ARR flag at every peer.  The owner zeroes the rows between an expert's last
-//               token and the end of its last tile itself (nobody else writes them).
-//   4. the owner waits for all ARR flags and runs the grouped GEMMs on the slab's rows; it copies the result into
-//      its output slab and publishes DONE at every peer.
-//   5. pull     after all DONE flags a source reads its rows back from the owners' output slabs (16-byte peer loads).
-// The backward pass is the same round with the roles of the two directions swapped (push of output gradients, pull of
-// input gradients) on a second pair of slabs and a second set of flags; the layout of step 2 is reused.
+//   3. offer    the source copies its rows into its staging buffer (symmetric memory) and stores, for each of its
+//               assignments, the entry (round, source, row index) into the owner's row table at the assignment's row;
+//               the last CTA to finish publishes the ARR flag at every peer.
+//   4. land     the owner waits for all ARR flags and pulls every row of its used tiles from the staging buffer its
+//               table entry names, into a private buffer; rows without an entry of this round (the tail of an
+//               expert's last tile) become zero.  The grouped GEMMs run on that buffer; the last one writes into the
+//               owner's output slab, then the owner publishes DONE at every peer.
+//   5. pull     after all DONE flags a source reads its rows back from the owners' output slabs.
+// The backward pass is the same round on a second set of buffers and flags (offer of output gradients, pull of input
+// gradients); the layout of step 2 is reused.
 //
-// Flags hold the round number (monotonic).  Every wait is bounded; on expiry the status word is set and the kernel
-// goes on (the step's result is wrong and the host raises when it reads the status).  A slab is rewritten only after
-// every reader finished with it: a rank starts round n + 1 after its pull of round n, the pull follows the DONE flags
-// of all owners, and an owner publishes DONE only after its own reads of round n.
+// Flags hold the round number (monotonic), table entries carry it, so nothing is ever reset.  Every wait is bounded;
+// on expiry the status word is set and the kernel goes on (the step's result is wrong and the host raises when it
+// reads the status).  A buffer is rewritten only after every reader finished with it: a rank starts round n + 1 after
+// its pull of round n, the pull follows the DONE flags of all owners, and an owner publishes DONE only after its own
+// reads of round n.
 // Included by lme_cuda.cu.
 
 namespace lme {
@@ -110,17 +115,15 @@ ep_dest_kernel(const long long* __restrict__ sel, const int* __restrict__ slot, 
     dest[a] = d;
 }
 
-// Source row blockIdx.x goes to its `rep` destinations dest[blockIdx.x * rep + j].  H % 8 == 0.
+// Table entry of a landing row: x = round * 8 + source rank, y = index of the source's staged row.
+// One thread per assignment stores its entry at the owner; the last CTA publishes the arrival flag everywhere.
 __global__ void __launch_bounds__(256)
-ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src, const int2* __restrict__ dest, EpPtrs slabs, EpPtrs pads,
-                    int rep, int H, unsigned int* __restrict__ counter, int rank, int world, int seq) {
-    const long long t = blockIdx.x;
-    const uint4* row = reinterpret_cast<const uint4*>(src + t * H);
-    for (int j = 0; j < rep; ++j) {
-        const int2 d = dest[t * rep + j];
-        if (d.y < 0) continue;
-        uint4* out = reinterpret_cast<uint4*>(slabs.p[d.x]) + static_cast<long long>(d.y) * (H / 8);
-        for (int c = threadIdx.x; c < H / 8; c += blockDim.x) out[c] = row[c];
+ep_offer_rows_kernel(const int2* __restrict__ dest, EpPtrs tables, EpPtrs pads, int A, unsigned int* __restrict__ counter,
+                     int rank, int world, int seq) {
+    const int a = blockIdx.x * blockDim.x + threadIdx.x;
+    if (a < A) {
+        const int2 d = dest[a];
+        if (d.y >= 0) reinterpret_cast<int2*>(tables.p[d.x])[d.y] = make_int2(seq * 8 + rank, a);
     }
     __threadfence_system();
     __syncthreads();
@@ -134,16 +137,27 @@ ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src, const int2* __restric
     }
 }
 
-// Rows [k0 + rows, k0 + 64 * kb) of each own expert := 0 (the tail of its last tiles).  grid (Le, 4).
+// Owner: rows of tiles that belong to an expert are fetched from the staging buffer their table entry names (staged
+// row = entry.y / rep), rows without an entry of round `seq` are zeroed, tiles without an expert are left alone.
+// Each CTA takes LAND_ROWS consecutive rows.
+constexpr int LAND_ROWS = 4;
 __global__ void __launch_bounds__(256)
-ep_zero_tail_rows_kernel(__nv_bfloat16* __restrict__ slab, const int* __restrict__ k0, const int* __restrict__ kb,
-                         const int* __restrict__ rows, int H) {
-    const int e = blockIdx.x;
-    const int first = k0[e] + rows[e], last = k0[e] + 64 * kb[e];
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int r = first + blockIdx.y; r < last; r += gridDim.y) {
-        uint4* out = reinterpret_cast<uint4*>(slab + static_cast<long long>(r) * H);
-        for (int c = threadIdx.x; c < H / 8; c += blockDim.x) out[c] = z;
+ep_land_rows_kernel(EpPtrs stages, const int2* __restrict__ table, const int* __restrict__ tile_group,
+                    __nv_bfloat16* __restrict__ out, int H, int rep, int seq) {
+    const int row0 = blockIdx.x * LAND_ROWS;
+    if (tile_group[row0 / 128] < 0) return;
+#pragma unroll
+    for (int i = 0; i < LAND_ROWS; ++i) {
+        const int row = row0 + i;
+        const int2 e = table[row];
+        uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(row) * H);
+        if ((e.x >> 3) == seq) {
+            const uint4* src = reinterpret_cast<const uint4*>(stages.p[e.x & 7]) +
+                               static_cast<long long>(e.y / rep) * (H / 8);
+            for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = ld_peer_v4(src + c);
+        } else {
+            for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = make_uint4(0, 0, 0, 0);
+        }
     }
 }
 
@@ -229,22 +243,24 @@ extern "C" int lme_ep_dest(const long long* sel, const int* slot, const int* k0_
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 
-// `rows` source rows of H bf16 elements, each stored to `rep` destinations; counter: one zeroed word of this rank.
-extern "C" int lme_ep_push_rows(const void* src, const void* dest, void* const* slabs, void* const* pads, int rows,
-                                int rep, int H, unsigned int* counter, int rank, int world, int seq, void* stream) {
-    if (!ep_world_ok(rank, world) || rows <= 0 || rep <= 0 || H <= 0 || H % 8) return LME_ERR_SHAPE;
-    if (reinterpret_cast<uintptr_t>(src) & 15) return LME_ERR_ALIGN;
-    ep_push_rows_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(src), static_cast<const int2*>(dest), ep_ptrs(slabs, world),
-        ep_ptrs(pads, world), rep, H, counter, rank, world, seq);
+// Stores this rank's table entries for its A assignments (dest: int32 [A][2]) into the owners' row tables and
+// publishes the arrival flag; counter: one zeroed word of this rank.  The staged rows must be complete in stream order.
+extern "C" int lme_ep_offer_rows(const void* dest, void* const* tables, void* const* pads, int A,
+                                 unsigned int* counter, int rank, int world, int seq, void* stream) {
+    if (!ep_world_ok(rank, world) || A <= 0 || seq <= 0 || seq >= (1 << 27)) return LME_ERR_SHAPE;
+    ep_offer_rows_kernel<<<(A + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const int2*>(dest), ep_ptrs(tables, world), ep_ptrs(pads, world), A, counter, rank, world, seq);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 
-extern "C" int lme_ep_zero_tail_rows(void* slab, const int* k0, const int* kb, const int* rows, int local_experts,
-                                     int H, void* stream) {
-    if (local_experts <= 0 || H <= 0 || H % 8) return LME_ERR_SHAPE;
-    ep_zero_tail_rows_kernel<<<dim3(local_experts, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16*>(slab), k0, kb, rows, H);
+// stages[r]: rank r's staging buffer (rows of H bf16); table: this rank's row table (int32 [cap][2]); out [cap][H].
+extern "C" int lme_ep_land_rows(void* const* stages, const void* table, const int* tile_group, void* out, int cap,
+                                int H, int rep, int seq, int world, void* stream) {
+    if (world <= 0 || world > EP_MAX_RANKS || cap <= 0 || cap % 128 || H <= 0 || H % 8 || rep <= 0)
+        return LME_ERR_SHAPE;
+    ep_land_rows_kernel<<<cap / LAND_ROWS, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        ep_ptrs(stages, world), static_cast<const int2*>(table), tile_group, static_cast<__nv_bfloat16*>(out), H, rep,
+        seq);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 

@@ -107,8 +107,8 @@ int lme_moe_topk_softmax_bwd(const void* logits, const long long* selected, cons
 
 // Expert-parallel token exchange over peer memory (kernels/ep_exchange.cu has the protocol).  Pointer arrays have one
 // entry per rank of the expert-parallel group ([rank] = this rank's own memory): counts[r] = rank r's [world][E] int32
-// table, pads[r] = rank r's flag block of this direction (lme_ep_flag_words() int32 words, zero at start), slabs[r] =
-// rank r's landing slab ([cap][H] bf16) for pushes or its output slab for pulls.  `seq` is the round number (grows by
+// table, pads[r] = rank r's flag block of this direction (lme_ep_flag_words() int32 words, zero at start), tables[r] =
+// rank r's row table (int32 [cap][2], zero at start), stages[r] = its staged rows, slabs[r] = its output slab.  `seq` is the round number (grows by
 // one per round of a direction, the same on every rank).  dest is int32 [A][2] = (owner, row or -1).
 int lme_ep_flag_words(void);
 int lme_ep_publish_counts(const long long* freq, void* const* counts, void* const* pads, int rank, int world, int E,
@@ -117,10 +117,10 @@ int lme_ep_bases(const int* counts, const int* pad, int rank, int world, int E, 
                  int* k0_own, int* kb_own, int* rows_own, int* tile_group, void* stream);
 int lme_ep_dest(const long long* sel, const int* slot, const int* k0_local, const int* base, int A, int E, int world,
                 int cap, void* dest, void* stream);
-int lme_ep_push_rows(const void* src, const void* dest, void* const* slabs, void* const* pads, int rows, int rep, int H,
-                     unsigned int* counter, int rank, int world, int seq, void* stream);
-int lme_ep_zero_tail_rows(void* slab, const int* k0, const int* kb, const int* rows, int local_experts, int H,
-                          void* stream);
+int lme_ep_offer_rows(const void* dest, void* const* tables, void* const* pads, int A, unsigned int* counter,
+                      int rank, int world, int seq, void* stream);
+int lme_ep_land_rows(void* const* stages, const void* table, const int* tile_group, void* out, int cap, int H, int rep,
+                     int seq, int world, void* stream);
 int lme_ep_wait(const int* pad, int which, int world, int seq, void* stream);   // which: 0 rows arrived, 1 output ready
 int lme_ep_signal_done(void* const* pads, int rank, int world, int seq, void* stream);
 int lme_ep_pull_rows(void* const* slabs, const void* dest, void* out, int T, int K, int H, int reduce, int world,

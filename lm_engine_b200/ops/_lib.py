@@ -75,8 +75,8 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_ep_publish_counts": [P, P, P, I, I, I, I, P],
             "lme_ep_bases": [P, P, I, I, I, I, I, P, P, P, P, P, P],
             "lme_ep_dest": [P, P, P, P, I, I, I, I, P, P],
-            "lme_ep_push_rows": [P, P, P, P, I, I, I, P, I, I, I, P],
-            "lme_ep_zero_tail_rows": [P, P, P, P, I, I, P],
+            "lme_ep_offer_rows": [P, P, P, I, P, I, I, I, P],
+            "lme_ep_land_rows": [P, P, P, P, I, I, I, I, I, P],
             "lme_ep_wait": [P, I, I, I, P],
             "lme_ep_signal_done": [P, I, I, I, P],
             "lme_ep_pull_rows": [P, P, P, I, I, I, I, I, P],

@@ -113,7 +113,10 @@ def _grouped_gemm(a: torch.Tensor, w2d: torch.Tensor, layout: GroupLayout, n: in
     from .gemm import _max_ctas
 
     if out is None:
-        out = torch.zeros((a.size(0), n // 2 if swiglu else n), dtype=torch.bfloat16, device=a.device)
+        # rows of tiles without an expert are never written and never read (every consumer walks the same tile table
+        # or the slots), so the buffer is not cleared: with a capacity of twice the routed rows the fills cost more
+        # than a millisecond per layer
+        out = torch.empty((a.size(0), n // 2 if swiglu else n), dtype=torch.bfloat16, device=a.device)
     else:
         assert out.shape == (a.size(0), n // 2 if swiglu else n) and out.dtype == torch.bfloat16
         out = out.view(out.shape)          # a new tensor object per call: autograd hangs its node on the object
@@ -134,7 +137,7 @@ class _GroupedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_pad, weight, layout: GroupLayout, swiglu: bool, out=None, dgrad_out=None):
         E, N, K = weight.shape
-        pre = torch.zeros((x_pad.size(0), N), dtype=x_pad.dtype, device=x_pad.device) if swiglu else None
+        pre = torch.empty((x_pad.size(0), N), dtype=x_pad.dtype, device=x_pad.device) if swiglu else None
         y = _grouped_gemm(x_pad, weight.view(E * N, K), layout, N, K, False, swiglu, pre, out=out)
         ctx.save_for_backward(x_pad, weight, pre)
         ctx.layout, ctx.swiglu, ctx.dgrad_out = layout, swiglu, dgrad_out
@@ -220,8 +223,9 @@ class _Combine(torch.autograd.Function):
     the row dot products for the gate gradients."""
 
     @staticmethod
-    def forward(ctx, y_pad, gates, slot):
+    def forward(ctx, y_pad, gates, slot, grad_buffer=None):
         y_pad, gates = y_pad.contiguous(), gates.contiguous()
+        ctx.grad_buffer = grad_buffer
         T, K = slot.shape
         out = torch.empty((T, y_pad.size(1)), dtype=y_pad.dtype, device=y_pad.device)
         _rows_call("lme_moe_gather_reduce", y_pad, slot, gates, out, T, y_pad.size(1), K)
@@ -237,12 +241,13 @@ class _Combine(torch.autograd.Function):
         H = y_pad.size(1)
         dy = dg = None
         if ctx.needs_input_grad[0]:
-            dy = torch.zeros_like(y_pad)
+            # grad_buffer: a caller-owned buffer of y_pad's shape whose every row is some token's slot (nothing to clear)
+            dy = torch.zeros_like(y_pad) if ctx.grad_buffer is None else ctx.grad_buffer.view(y_pad.shape)
             _rows_call("lme_moe_scatter_rows", dout, ctx.slot, gates, dy, T, H, K)
         if ctx.needs_input_grad[1]:
             dg = torch.empty_like(gates)
             _rows_call("lme_moe_row_dots", y_pad, ctx.slot, dout, dg, T, H, K)
-        return dy, dg, None
+        return dy, dg, None, None
 
 
 class _TopKSoftmax(torch.autograd.Function):
@@ -299,7 +304,7 @@ def dispatch_tokens(x: torch.Tensor, layout: GroupLayout) -> torch.Tensor:
 
 
 def combine_tokens(y_pad: torch.Tensor, gates: torch.Tensor, layout: GroupLayout) -> torch.Tensor:
-    return _Combine.apply(y_pad, gates, layout.slot)
+    return _Combine.apply(y_pad, gates, layout.slot, getattr(layout, "grad_buffer", None))
 
 
 def grouped_kernels_eligible(x: torch.Tensor, *weights: torch.Tensor) -> bool:

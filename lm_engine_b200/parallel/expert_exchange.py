@@ -10,14 +10,16 @@ One layer call (csrc/kernels/ep_exchange.cu documents the flags):
 
 * every rank derives the padded per-expert row layout of ITS tokens with the counting-sort kernels, publishes its
   counts to all peers, and computes - from the same table on every rank - where its rows go inside each owner's slab;
-* ``_Dispatch``: rows are pushed into the owners' landing slabs; the owner zeroes the tails of its experts' last
-  tiles, waits for the arrival flags and takes a private copy (the slab is reused by the next layer);
+* ``_Dispatch``: the source stages its rows in symmetric memory and stores one 8-byte table entry per assignment at
+  the owner; the owner waits for the arrival flags and pulls the rows of its tiles into a private buffer (rows
+  without an entry - the tail of an expert's last tile - become zero);
 * the grouped tcgen05 GEMMs run on the owner's rows exactly as without expert parallelism;
 * ``_Collect``: the owner publishes its output slab (the last GEMM wrote into it), the sources pull their rows back;
   the router-weighted sum is the ordinary combine kernel on the local rows.
 
-The backward pass mirrors it on a second pair of slabs.  The landing slabs hold ``capacity_factor * tokens * top_k``
-rows (``LME_EP_CAPACITY_FACTOR``, default 2, at most the group size = the worst case): a static bound is the price
+All row traffic is pulled with peer loads (scattered peer stores of rows measured at 0.47 of the peer-copy rate,
+peer loads at 0.8).  The backward pass mirrors the forward pass on a second set of buffers.  An owner's layout holds
+``capacity_factor * tokens * top_k`` rows (``LME_EP_CAPACITY_FACTOR``, default 2, at most the group size = the worst case): a static bound is the price
 of keeping the host out of the loop.  Overflow is detected on the device (every rank sees it in the same table), the
 overflowing rows are dropped and the status word makes the training loop raise at the end of the step.
 """
@@ -34,7 +36,7 @@ import torch.distributed as dist
 from ..ops import _lib
 from ..ops.moe import TILE_ROWS, GroupLayout, combine_tokens
 
-_BUFFERS = ("x_in", "y_out", "dy_in", "dx_out", "counts", "pad_f", "pad_b")
+_BUFFERS = ("x_stage", "x_table", "y_out", "dy_stage", "dy_table", "dx_out", "counts", "pad_f", "pad_b")
 _CONTEXTS: dict[tuple, "RankBuffers"] = {}
 
 
@@ -58,6 +60,7 @@ class RankBuffers:
 
     def __init__(self, rank: int, world: int, num_experts: int, cap: int, hidden: int,
                  tensors: dict[str, list[torch.Tensor]]) -> None:
+        """``tensors``: see :meth:`sizes`."""
         assert world <= 8 and num_experts % world == 0 and cap % TILE_ROWS == 0 and hidden % 8 == 0
         self.rank, self.world, self.E, self.cap, self.H = rank, world, num_experts, cap, hidden
         self.local_experts = num_experts // world
@@ -65,26 +68,28 @@ class RankBuffers:
         self.arr = {name: _ptr_array([t.data_ptr() for t in tensors[name]]) for name in _BUFFERS}
         for name in _BUFFERS:
             setattr(self, name, tensors[name][rank])
-        dev = self.x_in.device
+        dev = self.y_out.device
         self.counter = torch.zeros(4, dtype=torch.int32, device=dev)
         self.seq_f = self.seq_b = 0
         self._identity: dict[tuple[int, int], GroupLayout] = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def sizes(cls, world: int, num_experts: int, cap: int, hidden: int) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
-        words = 32
-        return {"x_in": ((cap, hidden), torch.bfloat16), "y_out": ((cap, hidden), torch.bfloat16),
-                "dy_in": ((cap, hidden), torch.bfloat16), "dx_out": ((cap, hidden), torch.bfloat16),
-                "counts": ((world, num_experts), torch.int32), "pad_f": ((words,), torch.int32),
-                "pad_b": ((words,), torch.int32)}
+    def sizes(cls, world: int, num_experts: int, cap: int, hidden: int, tokens: int, top_k: int
+              ) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
+        words, bf = 32, torch.bfloat16
+        return {"x_stage": ((tokens, hidden), bf), "x_table": ((cap, 2), torch.int32), "y_out": ((cap, hidden), bf),
+                "dy_stage": ((tokens * top_k, hidden), bf), "dy_table": ((cap, 2), torch.int32),
+                "dx_out": ((cap, hidden), bf), "counts": ((world, num_experts), torch.int32),
+                "pad_f": ((words,), torch.int32), "pad_b": ((words,), torch.int32)}
 
     @classmethod
-    def symmetric(cls, group, num_experts: int, cap: int, hidden: int, device: torch.device) -> "RankBuffers":
+    def symmetric(cls, group, num_experts: int, cap: int, hidden: int, tokens: int, top_k: int,
+                  device: torch.device) -> "RankBuffers":
         import torch.distributed._symmetric_memory as symm_mem
 
         world, rank = dist.get_world_size(group), dist.get_rank(group)
-        sizes = cls.sizes(world, num_experts, cap, hidden)
+        sizes = cls.sizes(world, num_experts, cap, hidden, tokens, top_k)
         offsets, total = {}, 0
         for name, (shape, dtype) in sizes.items():
             offsets[name] = total
@@ -101,10 +106,11 @@ class RankBuffers:
         return self
 
     @classmethod
-    def emulated(cls, world: int, num_experts: int, cap: int, hidden: int, device) -> list["RankBuffers"]:
+    def emulated(cls, world: int, num_experts: int, cap: int, hidden: int, tokens: int, top_k: int,
+                 device) -> list["RankBuffers"]:
         """All ranks of a group on ONE device (plain tensors instead of peer mappings): lets a single GPU run the
         kernels of every rank one phase after the other, so that no wait ever has to spin."""
-        sizes = cls.sizes(world, num_experts, cap, hidden)
+        sizes = cls.sizes(world, num_experts, cap, hidden, tokens, top_k)
         tensors = {name: [torch.zeros(shape, dtype=dtype, device=device) for _ in range(world)]
                    for name, (shape, dtype) in sizes.items()}
         return [cls(r, world, num_experts, cap, hidden, tensors) for r in range(world)]
@@ -143,34 +149,40 @@ class RankBuffers:
         plan.owner_layout = own
         return plan
 
-    def _dir(self, forward: bool) -> tuple[str, str, str, int]:
-        """(landing slab, output slab, flag block, counter word) of a direction."""
-        return ("x_in", "y_out", "pad_f", 0) if forward else ("dy_in", "dx_out", "pad_b", 1)
+    def _dir(self, forward: bool) -> tuple[str, str, str, str, int]:
+        """(staging buffer, row table, output slab, flag block, counter word) of a direction."""
+        return (("x_stage", "x_table", "y_out", "pad_f", 0) if forward
+                else ("dy_stage", "dy_table", "dx_out", "pad_b", 1))
 
-    def push(self, src: torch.Tensor, plan: Plan, rep: int, forward: bool, seq: int) -> None:
-        land, _, pad, word = self._dir(forward)
-        assert src.is_contiguous() and src.size(1) == self.H and src.size(0) * rep == plan.dest.size(0)
-        _lib.check(_lib.cuda_lib().lme_ep_push_rows(src.data_ptr(), plan.dest.data_ptr(), self.arr[land], self.arr[pad],
-                                                    src.size(0), rep, self.H, self.counter[word:].data_ptr(),
-                                                    self.rank, self.world, seq, _lib.stream_ptr()),
-                   f"lme_ep_push_rows rows={src.size(0)} rep={rep} H={self.H}")
+    def offer(self, src: torch.Tensor, plan: Plan, forward: bool, seq: int) -> None:
+        """Source side: stage the rows where the owners can read them, store the table entries, publish arrival."""
+        stage, table, _, pad, word = self._dir(forward)
+        staged = getattr(self, stage)
+        if src.data_ptr() != staged.data_ptr():
+            staged.copy_(src)
+        _lib.check(_lib.cuda_lib().lme_ep_offer_rows(plan.dest.data_ptr(), self.arr[table], self.arr[pad],
+                                                     plan.dest.size(0), self.counter[word:].data_ptr(), self.rank,
+                                                     self.world, seq, _lib.stream_ptr()),
+                   f"lme_ep_offer_rows A={plan.dest.size(0)}")
         _lib.count_launch()
 
     def land(self, plan: Plan, forward: bool, seq: int) -> torch.Tensor:
-        """Owner side of a push: zero the tails of the experts' last tiles, wait for every source's arrival flag,
-        return a private copy of the landing slab."""
-        land, _, pad, _ = self._dir(forward)
-        lib, slab, own = _lib.cuda_lib(), getattr(self, land), plan.owner_layout
-        _lib.check(lib.lme_ep_zero_tail_rows(slab.data_ptr(), own.k0.data_ptr(), own.kb.data_ptr(),
-                                             plan.rows_own.data_ptr(), self.local_experts, self.H,
-                                             _lib.stream_ptr()), "lme_ep_zero_tail_rows")
+        """Owner side: wait for every source's arrival flag, pull the rows of the used tiles into a private buffer
+        (rows of tiles without an expert stay uninitialised; no kernel reads them)."""
+        stage, table, _, pad, _ = self._dir(forward)
+        lib = _lib.cuda_lib()
         _lib.check(lib.lme_ep_wait(getattr(self, pad).data_ptr(), 0, self.world, seq, _lib.stream_ptr()),
                    "lme_ep_wait")
+        rows = torch.empty((self.cap, self.H), dtype=torch.bfloat16, device=self.y_out.device)
+        _lib.check(lib.lme_ep_land_rows(self.arr[stage], getattr(self, table).data_ptr(),
+                                        plan.owner_layout.tile_group.data_ptr(), rows.data_ptr(), self.cap, self.H,
+                                        plan.K if forward else 1, seq, self.world, _lib.stream_ptr()),
+                   f"lme_ep_land_rows cap={self.cap} H={self.H}")
         _lib.count_launch(2)
-        return slab.clone()
+        return rows
 
     def publish_output(self, rows: torch.Tensor, forward: bool, seq: int) -> None:
-        _, out, pad, _ = self._dir(forward)
+        _, _, out, pad, _ = self._dir(forward)
         slab = getattr(self, out)
         if rows.data_ptr() != slab.data_ptr():
             slab.copy_(rows)
@@ -180,12 +192,12 @@ class RankBuffers:
 
     def pull(self, plan: Plan, reduce: bool, forward: bool, seq: int) -> torch.Tensor:
         """After every owner's :meth:`publish_output` (the wait kernel checks their flags)."""
-        _, out, pad, _ = self._dir(forward)
+        _, _, out, pad, _ = self._dir(forward)
         lib = _lib.cuda_lib()
         _lib.check(lib.lme_ep_wait(getattr(self, pad).data_ptr(), 1, self.world, seq, _lib.stream_ptr()),
                    "lme_ep_wait")
         rows = torch.empty((plan.T if reduce else plan.T * plan.K, self.H), dtype=torch.bfloat16,
-                           device=self.x_in.device)
+                           device=self.y_out.device)
         _lib.check(lib.lme_ep_pull_rows(self.arr[out], plan.dest.data_ptr(), rows.data_ptr(), plan.T, plan.K, self.H,
                                         int(reduce), self.world, _lib.stream_ptr()),
                    f"lme_ep_pull_rows T={plan.T} K={plan.K} H={self.H}")
@@ -197,8 +209,10 @@ class RankBuffers:
         kernels."""
         if (T, K) not in self._identity:
             lay = GroupLayout.__new__(GroupLayout)
-            lay.slot = torch.arange(T * K, dtype=torch.int32, device=self.x_in.device).view(T, K)
+            lay.slot = torch.arange(T * K, dtype=torch.int32, device=self.y_out.device).view(T, K)
             lay.capacity, lay.dest = T * K, None
+            # the combine kernel's backward writes the row gradients where the owners will read them
+            lay.grad_buffer = self.dy_stage
             self._identity[(T, K)] = lay
         return self._identity[(T, K)]
 
@@ -209,7 +223,7 @@ class _Dispatch(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, rk: RankBuffers, plan: Plan):
-        rk.push(x.contiguous(), plan, plan.K, True, plan.seq_f)
+        rk.offer(x, plan, True, plan.seq_f)
         ctx.rk, ctx.plan = rk, plan
         return rk.land(plan, True, plan.seq_f)
 
@@ -222,7 +236,7 @@ class _Dispatch(torch.autograd.Function):
 
 class _Collect(torch.autograd.Function):
     """This owner's output rows ``[cap, H]`` -> the rows of this rank's own assignments ``[T * K, H]``, pulled from
-    their owners; backward pushes the row gradients to the owners."""
+    their owners; backward offers the row gradients to the owners."""
 
     @staticmethod
     def forward(ctx, y_pad, rk: RankBuffers, plan: Plan):
@@ -235,7 +249,7 @@ class _Collect(torch.autograd.Function):
         rk, plan = ctx.rk, ctx.plan
         rk.seq_b += 1
         plan.seq_b = rk.seq_b
-        rk.push(dy_rows.contiguous(), plan, 1, False, plan.seq_b)
+        rk.offer(dy_rows, plan, False, plan.seq_b)
         return rk.land(plan, False, plan.seq_b), None, None
 
 
@@ -258,12 +272,12 @@ def eligible(x: torch.Tensor, selected: torch.Tensor, num_experts: int, group) -
     return world <= 8 and num_experts <= 1024 and num_experts % world == 0
 
 
-def buffers_for(group, num_experts: int, assignments: int, hidden: int, device: torch.device) -> RankBuffers:
-    key = (id(group), num_experts, assignments, hidden)
+def buffers_for(group, num_experts: int, tokens: int, top_k: int, hidden: int, device: torch.device) -> RankBuffers:
+    key = (id(group), num_experts, tokens, top_k, hidden)
     if key not in _CONTEXTS:
         world = dist.get_world_size(group)
-        cap = capacity_rows(assignments, num_experts // world, world)
-        _CONTEXTS[key] = RankBuffers.symmetric(group, num_experts, cap, hidden, device)
+        cap = capacity_rows(tokens * top_k, num_experts // world, world)
+        _CONTEXTS[key] = RankBuffers.symmetric(group, num_experts, cap, hidden, tokens, top_k, device)
     return _CONTEXTS[key]
 
 
@@ -271,7 +285,7 @@ def expert_parallel_mlp(x: torch.Tensor, weights: torch.Tensor, selected: torch.
                         mlp) -> tuple[torch.Tensor, torch.Tensor]:
     """``x [T, H]``, router ``weights`` / ``selected [T, K]`` -> ``(sum_k w * expert(x) [T, H], counts [E])``;
     ``mlp(x_pad, layout)`` applies this rank's experts to rows in the padded layout."""
-    rk = buffers_for(group, num_experts, selected.numel(), x.size(1), x.device)
+    rk = buffers_for(group, num_experts, selected.size(0), selected.size(1), x.size(1), x.device)
     layout = GroupLayout.from_selection(selected, num_experts)
     plan = rk.make_plan(selected.contiguous(), layout, rk.publish_counts(layout))
     y_pad = mlp(_Dispatch.apply(x, rk, plan), plan.owner_layout)

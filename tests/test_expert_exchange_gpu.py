@@ -1,6 +1,6 @@
 """Expert-parallel exchange kernels with all ranks of the group emulated on ONE GPU: every phase runs for all ranks
 before the next phase starts, so each wait finds its flag already set (kernels of different ranks never wait on one
-another here).  The layout, the pushed rows, the zeroed tile tails, both pull modes and the overflow report are
+another here).  The layout, the landed rows, the zeroed tile tails, both pull modes and the overflow report are
 checked against plain PyTorch indexing."""
 
 import pytest
@@ -14,7 +14,7 @@ def _setup(world, E, K, T, H, cap, seed=0):
     from lm_engine_b200.parallel.expert_exchange import RankBuffers
 
     g = torch.Generator(device="cuda").manual_seed(seed)
-    ranks = RankBuffers.emulated(world, E, cap, H, "cuda")
+    ranks = RankBuffers.emulated(world, E, cap, H, T, K, "cuda")
     sel = [torch.randint(0, E, (T, K), device="cuda", generator=g) for _ in range(world)]
     if E > 4:
         for s in sel:
@@ -36,7 +36,7 @@ def test_exchange_round_trip_emulated_ranks(world, E, K, T, H):
     cap = (world * T * K + 127) // 128 * 128 + Le * 128        # worst case: nothing can overflow
     ranks, sel, x, plans, seqs = _setup(world, E, K, T, H, cap)
     for r in range(world):
-        ranks[r].push(x[r], plans[r], K, True, seqs[r])
+        ranks[r].offer(x[r], plans[r], True, seqs[r])
     x_pads = [ranks[r].land(plans[r], True, seqs[r]) for r in range(world)]
 
     # reference layout of owner r: experts in order, inside an expert the sources in rank order, inside a source the
@@ -71,7 +71,7 @@ def test_exchange_round_trip_emulated_ranks(world, E, K, T, H):
     for r in range(world):
         ranks[r].seq_b += 1
         plans[r].seq_b = ranks[r].seq_b
-        ranks[r].push(dy[r], plans[r], 1, False, plans[r].seq_b)
+        ranks[r].offer(dy[r], plans[r], False, plans[r].seq_b)
     dy_pads = [ranks[r].land(plans[r], False, plans[r].seq_b) for r in range(world)]
     for r in range(world):
         d = plans[r].dest.long()
@@ -84,6 +84,23 @@ def test_exchange_round_trip_emulated_ranks(world, E, K, T, H):
         dx = ranks[r].pull(plans[r], True, False, plans[r].seq_b)
         want = dy[r].view(T, K, H).float().sum(1)
         torch.testing.assert_close(dx.float(), want, rtol=1e-2, atol=1e-2)
+    # a second forward round with another routing: table entries of the first round must not leak into it
+    from lm_engine_b200.ops.moe import GroupLayout
+
+    sel2 = [torch.randint(0, E, (T, K), device="cuda", generator=g) for _ in range(world)]
+    lay2 = [GroupLayout.from_selection(sel2[r], E) for r in range(world)]
+    seq2 = [ranks[r].publish_counts(lay2[r]) for r in range(world)]
+    plan2 = [ranks[r].make_plan(sel2[r], lay2[r], seq2[r]) for r in range(world)]
+    for r in range(world):
+        ranks[r].offer(x[r], plan2[r], True, seq2[r])
+    for r in range(world):
+        pad2 = ranks[r].land(plan2[r], True, seq2[r])
+        own = plan2[r].owner_layout
+        for le, (k0, kb) in enumerate(zip(own.k0.tolist(), own.kb.tolist())):
+            e = r * Le + le
+            want = torch.cat([x[s][(sel2[s] == e).flatten().nonzero().flatten() // K] for s in range(world)])
+            assert torch.equal(pad2[k0:k0 + want.size(0)], want)
+            assert float(pad2[k0 + want.size(0):k0 + 64 * kb].float().abs().sum()) == 0.0
     torch.cuda.synchronize()
     assert _lib.read_status(clear=True)[0] == 0
 
@@ -97,9 +114,9 @@ def test_exchange_overflow_is_reported_not_written():
     world, E, K, T, H = 2, 4, 2, 400, 64
     cap = 512                                                   # 1600 assignments over 2 owners cannot fit
     ranks, sel, x, plans, seqs = _setup(world, E, K, T, H, cap)
-    guard = [ranks[r].tensors["y_out"][r] for r in range(world)]      # allocated right behind / near the slabs
+    guard = [ranks[r].tensors["y_out"][r] for r in range(world)]      # never written in this test
     for r in range(world):
-        ranks[r].push(x[r], plans[r], K, True, seqs[r])
+        ranks[r].offer(x[r], plans[r], True, seqs[r])
     pads = [ranks[r].land(plans[r], True, seqs[r]) for r in range(world)]
     torch.cuda.synchronize()
     status = _lib.read_status(clear=True)
@@ -134,7 +151,7 @@ def test_moe_layer_on_emulated_exchange_matches_local_experts():
     moe = MoE(256, cfg.mlp_blocks[0], "normal", 0.02, None, 1, True).cuda().to(torch.bfloat16)
     x = torch.randn(384, 256, device="cuda").to(torch.bfloat16)
     T, K, E = 384, 2, 8
-    rk = xx.RankBuffers.emulated(1, E, xx.capacity_rows(T * K, E, 1), 256, "cuda")[0]
+    rk = xx.RankBuffers.emulated(1, E, xx.capacity_rows(T * K, E, 1), 256, T, K, "cuda")[0]
 
     def run(exchange):
         moe.zero_grad()
