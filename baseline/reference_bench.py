@@ -108,9 +108,13 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
         # `use_reentrant` knob selects the checkpoint implementation without that comparison.
         cfg["distributed_args"]["gradient_checkpointing_args"] = {
             "use_reentrant": os.environ.get("LME_REF_REENTRANT", "1") == "1"}
+        tp, ga = getattr(a, "tp", 1), getattr(a, "ga", 1)
+        if tp > 1:      # the reference's async TP is an inductor pass (needs torch.compile): plain TP + SP here
+            cfg["distributed_args"].update(tensor_parallel_world_size=tp, sequence_parallel=True)
+        cfg["training_parameters"]["gradient_accumulation_steps"] = ga
         args = TrainingArgs(**cfg)
         d = args.distributed_args
-        ProcessGroupManager(zero_stage=d.stage)
+        ProcessGroupManager(zero_stage=d.stage, tensor_parallel_world_size=tp)
         world = ProcessGroupManager.get_world_size()
         rank = ProcessGroupManager.get_global_rank()
         args.training_parameters.reset_training_parameters(
@@ -138,7 +142,7 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
                 model_container=models, optimizer_container=opts, lr_scheduler_container=scheds,
                 train_dataloader=loader, gradient_clipping=1.0, forward_context=nullcontext,
                 backward_context=nullcontext, sync_every_gradient_accumulation_step=False,
-                micro_batch_size=a.mbs, gradient_accumulation_steps=1, sequence_length=a.seq,
+                micro_batch_size=a.mbs, gradient_accumulation_steps=ga, sequence_length=a.seq,
                 tuning_method=TuningMethod.pretraining)
 
         def barrier():
@@ -152,7 +156,7 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
             first_loss = float(m["loss"]) if a.warmup else None
             resident = _Batches(vocab, a.seq, a.mbs, dl_rank, dl_world, device=device)
             resident.cursor = host_iter.cursor
-            staged = iter([next(resident) for _ in range(a.steps)])
+            staged = iter([next(resident) for _ in range(a.steps * ga)])
             sampler = ClockSampler(torch.cuda.current_device())
             barrier()
             if rank == 0:
@@ -176,15 +180,16 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
         t = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = t.tolist()
-        tokens = world * a.mbs * a.seq * a.steps
+        tokens = dl_world * ga * a.mbs * a.seq * a.steps
         out = {
             "impl": "reference", "metric": "tokens/sec (whole job), pretraining step fwd+bwd+clip+AdamW",
             "value": tokens / (dev_ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random token ids, seeded random-init weights",
-            "config": {"model": a.model, "global_batch": world * a.mbs, "seq_len": a.seq,
-                       "parallelism": f"fsdp2-zero3-dp{world}", "micro_batch_per_gpu": a.mbs,
+            "config": {"model": a.model, "global_batch": dl_world * ga * a.mbs, "seq_len": a.seq,
+                       "parallelism": f"fsdp2-zero3-dp{dl_world}" + (f"-tp{tp}-sp" if tp > 1 else ""),
+                       "gradient_accumulation_steps": ga, "micro_batch_per_gpu": a.mbs,
                        "gradient_checkpointing": "block", "kernels": kernels,
                        "l2": "working set per step >> 126 MB L2, no flush"},
             "tokens_per_sec_per_gpu": tokens / (dev_ms * 1e-3) / world, "clocks": clocks,

@@ -36,6 +36,8 @@ MODELS = {
     # the mixture-of-experts target config: 24 layers, 64 SwiGLU-1024 experts, top-8, aux 0.01, micro batch 4 per GPU,
     # experts split over all N GPUs (expert parallel = N) with ZeRO-3 for the rest
     "moe-ep8": (50304, 24, 2048, 16, 4, 128, 1024, 10000),
+    # ~20B dense model of the tensor-parallel target config (run with --tp 4 --seq 8192 --mbs 1 --ga 8 on 8 GPUs)
+    "dense-20b": (128256, 48, 6144, 48, 8, 128, 16384, 500000),
     # hybrid: three Mamba-2 (SSD) layers per softmax-attention layer (see HYBRID), no positional embedding
     "hybrid-mamba2": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
     # hybrid: three matrix-state RNN layers per softmax-attention layer (see M2RNN_HYBRID)
@@ -192,9 +194,15 @@ def run_ours(a) -> dict:
     env_world = int(os.environ.get("WORLD_SIZE", "1"))
     ep = env_world if a.model == "moe-ep8" and MOE[a.model][0] % env_world == 0 else 1
     cfg["distributed_args"]["expert_parallel_world_size"] = ep
+    tp, ga = a.tp, a.ga
+    if tp > 1:
+        cfg["distributed_args"].update(tensor_parallel_world_size=tp, sequence_parallel=True,
+                                       use_async_tensor_parallel=True)
+    cfg["training_parameters"]["gradient_accumulation_steps"] = ga
     args = TrainingArgs(**cfg)
     d = args.distributed_args
-    ProcessGroupManager(zero_stage=d.stage, expert_parallel_world_size=ep)
+    ProcessGroupManager(zero_stage=d.stage, expert_parallel_world_size=ep, tensor_parallel_world_size=tp,
+                        use_async_tensor_parallel=tp > 1)
     world = ProcessGroupManager.get_world_size()
     rank = ProcessGroupManager.get_global_rank()
     args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
@@ -214,7 +222,7 @@ def run_ours(a) -> dict:
 
     def step(loader):
         # metrics are averaged over the data-parallel ranks and read back every step, as in the reference's step
-        return train_step_without_pipeline_parallel(models, opts, scheds, loader, 1, 1.0, reduce_metrics=True)
+        return train_step_without_pipeline_parallel(models, opts, scheds, loader, ga, 1.0, reduce_metrics=True)
 
     def barrier():
         if dist.is_initialized():
@@ -227,7 +235,7 @@ def run_ours(a) -> dict:
             m = step(host_iter)
         first_loss = float(m["loss"]) if a.warmup else None
         # ---- phase 1: device-timed, inputs resident on the device
-        resident = [{"text": next(host_iter)["text"].to(device)} for _ in range(a.steps)]
+        resident = [{"text": next(host_iter)["text"].to(device)} for _ in range(a.steps * ga)]
         it = iter(resident)
         sampler = ClockSampler(torch.cuda.current_device())
         barrier()
@@ -244,7 +252,7 @@ def run_ours(a) -> dict:
         launches = _lib.launch_count - launches0
         dev_ms = e0.elapsed_time(e1)
         # ---- phase 2: end to end (pinned host batch -> device each step, loss read back each step)
-        h2d = a.mbs * (a.seq + 1) * 8
+        h2d = ga * a.mbs * (a.seq + 1) * 8
         barrier()
         t0 = time.perf_counter()
         losses = []
@@ -257,10 +265,11 @@ def run_ours(a) -> dict:
     if dist.is_initialized():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = t.tolist()
-    tokens = world * a.mbs * a.seq * a.steps
+    dp_world = ProcessGroupManager.get_data_loading_world_size()      # tensor-parallel ranks share their batches
+    tokens = dp_world * ga * a.mbs * a.seq * a.steps
     value = tokens / (dev_ms * 1e-3)
     e2e_value = tokens / (e2e_ms * 1e-3)
-    tfl = get_model_tflops(models[0].config, world * a.mbs, a.seq, d.gradient_checkpointing_method,
+    tfl = get_model_tflops(models[0].config, dp_world * ga * a.mbs, a.seq, d.gradient_checkpointing_method,
                            d.gradient_checkpointing_args)
     peaks = measured_peaks()
     status = _lib.read_status(clear=False)
@@ -270,7 +279,10 @@ def run_ours(a) -> dict:
         "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": getattr(a, "dtype", "bf16"), "data": "synthetic uniform-random token ids, seeded random-init weights",
         "config": {"model": a.model if a.layers is None else f"{a.model}-{a.layers}layers",
-                   "global_batch": world * a.mbs, "seq_len": a.seq, "parallelism": f"fsdp2-zero3-dp{world}" + (f"-ep{ep}" if ep > 1 else ""), "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
+                   "global_batch": dp_world * ga * a.mbs, "seq_len": a.seq,
+                   "parallelism": f"fsdp2-zero3-dp{dp_world}" + (f"-ep{ep}" if ep > 1 else "")
+                   + (f"-tp{tp}-sp-asynctp" if tp > 1 else ""),
+                   "gradient_accumulation_steps": ga, "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
                    "optimizer": "AdamW fp32 master+state", "l2": "working set per step >> 126 MB L2, no flush"},
         "tokens_per_sec_per_gpu": value / world,
         "model_tflops_per_gpu": tfl / (dev_ms * 1e-3 / a.steps) / world,
@@ -284,7 +296,7 @@ def run_ours(a) -> dict:
         "device_status": status[:4],
         "impl": "lm_engine_b200",
     }
-    if world > 1:
+    if world > 1 and tp == 1:
         out["multi_gpu_check"] = multi_gpu_check(world, rank, device)
     ProcessGroupManager.destroy_process_groups()
     return out if rank == 0 else None
@@ -341,6 +353,8 @@ def main() -> None:
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--mbs", type=int, default=None, help="micro batch per GPU (default 2; 4 for the MoE models)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (with sequence parallel)")
+    ap.add_argument("--ga", type=int, default=1, help="gradient accumulation steps")
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (profiling captures on a small case; not a benchmark result)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
