@@ -81,6 +81,8 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_ep_signal_done": [P, I, I, I, P],
             "lme_ep_pull_rows": [P, P, P, I, I, I, I, I, P],
             "lme_moe_route_layout": [P, I, I, P, P, P, P, P, I, P, P],
+            "lme_delta_chain_fwd": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
+            "lme_delta_chain_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
             "lme_causal_conv1d_fwd": [P, P, P, P, P, I, I, I, I, I, P],
             "lme_causal_conv1d_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
             "lme_reduce_slices": [P, I, P, L, I, F, I, P],

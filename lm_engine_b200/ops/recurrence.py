@@ -139,16 +139,100 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, h0=None, use_qk_l2nor
     W = torch.linalg.solve_triangular(T, rhs, upper=False, unitriangular=True)
     Wv, Wk = W[..., :V], W[..., V:]                                        # [.., L, V], [.., L, K]
     qk = decay_incl * (qc @ kc.transpose(-1, -2))                          # [.., L(t), L(i)]
-    eG = torch.exp(G)[..., None]
+    qe = torch.exp(G)[..., None] * qc                                      # e^{G_t} q_t
     k_end = torch.exp(G[..., -1:, None] - G[..., None]) * kc               # e^{G_L - G_i} k_i
+    a_end = torch.exp(G[..., -1])                                          # decay of a whole block
     h = torch.zeros(B, N, K, V, dtype=torch.float32, device=q.device) if h0 is None else h0.float()
-    ys = []
-    for c in range(nc):
-        U = Wv[:, :, c] - Wk[:, :, c] @ h                                  # [B, N, L, V]
-        ys.append((eG[:, :, c] * qc[:, :, c]) @ h + qk[:, :, c] @ U)
-        h = torch.exp(G[:, :, c, -1])[..., None, None] * h + k_end[:, :, c].transpose(-1, -2) @ U
-    y = torch.stack(ys, dim=2).permute(0, 2, 3, 1, 4).reshape(B, nc * L, N, V)[:, :S]
+    y, h = delta_chain(Wk, Wv, qe, qk, k_end, a_end, h)
+    y = y.permute(0, 2, 3, 1, 4).reshape(B, nc * L, N, V)[:, :S]
     return y.to(dtype), h
+
+
+def delta_chain_reference(Wk, Wv, qe, qk, ke, a, h):
+    """The sequential part of the chunk-parallel delta rule, block by block: ``U = W_v - W_k h``,
+    ``y = Q_e h + QK U``, ``h <- a h + K_e^T U``.  Operands ``[B, N, nc, L, *]``, ``a [B, N, nc]``, ``h [B, N, K, V]``."""
+    ys = []
+    for c in range(Wk.size(2)):
+        U = Wv[:, :, c] - Wk[:, :, c] @ h
+        ys.append(qe[:, :, c] @ h + qk[:, :, c] @ U)
+        h = a[:, :, c, None, None] * h + ke[:, :, c].transpose(-1, -2) @ U
+    return torch.stack(ys, dim=2), h
+
+
+class _DeltaChain(torch.autograd.Function):
+    """:func:`delta_chain_reference` as two kernels (csrc/kernels/delta_rule.cu): the forward chain keeps the state of
+    64 columns in registers and leaves ``U`` and the state entering every block behind; the backward chain runs the
+    state gradient in reverse and leaves ``dU`` and the gradient leaving every block; the operand gradients are
+    batched tensor-core GEMMs over all blocks on those."""
+
+    @staticmethod
+    def forward(ctx, Wk, Wv, qe, qk, ke, a, h):
+        from . import _lib
+
+        B, N, nc, L, K = Wk.shape
+        V = Wv.size(-1)
+        bf, dev = torch.bfloat16, Wk.device
+        wk_neg = (-Wk).to(bf).contiguous()
+        qe_b, ke_b, qk_b = qe.to(bf).contiguous(), ke.to(bf).contiguous(), qk.to(bf).contiguous()
+        ket = ke_b.transpose(-1, -2).contiguous()
+        wv, a32, h32 = Wv.float().contiguous(), a.float().contiguous(), h.float().contiguous()
+        y = torch.empty((B, N, nc, L, V), dtype=torch.float32, device=dev)
+        u_all = torch.empty((B, N, nc, L, V), dtype=bf, device=dev)
+        h_all = torch.empty((B, N, nc, K, V), dtype=bf, device=dev)
+        h_final = torch.empty((B, N, K, V), dtype=torch.float32, device=dev)
+        _lib.check(_lib.cuda_lib().lme_delta_chain_fwd(
+            wk_neg.data_ptr(), qe_b.data_ptr(), ket.data_ptr(), qk_b.data_ptr(), wv.data_ptr(), a32.data_ptr(),
+            h32.data_ptr(), y.data_ptr(), u_all.data_ptr(), h_all.data_ptr(), h_final.data_ptr(), B * N, nc, K, V,
+            _lib.stream_ptr()), f"lme_delta_chain_fwd BN={B * N} nc={nc} K={K} V={V}")
+        _lib.count_launch()
+        ctx.save_for_backward(wk_neg, qe_b, ke_b, qk_b, a32, u_all, h_all)
+        return y, h_final
+
+    @staticmethod
+    def backward(ctx, dy, dh_final):
+        from . import _lib
+        from .gemm import _bmm_kernel
+
+        wk_neg, qe_b, ke_b, qk_b, a32, u_all, h_all = ctx.saved_tensors
+        B, N, nc, L, K = wk_neg.shape
+        V = u_all.size(-1)
+        bf, dev = torch.bfloat16, dy.device
+        dy = dy.float().contiguous()
+        qkt = qk_b.transpose(-1, -2).contiguous()
+        qet = qe_b.transpose(-1, -2).contiguous()
+        wkt_neg = wk_neg.transpose(-1, -2).contiguous()
+        du_all = torch.empty((B, N, nc, L, V), dtype=bf, device=dev)
+        dh_all = torch.empty((B, N, nc, K, V), dtype=bf, device=dev)
+        dh0 = torch.empty((B, N, K, V), dtype=torch.float32, device=dev)
+        dhf = None if dh_final is None else dh_final.float().contiguous()
+        _lib.check(_lib.cuda_lib().lme_delta_chain_bwd(
+            qkt.data_ptr(), ke_b.data_ptr(), qet.data_ptr(), wkt_neg.data_ptr(), dy.data_ptr(), a32.data_ptr(),
+            _lib.ptr(dhf), du_all.data_ptr(), dh_all.data_ptr(), dh0.data_ptr(), B * N, nc, K, V,
+            _lib.stream_ptr()), f"lme_delta_chain_bwd BN={B * N} nc={nc} K={K} V={V}")
+        _lib.count_launch()
+        # operand gradients: products over the V columns, one batch entry per (batch, head, block)
+        n = B * N * nc
+        dyb = dy.to(bf).view(n, L, V)
+        du, dh = du_all.view(n, L, V), dh_all.view(n, K, V)
+        u, hs = u_all.view(n, L, V), h_all.view(n, K, V)
+        f32 = torch.float32
+        dWk = -_bmm_kernel(du, hs, False, False, f32).view(B, N, nc, L, K)       # -dU h^T
+        dqe = _bmm_kernel(dyb, hs, False, False, f32).view(B, N, nc, L, K)       # dy h^T
+        dqk = _bmm_kernel(dyb, u, False, False, f32).view(B, N, nc, L, L)        # dy U^T
+        dke = _bmm_kernel(u, dh, False, False, f32).view(B, N, nc, L, K)         # U dh^T
+        da = (dh_all.float() * h_all.float()).sum((-1, -2))
+        return dWk, du_all.float(), dqe, dqk, dke, da, dh0
+
+
+def delta_chain_kernel_usable(Wk, Wv) -> bool:
+    return (Wk.is_cuda and Wk.size(-2) == 64 and Wk.size(-1) in (128, 256) and Wv.size(-1) % 64 == 0
+            and Wk.size(0) * Wk.size(1) <= 65535)
+
+
+def delta_chain(Wk, Wv, qe, qk, ke, a, h):
+    if delta_chain_kernel_usable(Wk, Wv):
+        return _DeltaChain.apply(Wk, Wv, qe, qk, ke, a, h)
+    return delta_chain_reference(Wk, Wv, qe, qk, ke, a, h)
 
 
 def linear_attention_scan(q, k, v, h0=None, attention_multiplier: float = 1.0):
@@ -198,6 +282,9 @@ def linear_attention(q, k, v, h0=None, attention_multiplier: float = 1.0):
 def gated_delta_rule(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: bool = True):
     if q.size(1) < 8:
         return gated_delta_rule_scan(q, k, v, g, beta, scale, h0, use_qk_l2norm)
+    if q.is_cuda and q.size(-1) in (128, 256) and v.size(-1) % 64 == 0:
+        # the chain over 64-step blocks is one kernel each way
+        return gated_delta_rule_chunked(q, k, v, g, beta, scale, h0, use_qk_l2norm, chunk=64)
     # the loop over blocks is the sequential (launch-bound) part and the block-local work is cheap: long sequences
     # take large blocks (the intra-block cost grows with the block length, the number of loop trips falls with it)
     chunk = LONG_CHUNK if q.size(1) >= 4 * LONG_CHUNK else CHUNK
