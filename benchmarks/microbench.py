@@ -213,7 +213,8 @@ def bench_recurrent(small: bool = False) -> list[dict]:
             return (*xs, *ws, None, 1.0)
         return make
 
-    # the chunk-parallel PyTorch forms (batched matmuls + triangular solve) at the published gated-delta-net layout
+    # the chunk-parallel forms at the published gated-delta-net layout (block operands by batched matmuls and a
+    # triangular solve in PyTorch; the delta rule's chain over the blocks on its own kernels)
     from lm_engine_b200.ops.recurrence import gated_delta_rule, linear_attention
 
     def chunked(name, fn, make_args):
@@ -229,7 +230,7 @@ def bench_recurrent(small: bool = False) -> list[dict]:
 
         tot = _time(both, 1, iters=5, warmup=2)
         rows.append({"name": name, "S": S, "fwd_ms": fwd * 1e3, "fwd_bwd_ms": tot * 1e3})
-        print(f"{name:34s} S={S}  fwd {fwd * 1e3:7.3f} ms  fwd+bwd {tot * 1e3:7.3f} ms   (chunk-parallel PyTorch ops)",
+        print(f"{name:34s} S={S}  fwd {fwd * 1e3:7.3f} ms  fwd+bwd {tot * 1e3:7.3f} ms   (chunk-parallel form)",
               flush=True)
 
     def gdn_args():

@@ -36,7 +36,8 @@ constexpr int VS = 64;   // state columns per CTA
 constexpr int PADE = 8;  // bf16 elements appended to every shared-memory row (spreads the rows over the banks)
 
 // C[16 x 8 NT] += A[m0 .. m0 + 16)[0 .. kd) * B[n0 .. n0 + 8 NT)[0 .. kd)^T; A row-major (lda), B n-major (ldb).
-template <int NT>
+// NEG: the product is subtracted (the sign bits of the A fragments are flipped on the way to the tensor core).
+template <int NT, bool NEG = false>
 __device__ __forceinline__ void warp_mma(float (&acc)[NT][4], const __nv_bfloat16* A, int lda, int m0,
                                          const __nv_bfloat16* B, int ldb, int n0, int kd, int g, int t) {
     for (int k0 = 0; k0 < kd; k0 += 16) {
@@ -46,6 +47,10 @@ __device__ __forceinline__ void warp_mma(float (&acc)[NT][4], const __nv_bfloat1
         a[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * lda);
         a[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
         a[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * lda + 8);
+        if (NEG) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] ^= 0x80008000u;
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const __nv_bfloat16* bp = B + (n0 + nt * 8 + g) * ldb + k0 + 2 * t;
@@ -64,7 +69,7 @@ __device__ __forceinline__ void stage_tile(__nv_bfloat16* dst, const __nv_bfloat
 }
 
 struct FwdArgs {
-    const __nv_bfloat16 *wk_neg, *qe, *ket, *qk;   // [BN][nc][L][K], [BN][nc][L][K], [BN][nc][K][L], [BN][nc][L][L]
+    const __nv_bfloat16 *wk, *qe, *ket, *qk;   // [BN][nc][L][K], [BN][nc][L][K], [BN][nc][K][L], [BN][nc][L][L]
     const float *wv, *a, *h0;                       // [BN][nc][L][V], [BN][nc], [BN][K][V] or null
     float* y;                                       // [BN][nc][L][V]
     __nv_bfloat16 *u_all, *h_all;                   // [BN][nc][L][V], [BN][nc][K][V] (state entering the chunk)
@@ -73,7 +78,7 @@ struct FwdArgs {
 };
 
 struct BwdArgs {
-    const __nv_bfloat16 *qkt, *ke, *qet, *wkt_neg;  // [BN][nc][L][L], [BN][nc][L][K], [BN][nc][K][L], [BN][nc][K][L]
+    const __nv_bfloat16 *qkt, *ke, *qet, *wkt;  // [BN][nc][L][L], [BN][nc][L][K], [BN][nc][K][L], [BN][nc][K][L]
     const float *dy, *a, *dh_final;                 // [BN][nc][L][V], [BN][nc], [BN][K][V] or null
     __nv_bfloat16 *du_all, *dh_all;                 // [BN][nc][L][V], [BN][nc][K][V] (gradient leaving the chunk)
     float* dh0;                                     // [BN][K][V]
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
 
     auto stage_first = [&](int c) {      // operands of the products with the state
         const long long o = (bn * nc + c) * L * K;
-        stage_tile(sWk, p.wk_neg + o, L, K);
+        stage_tile(sWk, p.wk + o, L, K);
         stage_tile(sQe, p.qe + o, L, K);
         cp_commit();
     };
@@ -153,7 +158,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
             accU[nt][0] = lo.x; accU[nt][1] = lo.y; accU[nt][2] = hi.x; accU[nt][3] = hi.y;
             accY[nt][0] = accY[nt][1] = accY[nt][2] = accY[nt][3] = 0.f;
         }
-        warp_mma<4>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
+        warp_mma<4, true>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
         warp_mma<4>(accY, sQe, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
         __nv_bfloat16* ug = p.u_all + chunk * L * V + v0;
 #pragma unroll
@@ -240,7 +245,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
     auto stage_second = [&](int c) {     // operands of the state-gradient update
         const long long o = (bn * nc + c) * K * L;
         stage_tile(sQet, p.qet + o, K, L);
-        stage_tile(sWkt, p.wkt_neg + o, K, L);
+        stage_tile(sWkt, p.wkt + o, K, L);
         cp_commit();
     };
     stage_first(nc - 1);
@@ -286,7 +291,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dh[mt][nt][i] *= a;
             warp_mma<8>(dh[mt], sQet, L + PADE, warp * (K / 8) + mt * 16, sDy, L + PADE, 0, L, g, t);
-            warp_mma<8>(dh[mt], sWkt, L + PADE, warp * (K / 8) + mt * 16, sDu, L + PADE, 0, L, g, t);
+            warp_mma<8, true>(dh[mt], sWkt, L + PADE, warp * (K / 8) + mt * 16, sDu, L + PADE, 0, L, g, t);
         }
         __syncthreads();
         if (c > 0) stage_second(c - 1); else cp_commit();
@@ -338,25 +343,25 @@ static int delta_chain_check(int BN, int nc, int K, int V) {
     return LME_OK;
 }
 
-extern "C" int lme_delta_chain_fwd(const void* wk_neg, const void* qe, const void* ket, const void* qk, const float* wv,
+extern "C" int lme_delta_chain_fwd(const void* wk, const void* qe, const void* ket, const void* qk, const float* wv,
                                    const float* a, const float* h0, float* y, void* u_all, void* h_all, float* h_final,
                                    int BN, int nc, int K, int V, void* stream) {
     if (int rc = delta_chain_check(BN, nc, K, V)) return rc;
     using bf = __nv_bfloat16;
-    lme::dr::FwdArgs p{static_cast<const bf*>(wk_neg), static_cast<const bf*>(qe), static_cast<const bf*>(ket),
+    lme::dr::FwdArgs p{static_cast<const bf*>(wk), static_cast<const bf*>(qe), static_cast<const bf*>(ket),
                        static_cast<const bf*>(qk), wv, a, h0, y, static_cast<bf*>(u_all), static_cast<bf*>(h_all),
                        h_final, nc, V};
     auto st = static_cast<cudaStream_t>(stream);
     return K == 256 ? lme::dr::launch_fwd<256>(p, BN, st) : lme::dr::launch_fwd<128>(p, BN, st);
 }
 
-extern "C" int lme_delta_chain_bwd(const void* qkt, const void* ke, const void* qet, const void* wkt_neg,
+extern "C" int lme_delta_chain_bwd(const void* qkt, const void* ke, const void* qet, const void* wkt,
                                    const float* dy, const float* a, const float* dh_final, void* du_all, void* dh_all,
                                    float* dh0, int BN, int nc, int K, int V, void* stream) {
     if (int rc = delta_chain_check(BN, nc, K, V)) return rc;
     using bf = __nv_bfloat16;
     lme::dr::BwdArgs p{static_cast<const bf*>(qkt), static_cast<const bf*>(ke), static_cast<const bf*>(qet),
-                       static_cast<const bf*>(wkt_neg), dy, a, dh_final, static_cast<bf*>(du_all),
+                       static_cast<const bf*>(wkt), dy, a, dh_final, static_cast<bf*>(du_all),
                        static_cast<bf*>(dh_all), dh0, nc, V};
     auto st = static_cast<cudaStream_t>(stream);
     return K == 256 ? lme::dr::launch_bwd<256>(p, BN, st) : lme::dr::launch_bwd<128>(p, BN, st);

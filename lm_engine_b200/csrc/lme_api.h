@@ -135,15 +135,15 @@ int lme_moe_route_layout(const long long* selected, int total, int E, int* scrat
                          int* tile_group, int ntiles, int* slot, void* stream);
 
 // Inter-chunk chain of the gated delta rule (kernels/delta_rule.cu has the recurrences).  BN = batch * heads, nc chunks
-// of 64 rows, K in {128, 256}, V % 64 == 0.  Forward operands (bf16): wk_neg = -W_k [BN][nc][64][K], qe [BN][nc][64][K],
+// of 64 rows, K in {128, 256}, V % 64 == 0.  Forward operands (bf16): wk = W_k [BN][nc][64][K], qe [BN][nc][64][K],
 // ket = K_e^T [BN][nc][K][64], qk [BN][nc][64][64]; fp32: wv [BN][nc][64][V], a [BN][nc], h0 [BN][K][V] or null.
 // Outputs: y fp32 [BN][nc][64][V], u_all bf16 [BN][nc][64][V], h_all bf16 [BN][nc][K][V] (state entering each chunk),
 // h_final fp32 [BN][K][V].  Backward operands (bf16): qkt = QK^T, ke [BN][nc][64][K], qet = Q_e^T [BN][nc][K][64],
-// wkt_neg = -W_k^T [BN][nc][K][64]; dy fp32; outputs du_all bf16, dh_all bf16 (gradient leaving each chunk), dh0 fp32.
-int lme_delta_chain_fwd(const void* wk_neg, const void* qe, const void* ket, const void* qk, const float* wv,
+// wkt = W_k^T [BN][nc][K][64]; dy fp32; outputs du_all bf16, dh_all bf16 (gradient leaving each chunk), dh0 fp32.
+int lme_delta_chain_fwd(const void* wk, const void* qe, const void* ket, const void* qk, const float* wv,
                         const float* a, const float* h0, float* y, void* u_all, void* h_all, float* h_final, int BN,
                         int nc, int K, int V, void* stream);
-int lme_delta_chain_bwd(const void* qkt, const void* ke, const void* qet, const void* wkt_neg, const float* dy,
+int lme_delta_chain_bwd(const void* qkt, const void* ke, const void* qet, const void* wkt, const float* dy,
                         const float* a, const float* dh_final, void* du_all, void* dh_all, float* dh0, int BN, int nc,
                         int K, int V, void* stream);
 

@@ -136,7 +136,10 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, h0=None, use_qk_l2nor
     decay_incl = torch.exp(diff.masked_fill(~incl, float("-inf")))
     T = torch.eye(L, device=q.device) + bc[..., :, None] * decay_strict * (kc @ kc.transpose(-1, -2))
     rhs = torch.cat((bc[..., None] * vc, (bc * torch.exp(G))[..., None] * kc), dim=-1)
-    W = torch.linalg.solve_triangular(T, rhs, upper=False, unitriangular=True)
+    # the inverse of the L x L unit-triangular factor once (a solve with L right-hand sides), then one product with
+    # the V + K columns: the solve against all V + K columns costs ten times the product
+    eye = torch.eye(L, device=q.device).expand_as(T)
+    W = torch.linalg.solve_triangular(T, eye, upper=False, unitriangular=True) @ rhs
     Wv, Wk = W[..., :V], W[..., V:]                                        # [.., L, V], [.., L, K]
     qk = decay_incl * (qc @ kc.transpose(-1, -2))                          # [.., L(t), L(i)]
     qe = torch.exp(G)[..., None] * qc                                      # e^{G_t} q_t
@@ -172,7 +175,7 @@ class _DeltaChain(torch.autograd.Function):
         B, N, nc, L, K = Wk.shape
         V = Wv.size(-1)
         bf, dev = torch.bfloat16, Wk.device
-        wk_neg = (-Wk).to(bf).contiguous()
+        wk_b = Wk.to(bf).contiguous()
         qe_b, ke_b, qk_b = qe.to(bf).contiguous(), ke.to(bf).contiguous(), qk.to(bf).contiguous()
         ket = ke_b.transpose(-1, -2).contiguous()
         wv, a32, h32 = Wv.float().contiguous(), a.float().contiguous(), h.float().contiguous()
@@ -181,11 +184,11 @@ class _DeltaChain(torch.autograd.Function):
         h_all = torch.empty((B, N, nc, K, V), dtype=bf, device=dev)
         h_final = torch.empty((B, N, K, V), dtype=torch.float32, device=dev)
         _lib.check(_lib.cuda_lib().lme_delta_chain_fwd(
-            wk_neg.data_ptr(), qe_b.data_ptr(), ket.data_ptr(), qk_b.data_ptr(), wv.data_ptr(), a32.data_ptr(),
+            wk_b.data_ptr(), qe_b.data_ptr(), ket.data_ptr(), qk_b.data_ptr(), wv.data_ptr(), a32.data_ptr(),
             h32.data_ptr(), y.data_ptr(), u_all.data_ptr(), h_all.data_ptr(), h_final.data_ptr(), B * N, nc, K, V,
             _lib.stream_ptr()), f"lme_delta_chain_fwd BN={B * N} nc={nc} K={K} V={V}")
         _lib.count_launch()
-        ctx.save_for_backward(wk_neg, qe_b, ke_b, qk_b, a32, u_all, h_all)
+        ctx.save_for_backward(wk_b, qe_b, ke_b, qk_b, a32, u_all, h_all)
         return y, h_final
 
     @staticmethod
@@ -193,20 +196,20 @@ class _DeltaChain(torch.autograd.Function):
         from . import _lib
         from .gemm import _bmm_kernel
 
-        wk_neg, qe_b, ke_b, qk_b, a32, u_all, h_all = ctx.saved_tensors
-        B, N, nc, L, K = wk_neg.shape
+        wk_b, qe_b, ke_b, qk_b, a32, u_all, h_all = ctx.saved_tensors
+        B, N, nc, L, K = wk_b.shape
         V = u_all.size(-1)
         bf, dev = torch.bfloat16, dy.device
         dy = dy.float().contiguous()
         qkt = qk_b.transpose(-1, -2).contiguous()
         qet = qe_b.transpose(-1, -2).contiguous()
-        wkt_neg = wk_neg.transpose(-1, -2).contiguous()
+        wkt = wk_b.transpose(-1, -2).contiguous()
         du_all = torch.empty((B, N, nc, L, V), dtype=bf, device=dev)
         dh_all = torch.empty((B, N, nc, K, V), dtype=bf, device=dev)
         dh0 = torch.empty((B, N, K, V), dtype=torch.float32, device=dev)
         dhf = None if dh_final is None else dh_final.float().contiguous()
         _lib.check(_lib.cuda_lib().lme_delta_chain_bwd(
-            qkt.data_ptr(), ke_b.data_ptr(), qet.data_ptr(), wkt_neg.data_ptr(), dy.data_ptr(), a32.data_ptr(),
+            qkt.data_ptr(), ke_b.data_ptr(), qet.data_ptr(), wkt.data_ptr(), dy.data_ptr(), a32.data_ptr(),
             _lib.ptr(dhf), du_all.data_ptr(), dh_all.data_ptr(), dh0.data_ptr(), B * N, nc, K, V,
             _lib.stream_ptr()), f"lme_delta_chain_bwd BN={B * N} nc={nc} K={K} V={V}")
         _lib.count_launch()
