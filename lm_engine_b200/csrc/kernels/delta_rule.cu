@@ -141,6 +141,19 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
     };
     stage_first(0);
     stage_second(0);
+    // W_v fragments (fp32, the initial value of the U accumulators) are fetched one chunk ahead into registers
+    float wv_next[4][4];
+    auto fetch_wv = [&](int c) {
+        const float* wv = p.wv + (bn * nc + c) * L * V + v0;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = nh * 32 + nt * 8 + 2 * t;
+            const float2 lo = *reinterpret_cast<const float2*>(wv + static_cast<long long>(mi * 16 + g) * V + col);
+            const float2 hi = *reinterpret_cast<const float2*>(wv + static_cast<long long>(mi * 16 + g + 8) * V + col);
+            wv_next[nt][0] = lo.x; wv_next[nt][1] = lo.y; wv_next[nt][2] = hi.x; wv_next[nt][3] = hi.y;
+        }
+    };
+    fetch_wv(0);
 
     for (int c = 0; c < nc; ++c) {
         const long long chunk = bn * nc + c;
@@ -149,15 +162,14 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
         __syncthreads();
         // U = W_v - W_k h,  y = Q_e h (+ QK U below)
         float accU[4][4], accY[4][4];
-        const float* wv = p.wv + chunk * L * V + v0;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = nh * 32 + nt * 8 + 2 * t;
-            const float2 lo = *reinterpret_cast<const float2*>(wv + static_cast<long long>(mi * 16 + g) * V + col);
-            const float2 hi = *reinterpret_cast<const float2*>(wv + static_cast<long long>(mi * 16 + g + 8) * V + col);
-            accU[nt][0] = lo.x; accU[nt][1] = lo.y; accU[nt][2] = hi.x; accU[nt][3] = hi.y;
-            accY[nt][0] = accY[nt][1] = accY[nt][2] = accY[nt][3] = 0.f;
-        }
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                accU[nt][i] = wv_next[nt][i];
+                accY[nt][i] = 0.f;
+            }
+        if (c + 1 < nc) fetch_wv(c + 1);
         warp_mma<4, true>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
         warp_mma<4>(accY, sQe, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
         __nv_bfloat16* ug = p.u_all + chunk * L * V + v0;
@@ -250,16 +262,28 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
     };
     stage_first(nc - 1);
     stage_second(nc - 1);
+    // the fp32 dy tile of a chunk is fetched one chunk ahead into registers (L * VS / 256 = 16 values per thread)
+    float dy_next[L * VS / 256];
+    auto fetch_dy = [&](int c) {
+        const float* dyg = p.dy + (bn * nc + c) * L * V + v0;
+#pragma unroll
+        for (int j = 0; j < L * VS / 256; ++j) {
+            const int i = threadIdx.x + j * 256;
+            dy_next[j] = dyg[static_cast<long long>(i / VS) * V + i % VS];
+        }
+    };
+    fetch_dy(nc - 1);
 
     for (int c = nc - 1; c >= 0; --c) {
         const long long chunk = bn * nc + c;
         cp_wait<1>();
         state_to_smem_and_global<K>(dh, sDh, p.dh_all + chunk * K * V + v0, V, warp, g, t);
-        const float* dyg = p.dy + chunk * L * V + v0;
-        for (int i = threadIdx.x; i < L * VS; i += blockDim.x) {
-            const int row = i / VS, col = i % VS;
-            sDy[col * (L + PADE) + row] = __float2bfloat16(dyg[static_cast<long long>(row) * V + col]);
+#pragma unroll
+        for (int j = 0; j < L * VS / 256; ++j) {
+            const int i = threadIdx.x + j * 256;
+            sDy[(i % VS) * (L + PADE) + i / VS] = __float2bfloat16(dy_next[j]);
         }
+        if (c > 0) fetch_dy(c - 1);
         __syncthreads();
         // dU = QK^T dy + K_e dh
         float accDU[4][4];

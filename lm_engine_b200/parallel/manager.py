@@ -357,6 +357,13 @@ class ProcessGroupManager:
 
     @staticmethod
     def destroy_process_groups() -> None:
+        # symmetric-memory contexts are keyed by their group: none may outlive it
+        import sys
+
+        for name in ("expert_exchange", "gathered_attention"):
+            mod = sys.modules.get(f"{__package__}.{name}")
+            if mod is not None:
+                mod._CONTEXTS.clear()
         if dist.is_initialized() and _S.owns_pg:
             dist.barrier()
             dist.destroy_process_group()
