@@ -10,8 +10,9 @@
 // (the parameter gradients are batched GEMMs over all chunks on what the two kernels leave behind: U_c, dU_c, the
 // state entering each chunk and the gradient leaving it).
 //
-// The columns of h are independent, so a CTA owns 64 columns of one (batch, head) and walks the chunks alone.  The
-// state lives in mma.sync accumulator registers in fp32 for the whole sequence (8 warps x K/8 rows x 64 columns);
+// The columns of h are independent, so a CTA owns VS = 64 (or 32, when that is needed to fill the GPU) columns of one
+// (batch, head) and walks the chunks alone.  The
+// state lives in mma.sync accumulator registers in fp32 for the whole sequence (8 warps x K/8 rows x VS columns);
 // per chunk it is rounded to bf16 once into shared memory as the B operand of the products that read it.  All
 // products are mma.sync m16n8k16 (bf16 in, fp32 accumulate) on operands staged by cp.async; the operands of the next
 // chunk are fetched while the current one is multiplied.  tcgen05 is deliberately not used: a chunk is four products
@@ -32,7 +33,6 @@ using m2::mma16816;
 using m2::pack2;
 
 constexpr int L = 64;    // rows of a chunk
-constexpr int VS = 64;   // state columns per CTA
 constexpr int PADE = 8;  // bf16 elements appended to every shared-memory row (spreads the rows over the banks)
 
 // C[16 x 8 NT] += A[m0 .. m0 + 16)[0 .. kd) * B[n0 .. n0 + 8 NT)[0 .. kd)^T; A row-major (lda), B n-major (ldb).
@@ -86,13 +86,13 @@ struct BwdArgs {
 };
 
 // state fragment (mt, nt, i) of warp w, lane (g, t): row = w * (K / 8) + mt * 16 + g + 8 * (i >> 1), col = nt * 8 + 2 t + (i & 1)
-template <int K>
-__device__ __forceinline__ void state_to_smem_and_global(const float (&h)[K / 128][8][4], __nv_bfloat16* sB,
+template <int K, int VS>
+__device__ __forceinline__ void state_to_smem_and_global(const float (&h)[K / 128][VS / 8][4], __nv_bfloat16* sB,
                                                          __nv_bfloat16* gdst, int V, int warp, int g, int t) {
 #pragma unroll
     for (int mt = 0; mt < K / 128; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = warp * (K / 8) + mt * 16 + g + 8 * half, col = nt * 8 + 2 * t;
@@ -103,8 +103,9 @@ __device__ __forceinline__ void state_to_smem_and_global(const float (&h)[K / 12
             }
 }
 
-template <int K>
+template <int K, int VS>
 __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
+    constexpr int NTL = VS / 16;   // 8-column tiles of an [L, VS] product per warp (two warps share a 16-row block)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sWk = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sQe = sWk + L * (K + PADE);
@@ -113,15 +114,15 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
     __nv_bfloat16* sH = sQk + L * (L + PADE);
     __nv_bfloat16* sU = sH + VS * (K + PADE);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int mi = warp & 3, nh = warp >> 2;                 // 16-row block and 32-column half of an [L, VS] product
+    const int mi = warp & 3, nh = warp >> 2;                 // 16-row block and column half of an [L, VS] product
     const long long bn = blockIdx.y;
     const int v0 = blockIdx.x * VS, V = p.V, nc = p.nc;
 
-    float h[K / 128][8][4];
+    float h[K / 128][VS / 8][4];
 #pragma unroll
     for (int mt = 0; mt < K / 128; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int row = warp * (K / 8) + mt * 16 + g + 8 * (i >> 1), col = nt * 8 + 2 * t + (i & 1);
@@ -142,12 +143,12 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
     stage_first(0);
     stage_second(0);
     // W_v fragments (fp32, the initial value of the U accumulators) are fetched one chunk ahead into registers
-    float wv_next[4][4];
+    float wv_next[NTL][4];
     auto fetch_wv = [&](int c) {
         const float* wv = p.wv + (bn * nc + c) * L * V + v0;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = nh * 32 + nt * 8 + 2 * t;
+        for (int nt = 0; nt < NTL; ++nt) {
+            const int col = nh * (VS / 2) + nt * 8 + 2 * t;
             const float2 lo = *reinterpret_cast<const float2*>(wv + static_cast<long long>(mi * 16 + g) * V + col);
             const float2 hi = *reinterpret_cast<const float2*>(wv + static_cast<long long>(mi * 16 + g + 8) * V + col);
             wv_next[nt][0] = lo.x; wv_next[nt][1] = lo.y; wv_next[nt][2] = hi.x; wv_next[nt][3] = hi.y;
@@ -158,26 +159,26 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
     for (int c = 0; c < nc; ++c) {
         const long long chunk = bn * nc + c;
         cp_wait<1>();                                        // W_k, Q_e of this chunk have landed (for this thread)
-        state_to_smem_and_global<K>(h, sH, p.h_all + chunk * K * V + v0, V, warp, g, t);
+        state_to_smem_and_global<K, VS>(h, sH, p.h_all + chunk * K * V + v0, V, warp, g, t);
         __syncthreads();
         // U = W_v - W_k h,  y = Q_e h (+ QK U below)
-        float accU[4][4], accY[4][4];
+        float accU[NTL][4], accY[NTL][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 accU[nt][i] = wv_next[nt][i];
                 accY[nt][i] = 0.f;
             }
         if (c + 1 < nc) fetch_wv(c + 1);
-        warp_mma<4, true>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
-        warp_mma<4>(accY, sQe, K + PADE, mi * 16, sH, K + PADE, nh * 32, K, g, t);
+        warp_mma<NTL, true>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * (VS / 2), K, g, t);
+        warp_mma<NTL>(accY, sQe, K + PADE, mi * 16, sH, K + PADE, nh * (VS / 2), K, g, t);
         __nv_bfloat16* ug = p.u_all + chunk * L * V + v0;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int row = mi * 16 + g + 8 * half, col = nh * 32 + nt * 8 + 2 * t;
+                const int row = mi * 16 + g + 8 * half, col = nh * (VS / 2) + nt * 8 + 2 * t;
                 const float x0 = accU[nt][2 * half], x1 = accU[nt][2 * half + 1];
                 sU[col * (L + PADE) + row] = __float2bfloat16(x0);
                 sU[(col + 1) * (L + PADE) + row] = __float2bfloat16(x1);
@@ -187,11 +188,11 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
         if (c + 1 < nc) stage_first(c + 1); else cp_commit();
         cp_wait<1>();                                        // K_e^T, QK of this chunk have landed
         __syncthreads();
-        warp_mma<4>(accY, sQk, L + PADE, mi * 16, sU, L + PADE, nh * 32, L, g, t);
+        warp_mma<NTL>(accY, sQk, L + PADE, mi * 16, sU, L + PADE, nh * (VS / 2), L, g, t);
         float* yg = p.y + chunk * L * V + v0;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = nh * 32 + nt * 8 + 2 * t;
+        for (int nt = 0; nt < NTL; ++nt) {
+            const int col = nh * (VS / 2) + nt * 8 + 2 * t;
             *reinterpret_cast<float2*>(yg + static_cast<long long>(mi * 16 + g) * V + col) =
                 make_float2(accY[nt][0], accY[nt][1]);
             *reinterpret_cast<float2*>(yg + static_cast<long long>(mi * 16 + g + 8) * V + col) =
@@ -202,10 +203,10 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
 #pragma unroll
         for (int mt = 0; mt < K / 128; ++mt) {
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) h[mt][nt][i] *= a;
-            warp_mma<8>(h[mt], sKet, L + PADE, warp * (K / 8) + mt * 16, sU, L + PADE, 0, L, g, t);
+            warp_mma<VS / 8>(h[mt], sKet, L + PADE, warp * (K / 8) + mt * 16, sU, L + PADE, 0, L, g, t);
         }
         __syncthreads();                                     // K_e^T, QK, U are free
         if (c + 1 < nc) stage_second(c + 1); else cp_commit();
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
 #pragma unroll
     for (int mt = 0; mt < K / 128; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = warp * (K / 8) + mt * 16 + g + 8 * half, col = nt * 8 + 2 * t;
@@ -223,8 +224,9 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
             }
 }
 
-template <int K>
+template <int K, int VS>
 __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
+    constexpr int NTL = VS / 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQkt = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sKe = sQkt + L * (L + PADE);
@@ -238,11 +240,11 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
     const long long bn = blockIdx.y;
     const int v0 = blockIdx.x * VS, V = p.V, nc = p.nc;
 
-    float dh[K / 128][8][4];
+    float dh[K / 128][VS / 8][4];
 #pragma unroll
     for (int mt = 0; mt < K / 128; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int row = warp * (K / 8) + mt * 16 + g + 8 * (i >> 1), col = nt * 8 + 2 * t + (i & 1);
@@ -277,7 +279,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
     for (int c = nc - 1; c >= 0; --c) {
         const long long chunk = bn * nc + c;
         cp_wait<1>();
-        state_to_smem_and_global<K>(dh, sDh, p.dh_all + chunk * K * V + v0, V, warp, g, t);
+        state_to_smem_and_global<K, VS>(dh, sDh, p.dh_all + chunk * K * V + v0, V, warp, g, t);
 #pragma unroll
         for (int j = 0; j < L * VS / 256; ++j) {
             const int i = threadIdx.x + j * 256;
@@ -286,17 +288,17 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
         if (c > 0) fetch_dy(c - 1);
         __syncthreads();
         // dU = QK^T dy + K_e dh
-        float accDU[4][4];
+        float accDU[NTL][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) accDU[nt][0] = accDU[nt][1] = accDU[nt][2] = accDU[nt][3] = 0.f;
-        warp_mma<4>(accDU, sQkt, L + PADE, mi * 16, sDy, L + PADE, nh * 32, L, g, t);
-        warp_mma<4>(accDU, sKe, K + PADE, mi * 16, sDh, K + PADE, nh * 32, K, g, t);
+        for (int nt = 0; nt < NTL; ++nt) accDU[nt][0] = accDU[nt][1] = accDU[nt][2] = accDU[nt][3] = 0.f;
+        warp_mma<NTL>(accDU, sQkt, L + PADE, mi * 16, sDy, L + PADE, nh * (VS / 2), L, g, t);
+        warp_mma<NTL>(accDU, sKe, K + PADE, mi * 16, sDh, K + PADE, nh * (VS / 2), K, g, t);
         __nv_bfloat16* dug = p.du_all + chunk * L * V + v0;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int row = mi * 16 + g + 8 * half, col = nh * 32 + nt * 8 + 2 * t;
+                const int row = mi * 16 + g + 8 * half, col = nh * (VS / 2) + nt * 8 + 2 * t;
                 const float x0 = accDU[nt][2 * half], x1 = accDU[nt][2 * half + 1];
                 sDu[col * (L + PADE) + row] = __float2bfloat16(x0);
                 sDu[(col + 1) * (L + PADE) + row] = __float2bfloat16(x1);
@@ -311,11 +313,11 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
 #pragma unroll
         for (int mt = 0; mt < K / 128; ++mt) {
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dh[mt][nt][i] *= a;
-            warp_mma<8>(dh[mt], sQet, L + PADE, warp * (K / 8) + mt * 16, sDy, L + PADE, 0, L, g, t);
-            warp_mma<8, true>(dh[mt], sWkt, L + PADE, warp * (K / 8) + mt * 16, sDu, L + PADE, 0, L, g, t);
+            warp_mma<VS / 8>(dh[mt], sQet, L + PADE, warp * (K / 8) + mt * 16, sDy, L + PADE, 0, L, g, t);
+            warp_mma<VS / 8, true>(dh[mt], sWkt, L + PADE, warp * (K / 8) + mt * 16, sDu, L + PADE, 0, L, g, t);
         }
         __syncthreads();
         if (c > 0) stage_second(c - 1); else cp_commit();
@@ -324,7 +326,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
 #pragma unroll
     for (int mt = 0; mt < K / 128; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < VS / 8; ++nt)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = warp * (K / 8) + mt * 16 + g + 8 * half, col = nt * 8 + 2 * t;
@@ -333,29 +335,29 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
             }
 }
 
-template <int K>
+template <int K, int VS>
 constexpr int fwd_smem_bytes() {
     return 2 * (2 * L * (K + PADE) + K * (L + PADE) + L * (L + PADE) + VS * (K + PADE) + VS * (L + PADE));
 }
-template <int K>
+template <int K, int VS>
 constexpr int bwd_smem_bytes() {
     return 2 * (L * (L + PADE) + L * (K + PADE) + 2 * K * (L + PADE) + 2 * VS * (L + PADE) + VS * (K + PADE));
 }
 
-template <int K>
+template <int K, int VS>
 static int launch_fwd(const FwdArgs& p, int BN, cudaStream_t st) {
-    if (cudaFuncSetAttribute(delta_chain_fwd_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             fwd_smem_bytes<K>()) != cudaSuccess)
+    if (cudaFuncSetAttribute(delta_chain_fwd_kernel<K, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fwd_smem_bytes<K, VS>()) != cudaSuccess)
         return LME_ERR_LAUNCH;
-    delta_chain_fwd_kernel<K><<<dim3(p.V / VS, BN), 256, fwd_smem_bytes<K>(), st>>>(p);
+    delta_chain_fwd_kernel<K, VS><<<dim3(p.V / VS, BN), 256, fwd_smem_bytes<K, VS>(), st>>>(p);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
-template <int K>
+template <int K, int VS>
 static int launch_bwd(const BwdArgs& p, int BN, cudaStream_t st) {
-    if (cudaFuncSetAttribute(delta_chain_bwd_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             bwd_smem_bytes<K>()) != cudaSuccess)
+    if (cudaFuncSetAttribute(delta_chain_bwd_kernel<K, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             bwd_smem_bytes<K, VS>()) != cudaSuccess)
         return LME_ERR_LAUNCH;
-    delta_chain_bwd_kernel<K><<<dim3(p.V / VS, BN), 256, bwd_smem_bytes<K>(), st>>>(p);
+    delta_chain_bwd_kernel<K, VS><<<dim3(p.V / VS, BN), 256, bwd_smem_bytes<K, VS>(), st>>>(p);
     return cudaGetLastError() == cudaSuccess ? LME_OK : LME_ERR_LAUNCH;
 }
 
@@ -363,7 +365,7 @@ static int launch_bwd(const BwdArgs& p, int BN, cudaStream_t st) {
 }  // namespace lme
 
 static int delta_chain_check(int BN, int nc, int K, int V) {
-    if (BN <= 0 || BN > 65535 || nc <= 0 || (K != 128 && K != 256) || V <= 0 || V % lme::dr::VS) return LME_ERR_SHAPE;
+    if (BN <= 0 || BN > 65535 || nc <= 0 || (K != 128 && K != 256) || V <= 0 || V % 64) return LME_ERR_SHAPE;
     return LME_OK;
 }
 
@@ -376,7 +378,10 @@ extern "C" int lme_delta_chain_fwd(const void* wk, const void* qe, const void* k
                        static_cast<const bf*>(qk), wv, a, h0, y, static_cast<bf*>(u_all), static_cast<bf*>(h_all),
                        h_final, nc, V};
     auto st = static_cast<cudaStream_t>(stream);
-    return K == 256 ? lme::dr::launch_fwd<256>(p, BN, st) : lme::dr::launch_fwd<128>(p, BN, st);
+    // 64-column slices unless they leave most SMs without a CTA
+    const bool narrow = static_cast<long long>(BN) * (V / 64) < 100;
+    if (K == 256) return narrow ? lme::dr::launch_fwd<256, 32>(p, BN, st) : lme::dr::launch_fwd<256, 64>(p, BN, st);
+    return narrow ? lme::dr::launch_fwd<128, 32>(p, BN, st) : lme::dr::launch_fwd<128, 64>(p, BN, st);
 }
 
 extern "C" int lme_delta_chain_bwd(const void* qkt, const void* ke, const void* qet, const void* wkt,
@@ -388,5 +393,7 @@ extern "C" int lme_delta_chain_bwd(const void* qkt, const void* ke, const void* 
                        static_cast<const bf*>(wkt), dy, a, dh_final, static_cast<bf*>(du_all),
                        static_cast<bf*>(dh_all), dh0, nc, V};
     auto st = static_cast<cudaStream_t>(stream);
-    return K == 256 ? lme::dr::launch_bwd<256>(p, BN, st) : lme::dr::launch_bwd<128>(p, BN, st);
+    const bool narrow = static_cast<long long>(BN) * (V / 64) < 100;
+    if (K == 256) return narrow ? lme::dr::launch_bwd<256, 32>(p, BN, st) : lme::dr::launch_bwd<256, 64>(p, BN, st);
+    return narrow ? lme::dr::launch_bwd<128, 32>(p, BN, st) : lme::dr::launch_bwd<128, 64>(p, BN, st);
 }

@@ -29,7 +29,9 @@ def _operands(B, N, nc, K, V, seed=0):
 
 
 @pytest.mark.parametrize("B,N,nc,K,V", [(1, 2, 1, 128, 64), (2, 3, 5, 256, 128), (1, 1, 16, 256, 512),
-                                        (2, 2, 3, 128, 192)])
+                                        (2, 2, 3, 128, 192),
+                                        # enough (batch, head, 64-column slice) triples for the 64-column kernels
+                                        (4, 4, 2, 128, 512), (4, 8, 3, 256, 256)])
 def test_chain_kernels_match_block_loop(B, N, nc, K, V):
     from lm_engine_b200.ops import _lib
     from lm_engine_b200.ops.recurrence import _DeltaChain, delta_chain_kernel_usable, delta_chain_reference
