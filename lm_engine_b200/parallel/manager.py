@@ -357,15 +357,19 @@ class ProcessGroupManager:
 
     @staticmethod
     def destroy_process_groups() -> None:
-        # symmetric-memory contexts are keyed by their group: none may outlive it
         import sys
 
-        for name in ("expert_exchange", "gathered_attention"):
-            mod = sys.modules.get(f"{__package__}.{name}")
-            if mod is not None:
-                mod._CONTEXTS.clear()
         if dist.is_initialized() and _S.owns_pg:
             dist.barrier()
+        # symmetric-memory contexts are keyed by their group: none may outlive it (freed behind the barrier, when no
+        # peer kernel can still be reading them)
+        for name in ("expert_exchange", "gathered_attention"):
+            mod = sys.modules.get(f"{__package__}.{name}")
+            if mod is not None and mod._CONTEXTS:
+                if torch.cuda.is_available():
+                    torch.cuda.synchronize()
+                mod._CONTEXTS.clear()
+        if dist.is_initialized() and _S.owns_pg:
             dist.destroy_process_group()
         _S.reset()
 
