@@ -212,6 +212,31 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __n
     }
 }
 
+// The same on rows grouped in 128-row tiles of which only those with tile_group[tile] >= 0 hold data (the padded
+// per-expert layout of the grouped GEMMs): one CTA per tile, tiles without an expert are not touched.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_tiles_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                        __nv_bfloat16* __restrict__ dx, int I8, const int* __restrict__ tile_group) {
+    if (tile_group[blockIdx.x] < 0) return;
+    const long long first = static_cast<long long>(blockIdx.x) * 128 * I8;
+    for (int u = threadIdx.x; u < 128 * I8; u += blockDim.x) {
+        const long long i = first + u;
+        float t0[8], t1[8], g[8], o0[8], o1[8];
+        load8(x + i * 16, t0);
+        load8(x + i * 16 + 8, t1);
+        load8(dy + i * 8, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float gate = j < 4 ? t0[2 * j] : t1[2 * j - 8], up = j < 4 ? t0[2 * j + 1] : t1[2 * j - 7];
+            const float s = 1.f / (1.f + __expf(-gate));
+            const float dg = g[j] * up * s * (1.f + gate * (1.f - s)), du = g[j] * gate * s;
+            if (j < 4) { o0[2 * j] = dg; o0[2 * j + 1] = du; } else { o1[2 * j - 8] = dg; o1[2 * j - 7] = du; }
+        }
+        store8(dx + i * 16, o0);
+        store8(dx + i * 16 + 8, o1);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- QKV split + RoPE
 // qkv [T, Hkv, (G+2)*D] (per KV head: G query heads, then K, then V)  <->  q [T, Hkv*G, D], k [T, Hkv, D], v [T, Hkv, D]
 // Rotation (NeoX half-rotation) on the last `rd` channels of each q / k head with angle table cos/sin [P, rd] (fp32,
@@ -527,6 +552,16 @@ extern "C" int lme_swiglu_bwd(const void* x, const void* dy, void* dx, long long
     swiglu_bwd_kernel<<<grid_for(n8, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
         static_cast<__nv_bfloat16*>(dx), n8);
+    return LME_LAUNCH_OK();
+}
+
+extern "C" int lme_swiglu_bwd_tiles(const void* x, const void* dy, void* dx, long long T, long long I,
+                                    const int* tile_group, void* stream) {
+    if (I % 8 || T % 128 || T / 128 > 0x7fffffffll) return LME_ERR_SHAPE;
+    if (T == 0 || I == 0) return LME_OK;
+    swiglu_bwd_tiles_kernel<<<static_cast<unsigned>(T / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx),
+        static_cast<int>(I / 8), tile_group);
     return LME_LAUNCH_OK();
 }
 

@@ -319,6 +319,9 @@ int lme_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* r
 // x [T, 2I] with (gate, up) interleaved -> y [T, I] = up * silu(gate)
 int lme_swiglu_fwd(const void* x, void* y, long long T, long long I, void* stream);
 int lme_swiglu_bwd(const void* x, const void* dy, void* dx, long long T, long long I, void* stream);
+// the same on 128-row tiles of which only those with tile_group[tile] >= 0 are read and written (T % 128 == 0)
+int lme_swiglu_bwd_tiles(const void* x, const void* dy, void* dx, long long T, long long I, const int* tile_group,
+                         void* stream);
 // fused QKV split + NeoX rotary embedding (inverse = 1: backward, packs dq/dk/dv into dqkv).  cos_t / sin_t are
 // [max_pos, rope_dim]; pos (optional) has T entries, else position = t % S.  A position outside the table sets the
 // status word (STATUS_BOUNDS) instead of reading out of bounds.

@@ -112,6 +112,7 @@ def cuda_lib() -> ctypes.CDLL:
             "lme_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
             "lme_swiglu_fwd": [P, P, L, L, P],
             "lme_swiglu_bwd": [P, P, P, L, L, P],
+            "lme_swiglu_bwd_tiles": [P, P, P, L, L, P, P],
             "lme_qkv_rope": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
             "lme_ce_stats": [P, L, P, P, P, P, I, I, I, P],
             "lme_ce_grad": [P, L, P, P, I, I, I, F, P, L, P],

@@ -48,12 +48,19 @@ def swiglu_packed(x: torch.Tensor) -> torch.Tensor:
     return swiglu_packed_reference(x)
 
 
-def swiglu_backward(preact: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
-    """d(preact) given the packed pre-activation and d(out) (used by the fused MLP op)."""
+def swiglu_backward(preact: torch.Tensor, dy: torch.Tensor, tile_group: torch.Tensor | None = None) -> torch.Tensor:
+    """d(preact) given the packed pre-activation and d(out) (used by the fused MLP op).  ``tile_group`` (int32, one
+    entry per 128 rows): only tiles with an entry >= 0 are read and written (the grouped GEMMs' padded layout)."""
     if preact.is_cuda and preact.dtype == torch.bfloat16:
         p2 = preact.reshape(-1, preact.size(-1))
         d2 = dy.reshape(p2.size(0), -1).contiguous()
         dx = torch.empty_like(p2)
+        if tile_group is not None and p2.size(0) == tile_group.numel() * 128:
+            _lib.check(_lib.cuda_lib().lme_swiglu_bwd_tiles(p2.data_ptr(), d2.data_ptr(), dx.data_ptr(), p2.size(0),
+                                                            d2.size(1), tile_group.data_ptr(), _lib.stream_ptr()),
+                       "lme_swiglu_bwd_tiles")
+            _lib.count_launch()
+            return dx.view(preact.shape)
         _lib.check(_lib.cuda_lib().lme_swiglu_bwd(p2.data_ptr(), d2.data_ptr(), dx.data_ptr(), p2.size(0),
                                                   d2.size(1), _lib.stream_ptr()), "lme_swiglu_bwd")
         _lib.count_launch()

@@ -154,7 +154,7 @@ class _GroupedLinear(torch.autograd.Function):
         E, N, K = weight.shape
         dy = dy.contiguous()
         if ctx.swiglu:
-            dy = swiglu_backward(pre, dy)
+            dy = swiglu_backward(pre, dy, layout.tile_group)
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dx = dy @ W[e]: W[e] is [N, K] = the MN-major operand whose contraction rows are offset by e * N

@@ -19,9 +19,12 @@ One layer call (csrc/kernels/ep_exchange.cu documents the flags):
 
 All row traffic is pulled with peer loads (scattered peer stores of rows measured at 0.47 of the peer-copy rate,
 peer loads at 0.8).  The backward pass mirrors the forward pass on a second set of buffers.  An owner's layout holds
-``capacity_factor * tokens * top_k`` rows (``LME_EP_CAPACITY_FACTOR``, default 2, at most the group size = the worst case): a static bound is the price
-of keeping the host out of the loop.  Overflow is detected on the device (every rank sees it in the same table), the
-overflowing rows are dropped and the status word makes the training loop raise at the end of the step.
+``capacity_factor * tokens * top_k`` rows.  The default factor is the group size, the worst case (every token of every
+rank routed to one owner), so nothing can overflow; no kernel touches rows of tiles without an expert, so the unused
+capacity costs address space and allocator memory, not time.  ``LME_EP_CAPACITY_FACTOR`` lowers it (a router in
+its first steps was seen to send more than twice the mean to one of four owners): overflow is then detected on the
+device (every rank sees it in the same table), the overflowing rows are dropped and the status word makes the
+training loop raise at the end of the step.
 """
 
 from __future__ import annotations
@@ -254,7 +257,7 @@ class _Collect(torch.autograd.Function):
 
 
 def capacity_rows(assignments: int, local_experts: int, world: int) -> int:
-    factor = min(max(float(os.environ.get("LME_EP_CAPACITY_FACTOR", "2")), 1.0), float(world))
+    factor = min(max(float(os.environ.get("LME_EP_CAPACITY_FACTOR", str(world))), 1.0), float(world))
     rows = int(math.ceil(factor * assignments))
     return (rows + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS + local_experts * TILE_ROWS
 
