@@ -44,3 +44,18 @@ def test_moe_topk_then_softmax():
 
 def test_moe_softmax_then_topk_with_shared_expert():
     _check(_moe_cfg(False, shared=32))
+
+
+def test_expert_exchange_capacity_defaults_to_the_worst_case(monkeypatch):
+    """Rows an owner can receive: every assignment of every rank by default (nothing can overflow); the switch lowers it
+    but never below the rank's own assignments, and the result is whole 128-row tiles plus one tile per local expert."""
+    from lm_engine_b200.parallel import expert_exchange as xx
+
+    monkeypatch.delenv("LME_EP_CAPACITY_FACTOR", raising=False)
+    assert xx.capacity_rows(1000, 4, 8) == 8 * 1000 // 128 * 128 + 128 + 4 * 128
+    monkeypatch.setenv("LME_EP_CAPACITY_FACTOR", "2")
+    assert xx.capacity_rows(1000, 4, 8) == 2048 + 4 * 128
+    monkeypatch.setenv("LME_EP_CAPACITY_FACTOR", "0.1")
+    assert xx.capacity_rows(1024, 2, 4) == 1024 + 2 * 128
+    monkeypatch.setenv("LME_EP_CAPACITY_FACTOR", "100")
+    assert xx.capacity_rows(1024, 2, 4) == 4096 + 2 * 128
