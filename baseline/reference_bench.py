@@ -99,7 +99,11 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
 
     try:
         tok_dir = _make_tokenizer_dir()
-        kernels = [k for k in os.environ.get("LME_REF_KERNELS", "flash_attention_2").split(",") if k]
+        # The reference's stock path with no kernel flag (attention through scaled_dot_product_attention) is its
+        # fastest configuration on B200 with the packages of this image: 818 ms per Llama-3-8B step on one GPU
+        # against 881 ms with `flash_attention_2` (what its YAMLs enable, flash-attn 2.8) and 866 ms with the QuACK
+        # flags added; LME_REF_KERNELS selects the others.
+        kernels = [k for k in os.environ.get("LME_REF_KERNELS", "").split(",") if k]
         cfg = training_config(a.model, a.seq, a.mbs, a.steps, kernels, tok_dir)
         cfg["distributed_args"].pop("expert_parallel_world_size", None)
         # With this torch version the reference's default (non-reentrant) block checkpointing raises CheckpointError:
@@ -157,6 +161,7 @@ def run_reference(a, training_config, ClockSampler) -> dict | None:
             resident = _Batches(vocab, a.seq, a.mbs, dl_rank, dl_world, device=device)
             resident.cursor = host_iter.cursor
             staged = iter([next(resident) for _ in range(a.steps * ga)])
+            host_iter.cursor = resident.cursor        # the end-to-end phase reads batches the model has not seen
             sampler = ClockSampler(torch.cuda.current_device())
             barrier()
             if rank == 0:
