@@ -275,10 +275,47 @@ def gated_delta_rule_scan(q, k, v, g, beta, scale=None, h0=None, use_qk_l2norm: 
     return torch.stack(ys, dim=1).to(dtype), h
 
 
+def linear_attention_on_chain(q, k, v, h0=None, attention_multiplier: float = 1.0, chain=None):
+    """Linear attention as a special case of the delta-rule chain: with ``W_k = 0`` and ``a = 1`` the chain computes
+    ``y = Q h + strict_tril(Q K^T) V`` and ``h <- h + K^T V`` per 64-step block, so the forward and backward chain
+    kernels serve this mixer as well (key width zero-padded to 128 / 256, value width to a multiple of 64).  ``chain``
+    replaces the kernels by another implementation of the same recurrences (the PyTorch block loop in CPU tests)."""
+    B, S, _, K = q.shape
+    V = v.size(-1)
+    N = max(q.size(2), k.size(2), v.size(2))
+    q, k, v = _rep(q, N, 2), _rep(k, N, 2), _rep(v, N, 2)
+    L = CHUNK
+    Kp = 128 if K <= 128 else 256
+    Vp = (V + 63) // 64 * 64
+    pad = (L - S % L) % L
+    pad_fn = torch.nn.functional.pad
+    qf = pad_fn(q.float(), (0, Kp - K, 0, 0, 0, pad))
+    kf = pad_fn(k.float(), (0, Kp - K, 0, 0, 0, pad))
+    vf = pad_fn(v.float(), (0, Vp - V, 0, 0, 0, pad))
+    nc = (S + pad) // L
+
+    def blocks(t):   # [B, S, N, X] -> [B, N, nc, L, X]
+        return t.view(B, nc, L, N, -1).permute(0, 3, 1, 2, 4)
+
+    qc, kc, vc = blocks(qf), blocks(kf), blocks(vf)
+    strict = torch.ones(L, L, dtype=torch.bool, device=q.device).tril(-1)
+    qk = (qc @ kc.transpose(-1, -2)).masked_fill(~strict, 0.0)
+    h = torch.zeros(B, N, Kp, Vp, dtype=torch.float32, device=q.device)
+    if h0 is not None:
+        h = pad_fn(h0.float(), (0, Vp - V, 0, Kp - K))
+    ones = torch.ones(B, N, nc, dtype=torch.float32, device=q.device)
+    y, h = (chain or _DeltaChain.apply)(torch.zeros_like(kc), vc, qc, qk, kc, ones, h)
+    y = y.permute(0, 2, 3, 1, 4).reshape(B, nc * L, N, Vp)[:, :S, :, :V]
+    return (y * attention_multiplier).to(q.dtype), h[:, :, :K, :V]
+
+
 def linear_attention(q, k, v, h0=None, attention_multiplier: float = 1.0):
-    """Token recurrence for short inputs (decode), chunk-parallel form otherwise."""
+    """Token recurrence for short inputs (decode); on CUDA the chain kernels of the delta rule (key width up to 256);
+    else the chunk-parallel PyTorch form."""
     if q.size(1) < 8:
         return linear_attention_scan(q, k, v, h0, attention_multiplier)
+    if q.is_cuda and q.size(-1) <= 256 and q.size(0) * max(q.size(2), k.size(2), v.size(2)) <= 65535:
+        return linear_attention_on_chain(q, k, v, h0, attention_multiplier)
     return linear_attention_chunked(q, k, v, h0, attention_multiplier)
 
 

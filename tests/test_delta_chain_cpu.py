@@ -53,3 +53,25 @@ def test_dispatcher_uses_the_block_loop_on_cpu():
     y, h = rec.delta_chain(*ops)
     y2, h2 = rec.delta_chain_reference(*ops)
     assert torch.equal(y, y2) and torch.equal(h, h2)
+
+
+def test_linear_attention_is_the_chain_without_correction():
+    """``W_k = 0``, ``a = 1`` turns the delta-rule chain into linear attention: checked against the token recurrence
+    (values, final state and gradients) with the PyTorch block loop standing in for the kernels."""
+    from lm_engine_b200.ops import recurrence as rec
+
+    torch.manual_seed(0)
+    B, S, N, K, V = 2, 150, 2, 24, 40
+    q, k, v = torch.randn(B, S, N, K) * 0.3, torch.randn(B, S, N, K) * 0.3, torch.randn(B, S, N, V)
+    h0 = torch.randn(B, N, K, V) * 0.1
+    a = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    b = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    y, h = rec.linear_attention_on_chain(*a, h0=h0, attention_multiplier=0.7, chain=rec.delta_chain_reference)
+    y2, h2 = rec.linear_attention_scan(*b, h0=h0, attention_multiplier=0.7)
+    torch.testing.assert_close(y, y2, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(h, h2, rtol=1e-4, atol=1e-4)
+    w = torch.randn_like(y2)
+    (y * w).sum().backward()
+    (y2 * w).sum().backward()
+    for u, t in zip(a, b):
+        torch.testing.assert_close(u.grad, t.grad, rtol=1e-3, atol=1e-4)

@@ -92,3 +92,25 @@ def test_gated_delta_rule_on_kernels_matches_token_scan(S, K, V):
     (y2 * w).sum().backward()
     for name, u, t in zip("qkvgb", a, b):
         assert _rel(u.grad, t.grad) < 5e-2, (name, _rel(u.grad, t.grad))
+
+
+@pytest.mark.parametrize("S,K,V", [(300, 64, 64), (128, 16, 16), (520, 128, 96)])
+def test_linear_attention_on_chain_kernels_matches_token_scan(S, K, V):
+    from lm_engine_b200.ops import recurrence as rec
+
+    torch.manual_seed(S + K)
+    B, N = 2, 3
+    q, k = (torch.randn(B, S, N, K, device="cuda") * K ** -0.5 for _ in range(2))
+    v = torch.randn(B, S, N, V, device="cuda")
+    h0 = torch.randn(B, N, K, V, device="cuda") * 0.1
+    a = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    b = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    y, h = rec.linear_attention(*a, h0=h0, attention_multiplier=0.5)        # dispatcher: chain kernels
+    y2, h2 = rec.linear_attention_scan(*b, h0=h0, attention_multiplier=0.5)
+    assert y.shape == y2.shape and h.shape == h2.shape
+    assert _rel(y, y2) < 2e-2 and _rel(h, h2) < 2e-2, (_rel(y, y2), _rel(h, h2))
+    w = torch.randn_like(y2)
+    (y * w).sum().backward()
+    (y2 * w).sum().backward()
+    for name, u, t in zip("qkv", a, b):
+        assert _rel(u.grad, t.grad) < 4e-2, (name, _rel(u.grad, t.grad))
