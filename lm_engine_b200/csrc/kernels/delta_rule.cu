@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
 
     auto stage_first = [&](int c) {      // operands of the products with the state
         const long long o = (bn * nc + c) * L * K;
-        stage_tile(sWk, p.wk + o, L, K);
+        if (p.wk) stage_tile(sWk, p.wk + o, L, K);     // null: no correction term (linear attention)
         stage_tile(sQe, p.qe + o, L, K);
         cp_commit();
     };
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_fwd_kernel(FwdArgs p) {
                 accY[nt][i] = 0.f;
             }
         if (c + 1 < nc) fetch_wv(c + 1);
-        warp_mma<NTL, true>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * (VS / 2), K, g, t);
+        if (p.wk) warp_mma<NTL, true>(accU, sWk, K + PADE, mi * 16, sH, K + PADE, nh * (VS / 2), K, g, t);
         warp_mma<NTL>(accY, sQe, K + PADE, mi * 16, sH, K + PADE, nh * (VS / 2), K, g, t);
         __nv_bfloat16* ug = p.u_all + chunk * L * V + v0;
 #pragma unroll
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
     auto stage_second = [&](int c) {     // operands of the state-gradient update
         const long long o = (bn * nc + c) * K * L;
         stage_tile(sQet, p.qet + o, K, L);
-        stage_tile(sWkt, p.wkt + o, K, L);
+        if (p.wkt) stage_tile(sWkt, p.wkt + o, K, L);
         cp_commit();
     };
     stage_first(nc - 1);
@@ -317,7 +317,8 @@ __global__ void __launch_bounds__(256, 1) delta_chain_bwd_kernel(BwdArgs p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dh[mt][nt][i] *= a;
             warp_mma<VS / 8>(dh[mt], sQet, L + PADE, warp * (K / 8) + mt * 16, sDy, L + PADE, 0, L, g, t);
-            warp_mma<VS / 8, true>(dh[mt], sWkt, L + PADE, warp * (K / 8) + mt * 16, sDu, L + PADE, 0, L, g, t);
+            if (p.wkt)
+                warp_mma<VS / 8, true>(dh[mt], sWkt, L + PADE, warp * (K / 8) + mt * 16, sDu, L + PADE, 0, L, g, t);
         }
         __syncthreads();
         if (c > 0) stage_second(c - 1); else cp_commit();

@@ -139,7 +139,7 @@ int lme_moe_route_layout(const long long* selected, int total, int E, int* scrat
 // ket = K_e^T [BN][nc][K][64], qk [BN][nc][64][64]; fp32: wv [BN][nc][64][V], a [BN][nc], h0 [BN][K][V] or null.
 // Outputs: y fp32 [BN][nc][64][V], u_all bf16 [BN][nc][64][V], h_all bf16 [BN][nc][K][V] (state entering each chunk),
 // h_final fp32 [BN][K][V].  Backward operands (bf16): qkt = QK^T, ke [BN][nc][64][K], qet = Q_e^T [BN][nc][K][64],
-// wkt = W_k^T [BN][nc][K][64]; dy fp32; outputs du_all bf16, dh_all bf16 (gradient leaving each chunk), dh0 fp32.
+// wkt = W_k^T [BN][nc][K][64] (wk / wkt may be null: no correction term, the chain of linear attention); dy fp32; outputs du_all bf16, dh_all bf16 (gradient leaving each chunk), dh0 fp32.
 int lme_delta_chain_fwd(const void* wk, const void* qe, const void* ket, const void* qk, const float* wv,
                         const float* a, const float* h0, float* y, void* u_all, void* h_all, float* h_final, int BN,
                         int nc, int K, int V, void* stream);

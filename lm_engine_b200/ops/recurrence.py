@@ -172,10 +172,10 @@ class _DeltaChain(torch.autograd.Function):
     def forward(ctx, Wk, Wv, qe, qk, ke, a, h):
         from . import _lib
 
-        B, N, nc, L, K = Wk.shape
+        B, N, nc, L, K = qe.shape
         V = Wv.size(-1)
-        bf, dev = torch.bfloat16, Wk.device
-        wk_b = Wk.to(bf).contiguous()
+        bf, dev = torch.bfloat16, qe.device
+        wk_b = None if Wk is None else Wk.to(bf).contiguous()          # None: no correction term (linear attention)
         qe_b, ke_b, qk_b = qe.to(bf).contiguous(), ke.to(bf).contiguous(), qk.to(bf).contiguous()
         ket = ke_b.transpose(-1, -2).contiguous()
         wv, a32, h32 = Wv.float().contiguous(), a.float().contiguous(), h.float().contiguous()
@@ -184,11 +184,12 @@ class _DeltaChain(torch.autograd.Function):
         h_all = torch.empty((B, N, nc, K, V), dtype=bf, device=dev)
         h_final = torch.empty((B, N, K, V), dtype=torch.float32, device=dev)
         _lib.check(_lib.cuda_lib().lme_delta_chain_fwd(
-            wk_b.data_ptr(), qe_b.data_ptr(), ket.data_ptr(), qk_b.data_ptr(), wv.data_ptr(), a32.data_ptr(),
+            _lib.ptr(wk_b), qe_b.data_ptr(), ket.data_ptr(), qk_b.data_ptr(), wv.data_ptr(), a32.data_ptr(),
             h32.data_ptr(), y.data_ptr(), u_all.data_ptr(), h_all.data_ptr(), h_final.data_ptr(), B * N, nc, K, V,
             _lib.stream_ptr()), f"lme_delta_chain_fwd BN={B * N} nc={nc} K={K} V={V}")
         _lib.count_launch()
-        ctx.save_for_backward(wk_b, qe_b, ke_b, qk_b, a32, u_all, h_all)
+        ctx.has_wk = wk_b is not None
+        ctx.save_for_backward(*([wk_b] if ctx.has_wk else []), qe_b, ke_b, qk_b, a32, u_all, h_all)
         return y, h_final
 
     @staticmethod
@@ -196,20 +197,22 @@ class _DeltaChain(torch.autograd.Function):
         from . import _lib
         from .gemm import _bmm_kernel
 
-        wk_b, qe_b, ke_b, qk_b, a32, u_all, h_all = ctx.saved_tensors
-        B, N, nc, L, K = wk_b.shape
+        saved = list(ctx.saved_tensors)
+        wk_b = saved.pop(0) if ctx.has_wk else None
+        qe_b, ke_b, qk_b, a32, u_all, h_all = saved
+        B, N, nc, L, K = qe_b.shape
         V = u_all.size(-1)
         bf, dev = torch.bfloat16, dy.device
         dy = dy.float().contiguous()
         qkt = qk_b.transpose(-1, -2).contiguous()
         qet = qe_b.transpose(-1, -2).contiguous()
-        wkt = wk_b.transpose(-1, -2).contiguous()
+        wkt = None if wk_b is None else wk_b.transpose(-1, -2).contiguous()
         du_all = torch.empty((B, N, nc, L, V), dtype=bf, device=dev)
         dh_all = torch.empty((B, N, nc, K, V), dtype=bf, device=dev)
         dh0 = torch.empty((B, N, K, V), dtype=torch.float32, device=dev)
         dhf = None if dh_final is None else dh_final.float().contiguous()
         _lib.check(_lib.cuda_lib().lme_delta_chain_bwd(
-            qkt.data_ptr(), ke_b.data_ptr(), qet.data_ptr(), wkt.data_ptr(), dy.data_ptr(), a32.data_ptr(),
+            qkt.data_ptr(), ke_b.data_ptr(), qet.data_ptr(), _lib.ptr(wkt), dy.data_ptr(), a32.data_ptr(),
             _lib.ptr(dhf), du_all.data_ptr(), dh_all.data_ptr(), dh0.data_ptr(), B * N, nc, K, V,
             _lib.stream_ptr()), f"lme_delta_chain_bwd BN={B * N} nc={nc} K={K} V={V}")
         _lib.count_launch()
@@ -219,7 +222,7 @@ class _DeltaChain(torch.autograd.Function):
         du, dh = du_all.view(n, L, V), dh_all.view(n, K, V)
         u, hs = u_all.view(n, L, V), h_all.view(n, K, V)
         f32 = torch.float32
-        dWk = -_bmm_kernel(du, hs, False, False, f32).view(B, N, nc, L, K)       # -dU h^T
+        dWk = None if wk_b is None else -_bmm_kernel(du, hs, False, False, f32).view(B, N, nc, L, K)   # -dU h^T
         dqe = _bmm_kernel(dyb, hs, False, False, f32).view(B, N, nc, L, K)       # dy h^T
         dqk = _bmm_kernel(dyb, u, False, False, f32).view(B, N, nc, L, L)        # dy U^T
         dke = _bmm_kernel(u, dh, False, False, f32).view(B, N, nc, L, K)         # U dh^T
@@ -304,7 +307,10 @@ def linear_attention_on_chain(q, k, v, h0=None, attention_multiplier: float = 1.
     if h0 is not None:
         h = pad_fn(h0.float(), (0, Vp - V, 0, Kp - K))
     ones = torch.ones(B, N, nc, dtype=torch.float32, device=q.device)
-    y, h = (chain or _DeltaChain.apply)(torch.zeros_like(kc), vc, qc, qk, kc, ones, h)
+    if chain is None:
+        y, h = _DeltaChain.apply(None, vc, qc, qk, kc, ones, h)
+    else:
+        y, h = chain(torch.zeros_like(kc), vc, qc, qk, kc, ones, h)
     y = y.permute(0, 2, 3, 1, 4).reshape(B, nc * L, N, Vp)[:, :S, :, :V]
     return (y * attention_multiplier).to(q.dtype), h[:, :, :K, :V]
 
