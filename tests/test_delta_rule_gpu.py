@@ -105,7 +105,7 @@ def test_linear_attention_on_chain_kernels_matches_token_scan(S, K, V):
     h0 = torch.randn(B, N, K, V, device="cuda") * 0.1
     a = [t.clone().requires_grad_(True) for t in (q, k, v)]
     b = [t.clone().requires_grad_(True) for t in (q, k, v)]
-    y, h = rec.linear_attention(*a, h0=h0, attention_multiplier=0.5)        # dispatcher: chain kernels
+    y, h = rec.linear_attention_on_chain(*a, h0=h0, attention_multiplier=0.5)
     y2, h2 = rec.linear_attention_scan(*b, h0=h0, attention_multiplier=0.5)
     assert y.shape == y2.shape and h.shape == h2.shape
     assert _rel(y, y2) < 2e-2 and _rel(h, h2) < 2e-2, (_rel(y, y2), _rel(h, h2))
