@@ -40,13 +40,16 @@ MODELS = {
     "dense-20b": (128256, 48, 6144, 48, 8, 128, 16384, 500000),
     # hybrid: three Mamba-2 (SSD) layers per softmax-attention layer (see HYBRID), no positional embedding
     "hybrid-mamba2": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
+    # the long-context hybrid target config (~2.7B): 48 layers, hidden 2560, every 6th layer attention (20 / 4 heads,
+    # RoPE theta 1e6), the others Mamba-2 (expand 2, head dim 64, state 128, chunk 256); run with --cp 4 --seq 32768
+    "hybrid-2p7b": (50304, 48, 2560, 20, 4, 128, 2048, 1000000),
     # hybrid: three matrix-state RNN layers per softmax-attention layer (see M2RNN_HYBRID)
     "hybrid-m2rnn": (32000, 16, 2048, 16, 4, 128, 8192, 10000),
 }
 # name: (experts, experts per token, shared expert intermediate size or None, router aux-loss coefficient)
 MOE = {"moe-64e": (64, 8, None, 0.01), "moe-ep8": (64, 8, None, 0.01)}
 # name: (attention every n-th layer, state size, SSM heads, conv kernel, chunk size)
-HYBRID = {"hybrid-mamba2": (4, 128, 64, 4, 256)}
+HYBRID = {"hybrid-mamba2": (4, 128, 64, 4, 256), "hybrid-2p7b": (6, 128, 80, 4, 256)}
 # name: (attention every n-th layer, k head dim, v head dim, heads, conv kernel): one q / k head shared by all value
 # heads, the layout of the published M2RNN hybrids
 M2RNN_HYBRID = {"hybrid-m2rnn": (4, 64, 16, 64, 4)}
@@ -63,12 +66,14 @@ def model_config(name: str, seq: int) -> dict:
         "model_type": "gpt_base", "vocab_size": v, "max_position_embeddings": seq, "hidden_size": h,
         "num_layers": L, "normalization_function": "rmsnorm", "layer_norm_epsilon": 1e-5,
         "initializer_range": 0.02, "bos_token_id": 0, "eos_token_id": 1, "pad_token_id": 2,
-        "position_embedding_type": "nope" if name in HYBRID or name in M2RNN_HYBRID else "rope", "rope_theta": theta, "rope_scaling": None, "m_emb": None,
+        "position_embedding_type": ("nope" if (name in HYBRID or name in M2RNN_HYBRID) and name != "hybrid-2p7b"
+                                    else "rope"), "rope_theta": theta, "rope_scaling": None, "m_emb": None,
         "m_width": None, "m_residual": None, "init_method": "normal", "embedding_init_method": "normal",
         "use_depth_scaled_init": False, "tie_word_embeddings": False,
         "sequence_mixer_blocks": [_mixer_block(name, i, h, nh, nkv, hd) for i in range(L)],
         "mlp_blocks": [_mlp_block(name, inter) for _ in range(L)],
         "router_aux_loss_coef": MOE[name][3] if name in MOE else 0.001,
+        **({"rope_dim": hd} if name == "hybrid-2p7b" else {}),
     }
 
 
@@ -198,11 +203,16 @@ def run_ours(a) -> dict:
     if tp > 1:
         cfg["distributed_args"].update(tensor_parallel_world_size=tp, sequence_parallel=True,
                                        use_async_tensor_parallel=True)
+    cp = a.cp
+    if cp > 1:
+        cfg["distributed_args"]["context_parallel_world_size"] = cp
     cfg["training_parameters"]["gradient_accumulation_steps"] = ga
     args = TrainingArgs(**cfg)
     d = args.distributed_args
     ProcessGroupManager(zero_stage=d.stage, expert_parallel_world_size=ep, tensor_parallel_world_size=tp,
-                        use_async_tensor_parallel=tp > 1)
+                        use_async_tensor_parallel=tp > 1, context_parallel_world_size=cp,
+                        context_parallel_load_balancing_method=d.context_parallel_load_balancing_method,
+                        context_parallel_attention=d.context_parallel_attention)
     world = ProcessGroupManager.get_world_size()
     rank = ProcessGroupManager.get_global_rank()
     args.training_parameters.reset_training_parameters(ProcessGroupManager.get_data_loading_world_size())
@@ -281,7 +291,7 @@ def run_ours(a) -> dict:
         "config": {"model": a.model if a.layers is None else f"{a.model}-{a.layers}layers",
                    "global_batch": dp_world * ga * a.mbs, "seq_len": a.seq,
                    "parallelism": f"fsdp2-zero3-dp{dp_world}" + (f"-ep{ep}" if ep > 1 else "")
-                   + (f"-tp{tp}-sp-asynctp" if tp > 1 else ""),
+                   + (f"-tp{tp}-sp-asynctp" if tp > 1 else "") + (f"-cp{cp}" if cp > 1 else ""),
                    "gradient_accumulation_steps": ga, "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
                    "optimizer": "AdamW fp32 master+state", "l2": "working set per step >> 126 MB L2, no flush"},
         "tokens_per_sec_per_gpu": value / world,
@@ -296,7 +306,7 @@ def run_ours(a) -> dict:
         "device_status": status[:4],
         "impl": "lm_engine_b200",
     }
-    if world > 1 and tp == 1:
+    if world > 1 and tp == 1 and cp == 1:
         out["multi_gpu_check"] = multi_gpu_check(world, rank, device)
     ProcessGroupManager.destroy_process_groups()
     return out if rank == 0 else None
@@ -355,6 +365,7 @@ def main() -> None:
     ap.add_argument("--mbs", type=int, default=None, help="micro batch per GPU (default 2; 4 for the MoE models)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (with sequence parallel)")
     ap.add_argument("--ga", type=int, default=1, help="gradient accumulation steps")
+    ap.add_argument("--cp", type=int, default=1, help="context-parallel group size (the sequence is split over it)")
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (profiling captures on a small case; not a benchmark result)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
