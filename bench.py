@@ -206,6 +206,7 @@ def run_ours(a) -> dict:
     cp = a.cp
     if cp > 1:
         cfg["distributed_args"]["context_parallel_world_size"] = cp
+        cfg["distributed_args"]["context_parallel_attention"] = a.cp_attention
     cfg["training_parameters"]["gradient_accumulation_steps"] = ga
     args = TrainingArgs(**cfg)
     d = args.distributed_args
@@ -291,7 +292,7 @@ def run_ours(a) -> dict:
         "config": {"model": a.model if a.layers is None else f"{a.model}-{a.layers}layers",
                    "global_batch": dp_world * ga * a.mbs, "seq_len": a.seq,
                    "parallelism": f"fsdp2-zero3-dp{dp_world}" + (f"-ep{ep}" if ep > 1 else "")
-                   + (f"-tp{tp}-sp-asynctp" if tp > 1 else "") + (f"-cp{cp}" if cp > 1 else ""),
+                   + (f"-tp{tp}-sp-asynctp" if tp > 1 else "") + (f"-cp{cp}-{a.cp_attention}" if cp > 1 else ""),
                    "gradient_accumulation_steps": ga, "micro_batch_per_gpu": a.mbs, "gradient_checkpointing": "block",
                    "optimizer": "AdamW fp32 master+state", "l2": "working set per step >> 126 MB L2, no flush"},
         "tokens_per_sec_per_gpu": value / world,
@@ -366,6 +367,8 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (with sequence parallel)")
     ap.add_argument("--ga", type=int, default=1, help="gradient accumulation steps")
     ap.add_argument("--cp", type=int, default=1, help="context-parallel group size (the sequence is split over it)")
+    ap.add_argument("--cp-attention", default="auto", choices=["auto", "ulysses", "gathered", "ring"],
+                    help="context-parallel attention algorithm")
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (profiling captures on a small case; not a benchmark result)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
