@@ -77,6 +77,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t* poisoned = tmem_base_smem + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // With key / value chunks that are still arriving from other GPUs the producer may wait as long as a peer wait
+    // lasts; every barrier behind it gets that time on top of its own.
+    const uint64_t wait_limit = p.kv_ready ? lme_peer_wait_ns + LME_WAIT_LIMIT_NS : LME_WAIT_LIMIT_NS;
     // blocks are handed out x first: x runs over (head, batch) and y over the query blocks, late (long) ones first,
     // so the longest blocks of ALL heads start first and the short ones fill the tail; neighbours in x share K / V
     const int qb = gridDim.y - 1 - blockIdx.y;
@@ -153,7 +156,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             auto load_k = [&](int j) -> bool {
                 const int s = j & 1;
                 if (!wait_chunk(j)) return false;
-                if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, 600 + s)) return false;
+                if (!mbar_wait_limit(&k_empty[s], ((j >> 1) & 1) ^ 1, 600 + s, wait_limit)) return false;
                 uint8_t* ks = smem + OFF_K + s * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
                 tma_load_2d(ks, &tmK, &k_full[s], hk * HD, tok_k + (j_begin + j) * BN);
@@ -164,7 +167,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int j = 0; j < n_tiles && ok; ++j) {
                 // K runs one tile ahead of V so that the wait for V's single stage never delays the next S product
                 if (j + 1 < n_tiles && !load_k(j + 1)) break;
-                if (!mbar_wait(v_empty, (j & 1) ^ 1, 605)) break;
+                if (!mbar_wait_limit(v_empty, (j & 1) ^ 1, 605, wait_limit)) break;
                 uint8_t* vs = smem + OFF_V;
                 mbar_expect_tx(v_full, KV_BYTES);
                 tma_load_2d(vs, &tmV, v_full, hk * HD, tok_k + (j_begin + j) * BN);
@@ -177,10 +180,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint32_t idesc_qk = make_idesc(1, 1, false, false, BM, BN);
             const uint32_t idesc_pv = make_idesc(1, 1, false, true, BM, HD);
             const uint32_t sq = smem_u32(smem + OFF_Q);
-            bool ok = mbar_wait(q_full, 0, 610);
+            bool ok = mbar_wait_limit(q_full, 0, 610, wait_limit);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j & 1;
-                if (!mbar_wait(&k_full[s], (j >> 1) & 1, 620 + s)) return false;
+                if (!mbar_wait_limit(&k_full[s], (j >> 1) & 1, 620 + s, wait_limit)) return false;
                 tc_fence_after();
                 const uint32_t sk = smem_u32(smem + OFF_K + s * KV_BYTES);
                 const uint32_t d = tmem_base + TM_S + s * BN;
@@ -199,8 +202,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j & 1;
                 if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
-                if (!mbar_wait(&p_full[s], (j >> 1) & 1, 630 + s)) { ok = false; break; }
-                if (!mbar_wait(v_full, j & 1, 640)) { ok = false; break; }
+                if (!mbar_wait_limit(&p_full[s], (j >> 1) & 1, 630 + s, wait_limit)) { ok = false; break; }
+                if (!mbar_wait_limit(v_full, j & 1, 640, wait_limit)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t sv = smem_u32(smem + OFF_V);
                 const uint32_t sp = smem_u32(smem + OFF_P + s * P_BYTES);
@@ -236,7 +239,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // every wait is voted on: the tcgen05.ld / st below are warp-collective, so the warp leaves together
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (j >> 1) & 1, 650 + s));
+            ok = __all_sync(0xffffffffu, mbar_wait_limit(&s_full[s], (j >> 1) & 1, 650 + s, wait_limit));
             if (!ok) break;
             tc_fence_after();
             const uint32_t ts = lane_base + TM_S + s * BN;
@@ -259,7 +262,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             const float m_new = fmaxf(m, mx);
             if (j >= 2) {   // this P buffer was last read by the P V product of tile j - 2
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[s], ((j >> 1) - 1) & 1, 655 + s));
+                ok = __all_sync(0xffffffffu, mbar_wait_limit(&pv_full[s], ((j >> 1) - 1) & 1, 655 + s, wait_limit));
                 if (!ok) break;
             }
             if (j == 0) {
@@ -268,7 +271,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const bool need = (m_new - m) * sl2 > 8.f;
                 if (__any_sync(0xffffffffu, need)) {
                     // O may only be touched when every earlier P V product has completed
-                    ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1, 660));
+                    ok = __all_sync(0xffffffffu, mbar_wait_limit(&pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1, 660, wait_limit));
                     if (!ok) break;
                     tc_fence_after();
                     const float alpha = need ? ex2((m - m_new) * sl2) : 1.f;
@@ -312,7 +315,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[s]);
         }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 670));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait_limit(&pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 670, wait_limit));
         if (ok) {
             const bool valid = q0 + row < len_q;    // tcgen05.ld is warp-collective: only the stores are predicated
             tc_fence_after();

@@ -97,19 +97,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false (after recording STATUS_MBAR_TIMEOUT) if the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t id = 0) {
+// limit_ns: LME_WAIT_LIMIT_NS for barriers that only this GPU's work feeds; a kernel whose producer itself waits for
+// another GPU passes that wait's limit plus its own, else the consumers give up while the producer still waits.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint32_t id, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3ff) == 0) {
-            if (globaltimer_ns() - t0 > LME_WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 report_error(STATUS_MBAR_TIMEOUT, id);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t id = 0) {
+    return mbar_wait_limit(bar, parity, id, LME_WAIT_LIMIT_NS);
 }
 
 // ------------------------------------------------------------------ TMA (per-CTA loads only)
