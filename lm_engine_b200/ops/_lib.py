@@ -153,6 +153,16 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+def raise_peer_wait_limit() -> None:
+    """Cross-GPU waits inside kernels (flags that another rank writes) get ``LME_PEER_WAIT_MS`` (default 60 s)
+    instead of the 2 s of waits that only this GPU's work feeds: ranks drift apart by seconds around first-step
+    allocations, lazy communicator set-up, evaluation and checkpoints.  Called by everything that sets up such waits."""
+    import os
+
+    check(cuda_lib().lme_set_peer_wait_limit_ms(int(os.environ.get("LME_PEER_WAIT_MS", "60000"))),
+          "lme_set_peer_wait_limit_ms")
+
+
 def read_status(clear: bool = True) -> list[int]:
     """Synchronises and returns the 8-word device status block (word 0 != 0: a bounded wait expired)."""
     buf = (ctypes.c_uint * 8)()

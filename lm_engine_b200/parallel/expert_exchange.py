@@ -104,6 +104,7 @@ class RankBuffers:
                    for name, (shape, dtype) in sizes.items()}
         self = cls(rank, world, num_experts, cap, hidden, tensors)
         self._arena, self._handle = arena, handle
+        _lib.raise_peer_wait_limit()
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
         return self

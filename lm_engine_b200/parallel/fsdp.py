@@ -530,8 +530,7 @@ class FSDPEngine:
             from ..ops import _lib
 
             # ranks drift apart by seconds around evaluation, checkpoints and first-step allocations
-            _lib.check(_lib.cuda_lib().lme_set_peer_wait_limit_ms(int(os.environ.get("LME_PEER_WAIT_MS", "60000"))),
-                       "lme_set_peer_wait_limit_ms")
+            _lib.raise_peer_wait_limit()
             torch.cuda.synchronize(self.device)
             dist.barrier(group=self.shard_group)
         except Exception as e:  # noqa: BLE001 - symmetric memory unavailable: keep the NCCL reduce-scatter

@@ -82,6 +82,8 @@ class _KVExchange:
         self.rs_seq = 0       # reduce-scatter launches of the backward pass
         self.bwd_calls = 0    # backward calls (gradient slot = bwd_calls & 1)
         self.stream_waits = True
+        # the attention kernel waits for chunks that a peer sends when IT reaches this layer
+        _lib.raise_peer_wait_limit()
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
