@@ -159,9 +159,11 @@ class SoftmaxAttention(nn.Module):
             from ...parallel import gathered_attention as gathered
 
             method = ProcessGroupManager.get_context_parallel_load_balancing_method()
-            if how in ("auto", "gathered") and dropout == 0 and gathered.eligible(q, k, self.causal,
-                                                                                  self._attended_keys, method):
-                # the K / V exchange runs inside the attention kernel (copy engines + readiness words)
+            if how == "gathered" and dropout == 0 and gathered.eligible(q, k, self.causal, self._attended_keys,
+                                                                        method):
+                # the K / V exchange runs inside the attention kernel (copy engines + readiness words).  Opt-in:
+                # it matches one GPU on 2 GPUs, but on 4 GPUs (2.7B hybrid, 32768 tokens) readiness words of some
+                # launches never arrived and the bounded waits ran out; until that is understood `auto` takes the ring
                 return gathered.gathered_kv_attention(q, k, v, softmax_scale=self.attention_multiplier)
             return ring_attention(q, k, v, causal=self.causal, softmax_scale=self.attention_multiplier,
                                   sliding_window=self._attended_keys)
