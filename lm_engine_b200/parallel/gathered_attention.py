@@ -118,6 +118,16 @@ def _gather_kv(ex: _KVExchange, k: torch.Tensor, v: torch.Tensor) -> tuple[torch
     stage[0].copy_(k.reshape(B, S_l, HD))
     stage[1].copy_(v.reshape(B, S_l, HD))
     kv_all = torch.empty((2, B, ex.S_total, HD), dtype=torch.bfloat16, device=k.device)
+    # This rank's own chunks go into the gathered buffer on the COMPUTE stream, ahead of the attention launches: a
+    # copy inside one device may run as a kernel, and a kernel queued on the side stream is not scheduled while an
+    # attention grid that fills every SM spins on exactly that chunk's word (seen as waits that ran out for a rank's
+    # own chunk on 4 GPUs, where the grid has 1280 CTAs; the peers' chunks arrive by copy engines over NVLink).
+    for j, g in enumerate(chunk_layout(ex.world, ex.rank, ex.method)):
+        for b in range(B):
+            for t in range(2):
+                kv_all[t, b, g * c:(g + 1) * c].copy_(stage[t, b, j * c:(j + 1) * c], non_blocking=True)
+            _lib.check(lib.lme_stream_write_words(ex.ready.data_ptr() + 4 * (b * ex.n_chunks + g), 1, seq,
+                                                  _lib.stream_ptr()), "lme_stream_write_words")
     ex.side.wait_stream(cur)
     with torch.cuda.stream(ex.side):
         side = _lib.stream_ptr()
@@ -131,14 +141,13 @@ def _gather_kv(ex: _KVExchange, k: torch.Tensor, v: torch.Tensor) -> tuple[torch
         announced = torch.cuda.Event()
         announced.record(ex.side)
         cur.wait_event(announced)
-        for i in range(ex.world):
+        for i in range(1, ex.world):
             p = (ex.rank + i) % ex.world
-            if p != ex.rank:
-                # a stream memory operation, not a kernel: it needs no SM while the attention CTAs hold theirs
-                rc = lib.lme_stream_wait_word(ex.pads[ex.rank] + 4 * p, seq, side) if ex.stream_waits else -1
-                if rc != _lib.LME_OK:
-                    ex.stream_waits = False      # not available for this memory: a one-thread bounded wait kernel
-                    _lib.check(lib.lme_gather_wait_peer(ex.pads[ex.rank], p, seq, side), "lme_gather_wait_peer")
+            # a stream memory operation, not a kernel: it needs no SM while the attention CTAs hold theirs
+            rc = lib.lme_stream_wait_word(ex.pads[ex.rank] + 4 * p, seq, side) if ex.stream_waits else -1
+            if rc != _lib.LME_OK:
+                ex.stream_waits = False      # not available for this memory: a one-thread bounded wait kernel
+                _lib.check(lib.lme_gather_wait_peer(ex.pads[ex.rank], p, seq, side), "lme_gather_wait_peer")
             src = ex.stage_peer[slot][p]
             for j, g in enumerate(chunk_layout(ex.world, p, ex.method)):
                 for b in range(B):      # one contiguous copy-engine transfer per (tensor, batch entry, chunk)
