@@ -155,6 +155,11 @@ def _gather_kv(ex: _KVExchange, k: torch.Tensor, v: torch.Tensor) -> tuple[torch
                         kv_all[t, b, g * c:(g + 1) * c].copy_(src[t, b, j * c:(j + 1) * c], non_blocking=True)
                     _lib.check(lib.lme_stream_write_words(ex.ready.data_ptr() + 4 * (b * ex.n_chunks + g), 1, seq,
                                                           side), "lme_stream_write_words")
+    if not ex.stream_waits:
+        # the peers' announcements are awaited by one-thread KERNELS on the side stream: an attention grid that fills
+        # every SM and spins on a chunk would keep such a kernel from ever starting, so without stream memory
+        # operations the attention launches wait for the whole exchange (correct, but nothing overlaps)
+        cur.wait_stream(ex.side)
     k.record_stream(ex.side)
     v.record_stream(ex.side)
     kv_all.record_stream(ex.side)
