@@ -27,18 +27,31 @@ def _is_block_linear(fqn: str, module: nn.Module) -> bool:
     return w.dim() == 2 and w.size(0) % 16 == 0 and w.size(1) % 16 == 0
 
 
-def convert_to_fp8_training(model: nn.Module, module_filter_fn=None) -> int:
+def convert_to_fp8_training(model: nn.Module, module_filter_fn=None, scaling: str | None = None) -> int:
     """Flags the weights of eligible linear layers; ``ops.linear`` / ``ops.linear_swiglu`` dispatch on the flag.
-    Returns the number of converted layers."""
-    n = 0
+    Returns the number of converted layers.  ``scaling`` (default: ``LME_FP8_SCALING``, else ``tensor``):
+    ``tensor`` = tensor-wise dynamic scales on the 8-bit tensor-core GEMM; ``block`` = the numerics of 1 x 128
+    activation / 128 x 128 weight scales (``ops/fp8_block.py``: operands rounded to block-scaled e4m3, products still
+    on the bf16 GEMM) for layers whose sizes are multiples of 128, tensor-wise for the rest."""
+    import os
+
+    scaling = scaling or os.environ.get("LME_FP8_SCALING", "tensor")
+    assert scaling in ("tensor", "block"), scaling
+    n = blocks = 0
     for fqn, m in model.named_modules():
         if not _is_block_linear(fqn, m):
             continue
         if module_filter_fn is not None and not module_filter_fn(m, fqn):
             continue
-        m.weight.fp8 = True
+        w = m.weight
+        if scaling == "block" and w.size(0) % 128 == 0 and w.size(1) % 128 == 0:
+            w.fp8 = "block"
+            blocks += 1
+        else:
+            w.fp8 = True
         n += 1
-    log_rank_0(logging.INFO, f"fp8: {n} linear layers run on the 8-bit tensor core path")
+    log_rank_0(logging.INFO, f"fp8: {n} linear layers converted ({blocks} with block-scaled numerics, "
+               f"{n - blocks} on the tensor-wise 8-bit tensor core path)")
     return n
 
 

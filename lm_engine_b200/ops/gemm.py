@@ -202,8 +202,13 @@ class _Linear(torch.autograd.Function):
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            residual: torch.Tensor | None = None) -> torch.Tensor:
     """``F.linear`` with an optional fused residual add; tcgen05 GEMMs on CUDA bf16, PyTorch elsewhere."""
+    if getattr(weight, "fp8", False) == "block":
+        from . import fp8_block
+
+        if fp8_block.block_eligible(x, weight):
+            return fp8_block.linear_block_scaled(x, weight, bias, residual)
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
-        if getattr(weight, "fp8", False):
+        if getattr(weight, "fp8", False) is True:
             from . import fp8
 
             if fp8.fp8_eligible(x, weight):
@@ -248,8 +253,14 @@ class _LinearSwiGLU(torch.autograd.Function):
 
 def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``up * silu(gate)`` of the packed projection ``x W^T`` (gate/up interleaved along the output features)."""
+    if getattr(weight, "fp8", False) == "block":
+        from . import fp8_block
+        from .activation import swiglu_packed
+
+        if fp8_block.block_eligible(x, weight):
+            return swiglu_packed(fp8_block.linear_block_scaled(x, weight))
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.size(0) % 16 == 0:
-        if getattr(weight, "fp8", False):
+        if getattr(weight, "fp8", False) is True:
             from . import fp8
 
             if fp8.fp8_eligible(x, weight):
