@@ -999,6 +999,22 @@ class FSDPEngine:
         self._reduce_norm(include_pipeline_group)
         return self.sumsq
 
+    def _replicated_grad_views(self) -> list[torch.Tensor]:
+        """This rank's pieces of the gradients of parameters that are replicated over the tensor-parallel group."""
+        cached = getattr(self, "_rep_views", None)
+        if cached is None or cached[0] != [u.grad_shard.data_ptr() for u in self.all_units]:
+            views = []
+            for u in self.all_units:
+                for s in u.slots:
+                    if getattr(s.param, "tp_shard_dim", None) is None:
+                        lo = max(s.offset, u.state_lo) - u.state_lo
+                        hi = min(s.offset + s.numel, u.state_hi) - u.state_lo
+                        if hi > lo:
+                            views.append(u.grad_shard[lo:hi])
+            cached = ([u.grad_shard.data_ptr() for u in self.all_units], views)
+            self._rep_views = cached
+        return cached[1]
+
     def _reduce_norm(self, include_pipeline_group: bool = True) -> None:
         """Sum of squares over every group that holds a distinct piece of the model."""
         if self.stage >= 1 and self.shard_group is not None:
@@ -1010,13 +1026,11 @@ class FSDPEngine:
             # replicated parameters were counted tp times; their share is small and the reference counts DTensor
             # replicas once, so subtract the surplus
             rep = torch.zeros(1, dtype=torch.float32, device=self.device)
-            for u in self.all_units:
-                for s in u.slots:
-                    if getattr(s.param, "tp_shard_dim", None) is None:
-                        lo = max(s.offset, u.state_lo) - u.state_lo
-                        hi = min(s.offset + s.numel, u.state_hi) - u.state_lo
-                        if hi > lo:
-                            rep += u.grad_shard[lo:hi].float().pow(2).sum()
+            views = self._replicated_grad_views()
+            if views:
+                # one multi-tensor launch over all replicated pieces (the gradient buffers are allocated once, so
+                # the views are too), not a Python loop of reductions per parameter
+                rep += torch.stack(torch._foreach_norm(views, 2, dtype=torch.float32)).pow(2).sum()
             if self.stage >= 1 and self.shard_group is not None:
                 dist.all_reduce(rep, group=self.shard_group)
             tpw = dist.get_world_size(tp)
