@@ -923,6 +923,7 @@ class FSDPEngine:
             self._cross_rank_fence()
             self.prefetch_first_units()
             return self.grad_norm
+        refreshes = []
         for u in self.all_units:
             for g in u.local_group_ranges():
                 sl = slice(g.start, g.end)
@@ -931,7 +932,12 @@ class FSDPEngine:
                                weight_decay=0.0 if g.name == "no_weight_decay" else weight_decay,
                                step=self.step_count, gscale=self.clip_coef)
             if self.stage in (1, 2) and u.world > 1:
-                dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group)
+                # ZeRO-1 / 2 keep whole parameters: refresh them from the updated shards.  Issued asynchronously, so
+                # that the gather of one unit runs under the update of the next instead of holding the stream.
+                refreshes.append(dist.all_gather_into_tensor(u.flat_param, u.lp_shard.clone(), group=u.group,
+                                                             async_op=True))
+        for work in refreshes:
+            work.wait()
         self._cross_rank_fence()
         self.prefetch_first_units()
         return self.grad_norm
