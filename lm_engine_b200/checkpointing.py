@@ -29,6 +29,7 @@ import subprocess
 
 import numpy as np
 import torch
+import torch.distributed as dist
 import torch.distributed.checkpoint as dcp
 import yaml
 from torch.distributed.tensor import DTensor, Replicate, Shard
@@ -94,9 +95,22 @@ def _to_dtensor(engine, local_full: torch.Tensor, param: torch.nn.Parameter) -> 
         return DTensor.from_local(chunk, mesh, [Shard(0)], run_check=False, shape=local_full.shape,
                                   stride=local_full.stride())
     if tp_group is not None:
+        tp_placement = Shard(tp_dim) if tp_dim is not None else Replicate()
+        if engine.shard_group is not None and engine.stage >= 1 and engine.world > 1 and local_full.dim() >= 1:
+            # tensor parallel x sharded data parallel: every rank offers only its block of rows of the TP-local
+            # tensor.  Mesh order (tp, fsdp): a dimension split by both is split tp-major, as the model lays it out.
+            mesh = ProcessGroupManager.get_device_mesh_2d("tp", "fsdp")
+            n, world, rank = local_full.size(0), engine.world, engine.rank
+            per = -(-n // world)
+            lo, hi = min(rank * per, n), min((rank + 1) * per, n)
+            shape = list(local_full.shape)
+            if tp_dim is not None:
+                shape[tp_dim] *= dist.get_world_size(tp_group)
+            stride = torch.empty(shape, device="meta").stride()
+            return DTensor.from_local(local_full[lo:hi].clone(), mesh, [tp_placement, Shard(0)], run_check=False,
+                                      shape=torch.Size(shape), stride=stride)
         mesh = ProcessGroupManager.get_device_mesh("tp")
-        placement = [Shard(tp_dim)] if tp_dim is not None else [Replicate()]
-        return DTensor.from_local(local_full.clone(), mesh, placement, run_check=False)
+        return DTensor.from_local(local_full.clone(), mesh, [tp_placement], run_check=False)
     return local_full.clone()
 
 
@@ -126,8 +140,12 @@ def _from_saved(value: torch.Tensor, engine) -> torch.Tensor:
     """Inverse of :func:`_to_dtensor`: the full per-TP-rank tensor."""
     if isinstance(value, DTensor):
         tp = ProcessGroupManager.get_tensor_parallel_group()
-        if tp is not None and value.device_mesh.mesh_dim_names == ("tp",):
+        names = value.device_mesh.mesh_dim_names
+        if tp is not None and names == ("tp",):
             return value.to_local()
+        if tp is not None and names == ("tp", "fsdp"):
+            # gather the row blocks over the sharding group, keep the tensor-parallel slice
+            return value.redistribute(placements=[value.placements[0], Replicate()]).to_local()
         return value.full_tensor()
     return value
 

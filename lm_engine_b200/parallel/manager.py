@@ -334,6 +334,24 @@ class ProcessGroupManager:
                 _S.meshes[axis] = DeviceMesh(device, ranks, mesh_dim_names=(axis,))
         return _S.meshes[axis]
 
+    @staticmethod
+    def get_device_mesh_2d(outer: str, inner: str):
+        """2-D ``DeviceMesh`` ``[outer, inner]`` over the ranks that share this rank's other coordinates, on the
+        existing process groups of the two axes (entry ``[i][j]``: the rank with index ``i`` on ``outer`` inside the
+        ``inner`` group of ...): row ``i`` is the ``inner`` group of the ``i``-th member of this rank's ``outer``
+        group."""
+        from torch.distributed.device_mesh import DeviceMesh
+
+        key = f"{outer}x{inner}"
+        if key not in _S.meshes:
+            topo = ProcessGroupManager.topology()
+            grid = [topo.group(inner, r) for r in topo.group(outer, _S.rank)]
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+            groups = [_S.groups.get(outer), _S.groups.get(inner)]
+            assert all(g is not None for g in groups), f"no process group for {outer} / {inner}"
+            _S.meshes[key] = DeviceMesh.from_group(groups, device, mesh=grid, mesh_dim_names=(outer, inner))
+        return _S.meshes[key]
+
     # ------------------------------------------------------------------ misc
     @staticmethod
     def is_tracking_rank() -> bool:

@@ -187,3 +187,61 @@ def test_resume_keeps_amsgrad_state(tmp_path):
     from lm_engine_b200.parallel.manager import ProcessGroupManager
 
     ProcessGroupManager.destroy_process_groups()
+
+
+def _tp2_dp2(rank, world, path, phase):
+    """Tensor parallel 2 x ZeRO-3 over 2.  ``save``: two steps, checkpoint, return the local state and what each rank
+    offers to the checkpoint writer.  ``load``: fresh model of the same topology, load, return the local state."""
+    from lm_engine_b200.arguments import TrainingArgs
+    from lm_engine_b200.checkpointing import load_checkpoint_for_training, model_state_dict, save_checkpoint
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    args = _args(path, load_path=path if phase == "load" else None)
+    args.distributed_args.tensor_parallel_world_size = 2
+    ProcessGroupManager(zero_stage=3, tensor_parallel_world_size=2)
+    models, opts, scheds = _build(args, init_groups=False)
+    dp_rank, dp_world = ProcessGroupManager.get_data_parallel_rank(), ProcessGroupManager.get_data_parallel_world_size()
+    if phase == "save":
+        _steps(models, opts, scheds, _data(2, dp_rank, dp_world))
+        save_checkpoint(args, models, opts, scheds, None, None, 2, {})
+        offered = {k: (tuple(v.to_local().shape), tuple(v.shape), v.device_mesh.mesh_dim_names)
+                   for k, v in model_state_dict(models).items() if hasattr(v, "to_local")}
+    else:
+        load_checkpoint_for_training(args, TrainingArgs, models, opts, scheds, None)
+        offered = {}
+    eng = models[0].engine
+    local = {k: v.numpy().copy() for k, v in eng.full_state_dict().items()}
+    moments = {k: v.numpy().copy() for k, v in eng.full_state_dict("exp_avg").items()}
+    return local, moments, offered, ProcessGroupManager.get_tensor_parallel_rank(), eng.step_count
+
+
+def test_tensor_parallel_times_sharded_checkpoint_is_two_dimensional(tmp_path):
+    """Under TP 2 x ZeRO-3 over 2 every rank offers only its block of rows of its tensor-parallel slice (a DTensor on
+    the (tp, fsdp) mesh), the checkpoint holds the global tensors, and it loads back bit-exactly."""
+    from lm_engine_b200.checkpointing import read_full_model_state
+
+    path = str(tmp_path / "ckpt")
+    saved = run_distributed(_tp2_dp2, 4, path, "save", timeout=600)
+    state, _, _ = read_full_model_state(path)
+    for local, _, offered, tp_rank, _ in saved:
+        assert offered and all(names == ("tp", "fsdp") for _, _, names in offered.values())
+        for key, (local_shape, global_shape, _) in offered.items():
+            # a rank's piece is at most half (rounded up) of the rows of its tensor-parallel slice
+            name = key[len("model."):]
+            tp_local_rows = local[name].shape[0]
+            assert local_shape[0] <= -(-tp_local_rows // 2), (key, local_shape, tp_local_rows)
+            assert tuple(state[key].shape) == global_shape
+        for name, v in local.items():                      # the global tensor contains this rank's slice
+            g = state[f"model.{name}"].numpy()
+            if g.shape == v.shape:
+                assert np.array_equal(g, v), name
+            else:
+                dim = [i for i, (a, b) in enumerate(zip(g.shape, v.shape)) if a != b][0]
+                n = v.shape[dim]
+                assert np.array_equal(np.take(g, range(tp_rank * n, (tp_rank + 1) * n), axis=dim), v), name
+    loaded = run_distributed(_tp2_dp2, 4, path, "load", timeout=600)
+    for (a, ma, _, _, _), (b, mb, _, _, step) in zip(saved, loaded):
+        assert step == 2
+        for k in a:
+            assert np.array_equal(a[k], b[k]), k
+            assert np.array_equal(ma[k], mb[k]), k
