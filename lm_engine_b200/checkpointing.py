@@ -115,10 +115,22 @@ def _to_dtensor(engine, local_full: torch.Tensor, param: torch.nn.Parameter) -> 
 
 
 def _chunk_dtensor(engine, chunk: torch.Tensor, param: torch.nn.Parameter, shape: torch.Size) -> torch.Tensor:
-    """``Shard(0)`` DTensor over the sharding group from this rank's block of rows (see ``FSDPEngine.row_chunks``)."""
-    mesh = ProcessGroupManager.get_device_mesh("fsdp")
-    stride = torch.empty(shape, device="meta").stride()
-    return DTensor.from_local(chunk.contiguous(), mesh, [Shard(0)], run_check=False, shape=shape, stride=stride)
+    """DTensor from this rank's block of rows (see ``FSDPEngine.row_chunks``): ``Shard(0)`` over the sharding group,
+    or on the (tp, fsdp) mesh when the parameter is a tensor-parallel slice (``shape`` is the slice's shape)."""
+    tp_group = ProcessGroupManager.get_tensor_parallel_group()
+    if tp_group is None:
+        mesh = ProcessGroupManager.get_device_mesh("fsdp")
+        stride = torch.empty(shape, device="meta").stride()
+        return DTensor.from_local(chunk.contiguous(), mesh, [Shard(0)], run_check=False, shape=shape, stride=stride)
+    tp_dim = getattr(param, "tp_shard_dim", None)
+    full = list(shape)
+    if tp_dim is not None:
+        full[tp_dim] *= dist.get_world_size(tp_group)
+    stride = torch.empty(full, device="meta").stride()
+    mesh = ProcessGroupManager.get_device_mesh_2d("tp", "fsdp")
+    return DTensor.from_local(chunk.contiguous(), mesh, [Shard(tp_dim) if tp_dim is not None else Replicate(),
+                                                         Shard(0)], run_check=False, shape=torch.Size(full),
+                              stride=stride)
 
 
 def _unit_state_tensors(eng, u, which) -> dict[str, torch.Tensor]:

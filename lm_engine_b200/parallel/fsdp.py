@@ -1062,10 +1062,10 @@ class FSDPEngine:
 
     # ------------------------------------------------------------------ row chunks for sharded checkpoints
     def can_exchange_row_chunks(self, u: ShardedUnit) -> bool:
-        """Whether :meth:`row_chunks` applies: state sharded over the data-parallel sharding group, parameters not
-        split any further (tensor / expert parallel slices keep the gather-based path)."""
-        return (u.shard_state and u.group is self.shard_group and not u.is_expert
-                and ProcessGroupManager.get_tensor_parallel_group() is None and self.ep_world == 1)
+        """Whether :meth:`row_chunks` applies: state sharded over the data-parallel sharding group and no expert
+        parallelism (expert slices keep the gather-based path).  Under tensor parallelism the rows are those of the
+        rank's tensor-parallel slice."""
+        return u.shard_state and u.group is self.shard_group and not u.is_expert and self.ep_world == 1
 
     @torch.no_grad()
     def row_chunks(self, u: ShardedUnit, which: str | torch.Tensor = "master") -> dict[str, torch.Tensor]:
