@@ -177,6 +177,30 @@ def model_state_dict(model_container: ModelContainer, which: str = "master") -> 
     return out
 
 
+def _is_row_block(value) -> bool:
+    """A DTensor in the layout of :func:`_chunk_dtensor` (this rank holds a block of rows)."""
+    if not isinstance(value, DTensor):
+        return False
+    names, pl = value.device_mesh.mesh_dim_names, value.placements
+    return ((names == ("fsdp",) and pl[0] == Shard(0))
+            or (names == ("tp", "fsdp") and pl[1] == Shard(0) and ProcessGroupManager.get_tensor_parallel_group()
+                is not None))
+
+
+def _load_engine_state(eng, values: dict[str, torch.Tensor], which: str) -> None:
+    """``values``: slot name -> loaded value in the checkpoint layout.  Unit by unit, so that at most one unit is ever
+    whole on a rank; units whose parameters all arrived as row blocks are re-cut with one all-to-all and no gather."""
+    for u in eng.all_units:
+        mine = {s.name: values[s.name] for s in u.slots if s.name in values}
+        if not mine:
+            continue
+        if len(mine) == len(u.slots) and eng.can_exchange_row_chunks(u) and all(_is_row_block(v)
+                                                                                for v in mine.values()):
+            eng.load_row_chunks(u, {n: v.to_local() for n, v in mine.items()}, which)
+        else:
+            eng.load_full_state_dict({n: _from_saved(v, eng) for n, v in mine.items()}, which)
+
+
 def load_model_state_dict(model_container: ModelContainer, state: dict[str, torch.Tensor],
                           which: str = "master") -> None:
     for wrapper in model_container:
@@ -185,13 +209,8 @@ def load_model_state_dict(model_container: ModelContainer, state: dict[str, torc
             wrapper.model.load_state_dict({k[len("model."):]: _from_saved(v, None) for k, v in state.items()},
                                           strict=False)
             continue
-        plain = {}
-        for u in eng.all_units:
-            for s in u.slots:
-                key = f"model.{s.name}"
-                if key in state:
-                    plain[s.name] = _from_saved(state[key], eng)
-        eng.load_full_state_dict(plain, which)
+        names = [s.name for u in eng.all_units for s in u.slots]
+        _load_engine_state(eng, {n: state[f"model.{n}"] for n in names if f"model.{n}" in state}, which)
 
 
 _GROUP_KEYS = ("lr", "betas", "eps", "weight_decay", "initial_lr")
@@ -265,8 +284,7 @@ def load_optimizer_state_dict(model_container, optimizer_container, state: dict)
                     found.setdefault(which, {})[name] = v
         if fused:
             for which in ("exp_avg", "exp_avg_sq"):
-                plain = {n: _from_saved(v, eng) for n, v in found.get(which, {}).items()}
-                eng.load_full_state_dict(plain, which)
+                _load_engine_state(eng, found.get(which, {}), which)
         else:
             scalars = {}
             for which, by_slot in found.items():

@@ -1125,6 +1125,62 @@ class FSDPEngine:
             out[sl.name] = data.view(rows, *sl.shape[1:]) if len(sl.shape) > 0 else data.view(sl.shape)
         return out
 
+    @torch.no_grad()
+    def load_row_chunks(self, u: ShardedUnit, chunks: dict[str, torch.Tensor], which: str = "master") -> None:
+        """Inverse of :meth:`row_chunks`: every parameter of the unit arrives as this rank's block of rows (what a
+        checkpoint load delivers into the ``Shard(0)`` layout), and ONE all-to-all moves the pieces to the ranks whose
+        flat state slices they belong to.  No rank ever holds the whole unit."""
+        dst = {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq}[which]
+        W, S, me = u.world, u.shard_size, u.rank
+
+        def block(sl: _Slot, r: int) -> tuple[int, int]:
+            n0 = sl.shape[0] if len(sl.shape) > 0 else 1
+            row = sl.numel // max(n0, 1)
+            per = -(-n0 // W)
+            lo, hi = min(r * per, n0), min((r + 1) * per, n0)
+            return sl.offset + lo * row, sl.offset + hi * row
+
+        send_parts: list[list[torch.Tensor]] = [[] for _ in range(W)]
+        recv_plan: list[list[tuple[int, int]]] = [[] for _ in range(W)]    # per source rank: (offset in my slice, n)
+        for sl in u.slots:
+            lo, hi = block(sl, me)
+            mine = chunks[sl.name].to(self.device, torch.float32).reshape(-1)
+            assert mine.numel() == hi - lo, (sl.name, mine.numel(), hi - lo)
+            for q in range(W):                                   # my rows that lie in rank q's flat slice
+                a, b = max(lo, q * S), min(hi, (q + 1) * S)
+                if b > a:
+                    send_parts[q].append(mine[a - lo:b - lo])
+            for r in range(W):                                   # rank r's rows that lie in my flat slice
+                lo_r, hi_r = block(sl, r)
+                a, b = max(lo_r, me * S), min(hi_r, (me + 1) * S)
+                if b > a:
+                    recv_plan[r].append((a - me * S, b - a))
+        send_sizes = [sum(p.numel() for p in parts) for parts in send_parts]
+        recv_sizes = [sum(n for _, n in plan) for plan in recv_plan]
+        flat_send = (torch.cat([p for parts in send_parts for p in parts]) if sum(send_sizes)
+                     else torch.empty(0, dtype=torch.float32, device=self.device))
+        flat_recv = torch.empty(sum(recv_sizes), dtype=torch.float32, device=self.device)
+        dist.all_to_all_single(flat_recv, flat_send.contiguous(), recv_sizes, send_sizes, group=u.group)
+        local = torch.zeros(u.state_hi - u.state_lo, dtype=torch.float32, device=self.device)
+        local.copy_(dst.to(self.device, torch.float32))           # padding past the last parameter keeps its value
+        cursor = 0
+        for r in range(W):
+            for off, n in recv_plan[r]:
+                local[off - (u.state_lo - me * S):off - (u.state_lo - me * S) + n].copy_(flat_recv[cursor:cursor + n])
+                cursor += n
+        dst.copy_(local.to(dst.device, dst.dtype))
+        if which == "master":
+            if u.shard_params:
+                u.lp_shard.copy_(u.master.to(self.device))
+            else:
+                dist.all_gather_into_tensor(u.flat_param, u.master.to(self.device, u.flat_param.dtype).contiguous(),
+                                            group=u.group)
+            if self._inflight:
+                if self.is_cuda:
+                    torch.cuda.synchronize(self.device)
+                self._inflight.clear()
+            self._cross_rank_fence()
+
     def _slot_full(self, s: "_Slot", local: torch.Tensor) -> torch.Tensor:
         """Expert-parallel parameters: the tensor over all experts (concatenated over the expert-parallel group)."""
         dim = getattr(s.param, "ep_shard_dim", None)
@@ -1152,6 +1208,8 @@ class FSDPEngine:
     @torch.no_grad()
     def load_full_state_dict(self, sd: dict[str, torch.Tensor], which: str = "master") -> None:
         for u in self.all_units:
+            if not any(s.name in sd for s in u.slots):      # the same keys on every rank: no collective is skipped
+                continue                                    # on one rank only
             full = self.gather_full(u, which)
             for s in u.slots:
                 if s.name in sd:

@@ -207,8 +207,19 @@ def _tp2_dp2(rank, world, path, phase):
         offered = {k: (tuple(v.to_local().shape), tuple(v.shape), v.device_mesh.mesh_dim_names)
                    for k, v in model_state_dict(models).items() if hasattr(v, "to_local")}
     else:
-        load_checkpoint_for_training(args, TrainingArgs, models, opts, scheds, None)
-        offered = {}
+        from lm_engine_b200.parallel.fsdp import FSDPEngine
+
+        calls, gathers = [], []
+        inner, inner_full = FSDPEngine.load_row_chunks, FSDPEngine.load_full_state_dict
+        FSDPEngine.load_row_chunks = lambda self, u, chunks, which="master": (calls.append(u.name),
+                                                                               inner(self, u, chunks, which))[1]
+        FSDPEngine.load_full_state_dict = lambda self, sd, which="master": (gathers.append(len(sd)),
+                                                                             inner_full(self, sd, which))[1]
+        try:
+            load_checkpoint_for_training(args, TrainingArgs, models, opts, scheds, None)
+        finally:
+            FSDPEngine.load_row_chunks, FSDPEngine.load_full_state_dict = inner, inner_full
+        offered = {"row_block_loads": len(calls), "gather_loads": len(gathers)}
     eng = models[0].engine
     local = {k: v.numpy().copy() for k, v in eng.full_state_dict().items()}
     moments = {k: v.numpy().copy() for k, v in eng.full_state_dict("exp_avg").items()}
@@ -240,8 +251,10 @@ def test_tensor_parallel_times_sharded_checkpoint_is_two_dimensional(tmp_path):
                 n = v.shape[dim]
                 assert np.array_equal(np.take(g, range(tp_rank * n, (tp_rank + 1) * n), axis=dim), v), name
     loaded = run_distributed(_tp2_dp2, 4, path, "load", timeout=600)
-    for (a, ma, _, _, _), (b, mb, _, _, step) in zip(saved, loaded):
+    for (a, ma, _, _, _), (b, mb, info, _, step) in zip(saved, loaded):
         assert step == 2
+        # weights and both moments of every unit came in as row blocks and were re-cut without a gather
+        assert info["row_block_loads"] > 0 and info["gather_loads"] == 0, info
         for k in a:
             assert np.array_equal(a[k], b[k]), k
             assert np.array_equal(ma[k], mb[k]), k
