@@ -90,14 +90,24 @@ class Mamba2(nn.Module):
             y, h = ssd_recurrent_step(xs[:, 0], dt[:, 0], A, B[:, 0], C[:, 0], self.D, h)
             y = y[:, None]
         else:
-            h0 = h
             cp = ProcessGroupManager.get_context_parallel_group()
             if cp is not None:
+                # Context parallel: ONE scan per rank.  The recurrence is linear in the state, so the shard is
+                # scanned from a zero state (all ranks at once), the boundary states are exchanged and combined
+                # (ssd_context_parallel_initial_state), and what the entering state h0 adds to every position is a
+                # closed form: y_t += exp(sum_{tau <= t} A dt_tau) C_t . h0, and the state leaving the shard is
+                # exp(sum A dt) h0 + (final state from zero).
                 assert h is None
-                _, f0 = ssd_chunk_scan(xs, dt, A, B, C, self.D, self.chunk_size)
-                decay = torch.exp(A[None, :] * dt.sum(1))
-                h0 = ssd_context_parallel_initial_state(f0, decay, cp)
-            y, h = ssd_chunk_scan(xs, dt, A, B, C, self.D, self.chunk_size, initial_state=h0)
+                y, f0 = ssd_chunk_scan(xs, dt, A, B, C, self.D, self.chunk_size)
+                log_decay = (A[None, None, :] * dt.float()).cumsum(1)                       # [b, S, N]
+                total = torch.exp(log_decay[:, -1])                                         # [b, N]
+                h0 = ssd_context_parallel_initial_state(f0, total, cp)                      # [b, N, P, Sd]
+                hg = h0.float().reshape(b, G, N // G, P, Sd)
+                add = torch.einsum("bsgd,bgjpd->bsgjp", C.float(), hg).reshape(b, S, N, P)
+                y = (y.float() + torch.exp(log_decay)[..., None] * add).to(y.dtype)
+                h = total[..., None, None] * h0 + f0
+            else:
+                y, h = ssd_chunk_scan(xs, dt, A, B, C, self.D, self.chunk_size, initial_state=h)
         if cache_params is not None:
             cache_params.update(self.layer_idx, "conv", c, GenerationCache.REPLACE, num_tokens_added=S)
             cache_params.update(self.layer_idx, "ssm", h, GenerationCache.REPLACE)
