@@ -258,3 +258,32 @@ def test_tensor_parallel_times_sharded_checkpoint_is_two_dimensional(tmp_path):
         for k in a:
             assert np.array_equal(a[k], b[k]), k
             assert np.array_equal(ma[k], mb[k]), k
+
+
+def _row_block_round_trip(rank, world):
+    """``row_chunks`` followed by ``load_row_chunks`` is the identity on every unit's state, on a group size that
+    divides neither the rows nor the flat sizes (empty and partial blocks occur)."""
+    args = _args("/nonexistent")
+    models, opts, scheds = _build(args)
+    _steps(models, opts, scheds, _data(1, rank, world))
+    eng = models[0].engine
+    ok = True
+    for which in ("master", "exp_avg"):
+        for u in eng.all_units:
+            if not eng.can_exchange_row_chunks(u) or any(len(s.shape) == 0 for s in u.slots):
+                continue
+            state = {"master": u.master, "exp_avg": u.exp_avg}[which]
+            before = state.clone()
+            chunks = eng.row_chunks(u, which)
+            for s in u.slots:                                   # the block sizes of an even split of the rows
+                per = -(-s.shape[0] // world)
+                rows = max(min((rank + 1) * per, s.shape[0]) - min(rank * per, s.shape[0]), 0)
+                ok &= chunks[s.name].shape[0] == rows
+            state.zero_()
+            eng.load_row_chunks(u, chunks, which)
+            ok &= bool(torch.equal(state, before))
+    return ok
+
+
+def test_row_block_exchange_round_trip_on_three_ranks():
+    assert all(run_distributed(_row_block_round_trip, 3, timeout=600))
