@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch.nn as nn
 
 from ...ops.recurrence import gated_delta_rule
+from ...parallel.manager import ProcessGroupManager
 from ...utils import divide_if_divisible
 from ..context import AttentionMaskInfo, GenerationCache, PositionInfo, resolve_attention_and_position_info
 from .activations import silu
@@ -27,6 +28,7 @@ class GatedDeltaNet(nn.Module):
                  m_width, num_layers: int, use_depth_scaled_init: bool, use_padding_free_transformer: bool = False,
                  layer_norm_epsilon: float = 1e-5) -> None:
         super().__init__()
+        ProcessGroupManager.reject_context_parallel("gated delta net")
         self.use_padding_free_transformer = use_padding_free_transformer
         self.allow_neg_eigval, self.use_gate, self.layer_idx = config.allow_neg_eigval, config.use_gate, layer_idx
         self.num_k_heads, self.num_v_heads = config.num_k_heads, config.num_v_heads

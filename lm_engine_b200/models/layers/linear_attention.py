@@ -7,6 +7,7 @@ from __future__ import annotations
 import torch.nn as nn
 
 from ...ops.recurrence import linear_attention
+from ...parallel.manager import ProcessGroupManager
 from ...parameter import mark_parameter_as_mup_learning_rate
 from ...utils import divide_if_divisible
 from ..context import AttentionMaskInfo, GenerationCache, PositionInfo, resolve_attention_and_position_info
@@ -25,6 +26,7 @@ class LinearAttention(nn.Module):
                  use_padding_free_transformer: bool = False, layer_norm_epsilon: float = 1e-5) -> None:
         super().__init__()
         self.use_padding_free_transformer = use_padding_free_transformer
+        ProcessGroupManager.reject_context_parallel("linear attention")
         self.k_head_dim, self.v_head_dim, self.layer_idx = config.k_head_dim, config.v_head_dim, layer_idx
         self.kernel_size, self.activation_string = config.kernel_size, config.activation_function
         self.num_q_heads, self.num_k_heads = config.num_q_heads, config.num_k_heads

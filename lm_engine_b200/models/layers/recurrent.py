@@ -8,6 +8,7 @@ import torch
 import torch.nn as nn
 
 from ...ops.recurrence import gru, rnn
+from ...parallel.manager import ProcessGroupManager
 from ...parameter import (
     mark_parameter_as_initialized,
     mark_parameter_as_mup_learning_rate,
@@ -50,6 +51,7 @@ class _RecurrentBase(nn.Module):
                 use_depth_scaled_init, use_padding_free_transformer, in_width: int) -> None:
         self.use_padding_free_transformer = use_padding_free_transformer
         self.layer_idx = layer_idx
+        ProcessGroupManager.reject_context_parallel("RNN / GRU")
         self.gradient_clipping = config.gradient_clipping
         self.state_head_dim = config.state_head_dim
         self.state_size = self.num_heads * self.state_head_dim

@@ -335,6 +335,14 @@ class ProcessGroupManager:
         return _S.meshes[axis]
 
     @staticmethod
+    def reject_context_parallel(what: str) -> None:
+        """For layers whose recurrence has no context-parallel form here (the reference runs them on each rank's
+        shard as if it were the whole sequence, which is silently wrong): fail at construction."""
+        if ProcessGroupManager.is_context_parallel_enabled():
+            raise NotImplementedError(f"{what}: context parallelism is implemented for softmax attention, Mamba-2 "
+                                      "and M2RNN only")
+
+    @staticmethod
     def get_device_mesh_2d(outer: str, inner: str):
         """2-D ``DeviceMesh`` ``[outer, inner]`` over the ranks that share this rank's other coordinates, on the
         existing process groups of the two axes (entry ``[i][j]``: the rank with index ``i`` on ``outer`` inside the

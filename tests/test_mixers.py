@@ -259,3 +259,14 @@ def test_sliding_window_counts_keys_like_the_reference():
         near[0, 11 - w] = (near[0, 11 - w] + 7) % 256                   # the oldest key inside it
         assert torch.allclose(model(input_ids=far).logits[0, -1], base, atol=1e-6)
         assert not torch.allclose(model(input_ids=near).logits[0, -1], base, atol=1e-4)
+
+
+def test_mixers_without_a_context_parallel_form_refuse_it(monkeypatch):
+    """RNN, GRU, linear attention and the gated delta net would treat a rank's shard as the whole sequence: they
+    fail at construction under context parallelism instead (Mamba-2, M2RNN and softmax attention have a form)."""
+    from lm_engine_b200.parallel.manager import ProcessGroupManager
+
+    monkeypatch.setattr(ProcessGroupManager, "is_context_parallel_enabled", staticmethod(lambda: True))
+    for mixer in (RNN_, GRU_, LINATT_, GDN_):
+        with pytest.raises(NotImplementedError, match="context parallelism"):
+            build_model(config_from_dict(_base(1, [dict(mixer)])))
